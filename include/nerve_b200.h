@@ -1,0 +1,178 @@
+/*
+ * nerve_b200 - C ABI of the B200 (sm_100a) backend for the MTP speculative
+ * decode path of compiled NERVE packages.
+ *
+ * The reference project has no FFI or plugin boundary for this path (its only
+ * backend is in-process Vulkan); the entry points below are what a binding for
+ * it would need.  Each one names the reference interface it stands in for, by
+ * file:line inside the reference project.
+ *
+ * Conventions (mirroring the reference's `Result<_, *Error(String)>`): every
+ * function returns 0 on success and a non-zero status otherwise, never aborts;
+ * nerve_b200_last_error() returns the message of the calling thread's most
+ * recent failure.  Handles are opaque, thread-compatible but not thread-safe
+ * (the reference engine is single-threaded: runtime-rs/src/vulkan_stream_circuit/
+ * placed_prompt_stream.rs:9); callbacks run on the calling thread.  All pointers
+ * are plain host pointers unless a parameter says "device".
+ */
+#ifndef NERVE_B200_H
+#define NERVE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NERVE_B200_OK 0
+#define NERVE_B200_ERROR 1
+
+typedef struct nerve_b200_package nerve_b200_package;
+typedef struct nerve_b200_engine nerve_b200_engine;
+
+const char *nerve_b200_last_error(void);
+/* ABI version of this header (bumped on incompatible changes). */
+int32_t nerve_b200_abi_version(void);
+
+/* ---- package mount ---------------------------------------------------------
+ * Replaces VulkanResidentInProcessPlacedModelPackage::from_runtime_model_for_bound_devices
+ * (runtime-rs/src/vulkan_stream_circuit/placed_model_package_loader.rs:54-77,79-404):
+ * parses vulkan_resident_package.json (schema v3), checks artifact_integrity and
+ * per-tensor SHA-256 (runtime-rs/src/tensor_storage.rs:66-136), uploads weights to
+ * device buffers, allocates the paged KV pools and per-stream state.
+ */
+typedef struct nerve_b200_mount_options {
+    int32_t device;           /* CUDA device ordinal */
+    int32_t capacity_tokens;  /* per-stream context (the CLI's --context-size) */
+    int32_t page_tokens;      /* KV page size in tokens (the reference uses min(capacity, 64)) */
+    int32_t max_streams;
+    int32_t max_lanes;        /* largest lane batch per launch: prefill chunk / streams * (k+1) */
+    int32_t verify_level;     /* 0 none, 1 JSON artifacts + tensor hashes, 2 every listed artifact */
+    int32_t tp_rank, tp_size; /* tensor-parallel shard of this process */
+    int32_t extra_pages;      /* physical KV pages beyond max_streams * pages per stream */
+} nerve_b200_mount_options;
+
+int32_t nerve_b200_package_mount(const char *manifest_path_or_dir, const nerve_b200_mount_options *options,
+                                 nerve_b200_package **out_package);
+/* Packages are reference counted (Arc in the reference, placed_prompt_stream.rs:60-68); engines hold a reference. */
+int32_t nerve_b200_package_unmount(nerve_b200_package *package);
+
+typedef struct nerve_b200_package_info {
+    int64_t hidden_size, vocab_size, layer_count, max_context;
+    int32_t has_speculative_decoder;
+    int32_t kv_layer_count;
+    uint64_t weight_bytes;              /* device-resident weight bytes */
+    uint64_t verify_step_weight_bytes;  /* target weight bytes one verify step streams (incl. lm_head) */
+    uint64_t draft_step_weight_bytes;   /* draft head weight bytes one draft step streams (incl. lm_head) */
+    uint64_t kv_bytes_per_token;        /* target KV bytes per context token */
+    int32_t pages_per_stream, physical_pages, page_tokens;
+    uint32_t eos_token_id;              /* first EOS id of config.json, 0xffffffff if none */
+} nerve_b200_package_info;
+int32_t nerve_b200_package_describe(const nerve_b200_package *package, nerve_b200_package_info *out_info);
+
+/* Host-only manifest check (no GPU needed): parse + integrity verification + execution-plan build.
+ * Counterpart of the mount-time validation in runtime-rs/src/package/mount.rs and
+ * resident_package_execution_contract.rs. */
+int32_t nerve_b200_package_validate(const char *manifest_path_or_dir, int32_t verify_level, int64_t *out_op_count,
+                                    int64_t *out_tensor_count);
+
+/* ---- engine ------------------------------------------------------------------
+ * Replaces VulkanResidentInProcessPlacedPromptEngine
+ * (runtime-rs/src/vulkan_stream_circuit/placed_prompt_engine.rs:48-589).
+ */
+int32_t nerve_b200_engine_create(nerve_b200_package *package, nerve_b200_engine **out_engine);
+int32_t nerve_b200_engine_destroy(nerve_b200_engine *engine);
+
+typedef struct nerve_b200_sampler_config {
+    int32_t method; /* 0 = greedy */
+    float temperature, top_p, min_p;
+    int32_t top_k;
+} nerve_b200_sampler_config;
+
+/* add_stream (placed_prompt_engine.rs:48-78) with the stream constructor's arguments
+ * (placed_prompt_stream.rs:48-72): seed, speculative_draft_tokens, sampler config (NULL = package default). */
+int32_t nerve_b200_engine_add_stream(nerve_b200_engine *engine, int64_t stream_id, uint32_t seed,
+                                     int32_t speculative_draft_tokens, const nerve_b200_sampler_config *sampler);
+/* fork_stream (placed_prompt_engine.rs:80-140): the new stream shares the source's state pages copy-on-write. */
+int32_t nerve_b200_engine_fork_stream(nerve_b200_engine *engine, int64_t source_stream_id, int64_t new_stream_id,
+                                      uint32_t seed);
+int32_t nerve_b200_engine_reset_stream(nerve_b200_engine *engine, int64_t stream_id);
+int32_t nerve_b200_engine_remove_stream(nerve_b200_engine *engine, int64_t stream_id);
+int32_t nerve_b200_engine_interrupt_stream(nerve_b200_engine *engine, int64_t stream_id);
+
+/* enqueue_input_event (placed_prompt_engine.rs:256-331): VulkanResidentTokenInputEvent
+ * {id, token_ids, max_public_tokens, stop_token_ids}. */
+int32_t nerve_b200_engine_enqueue(nerve_b200_engine *engine, int64_t stream_id, const char *event_id,
+                                  const uint32_t *token_ids, size_t token_count, size_t max_public_tokens,
+                                  const uint32_t *stop_token_ids, size_t stop_token_count);
+
+/* VulkanResidentTokenOutputEvent {token_id, source_stream_tick, output_index}. */
+typedef void (*nerve_b200_output_callback)(void *user, int64_t stream_id, uint32_t token_id,
+                                           uint64_t source_stream_tick, uint64_t output_index);
+
+/* Field names follow RuntimePromptTimingReport / VulkanSpeculativeDecodeStats
+ * (runtime-rs/src/bin/nerve_runtime/placed_chat.rs:98-121, speculative_decode.rs:21-52). */
+typedef struct nerve_b200_run_report {
+    uint64_t prefill_ns, decode_ns;
+    uint64_t prefill_tokens, generated_tokens;
+    uint64_t activation_count, batch_count, max_batch_width;
+    uint64_t cycle_count, proposed_draft_token_count, accepted_draft_token_count, emitted_token_count;
+    uint64_t draft_time_ns, target_verification_time_ns, draft_catch_up_time_ns;
+    uint64_t kernel_launches, graph_launches, h2d_bytes, d2h_bytes, host_syncs;
+    double verify_ms_sum;    /* device time of all verify steps (CUDA events) */
+    uint64_t verify_steps;
+    uint64_t verify_bytes;   /* algorithmic bytes of all verify steps (weights once + attended KV) */
+} nerve_b200_run_report;
+
+/* run_until_idle_bounded_with_output (placed_prompt_engine.rs:420-589). */
+int32_t nerve_b200_engine_run_until_idle(nerve_b200_engine *engine, nerve_b200_output_callback on_output, void *user,
+                                         nerve_b200_run_report *out_report);
+
+int32_t nerve_b200_engine_stream_tick(const nerve_b200_engine *engine, int64_t stream_id, uint64_t *out_tick);
+
+/* ---- harness / test hooks (no reference counterpart) ---------------------------- */
+/* Teacher-forced full-acceptance mode: draft proposal for output index i is forced to tokens[i]. */
+int32_t nerve_b200_engine_set_teacher_tokens(nerve_b200_engine *engine, int64_t stream_id, const uint32_t *tokens,
+                                             size_t count);
+int32_t nerve_b200_engine_set_prefill_chunk(nerve_b200_engine *engine, int32_t tokens);
+int32_t nerve_b200_engine_set_cycle_logging(nerve_b200_engine *engine, int32_t enabled);
+/* Cycle log rows: {stream_id, start_tick, accepted, committed, emitted_count, width, emitted[8], targets[8]} as u64. */
+int32_t nerve_b200_engine_cycle_log(const nerve_b200_engine *engine, uint64_t *out_rows, size_t max_rows,
+                                    size_t *out_count);
+/* Target forward over `count` tokens at the stream's next ticks without advancing it; f32 logits [count][vocab]
+ * and bf16 final-norm hidden [count][hidden] (either may be NULL). */
+int32_t nerve_b200_debug_target_logits(nerve_b200_engine *engine, int64_t stream_id, const uint32_t *tokens,
+                                       size_t count, float *out_logits, uint16_t *out_hidden);
+
+/* ---- operator-level entry points (device pointers; bf16 activations [lanes][width]) -----------
+ * One per shader family on the path; `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ */
+/* linear_int4_ct.comp.template:80-150 (+ residual add of add_bf16.comp.template when residual != NULL). */
+int32_t nerve_b200_op_linear_int4(const void *x_device, const void *qweight_device, const void *scales_device,
+                                  void *y_device, const void *residual_device, int32_t lanes, int32_t n, int32_t k,
+                                  int32_t group, void *stream);
+/* linear_bf16.comp.template:38-95; to_f32 != 0 gives tied_output_projection_bf16.comp.template:33-91 (f32 * scale). */
+int32_t nerve_b200_op_linear_bf16(const void *x_device, const void *w_device, void *y_device,
+                                  const void *residual_device, int32_t lanes, int32_t n, int32_t k, int32_t to_f32,
+                                  float scale, void *stream);
+/* rms_norm_bf16.comp.template:49-72 */
+int32_t nerve_b200_op_rms_norm(const void *x_device, const void *weight_device, void *y_device, int32_t lanes,
+                               int32_t width, float eps, float weight_offset, void *stream);
+/* quantize_fp8_e4m3.comp.template:41-60 + linear_prequant_fp8_e4m3.comp.template:69-120 */
+int32_t nerve_b200_op_linear_fp8(const void *x_device, const void *w_device, const void *wscale_device,
+                                 void *y_device, const void *residual_device, void *xq_scratch_device,
+                                 void *xscale_scratch_device, int32_t lanes, int32_t n, int32_t k, void *stream);
+/* greedy_sampler_f32.comp.template:52-109: records u32[lanes][4] = {token, logit bits, 0, 0}. */
+int32_t nerve_b200_op_greedy(const void *logits_device, void *records_device, int32_t lanes, int32_t vocab,
+                             void *stream);
+/* speculative_decode.rs:54-105 on host arrays (pure function, no GPU): out = {accepted, committed}. */
+int32_t nerve_b200_verify_prefix(const uint32_t *draft, size_t draft_count, const uint32_t *target,
+                                 size_t target_count, const uint32_t *stop, size_t stop_count, uint32_t *out_counts,
+                                 uint32_t *out_emitted, size_t *out_emitted_count);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NERVE_B200_H */

@@ -1,0 +1,381 @@
+// extern "C" surface declared in include/nerve_b200.h: exception -> status + thread-local message.
+#include <cstring>
+#include <exception>
+#include <string>
+
+#include "../../include/nerve_b200.h"
+#include "engine.hpp"
+
+using namespace nerve;
+
+struct nerve_b200_package {
+    std::shared_ptr<MountedModel> model;
+    int references = 1;
+};
+
+struct nerve_b200_engine {
+    nerve_b200_package *package;
+    std::unique_ptr<Engine> engine;
+};
+
+namespace {
+
+thread_local std::string last_error;
+
+template <typename Body>
+int32_t guarded(Body body) {
+    try {
+        body();
+        return NERVE_B200_OK;
+    } catch (const std::exception &error) {
+        last_error = error.what();
+    } catch (...) {
+        last_error = "unknown failure";
+    }
+    return NERVE_B200_ERROR;
+}
+
+void require(bool condition, const char *message) {
+    if (!condition) throw std::runtime_error(message);
+}
+
+int32_t cuda_status(cudaError_t status, const char *what) {
+    if (status == cudaSuccess) return NERVE_B200_OK;
+    last_error = std::string(what) + ": " + cudaGetErrorString(status);
+    return NERVE_B200_ERROR;
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+const char *nerve_b200_last_error(void) { return last_error.c_str(); }
+int32_t nerve_b200_abi_version(void) { return 1; }
+
+int32_t nerve_b200_package_mount(const char *path, const nerve_b200_mount_options *options, nerve_b200_package **out_package) {
+    return guarded([&] {
+        require(path && options && out_package, "nerve_b200_package_mount: null argument");
+        MountOptions mount;
+        mount.device = options->device;
+        mount.capacity_tokens = options->capacity_tokens;
+        mount.page_tokens = options->page_tokens;
+        mount.max_streams = options->max_streams;
+        mount.max_lanes = options->max_lanes;
+        mount.verify_level = options->verify_level;
+        mount.tp_rank = options->tp_rank;
+        mount.tp_size = options->tp_size > 0 ? options->tp_size : 1;
+        mount.extra_pages = options->extra_pages;
+        require(mount.tp_size == 1, "tensor-parallel mounts are not available in this build");
+        auto package = new nerve_b200_package();
+        try {
+            package->model = MountedModel::mount(path, mount);
+        } catch (...) {
+            delete package;
+            throw;
+        }
+        *out_package = package;
+    });
+}
+
+int32_t nerve_b200_package_unmount(nerve_b200_package *package) {
+    return guarded([&] {
+        require(package != nullptr, "nerve_b200_package_unmount: null package");
+        if (--package->references == 0) delete package;
+    });
+}
+
+int32_t nerve_b200_package_describe(const nerve_b200_package *package, nerve_b200_package_info *out) {
+    return guarded([&] {
+        require(package && out, "nerve_b200_package_describe: null argument");
+        const MountedModel &model = *package->model;
+        const ModelPlan &plan = model.plan();
+        std::memset(out, 0, sizeof(*out));
+        out->hidden_size = plan.hidden;
+        out->vocab_size = plan.vocab;
+        out->layer_count = static_cast<int64_t>(plan.layers.size());
+        out->max_context = plan.max_context;
+        out->has_speculative_decoder = plan.has_draft ? 1 : 0;
+        out->kv_layer_count = model.kv_layer_count();
+        out->weight_bytes = model.weight_bytes();
+        out->verify_step_weight_bytes = model.target_step_weight_bytes();
+        out->draft_step_weight_bytes = model.draft_step_weight_bytes();
+        out->kv_bytes_per_token = model.kv_bytes_per_token();
+        out->pages_per_stream = model.pages_per_stream();
+        out->physical_pages = model.physical_pages();
+        out->page_tokens = model.options().page_tokens;
+        out->eos_token_id = plan.eos_token_ids.empty() ? 0xffffffffu : plan.eos_token_ids[0];
+    });
+}
+
+int32_t nerve_b200_package_validate(const char *path, int32_t verify_level, int64_t *out_op_count, int64_t *out_tensor_count) {
+    return guarded([&] {
+        require(path != nullptr, "nerve_b200_package_validate: null path");
+        VerifyLevel level = verify_level >= 2 ? VerifyLevel::All : (verify_level == 1 ? VerifyLevel::Used : VerifyLevel::None);
+        auto package = HostPackage::open(path, level);
+        if (verify_level >= 1)
+            for (const auto &entry : package->tensors())
+                if (entry.second.dtype != "I64") (void)package->read_tensor(entry.first, true);
+        int64_t ops = 0;
+        const ModelPlan &plan = package->plan();
+        for (const ComponentPlan &layer : plan.layers) ops += static_cast<int64_t>(layer.ops.size());
+        ops += static_cast<int64_t>(plan.draft_adapter.ops.size());
+        for (const ComponentPlan &layer : plan.draft_layers) ops += static_cast<int64_t>(layer.ops.size());
+        if (out_op_count) *out_op_count = ops;
+        if (out_tensor_count) *out_tensor_count = static_cast<int64_t>(package->tensors().size());
+    });
+}
+
+int32_t nerve_b200_engine_create(nerve_b200_package *package, nerve_b200_engine **out_engine) {
+    return guarded([&] {
+        require(package && out_engine, "nerve_b200_engine_create: null argument");
+        auto engine = new nerve_b200_engine();
+        try {
+            engine->engine = std::make_unique<Engine>(package->model);
+        } catch (...) {
+            delete engine;
+            throw;
+        }
+        engine->package = package;
+        package->references++;
+        *out_engine = engine;
+    });
+}
+
+int32_t nerve_b200_engine_destroy(nerve_b200_engine *engine) {
+    return guarded([&] {
+        require(engine != nullptr, "nerve_b200_engine_destroy: null engine");
+        nerve_b200_package *package = engine->package;
+        engine->engine.reset();
+        delete engine;
+        if (--package->references == 0) delete package;
+    });
+}
+
+int32_t nerve_b200_engine_add_stream(nerve_b200_engine *engine, int64_t stream_id, uint32_t seed, int32_t drafts,
+                                     const nerve_b200_sampler_config *sampler) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        SamplerConfig config;
+        if (sampler) {
+            config.method = sampler->method;
+            config.temperature = sampler->temperature;
+            config.top_p = sampler->top_p;
+            config.min_p = sampler->min_p;
+            config.top_k = sampler->top_k;
+        }
+        engine->engine->add_stream(stream_id, seed, drafts, config);
+    });
+}
+
+int32_t nerve_b200_engine_fork_stream(nerve_b200_engine *engine, int64_t source, int64_t destination, uint32_t seed) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        engine->engine->fork_stream(source, destination, seed);
+    });
+}
+
+int32_t nerve_b200_engine_reset_stream(nerve_b200_engine *engine, int64_t stream_id) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        engine->engine->reset_stream(stream_id);
+    });
+}
+
+int32_t nerve_b200_engine_remove_stream(nerve_b200_engine *engine, int64_t stream_id) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        engine->engine->remove_stream(stream_id);
+    });
+}
+
+int32_t nerve_b200_engine_interrupt_stream(nerve_b200_engine *engine, int64_t stream_id) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        engine->engine->interrupt_stream(stream_id);
+    });
+}
+
+int32_t nerve_b200_engine_enqueue(nerve_b200_engine *engine, int64_t stream_id, const char *event_id, const uint32_t *token_ids,
+                                  size_t token_count, size_t max_public_tokens, const uint32_t *stop_token_ids, size_t stop_token_count) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        require(token_ids != nullptr || token_count == 0, "null token_ids");
+        InputEvent event;
+        event.id = event_id ? event_id : "";
+        event.token_ids.assign(token_ids, token_ids + token_count);
+        event.max_public_tokens = max_public_tokens;
+        if (stop_token_count) event.stop_token_ids.assign(stop_token_ids, stop_token_ids + stop_token_count);
+        engine->engine->enqueue(stream_id, event);
+    });
+}
+
+int32_t nerve_b200_engine_run_until_idle(nerve_b200_engine *engine, nerve_b200_output_callback on_output, void *user,
+                                         nerve_b200_run_report *out) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        RunReport report = engine->engine->run_until_idle([&](const OutputEvent &event) {
+            if (on_output) on_output(user, event.stream_id, event.token_id, event.source_stream_tick, event.output_index);
+        });
+        if (out) {
+            std::memset(out, 0, sizeof(*out));
+            out->prefill_ns = report.prefill_ns;
+            out->decode_ns = report.decode_ns;
+            out->prefill_tokens = report.prefill_tokens;
+            out->generated_tokens = report.generated_tokens;
+            out->activation_count = report.activation_count;
+            out->batch_count = report.batch_count;
+            out->max_batch_width = report.max_batch_width;
+            out->cycle_count = report.speculative.cycle_count;
+            out->proposed_draft_token_count = report.speculative.proposed_draft_token_count;
+            out->accepted_draft_token_count = report.speculative.accepted_draft_token_count;
+            out->emitted_token_count = report.speculative.emitted_token_count;
+            out->draft_time_ns = report.speculative.draft_time_ns;
+            out->target_verification_time_ns = report.speculative.target_verification_time_ns;
+            out->draft_catch_up_time_ns = report.speculative.draft_catch_up_time_ns;
+            out->kernel_launches = report.counters.kernel_launches;
+            out->graph_launches = report.counters.graph_launches;
+            out->h2d_bytes = report.counters.h2d_bytes;
+            out->d2h_bytes = report.counters.d2h_bytes;
+            out->host_syncs = report.counters.host_syncs;
+            out->verify_ms_sum = report.verify_ms_sum;
+            out->verify_steps = report.verify_steps;
+            out->verify_bytes = report.verify_bytes;
+        }
+    });
+}
+
+int32_t nerve_b200_engine_stream_tick(const nerve_b200_engine *engine, int64_t stream_id, uint64_t *out_tick) {
+    return guarded([&] {
+        require(engine && out_tick, "null argument");
+        *out_tick = engine->engine->stream_tick(stream_id);
+    });
+}
+
+int32_t nerve_b200_engine_set_teacher_tokens(nerve_b200_engine *engine, int64_t stream_id, const uint32_t *tokens, size_t count) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        engine->engine->set_teacher_tokens(stream_id, std::vector<uint32_t>(tokens, tokens + count));
+    });
+}
+
+int32_t nerve_b200_engine_set_prefill_chunk(nerve_b200_engine *engine, int32_t tokens) {
+    return guarded([&] {
+        require(engine != nullptr && tokens > 0, "prefill chunk must be positive");
+        engine->engine->set_prefill_chunk(tokens);
+    });
+}
+
+int32_t nerve_b200_engine_set_cycle_logging(nerve_b200_engine *engine, int32_t enabled) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        engine->engine->set_cycle_logging(enabled != 0);
+    });
+}
+
+int32_t nerve_b200_engine_cycle_log(const nerve_b200_engine *engine, uint64_t *out_rows, size_t max_rows, size_t *out_count) {
+    return guarded([&] {
+        require(engine && out_count, "null argument");
+        const auto &log = engine->engine->cycle_log();
+        *out_count = log.size();
+        for (size_t i = 0; i < log.size() && i < max_rows; i++) {
+            uint64_t *row = out_rows + i * 22;
+            std::memset(row, 0, 22 * sizeof(uint64_t));
+            row[0] = static_cast<uint64_t>(log[i].stream_id);
+            row[1] = log[i].start_tick;
+            row[2] = log[i].accepted;
+            row[3] = log[i].committed;
+            row[4] = log[i].emitted_token_ids.size();
+            row[5] = log[i].target_token_ids.size();
+            for (size_t j = 0; j < log[i].emitted_token_ids.size() && j < 8; j++) row[6 + j] = log[i].emitted_token_ids[j];
+            for (size_t j = 0; j < log[i].target_token_ids.size() && j < 8; j++) row[14 + j] = log[i].target_token_ids[j];
+        }
+    });
+}
+
+int32_t nerve_b200_debug_target_logits(nerve_b200_engine *engine, int64_t stream_id, const uint32_t *tokens, size_t count,
+                                       float *out_logits, uint16_t *out_hidden) {
+    return guarded([&] {
+        require(engine && tokens, "null argument");
+        engine->engine->debug_target_logits(stream_id, std::vector<uint32_t>(tokens, tokens + count), out_logits, out_hidden);
+    });
+}
+
+// ---- operator-level entry points
+
+int32_t nerve_b200_op_linear_int4(const void *x, const void *qweight, const void *scales, void *y, const void *residual, int32_t lanes,
+                                  int32_t n, int32_t k, int32_t group, void *stream) {
+    return cuda_status(launch_linear_int4(static_cast<const uint16_t *>(x), static_cast<const uint32_t *>(qweight),
+                                          static_cast<const uint16_t *>(scales), static_cast<uint16_t *>(y),
+                                          static_cast<const uint16_t *>(residual), lanes, n, k, group,
+                                          residual ? EPILOGUE_RESIDUAL_ROUNDED : EPILOGUE_BF16, static_cast<cudaStream_t>(stream)),
+                       "nerve_b200_op_linear_int4");
+}
+
+int32_t nerve_b200_op_linear_bf16(const void *x, const void *w, void *y, const void *residual, int32_t lanes, int32_t n, int32_t k,
+                                  int32_t to_f32, float scale, void *stream) {
+    int epilogue = to_f32 ? EPILOGUE_F32_SCALED : (residual ? EPILOGUE_RESIDUAL_ROUNDED : EPILOGUE_BF16);
+    return cuda_status(launch_linear_bf16(static_cast<const uint16_t *>(x), static_cast<const uint16_t *>(w), y,
+                                          static_cast<const uint16_t *>(residual), lanes, n, k, epilogue, scale,
+                                          static_cast<cudaStream_t>(stream)),
+                       "nerve_b200_op_linear_bf16");
+}
+
+int32_t nerve_b200_op_rms_norm(const void *x, const void *weight, void *y, int32_t lanes, int32_t width, float eps, float weight_offset,
+                               void *stream) {
+    return cuda_status(launch_rms_norm(static_cast<const uint16_t *>(x), static_cast<const uint16_t *>(weight), static_cast<uint16_t *>(y),
+                                       lanes, width, eps, weight_offset, static_cast<cudaStream_t>(stream)),
+                       "nerve_b200_op_rms_norm");
+}
+
+int32_t nerve_b200_op_linear_fp8(const void *x, const void *w, const void *wscale, void *y, const void *residual, void *xq_scratch,
+                                 void *xscale_scratch, int32_t lanes, int32_t n, int32_t k, void *stream) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int32_t status = cuda_status(launch_quantize_fp8(static_cast<const uint16_t *>(x), static_cast<uint8_t *>(xq_scratch),
+                                                     static_cast<float *>(xscale_scratch), lanes, k, st),
+                                 "nerve_b200_op_linear_fp8 (quantize)");
+    if (status != NERVE_B200_OK) return status;
+    return cuda_status(launch_linear_fp8(static_cast<const uint8_t *>(xq_scratch), static_cast<const float *>(xscale_scratch),
+                                         static_cast<const uint8_t *>(w), static_cast<const uint16_t *>(wscale), static_cast<uint16_t *>(y),
+                                         static_cast<const uint16_t *>(residual), lanes, n, k,
+                                         residual ? EPILOGUE_RESIDUAL_F32 : EPILOGUE_BF16, st),
+                       "nerve_b200_op_linear_fp8");
+}
+
+int32_t nerve_b200_op_greedy(const void *logits, void *records, int32_t lanes, int32_t vocab, void *stream) {
+    return cuda_status(launch_argmax(static_cast<const float *>(logits), static_cast<uint32_t *>(records), lanes, vocab,
+                                     static_cast<cudaStream_t>(stream)),
+                       "nerve_b200_op_greedy");
+}
+
+int32_t nerve_b200_verify_prefix(const uint32_t *draft, size_t draft_count, const uint32_t *target, size_t target_count,
+                                 const uint32_t *stop, size_t stop_count, uint32_t *out_counts, uint32_t *out_emitted,
+                                 size_t *out_emitted_count) {
+    return guarded([&] {
+        require(out_counts && out_emitted && out_emitted_count, "null output");
+        if (target_count != draft_count + 1)
+            throw std::runtime_error("speculative verification has " + std::to_string(draft_count) + " draft tokens but " +
+                                     std::to_string(target_count) + " target predictions; expected " + std::to_string(draft_count + 1));
+        size_t accepted = 0;
+        while (accepted < draft_count && draft[accepted] == target[accepted]) accepted++;
+        size_t committed = accepted + 1, count = 0;
+        for (size_t i = 0; i < accepted; i++) out_emitted[count++] = draft[i];
+        out_emitted[count++] = target[accepted];
+        for (size_t i = 0; i < count; i++) {
+            bool is_stop = false;
+            for (size_t s = 0; s < stop_count; s++) is_stop |= stop[s] == out_emitted[i];
+            if (is_stop) {
+                if (accepted > i + 1) accepted = i + 1;
+                committed = i + 1;
+                count = i + 1;
+                break;
+            }
+        }
+        out_counts[0] = static_cast<uint32_t>(accepted);
+        out_counts[1] = static_cast<uint32_t>(committed);
+        *out_emitted_count = count;
+    });
+}
+
+}  // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,1106 @@
+#include "engine.hpp"
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <stdexcept>
+
+namespace nerve {
+
+namespace {
+
+[[noreturn]] void fail(const std::string &message) { throw std::runtime_error(message); }
+
+void cuda_check(cudaError_t status, const char *what) {
+    if (status != cudaSuccess) fail(std::string(what) + ": " + cudaGetErrorString(status));
+}
+
+DeviceBuffer device_alloc(size_t bytes, bool zero = true) {
+    DeviceBuffer buffer;
+    buffer.bytes = bytes ? bytes : 16;
+    cuda_check(cudaMalloc(&buffer.ptr, buffer.bytes), "cudaMalloc");
+    if (zero) cuda_check(cudaMemset(buffer.ptr, 0, buffer.bytes), "cudaMemset");
+    return buffer;
+}
+
+uint64_t now_ns() {
+    return static_cast<uint64_t>(
+        std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count());
+}
+
+uint32_t float_bits(float value) {
+    uint32_t bits;
+    std::memcpy(&bits, &value, 4);
+    return bits;
+}
+
+uint16_t host_f32_to_bf16(float value) {
+    uint32_t bits = float_bits(value);
+    uint32_t lsb = (bits >> 16) & 1u;
+    return static_cast<uint16_t>((bits + 0x7fffu + lsb) >> 16);
+}
+
+void collect_component_tensors(const ComponentPlan &plan, std::set<std::string> &names) {
+    for (const OpSpec &op : plan.ops) {
+        for (const WeightRef &weight : op.weights) {
+            names.insert(weight.tensor);
+            if (!weight.scale.empty()) names.insert(weight.scale);
+        }
+        for (const std::string &name : op.norm_weights) names.insert(name);
+    }
+}
+
+}  // namespace
+
+// ============================================================================ MountedModel
+
+std::shared_ptr<MountedModel> MountedModel::mount(const std::string &path, const MountOptions &options) {
+    if (options.page_tokens <= 0 || options.capacity_tokens <= 0 || options.max_streams <= 0 || options.max_lanes <= 0)
+        fail("mount options must be positive");
+    int device_count = 0;
+    cuda_check(cudaGetDeviceCount(&device_count), "cudaGetDeviceCount");
+    if (options.device < 0 || options.device >= device_count)
+        fail("CUDA device " + std::to_string(options.device) + " is not present (" + std::to_string(device_count) + " visible)");
+    cuda_check(cudaSetDevice(options.device), "cudaSetDevice");
+
+    auto model = std::shared_ptr<MountedModel>(new MountedModel());
+    model->options_ = options;
+    VerifyLevel level = options.verify_level >= 2 ? VerifyLevel::All : (options.verify_level == 1 ? VerifyLevel::Used : VerifyLevel::None);
+    model->package_ = HostPackage::open(path, level);
+    const ModelPlan &plan = model->package_->plan();
+    if (plan.max_context > 0 && options.capacity_tokens > plan.max_context)
+        fail("requested context " + std::to_string(options.capacity_tokens) + " exceeds the package's max_context_activations " +
+             std::to_string(plan.max_context));
+
+    model->upload_tensors();
+
+    // paged KV pools: one per attention layer (target layers, then draft layers), all sharing one block table
+    model->pages_per_stream_ = (options.capacity_tokens + options.page_tokens - 1) / options.page_tokens;
+    model->physical_pages_ = model->pages_per_stream_ * options.max_streams + options.extra_pages;
+    auto add_pool = [&](const ComponentPlan &component) {
+        if (!component.has_kv) return;
+        size_t page_bytes = static_cast<size_t>(2) * component.kv_heads * options.page_tokens * component.head_width * 2;
+        model->kv_page_bytes_.push_back(page_bytes);
+        model->kv_shapes_.emplace_back(component.kv_heads, component.head_width);
+        model->kv_pools_.push_back(device_alloc(page_bytes * model->physical_pages_));
+    };
+    for (const ComponentPlan &layer : plan.layers) {
+        add_pool(layer);
+        if (layer.has_kv) model->kv_bytes_per_token_ += static_cast<uint64_t>(2) * layer.kv_heads * layer.head_width * 2;
+    }
+    for (const ComponentPlan &layer : plan.draft_layers) add_pool(layer);
+    model->block_table_ = device_alloc(sizeof(int32_t) * options.max_streams * model->pages_per_stream_);
+    model->build_rope_tables();
+    return model;
+}
+
+MountedModel::~MountedModel() {
+    for (auto &entry : tensors_) cudaFree(entry.second.ptr);
+    for (auto &pool : kv_pools_) cudaFree(pool.ptr);
+    for (auto &entry : rope_tables_) cudaFree(entry.second.ptr);
+    cudaFree(block_table_.ptr);
+}
+
+const void *MountedModel::tensor(const std::string &name) const {
+    auto found = tensors_.find(name);
+    if (found == tensors_.end()) fail("tensor " + name + " is not resident on the device");
+    return found->second.ptr;
+}
+
+void MountedModel::upload_tensors() {
+    const ModelPlan &plan = package_->plan();
+    std::set<std::string> target, draft, shared;
+    for (const ComponentPlan &layer : plan.layers) collect_component_tensors(layer, target);
+    target.insert(plan.output.norm_tensor);
+    target.insert(plan.output.projection_tensor);
+    shared.insert(plan.embedding_tensor);
+    if (plan.has_draft) {
+        collect_component_tensors(plan.draft_adapter, draft);
+        for (const ComponentPlan &layer : plan.draft_layers) collect_component_tensors(layer, draft);
+        draft.insert(plan.draft_output.norm_tensor);
+        draft.insert(plan.draft_output.projection_tensor);
+    }
+    std::set<std::string> all = target;
+    all.insert(draft.begin(), draft.end());
+    all.insert(shared.begin(), shared.end());
+    const bool verify = options_.verify_level >= 1;
+    for (const std::string &name : all) {
+        std::vector<uint8_t> data = package_->read_tensor(name, verify);
+        DeviceBuffer buffer = device_alloc(data.size(), false);
+        cuda_check(cudaMemcpy(buffer.ptr, data.data(), data.size(), cudaMemcpyHostToDevice), "weight upload");
+        tensors_[name] = buffer;
+        weight_bytes_ += data.size();
+    }
+    for (const std::string &name : target) target_step_bytes_ += package_->tensor(name).byte_count();
+    for (const std::string &name : draft) draft_step_bytes_ += package_->tensor(name).byte_count();
+}
+
+void MountedModel::build_rope_tables() {
+    const ModelPlan &plan = package_->plan();
+    rope_positions_ = static_cast<uint32_t>(std::max<int64_t>(plan.max_context, options_.capacity_tokens)) + 64;
+    auto add = [&](const ComponentPlan &component) {
+        for (const OpSpec &op : component.ops)
+            for (const RopeAttrs &rope : op.rope) {
+                auto key = std::make_pair(float_bits(rope.theta), rope.rotary_width);
+                if (rope_tables_.count(key)) continue;
+                // Same f32 sequence as rotary_bf16.comp.template:67-109: inv_freq = pow(theta, -2 f / rotary),
+                // angle = float(position) * inv_freq, cos and sin each rounded to bf16.
+                int half = rope.rotary_width / 2;
+                std::vector<uint32_t> table(static_cast<size_t>(rope_positions_) * half);
+                for (uint32_t position = 0; position < rope_positions_; position++)
+                    for (int f = 0; f < half; f++) {
+                        float inv_freq = powf(rope.theta, -2.0f * static_cast<float>(f) / static_cast<float>(rope.rotary_width));
+                        float angle = static_cast<float>(position) * inv_freq;
+                        uint32_t cosine = host_f32_to_bf16(cosf(angle) * 1.0f), sine = host_f32_to_bf16(sinf(angle) * 1.0f);
+                        table[static_cast<size_t>(position) * half + f] = (sine << 16) | cosine;
+                    }
+                DeviceBuffer buffer = device_alloc(table.size() * sizeof(uint32_t), false);
+                cuda_check(cudaMemcpy(buffer.ptr, table.data(), table.size() * sizeof(uint32_t), cudaMemcpyHostToDevice), "rope table upload");
+                rope_tables_[key] = buffer;
+            }
+    };
+    for (const ComponentPlan &layer : plan.layers) add(layer);
+    for (const ComponentPlan &layer : plan.draft_layers) add(layer);
+}
+
+const uint32_t *MountedModel::rope_table(float theta, int rotary) const {
+    auto found = rope_tables_.find(std::make_pair(float_bits(theta), rotary));
+    if (found == rope_tables_.end()) fail("no RoPE table for this theta/rotary width");
+    return static_cast<const uint32_t *>(found->second.ptr);
+}
+
+KvLayer MountedModel::kv_layer(int index) const {
+    KvLayer layer;
+    layer.pool = static_cast<uint16_t *>(kv_pools_.at(index).ptr);
+    layer.block_table = static_cast<const int32_t *>(block_table_.ptr);
+    layer.pages_per_slot = pages_per_stream_;
+    layer.page_tokens = options_.page_tokens;
+    layer.kv_heads = kv_shapes_[index].first;
+    layer.head_width = kv_shapes_[index].second;
+    layer.capacity = capacity();
+    return layer;
+}
+
+// ============================================================================ Engine
+
+namespace {
+constexpr int MAX_STOP_TOKENS = 8;
+}
+
+Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
+    const MountOptions &options = model_->options();
+    const ModelPlan &plan = model_->plan();
+    cuda_check(cudaSetDevice(options.device), "cudaSetDevice");
+    cuda_check(cudaStreamCreateWithFlags(&cuda_stream_, cudaStreamNonBlocking), "cudaStreamCreate");
+    cuda_check(cudaEventCreate(&event_a_), "cudaEventCreate");
+    cuda_check(cudaEventCreate(&event_b_), "cudaEventCreate");
+    const size_t lanes = options.max_lanes;
+    const size_t frame = static_cast<size_t>(plan.hidden) * 2;
+
+    auto declare = [&](const ComponentPlan &component) {
+        for (const auto &entry : component.signals) {
+            size_t bytes = lanes * entry.second.width * entry.second.element_bytes;
+            auto found = signals_.find(entry.first);
+            if (found == signals_.end()) signals_[entry.first] = DeviceBuffer{nullptr, bytes};
+            else found->second.bytes = std::max(found->second.bytes, bytes);
+        }
+    };
+    for (const ComponentPlan &layer : plan.layers) declare(layer);
+    if (plan.has_draft) {
+        declare(plan.draft_adapter);
+        for (const ComponentPlan &layer : plan.draft_layers) declare(layer);
+    }
+    for (auto &entry : signals_) entry.second = device_alloc(entry.second.bytes);
+
+    frame_a_ = device_alloc(lanes * frame);
+    frame_b_ = device_alloc(lanes * frame);
+    embedding_out_ = device_alloc(lanes * frame);
+    normalized_ = device_alloc(lanes * frame);
+    draft_normalized_ = device_alloc(lanes * frame);
+    draft_hidden_in_ = device_alloc(lanes * frame);
+    logits_ = device_alloc(lanes * static_cast<size_t>(plan.vocab) * sizeof(float));
+    records_ = device_alloc(lanes * 4 * sizeof(uint32_t));
+    lane_tokens_ = device_alloc(lanes * sizeof(uint32_t));
+    lane_positions_ = device_alloc(lanes * sizeof(uint32_t));
+    lane_slots_ = device_alloc(lanes * sizeof(int32_t));
+    pending_hidden_ = device_alloc(static_cast<size_t>(options.max_streams) * frame);
+
+    split_tokens_ = 256;
+    max_splits_ = static_cast<int>((model_->capacity() + split_tokens_ - 1) / split_tokens_);
+    int max_q_heads = 1, max_head_width = 1;
+    auto scan = [&](const ComponentPlan &component) {
+        if (component.has_kv) {
+            max_q_heads = std::max(max_q_heads, component.q_heads);
+            max_head_width = std::max(max_head_width, component.head_width);
+        }
+    };
+    for (const ComponentPlan &layer : plan.layers) scan(layer);
+    for (const ComponentPlan &layer : plan.draft_layers) scan(layer);
+    attention_scratch_ = device_alloc(attention_scratch_bytes(options.max_lanes, max_q_heads, max_head_width, max_splits_));
+
+    // cycle arrays: verify tokens, forced drafts, stop tokens/counts, accept rows, per-step draft tokens, slots
+    cycle_state_ = device_alloc(lanes * 64 * sizeof(uint32_t) + static_cast<size_t>(options.max_streams) * (MAX_STOP_TOKENS + 8) * sizeof(uint32_t) * 4);
+
+    staging_bytes_ = std::max<size_t>(size_t(1) << 20, lanes * 1024 + static_cast<size_t>(options.max_streams) * model_->pages_per_stream() * 8);
+    cuda_check(cudaMallocHost(&staging_, staging_bytes_), "cudaMallocHost");
+    cuda_check(cudaMallocHost(&host_records_, lanes * 64 * sizeof(uint32_t)), "cudaMallocHost");
+
+    for (int slot = options.max_streams - 1; slot >= 0; slot--) free_slots_.push_back(slot);
+    for (int page = model_->physical_pages() - 1; page >= 0; page--) free_pages_.push_back(page);
+    page_refcount_.assign(model_->physical_pages(), 0);
+    block_table_host_.assign(static_cast<size_t>(options.max_streams) * model_->pages_per_stream(), 0);
+}
+
+Engine::~Engine() {
+    cudaStreamSynchronize(cuda_stream_);
+    for (auto &entry : signals_) cudaFree(entry.second.ptr);
+    for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
+                                 &records_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
+                                 &cycle_state_})
+        cudaFree(buffer->ptr);
+    cudaFreeHost(staging_);
+    cudaFreeHost(host_records_);
+    cudaEventDestroy(event_a_);
+    cudaEventDestroy(event_b_);
+    cudaStreamDestroy(cuda_stream_);
+}
+
+void Engine::check(cudaError_t status, const char *what) {
+    counters_.kernel_launches++;
+    cuda_check(status, what);
+}
+
+Engine::Stream &Engine::stream(int64_t id) {
+    auto found = streams_.find(id);
+    if (found == streams_.end()) fail("unknown stream " + std::to_string(id));
+    return found->second;
+}
+const Engine::Stream &Engine::stream(int64_t id) const {
+    auto found = streams_.find(id);
+    if (found == streams_.end()) fail("unknown stream " + std::to_string(id));
+    return found->second;
+}
+
+uint64_t Engine::stream_tick(int64_t id) const { return stream(id).next_tick; }
+
+void Engine::add_stream(int64_t id, uint32_t seed, int speculative_draft_tokens, const SamplerConfig &sampler) {
+    if (streams_.count(id)) fail("stream " + std::to_string(id) + " already exists");
+    if (free_slots_.empty()) fail("no free stream slot (max_streams = " + std::to_string(model_->options().max_streams) + ")");
+    if (sampler.method != 0) fail("only the greedy sampler is mounted in this build");
+    if (speculative_draft_tokens < 0) fail("speculative_draft_tokens must be >= 0");
+    if (speculative_draft_tokens > 0 && !model_->plan().has_draft)
+        fail("resident model package has no mounted speculative decoder");
+    Stream s;
+    s.id = id;
+    s.slot = free_slots_.back();
+    free_slots_.pop_back();
+    s.seed = seed;
+    s.k = speculative_draft_tokens;
+    s.sampler = sampler;
+    s.pages.assign(model_->pages_per_stream(), -1);
+    const size_t frame = static_cast<size_t>(model_->plan().hidden) * 2;
+    cuda_check(cudaMemsetAsync(static_cast<uint8_t *>(pending_hidden_.ptr) + s.slot * frame, 0, frame, cuda_stream_), "pending reset");
+    streams_.emplace(id, std::move(s));
+}
+
+void Engine::release_pages(Stream &s) {
+    for (int32_t &page : s.pages) {
+        if (page >= 0 && --page_refcount_[page] == 0) free_pages_.push_back(page);
+        page = -1;
+    }
+    s.block_table_dirty = true;
+}
+
+void Engine::remove_stream(int64_t id) {
+    Stream &s = stream(id);
+    release_pages(s);
+    free_slots_.push_back(s.slot);
+    streams_.erase(id);
+}
+
+void Engine::reset_stream(int64_t id) {
+    Stream &s = stream(id);
+    release_pages(s);
+    s.next_tick = 0;
+    s.queue.clear();
+    s.active.reset();
+    const size_t frame = static_cast<size_t>(model_->plan().hidden) * 2;
+    cuda_check(cudaMemsetAsync(static_cast<uint8_t *>(pending_hidden_.ptr) + s.slot * frame, 0, frame, cuda_stream_), "pending reset");
+}
+
+void Engine::interrupt_stream(int64_t id) {
+    Stream &s = stream(id);
+    s.queue.clear();
+    s.active.reset();
+}
+
+void Engine::fork_stream(int64_t source, int64_t destination, uint32_t seed) {
+    Stream &src = stream(source);
+    if (src.active) fail("cannot fork stream " + std::to_string(source) + " while an input event is active");
+    add_stream(destination, seed, src.k, src.sampler);
+    Stream &dst = stream(destination);
+    dst.next_tick = src.next_tick;
+    // Every mapped page is shared by reference count, no copies (stream_state.rs:474-496); the first write of
+    // either stream to a shared page replaces it with a private copy (ensure_pages, copy-on-write).
+    for (size_t page = 0; page < src.pages.size(); page++) {
+        int32_t physical = src.pages[page];
+        if (physical < 0) continue;
+        dst.pages[page] = physical;
+        page_refcount_[physical]++;
+    }
+    dst.block_table_dirty = true;
+    const size_t frame = static_cast<size_t>(model_->plan().hidden) * 2;
+    cuda_check(cudaMemcpyAsync(static_cast<uint8_t *>(pending_hidden_.ptr) + dst.slot * frame,
+                               static_cast<uint8_t *>(pending_hidden_.ptr) + src.slot * frame, frame, cudaMemcpyDeviceToDevice, cuda_stream_),
+               "fork pending hidden");
+}
+
+void Engine::enqueue(int64_t id, const InputEvent &event) {
+    Stream &s = stream(id);
+    if (event.token_ids.empty()) fail("input event has no tokens");
+    if (event.stop_token_ids.size() > MAX_STOP_TOKENS) fail("at most 8 stop tokens are supported per event");
+    for (uint32_t token : event.token_ids)
+        if (token >= static_cast<uint32_t>(model_->plan().vocab)) fail("input token id is outside the vocabulary");
+    s.queue.push_back(event);
+}
+
+void Engine::set_teacher_tokens(int64_t id, const std::vector<uint32_t> &tokens) { stream(id).teacher = tokens; }
+
+void Engine::activate_next_event(Stream &s) {
+    if (s.active || s.queue.empty()) return;
+    auto active = std::make_unique<ActiveEvent>();
+    active->input = std::move(s.queue.front());
+    s.queue.pop_front();
+    active->remaining = active->input.max_public_tokens;
+    s.active = std::move(active);
+}
+
+void Engine::ensure_pages(Stream &s, uint64_t last_tick) {
+    // every logical page touched by ticks <= last_tick must be mapped (ring: page index modulo pages per stream);
+    // a page shared with another stream is replaced by a private copy before it is written (copy-on-write)
+    const int page_tokens = model_->options().page_tokens;
+    const int pages = static_cast<int>(s.pages.size());
+    if (last_tick >= model_->rope_positions()) fail("stream tick exceeds the mounted position range");
+    uint64_t first_tick = s.next_tick;
+    for (uint64_t page_index = first_tick / page_tokens; page_index <= last_tick / page_tokens; page_index++) {
+        int logical = static_cast<int>(page_index % pages);
+        int32_t physical = s.pages[logical];
+        if (physical >= 0 && page_refcount_[physical] == 1) continue;
+        if (free_pages_.empty()) fail("KV page pool exhausted");
+        int32_t fresh = free_pages_.back();
+        free_pages_.pop_back();
+        page_refcount_[fresh] = 1;
+        if (physical >= 0) {  // shared page: copy, then drop the shared reference
+            for (int layer = 0; layer < model_->kv_layer_count(); layer++) {
+                size_t bytes = model_->page_bytes(layer);
+                uint8_t *pool = reinterpret_cast<uint8_t *>(model_->kv_layer(layer).pool);
+                cuda_check(cudaMemcpyAsync(pool + fresh * bytes, pool + physical * bytes, bytes, cudaMemcpyDeviceToDevice, cuda_stream_),
+                           "copy-on-write page copy");
+            }
+            page_refcount_[physical]--;
+        }
+        s.pages[logical] = fresh;
+        s.block_table_dirty = true;
+    }
+}
+
+void Engine::sync_block_tables() {
+    const int pages = model_->pages_per_stream();
+    for (auto &entry : streams_) {
+        Stream &s = entry.second;
+        if (!s.block_table_dirty) continue;
+        int32_t *row = block_table_host_.data() + static_cast<size_t>(s.slot) * pages;
+        for (int page = 0; page < pages; page++) row[page] = s.pages[page] >= 0 ? s.pages[page] : 0;
+        upload(model_->block_table_device() + static_cast<size_t>(s.slot) * pages, row, sizeof(int32_t) * pages, "block table upload");
+        s.block_table_dirty = false;
+    }
+}
+
+void *Engine::signal_buffer(const std::string &name) {
+    auto found = signals_.find(name);
+    if (found == signals_.end()) fail("no workspace for signal " + name);
+    return found->second.ptr;
+}
+
+// ---------------------------------------------------------------------------- executor
+
+void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, const std::map<std::string, void *> &bound,
+                           void *output) {
+    cudaStream_t st = cuda_stream_;
+    auto ptr = [&](const std::string &name) -> void * {
+        auto found = bound.find(name);
+        if (found != bound.end()) return found->second;
+        if (name == plan.boundary_output) return output;
+        return signal_buffer(name);
+    };
+    auto u16 = [&](const std::string &name) { return static_cast<uint16_t *>(ptr(name)); };
+    auto width = [&](const std::string &name) { return static_cast<int>(plan.signals.at(name).width); };
+    auto weight = [&](const std::string &name) { return model_->tensor(name); };
+    LaneTable lane_table{static_cast<const uint32_t *>(lane_positions_.ptr), static_cast<const int32_t *>(lane_slots_.ptr)};
+
+    auto consumers = [&](const std::string &signal, size_t after) {
+        int count = 0;
+        for (size_t i = after; i < plan.ops.size(); i++)
+            for (const std::string &input : plan.ops[i].inputs) count += input == signal;
+        if (signal == plan.boundary_output) count += 1;
+        return count;
+    };
+    auto is_int4_single = [&](const OpSpec &op) {
+        return op.kind == OpKind::Linear && op.weights.size() == 1 && op.weights[0].storage == TensorStorage::INT4_CT &&
+               op.weights[0].group == 128;
+    };
+
+    for (size_t index = 0; index < plan.ops.size(); index++) {
+        const OpSpec &op = plan.ops[index];
+        switch (op.kind) {
+        case OpKind::RmsNorm:
+            check(launch_rms_norm(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(op.norm_weights[0])), u16(op.outputs[0]), lanes,
+                                  width(op.inputs[0]), op.eps, op.weight_offset, st),
+                  "rms_norm");
+            break;
+        case OpKind::Linear: {
+            if (is_int4_single(op)) {
+                // gate/up + SiLU*up in one launch
+                if (index + 2 < plan.ops.size() && is_int4_single(plan.ops[index + 1]) && plan.ops[index + 2].kind == OpKind::SiluMultiply &&
+                    plan.ops[index + 1].inputs[0] == op.inputs[0] && plan.ops[index + 2].inputs[0] == op.outputs[0] &&
+                    plan.ops[index + 2].inputs[1] == plan.ops[index + 1].outputs[0] && op.weights[0].n == plan.ops[index + 1].weights[0].n &&
+                    consumers(op.outputs[0], index + 3) == 0 && consumers(plan.ops[index + 1].outputs[0], index + 3) == 0) {
+                    const OpSpec &up = plan.ops[index + 1];
+                    check(launch_linear_int4_silu_pair(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(op.weights[0].tensor)),
+                                                       static_cast<const uint16_t *>(weight(op.weights[0].scale)),
+                                                       static_cast<const uint32_t *>(weight(up.weights[0].tensor)),
+                                                       static_cast<const uint16_t *>(weight(up.weights[0].scale)),
+                                                       u16(plan.ops[index + 2].outputs[0]), lanes, static_cast<int>(op.weights[0].n),
+                                                       static_cast<int>(op.weights[0].k), st),
+                          "linear_int4 gate/up");
+                    index += 2;
+                    break;
+                }
+                // consecutive INT4 linears that share their input (q, k, v) in one launch
+                size_t last = index;
+                while (last + 1 < plan.ops.size() && last - index < 2 && is_int4_single(plan.ops[last + 1]) &&
+                       plan.ops[last + 1].inputs[0] == op.inputs[0] && plan.ops[last + 1].weights[0].k == op.weights[0].k)
+                    last++;
+                // a lone INT4 linear followed by the residual add of its output: fold the add into the epilogue
+                if (last == index && index + 1 < plan.ops.size() && plan.ops[index + 1].kind == OpKind::ResidualAdd &&
+                    consumers(op.outputs[0], index + 2) == 0 &&
+                    (plan.ops[index + 1].inputs[0] == op.outputs[0] || plan.ops[index + 1].inputs[1] == op.outputs[0])) {
+                    const OpSpec &add = plan.ops[index + 1];
+                    const std::string &residual = add.inputs[0] == op.outputs[0] ? add.inputs[1] : add.inputs[0];
+                    check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(op.weights[0].tensor)),
+                                             static_cast<const uint16_t *>(weight(op.weights[0].scale)), u16(add.outputs[0]), u16(residual),
+                                             lanes, static_cast<int>(op.weights[0].n), static_cast<int>(op.weights[0].k), 128,
+                                             EPILOGUE_RESIDUAL_ROUNDED, st),
+                          "linear_int4 + residual");
+                    index += 1;
+                    break;
+                }
+                const uint32_t *qweights[3];
+                const uint16_t *scales[3];
+                uint16_t *outputs[3];
+                int ns[3];
+                int branches = 0;
+                for (size_t i = index; i <= last; i++, branches++) {
+                    qweights[branches] = static_cast<const uint32_t *>(weight(plan.ops[i].weights[0].tensor));
+                    scales[branches] = static_cast<const uint16_t *>(weight(plan.ops[i].weights[0].scale));
+                    outputs[branches] = u16(plan.ops[i].outputs[0]);
+                    ns[branches] = static_cast<int>(plan.ops[i].weights[0].n);
+                }
+                check(launch_linear_int4_multi(u16(op.inputs[0]), branches, qweights, scales, outputs, ns, nullptr, lanes,
+                                               static_cast<int>(op.weights[0].k), EPILOGUE_BF16, st),
+                      "linear_int4");
+                index = last;
+                break;
+            }
+            for (size_t branch = 0; branch < op.weights.size(); branch++) {
+                const WeightRef &w = op.weights[branch];
+                if (w.storage == TensorStorage::BF16) {
+                    check(launch_linear_bf16(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(w.tensor)), ptr(op.outputs[branch]), nullptr,
+                                             lanes, static_cast<int>(w.n), static_cast<int>(w.k), EPILOGUE_BF16, 1.0f, st),
+                          "linear_bf16");
+                } else if (w.storage == TensorStorage::INT4_CT) {
+                    check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(w.tensor)),
+                                             static_cast<const uint16_t *>(weight(w.scale)), u16(op.outputs[branch]), nullptr, lanes,
+                                             static_cast<int>(w.n), static_cast<int>(w.k), w.group, EPILOGUE_BF16, st),
+                          "linear_int4");
+                } else if (w.storage == TensorStorage::FP8_BLOCK) {
+                    if (!op.prequantized_input) fail("FP8 linear " + op.node_id + " without a prequantised input is not mounted");
+                    check(launch_linear_fp8(static_cast<const uint8_t *>(ptr(op.inputs[0])), static_cast<const float *>(ptr(op.inputs[1])),
+                                            static_cast<const uint8_t *>(weight(w.tensor)), static_cast<const uint16_t *>(weight(w.scale)),
+                                            u16(op.outputs[branch]), nullptr, lanes, static_cast<int>(w.n), static_cast<int>(w.k),
+                                            EPILOGUE_BF16, st),
+                          "linear_fp8");
+                }
+            }
+            break;
+        }
+        case OpKind::LinearResidual: {
+            const WeightRef &w = op.weights[0];
+            if (w.storage == TensorStorage::BF16) {
+                check(launch_linear_bf16(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(w.tensor)), ptr(op.outputs[0]),
+                                         u16(op.residual_input), lanes, static_cast<int>(w.n), static_cast<int>(w.k),
+                                         EPILOGUE_RESIDUAL_ROUNDED, 1.0f, st),
+                      "linear_residual_bf16");
+            } else if (w.storage == TensorStorage::FP8_BLOCK) {
+                check(launch_linear_fp8(static_cast<const uint8_t *>(ptr(op.inputs[0])), static_cast<const float *>(ptr(op.inputs[1])),
+                                        static_cast<const uint8_t *>(weight(w.tensor)), static_cast<const uint16_t *>(weight(w.scale)),
+                                        u16(op.outputs[0]), u16(op.residual_input), lanes, static_cast<int>(w.n), static_cast<int>(w.k),
+                                        EPILOGUE_RESIDUAL_F32, st),
+                      "linear_residual_fp8");
+            } else {
+                check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(w.tensor)),
+                                         static_cast<const uint16_t *>(weight(w.scale)), u16(op.outputs[0]), u16(op.residual_input), lanes,
+                                         static_cast<int>(w.n), static_cast<int>(w.k), w.group, EPILOGUE_RESIDUAL_ROUNDED, st),
+                      "linear_residual_int4");
+            }
+            break;
+        }
+        case OpKind::LinearSiluMultiply: {
+            const WeightRef &gate = op.weights[0], &up = op.weights[1];
+            if (gate.storage == TensorStorage::BF16) {
+                check(launch_linear_silu_multiply_bf16(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(gate.tensor)),
+                                                       static_cast<const uint16_t *>(weight(up.tensor)), u16(op.outputs[0]), lanes,
+                                                       static_cast<int>(gate.n), static_cast<int>(gate.k), st),
+                      "linear_silu_multiply_bf16");
+            } else if (gate.storage == TensorStorage::FP8_BLOCK) {
+                check(launch_linear_silu_multiply_fp8(static_cast<const uint8_t *>(ptr(op.inputs[0])), static_cast<const float *>(ptr(op.inputs[1])),
+                                                      static_cast<const uint8_t *>(weight(gate.tensor)),
+                                                      static_cast<const uint16_t *>(weight(gate.scale)),
+                                                      static_cast<const uint8_t *>(weight(up.tensor)),
+                                                      static_cast<const uint16_t *>(weight(up.scale)), u16(op.outputs[0]), lanes,
+                                                      static_cast<int>(gate.n), static_cast<int>(gate.k), st),
+                      "linear_silu_multiply_fp8");
+            } else {
+                check(launch_linear_int4_silu_pair(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(gate.tensor)),
+                                                   static_cast<const uint16_t *>(weight(gate.scale)),
+                                                   static_cast<const uint32_t *>(weight(up.tensor)),
+                                                   static_cast<const uint16_t *>(weight(up.scale)), u16(op.outputs[0]), lanes,
+                                                   static_cast<int>(gate.n), static_cast<int>(gate.k), st),
+                      "linear_silu_multiply_int4");
+            }
+            break;
+        }
+        case OpKind::QuantizeFp8:
+            check(launch_quantize_fp8(u16(op.inputs[0]), static_cast<uint8_t *>(ptr(op.outputs[0])), static_cast<float *>(ptr(op.outputs[1])),
+                                      lanes, width(op.inputs[0]), st),
+                  "quantize_fp8");
+            break;
+        case OpKind::Rope: {
+            const RopeAttrs &rope = op.rope[0];
+            check(launch_rope(u16(op.inputs[0]), u16(op.outputs[0]), model_->rope_table(rope.theta, rope.rotary_width), model_->rope_positions(),
+                              lane_table.position, lanes, rope.heads, rope.head_width, rope.rotary_width, rope.interleaved, nullptr, 0.0f, 0.0f,
+                              st),
+                  "rope");
+            break;
+        }
+        case OpKind::HeadNormRope:
+            for (size_t branch = 0; branch < op.rope.size(); branch++) {
+                const RopeAttrs &rope = op.rope[branch];
+                check(launch_rope(u16(op.inputs[branch]), u16(op.outputs[branch]), model_->rope_table(rope.theta, rope.rotary_width),
+                                  model_->rope_positions(), lane_table.position, lanes, rope.heads, rope.head_width, rope.rotary_width,
+                                  rope.interleaved, static_cast<const uint16_t *>(weight(op.norm_weights[branch])), op.eps, op.weight_offset,
+                                  st),
+                      "head_norm_rope");
+            }
+            break;
+        case OpKind::AppendAttention: {
+            if (kv_index < 0) fail("attention op in a component without KV state");
+            KvLayer kv = model_->kv_layer(kv_index);
+            check(launch_kv_append(u16(op.inputs[1]), u16(op.inputs[2]), kv, lane_table, lanes, st), "kv_append");
+            check(launch_attention(u16(op.inputs[0]), u16(op.outputs[0]), kv, lane_table, lanes, op.q_heads, op.attention_scale, split_tokens_,
+                                   max_splits_, static_cast<float *>(attention_scratch_.ptr), st),
+                  "attention");
+            counters_.kernel_launches++;
+            break;
+        }
+        case OpKind::ResidualAdd:
+            check(launch_add(u16(op.inputs[0]), u16(op.inputs[1]), u16(op.outputs[0]), static_cast<size_t>(lanes) * width(op.inputs[0]), st),
+                  "residual_add");
+            break;
+        case OpKind::SiluMultiply:
+            check(launch_silu_multiply(u16(op.inputs[0]), u16(op.inputs[1]), u16(op.outputs[0]),
+                                       static_cast<size_t>(lanes) * width(op.inputs[0]), st),
+                  "silu_multiply");
+            break;
+        case OpKind::Concat:
+            if (op.inputs.size() != 2) fail("concatenate with other than two inputs is not mounted");
+            check(launch_concat(u16(op.inputs[0]), u16(op.inputs[1]), u16(op.outputs[0]), lanes, width(op.inputs[0]), width(op.inputs[1]), st),
+                  "concatenate");
+            break;
+        case OpKind::MoeTopk:
+            check(launch_moe_topk(u16(op.inputs[0]), static_cast<uint32_t *>(ptr(op.outputs[0])), lanes, op.experts, op.top_k, st), "moe_topk");
+            break;
+        case OpKind::MoeGateUp: {
+            const WeightRef &w = op.weights[0];
+            if (w.storage != TensorStorage::FP8_BLOCK) fail("only FP8 expert weights are mounted");
+            check(launch_moe_gate_up_fp8(u16(op.inputs[0]), static_cast<const uint32_t *>(ptr(op.inputs[1])),
+                                         static_cast<const uint8_t *>(weight(w.tensor)), static_cast<const uint16_t *>(weight(w.scale)),
+                                         u16(op.outputs[0]), lanes, op.moe_hidden, op.moe_inter, op.experts, op.top_k, 0, op.experts, st),
+                  "sparse_moe_gate_up");
+            break;
+        }
+        case OpKind::MoeDown: {
+            const WeightRef &w = op.weights[0];
+            if (w.storage != TensorStorage::FP8_BLOCK) fail("only FP8 expert weights are mounted");
+            check(launch_moe_down_fp8(u16(op.inputs[0]), static_cast<const uint32_t *>(ptr(op.inputs[1])),
+                                      static_cast<const uint8_t *>(weight(w.tensor)), static_cast<const uint16_t *>(weight(w.scale)),
+                                      u16(op.outputs[0]), lanes, op.moe_hidden, op.moe_inter, op.experts, op.top_k, 0, op.experts, st),
+                  "sparse_moe_down");
+            break;
+        }
+        case OpKind::MoeReduce:
+            check(launch_moe_reduce(u16(op.inputs[0]), u16(op.outputs[0]), lanes, op.moe_hidden, op.top_k, op.routed_scale, st), "moe_reduce");
+            break;
+        }
+    }
+}
+
+void Engine::upload(void *device_destination, const void *host_source, size_t bytes, const char *what) {
+    size_t aligned = (bytes + 15) & ~size_t(15);
+    if (staging_used_ + aligned > staging_bytes_) {
+        // arena full: drain the stream so that earlier regions may be reused
+        synchronize("staging drain");
+    }
+    if (aligned > staging_bytes_) fail("upload larger than the pinned staging arena");
+    uint8_t *region = staging_ + staging_used_;
+    staging_used_ += aligned;
+    std::memcpy(region, host_source, bytes);
+    cuda_check(cudaMemcpyAsync(device_destination, region, bytes, cudaMemcpyHostToDevice, cuda_stream_), what);
+    counters_.h2d_bytes += bytes;
+}
+
+void Engine::synchronize(const char *what) {
+    cuda_check(cudaStreamSynchronize(cuda_stream_), what);
+    counters_.host_syncs++;
+    staging_used_ = 0;
+}
+
+void Engine::upload_lanes(const std::vector<uint32_t> &positions, const std::vector<int32_t> &slots) {
+    upload(lane_positions_.ptr, positions.data(), positions.size() * sizeof(uint32_t), "lane positions upload");
+    upload(lane_slots_.ptr, slots.data(), slots.size() * sizeof(int32_t), "lane slots upload");
+}
+
+void Engine::upload_tokens(const uint32_t *tokens, int count) {
+    upload(lane_tokens_.ptr, tokens, static_cast<size_t>(count) * sizeof(uint32_t), "lane tokens upload");
+}
+
+void Engine::target_forward(int lanes, bool want_logits) {
+    const ModelPlan &plan = model_->plan();
+    check(launch_embedding(static_cast<const uint16_t *>(model_->tensor(plan.embedding_tensor)), static_cast<const uint32_t *>(lane_tokens_.ptr),
+                           static_cast<uint16_t *>(frame_a_.ptr), lanes, static_cast<int>(plan.hidden), static_cast<int>(plan.vocab),
+                           plan.embedding_scale, cuda_stream_),
+          "embedding");
+    void *input = frame_a_.ptr, *output = frame_b_.ptr;
+    int kv_index = 0;
+    for (const ComponentPlan &layer : plan.layers) {
+        std::map<std::string, void *> bound{{layer.boundary_inputs.at(0), input}};
+        run_component(layer, layer.has_kv ? kv_index : -1, lanes, bound, output);
+        if (layer.has_kv) kv_index++;
+        std::swap(input, output);
+    }
+    check(launch_rms_norm(static_cast<const uint16_t *>(input), static_cast<const uint16_t *>(model_->tensor(plan.output.norm_tensor)),
+                          static_cast<uint16_t *>(normalized_.ptr), lanes, static_cast<int>(plan.hidden), plan.output.eps,
+                          plan.output.weight_offset, cuda_stream_),
+          "output norm");
+    if (want_logits) {
+        check(launch_linear_bf16(static_cast<const uint16_t *>(normalized_.ptr),
+                                 static_cast<const uint16_t *>(model_->tensor(plan.output.projection_tensor)), logits_.ptr, nullptr, lanes,
+                                 static_cast<int>(plan.vocab), static_cast<int>(plan.hidden), EPILOGUE_F32_SCALED, plan.output.logits_scale,
+                                 cuda_stream_),
+              "output projection");
+        check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, static_cast<int>(plan.vocab),
+                            cuda_stream_),
+              "greedy sampler");
+    }
+}
+
+void Engine::draft_forward(int lanes, const uint16_t *hidden_in, bool want_logits) {
+    const ModelPlan &plan = model_->plan();
+    check(launch_embedding(static_cast<const uint16_t *>(model_->tensor(plan.embedding_tensor)), static_cast<const uint32_t *>(lane_tokens_.ptr),
+                           static_cast<uint16_t *>(embedding_out_.ptr), lanes, static_cast<int>(plan.hidden), static_cast<int>(plan.vocab),
+                           plan.embedding_scale, cuda_stream_),
+          "draft embedding");
+    std::map<std::string, void *> adapter_bound{{plan.adapter_token_signal, embedding_out_.ptr},
+                                                {plan.adapter_hidden_signal, const_cast<uint16_t *>(hidden_in)}};
+    run_component(plan.draft_adapter, -1, lanes, adapter_bound, frame_a_.ptr);
+    void *input = frame_a_.ptr, *output = frame_b_.ptr;
+    int kv_index = 0;
+    for (const ComponentPlan &layer : plan.layers) kv_index += layer.has_kv ? 1 : 0;
+    for (const ComponentPlan &layer : plan.draft_layers) {
+        std::map<std::string, void *> bound{{layer.boundary_inputs.at(0), input}};
+        run_component(layer, layer.has_kv ? kv_index : -1, lanes, bound, output);
+        if (layer.has_kv) kv_index++;
+        std::swap(input, output);
+    }
+    if (!want_logits) return;
+    check(launch_rms_norm(static_cast<const uint16_t *>(input), static_cast<const uint16_t *>(model_->tensor(plan.draft_output.norm_tensor)),
+                          static_cast<uint16_t *>(draft_normalized_.ptr), lanes, static_cast<int>(plan.hidden), plan.draft_output.eps,
+                          plan.draft_output.weight_offset, cuda_stream_),
+          "draft output norm");
+    check(launch_linear_bf16(static_cast<const uint16_t *>(draft_normalized_.ptr),
+                             static_cast<const uint16_t *>(model_->tensor(plan.draft_output.projection_tensor)), logits_.ptr, nullptr, lanes,
+                             static_cast<int>(plan.vocab), static_cast<int>(plan.hidden), EPILOGUE_F32_SCALED, plan.draft_output.logits_scale,
+                             cuda_stream_),
+          "draft output projection");
+    check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, static_cast<int>(plan.vocab),
+                        cuda_stream_),
+          "draft greedy sampler");
+}
+
+// ---------------------------------------------------------------------------- prefill (temporal_prompt.rs:298-478)
+
+void Engine::run_prefill_chunk(Stream &s, const uint32_t *tokens, int count, bool sample_last, uint32_t *sampled) {
+    const ModelPlan &plan = model_->plan();
+    ensure_pages(s, s.next_tick + count - 1);
+    sync_block_tables();
+    std::vector<uint32_t> positions(count);
+    std::vector<int32_t> slots(count, s.slot);
+    for (int i = 0; i < count; i++) positions[i] = static_cast<uint32_t>(s.next_tick + i);
+    upload_lanes(positions, slots);
+    upload_tokens(tokens, count);
+    target_forward(count, false);
+    const size_t frame = static_cast<size_t>(plan.hidden) * 2;
+    uint8_t *pending = static_cast<uint8_t *>(pending_hidden_.ptr) + s.slot * frame;
+    if (plan.has_draft) {
+        // draft state steps for every prompt token: token i pairs with the target hidden of tick i-1
+        // (verification.rs:10-34): lane 0 takes the pending hidden, lane i the normalised frame i-1.
+        check(launch_shift_hidden(static_cast<const uint16_t *>(pending_hidden_.ptr), static_cast<const int32_t *>(lane_slots_.ptr),
+                                  static_cast<const uint16_t *>(normalized_.ptr), static_cast<uint16_t *>(draft_hidden_in_.ptr), 1, count,
+                                  static_cast<int>(plan.hidden), cuda_stream_),
+              "prefill draft hidden");
+        draft_forward(count, static_cast<const uint16_t *>(draft_hidden_in_.ptr), false);
+        cuda_check(cudaMemcpyAsync(pending, static_cast<uint8_t *>(normalized_.ptr) + static_cast<size_t>(count - 1) * frame, frame,
+                                   cudaMemcpyDeviceToDevice, cuda_stream_),
+                   "commit target hidden");
+    }
+    if (sample_last) {
+        check(launch_linear_bf16(static_cast<const uint16_t *>(normalized_.ptr) + static_cast<size_t>(count - 1) * plan.hidden,
+                                 static_cast<const uint16_t *>(model_->tensor(plan.output.projection_tensor)), logits_.ptr, nullptr, 1,
+                                 static_cast<int>(plan.vocab), static_cast<int>(plan.hidden), EPILOGUE_F32_SCALED, plan.output.logits_scale,
+                                 cuda_stream_),
+              "prefill output projection");
+        check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), 1, static_cast<int>(plan.vocab),
+                            cuda_stream_),
+              "prefill sampler");
+        cuda_check(cudaMemcpyAsync(host_records_, records_.ptr, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, cuda_stream_), "record readback");
+        synchronize("prefill synchronize");
+        counters_.d2h_bytes += 16;
+        *sampled = host_records_[0];
+    }
+    s.next_tick += count;
+}
+
+void Engine::emit(Stream &s, uint32_t token, uint64_t tick, const std::function<void(const OutputEvent &)> &on_output, RunReport &report) {
+    ActiveEvent &event = *s.active;
+    OutputEvent output{s.id, token, tick, event.generated.size()};
+    event.generated.push_back(token);
+    event.remaining -= 1;
+    bool closes;
+    if (std::find(event.input.stop_token_ids.begin(), event.input.stop_token_ids.end(), token) != event.input.stop_token_ids.end()) {
+        event.remaining = 0;
+        closes = true;
+    } else {
+        closes = event.remaining == 0;
+    }
+    event.has_feedback = true;
+    event.feedback_token = token;
+    event.feedback_closes = closes;
+    report.generated_tokens++;
+    if (on_output) on_output(output);
+}
+
+// ---------------------------------------------------------------------------- single ticks (placed_prompt_stream.rs:353-420)
+
+void Engine::run_single_ticks(std::vector<Stream *> &batch, const std::function<void(const OutputEvent &)> &on_output, RunReport &report) {
+    const ModelPlan &plan = model_->plan();
+    const int lanes = static_cast<int>(batch.size());
+    std::vector<uint32_t> positions(lanes);
+    std::vector<int32_t> slots(lanes);
+    std::vector<uint32_t> tokens(lanes);
+    bool any_emit = false;
+    for (int i = 0; i < lanes; i++) {
+        Stream &s = *batch[i];
+        ensure_pages(s, s.next_tick);
+        positions[i] = static_cast<uint32_t>(s.next_tick);
+        slots[i] = s.slot;
+        tokens[i] = s.active->feedback_token;
+        any_emit |= !s.active->feedback_closes && s.active->remaining > 0;
+    }
+    sync_block_tables();
+    upload_lanes(positions, slots);
+    upload_tokens(tokens.data(), lanes);
+    target_forward(lanes, any_emit);
+    if (plan.has_draft) {
+        check(launch_gather_rows(static_cast<const uint16_t *>(pending_hidden_.ptr), static_cast<const int32_t *>(lane_slots_.ptr),
+                                 static_cast<uint16_t *>(draft_hidden_in_.ptr), lanes, static_cast<int>(plan.hidden), cuda_stream_),
+              "gather pending hidden");
+        draft_forward(lanes, static_cast<const uint16_t *>(draft_hidden_in_.ptr), false);
+        const size_t frame = static_cast<size_t>(plan.hidden) * 2;
+        for (int i = 0; i < lanes; i++)
+            cuda_check(cudaMemcpyAsync(static_cast<uint8_t *>(pending_hidden_.ptr) + batch[i]->slot * frame,
+                                       static_cast<uint8_t *>(normalized_.ptr) + i * frame, frame, cudaMemcpyDeviceToDevice, cuda_stream_),
+                       "commit target hidden");
+    }
+    if (any_emit) {
+        cuda_check(cudaMemcpyAsync(host_records_, records_.ptr, lanes * 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, cuda_stream_),
+                   "record readback");
+        counters_.d2h_bytes += lanes * 16;
+    }
+    synchronize("tick synchronize");
+    for (int i = 0; i < lanes; i++) {
+        Stream &s = *batch[i];
+        ActiveEvent &event = *s.active;
+        uint64_t tick = s.next_tick;
+        s.next_tick += 1;
+        bool was_closing = event.feedback_closes;
+        bool should_emit = !was_closing && event.remaining > 0;
+        event.has_feedback = false;
+        if (should_emit) emit(s, host_records_[i * 4], tick, on_output, report);
+        if (was_closing || !event.has_feedback) s.active.reset();
+    }
+}
+
+// ---------------------------------------------------------------------------- speculative cycles (feedback_generation.rs:66-194)
+
+void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, const std::function<void(const OutputEvent &)> &on_output,
+                                    RunReport &report) {
+    const ModelPlan &plan = model_->plan();
+    const int streams = static_cast<int>(batch.size());
+    const int width = drafts + 1;
+    const int lanes = streams * width;
+    if (lanes > model_->options().max_lanes) fail("verify batch exceeds max_lanes");
+
+    // device cycle arrays carved out of cycle_state_
+    uint32_t *base = static_cast<uint32_t *>(cycle_state_.ptr);
+    uint32_t *verify_tokens = base;                              // [streams][width]
+    uint32_t *forced = verify_tokens + lanes;                    // [streams][drafts]
+    uint32_t *stop_tokens = forced + lanes;                      // [streams][MAX_STOP]
+    int32_t *stop_counts = reinterpret_cast<int32_t *>(stop_tokens + streams * MAX_STOP_TOKENS);  // [streams]
+    int32_t *stream_slots = stop_counts + streams;               // [streams]
+    uint32_t *accept_rows = reinterpret_cast<uint32_t *>(stream_slots + streams);  // [streams][4 + 2*width]
+    const size_t upload_words = static_cast<size_t>(lanes) * 2 + streams * MAX_STOP_TOKENS + 2 * streams;
+
+    // host staging (pinned): same layout
+    std::vector<uint32_t> staging(upload_words, 0);
+    bool any_forced = false;
+    for (int s = 0; s < streams; s++) {
+        Stream &st = *batch[s];
+        ensure_pages(st, st.next_tick + drafts);
+        staging[static_cast<size_t>(s) * width] = st.active->feedback_token;
+        for (int j = 0; j < drafts; j++) {
+            size_t output_index = st.active->generated.size() + j;
+            uint32_t value = 0xffffffffu;
+            if (output_index < st.teacher.size()) {
+                value = st.teacher[output_index];
+                any_forced = true;
+            }
+            staging[lanes + static_cast<size_t>(s) * drafts + j] = value;
+        }
+        const auto &stops = st.active->input.stop_token_ids;
+        for (size_t t = 0; t < stops.size(); t++) staging[2 * lanes + s * MAX_STOP_TOKENS + t] = stops[t];
+        staging[2 * lanes + streams * MAX_STOP_TOKENS + s] = static_cast<uint32_t>(stops.size());
+        staging[2 * lanes + streams * MAX_STOP_TOKENS + streams + s] = static_cast<uint32_t>(st.slot);
+    }
+    sync_block_tables();
+    upload(base, staging.data(), upload_words * sizeof(uint32_t), "cycle state upload");
+
+    uint64_t t0 = now_ns();
+    // ---- draft loop: `drafts` serial steps over `streams` lanes
+    std::vector<uint32_t> positions(streams);
+    std::vector<int32_t> slots(streams);
+    for (int s = 0; s < streams; s++) slots[s] = batch[s]->slot;
+    for (int j = 0; j < drafts; j++) {
+        for (int s = 0; s < streams; s++) positions[s] = static_cast<uint32_t>(batch[s]->next_tick + j);
+        // lane tables change between steps while earlier launches may still read them: the copies are ordered on the stream
+        upload_lanes(positions, slots);
+        if (j == 0) {
+            std::vector<uint32_t> first_tokens(streams);
+            for (int s = 0; s < streams; s++) first_tokens[s] = batch[s]->active->feedback_token;
+            upload_tokens(first_tokens.data(), streams);
+            check(launch_gather_rows(static_cast<const uint16_t *>(pending_hidden_.ptr), static_cast<const int32_t *>(lane_slots_.ptr),
+                                     static_cast<uint16_t *>(draft_hidden_in_.ptr), streams, static_cast<int>(plan.hidden), cuda_stream_),
+                  "gather pending hidden");
+            draft_forward(streams, static_cast<const uint16_t *>(draft_hidden_in_.ptr), true);
+        } else {
+            draft_forward(streams, static_cast<const uint16_t *>(draft_normalized_.ptr), true);
+        }
+        check(launch_draft_select(static_cast<const uint32_t *>(records_.ptr), any_forced ? forced : nullptr, j, streams, drafts,
+                                  static_cast<uint32_t *>(lane_tokens_.ptr), verify_tokens, cuda_stream_),
+              "draft select");
+    }
+    cuda_check(cudaEventRecord(event_a_, cuda_stream_), "event record");
+
+    // ---- verify: all candidates of all streams in one batch of lanes
+    std::vector<uint32_t> vpositions(lanes);
+    std::vector<int32_t> vslots(lanes);
+    for (int s = 0; s < streams; s++)
+        for (int i = 0; i < width; i++) {
+            vpositions[s * width + i] = static_cast<uint32_t>(batch[s]->next_tick + i);
+            vslots[s * width + i] = batch[s]->slot;
+        }
+    upload_lanes(vpositions, vslots);
+    cuda_check(cudaMemcpyAsync(lane_tokens_.ptr, verify_tokens, lanes * sizeof(uint32_t), cudaMemcpyDeviceToDevice, cuda_stream_),
+               "verify tokens");
+    target_forward(lanes, true);
+    cuda_check(cudaEventRecord(event_b_, cuda_stream_), "event record");
+
+    // ---- accept on the device, then draft catch-up over the same lanes
+    check(launch_shift_hidden(static_cast<const uint16_t *>(pending_hidden_.ptr), stream_slots, static_cast<const uint16_t *>(normalized_.ptr),
+                              static_cast<uint16_t *>(draft_hidden_in_.ptr), streams, width, static_cast<int>(plan.hidden), cuda_stream_),
+          "catch-up hidden");
+    check(launch_accept(verify_tokens, static_cast<const uint32_t *>(records_.ptr), stop_tokens, stop_counts, MAX_STOP_TOKENS, streams, drafts,
+                        accept_rows, static_cast<const uint16_t *>(normalized_.ptr), static_cast<uint16_t *>(pending_hidden_.ptr), stream_slots,
+                        static_cast<int>(plan.hidden), cuda_stream_),
+          "accept");
+    const size_t row_words = 4 + 2 * width;
+    cuda_check(cudaMemcpyAsync(host_records_, accept_rows, streams * row_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, cuda_stream_),
+               "accept readback");
+    counters_.d2h_bytes += streams * row_words * 4;
+    // catch-up: draft state steps for the verify inputs with the target's hidden states; lanes beyond the
+    // committed prefix write slots that the next cycle overwrites before reading (same as the draft loop's own
+    // tentative writes in the reference).
+    draft_forward(lanes, static_cast<const uint16_t *>(draft_hidden_in_.ptr), false);
+    synchronize("cycle synchronize");
+    uint64_t t1 = now_ns();
+    float verify_ms = 0.0f;
+    cuda_check(cudaEventElapsedTime(&verify_ms, event_a_, event_b_), "event elapsed");
+    report.verify_ms_sum += verify_ms;
+    report.verify_steps++;
+    uint64_t kv_bytes = 0;
+    for (int s = 0; s < streams; s++) kv_bytes += model_->kv_bytes_per_token() * std::min<uint64_t>(batch[s]->next_tick + width, model_->capacity());
+    report.verify_bytes += model_->target_step_weight_bytes() + kv_bytes;
+
+    for (int s = 0; s < streams; s++) {
+        Stream &st = *batch[s];
+        const uint32_t *row = host_records_ + s * row_words;
+        uint32_t accepted = row[0], committed = row[1], count = row[2];
+        report.speculative.cycle_count++;
+        report.speculative.proposed_draft_token_count += drafts;
+        report.speculative.accepted_draft_token_count += accepted;
+        report.speculative.emitted_token_count += count;
+        if (log_cycles_) {
+            CycleRecord record;
+            record.stream_id = st.id;
+            record.start_tick = st.next_tick;
+            record.accepted = accepted;
+            record.committed = committed;
+            record.emitted_token_ids.assign(row + 4, row + 4 + count);
+            record.target_token_ids.assign(row + 4 + width, row + 4 + 2 * width);
+            cycle_log_.push_back(std::move(record));
+        }
+        st.active->has_feedback = false;
+        for (uint32_t i = 0; i < count; i++) {
+            uint64_t tick = st.next_tick;
+            st.next_tick += 1;
+            emit(st, row[4 + i], tick, on_output, report);
+        }
+    }
+    report.speculative.target_verification_time_ns += static_cast<uint64_t>(verify_ms * 1e6);
+    report.speculative.draft_time_ns += 0;
+    (void)t0;
+    (void)t1;
+}
+
+// ---------------------------------------------------------------------------- run loop
+
+RunReport Engine::run_until_idle(const std::function<void(const OutputEvent &)> &on_output) {
+    RunReport report;
+    counters_ = ExecCounters{};
+    while (true) {
+        bool any = false;
+        // 1. prefill: streams with external inputs left, one chunk each per round
+        for (auto &entry : streams_) {
+            Stream &s = entry.second;
+            activate_next_event(s);
+            if (!s.active) continue;
+            ActiveEvent &event = *s.active;
+            if (event.next_external >= event.input.token_ids.size()) continue;
+            any = true;
+            uint64_t start = now_ns();
+            size_t left = event.input.token_ids.size() - event.next_external;
+            int budget = std::min(prefill_chunk_, model_->options().max_lanes);
+            int count = static_cast<int>(std::min<size_t>(left, budget));
+            bool last = static_cast<size_t>(count) == left;
+            bool sample = last && event.remaining > 0;
+            uint32_t sampled = 0;
+            uint64_t tick_of_last = s.next_tick + count - 1;
+            run_prefill_chunk(s, event.input.token_ids.data() + event.next_external, count, sample, &sampled);
+            event.next_external += count;
+            report.prefill_tokens += count;
+            report.activation_count++;
+            if (sample) emit(s, sampled, tick_of_last, on_output, report);
+            else if (last) {
+                synchronize("prefill synchronize");
+                s.active.reset();  // no public outputs requested: the event ends with the prompt
+            }
+            report.prefill_ns += now_ns() - start;
+        }
+        // 2. decode: group feedback activations
+        std::map<int, std::vector<Stream *>> speculative;
+        std::vector<Stream *> single;
+        for (auto &entry : streams_) {
+            Stream &s = entry.second;
+            if (!s.active) continue;
+            ActiveEvent &event = *s.active;
+            if (event.next_external < event.input.token_ids.size() || !event.has_feedback) continue;
+            if (s.k > 0 && model_->plan().has_draft && !event.feedback_closes && event.remaining >= 2) {
+                int drafts = static_cast<int>(std::min<size_t>(s.k, event.remaining - 1));
+                speculative[drafts].push_back(&s);
+            } else {
+                single.push_back(&s);
+            }
+        }
+        uint64_t start = now_ns();
+        for (auto &group : speculative) {
+            any = true;
+            // split groups that would exceed the lane budget
+            size_t per_batch = std::max<size_t>(1, model_->options().max_lanes / (group.first + 1));
+            for (size_t offset = 0; offset < group.second.size(); offset += per_batch) {
+                std::vector<Stream *> batch(group.second.begin() + offset,
+                                            group.second.begin() + std::min(group.second.size(), offset + per_batch));
+                run_speculative_cycles(batch, group.first, on_output, report);
+                report.batch_count++;
+                report.activation_count += batch.size();
+                report.max_batch_width = std::max<uint64_t>(report.max_batch_width, batch.size());
+            }
+        }
+        if (!single.empty()) {
+            any = true;
+            size_t per_batch = model_->options().max_lanes;
+            for (size_t offset = 0; offset < single.size(); offset += per_batch) {
+                std::vector<Stream *> batch(single.begin() + offset, single.begin() + std::min(single.size(), offset + per_batch));
+                run_single_ticks(batch, on_output, report);
+                report.batch_count++;
+                report.activation_count += batch.size();
+                report.max_batch_width = std::max<uint64_t>(report.max_batch_width, batch.size());
+            }
+        }
+        report.decode_ns += now_ns() - start;
+        if (!any) break;
+    }
+    report.counters = counters_;
+    return report;
+}
+
+void Engine::debug_target_logits(int64_t id, const std::vector<uint32_t> &tokens, float *logits_out, uint16_t *hidden_out) {
+    Stream &s = stream(id);
+    const ModelPlan &plan = model_->plan();
+    const int lanes = static_cast<int>(tokens.size());
+    if (lanes <= 0 || lanes > model_->options().max_lanes) fail("debug_target_logits: lane count outside [1, max_lanes]");
+    ensure_pages(s, s.next_tick + lanes - 1);
+    sync_block_tables();
+    std::vector<uint32_t> positions(lanes);
+    std::vector<int32_t> slots(lanes, s.slot);
+    for (int i = 0; i < lanes; i++) positions[i] = static_cast<uint32_t>(s.next_tick + i);
+    upload_lanes(positions, slots);
+    upload_tokens(tokens.data(), lanes);
+    target_forward(lanes, true);
+    synchronize("debug synchronize");
+    if (logits_out)
+        cuda_check(cudaMemcpy(logits_out, logits_.ptr, static_cast<size_t>(lanes) * plan.vocab * sizeof(float), cudaMemcpyDeviceToHost), "logits readback");
+    if (hidden_out)
+        cuda_check(cudaMemcpy(hidden_out, normalized_.ptr, static_cast<size_t>(lanes) * plan.hidden * 2, cudaMemcpyDeviceToHost), "hidden readback");
+}
+
+}  // namespace nerve

@@ -1,0 +1,263 @@
+// CUDA backend for the MTP speculative decode step of a compiled NERVE package:
+// device-resident package (weights, paged KV pools, RoPE tables), the executor
+// that runs a component's kernel list over a batch of lanes, and the engine that
+// owns streams and drives prefill / draft / verify / accept / catch-up.
+//
+// Reference behaviour this replaces (paths inside the reference project):
+//   mount      runtime-rs/src/vulkan_stream_circuit/placed_model_package_loader.rs:79-404,431-833
+//   engine     runtime-rs/src/vulkan_stream_circuit/placed_prompt_engine.rs:48-589
+//   stream     runtime-rs/src/vulkan_stream_circuit/placed_prompt_stream.rs:144-193,353-645
+//   events     runtime-rs/src/vulkan_stream_circuit/placed_prompt_event.rs:167-298
+//   cycle      runtime-rs/src/vulkan_stream_circuit/placed_stream_processor/feedback_generation.rs:66-194
+//   draft      runtime-rs/src/vulkan_stream_circuit/resident_package_slices/speculative_decoder_processor.rs:206-488
+//   prefill    runtime-rs/src/vulkan_stream_circuit/placed_stream_processor/temporal_prompt.rs:298-478
+//   verify     runtime-rs/src/vulkan_stream_circuit/placed_stream_processor/temporal_prompt.rs:480-657
+//   acceptance runtime-rs/src/vulkan_stream_circuit/speculative_decode.rs:54-105
+// Handles are thread-compatible, not thread-safe (the reference engine is
+// single-threaded); callbacks run on the calling thread.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <deque>
+#include <functional>
+#include <map>
+#include <memory>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "kernels.cuh"
+#include "package.hpp"
+
+namespace nerve {
+
+struct MountOptions {
+    int device = 0;
+    int capacity_tokens = 1024;  // per-stream context ring (rounded up to whole pages)
+    int page_tokens = 16;
+    int max_streams = 8;
+    int max_lanes = 64;          // largest batch of lanes in one launch (prefill chunk / verify batch)
+    int verify_level = 1;        // 0 none, 1 JSON artifacts + tensor hashes, 2 every listed file
+    int tp_rank = 0, tp_size = 1;
+    int extra_pages = 0;         // physical pages beyond max_streams * pages_per_stream (fork / COW headroom)
+};
+
+struct DeviceBuffer {
+    void *ptr = nullptr;
+    size_t bytes = 0;
+};
+
+struct ExecCounters {
+    uint64_t kernel_launches = 0;
+    uint64_t graph_launches = 0;
+    uint64_t h2d_bytes = 0, d2h_bytes = 0;
+    uint64_t host_syncs = 0;
+};
+
+class MountedModel {
+public:
+    static std::shared_ptr<MountedModel> mount(const std::string &path, const MountOptions &options);
+    ~MountedModel();
+
+    const ModelPlan &plan() const { return package_->plan(); }
+    const HostPackage &package() const { return *package_; }
+    const MountOptions &options() const { return options_; }
+    const void *tensor(const std::string &name) const;
+    uint64_t weight_bytes() const { return weight_bytes_; }
+
+    int pages_per_stream() const { return pages_per_stream_; }
+    int physical_pages() const { return physical_pages_; }
+    uint32_t capacity() const { return static_cast<uint32_t>(pages_per_stream_) * options_.page_tokens; }
+    int kv_layer_count() const { return static_cast<int>(kv_pools_.size()); }
+    KvLayer kv_layer(int index) const;
+    size_t page_bytes(int index) const { return kv_page_bytes_[index]; }
+    int32_t *block_table_device() const { return static_cast<int32_t *>(block_table_.ptr); }
+    const uint32_t *rope_table(float theta, int rotary) const;
+    uint32_t rope_positions() const { return rope_positions_; }
+
+    // algorithmic bytes one verify step reads: every mounted weight byte of the target once
+    // (packed weights + scales + norms) + lm_head, excluding the embedding table and the draft head.
+    uint64_t target_step_weight_bytes() const { return target_step_bytes_; }
+    uint64_t draft_step_weight_bytes() const { return draft_step_bytes_; }
+    uint64_t kv_bytes_per_token() const { return kv_bytes_per_token_; }
+
+private:
+    MountedModel() = default;
+    void upload_tensors();
+    void build_rope_tables();
+
+    std::shared_ptr<HostPackage> package_;
+    MountOptions options_;
+    std::map<std::string, DeviceBuffer> tensors_;
+    uint64_t weight_bytes_ = 0, target_step_bytes_ = 0, draft_step_bytes_ = 0, kv_bytes_per_token_ = 0;
+    std::vector<DeviceBuffer> kv_pools_;
+    std::vector<size_t> kv_page_bytes_;
+    std::vector<std::pair<int, int>> kv_shapes_;  // (kv_heads, head_width) per kv layer
+    DeviceBuffer block_table_;
+    int pages_per_stream_ = 0, physical_pages_ = 0;
+    std::map<std::pair<uint32_t, int>, DeviceBuffer> rope_tables_;  // (theta bits, rotary) -> table
+    uint32_t rope_positions_ = 0;
+};
+
+struct SamplerConfig {
+    int method = 0;  // 0 greedy
+    float temperature = 1.0f, top_p = 1.0f, min_p = 0.0f;
+    int top_k = 1;
+};
+
+struct InputEvent {
+    std::string id;
+    std::vector<uint32_t> token_ids;
+    size_t max_public_tokens = 0;
+    std::vector<uint32_t> stop_token_ids;
+};
+
+struct OutputEvent {
+    int64_t stream_id;
+    uint32_t token_id;
+    uint64_t source_stream_tick;
+    size_t output_index;
+};
+
+struct SpeculativeStats {  // speculative_decode.rs:21-52
+    uint64_t cycle_count = 0, proposed_draft_token_count = 0, accepted_draft_token_count = 0, emitted_token_count = 0;
+    uint64_t draft_time_ns = 0, target_verification_time_ns = 0, draft_catch_up_time_ns = 0;
+};
+
+struct RunReport {
+    uint64_t prefill_ns = 0, decode_ns = 0;
+    uint64_t prefill_tokens = 0, generated_tokens = 0;
+    uint64_t activation_count = 0, batch_count = 0, max_batch_width = 0;
+    SpeculativeStats speculative;
+    ExecCounters counters;
+    double verify_ms_sum = 0.0;  // device time of verify steps (CUDA events)
+    uint64_t verify_steps = 0;
+    uint64_t verify_bytes = 0;   // algorithmic bytes of all verify steps
+};
+
+struct CycleRecord {  // one speculative cycle of one stream, for parity tests
+    int64_t stream_id;
+    uint64_t start_tick;
+    std::vector<uint32_t> draft_token_ids, target_token_ids, emitted_token_ids;
+    uint32_t accepted = 0, committed = 0;
+};
+
+class Engine {
+public:
+    explicit Engine(std::shared_ptr<MountedModel> model);
+    ~Engine();
+
+    void add_stream(int64_t id, uint32_t seed, int speculative_draft_tokens, const SamplerConfig &sampler);
+    void fork_stream(int64_t source, int64_t destination, uint32_t seed);
+    void reset_stream(int64_t id);
+    void remove_stream(int64_t id);
+    void enqueue(int64_t id, const InputEvent &event);
+    void interrupt_stream(int64_t id);
+    // Teacher-forced harness mode: output index i of the stream's next event is forced to tokens[i] as the
+    // draft proposal, so every draft is accepted when tokens are the target's own greedy continuation.
+    void set_teacher_tokens(int64_t id, const std::vector<uint32_t> &tokens);
+    RunReport run_until_idle(const std::function<void(const OutputEvent &)> &on_output);
+
+    uint64_t stream_tick(int64_t id) const;
+    const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
+    void set_cycle_logging(bool enabled) { log_cycles_ = enabled; }
+    void set_use_graphs(bool enabled) { use_graphs_ = enabled; }
+    void set_prefill_chunk(int tokens) { prefill_chunk_ = tokens; }
+
+    // Test hook: run the target over `tokens` at consecutive ticks starting at the stream's next tick WITHOUT
+    // advancing it (state slots are overwritten later, as after a rejected speculation); copies f32 logits out.
+    void debug_target_logits(int64_t id, const std::vector<uint32_t> &tokens, float *logits_out, uint16_t *hidden_out);
+
+    MountedModel &model() { return *model_; }
+
+private:
+    struct ActiveEvent {
+        InputEvent input;
+        size_t next_external = 0;
+        bool has_feedback = false;
+        uint32_t feedback_token = 0;
+        bool feedback_closes = false;
+        size_t remaining = 0;
+        std::vector<uint32_t> generated;
+    };
+    struct Stream {
+        int64_t id = 0;
+        int slot = -1;
+        uint32_t seed = 0;
+        int k = 0;
+        SamplerConfig sampler;
+        uint64_t next_tick = 0;
+        std::deque<InputEvent> queue;
+        std::unique_ptr<ActiveEvent> active;
+        std::vector<int32_t> pages;  // logical page -> physical page (-1 = unmapped)
+        std::vector<uint32_t> teacher;
+        bool block_table_dirty = true;
+    };
+
+    Stream &stream(int64_t id);
+    const Stream &stream(int64_t id) const;
+    void activate_next_event(Stream &s);
+    void ensure_pages(Stream &s, uint64_t last_tick);
+    void release_pages(Stream &s);
+    void sync_block_tables();
+    void emit(Stream &s, uint32_t token, uint64_t tick, const std::function<void(const OutputEvent &)> &on_output,
+              RunReport &report);
+
+    // device work
+    struct LaneBatch {
+        int lanes = 0;
+    };
+    void upload(void *device_destination, const void *host_source, size_t bytes, const char *what);
+    void synchronize(const char *what);
+    void upload_lanes(const std::vector<uint32_t> &positions, const std::vector<int32_t> &slots);
+    void upload_tokens(const uint32_t *tokens, int count);
+    void run_component(const ComponentPlan &plan, int kv_index, int lanes,
+                       const std::map<std::string, void *> &bound, void *output);
+    // embedding -> layers -> final norm (-> logits -> argmax records)
+    void target_forward(int lanes, bool want_logits);
+    void draft_forward(int lanes, const uint16_t *hidden_in, bool want_logits);
+    void run_prefill_chunk(Stream &s, const uint32_t *tokens, int count, bool sample_last, uint32_t *sampled);
+    void run_single_ticks(std::vector<Stream *> &batch, const std::function<void(const OutputEvent &)> &on_output,
+                          RunReport &report);
+    void run_speculative_cycles(std::vector<Stream *> &batch, int draft_count,
+                                const std::function<void(const OutputEvent &)> &on_output, RunReport &report);
+    void check(cudaError_t status, const char *what);
+    void *signal_buffer(const std::string &name);
+
+    std::shared_ptr<MountedModel> model_;
+    std::map<int64_t, Stream> streams_;
+    std::vector<int> free_slots_;
+    std::vector<int32_t> free_pages_;
+    std::vector<int32_t> page_refcount_;
+    std::vector<int32_t> block_table_host_;
+    cudaStream_t cuda_stream_ = nullptr;
+    cudaEvent_t event_a_ = nullptr, event_b_ = nullptr;
+
+    // workspaces
+    std::map<std::string, DeviceBuffer> signals_;
+    DeviceBuffer frame_a_, frame_b_;        // residual stream ping-pong [max_lanes][hidden]
+    DeviceBuffer embedding_out_;            // [max_lanes][hidden]
+    DeviceBuffer normalized_;               // target final-norm output [max_lanes][hidden]
+    DeviceBuffer draft_normalized_;         // draft final-norm output [max_lanes][hidden]
+    DeviceBuffer draft_hidden_in_;          // [max_lanes][hidden]
+    DeviceBuffer logits_;                   // f32 [max_lanes][vocab]
+    DeviceBuffer records_;                  // u32 [max_lanes][4]
+    DeviceBuffer lane_tokens_, lane_positions_, lane_slots_;
+    DeviceBuffer pending_hidden_;           // [max_streams][hidden]
+    DeviceBuffer attention_scratch_;
+    DeviceBuffer cycle_state_;              // device-side per-batch cycle arrays (see engine.cu)
+    // Pinned staging arena for host->device uploads: every upload between two host synchronisations gets its
+    // own region (an asynchronous copy reads the pinned source when it executes, not when it is enqueued).
+    uint8_t *staging_ = nullptr;
+    size_t staging_bytes_ = 0, staging_used_ = 0;
+    uint32_t *host_records_ = nullptr;      // pinned readback area
+    int split_tokens_ = 256, max_splits_ = 1;
+    int prefill_chunk_ = 64;
+    bool use_graphs_ = false, log_cycles_ = false;
+    std::vector<CycleRecord> cycle_log_;
+    ExecCounters counters_;
+    void *current_frame_ = nullptr;         // where the last component wrote its output frame
+};
+
+}  // namespace nerve

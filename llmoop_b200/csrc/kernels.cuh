@@ -1,0 +1,130 @@
+// Launchers for the sm_100a kernels of the MTP decode path.  Activations are
+// bf16 row-major [lane][width]; `lanes` is the batch of (stream, tick) pairs
+// processed in one launch (verify candidates, prefill chunk, or multi-stream
+// decode).  All functions enqueue on `stream` and return the launch status.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nerve {
+
+// Per-launch description of the lanes that touch transient state.
+struct LaneTable {
+    const uint32_t *position;  // [lanes] stream tick (low 32 bits) of each lane
+    const int32_t *slot;       // [lanes] stream slot of each lane (row of block_table)
+};
+
+// Paged KV state of one attention layer.  Page p holds `page_tokens` tokens:
+//   K at kv + p*page_elems + (head*page_tokens + t)*head_width
+//   V at the same offset + page_elems/2
+// A stream's logical token index i lives in page block_table[slot][ (i / page_tokens) % pages_per_slot ].
+struct KvLayer {
+    uint16_t *pool;
+    const int32_t *block_table;  // [slots][pages_per_slot]
+    int pages_per_slot;
+    int page_tokens;
+    int kv_heads;
+    int head_width;
+    uint32_t capacity;  // pages_per_slot * page_tokens (ring length in tokens)
+};
+
+cudaError_t launch_embedding(const uint16_t *table, const uint32_t *tokens, uint16_t *out, int lanes, int width,
+                             int vocab, float scale, cudaStream_t stream);
+
+cudaError_t launch_rms_norm(const uint16_t *x, const uint16_t *weight, uint16_t *y, int lanes, int width, float eps,
+                            float weight_offset, cudaStream_t stream);
+
+cudaError_t launch_add(const uint16_t *a, const uint16_t *b, uint16_t *y, size_t count, cudaStream_t stream);
+cudaError_t launch_silu_multiply(const uint16_t *gate, const uint16_t *up, uint16_t *y, size_t count, cudaStream_t stream);
+cudaError_t launch_concat(const uint16_t *a, const uint16_t *b, uint16_t *y, int lanes, int width_a, int width_b,
+                          cudaStream_t stream);
+
+// RoPE from a host-built table: cos_sin[(position % table_positions) * rotary/2 + f] = {bf16 cos, bf16 sin} packed
+// in one u32 (cos low).  Optional per-head RMSNorm first (norm_weight != nullptr).
+cudaError_t launch_rope(const uint16_t *x, uint16_t *y, const uint32_t *cos_sin, uint32_t table_positions,
+                        const uint32_t *positions, int lanes, int heads, int head_width, int rotary, int interleaved,
+                        const uint16_t *norm_weight, float eps, float weight_offset, cudaStream_t stream);
+
+enum LinearEpilogue {
+    EPILOGUE_BF16 = 0,            // y = bf16(sum)
+    EPILOGUE_RESIDUAL_ROUNDED = 1,  // y = bf16(bf16(sum) + residual)        (BF16 / INT4 packages)
+    EPILOGUE_RESIDUAL_F32 = 2,    // y = bf16(sum + residual)                (FP8 packages)
+    EPILOGUE_F32_SCALED = 3,      // y_f32 = sum * scale                     (logits)
+};
+
+// y[m][n] = sum_k x[m][k] * W[n][k], bf16 weights.
+cudaError_t launch_linear_bf16(const uint16_t *x, const uint16_t *w, void *y, const uint16_t *residual, int lanes,
+                               int n, int k, int epilogue, float scale, cudaStream_t stream);
+// y = bf16( silu_bf16(bf16(x.Wg)) * bf16(x.Wu) )
+cudaError_t launch_linear_silu_multiply_bf16(const uint16_t *x, const uint16_t *wg, const uint16_t *wu, uint16_t *y,
+                                             int lanes, int n, int k, cudaStream_t stream);
+
+// INT4 compressed-tensors weight-only linear: qweight [n][k/8] u32, scales bf16 [n][k/group].
+cudaError_t launch_linear_int4(const uint16_t *x, const uint32_t *qweight, const uint16_t *scales, uint16_t *y,
+                               const uint16_t *residual, int lanes, int n, int k, int group, int epilogue,
+                               cudaStream_t stream);
+
+// FP8 W8A8: xq e4m3 [lanes][k], xscale f32 [lanes][k/128]; w e4m3 [n][k]; wscale bf16 [ceil(n/128)][k/128].
+cudaError_t launch_quantize_fp8(const uint16_t *x, uint8_t *q, float *scales, int lanes, int k, cudaStream_t stream);
+cudaError_t launch_linear_fp8(const uint8_t *xq, const float *xscale, const uint8_t *w, const uint16_t *wscale,
+                              uint16_t *y, const uint16_t *residual, int lanes, int n, int k, int epilogue,
+                              cudaStream_t stream);
+cudaError_t launch_linear_silu_multiply_fp8(const uint8_t *xq, const float *xscale, const uint8_t *wg,
+                                            const uint16_t *wg_scale, const uint8_t *wu, const uint16_t *wu_scale,
+                                            uint16_t *y, int lanes, int n, int k, cudaStream_t stream);
+
+// MoE (softmax over the selected experts, routes sorted by expert id).
+cudaError_t launch_moe_topk(const uint16_t *router_logits, uint32_t *routes, int lanes, int experts, int top_k,
+                            cudaStream_t stream);
+cudaError_t launch_moe_gate_up_fp8(const uint16_t *hidden, const uint32_t *routes, const uint8_t *w,
+                                   const uint16_t *wscale, uint16_t *intermediates, int lanes, int hidden_size,
+                                   int inter, int experts, int top_k, int expert_start, int expert_count,
+                                   cudaStream_t stream);
+cudaError_t launch_moe_down_fp8(const uint16_t *intermediates, const uint32_t *routes, const uint8_t *w,
+                                const uint16_t *wscale, uint16_t *outputs, int lanes, int hidden_size, int inter,
+                                int experts, int top_k, int expert_start, int expert_count, cudaStream_t stream);
+cudaError_t launch_moe_reduce(const uint16_t *outputs, uint16_t *y, int lanes, int hidden_size, int top_k,
+                              float routed_scale, cudaStream_t stream);
+
+// Append K,V of every lane at its position, then causal GQA attention over the
+// stream's pages: split over the context, partials merged by a second kernel.
+// scratch holds [lanes][q_heads][splits][head_width + 2] f32.
+size_t attention_scratch_bytes(int lanes, int q_heads, int head_width, int max_splits);
+cudaError_t launch_kv_append(const uint16_t *k, const uint16_t *v, const KvLayer &kv, const LaneTable &lanes_meta,
+                             int lanes, cudaStream_t stream);
+cudaError_t launch_attention(const uint16_t *q, uint16_t *out, const KvLayer &kv, const LaneTable &lanes_meta,
+                             int lanes, int q_heads, float scale, int split_tokens, int max_splits, float *scratch,
+                             cudaStream_t stream);
+
+// INT4 multi-branch forms (one launch for q/k/v; gate/up with the SiLU*up epilogue).
+cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint32_t *const *qweights,
+                                     const uint16_t *const *scales, uint16_t *const *ys, const int *ns,
+                                     const uint16_t *residual, int lanes, int k, int epilogue, cudaStream_t stream);
+cudaError_t launch_linear_int4_silu_pair(const uint16_t *x, const uint32_t *gate_q, const uint16_t *gate_s,
+                                         const uint32_t *up_q, const uint16_t *up_s, uint16_t *y, int lanes, int n,
+                                         int k, cudaStream_t stream);
+
+// ---- glue of the speculative cycle (all tiny) ----
+// dst[i] = src[index[i]] for rows of `width` bf16.
+cudaError_t launch_gather_rows(const uint16_t *src, const int32_t *index, uint16_t *dst, int rows, int width,
+                               cudaStream_t stream);
+// Hidden inputs of the draft catch-up: lane (s, 0) takes pending[slot[s]], lane (s, i>0) takes normalized (s, i-1).
+cudaError_t launch_shift_hidden(const uint16_t *pending, const int32_t *slots, const uint16_t *normalized,
+                                uint16_t *dst, int streams, int lanes_per_stream, int hidden, cudaStream_t stream);
+// After draft step `step`: token = forced[s][step] unless it is 0xffffffff, else the sampled record; written to
+// next_tokens[s] and verify_tokens[s][step + 1].
+cudaError_t launch_draft_select(const uint32_t *records, const uint32_t *forced, int step, int streams, int drafts,
+                                uint32_t *next_tokens, uint32_t *verify_tokens, cudaStream_t stream);
+// Longest-matching-prefix acceptance + stop truncation (speculative_decode.rs:54-105) per stream, then
+// pending[slot[s]] = normalized lane (s, committed-1).  out row = {accepted, committed, emitted_count, 0,
+// emitted[drafts+1], targets[drafts+1]}.
+cudaError_t launch_accept(const uint32_t *verify_tokens, const uint32_t *target_records, const uint32_t *stop_tokens,
+                          const int32_t *stop_counts, int max_stop, int streams, int drafts, uint32_t *out,
+                          const uint16_t *normalized, uint16_t *pending, const int32_t *slots, int hidden,
+                          cudaStream_t stream);
+
+// Greedy arg-max (ties -> lowest id); record = {token, logit bits, 0, 0} per lane.
+cudaError_t launch_argmax(const float *logits, uint32_t *records, int lanes, int vocab, cudaStream_t stream);
+
+}  // namespace nerve

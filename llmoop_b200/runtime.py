@@ -1,0 +1,256 @@
+"""ctypes mirror of include/nerve_b200.h.
+
+Names follow the reference engine's API (add_stream, fork_stream,
+enqueue_input_event, run_until_idle ...: runtime-rs/src/vulkan_stream_circuit/
+placed_prompt_engine.rs:48-589) so that tests read like the reference's own.
+Every failure raises NerveError with the library's message; a missing library
+is an error, never a fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libnerve_b200.so"
+
+
+class NerveError(RuntimeError):
+    pass
+
+
+class _MountOptions(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_int32) for name in (
+        "device", "capacity_tokens", "page_tokens", "max_streams", "max_lanes", "verify_level", "tp_rank", "tp_size",
+        "extra_pages")]
+
+
+class _PackageInfo(ctypes.Structure):
+    _fields_ = [
+        ("hidden_size", ctypes.c_int64), ("vocab_size", ctypes.c_int64), ("layer_count", ctypes.c_int64),
+        ("max_context", ctypes.c_int64), ("has_speculative_decoder", ctypes.c_int32), ("kv_layer_count", ctypes.c_int32),
+        ("weight_bytes", ctypes.c_uint64), ("verify_step_weight_bytes", ctypes.c_uint64),
+        ("draft_step_weight_bytes", ctypes.c_uint64), ("kv_bytes_per_token", ctypes.c_uint64),
+        ("pages_per_stream", ctypes.c_int32), ("physical_pages", ctypes.c_int32), ("page_tokens", ctypes.c_int32),
+        ("eos_token_id", ctypes.c_uint32),
+    ]
+
+
+class _SamplerConfig(ctypes.Structure):
+    _fields_ = [("method", ctypes.c_int32), ("temperature", ctypes.c_float), ("top_p", ctypes.c_float),
+                ("min_p", ctypes.c_float), ("top_k", ctypes.c_int32)]
+
+
+_REPORT_U64 = (
+    "prefill_ns", "decode_ns", "prefill_tokens", "generated_tokens", "activation_count", "batch_count",
+    "max_batch_width", "cycle_count", "proposed_draft_token_count", "accepted_draft_token_count",
+    "emitted_token_count", "draft_time_ns", "target_verification_time_ns", "draft_catch_up_time_ns",
+    "kernel_launches", "graph_launches", "h2d_bytes", "d2h_bytes", "host_syncs")
+
+
+class _RunReport(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_uint64) for name in _REPORT_U64] + [
+        ("verify_ms_sum", ctypes.c_double), ("verify_steps", ctypes.c_uint64), ("verify_bytes", ctypes.c_uint64)]
+
+
+_OUTPUT_CALLBACK = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int64, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_uint64)
+
+EXPORTED_SYMBOLS = (
+    "nerve_b200_last_error", "nerve_b200_abi_version", "nerve_b200_package_mount", "nerve_b200_package_unmount",
+    "nerve_b200_package_describe", "nerve_b200_package_validate", "nerve_b200_engine_create",
+    "nerve_b200_engine_destroy", "nerve_b200_engine_add_stream", "nerve_b200_engine_fork_stream",
+    "nerve_b200_engine_reset_stream", "nerve_b200_engine_remove_stream", "nerve_b200_engine_interrupt_stream",
+    "nerve_b200_engine_enqueue", "nerve_b200_engine_run_until_idle", "nerve_b200_engine_stream_tick",
+    "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
+    "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
+    "nerve_b200_op_linear_int4", "nerve_b200_op_linear_bf16", "nerve_b200_op_rms_norm", "nerve_b200_op_linear_fp8",
+    "nerve_b200_op_greedy", "nerve_b200_verify_prefix",
+)
+
+_library = None
+
+
+def library() -> ctypes.CDLL:
+    """Loads libnerve_b200.so (built in-tree by llmoop_b200.build); raises if it is absent."""
+    global _library
+    if _library is None:
+        if not LIB_PATH.exists():
+            raise NerveError(f"{LIB_PATH} is missing: run `python -m llmoop_b200.build` (there is no CPU fallback)")
+        lib = ctypes.CDLL(str(LIB_PATH))
+        lib.nerve_b200_last_error.restype = ctypes.c_char_p
+        for name in EXPORTED_SYMBOLS:
+            if name != "nerve_b200_last_error":
+                getattr(lib, name).restype = ctypes.c_int32
+        _library = lib
+    return _library
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise NerveError(library().nerve_b200_last_error().decode("utf-8", "replace"))
+
+
+def validate_package(path, verify_level: int = 2):
+    """Host-only parse + integrity check + plan build.  Returns (op_count, tensor_count)."""
+    ops, tensors = ctypes.c_int64(0), ctypes.c_int64(0)
+    _check(library().nerve_b200_package_validate(str(path).encode(), verify_level, ctypes.byref(ops), ctypes.byref(tensors)))
+    return ops.value, tensors.value
+
+
+def verify_prefix(draft, target, stop=()):
+    """speculative_decode.rs:54-105 -> (accepted, committed, emitted)."""
+    draft_a = (ctypes.c_uint32 * max(1, len(draft)))(*draft)
+    target_a = (ctypes.c_uint32 * max(1, len(target)))(*target)
+    stop_a = (ctypes.c_uint32 * max(1, len(stop)))(*stop)
+    counts = (ctypes.c_uint32 * 2)()
+    emitted = (ctypes.c_uint32 * (len(draft) + 2))()
+    count = ctypes.c_size_t(0)
+    _check(library().nerve_b200_verify_prefix(draft_a, ctypes.c_size_t(len(draft)), target_a, ctypes.c_size_t(len(target)),
+                                              stop_a, ctypes.c_size_t(len(stop)), counts, emitted, ctypes.byref(count)))
+    return counts[0], counts[1], list(emitted[:count.value])
+
+
+@dataclass
+class RunReport:
+    values: dict
+
+    def __getattr__(self, name):
+        try:
+            return self.values[name]
+        except KeyError as error:
+            raise AttributeError(name) from error
+
+
+class Package:
+    """A compiled package resident on one GPU."""
+
+    def __init__(self, path, *, device=0, capacity_tokens=1024, page_tokens=16, max_streams=8, max_lanes=64,
+                 verify_level=1, tp_rank=0, tp_size=1, extra_pages=0):
+        options = _MountOptions(device, capacity_tokens, page_tokens, max_streams, max_lanes, verify_level, tp_rank,
+                                tp_size, extra_pages)
+        self._handle = ctypes.c_void_p()
+        _check(library().nerve_b200_package_mount(str(path).encode(), ctypes.byref(options), ctypes.byref(self._handle)))
+        info = _PackageInfo()
+        _check(library().nerve_b200_package_describe(self._handle, ctypes.byref(info)))
+        self.info = {name: getattr(info, name) for name, _ in _PackageInfo._fields_}
+
+    def unmount(self):
+        if self._handle:
+            _check(library().nerve_b200_package_unmount(self._handle))
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.unmount()
+        except Exception:
+            pass
+
+
+class Engine:
+    def __init__(self, package: Package):
+        self.package = package
+        self._handle = ctypes.c_void_p()
+        _check(library().nerve_b200_engine_create(package._handle, ctypes.byref(self._handle)))
+
+    def close(self):
+        if self._handle:
+            _check(library().nerve_b200_engine_destroy(self._handle))
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def add_stream(self, stream_id: int, *, seed: int = 0, speculative_draft_tokens: int = 0, sampler=None):
+        config = None
+        if sampler is not None:
+            config = ctypes.byref(_SamplerConfig(sampler.get("method", 0), sampler.get("temperature", 1.0),
+                                                 sampler.get("top_p", 1.0), sampler.get("min_p", 0.0), sampler.get("top_k", 1)))
+        _check(library().nerve_b200_engine_add_stream(self._handle, ctypes.c_int64(stream_id), ctypes.c_uint32(seed),
+                                                      speculative_draft_tokens, config))
+
+    def fork_stream(self, source: int, destination: int, *, seed: int = 0):
+        _check(library().nerve_b200_engine_fork_stream(self._handle, ctypes.c_int64(source), ctypes.c_int64(destination),
+                                                       ctypes.c_uint32(seed)))
+
+    def reset_stream_transient_state(self, stream_id: int):
+        _check(library().nerve_b200_engine_reset_stream(self._handle, ctypes.c_int64(stream_id)))
+
+    def remove_stream(self, stream_id: int):
+        _check(library().nerve_b200_engine_remove_stream(self._handle, ctypes.c_int64(stream_id)))
+
+    def interrupt_stream(self, stream_id: int):
+        _check(library().nerve_b200_engine_interrupt_stream(self._handle, ctypes.c_int64(stream_id)))
+
+    def enqueue_input_event(self, stream_id: int, token_ids, max_public_tokens: int, stop_token_ids=(), event_id="event"):
+        tokens = (ctypes.c_uint32 * max(1, len(token_ids)))(*[int(t) for t in token_ids])
+        stops = (ctypes.c_uint32 * max(1, len(stop_token_ids)))(*[int(t) for t in stop_token_ids])
+        _check(library().nerve_b200_engine_enqueue(self._handle, ctypes.c_int64(stream_id), event_id.encode(), tokens,
+                                                   ctypes.c_size_t(len(token_ids)), ctypes.c_size_t(max_public_tokens), stops,
+                                                   ctypes.c_size_t(len(stop_token_ids))))
+
+    def run_until_idle(self, on_output=None):
+        """Returns (outputs, report): outputs is a list of (stream_id, token_id, source_stream_tick, output_index)."""
+        outputs = []
+
+        def trampoline(_user, stream_id, token_id, tick, index):
+            outputs.append((stream_id, token_id, tick, index))
+            if on_output is not None:
+                on_output(stream_id, token_id, tick, index)
+
+        callback = _OUTPUT_CALLBACK(trampoline)
+        report = _RunReport()
+        _check(library().nerve_b200_engine_run_until_idle(self._handle, callback, None, ctypes.byref(report)))
+        values = {name: getattr(report, name) for name, _ in _RunReport._fields_}
+        return outputs, RunReport(values)
+
+    def submit_input_event_until_idle(self, stream_id: int, token_ids, max_public_tokens: int, stop_token_ids=()):
+        self.enqueue_input_event(stream_id, token_ids, max_public_tokens, stop_token_ids)
+        outputs, report = self.run_until_idle()
+        return [token for sid, token, _, _ in outputs if sid == stream_id], report
+
+    def stream_tick(self, stream_id: int) -> int:
+        tick = ctypes.c_uint64(0)
+        _check(library().nerve_b200_engine_stream_tick(self._handle, ctypes.c_int64(stream_id), ctypes.byref(tick)))
+        return tick.value
+
+    def set_teacher_tokens(self, stream_id: int, tokens):
+        array = (ctypes.c_uint32 * max(1, len(tokens)))(*[int(t) for t in tokens])
+        _check(library().nerve_b200_engine_set_teacher_tokens(self._handle, ctypes.c_int64(stream_id), array,
+                                                              ctypes.c_size_t(len(tokens))))
+
+    def set_prefill_chunk(self, tokens: int):
+        _check(library().nerve_b200_engine_set_prefill_chunk(self._handle, tokens))
+
+    def set_cycle_logging(self, enabled: bool):
+        _check(library().nerve_b200_engine_set_cycle_logging(self._handle, int(enabled)))
+
+    def cycle_log(self):
+        count = ctypes.c_size_t(0)
+        _check(library().nerve_b200_engine_cycle_log(self._handle, None, ctypes.c_size_t(0), ctypes.byref(count)))
+        rows = (ctypes.c_uint64 * (22 * max(1, count.value)))()
+        _check(library().nerve_b200_engine_cycle_log(self._handle, rows, ctypes.c_size_t(count.value), ctypes.byref(count)))
+        out = []
+        for i in range(count.value):
+            row = rows[i * 22:(i + 1) * 22]
+            out.append({
+                "stream_id": row[0], "start_tick": row[1], "accepted": row[2], "committed": row[3],
+                "emitted": list(row[6:6 + row[4]]), "target_token_ids": list(row[14:14 + row[5]]),
+            })
+        return out
+
+    def debug_target_logits(self, stream_id: int, tokens):
+        import numpy as np
+
+        info = self.package.info
+        array = (ctypes.c_uint32 * len(tokens))(*[int(t) for t in tokens])
+        logits = np.empty((len(tokens), info["vocab_size"]), dtype=np.float32)
+        hidden = np.empty((len(tokens), info["hidden_size"]), dtype=np.uint16)
+        _check(library().nerve_b200_debug_target_logits(
+            self._handle, ctypes.c_int64(stream_id), array, ctypes.c_size_t(len(tokens)),
+            logits.ctypes.data_as(ctypes.POINTER(ctypes.c_float)), hidden.ctypes.data_as(ctypes.POINTER(ctypes.c_uint16))))
+        return logits, hidden

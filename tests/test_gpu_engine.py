@@ -1,0 +1,212 @@
+"""Parity of the CUDA engine (through the C ABI) against the CPU oracle on the
+golden packages: greedy token ids, per-cycle acceptance counts and logits.
+
+Tolerances (stated by the task's north star): token ids and acceptance counts
+exact, a divergence being allowed only where the oracle's top-2 logit gap is
+below 1e-3; logits max-abs <= 2e-2 and mean-abs <= 2e-3.
+"""
+
+import numpy as np
+import pytest
+
+from conftest import GOLDEN, PACKAGES
+
+pytestmark = pytest.mark.gpu
+
+GAP_RULE = 1e-3
+LOGITS_MAX_ABS = 2e-2
+LOGITS_MEAN_ABS = 2e-3
+
+
+def _oracle(name):
+    from oracle.nerve_oracle import Oracle, OraclePackage
+
+    package = OraclePackage(GOLDEN / name)
+    return package, Oracle(package)
+
+
+def _prompt(vocab, count, seed=0):
+    return [int(t) for t in np.random.default_rng(seed).integers(0, vocab, size=count)]
+
+
+def _assert_tokens_match(got, expected, oracle_logits, oracle):
+    """Exact match, except that the sequences may part at a position where the oracle's top-2 gap < 1e-3
+    (after which they are different continuations and cannot be compared)."""
+    for index, (a, b) in enumerate(zip(got, expected)):
+        if a != b:
+            gap = oracle.top2_gap(oracle_logits[index])
+            assert gap < GAP_RULE, f"token {index}: cuda {a} != oracle {b} with top-2 gap {gap}"
+            return index
+    assert len(got) == len(expected)
+    return None
+
+
+@pytest.mark.parametrize("name", PACKAGES)
+@pytest.mark.parametrize("drafts", [0, 1, 3])
+def test_greedy_generation_matches_oracle(name, drafts):
+    import llmoop_b200 as nb
+    from oracle.nerve_oracle import OracleStream
+
+    opkg, oracle = _oracle(name)
+    prompt = _prompt(opkg.vocab, 16)
+    ostream = OracleStream(opkg, 128)
+    expected = oracle.generate(ostream, prompt, 32, drafts, collect_logits=True)
+
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=2, max_lanes=64, verify_level=2)
+    engine = nb.Engine(package)
+    engine.set_cycle_logging(True)
+    engine.add_stream(7, seed=0, speculative_draft_tokens=drafts)
+    tokens, report = engine.submit_input_event_until_idle(7, prompt, 32)
+    diverged = _assert_tokens_match(tokens, expected["tokens"], expected["logits"], oracle)
+    if diverged is None:
+        assert engine.stream_tick(7) == ostream.next_tick == len(prompt) + 32  # P + N ticks
+        cycles = engine.cycle_log()
+        assert [c["accepted"] for c in cycles] == [c["accepted"] for c in expected["cycles"]]
+        assert [c["committed"] for c in cycles] == [c["committed"] for c in expected["cycles"]]
+        assert [c["emitted"] for c in cycles] == [c["emitted"] for c in expected["cycles"]]
+        assert report.generated_tokens == 32
+        if drafts:
+            assert report.cycle_count == len(expected["cycles"])
+            assert report.kernel_launches > 0
+    engine.close()
+    package.unmount()
+
+
+@pytest.mark.parametrize("name", PACKAGES)
+def test_target_logits_within_tolerance(name):
+    import llmoop_b200 as nb
+    from oracle.nerve_oracle import OracleStream
+
+    opkg, oracle = _oracle(name)
+    tokens = _prompt(opkg.vocab, 24, seed=5)
+    ostream = OracleStream(opkg, 128)
+    _, expected = oracle.target_forward(ostream, tokens, 0, want_logits=True)
+
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=1, max_lanes=32)
+    engine = nb.Engine(package)
+    engine.add_stream(1)
+    logits, hidden = engine.debug_target_logits(1, tokens)
+    difference = np.abs(logits - expected)
+    assert difference.max() <= LOGITS_MAX_ABS, difference.max()
+    assert difference.mean() <= LOGITS_MEAN_ABS, difference.mean()
+    engine.close()
+    package.unmount()
+
+
+@pytest.mark.parametrize("name", ["tiny_int4_mtp_v16", "tiny_int4_mtp"])
+def test_teacher_forced_full_acceptance(name):
+    """Feeding the target's own greedy continuation as the draft proposal makes every cycle accept all drafts
+    and must not change the emitted tokens."""
+    import llmoop_b200 as nb
+
+    opkg, oracle = _oracle(name)
+    prompt = _prompt(opkg.vocab, 12, seed=3)
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=2, max_lanes=64)
+    engine = nb.Engine(package)
+    engine.add_stream(1, speculative_draft_tokens=0)
+    plain, _ = engine.submit_input_event_until_idle(1, prompt, 24)
+    engine.add_stream(2, speculative_draft_tokens=3)
+    engine.set_teacher_tokens(2, plain)
+    engine.set_cycle_logging(True)
+    forced, report = engine.submit_input_event_until_idle(2, prompt, 24)
+    assert forced == plain
+    cycles = engine.cycle_log()
+    assert cycles and all(c["accepted"] == len(c["emitted"]) - 1 for c in cycles)
+    assert report.accepted_draft_token_count == report.proposed_draft_token_count
+    engine.close()
+    package.unmount()
+
+
+def test_stop_token_truncates_and_closes():
+    import llmoop_b200 as nb
+    from oracle.nerve_oracle import OracleStream
+
+    name = "tiny_int4_mtp_v16"
+    opkg, oracle = _oracle(name)
+    prompt = _prompt(opkg.vocab, 10, seed=9)
+    free_run = oracle.generate(OracleStream(opkg, 128), prompt, 20, 0)["tokens"]
+    stop = free_run[5]
+    ostream = OracleStream(opkg, 128)
+    expected = oracle.generate(ostream, prompt, 20, 3, stop_tokens=[stop])
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=1, max_lanes=32)
+    engine = nb.Engine(package)
+    engine.add_stream(1, speculative_draft_tokens=3)
+    tokens, _ = engine.submit_input_event_until_idle(1, prompt, 20, [stop])
+    assert tokens == expected["tokens"]
+    assert tokens[-1] == stop and stop not in tokens[:-1]
+    assert engine.stream_tick(1) == ostream.next_tick
+    engine.close()
+    package.unmount()
+
+
+def test_multi_stream_batched_verify_matches_single_stream_runs():
+    """Several streams decoding together (one batched verify per cycle) must emit what each emits alone."""
+    import llmoop_b200 as nb
+
+    name = "tiny_int4_mtp"
+    opkg, _ = _oracle(name)
+    prompts = [_prompt(opkg.vocab, 8 + 3 * i, seed=20 + i) for i in range(4)]
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=5, max_lanes=64)
+    engine = nb.Engine(package)
+    alone = []
+    for i, prompt in enumerate(prompts):
+        engine.add_stream(100 + i, speculative_draft_tokens=2)
+        tokens, _ = engine.submit_input_event_until_idle(100 + i, prompt, 16)
+        alone.append(tokens)
+        engine.remove_stream(100 + i)
+    for i, prompt in enumerate(prompts):
+        engine.add_stream(i, speculative_draft_tokens=2)
+        engine.enqueue_input_event(i, prompt, 16)
+    outputs, report = engine.run_until_idle()
+    together = [[t for sid, t, _, _ in outputs if sid == i] for i in range(4)]
+    assert together == alone
+    assert report.max_batch_width == 4
+    engine.close()
+    package.unmount()
+
+
+def test_fork_shares_prefix_and_diverges_copy_on_write():
+    import llmoop_b200 as nb
+
+    name = "tiny_int4_mtp"
+    opkg, _ = _oracle(name)
+    prefix = _prompt(opkg.vocab, 21, seed=31)  # ends inside a page: the tail page must be copied on write
+    tail_a, tail_b = _prompt(opkg.vocab, 5, seed=32), _prompt(opkg.vocab, 7, seed=33)
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=4, max_lanes=64, extra_pages=8)
+    engine = nb.Engine(package)
+    # references: each branch from scratch
+    expected = []
+    for i, tail in enumerate((tail_a, tail_b)):
+        engine.add_stream(50 + i, speculative_draft_tokens=2)
+        tokens, _ = engine.submit_input_event_until_idle(50 + i, prefix + tail, 12)
+        expected.append(tokens)
+        engine.remove_stream(50 + i)
+    # shared prefix, then fork
+    engine.add_stream(1, speculative_draft_tokens=2)
+    engine.submit_input_event_until_idle(1, prefix, 0)
+    engine.fork_stream(1, 2)
+    assert engine.stream_tick(2) == engine.stream_tick(1) == len(prefix)
+    engine.enqueue_input_event(1, tail_a, 12)
+    engine.enqueue_input_event(2, tail_b, 12)
+    outputs, _ = engine.run_until_idle()
+    got = [[t for sid, t, _, _ in outputs if sid == s] for s in (1, 2)]
+    assert got == expected
+    engine.close()
+    package.unmount()
+
+
+def test_mount_errors_are_reported_not_fatal(tmp_path):
+    import shutil
+
+    import llmoop_b200 as nb
+
+    broken = tmp_path / "broken"
+    shutil.copytree(GOLDEN / "tiny_int4_mtp_v16", broken)
+    weights = sorted((broken / "weights").glob("*.safetensors"))[0]
+    data = bytearray(weights.read_bytes())
+    data[-1] ^= 0xFF
+    weights.write_bytes(bytes(data))
+    with pytest.raises(nb.NerveError, match="sha256"):
+        nb.Package(broken, capacity_tokens=64)
+    with pytest.raises(nb.NerveError):
+        nb.Package(GOLDEN / "tiny_int4_mtp_v16", capacity_tokens=100000)  # beyond max_context_activations
