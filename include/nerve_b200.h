@@ -123,11 +123,19 @@ typedef struct nerve_b200_run_report {
     double verify_ms_sum;    /* device time of all verify steps (CUDA events) */
     uint64_t verify_steps;
     uint64_t verify_bytes;   /* algorithmic bytes of all verify steps (weights once + attended KV) */
+    double device_ms;        /* CUDA-event time from the first to the last launch of the run */
+    double int4_ms;          /* profiling mode: summed device time of the INT4 linear launches */
+    uint64_t int4_bytes, int4_launches;
+    int32_t idle;            /* 0 when a bounded run stopped with work left */
 } nerve_b200_run_report;
 
 /* run_until_idle_bounded_with_output (placed_prompt_engine.rs:420-589). */
 int32_t nerve_b200_engine_run_until_idle(nerve_b200_engine *engine, nerve_b200_output_callback on_output, void *user,
                                          nerve_b200_run_report *out_report);
+
+/* Bounded form: stops after max_batches decode batches (speculative cycles / single-tick batches); 0 = unbounded. */
+int32_t nerve_b200_engine_run(nerve_b200_engine *engine, uint64_t max_batches, nerve_b200_output_callback on_output,
+                              void *user, nerve_b200_run_report *out_report);
 
 int32_t nerve_b200_engine_stream_tick(const nerve_b200_engine *engine, int64_t stream_id, uint64_t *out_tick);
 
@@ -137,6 +145,8 @@ int32_t nerve_b200_engine_set_teacher_tokens(nerve_b200_engine *engine, int64_t 
                                              size_t count);
 int32_t nerve_b200_engine_set_prefill_chunk(nerve_b200_engine *engine, int32_t tokens);
 int32_t nerve_b200_engine_set_cycle_logging(nerve_b200_engine *engine, int32_t enabled);
+/* Records CUDA events around every INT4 linear launch (adds launch overhead; for roofline measurement only). */
+int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabled);
 /* Cycle log rows: {stream_id, start_tick, accepted, committed, emitted_count, width, emitted[8], targets[8]} as u64. */
 int32_t nerve_b200_engine_cycle_log(const nerve_b200_engine *engine, uint64_t *out_rows, size_t max_rows,
                                     size_t *out_count);

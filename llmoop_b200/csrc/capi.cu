@@ -212,9 +212,21 @@ int32_t nerve_b200_engine_enqueue(nerve_b200_engine *engine, int64_t stream_id, 
 
 int32_t nerve_b200_engine_run_until_idle(nerve_b200_engine *engine, nerve_b200_output_callback on_output, void *user,
                                          nerve_b200_run_report *out) {
+    return nerve_b200_engine_run(engine, 0, on_output, user, out);
+}
+
+int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabled) {
     return guarded([&] {
         require(engine != nullptr, "null engine");
-        RunReport report = engine->engine->run_until_idle([&](const OutputEvent &event) {
+        engine->engine->set_profiling(enabled != 0);
+    });
+}
+
+int32_t nerve_b200_engine_run(nerve_b200_engine *engine, uint64_t max_batches, nerve_b200_output_callback on_output, void *user,
+                              nerve_b200_run_report *out) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        RunReport report = engine->engine->run(max_batches, [&](const OutputEvent &event) {
             if (on_output) on_output(user, event.stream_id, event.token_id, event.source_stream_tick, event.output_index);
         });
         if (out) {
@@ -241,6 +253,11 @@ int32_t nerve_b200_engine_run_until_idle(nerve_b200_engine *engine, nerve_b200_o
             out->verify_ms_sum = report.verify_ms_sum;
             out->verify_steps = report.verify_steps;
             out->verify_bytes = report.verify_bytes;
+            out->device_ms = report.device_ms;
+            out->int4_ms = report.int4_ms;
+            out->int4_bytes = report.int4_bytes;
+            out->int4_launches = report.int4_launches;
+            out->idle = report.idle ? 1 : 0;
         }
     });
 }

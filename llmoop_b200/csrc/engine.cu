@@ -261,6 +261,7 @@ Engine::~Engine() {
         cudaFree(buffer->ptr);
     cudaFreeHost(staging_);
     cudaFreeHost(host_records_);
+    for (cudaEvent_t event : profile_events_) cudaEventDestroy(event);
     cudaEventDestroy(event_a_);
     cudaEventDestroy(event_b_);
     cudaStreamDestroy(cuda_stream_);
@@ -467,6 +468,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                     plan.ops[index + 2].inputs[1] == plan.ops[index + 1].outputs[0] && op.weights[0].n == plan.ops[index + 1].weights[0].n &&
                     consumers(op.outputs[0], index + 3) == 0 && consumers(plan.ops[index + 1].outputs[0], index + 3) == 0) {
                     const OpSpec &up = plan.ops[index + 1];
+                    profile_begin(2 * static_cast<uint64_t>(op.weights[0].n) * (op.weights[0].k / 2 + op.weights[0].k / 64));
                     check(launch_linear_int4_silu_pair(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(op.weights[0].tensor)),
                                                        static_cast<const uint16_t *>(weight(op.weights[0].scale)),
                                                        static_cast<const uint32_t *>(weight(up.weights[0].tensor)),
@@ -474,6 +476,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                                                        u16(plan.ops[index + 2].outputs[0]), lanes, static_cast<int>(op.weights[0].n),
                                                        static_cast<int>(op.weights[0].k), st),
                           "linear_int4 gate/up");
+                    profile_end();
                     index += 2;
                     break;
                 }
@@ -488,11 +491,13 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                     (plan.ops[index + 1].inputs[0] == op.outputs[0] || plan.ops[index + 1].inputs[1] == op.outputs[0])) {
                     const OpSpec &add = plan.ops[index + 1];
                     const std::string &residual = add.inputs[0] == op.outputs[0] ? add.inputs[1] : add.inputs[0];
+                    profile_begin(static_cast<uint64_t>(op.weights[0].n) * (op.weights[0].k / 2 + op.weights[0].k / 64));
                     check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(op.weights[0].tensor)),
                                              static_cast<const uint16_t *>(weight(op.weights[0].scale)), u16(add.outputs[0]), u16(residual),
                                              lanes, static_cast<int>(op.weights[0].n), static_cast<int>(op.weights[0].k), 128,
                                              EPILOGUE_RESIDUAL_ROUNDED, st),
                           "linear_int4 + residual");
+                    profile_end();
                     index += 1;
                     break;
                 }
@@ -501,15 +506,19 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                 uint16_t *outputs[3];
                 int ns[3];
                 int branches = 0;
+                uint64_t branch_bytes = 0;
                 for (size_t i = index; i <= last; i++, branches++) {
+                    branch_bytes += static_cast<uint64_t>(plan.ops[i].weights[0].n) * (plan.ops[i].weights[0].k / 2 + plan.ops[i].weights[0].k / 64);
                     qweights[branches] = static_cast<const uint32_t *>(weight(plan.ops[i].weights[0].tensor));
                     scales[branches] = static_cast<const uint16_t *>(weight(plan.ops[i].weights[0].scale));
                     outputs[branches] = u16(plan.ops[i].outputs[0]);
                     ns[branches] = static_cast<int>(plan.ops[i].weights[0].n);
                 }
+                profile_begin(branch_bytes);
                 check(launch_linear_int4_multi(u16(op.inputs[0]), branches, qweights, scales, outputs, ns, nullptr, lanes,
                                                static_cast<int>(op.weights[0].k), EPILOGUE_BF16, st),
                       "linear_int4");
+                profile_end();
                 index = last;
                 break;
             }
@@ -674,6 +683,32 @@ void Engine::synchronize(const char *what) {
     cuda_check(cudaStreamSynchronize(cuda_stream_), what);
     counters_.host_syncs++;
     staging_used_ = 0;
+    for (size_t i = 0; i + 1 < profile_used_; i += 2) {
+        float ms = 0.0f;
+        cuda_check(cudaEventElapsedTime(&ms, profile_events_[i], profile_events_[i + 1]), "profile event elapsed");
+        profile_ms_ += ms;
+    }
+    profile_used_ = 0;
+}
+
+void Engine::profile_begin(uint64_t bytes) {
+    if (!profile_) return;
+    if (profile_used_ + 2 > profile_events_.size()) {
+        for (int i = 0; i < 2; i++) {
+            cudaEvent_t event;
+            cuda_check(cudaEventCreate(&event), "cudaEventCreate");
+            profile_events_.push_back(event);
+        }
+    }
+    cuda_check(cudaEventRecord(profile_events_[profile_used_], cuda_stream_), "profile event record");
+    profile_bytes_ += bytes;
+    profile_launches_++;
+}
+
+void Engine::profile_end() {
+    if (!profile_) return;
+    cuda_check(cudaEventRecord(profile_events_[profile_used_ + 1], cuda_stream_), "profile event record");
+    profile_used_ += 2;
 }
 
 void Engine::upload_lanes(const std::vector<uint32_t> &positions, const std::vector<int32_t> &slots) {
@@ -1004,10 +1039,22 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
 
 // ---------------------------------------------------------------------------- run loop
 
-RunReport Engine::run_until_idle(const std::function<void(const OutputEvent &)> &on_output) {
+RunReport Engine::run_until_idle(const std::function<void(const OutputEvent &)> &on_output) { return run(0, on_output); }
+
+RunReport Engine::run(uint64_t max_batches, const std::function<void(const OutputEvent &)> &on_output) {
     RunReport report;
     counters_ = ExecCounters{};
+    profile_ms_ = 0.0;
+    profile_bytes_ = profile_launches_ = 0;
+    cudaEvent_t run_begin, run_end;
+    cuda_check(cudaEventCreate(&run_begin), "cudaEventCreate");
+    cuda_check(cudaEventCreate(&run_end), "cudaEventCreate");
+    cuda_check(cudaEventRecord(run_begin, cuda_stream_), "event record");
     while (true) {
+        if (max_batches && report.batch_count >= max_batches) {
+            report.idle = false;
+            break;
+        }
         bool any = false;
         // 1. prefill: streams with external inputs left, one chunk each per round
         for (auto &entry : streams_) {
@@ -1079,6 +1126,16 @@ RunReport Engine::run_until_idle(const std::function<void(const OutputEvent &)> 
         report.decode_ns += now_ns() - start;
         if (!any) break;
     }
+    cuda_check(cudaEventRecord(run_end, cuda_stream_), "event record");
+    synchronize("run synchronize");
+    float device_ms = 0.0f;
+    cuda_check(cudaEventElapsedTime(&device_ms, run_begin, run_end), "event elapsed");
+    cudaEventDestroy(run_begin);
+    cudaEventDestroy(run_end);
+    report.device_ms = device_ms;
+    report.int4_ms = profile_ms_;
+    report.int4_bytes = profile_bytes_;
+    report.int4_launches = profile_launches_;
     report.counters = counters_;
     return report;
 }

@@ -134,6 +134,10 @@ struct RunReport {
     double verify_ms_sum = 0.0;  // device time of verify steps (CUDA events)
     uint64_t verify_steps = 0;
     uint64_t verify_bytes = 0;   // algorithmic bytes of all verify steps
+    double device_ms = 0.0;      // CUDA-event time from the first to the last launch of this run
+    double int4_ms = 0.0;        // with profiling on: summed device time of the INT4 linear launches
+    uint64_t int4_bytes = 0, int4_launches = 0;
+    bool idle = true;            // false when the run stopped at max_batches with work left
 };
 
 struct CycleRecord {  // one speculative cycle of one stream, for parity tests
@@ -158,6 +162,10 @@ public:
     // draft proposal, so every draft is accepted when tokens are the target's own greedy continuation.
     void set_teacher_tokens(int64_t id, const std::vector<uint32_t> &tokens);
     RunReport run_until_idle(const std::function<void(const OutputEvent &)> &on_output);
+    // Bounded form (run_until_idle_bounded, placed_prompt_engine.rs:420-589): stops after `max_batches` decode
+    // batches (speculative cycles or single-tick batches); 0 = unbounded.
+    RunReport run(uint64_t max_batches, const std::function<void(const OutputEvent &)> &on_output);
+    void set_profiling(bool enabled) { profile_ = enabled; }
 
     uint64_t stream_tick(int64_t id) const;
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
@@ -257,6 +265,14 @@ private:
     bool use_graphs_ = false, log_cycles_ = false;
     std::vector<CycleRecord> cycle_log_;
     ExecCounters counters_;
+    // per-launch CUDA events around the INT4 linears (profiling mode only)
+    bool profile_ = false;
+    std::vector<cudaEvent_t> profile_events_;
+    size_t profile_used_ = 0;
+    double profile_ms_ = 0.0;
+    uint64_t profile_bytes_ = 0, profile_launches_ = 0;
+    void profile_begin(uint64_t bytes);
+    void profile_end();
     void *current_frame_ = nullptr;         // where the last component wrote its output frame
 };
 

@@ -52,7 +52,9 @@ _REPORT_U64 = (
 
 class _RunReport(ctypes.Structure):
     _fields_ = [(name, ctypes.c_uint64) for name in _REPORT_U64] + [
-        ("verify_ms_sum", ctypes.c_double), ("verify_steps", ctypes.c_uint64), ("verify_bytes", ctypes.c_uint64)]
+        ("verify_ms_sum", ctypes.c_double), ("verify_steps", ctypes.c_uint64), ("verify_bytes", ctypes.c_uint64),
+        ("device_ms", ctypes.c_double), ("int4_ms", ctypes.c_double), ("int4_bytes", ctypes.c_uint64),
+        ("int4_launches", ctypes.c_uint64), ("idle", ctypes.c_int32)]
 
 
 _OUTPUT_CALLBACK = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int64, ctypes.c_uint32, ctypes.c_uint64, ctypes.c_uint64)
@@ -62,7 +64,8 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_package_describe", "nerve_b200_package_validate", "nerve_b200_engine_create",
     "nerve_b200_engine_destroy", "nerve_b200_engine_add_stream", "nerve_b200_engine_fork_stream",
     "nerve_b200_engine_reset_stream", "nerve_b200_engine_remove_stream", "nerve_b200_engine_interrupt_stream",
-    "nerve_b200_engine_enqueue", "nerve_b200_engine_run_until_idle", "nerve_b200_engine_stream_tick",
+    "nerve_b200_engine_enqueue", "nerve_b200_engine_run_until_idle", "nerve_b200_engine_run",
+    "nerve_b200_engine_set_profiling", "nerve_b200_engine_stream_tick",
     "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_bf16", "nerve_b200_op_rms_norm", "nerve_b200_op_linear_fp8",
@@ -195,6 +198,13 @@ class Engine:
 
     def run_until_idle(self, on_output=None):
         """Returns (outputs, report): outputs is a list of (stream_id, token_id, source_stream_tick, output_index)."""
+        return self.run(0, on_output)
+
+    def set_profiling(self, enabled: bool):
+        _check(library().nerve_b200_engine_set_profiling(self._handle, int(enabled)))
+
+    def run(self, max_batches: int = 0, on_output=None):
+        """Bounded run: stops after `max_batches` decode batches (0 = until idle)."""
         outputs = []
 
         def trampoline(_user, stream_id, token_id, tick, index):
@@ -204,7 +214,7 @@ class Engine:
 
         callback = _OUTPUT_CALLBACK(trampoline)
         report = _RunReport()
-        _check(library().nerve_b200_engine_run_until_idle(self._handle, callback, None, ctypes.byref(report)))
+        _check(library().nerve_b200_engine_run(self._handle, ctypes.c_uint64(max_batches), callback, None, ctypes.byref(report)))
         values = {name: getattr(report, name) for name, _ in _RunReport._fields_}
         return outputs, RunReport(values)
 

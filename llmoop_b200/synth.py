@@ -237,3 +237,76 @@ def write_source_checkpoint(spec: ModelSpec, directory) -> None:
         json.dumps({"bos_token": "[BOS]", "eos_token": "[EOS]", "pad_token": "[PAD]", "unk_token": "[UNK]"}, indent=2)
         + "\n"
     )
+
+
+def iter_checkpoint_torch(spec: ModelSpec, device="cuda"):
+    """Large-model variant of build_checkpoint: tensors are drawn and quantised with torch on `device` (seeded
+    torch.Generator) and yielded one at a time as (name, dtype, shape, numpy array), so an 8B-parameter package
+    streams to disk without ever being resident in host memory.  Same distributions and formats as the numpy
+    builder; the random stream differs (torch Philox instead of numpy PCG64)."""
+    import torch
+
+    if spec.experts or spec.quant not in ("bf16", "int4"):
+        raise ValueError("iter_checkpoint_torch covers dense BF16 and INT4 decoders")
+    generator = torch.Generator(device=device)
+    generator.manual_seed(spec.seed)
+
+    def bf16_bits(values):
+        bits = values.contiguous().view(torch.int32)
+        lsb = (bits >> 16) & 1
+        return (((bits + 0x7FFF + lsb) >> 16) & 0xFFFF).to(torch.int32)
+
+    def to_u16(values_bits):
+        return values_bits.to(torch.int16).cpu().numpy().view(np.uint16)
+
+    def normal(shape):
+        return torch.randn(shape, generator=generator, device=device, dtype=torch.float32) * spec.std
+
+    def ones(name, width):
+        return name, "BF16", (width,), f32_to_bf16_bits(np.ones(width, dtype=np.float32))
+
+    def linear(name, n, k, quantize=True):
+        w = normal((n, k))
+        if quantize and spec.quant == "int4":
+            grouped = w.view(n, k // 128, 128)
+            absmax = grouped.abs().amax(dim=2)
+            scale_bits = bf16_bits(torch.clamp(absmax / 7.0, min=1e-8))
+            scale = (scale_bits << 16).view(torch.float32)
+            q = torch.clamp(torch.round(grouped / scale[:, :, None]), -8, 7).to(torch.int32) + 8
+            q = q.view(n, k // 8, 8)
+            packed = torch.zeros((n, k // 8), dtype=torch.int32, device=device)
+            for j in range(8):
+                packed |= q[:, :, j] << (4 * j)
+            yield name + ".weight_packed", "I32", (n, k // 8), packed.cpu().numpy()
+            yield name + ".weight_scale", "BF16", (n, k // 128), to_u16(scale_bits)
+        else:
+            yield name + ".weight", "BF16", (n, k), to_u16(bf16_bits(w))
+
+    def layer(prefix):
+        h = spec.hidden
+        yield ones(prefix + ".input_layernorm.weight", h)
+        yield ones(prefix + ".post_attention_layernorm.weight", h)
+        yield from linear(prefix + ".self_attn.q_proj", spec.q_heads * spec.head_dim, h)
+        yield from linear(prefix + ".self_attn.k_proj", spec.kv_heads * spec.head_dim, h)
+        yield from linear(prefix + ".self_attn.v_proj", spec.kv_heads * spec.head_dim, h)
+        yield from linear(prefix + ".self_attn.o_proj", h, spec.q_heads * spec.head_dim)
+        yield from linear(prefix + ".mlp.gate_proj", spec.ffn, h)
+        yield from linear(prefix + ".mlp.up_proj", spec.ffn, h)
+        yield from linear(prefix + ".mlp.down_proj", h, spec.ffn)
+
+    yield from linear("model.embed_tokens", spec.vocab, spec.hidden, quantize=False)
+    yield ones("model.norm.weight", spec.hidden)
+    if not spec.tied:
+        yield from linear("lm_head", spec.vocab, spec.hidden, quantize=False)
+    for index in range(spec.layers):
+        yield from layer(f"model.layers.{index}")
+    if spec.mtp:
+        yield from linear("mtp.fc", spec.hidden, 2 * spec.hidden, quantize=False)
+        yield ones("mtp.pre_fc_norm_embedding.weight", spec.hidden)
+        yield ones("mtp.pre_fc_norm_hidden.weight", spec.hidden)
+        yield ones("mtp.norm.weight", spec.hidden)
+        yield from layer("mtp.layers.0")
+
+
+LLAMA3_8B_INT4 = dict(hidden=4096, layers=32, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256,
+                      rope_theta=500000.0, quant="int4", std=0.02, max_positions=34816)
