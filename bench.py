@@ -203,6 +203,10 @@ def main():
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--skip-cpu-baseline", action="store_true")
+    parser.add_argument("--profile-cycles", type=int, default=0,
+                        help="profiling aid: mount, prefill, --warmup cycles, then this many cycles, and exit "
+                             "(small enough to run under ncu)")
+    parser.add_argument("--profile-prompt", type=int, default=PROMPT_TOKENS)
     args = parser.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -272,6 +276,14 @@ def main():
     engine = nb.Engine(package)
     engine.set_prefill_chunk(PROMPT_TOKENS)
     engine.add_stream(0, seed=0, speculative_draft_tokens=DRAFTS)
+
+    if args.profile_cycles:
+        short_prompt = prompt[:args.profile_prompt]
+        report, wall = timed_cycles(engine, 0, short_prompt, budget, warmup, args.profile_cycles, None, barrier)
+        print(json.dumps({"profile_cycles": args.profile_cycles, "device_ms_per_cycle": report.device_ms / args.profile_cycles,
+                          "verify_ms": report.verify_ms_sum / max(1, report.verify_steps),
+                          "kernel_launches": report.kernel_launches}))
+        return
 
     # ---- e2e: whole events through the public API (natural, then teacher-forced with the same tokens)
     natural_tokens, natural_report, _ = run_event(engine, 0, prompt, EVENT_TOKENS)

@@ -173,9 +173,11 @@ int32_t nerve_b200_op_rms_norm(const void *x_device, const void *weight_device, 
 int32_t nerve_b200_op_linear_fp8(const void *x_device, const void *w_device, const void *wscale_device,
                                  void *y_device, const void *residual_device, void *xq_scratch_device,
                                  void *xscale_scratch_device, int32_t lanes, int32_t n, int32_t k, void *stream);
-/* greedy_sampler_f32.comp.template:52-109: records u32[lanes][4] = {token, logit bits, 0, 0}. */
-int32_t nerve_b200_op_greedy(const void *logits_device, void *records_device, int32_t lanes, int32_t vocab,
-                             void *stream);
+/* greedy_sampler_f32.comp.template:52-109: records u32[lanes][4] = {token, logit bits, 0, 0}.  Two-stage
+ * reduction: scratch_device must hold nerve_b200_op_greedy_scratch_bytes(lanes) bytes. */
+int32_t nerve_b200_op_greedy(const void *logits_device, void *records_device, void *scratch_device, int32_t lanes,
+                             int32_t vocab, void *stream);
+uint64_t nerve_b200_op_greedy_scratch_bytes(int32_t lanes);
 /* speculative_decode.rs:54-105 on host arrays (pure function, no GPU): out = {accepted, committed}. */
 int32_t nerve_b200_verify_prefix(const uint32_t *draft, size_t draft_count, const uint32_t *target,
                                  size_t target_count, const uint32_t *stop, size_t stop_count, uint32_t *out_counts,

@@ -359,11 +359,17 @@ int32_t nerve_b200_op_linear_fp8(const void *x, const void *w, const void *wscal
                        "nerve_b200_op_linear_fp8");
 }
 
-int32_t nerve_b200_op_greedy(const void *logits, void *records, int32_t lanes, int32_t vocab, void *stream) {
-    return cuda_status(launch_argmax(static_cast<const float *>(logits), static_cast<uint32_t *>(records), lanes, vocab,
+int32_t nerve_b200_op_greedy(const void *logits, void *records, void *scratch, int32_t lanes, int32_t vocab, void *stream) {
+    if (scratch == nullptr) {
+        last_error = "nerve_b200_op_greedy: scratch must hold nerve_b200_op_greedy_scratch_bytes(lanes) device bytes";
+        return NERVE_B200_ERROR;
+    }
+    return cuda_status(launch_argmax(static_cast<const float *>(logits), static_cast<uint32_t *>(records), lanes, vocab, scratch,
                                      static_cast<cudaStream_t>(stream)),
                        "nerve_b200_op_greedy");
 }
+
+uint64_t nerve_b200_op_greedy_scratch_bytes(int32_t lanes) { return argmax_scratch_bytes(lanes); }
 
 int32_t nerve_b200_verify_prefix(const uint32_t *draft, size_t draft_count, const uint32_t *target, size_t target_count,
                                  const uint32_t *stop, size_t stop_count, uint32_t *out_counts, uint32_t *out_emitted,

@@ -221,12 +221,13 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     draft_hidden_in_ = device_alloc(lanes * frame);
     logits_ = device_alloc(lanes * static_cast<size_t>(plan.vocab) * sizeof(float));
     records_ = device_alloc(lanes * 4 * sizeof(uint32_t));
+    argmax_scratch_ = device_alloc(argmax_scratch_bytes(options.max_lanes));
     lane_tokens_ = device_alloc(lanes * sizeof(uint32_t));
     lane_positions_ = device_alloc(lanes * sizeof(uint32_t));
     lane_slots_ = device_alloc(lanes * sizeof(int32_t));
     pending_hidden_ = device_alloc(static_cast<size_t>(options.max_streams) * frame);
 
-    split_tokens_ = 256;
+    split_tokens_ = 64;
     max_splits_ = static_cast<int>((model_->capacity() + split_tokens_ - 1) / split_tokens_);
     int max_q_heads = 1, max_head_width = 1;
     auto scan = [&](const ComponentPlan &component) {
@@ -240,7 +241,7 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     attention_scratch_ = device_alloc(attention_scratch_bytes(options.max_lanes, max_q_heads, max_head_width, max_splits_));
 
     // cycle arrays: verify tokens, forced drafts, stop tokens/counts, accept rows, per-step draft tokens, slots
-    cycle_state_ = device_alloc(lanes * 64 * sizeof(uint32_t) + static_cast<size_t>(options.max_streams) * (MAX_STOP_TOKENS + 8) * sizeof(uint32_t) * 4);
+    cycle_state_ = device_alloc(lanes * 64 * sizeof(uint32_t) + static_cast<size_t>(options.max_streams) * (MAX_STOP_TOKENS + 64) * sizeof(uint32_t) * 4);
 
     staging_bytes_ = std::max<size_t>(size_t(1) << 20, lanes * 1024 + static_cast<size_t>(options.max_streams) * model_->pages_per_stream() * 8);
     cuda_check(cudaMallocHost(&staging_, staging_bytes_), "cudaMallocHost");
@@ -256,12 +257,14 @@ Engine::~Engine() {
     cudaStreamSynchronize(cuda_stream_);
     for (auto &entry : signals_) cudaFree(entry.second.ptr);
     for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
-                                 &records_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
+                                 &records_, &argmax_scratch_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
                                  &cycle_state_})
         cudaFree(buffer->ptr);
     cudaFreeHost(staging_);
     cudaFreeHost(host_records_);
     for (cudaEvent_t event : profile_events_) cudaEventDestroy(event);
+    for (auto &entry : graphs_)
+        if (entry.second.exec) cudaGraphExecDestroy(entry.second.exec);
     cudaEventDestroy(event_a_);
     cudaEventDestroy(event_b_);
     cudaStreamDestroy(cuda_stream_);
@@ -438,7 +441,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
     auto u16 = [&](const std::string &name) { return static_cast<uint16_t *>(ptr(name)); };
     auto width = [&](const std::string &name) { return static_cast<int>(plan.signals.at(name).width); };
     auto weight = [&](const std::string &name) { return model_->tensor(name); };
-    LaneTable lane_table{static_cast<const uint32_t *>(lane_positions_.ptr), static_cast<const int32_t *>(lane_slots_.ptr)};
+    const LaneTable lane_table = current_lanes_;
 
     auto consumers = [&](const std::string &signal, size_t after) {
         int count = 0;
@@ -617,8 +620,8 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
             if (kv_index < 0) fail("attention op in a component without KV state");
             KvLayer kv = model_->kv_layer(kv_index);
             check(launch_kv_append(u16(op.inputs[1]), u16(op.inputs[2]), kv, lane_table, lanes, st), "kv_append");
-            check(launch_attention(u16(op.inputs[0]), u16(op.outputs[0]), kv, lane_table, lanes, op.q_heads, op.attention_scale, split_tokens_,
-                                   max_splits_, static_cast<float *>(attention_scratch_.ptr), st),
+            check(launch_attention(u16(op.inputs[0]), u16(op.outputs[0]), kv, lane_table, lanes, current_width_, op.q_heads, op.attention_scale, split_tokens_,
+                                   current_splits_, static_cast<float *>(attention_scratch_.ptr), st),
                   "attention");
             counters_.kernel_launches++;
             break;
@@ -714,15 +717,64 @@ void Engine::profile_end() {
 void Engine::upload_lanes(const std::vector<uint32_t> &positions, const std::vector<int32_t> &slots) {
     upload(lane_positions_.ptr, positions.data(), positions.size() * sizeof(uint32_t), "lane positions upload");
     upload(lane_slots_.ptr, slots.data(), slots.size() * sizeof(int32_t), "lane slots upload");
+    current_lanes_ = LaneTable{static_cast<const uint32_t *>(lane_positions_.ptr), static_cast<const int32_t *>(lane_slots_.ptr)};
+    uint32_t newest = 0;
+    for (uint32_t position : positions) newest = std::max(newest, position);
+    current_splits_ = splits_for(newest);
 }
 
 void Engine::upload_tokens(const uint32_t *tokens, int count) {
     upload(lane_tokens_.ptr, tokens, static_cast<size_t>(count) * sizeof(uint32_t), "lane tokens upload");
+    current_tokens_ = static_cast<const uint32_t *>(lane_tokens_.ptr);
+}
+
+// Attention launches cover ceil(context / split_tokens) splits, rounded up to a power of two so that a handful of
+// graph shapes serves a growing context.
+int Engine::splits_for(uint64_t newest_tick) const {
+    uint64_t tokens = std::min<uint64_t>(newest_tick + 1, model_->capacity());
+    int needed = static_cast<int>((tokens + split_tokens_ - 1) / split_tokens_);
+    int bucket = 1;
+    while (bucket < needed) bucket <<= 1;
+    return std::min(bucket, max_splits_);
+}
+
+// Runs `body` (stream-ordered launches only: no uploads, read-backs or synchronisation) directly the first time a
+// key is seen, then captures it into a CUDA graph and replays the graph from the third call on.
+void Engine::run_phase(const std::vector<int> &key, const std::function<void()> &body) {
+    if (!use_graphs_ || profile_) {
+        body();
+        return;
+    }
+    GraphEntry &entry = graphs_[key];
+    if (entry.exec == nullptr) {
+        if (entry.warm++ == 0) {
+            body();
+            return;
+        }
+        uint64_t before = counters_.kernel_launches;
+        cudaGraph_t graph = nullptr;
+        cuda_check(cudaStreamBeginCapture(cuda_stream_, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+        try {
+            body();
+        } catch (...) {
+            cudaStreamEndCapture(cuda_stream_, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            throw;
+        }
+        cuda_check(cudaStreamEndCapture(cuda_stream_, &graph), "cudaStreamEndCapture");
+        entry.kernel_nodes = counters_.kernel_launches - before;
+        counters_.kernel_launches = before;
+        cuda_check(cudaGraphInstantiate(&entry.exec, graph, 0), "cudaGraphInstantiate");
+        cudaGraphDestroy(graph);
+    }
+    cuda_check(cudaGraphLaunch(entry.exec, cuda_stream_), "cudaGraphLaunch");
+    counters_.graph_launches++;
+    counters_.kernel_launches += entry.kernel_nodes;
 }
 
 void Engine::target_forward(int lanes, bool want_logits) {
     const ModelPlan &plan = model_->plan();
-    check(launch_embedding(static_cast<const uint16_t *>(model_->tensor(plan.embedding_tensor)), static_cast<const uint32_t *>(lane_tokens_.ptr),
+    check(launch_embedding(static_cast<const uint16_t *>(model_->tensor(plan.embedding_tensor)), current_tokens_,
                            static_cast<uint16_t *>(frame_a_.ptr), lanes, static_cast<int>(plan.hidden), static_cast<int>(plan.vocab),
                            plan.embedding_scale, cuda_stream_),
           "embedding");
@@ -745,14 +797,14 @@ void Engine::target_forward(int lanes, bool want_logits) {
                                  cuda_stream_),
               "output projection");
         check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, static_cast<int>(plan.vocab),
-                            cuda_stream_),
+                            argmax_scratch_.ptr, cuda_stream_),
               "greedy sampler");
     }
 }
 
 void Engine::draft_forward(int lanes, const uint16_t *hidden_in, bool want_logits) {
     const ModelPlan &plan = model_->plan();
-    check(launch_embedding(static_cast<const uint16_t *>(model_->tensor(plan.embedding_tensor)), static_cast<const uint32_t *>(lane_tokens_.ptr),
+    check(launch_embedding(static_cast<const uint16_t *>(model_->tensor(plan.embedding_tensor)), current_tokens_,
                            static_cast<uint16_t *>(embedding_out_.ptr), lanes, static_cast<int>(plan.hidden), static_cast<int>(plan.vocab),
                            plan.embedding_scale, cuda_stream_),
           "draft embedding");
@@ -779,7 +831,7 @@ void Engine::draft_forward(int lanes, const uint16_t *hidden_in, bool want_logit
                              cuda_stream_),
           "draft output projection");
     check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, static_cast<int>(plan.vocab),
-                        cuda_stream_),
+                        argmax_scratch_.ptr, cuda_stream_),
           "draft greedy sampler");
 }
 
@@ -794,6 +846,7 @@ void Engine::run_prefill_chunk(Stream &s, const uint32_t *tokens, int count, boo
     for (int i = 0; i < count; i++) positions[i] = static_cast<uint32_t>(s.next_tick + i);
     upload_lanes(positions, slots);
     upload_tokens(tokens, count);
+    current_width_ = count;
     target_forward(count, false);
     const size_t frame = static_cast<size_t>(plan.hidden) * 2;
     uint8_t *pending = static_cast<uint8_t *>(pending_hidden_.ptr) + s.slot * frame;
@@ -816,7 +869,7 @@ void Engine::run_prefill_chunk(Stream &s, const uint32_t *tokens, int count, boo
                                  cuda_stream_),
               "prefill output projection");
         check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), 1, static_cast<int>(plan.vocab),
-                            cuda_stream_),
+                            argmax_scratch_.ptr, cuda_stream_),
               "prefill sampler");
         cuda_check(cudaMemcpyAsync(host_records_, records_.ptr, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, cuda_stream_), "record readback");
         synchronize("prefill synchronize");
@@ -865,6 +918,7 @@ void Engine::run_single_ticks(std::vector<Stream *> &batch, const std::function<
     sync_block_tables();
     upload_lanes(positions, slots);
     upload_tokens(tokens.data(), lanes);
+    current_width_ = 1;
     target_forward(lanes, any_emit);
     if (plan.has_draft) {
         check(launch_gather_rows(static_cast<const uint16_t *>(pending_hidden_.ptr), static_cast<const int32_t *>(lane_slots_.ptr),
@@ -906,96 +960,101 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
     const int lanes = streams * width;
     if (lanes > model_->options().max_lanes) fail("verify batch exceeds max_lanes");
 
-    // device cycle arrays carved out of cycle_state_
+    // device cycle arrays carved out of cycle_state_; everything up to `accept_rows` is uploaded in one copy
     uint32_t *base = static_cast<uint32_t *>(cycle_state_.ptr);
     uint32_t *verify_tokens = base;                              // [streams][width]
     uint32_t *forced = verify_tokens + lanes;                    // [streams][drafts]
     uint32_t *stop_tokens = forced + lanes;                      // [streams][MAX_STOP]
     int32_t *stop_counts = reinterpret_cast<int32_t *>(stop_tokens + streams * MAX_STOP_TOKENS);  // [streams]
     int32_t *stream_slots = stop_counts + streams;               // [streams]
-    uint32_t *accept_rows = reinterpret_cast<uint32_t *>(stream_slots + streams);  // [streams][4 + 2*width]
-    const size_t upload_words = static_cast<size_t>(lanes) * 2 + streams * MAX_STOP_TOKENS + 2 * streams;
+    uint32_t *draft_positions = reinterpret_cast<uint32_t *>(stream_slots + streams);  // [drafts][streams]
+    uint32_t *verify_positions = draft_positions + drafts * streams;                   // [lanes]
+    int32_t *verify_slots = reinterpret_cast<int32_t *>(verify_positions + lanes);     // [lanes]
+    uint32_t *draft_tokens = reinterpret_cast<uint32_t *>(verify_slots + lanes);       // [streams]
+    const size_t upload_words = static_cast<size_t>(lanes) * 4 + streams * MAX_STOP_TOKENS + 3 * streams + drafts * streams;
+    uint32_t *accept_rows = base + upload_words;                 // [streams][4 + 2*width]
 
-    // host staging (pinned): same layout
     std::vector<uint32_t> staging(upload_words, 0);
-    bool any_forced = false;
+    uint32_t *s_forced = staging.data() + lanes, *s_stop = s_forced + lanes, *s_counts = s_stop + streams * MAX_STOP_TOKENS;
+    uint32_t *s_slots = s_counts + streams, *s_dpos = s_slots + streams, *s_vpos = s_dpos + drafts * streams;
+    uint32_t *s_vslots = s_vpos + lanes, *s_dtokens = s_vslots + lanes;
+    uint64_t newest_tick = 0;
     for (int s = 0; s < streams; s++) {
         Stream &st = *batch[s];
         ensure_pages(st, st.next_tick + drafts);
+        newest_tick = std::max<uint64_t>(newest_tick, st.next_tick + drafts);
         staging[static_cast<size_t>(s) * width] = st.active->feedback_token;
+        s_dtokens[s] = st.active->feedback_token;
         for (int j = 0; j < drafts; j++) {
             size_t output_index = st.active->generated.size() + j;
-            uint32_t value = 0xffffffffu;
-            if (output_index < st.teacher.size()) {
-                value = st.teacher[output_index];
-                any_forced = true;
-            }
-            staging[lanes + static_cast<size_t>(s) * drafts + j] = value;
+            s_forced[static_cast<size_t>(s) * drafts + j] = output_index < st.teacher.size() ? st.teacher[output_index] : 0xffffffffu;
+            s_dpos[static_cast<size_t>(j) * streams + s] = static_cast<uint32_t>(st.next_tick + j);
         }
         const auto &stops = st.active->input.stop_token_ids;
-        for (size_t t = 0; t < stops.size(); t++) staging[2 * lanes + s * MAX_STOP_TOKENS + t] = stops[t];
-        staging[2 * lanes + streams * MAX_STOP_TOKENS + s] = static_cast<uint32_t>(stops.size());
-        staging[2 * lanes + streams * MAX_STOP_TOKENS + streams + s] = static_cast<uint32_t>(st.slot);
+        for (size_t t = 0; t < stops.size(); t++) s_stop[s * MAX_STOP_TOKENS + t] = stops[t];
+        s_counts[s] = static_cast<uint32_t>(stops.size());
+        s_slots[s] = static_cast<uint32_t>(st.slot);
+        for (int i = 0; i < width; i++) {
+            s_vpos[s * width + i] = static_cast<uint32_t>(st.next_tick + i);
+            s_vslots[s * width + i] = static_cast<uint32_t>(st.slot);
+        }
     }
     sync_block_tables();
     upload(base, staging.data(), upload_words * sizeof(uint32_t), "cycle state upload");
+    const int splits = splits_for(newest_tick);
+    current_splits_ = splits;
 
     uint64_t t0 = now_ns();
     // ---- draft loop: `drafts` serial steps over `streams` lanes
-    std::vector<uint32_t> positions(streams);
-    std::vector<int32_t> slots(streams);
-    for (int s = 0; s < streams; s++) slots[s] = batch[s]->slot;
-    for (int j = 0; j < drafts; j++) {
-        for (int s = 0; s < streams; s++) positions[s] = static_cast<uint32_t>(batch[s]->next_tick + j);
-        // lane tables change between steps while earlier launches may still read them: the copies are ordered on the stream
-        upload_lanes(positions, slots);
-        if (j == 0) {
-            std::vector<uint32_t> first_tokens(streams);
-            for (int s = 0; s < streams; s++) first_tokens[s] = batch[s]->active->feedback_token;
-            upload_tokens(first_tokens.data(), streams);
-            check(launch_gather_rows(static_cast<const uint16_t *>(pending_hidden_.ptr), static_cast<const int32_t *>(lane_slots_.ptr),
-                                     static_cast<uint16_t *>(draft_hidden_in_.ptr), streams, static_cast<int>(plan.hidden), cuda_stream_),
-                  "gather pending hidden");
-            draft_forward(streams, static_cast<const uint16_t *>(draft_hidden_in_.ptr), true);
-        } else {
-            draft_forward(streams, static_cast<const uint16_t *>(draft_normalized_.ptr), true);
+    run_phase({0, streams, drafts, splits}, [&] {
+        for (int j = 0; j < drafts; j++) {
+            current_lanes_ = LaneTable{draft_positions + static_cast<size_t>(j) * streams, stream_slots};
+            current_tokens_ = draft_tokens;
+            current_width_ = 1;
+            if (j == 0) {
+                check(launch_gather_rows(static_cast<const uint16_t *>(pending_hidden_.ptr), stream_slots,
+                                         static_cast<uint16_t *>(draft_hidden_in_.ptr), streams, static_cast<int>(plan.hidden), cuda_stream_),
+                      "gather pending hidden");
+                draft_forward(streams, static_cast<const uint16_t *>(draft_hidden_in_.ptr), true);
+            } else {
+                draft_forward(streams, static_cast<const uint16_t *>(draft_normalized_.ptr), true);
+            }
+            check(launch_draft_select(static_cast<const uint32_t *>(records_.ptr), forced, j, streams, drafts, draft_tokens, verify_tokens,
+                                      cuda_stream_),
+                  "draft select");
         }
-        check(launch_draft_select(static_cast<const uint32_t *>(records_.ptr), any_forced ? forced : nullptr, j, streams, drafts,
-                                  static_cast<uint32_t *>(lane_tokens_.ptr), verify_tokens, cuda_stream_),
-              "draft select");
-    }
+    });
     cuda_check(cudaEventRecord(event_a_, cuda_stream_), "event record");
 
     // ---- verify: all candidates of all streams in one batch of lanes
-    std::vector<uint32_t> vpositions(lanes);
-    std::vector<int32_t> vslots(lanes);
-    for (int s = 0; s < streams; s++)
-        for (int i = 0; i < width; i++) {
-            vpositions[s * width + i] = static_cast<uint32_t>(batch[s]->next_tick + i);
-            vslots[s * width + i] = batch[s]->slot;
-        }
-    upload_lanes(vpositions, vslots);
-    cuda_check(cudaMemcpyAsync(lane_tokens_.ptr, verify_tokens, lanes * sizeof(uint32_t), cudaMemcpyDeviceToDevice, cuda_stream_),
-               "verify tokens");
-    target_forward(lanes, true);
+    run_phase({1, streams, drafts, splits}, [&] {
+        current_lanes_ = LaneTable{verify_positions, verify_slots};
+        current_tokens_ = verify_tokens;
+        current_width_ = width;
+        target_forward(lanes, true);
+    });
     cuda_check(cudaEventRecord(event_b_, cuda_stream_), "event record");
 
-    // ---- accept on the device, then draft catch-up over the same lanes
-    check(launch_shift_hidden(static_cast<const uint16_t *>(pending_hidden_.ptr), stream_slots, static_cast<const uint16_t *>(normalized_.ptr),
-                              static_cast<uint16_t *>(draft_hidden_in_.ptr), streams, width, static_cast<int>(plan.hidden), cuda_stream_),
-          "catch-up hidden");
-    check(launch_accept(verify_tokens, static_cast<const uint32_t *>(records_.ptr), stop_tokens, stop_counts, MAX_STOP_TOKENS, streams, drafts,
-                        accept_rows, static_cast<const uint16_t *>(normalized_.ptr), static_cast<uint16_t *>(pending_hidden_.ptr), stream_slots,
-                        static_cast<int>(plan.hidden), cuda_stream_),
-          "accept");
+    // ---- accept on the device, then the draft catch-up over the same lanes: state steps for the verify inputs
+    // with the target's hidden states.  Lanes beyond the committed prefix write slots that the next cycle
+    // overwrites before reading (like the draft loop's own tentative writes in the reference).
     const size_t row_words = 4 + 2 * width;
+    run_phase({2, streams, drafts, splits}, [&] {
+        current_lanes_ = LaneTable{verify_positions, verify_slots};
+        current_tokens_ = verify_tokens;
+        current_width_ = width;
+        check(launch_shift_hidden(static_cast<const uint16_t *>(pending_hidden_.ptr), stream_slots, static_cast<const uint16_t *>(normalized_.ptr),
+                                  static_cast<uint16_t *>(draft_hidden_in_.ptr), streams, width, static_cast<int>(plan.hidden), cuda_stream_),
+              "catch-up hidden");
+        check(launch_accept(verify_tokens, static_cast<const uint32_t *>(records_.ptr), stop_tokens, stop_counts, MAX_STOP_TOKENS, streams, drafts,
+                            accept_rows, static_cast<const uint16_t *>(normalized_.ptr), static_cast<uint16_t *>(pending_hidden_.ptr), stream_slots,
+                            static_cast<int>(plan.hidden), cuda_stream_),
+              "accept");
+        draft_forward(lanes, static_cast<const uint16_t *>(draft_hidden_in_.ptr), false);
+    });
     cuda_check(cudaMemcpyAsync(host_records_, accept_rows, streams * row_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, cuda_stream_),
                "accept readback");
     counters_.d2h_bytes += streams * row_words * 4;
-    // catch-up: draft state steps for the verify inputs with the target's hidden states; lanes beyond the
-    // committed prefix write slots that the next cycle overwrites before reading (same as the draft loop's own
-    // tentative writes in the reference).
-    draft_forward(lanes, static_cast<const uint16_t *>(draft_hidden_in_.ptr), false);
     synchronize("cycle synchronize");
     uint64_t t1 = now_ns();
     float verify_ms = 0.0f;
@@ -1152,6 +1211,7 @@ void Engine::debug_target_logits(int64_t id, const std::vector<uint32_t> &tokens
     for (int i = 0; i < lanes; i++) positions[i] = static_cast<uint32_t>(s.next_tick + i);
     upload_lanes(positions, slots);
     upload_tokens(tokens.data(), lanes);
+    current_width_ = lanes;
     target_forward(lanes, true);
     synchronize("debug synchronize");
     if (logits_out)

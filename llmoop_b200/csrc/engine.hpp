@@ -251,6 +251,7 @@ private:
     DeviceBuffer draft_hidden_in_;          // [max_lanes][hidden]
     DeviceBuffer logits_;                   // f32 [max_lanes][vocab]
     DeviceBuffer records_;                  // u32 [max_lanes][4]
+    DeviceBuffer argmax_scratch_;
     DeviceBuffer lane_tokens_, lane_positions_, lane_slots_;
     DeviceBuffer pending_hidden_;           // [max_streams][hidden]
     DeviceBuffer attention_scratch_;
@@ -262,7 +263,7 @@ private:
     uint32_t *host_records_ = nullptr;      // pinned readback area
     int split_tokens_ = 256, max_splits_ = 1;
     int prefill_chunk_ = 64;
-    bool use_graphs_ = false, log_cycles_ = false;
+    bool use_graphs_ = true, log_cycles_ = false;
     std::vector<CycleRecord> cycle_log_;
     ExecCounters counters_;
     // per-launch CUDA events around the INT4 linears (profiling mode only)
@@ -273,7 +274,20 @@ private:
     uint64_t profile_bytes_ = 0, profile_launches_ = 0;
     void profile_begin(uint64_t bytes);
     void profile_end();
-    void *current_frame_ = nullptr;         // where the last component wrote its output frame
+    // lane table and token ids the forward passes read (device pointers; fixed per phase so that a phase can be
+    // replayed as a CUDA graph while the host only rewrites the arrays' contents)
+    LaneTable current_lanes_{nullptr, nullptr};
+    const uint32_t *current_tokens_ = nullptr;
+    int current_width_ = 1;                 // lanes per stream of the current batch (stream-major lane order)
+    int current_splits_ = 1;                // attention split count (stride of the scratch partials) of this launch
+    struct GraphEntry {
+        cudaGraphExec_t exec = nullptr;
+        uint64_t kernel_nodes = 0;
+        int warm = 0;
+    };
+    std::map<std::vector<int>, GraphEntry> graphs_;
+    void run_phase(const std::vector<int> &key, const std::function<void()> &body);
+    int splits_for(uint64_t newest_tick) const;
 };
 
 }  // namespace nerve

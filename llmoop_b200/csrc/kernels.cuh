@@ -93,9 +93,10 @@ cudaError_t launch_moe_reduce(const uint16_t *outputs, uint16_t *y, int lanes, i
 size_t attention_scratch_bytes(int lanes, int q_heads, int head_width, int max_splits);
 cudaError_t launch_kv_append(const uint16_t *k, const uint16_t *v, const KvLayer &kv, const LaneTable &lanes_meta,
                              int lanes, cudaStream_t stream);
+// Lanes are stream-major: every stream of the batch contributes `lanes_per_stream` consecutive lanes.
 cudaError_t launch_attention(const uint16_t *q, uint16_t *out, const KvLayer &kv, const LaneTable &lanes_meta,
-                             int lanes, int q_heads, float scale, int split_tokens, int max_splits, float *scratch,
-                             cudaStream_t stream);
+                             int lanes, int lanes_per_stream, int q_heads, float scale, int split_tokens, int max_splits,
+                             float *scratch, cudaStream_t stream);
 
 // INT4 multi-branch forms (one launch for q/k/v; gate/up with the SiLU*up epilogue).
 cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint32_t *const *qweights,
@@ -125,6 +126,8 @@ cudaError_t launch_accept(const uint32_t *verify_tokens, const uint32_t *target_
                           cudaStream_t stream);
 
 // Greedy arg-max (ties -> lowest id); record = {token, logit bits, 0, 0} per lane.
-cudaError_t launch_argmax(const float *logits, uint32_t *records, int lanes, int vocab, cudaStream_t stream);
+// `scratch` holds argmax_scratch_bytes(lanes) bytes of per-chunk partial winners.
+size_t argmax_scratch_bytes(int lanes);
+cudaError_t launch_argmax(const float *logits, uint32_t *records, int lanes, int vocab, void *scratch, cudaStream_t stream);
 
 }  // namespace nerve

@@ -69,7 +69,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_bf16", "nerve_b200_op_rms_norm", "nerve_b200_op_linear_fp8",
-    "nerve_b200_op_greedy", "nerve_b200_verify_prefix",
+    "nerve_b200_op_greedy", "nerve_b200_op_greedy_scratch_bytes", "nerve_b200_verify_prefix",
 )
 
 _library = None
@@ -86,6 +86,7 @@ def library() -> ctypes.CDLL:
         for name in EXPORTED_SYMBOLS:
             if name != "nerve_b200_last_error":
                 getattr(lib, name).restype = ctypes.c_int32
+        lib.nerve_b200_op_greedy_scratch_bytes.restype = ctypes.c_uint64
         _library = lib
     return _library
 

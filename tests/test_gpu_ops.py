@@ -107,7 +107,8 @@ def test_linear_bf16_and_logits_match_oracle(lanes):
     assert np.abs(dl.cpu().numpy().reshape(lanes, n) - want_logits).max() < 1e-4
     # greedy sampler: arg-max with ties to the lowest id
     records = torch.zeros(lanes * 4, dtype=torch.int32, device="cuda")
-    assert nb.library().nerve_b200_op_greedy(_ptr(dl), _ptr(records), lanes, n, None) == 0
+    scratch = torch.zeros(nb.library().nerve_b200_op_greedy_scratch_bytes(lanes), dtype=torch.uint8, device="cuda")
+    assert nb.library().nerve_b200_op_greedy(_ptr(dl), _ptr(records), _ptr(scratch), lanes, n, None) == 0
     torch.cuda.synchronize()
     tokens = records.cpu().numpy().reshape(lanes, 4)[:, 0]
     assert list(tokens) == list(dl.cpu().numpy().reshape(lanes, n).argmax(axis=1))
@@ -123,7 +124,8 @@ def test_greedy_ties_resolve_to_lowest_id():
     logits[1, :] = -1.0
     d = _dev(logits)
     records = torch.zeros(8, dtype=torch.int32, device="cuda")
-    assert nb.library().nerve_b200_op_greedy(_ptr(d), _ptr(records), 2, 5000, None) == 0
+    scratch = torch.zeros(nb.library().nerve_b200_op_greedy_scratch_bytes(2), dtype=torch.uint8, device="cuda")
+    assert nb.library().nerve_b200_op_greedy(_ptr(d), _ptr(records), _ptr(scratch), 2, 5000, None) == 0
     torch.cuda.synchronize()
     out = records.cpu().numpy().view(np.uint32).reshape(2, 4)
     assert out[0, 0] == 123 and out[1, 0] == 0
