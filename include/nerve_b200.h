@@ -178,6 +178,16 @@ int32_t nerve_b200_op_linear_fp8(const void *x_device, const void *w_device, con
 int32_t nerve_b200_op_greedy(const void *logits_device, void *records_device, void *scratch_device, int32_t lanes,
                              int32_t vocab, void *stream);
 uint64_t nerve_b200_op_greedy_scratch_bytes(int32_t lanes);
+/* Kernel-ABI byte layouts of the reference (pure host functions): the 20-byte stream-control record
+ * (stream_control_bytes.rs:8-18) and the transient-state header + page table
+ * (transient_state_buffer_layout.rs:24-154; out_layout = {block capacity, page count, page bytes, page-table
+ * bytes, static offset, dynamic offset, byte capacity}; logical_to_physical NULL = identity). */
+int32_t nerve_b200_stream_control_bytes(uint32_t token_id, uint64_t stream_tick, uint32_t control_flags,
+                                        uint32_t capacity, uint8_t *out_20_bytes);
+int32_t nerve_b200_state_page_table_bytes(int64_t static_bytes, int64_t bytes_per_activation,
+                                          int64_t max_dynamic_activations, int64_t capacity_activations,
+                                          const uint32_t *logical_to_physical, size_t mapping_count,
+                                          uint8_t *out_bytes, size_t out_capacity, int64_t *out_layout);
 /* speculative_decode.rs:54-105 on host arrays (pure function, no GPU): out = {accepted, committed}. */
 int32_t nerve_b200_verify_prefix(const uint32_t *draft, size_t draft_count, const uint32_t *target,
                                  size_t target_count, const uint32_t *stop, size_t stop_count, uint32_t *out_counts,

@@ -5,6 +5,7 @@
 
 #include "../../include/nerve_b200.h"
 #include "engine.hpp"
+#include "state_abi.hpp"
 
 using namespace nerve;
 
@@ -370,6 +371,34 @@ int32_t nerve_b200_op_greedy(const void *logits, void *records, void *scratch, i
 }
 
 uint64_t nerve_b200_op_greedy_scratch_bytes(int32_t lanes) { return argmax_scratch_bytes(lanes); }
+
+int32_t nerve_b200_stream_control_bytes(uint32_t token_id, uint64_t stream_tick, uint32_t control_flags, uint32_t capacity,
+                                        uint8_t *out_20_bytes) {
+    return guarded([&] {
+        require(out_20_bytes != nullptr, "null output");
+        stream_control_bytes(token_id, stream_tick, control_flags, capacity, out_20_bytes);
+    });
+}
+
+int32_t nerve_b200_state_page_table_bytes(int64_t static_bytes, int64_t bytes_per_activation, int64_t max_dynamic_activations,
+                                          int64_t capacity_activations, const uint32_t *logical_to_physical, size_t mapping_count,
+                                          uint8_t *out_bytes, size_t out_capacity, int64_t *out_layout) {
+    return guarded([&] {
+        StateLayout layout = state_layout(static_bytes, bytes_per_activation, max_dynamic_activations, capacity_activations);
+        std::vector<uint32_t> mapping;
+        if (logical_to_physical && mapping_count) mapping.assign(logical_to_physical, logical_to_physical + mapping_count);
+        std::vector<uint8_t> bytes = state_page_table_bytes(layout, mapping);
+        if (out_layout) {
+            const int64_t values[7] = {layout.block_activation_capacity, layout.page_count, layout.page_bytes, layout.page_table_bytes,
+                                       layout.static_offset, layout.dynamic_offset, layout.byte_capacity};
+            std::memcpy(out_layout, values, sizeof(values));
+        }
+        if (out_bytes) {
+            require(out_capacity >= bytes.size(), "output buffer is smaller than the page table");
+            std::memcpy(out_bytes, bytes.data(), bytes.size());
+        }
+    });
+}
 
 int32_t nerve_b200_verify_prefix(const uint32_t *draft, size_t draft_count, const uint32_t *target, size_t target_count,
                                  const uint32_t *stop, size_t stop_count, uint32_t *out_counts, uint32_t *out_emitted,

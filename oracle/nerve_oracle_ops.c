@@ -610,3 +610,58 @@ ORC_API int orc_verify_prefix(const uint32_t *draft, int draft_count, const uint
     *emitted_count = count;
     return 0;
 }
+
+/* ---- kernel-ABI byte layouts the reference's tests pin ----------------------- */
+
+/* stream_control_bytes.rs:8-18: {token u32, tick u64 LE, flags u32, capacity u32} = 20 bytes. */
+ORC_API void orc_stream_control_bytes(uint32_t token, uint64_t tick, uint32_t flags, uint32_t capacity, uint8_t *out) {
+    uint32_t words[5] = {token, (uint32_t)tick, (uint32_t)(tick >> 32), flags, capacity};
+    memcpy(out, words, 20);
+}
+
+/* greedy_sampler_f32.comp.template:97-104: the sampler writes the token into word 0 and advances the 64-bit
+ * tick held in words 1 (low) and 2 (high). */
+ORC_API void orc_sampler_advance_control(uint32_t *control_words, uint32_t token) {
+    control_words[0] = token;
+    uint32_t next_low = control_words[1] + 1u;
+    if (next_low == 0u) control_words[2] += 1u;
+    control_words[1] = next_low;
+}
+
+/* transient_state_buffer_layout.rs:24-154: header u32[9] = {magic, version, static bytes, static offset,
+ * page bytes, page count, dynamic capacity, block capacity, dynamic offset}, then page_table[page_count]
+ * (identity), padded to 256 bytes.  Returns the page-table byte capacity; layout_out (if given) receives
+ * {block_capacity, page_count, page_bytes, page_table_bytes, static_offset, dynamic_offset, byte_capacity}. */
+ORC_API int64_t orc_state_page_table(int64_t static_bytes, int64_t bytes_per_activation, int64_t max_dynamic,
+                                     int64_t capacity, uint8_t *table_out, int64_t table_capacity, int64_t *layout_out) {
+    const int64_t window = 64, align = 256;
+    int64_t dynamic_capacity = 0, block = 0, page_bytes = 0, pages = 0;
+    if (bytes_per_activation > 0) {
+        if (capacity == 0) return -1;
+        dynamic_capacity = max_dynamic > 0 && max_dynamic < capacity ? max_dynamic : capacity;
+        block = dynamic_capacity < window ? dynamic_capacity : window;
+        page_bytes = bytes_per_activation * block;
+        pages = (dynamic_capacity + block - 1) / block;
+    }
+    if (static_bytes == 0 && pages == 0) return -1;
+    int64_t table_bytes = ((9 + pages) * 4 + align - 1) / align * align;
+    int64_t static_offset = table_bytes;
+    int64_t dynamic_offset = (static_offset + static_bytes + align - 1) / align * align;
+    int64_t total = dynamic_offset + page_bytes * pages;
+    if (layout_out) {
+        int64_t values[7] = {block, pages, page_bytes, table_bytes, static_offset, dynamic_offset, total};
+        memcpy(layout_out, values, sizeof(values));
+    }
+    if (table_out) {
+        if (table_capacity < table_bytes) return -1;
+        memset(table_out, 0, (size_t)table_bytes);
+        uint32_t header[9] = {0x4e525653u, 1u, (uint32_t)static_bytes, (uint32_t)static_offset, (uint32_t)page_bytes,
+                              (uint32_t)pages, (uint32_t)dynamic_capacity, (uint32_t)block, (uint32_t)dynamic_offset};
+        memcpy(table_out, header, sizeof(header));
+        for (int64_t page = 0; page < pages; page++) {
+            uint32_t value = (uint32_t)page;
+            memcpy(table_out + (9 + page) * 4, &value, 4);
+        }
+    }
+    return table_bytes;
+}

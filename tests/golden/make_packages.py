@@ -92,6 +92,54 @@ def compile_one(reference: Path, spec: ModelSpec, features, destination: Path) -
     (destination / "synthetic_spec.json").write_text(json.dumps(spec.to_json(), indent=2) + "\n")
 
 
+def compile_reference_fixture(reference: Path, destination: Path) -> None:
+    """The reference's own tiny test model (scripts/generate_tiny_test_model.py:28-99: 1 layer, hidden 16, 2 q /
+    1 kv heads, head 8, FFN 32, vocab 32, BF16 values ((i mod 29) - 14) / 29, tied lm_head, no MTP), rebuilt from
+    the formula so that the result can be compared with the package checked into the reference."""
+    import numpy as np
+
+    from llmoop_b200.safetensors_io import f32_to_bf16_bits, write_safetensors
+    from nerve.compiler_target import CompilerTarget
+    from nerve.model_compiler import compile_model
+
+    def tensor(shape, offset):
+        count = int(np.prod(shape))
+        values = np.arange(offset, offset + count, dtype=np.float32)
+        values = ((np.remainder(values, 29) - 14) / np.float32(29)).astype(np.float32)
+        return ("BF16", shape, f32_to_bf16_bits(values).reshape(shape))
+
+    ones = lambda n: ("BF16", (n,), f32_to_bf16_bits(np.ones(n, dtype=np.float32)))
+    tensors = {
+        "model.embed_tokens.weight": tensor((32, 16), 0), "model.norm.weight": ones(16),
+        "model.layers.0.input_layernorm.weight": ones(16), "model.layers.0.post_attention_layernorm.weight": ones(16),
+        "model.layers.0.self_attn.q_proj.weight": tensor((16, 16), 512), "model.layers.0.self_attn.k_proj.weight": tensor((8, 16), 768),
+        "model.layers.0.self_attn.v_proj.weight": tensor((8, 16), 896), "model.layers.0.self_attn.o_proj.weight": tensor((16, 16), 1024),
+        "model.layers.0.mlp.gate_proj.weight": tensor((32, 16), 1280), "model.layers.0.mlp.up_proj.weight": tensor((32, 16), 1792),
+        "model.layers.0.mlp.down_proj.weight": tensor((16, 32), 2304),
+    }
+    config = {
+        "architectures": ["TinyTestForCausalLM"], "model_type": "tiny_test", "dtype": "bfloat16", "torch_dtype": "bfloat16",
+        "hidden_size": 16, "intermediate_size": 32, "num_hidden_layers": 1, "num_attention_heads": 2, "num_key_value_heads": 1,
+        "head_dim": 8, "max_position_embeddings": 64, "rms_norm_eps": 1e-5, "rope_theta": 10_000.0, "hidden_act": "silu",
+        "vocab_size": 32, "bos_token_id": 1, "eos_token_id": 2, "pad_token_id": 0, "layer_types": ["full_attention"],
+    }
+    with tempfile.TemporaryDirectory(prefix="golden-src-") as temporary:
+        source = Path(temporary) / "source"
+        source.mkdir()
+        (source / "config.json").write_text(json.dumps(config, indent=2) + "\n")
+        (source / "generation_config.json").write_text(json.dumps({"do_sample": False, "bos_token_id": 1, "eos_token_id": 2, "pad_token_id": 0}, indent=2) + "\n")
+        write_safetensors(source / "model.safetensors", tensors, metadata={"format": "pt"})
+        vocabulary = {"[PAD]": 0, "[BOS]": 1, "[EOS]": 2, "[UNK]": 3, **{f"token_{index:02d}": index for index in range(4, 32)}}
+        (source / "tokenizer.json").write_text(json.dumps({
+            "version": "1.0", "truncation": None, "padding": None, "added_tokens": [], "normalizer": None,
+            "pre_tokenizer": {"type": "Whitespace"}, "post_processor": None, "decoder": None,
+            "model": {"type": "WordLevel", "vocab": vocabulary, "unk_token": "[UNK]"}}))
+        (source / "tokenizer_config.json").write_text(json.dumps({"bos_token": "[BOS]", "eos_token": "[EOS]", "pad_token": "[PAD]", "unk_token": "[UNK]"}, indent=2) + "\n")
+        shutil.rmtree(destination, ignore_errors=True)
+        compile_model(source, compiled_model_dir=destination, shader_source_dir=reference / "runtime-rs" / "shaders",
+                      target=CompilerTarget.for_features(BF16_FEATURES))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", type=Path, required=True)
@@ -106,6 +154,9 @@ def main() -> None:
             continue
         compile_one(args.reference, spec, features, args.out / spec.name)
         print("compiled", spec.name)
+    if not args.only or args.only == "reference_tiny_model":
+        compile_reference_fixture(args.reference, args.out / "reference_tiny_model")
+        print("compiled reference_tiny_model")
 
 
 if __name__ == "__main__":

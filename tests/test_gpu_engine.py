@@ -210,3 +210,25 @@ def test_mount_errors_are_reported_not_fatal(tmp_path):
         nb.Package(broken, capacity_tokens=64)
     with pytest.raises(nb.NerveError):
         nb.Package(GOLDEN / "tiny_int4_mtp_v16", capacity_tokens=100000)  # beyond max_context_activations
+
+
+def test_reference_tiny_model_greedy_decode_matches_oracle():
+    """The reference's own test fixture (1 layer, hidden 16, head 8, tied lm_head, no MTP decoder)."""
+    import llmoop_b200 as nb
+    from oracle.nerve_oracle import OracleStream
+
+    name = "reference_tiny_model"
+    opkg, oracle = _oracle(name)
+    prompt = _prompt(opkg.vocab, 9, seed=4)
+    ostream = OracleStream(opkg, 64)
+    expected = oracle.generate(ostream, prompt, 20, 0, collect_logits=True)
+    package = nb.Package(GOLDEN / name, capacity_tokens=64, page_tokens=16, max_streams=1, max_lanes=16, verify_level=2)
+    assert package.info["has_speculative_decoder"] == 0
+    engine = nb.Engine(package)
+    with pytest.raises(nb.NerveError, match="no mounted speculative decoder"):
+        engine.add_stream(9, speculative_draft_tokens=2)
+    engine.add_stream(1)
+    tokens, _ = engine.submit_input_event_until_idle(1, prompt, 20)
+    _assert_tokens_match(tokens, expected["tokens"], expected["logits"], oracle)
+    engine.close()
+    package.unmount()
