@@ -162,6 +162,14 @@ int32_t nerve_b200_debug_target_logits(nerve_b200_engine *engine, int64_t stream
 int32_t nerve_b200_op_linear_int4(const void *x_device, const void *qweight_device, const void *scales_device,
                                   void *y_device, const void *residual_device, int32_t lanes, int32_t n, int32_t k,
                                   int32_t group, void *stream);
+/* gate/up pair + silu_multiply_bf16.comp.template:30-52 in one launch: y = bf16(silu_bf16(bf16(x.Wg)) * bf16(x.Wu)). */
+int32_t nerve_b200_op_linear_int4_silu_pair(const void *x_device, const void *gate_qweight_device,
+                                            const void *gate_scales_device, const void *up_qweight_device,
+                                            const void *up_scales_device, void *y_device, int32_t lanes, int32_t n,
+                                            int32_t k, void *stream);
+/* Selects the INT4 kernel: 0 = register-prefetch kernel (default), 1 = bulk-copy pipelined kernel (used where
+ * k % 2048 == 0, otherwise the register kernel still runs). Process-wide; not to be changed while work is queued. */
+int32_t nerve_b200_set_int4_kernel(int32_t pipelined);
 /* linear_bf16.comp.template:38-95; to_f32 != 0 gives tied_output_projection_bf16.comp.template:33-91 (f32 * scale). */
 int32_t nerve_b200_op_linear_bf16(const void *x_device, const void *w_device, void *y_device,
                                   const void *residual_device, int32_t lanes, int32_t n, int32_t k, int32_t to_f32,

@@ -330,6 +330,20 @@ int32_t nerve_b200_op_linear_int4(const void *x, const void *qweight, const void
                        "nerve_b200_op_linear_int4");
 }
 
+int32_t nerve_b200_op_linear_int4_silu_pair(const void *x, const void *gate_q, const void *gate_s, const void *up_q, const void *up_s,
+                                            void *y, int32_t lanes, int32_t n, int32_t k, void *stream) {
+    return cuda_status(launch_linear_int4_silu_pair(static_cast<const uint16_t *>(x), static_cast<const uint32_t *>(gate_q),
+                                                    static_cast<const uint16_t *>(gate_s), static_cast<const uint32_t *>(up_q),
+                                                    static_cast<const uint16_t *>(up_s), static_cast<uint16_t *>(y), lanes, n, k,
+                                                    static_cast<cudaStream_t>(stream)),
+                       "nerve_b200_op_linear_int4_silu_pair");
+}
+
+int32_t nerve_b200_set_int4_kernel(int32_t pipelined) {
+    set_int4_stream_enabled(pipelined);
+    return NERVE_B200_OK;
+}
+
 int32_t nerve_b200_op_linear_bf16(const void *x, const void *w, void *y, const void *residual, int32_t lanes, int32_t n, int32_t k,
                                   int32_t to_f32, float scale, void *stream) {
     int epilogue = to_f32 ? EPILOGUE_F32_SCALED : (residual ? EPILOGUE_RESIDUAL_ROUNDED : EPILOGUE_BF16);

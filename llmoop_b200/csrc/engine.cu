@@ -247,6 +247,9 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     cuda_check(cudaMallocHost(&staging_, staging_bytes_), "cudaMallocHost");
     cuda_check(cudaMallocHost(&host_records_, lanes * 64 * sizeof(uint32_t)), "cudaMallocHost");
 
+    kernel_error_ = device_alloc(sizeof(int));
+    set_int4_error_flag(static_cast<int *>(kernel_error_.ptr));
+
     for (int slot = options.max_streams - 1; slot >= 0; slot--) free_slots_.push_back(slot);
     for (int page = model_->physical_pages() - 1; page >= 0; page--) free_pages_.push_back(page);
     page_refcount_.assign(model_->physical_pages(), 0);
@@ -255,10 +258,11 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
 
 Engine::~Engine() {
     cudaStreamSynchronize(cuda_stream_);
+    set_int4_error_flag(nullptr);
     for (auto &entry : signals_) cudaFree(entry.second.ptr);
     for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
                                  &records_, &argmax_scratch_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
-                                 &cycle_state_})
+                                 &cycle_state_, &kernel_error_})
         cudaFree(buffer->ptr);
     cudaFreeHost(staging_);
     cudaFreeHost(host_records_);
@@ -1186,7 +1190,12 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
         if (!any) break;
     }
     cuda_check(cudaEventRecord(run_end, cuda_stream_), "event record");
+    cuda_check(cudaMemcpyAsync(host_records_, kernel_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, cuda_stream_), "kernel status readback");
     synchronize("run synchronize");
+    if (host_records_[0] != 0) {
+        cuda_check(cudaMemsetAsync(kernel_error_.ptr, 0, sizeof(int), cuda_stream_), "kernel status reset");
+        fail("a pipelined kernel gave up waiting on its copy pipeline; results of this run are invalid");
+    }
     float device_ms = 0.0f;
     cuda_check(cudaEventElapsedTime(&device_ms, run_begin, run_end), "event elapsed");
     cudaEventDestroy(run_begin);

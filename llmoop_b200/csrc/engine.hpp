@@ -255,6 +255,7 @@ private:
     DeviceBuffer lane_tokens_, lane_positions_, lane_slots_;
     DeviceBuffer pending_hidden_;           // [max_streams][hidden]
     DeviceBuffer attention_scratch_;
+    DeviceBuffer kernel_error_;             // device word set by pipelined kernels whose bounded waits expired
     DeviceBuffer cycle_state_;              // device-side per-batch cycle arrays (see engine.cu)
     // Pinned staging arena for host->device uploads: every upload between two host synchronisations gets its
     // own region (an asynchronous copy reads the pinned source when it executes, not when it is enqueued).

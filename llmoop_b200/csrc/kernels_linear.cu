@@ -20,6 +20,8 @@
 // at 3 ALU ops per nibble pair.
 #include <mma.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -208,10 +210,13 @@ struct Int4Launch {
 
 constexpr int INT4_WARPS = 8;
 
-// RT row tiles (16 rows each) per CTA; SILU_PAIR: rt 0 = gate rows, rt 1 = the
-// same rows of the up projection, epilogue bf16(silu_bf16(bf16 gate) * bf16 up).
-template <int RT, bool SILU_PAIR>
-__global__ void __launch_bounds__(INT4_WARPS * 32)
+// RT row tiles (16 rows each) per CTA; SILU_PAIR: rt 0 = gate rows, rt 1 = the same rows of the up projection,
+// epilogue bf16(silu_bf16(bf16 gate) * bf16 up).  The 8 warps of a CTA split K by 128-column groups
+// (warp w takes groups w, w+8, ...) and keep STAGES groups of packed weights in flight in registers: with
+// ~1 us of loaded-memory latency a warp must have several KB outstanding for the SM to reach its share of HBM
+// bandwidth (Little's law: ~44 KB per SM at 6.5 TB/s).
+template <int RT, bool SILU_PAIR, int STAGES>
+__global__ void __launch_bounds__(INT4_WARPS * 32, 2)
 linear_int4_mma_kernel(const Int4Launch p) {
     __shared__ float reduce[INT4_WARPS][RT * 16][8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -252,66 +257,67 @@ linear_int4_mma_kernel(const Int4Launch p) {
 #pragma unroll
         for (int i = 0; i < 4; i++) acc[rt][i] = 0.0f;
 
-    // First weight fetch does not depend on the producer of x: issue it before the dependency wait.
-    int group = warp;
-    uint4 wq[RT][2];
-    if (group < groups) {
+    // Weights do not depend on the producer of x: the first STAGES groups are requested before the dependency wait.
+    uint4 wq[STAGES][RT][2];
 #pragma unroll
-        for (int rt = 0; rt < RT; rt++)
+    for (int s = 0; s < STAGES; s++) {
+        const int group = warp + s * INT4_WARPS;
+        if (group < groups) {
 #pragma unroll
-            for (int h = 0; h < 2; h++) wq[rt][h] = __ldg(reinterpret_cast<const uint4 *>(wrow[rt][h] + group * 16));
+            for (int rt = 0; rt < RT; rt++)
+#pragma unroll
+                for (int h = 0; h < 2; h++) wq[s][rt][h] = __ldg(reinterpret_cast<const uint4 *>(wrow[rt][h] + group * 16));
+        }
     }
     grid_dependency_wait();
 
-    for (; group < groups; group += INT4_WARPS) {
-        // prefetch the next group's weights (software pipelining, one stage)
-        uint4 wnext[RT][2];
-        const int next = group + INT4_WARPS;
-        if (next < groups) {
+    for (int base = warp; base < groups; base += INT4_WARPS * STAGES) {
 #pragma unroll
-            for (int rt = 0; rt < RT; rt++)
+        for (int s = 0; s < STAGES; s++) {
+            const int group = base + s * INT4_WARPS;
+            if (group >= groups) break;
+            // activations of lane g for this thread's 32 columns, permuted to match the nibble pairs
+            uint32_t bfrag[8][2];
+            if (lane_active) {
 #pragma unroll
-                for (int h = 0; h < 2; h++) wnext[rt][h] = __ldg(reinterpret_cast<const uint4 *>(wrow[rt][h] + next * 16));
-        }
-        // activations of lane g for this thread's 32 columns, permuted to match the nibble pairs
-        uint32_t bfrag[8][2];
-        if (lane_active) {
+                for (int word = 0; word < 4; word++) {
+                    uint4 xv = __ldg(reinterpret_cast<const uint4 *>(xrow + group * 128) + word);
+                    bfrag[2 * word][0] = __byte_perm(xv.x, xv.z, 0x5410);      // (v0, v4)
+                    bfrag[2 * word][1] = __byte_perm(xv.x, xv.z, 0x7632);      // (v1, v5)
+                    bfrag[2 * word + 1][0] = __byte_perm(xv.y, xv.w, 0x5410);  // (v2, v6)
+                    bfrag[2 * word + 1][1] = __byte_perm(xv.y, xv.w, 0x7632);  // (v3, v7)
+                }
+            } else {
 #pragma unroll
-            for (int word = 0; word < 4; word++) {
-                uint4 xv = __ldg(reinterpret_cast<const uint4 *>(xrow + group * 128) + word);
-                bfrag[2 * word][0] = __byte_perm(xv.x, xv.z, 0x5410);      // (v0, v4)
-                bfrag[2 * word][1] = __byte_perm(xv.x, xv.z, 0x7632);      // (v1, v5)
-                bfrag[2 * word + 1][0] = __byte_perm(xv.y, xv.w, 0x5410);  // (v2, v6)
-                bfrag[2 * word + 1][1] = __byte_perm(xv.y, xv.w, 0x7632);  // (v3, v7)
+                for (int step = 0; step < 8; step++) bfrag[step][0] = bfrag[step][1] = 0u;
             }
-        } else {
 #pragma unroll
-            for (int step = 0; step < 8; step++) bfrag[step][0] = bfrag[step][1] = 0u;
-        }
+            for (int rt = 0; rt < RT; rt++) {
+                float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const uint32_t wa[4] = {wq[s][rt][0].x, wq[s][rt][0].y, wq[s][rt][0].z, wq[s][rt][0].w};
+                const uint32_t wb[4] = {wq[s][rt][1].x, wq[s][rt][1].y, wq[s][rt][1].z, wq[s][rt][1].w};
 #pragma unroll
-        for (int rt = 0; rt < RT; rt++) {
-            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const uint32_t wa[4] = {wq[rt][0].x, wq[rt][0].y, wq[rt][0].z, wq[rt][0].w};
-            const uint32_t wb[4] = {wq[rt][1].x, wq[rt][1].y, wq[rt][1].z, wq[rt][1].w};
-#pragma unroll
-            for (int word = 0; word < 4; word++) {
-                mma_bf16_16816(c, dequant_pair(wa[word], 0), dequant_pair(wb[word], 0), dequant_pair(wa[word], 4),
-                               dequant_pair(wb[word], 4), bfrag[2 * word][0], bfrag[2 * word][1]);
-                mma_bf16_16816(c, dequant_pair(wa[word], 8), dequant_pair(wb[word], 8), dequant_pair(wa[word], 12),
-                               dequant_pair(wb[word], 12), bfrag[2 * word + 1][0], bfrag[2 * word + 1][1]);
+                for (int word = 0; word < 4; word++) {
+                    mma_bf16_16816(c, dequant_pair(wa[word], 0), dequant_pair(wb[word], 0), dequant_pair(wa[word], 4),
+                                   dequant_pair(wb[word], 4), bfrag[2 * word][0], bfrag[2 * word][1]);
+                    mma_bf16_16816(c, dequant_pair(wa[word], 8), dequant_pair(wb[word], 8), dequant_pair(wa[word], 12),
+                                   dequant_pair(wb[word], 12), bfrag[2 * word + 1][0], bfrag[2 * word + 1][1]);
+                }
+                float sa = bf16_bits_to_f32(srow[rt][0][group]);
+                float sb = bf16_bits_to_f32(srow[rt][1][group]);
+                acc[rt][0] = fmaf(c[0], sa, acc[rt][0]);
+                acc[rt][1] = fmaf(c[1], sa, acc[rt][1]);
+                acc[rt][2] = fmaf(c[2], sb, acc[rt][2]);
+                acc[rt][3] = fmaf(c[3], sb, acc[rt][3]);
             }
-            float sa = bf16_bits_to_f32(srow[rt][0][group]);
-            float sb = bf16_bits_to_f32(srow[rt][1][group]);
-            acc[rt][0] = fmaf(c[0], sa, acc[rt][0]);
-            acc[rt][1] = fmaf(c[1], sa, acc[rt][1]);
-            acc[rt][2] = fmaf(c[2], sb, acc[rt][2]);
-            acc[rt][3] = fmaf(c[3], sb, acc[rt][3]);
-        }
-        if (next < groups) {
+            // refill this stage's registers with the group STAGES rounds ahead
+            const int next = group + INT4_WARPS * STAGES;
+            if (next < groups) {
 #pragma unroll
-            for (int rt = 0; rt < RT; rt++)
+                for (int rt = 0; rt < RT; rt++)
 #pragma unroll
-                for (int h = 0; h < 2; h++) wq[rt][h] = wnext[rt][h];
+                    for (int h = 0; h < 2; h++) wq[s][rt][h] = __ldg(reinterpret_cast<const uint4 *>(wrow[rt][h] + next * 16));
+            }
         }
     }
     grid_launch_dependents();
@@ -370,11 +376,27 @@ static cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t
     return cudaLaunchKernelEx(&config, kernel, params);
 }
 
+static int *g_int4_error_flag = nullptr;
+static int g_int4_stream_enabled = -1;
+
+void set_int4_error_flag(int *device_word) { g_int4_error_flag = device_word; }
+void set_int4_stream_enabled(int enabled) { g_int4_stream_enabled = enabled ? 1 : 0; }
+
+static bool use_stream_kernel(int k) {
+    if (g_int4_stream_enabled < 0) {
+        const char *value = getenv("NERVE_B200_INT4_STREAM");
+        g_int4_stream_enabled = (value != nullptr && value[0] == '1') ? 1 : 0;
+    }
+    return g_int4_stream_enabled == 1 && linear_int4_stream_supported(k);
+}
+
 cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint32_t *const *qweights,
                                      const uint16_t *const *scales, uint16_t *const *ys, const int *ns,
                                      const uint16_t *residual, int lanes, int k, int epilogue, cudaStream_t stream) {
     if (lanes <= 0) return cudaSuccess;
     if (k % 128 != 0 || branches < 1 || branches > 3) return cudaErrorInvalidValue;
+    if (use_stream_kernel(k))
+        return launch_linear_int4_stream(x, branches, qweights, scales, ys, ns, residual, lanes, k, epilogue, g_int4_error_flag, stream);
     Int4Launch params = {};
     params.branches = branches;
     params.x = x;
@@ -384,16 +406,14 @@ cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint
     params.epilogue = epilogue;
     long total_rows = 0;
     for (int b = 0; b < branches; b++) total_rows += ns[b];
-    // Two row tiles per CTA once one tile per CTA would oversubscribe the resident slots (148 SMs x 8 CTAs).
-    const int rt = total_rows / 16 > 148 * 8 ? 2 : 1;
+    const int rt = 1;
     int tiles = 0;
     for (int b = 0; b < branches; b++) {
         params.branch[b] = Int4Branch{qweights[b], scales[b], ys[b], ns[b], tiles};
         tiles += (ns[b] + 16 * rt - 1) / (16 * rt);
     }
     dim3 grid(tiles, (lanes + 7) / 8);
-    if (rt == 2) return launch_pdl(linear_int4_mma_kernel<2, false>, grid, dim3(INT4_WARPS * 32), stream, params);
-    return launch_pdl(linear_int4_mma_kernel<1, false>, grid, dim3(INT4_WARPS * 32), stream, params);
+    return launch_pdl(linear_int4_mma_kernel<1, false, 4>, grid, dim3(INT4_WARPS * 32), stream, params);
 }
 
 cudaError_t launch_linear_int4(const uint16_t *x, const uint32_t *qweight, const uint16_t *scales, uint16_t *y,
@@ -410,6 +430,8 @@ cudaError_t launch_linear_int4_silu_pair(const uint16_t *x, const uint32_t *gate
                                          int k, cudaStream_t stream) {
     if (lanes <= 0) return cudaSuccess;
     if (k % 128 != 0) return cudaErrorInvalidValue;
+    if (use_stream_kernel(k))
+        return launch_linear_int4_stream_silu_pair(x, gate_q, gate_s, up_q, up_s, y, lanes, n, k, g_int4_error_flag, stream);
     Int4Launch params = {};
     params.branches = 2;
     params.x = x;
@@ -419,7 +441,7 @@ cudaError_t launch_linear_int4_silu_pair(const uint16_t *x, const uint32_t *gate
     params.branch[1] = Int4Branch{up_q, up_s, nullptr, n, 0};
     params.branch[2] = Int4Branch{nullptr, nullptr, y, n, 0};
     dim3 grid((n + 15) / 16, (lanes + 7) / 8);
-    return launch_pdl(linear_int4_mma_kernel<2, true>, grid, dim3(INT4_WARPS * 32), stream, params);
+    return launch_pdl(linear_int4_mma_kernel<2, true, 2>, grid, dim3(INT4_WARPS * 32), stream, params);
 }
 
 // ----------------------------------------------------------------------------- FP8 W8A8 (block-scaled)

@@ -21,18 +21,21 @@ def main():
     import llmoop_b200 as nb
 
     parser = argparse.ArgumentParser()
-    parser.add_argument("--op", default="int4", choices=["int4", "bf16"])
+    parser.add_argument("--op", default="int4", choices=["int4", "int4pair", "bf16"])
     parser.add_argument("--n", type=int, default=28672)
     parser.add_argument("--k", type=int, default=4096)
     parser.add_argument("--lanes", type=int, default=4)
     parser.add_argument("--iters", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--working-set-mb", type=int, default=512)
+    parser.add_argument("--register-kernel", action="store_true", help="use the register-prefetch INT4 kernel")
     args = parser.parse_args()
 
     lib = nb.library()
+    if args.register_kernel:
+        lib.nerve_b200_set_int4_kernel(0)
     n, k, lanes = args.n, args.k, args.lanes
-    if args.op == "int4":
+    if args.op in ("int4", "int4pair"):
         weight_bytes = n * k // 2
         scale_bytes = n * (k // 128) * 2
     else:
@@ -52,7 +55,12 @@ def main():
 
     def launch(index):
         w, s = weights[index % copies], scales[index % copies]
-        if args.op == "int4":
+        if args.op == "int4pair":
+            w2, s2 = weights[(index + 1) % copies], scales[(index + 1) % copies]
+            status = lib.nerve_b200_op_linear_int4_silu_pair(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(s.data_ptr()),
+                                                             ctypes.c_void_p(w2.data_ptr()), ctypes.c_void_p(s2.data_ptr()),
+                                                             ctypes.c_void_p(y.data_ptr()), lanes, n, k, handle)
+        elif args.op == "int4":
             status = lib.nerve_b200_op_linear_int4(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(s.data_ptr()),
                                                    ctypes.c_void_p(y.data_ptr()), None, lanes, n, k, 128, handle)
         else:
@@ -71,7 +79,7 @@ def main():
     end.record(stream)
     torch.cuda.synchronize()
     ms = begin.elapsed_time(end) / args.iters
-    algorithmic = weight_bytes + scale_bytes
+    algorithmic = (weight_bytes + scale_bytes) * (2 if args.op == "int4pair" else 1)
     print(json.dumps({"op": args.op, "n": n, "k": k, "lanes": lanes, "us_per_launch": ms * 1e3,
                       "algorithmic_bytes": algorithmic, "gbs": algorithmic / (ms * 1e-3) / 1e9, "weight_copies": copies}))
 

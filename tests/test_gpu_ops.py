@@ -43,9 +43,20 @@ def _ulp_report(got_bits, want_bits):
     return exact, worst
 
 
+@pytest.fixture
+def int4_kernel(request):
+    """Runs the test under one of the two INT4 kernels and restores the default afterwards."""
+    import llmoop_b200 as nb
+
+    nb.library().nerve_b200_set_int4_kernel(request.param)
+    yield request.param
+    nb.library().nerve_b200_set_int4_kernel(0)
+
+
+@pytest.mark.parametrize("int4_kernel", [0, 1], indirect=True)
 @pytest.mark.parametrize("lanes", [1, 4, 8, 11])
 @pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 4096), (4096, 14336), (272, 256)])
-def test_linear_int4_matches_oracle(lanes, n, k):
+def test_linear_int4_matches_oracle(lanes, n, k, int4_kernel):
     import torch
 
     import llmoop_b200 as nb
@@ -76,6 +87,44 @@ def test_linear_int4_matches_oracle(lanes, n, k):
     got = dy.cpu().numpy().view(np.uint16).reshape(lanes, n)
     exact, worst = _ulp_report(got, want_res)
     assert exact > 0.97, (exact, worst)
+
+
+@pytest.mark.parametrize("int4_kernel", [0, 1], indirect=True)
+@pytest.mark.parametrize("lanes", [1, 4, 7])
+@pytest.mark.parametrize("n,k", [(14336, 4096), (528, 2048), (96, 384)])
+def test_linear_int4_silu_pair_matches_oracle(lanes, n, k, int4_kernel):
+    """gate/up projections + rounded SiLU multiply in one launch against the oracle's
+    three separate steps (linear, linear, silu_multiply)."""
+    import torch
+
+    import llmoop_b200 as nb
+    from llmoop_b200.synth import quantize_int4_group
+    from oracle import nerve_oracle as orc
+
+    rng = np.random.default_rng(n * 17 + k + lanes)
+    x = _bf16(rng.standard_normal((lanes, k), dtype=np.float32))
+    parts = []
+    for _ in range(2):
+        weight = rng.standard_normal((n, k), dtype=np.float32) * 0.03
+        packed, scales = quantize_int4_group(weight)
+        out = np.empty((lanes, n), dtype=np.uint16)
+        orc.lib().orc_linear_int4_ct(orc._p(x, orc._u16p), orc._p(packed.view(np.uint32), orc._u32p),
+                                     orc._p(scales, orc._u16p), orc._p(out, orc._u16p), lanes, n, k, 128)
+        parts.append((packed, scales, out))
+    want = np.empty((lanes, n), dtype=np.uint16)
+    orc.lib().orc_silu_multiply(orc._p(parts[0][2], orc._u16p), orc._p(parts[1][2], orc._u16p), orc._p(want, orc._u16p),
+                                lanes * n)
+    dx = _dev(x)
+    dgq, dgs, duq, dus = _dev(parts[0][0]), _dev(parts[0][1]), _dev(parts[1][0]), _dev(parts[1][1])
+    dy = torch.zeros(lanes * n * 2, dtype=torch.uint8, device="cuda")
+    status = nb.library().nerve_b200_op_linear_int4_silu_pair(_ptr(dx), _ptr(dgq), _ptr(dgs), _ptr(duq), _ptr(dus),
+                                                              _ptr(dy), lanes, n, k, None)
+    assert status == 0, nb.library().nerve_b200_last_error()
+    torch.cuda.synchronize()
+    got = dy.cpu().numpy().view(np.uint16).reshape(lanes, n)
+    exact, worst = _ulp_report(got, want)
+    # a one-ulp difference in either projection moves the product by up to ~2 ulp
+    assert worst <= 3.0 and exact > 0.93, (exact, worst)
 
 
 @pytest.mark.parametrize("lanes", [1, 4, 9])
