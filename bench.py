@@ -269,7 +269,7 @@ def main():
 
     # natural-mode budget: one token per cycle when no draft is accepted, up to k+1 when all are
     budget = (warmup + steps) * (DRAFTS + 1) + 8
-    capacity = PROMPT_TOKENS + budget + 64
+    capacity = PROMPT_TOKENS + max(budget, EVENT_TOKENS + 8) + 64  # the context ring never wraps in this workload
     package = nb.Package(directory, device=local_rank, capacity_tokens=capacity, page_tokens=16, max_streams=1,
                          max_lanes=PROMPT_TOKENS, verify_level=0)
     info = package.info

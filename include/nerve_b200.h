@@ -68,6 +68,9 @@ typedef struct nerve_b200_package_info {
     uint64_t kv_bytes_per_token;        /* target KV bytes per context token */
     int32_t pages_per_stream, physical_pages, page_tokens;
     uint32_t eos_token_id;              /* first EOS id of config.json, 0xffffffff if none */
+    int32_t target_decode_stack;        /* 1 when the target layers run as one persistent kernel for batches <= 8 lanes */
+    int32_t draft_decode_stack;         /* same for the speculative decoder's layers */
+    uint64_t target_stack_weight_bytes; /* bytes one pass of that kernel streams (tile-major INT4 + scales + norms) */
 } nerve_b200_package_info;
 int32_t nerve_b200_package_describe(const nerve_b200_package *package, nerve_b200_package_info *out_info);
 
@@ -147,6 +150,15 @@ int32_t nerve_b200_engine_set_prefill_chunk(nerve_b200_engine *engine, int32_t t
 int32_t nerve_b200_engine_set_cycle_logging(nerve_b200_engine *engine, int32_t enabled);
 /* Records CUDA events around every INT4 linear launch (adds launch overhead; for roofline measurement only). */
 int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabled);
+/* Batches of at most 8 lanes of a dense INT4 g128 layer stack (the verify batch, draft and single-tick steps) run
+ * as one persistent kernel per stack; 0 selects the kernel-per-operator path for them as well.  Default: the
+ * value of NERVE_B200_DECODE_STACK in the environment (1 = on), else off.  No counterpart in the reference: its Vulkan
+ * runtime always records one dispatch per kernel (placed_stream_processor/temporal_prompt.rs:480-657). */
+int32_t nerve_b200_engine_set_decode_stack(nerve_b200_engine *engine, int32_t enabled);
+/* Profiling aid (no reference counterpart): with profiling on, CTA 0 of the persistent kernel stamps the GPU's
+ * nanosecond timer at each layer's start and after each of its six grid barriers; this copies the stamps of the
+ * last target-stack launch, [layers][8] (entries 7 unused).  *out_count = stamps available. */
+int32_t nerve_b200_engine_decode_stack_timing(nerve_b200_engine *engine, uint64_t *out_stamps, size_t max_stamps, size_t *out_count);
 /* Cycle log rows: {stream_id, start_tick, accepted, committed, emitted_count, width, emitted[8], targets[8]} as u64. */
 int32_t nerve_b200_engine_cycle_log(const nerve_b200_engine *engine, uint64_t *out_rows, size_t max_rows,
                                     size_t *out_count);

@@ -106,6 +106,9 @@ int32_t nerve_b200_package_describe(const nerve_b200_package *package, nerve_b20
         out->physical_pages = model.physical_pages();
         out->page_tokens = model.options().page_tokens;
         out->eos_token_id = plan.eos_token_ids.empty() ? 0xffffffffu : plan.eos_token_ids[0];
+        out->target_decode_stack = model.target_stack().available ? 1 : 0;
+        out->draft_decode_stack = model.draft_stack().available ? 1 : 0;
+        out->target_stack_weight_bytes = model.target_stack().weight_bytes;
     });
 }
 
@@ -214,6 +217,22 @@ int32_t nerve_b200_engine_enqueue(nerve_b200_engine *engine, int64_t stream_id, 
 int32_t nerve_b200_engine_run_until_idle(nerve_b200_engine *engine, nerve_b200_output_callback on_output, void *user,
                                          nerve_b200_run_report *out) {
     return nerve_b200_engine_run(engine, 0, on_output, user, out);
+}
+
+int32_t nerve_b200_engine_set_decode_stack(nerve_b200_engine *engine, int32_t enabled) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        engine->engine->set_decode_stack(enabled != 0);
+    });
+}
+
+int32_t nerve_b200_engine_decode_stack_timing(nerve_b200_engine *engine, uint64_t *out_stamps, size_t max_stamps, size_t *out_count) {
+    return guarded([&] {
+        require(engine && out_count, "null argument");
+        std::vector<unsigned long long> stamps = engine->engine->decode_stack_timing();
+        *out_count = stamps.size();
+        for (size_t i = 0; i < stamps.size() && i < max_stamps && out_stamps; i++) out_stamps[i] = stamps[i];
+    });
 }
 
 int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabled) {

@@ -3,6 +3,8 @@
 #include <algorithm>
 #include <chrono>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <stdexcept>
 
@@ -92,6 +94,12 @@ std::shared_ptr<MountedModel> MountedModel::mount(const std::string &path, const
     for (const ComponentPlan &layer : plan.draft_layers) add_pool(layer);
     model->block_table_ = device_alloc(sizeof(int32_t) * options.max_streams * model->pages_per_stream_);
     model->build_rope_tables();
+    {
+        int target_kv_layers = 0;
+        for (const ComponentPlan &layer : plan.layers) target_kv_layers += layer.has_kv ? 1 : 0;
+        model->build_stack(plan.layers, 0, model->target_stack_);
+        if (plan.has_draft) model->build_stack(plan.draft_layers, target_kv_layers, model->draft_stack_);
+    }
     return model;
 }
 
@@ -99,6 +107,10 @@ MountedModel::~MountedModel() {
     for (auto &entry : tensors_) cudaFree(entry.second.ptr);
     for (auto &pool : kv_pools_) cudaFree(pool.ptr);
     for (auto &entry : rope_tables_) cudaFree(entry.second.ptr);
+    for (StackPlan *stack : {&target_stack_, &draft_stack_}) {
+        for (DeviceBuffer &buffer : stack->storage) cudaFree(buffer.ptr);
+        cudaFree(stack->device_layers.ptr);
+    }
     cudaFree(block_table_.ptr);
 }
 
@@ -162,6 +174,127 @@ void MountedModel::build_rope_tables() {
     };
     for (const ComponentPlan &layer : plan.layers) add(layer);
     for (const ComponentPlan &layer : plan.draft_layers) add(layer);
+}
+
+// Recognises the kernel list of a dense Llama-style layer whose seven linears are INT4 g128
+// (rms_norm, q, k, v, rope q, rope k, append attention, o, residual, rms_norm, gate, up, silu*up, down, residual)
+// and makes the tile-major weight copies the persistent decode kernel streams.
+void MountedModel::build_stack(const std::vector<ComponentPlan> &layers, int first_kv_index, StackPlan &out) {
+    out = StackPlan{};
+    auto refuse = [&](const std::string &why) {
+        out.reason = why;
+        if (getenv("NERVE_B200_VERBOSE")) fprintf(stderr, "nerve_b200: decode stack kernel not used: %s\n", why.c_str());
+    };
+    if (layers.empty()) return refuse("no layers");
+    auto int4 = [](const OpSpec &op) {
+        return op.kind == OpKind::Linear && op.weights.size() == 1 && op.weights[0].storage == TensorStorage::INT4_CT &&
+               op.weights[0].group == 128;
+    };
+    static const OpKind expected[15] = {OpKind::RmsNorm, OpKind::Linear, OpKind::Linear, OpKind::Linear, OpKind::Rope, OpKind::Rope,
+                                        OpKind::AppendAttention, OpKind::Linear, OpKind::ResidualAdd, OpKind::RmsNorm, OpKind::Linear,
+                                        OpKind::Linear, OpKind::SiluMultiply, OpKind::Linear, OpKind::ResidualAdd};
+    StackShape shape{};
+    int kv_index = first_kv_index;
+    std::vector<StackLayer> built;
+    std::vector<DeviceBuffer> storage;
+    uint64_t bytes = 0;
+    auto drop = [&]() {
+        for (DeviceBuffer &buffer : storage) cudaFree(buffer.ptr);
+    };
+    for (size_t index = 0; index < layers.size(); index++) {
+        const ComponentPlan &layer = layers[index];
+        if (layer.ops.size() != 15 || !layer.has_kv || layer.boundary_inputs.size() != 1) return drop(), refuse("layer is not the dense 15-kernel form");
+        for (int i = 0; i < 15; i++)
+            if (layer.ops[i].kind != expected[i]) return drop(), refuse("layer kernel " + std::to_string(i) + " differs from the dense form");
+        const OpSpec &norm1 = layer.ops[0], &q = layer.ops[1], &k = layer.ops[2], &v = layer.ops[3], &rope_q = layer.ops[4], &rope_k = layer.ops[5],
+                     &attention = layer.ops[6], &o = layer.ops[7], &add1 = layer.ops[8], &norm2 = layer.ops[9], &gate = layer.ops[10],
+                     &up = layer.ops[11], &silu = layer.ops[12], &down = layer.ops[13], &add2 = layer.ops[14];
+        for (const OpSpec *linear : {&q, &k, &v, &o, &gate, &up, &down})
+            if (!int4(*linear)) return drop(), refuse("a linear of the layer is not INT4 g128");
+        const std::string &input = layer.boundary_inputs[0];
+        auto is_pair = [](const OpSpec &add, const std::string &a, const std::string &b) {
+            return add.inputs.size() == 2 && ((add.inputs[0] == a && add.inputs[1] == b) || (add.inputs[0] == b && add.inputs[1] == a));
+        };
+        bool wired = norm1.inputs[0] == input && q.inputs[0] == norm1.outputs[0] && k.inputs[0] == norm1.outputs[0] &&
+                     v.inputs[0] == norm1.outputs[0] && rope_q.inputs[0] == q.outputs[0] && rope_k.inputs[0] == k.outputs[0] &&
+                     attention.inputs.size() >= 3 && attention.inputs[0] == rope_q.outputs[0] && attention.inputs[1] == rope_k.outputs[0] &&
+                     attention.inputs[2] == v.outputs[0] && o.inputs[0] == attention.outputs[0] && is_pair(add1, o.outputs[0], input) &&
+                     norm2.inputs[0] == add1.outputs[0] && gate.inputs[0] == norm2.outputs[0] && up.inputs[0] == norm2.outputs[0] &&
+                     silu.inputs.size() == 2 && silu.inputs[0] == gate.outputs[0] && silu.inputs[1] == up.outputs[0] &&
+                     down.inputs[0] == silu.outputs[0] && is_pair(add2, down.outputs[0], add1.outputs[0]) &&
+                     add2.outputs[0] == layer.boundary_output;
+        if (!wired) return drop(), refuse("layer wiring differs from the dense form");
+        if (rope_q.rope.size() != 1 || rope_k.rope.size() != 1) return drop(), refuse("rotary attributes missing");
+        const RopeAttrs &rq = rope_q.rope[0], &rk = rope_k.rope[0];
+        StackShape here{};
+        here.hidden = static_cast<int>(q.weights[0].k);
+        here.q_heads = attention.q_heads;
+        here.kv_heads = attention.kv_heads;
+        here.head_width = attention.head_width;
+        here.ffn = static_cast<int>(gate.weights[0].n);
+        here.eps = norm1.eps;
+        here.norm_offset = norm1.weight_offset;
+        here.attention_scale = attention.attention_scale;
+        bool dims = rq.head_width == here.head_width && rk.head_width == here.head_width && rq.rotary_width == here.head_width &&
+                    rk.rotary_width == here.head_width && !rq.interleaved && !rk.interleaved && float_bits(rq.theta) == float_bits(rk.theta) &&
+                    rq.heads == here.q_heads && rk.heads == here.kv_heads && q.weights[0].n == int64_t(here.q_heads) * here.head_width &&
+                    k.weights[0].n == int64_t(here.kv_heads) * here.head_width && v.weights[0].n == k.weights[0].n &&
+                    k.weights[0].k == here.hidden && v.weights[0].k == here.hidden && o.weights[0].k == q.weights[0].n &&
+                    o.weights[0].n == here.hidden && gate.weights[0].k == here.hidden && up.weights[0].k == here.hidden &&
+                    up.weights[0].n == here.ffn && down.weights[0].k == here.ffn && down.weights[0].n == here.hidden &&
+                    float_bits(norm2.eps) == float_bits(norm1.eps) && float_bits(norm2.weight_offset) == float_bits(norm1.weight_offset) &&
+                    here.head_width % 16 == 0 && here.hidden % 128 == 0 && here.ffn % 128 == 0 && (here.q_heads * here.head_width) % 128 == 0 &&
+                    layer.kv_heads == here.kv_heads && layer.head_width == here.head_width;
+        if (!dims) return drop(), refuse("layer dimensions or rotary form are outside the decode stack kernel");
+        here.rope_table = rope_table(rq.theta, rq.rotary_width);
+        here.rope_positions = rope_positions_;
+        if (index == 0) shape = here;
+        else if (std::memcmp(&shape, &here, sizeof(StackShape)) != 0) return drop(), refuse("layers differ in shape");
+        size_t unused = 0;
+        if (!decode_stack_supported(shape, 1, &unused)) return drop(), refuse("no decode stack kernel instance for this head shape");
+
+        auto tiled = [&](std::initializer_list<const OpSpec *> sources, bool pair, bool rope_first_two) {
+            RelayoutSegment segments[3];
+            int count = 0, tiles = 0;
+            const int kk = static_cast<int>((*sources.begin())->weights[0].k);
+            for (const OpSpec *source : sources) {
+                const WeightRef &w = source->weights[0];
+                segments[count].qweight = static_cast<const uint32_t *>(tensor(w.tensor));
+                segments[count].scales = static_cast<const uint16_t *>(tensor(w.scale));
+                segments[count].rows = static_cast<int>(w.n);
+                segments[count].rope_head_width = (rope_first_two && count < 2) ? here.head_width : 0;
+                if (!pair || count == 0) tiles += static_cast<int>(w.n) / 16;
+                count++;
+            }
+            const int rt = pair ? 2 : 1, groups = kk / 128;
+            DeviceBuffer weights = device_alloc(static_cast<size_t>(tiles) * groups * rt * 64 * sizeof(uint4), false);
+            DeviceBuffer scales = device_alloc(static_cast<size_t>(tiles) * groups * rt * 8 * sizeof(uint32_t), false);
+            storage.push_back(weights);
+            storage.push_back(scales);
+            cuda_check(launch_int4_tile_major(segments, count, pair, kk, static_cast<uint4 *>(weights.ptr), static_cast<uint32_t *>(scales.ptr), nullptr),
+                       "tile-major INT4 copy");
+            bytes += weights.bytes + scales.bytes;
+            return TiledInt4{static_cast<const uint4 *>(weights.ptr), static_cast<const uint32_t *>(scales.ptr), tiles, groups};
+        };
+        StackLayer spec{};
+        spec.qkv = tiled({&q, &k, &v}, false, true);
+        spec.o = tiled({&o}, false, false);
+        spec.gate_up = tiled({&gate, &up}, true, false);
+        spec.down = tiled({&down}, false, false);
+        spec.input_norm = static_cast<const uint16_t *>(tensor(norm1.norm_weights[0]));
+        spec.post_norm = static_cast<const uint16_t *>(tensor(norm2.norm_weights[0]));
+        spec.kv = kv_layer(kv_index++);
+        bytes += 2 * static_cast<uint64_t>(here.hidden) * 2;
+        built.push_back(spec);
+    }
+    cuda_check(cudaDeviceSynchronize(), "tile-major INT4 copies");
+    out.available = true;
+    out.shape = shape;
+    out.layers = built;
+    out.storage = storage;
+    out.weight_bytes = bytes;
+    out.device_layers = device_alloc(built.size() * sizeof(StackLayer), false);
+    cuda_check(cudaMemcpy(out.device_layers.ptr, built.data(), built.size() * sizeof(StackLayer), cudaMemcpyHostToDevice), "stack layer table upload");
 }
 
 const uint32_t *MountedModel::rope_table(float theta, int rotary) const {
@@ -249,6 +382,23 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
 
     kernel_error_ = device_alloc(sizeof(int));
     set_int4_error_flag(static_cast<int *>(kernel_error_.ptr));
+    {
+        size_t q_width = 0, ffn = 0;
+        for (const StackPlan *stack : {&model_->target_stack(), &model_->draft_stack()})
+            if (stack->available) {
+                q_width = std::max<size_t>(q_width, static_cast<size_t>(stack->shape.q_heads) * stack->shape.head_width);
+                ffn = std::max<size_t>(ffn, stack->shape.ffn);
+            }
+        if (q_width != 0) {
+            stack_q_ = device_alloc(8 * q_width * 2);
+            stack_attention_out_ = device_alloc(8 * q_width * 2);
+            stack_activation_ = device_alloc(8 * ffn * 2);
+            stack_barrier_ = device_alloc(2 * sizeof(unsigned int));
+            stack_timing_ = device_alloc(std::max<size_t>(1, plan.layers.size()) * 8 * sizeof(unsigned long long));
+        }
+        const char *value = getenv("NERVE_B200_DECODE_STACK");
+        if (value != nullptr) stack_enabled_ = value[0] == '1';
+    }
 
     for (int slot = options.max_streams - 1; slot >= 0; slot--) free_slots_.push_back(slot);
     for (int page = model_->physical_pages() - 1; page >= 0; page--) free_pages_.push_back(page);
@@ -262,7 +412,7 @@ Engine::~Engine() {
     for (auto &entry : signals_) cudaFree(entry.second.ptr);
     for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
                                  &records_, &argmax_scratch_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
-                                 &cycle_state_, &kernel_error_})
+                                 &cycle_state_, &kernel_error_, &stack_q_, &stack_attention_out_, &stack_activation_, &stack_barrier_, &stack_timing_})
         cudaFree(buffer->ptr);
     cudaFreeHost(staging_);
     cudaFreeHost(host_records_);
@@ -776,6 +926,38 @@ void Engine::run_phase(const std::vector<int> &key, const std::function<void()> 
     counters_.kernel_launches += entry.kernel_nodes;
 }
 
+// Runs a whole layer stack over `hidden` ([lanes][hidden], in place) with the persistent decode kernel when the
+// stack and the batch qualify; false = the caller runs the layers kernel by kernel.
+bool Engine::run_stack(const StackPlan &stack, int lanes, void *hidden) {
+    if (!stack_enabled_ || !stack.available || lanes < 1 || lanes > 8 || current_width_ <= 0 || lanes % current_width_ != 0) return false;
+    size_t smem = 0;
+    if (!decode_stack_supported(stack.shape, lanes, &smem)) return false;
+    StackBuffers buffers{};
+    buffers.hidden = static_cast<uint16_t *>(hidden);
+    buffers.q = static_cast<uint16_t *>(stack_q_.ptr);
+    buffers.attention_scratch = static_cast<float *>(attention_scratch_.ptr);
+    buffers.attention_out = static_cast<uint16_t *>(stack_attention_out_.ptr);
+    buffers.activation = static_cast<uint16_t *>(stack_activation_.ptr);
+    buffers.barrier = static_cast<unsigned int *>(stack_barrier_.ptr);
+    buffers.error_flag = static_cast<int *>(kernel_error_.ptr);
+    buffers.timing = (profile_ && &stack == &model_->target_stack()) ? static_cast<unsigned long long *>(stack_timing_.ptr) : nullptr;
+    profile_begin(stack.weight_bytes);
+    check(launch_decode_stack(static_cast<const StackLayer *>(stack.device_layers.ptr), static_cast<int>(stack.layers.size()), stack.shape,
+                              buffers, current_lanes_, lanes, current_width_, split_tokens_, current_splits_, cuda_stream_),
+          "decode stack");
+    profile_end();
+    return true;
+}
+
+std::vector<unsigned long long> Engine::decode_stack_timing() {
+    std::vector<unsigned long long> stamps;
+    if (!stack_timing_.ptr || !model_->target_stack().available) return stamps;
+    stamps.resize(model_->target_stack().layers.size() * 8);
+    cuda_check(cudaStreamSynchronize(cuda_stream_), "stream synchronize");
+    cuda_check(cudaMemcpy(stamps.data(), stack_timing_.ptr, stamps.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost), "timing readback");
+    return stamps;
+}
+
 void Engine::target_forward(int lanes, bool want_logits) {
     const ModelPlan &plan = model_->plan();
     check(launch_embedding(static_cast<const uint16_t *>(model_->tensor(plan.embedding_tensor)), current_tokens_,
@@ -783,12 +965,14 @@ void Engine::target_forward(int lanes, bool want_logits) {
                            plan.embedding_scale, cuda_stream_),
           "embedding");
     void *input = frame_a_.ptr, *output = frame_b_.ptr;
-    int kv_index = 0;
-    for (const ComponentPlan &layer : plan.layers) {
-        std::map<std::string, void *> bound{{layer.boundary_inputs.at(0), input}};
-        run_component(layer, layer.has_kv ? kv_index : -1, lanes, bound, output);
-        if (layer.has_kv) kv_index++;
-        std::swap(input, output);
+    if (!run_stack(model_->target_stack(), lanes, input)) {
+        int kv_index = 0;
+        for (const ComponentPlan &layer : plan.layers) {
+            std::map<std::string, void *> bound{{layer.boundary_inputs.at(0), input}};
+            run_component(layer, layer.has_kv ? kv_index : -1, lanes, bound, output);
+            if (layer.has_kv) kv_index++;
+            std::swap(input, output);
+        }
     }
     check(launch_rms_norm(static_cast<const uint16_t *>(input), static_cast<const uint16_t *>(model_->tensor(plan.output.norm_tensor)),
                           static_cast<uint16_t *>(normalized_.ptr), lanes, static_cast<int>(plan.hidden), plan.output.eps,
@@ -816,13 +1000,15 @@ void Engine::draft_forward(int lanes, const uint16_t *hidden_in, bool want_logit
                                                 {plan.adapter_hidden_signal, const_cast<uint16_t *>(hidden_in)}};
     run_component(plan.draft_adapter, -1, lanes, adapter_bound, frame_a_.ptr);
     void *input = frame_a_.ptr, *output = frame_b_.ptr;
-    int kv_index = 0;
-    for (const ComponentPlan &layer : plan.layers) kv_index += layer.has_kv ? 1 : 0;
-    for (const ComponentPlan &layer : plan.draft_layers) {
-        std::map<std::string, void *> bound{{layer.boundary_inputs.at(0), input}};
-        run_component(layer, layer.has_kv ? kv_index : -1, lanes, bound, output);
-        if (layer.has_kv) kv_index++;
-        std::swap(input, output);
+    if (!run_stack(model_->draft_stack(), lanes, input)) {
+        int kv_index = 0;
+        for (const ComponentPlan &layer : plan.layers) kv_index += layer.has_kv ? 1 : 0;
+        for (const ComponentPlan &layer : plan.draft_layers) {
+            std::map<std::string, void *> bound{{layer.boundary_inputs.at(0), input}};
+            run_component(layer, layer.has_kv ? kv_index : -1, lanes, bound, output);
+            if (layer.has_kv) kv_index++;
+            std::swap(input, output);
+        }
     }
     if (!want_logits) return;
     check(launch_rms_norm(static_cast<const uint16_t *>(input), static_cast<const uint16_t *>(model_->tensor(plan.draft_output.norm_tensor)),
@@ -1193,8 +1379,11 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
     cuda_check(cudaMemcpyAsync(host_records_, kernel_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, cuda_stream_), "kernel status readback");
     synchronize("run synchronize");
     if (host_records_[0] != 0) {
+        const int code = static_cast<int>(host_records_[0]);
         cuda_check(cudaMemsetAsync(kernel_error_.ptr, 0, sizeof(int), cuda_stream_), "kernel status reset");
-        fail("a pipelined kernel gave up waiting on its copy pipeline; results of this run are invalid");
+        if (stack_barrier_.ptr) cuda_check(cudaMemsetAsync(stack_barrier_.ptr, 0, stack_barrier_.bytes, cuda_stream_), "barrier reset");
+        fail(code == 2 ? "the decode stack kernel gave up waiting at a grid barrier; results of this run are invalid"
+                       : "a pipelined kernel gave up waiting on its copy pipeline; results of this run are invalid");
     }
     float device_ms = 0.0f;
     cuda_check(cudaEventElapsedTime(&device_ms, run_begin, run_end), "event elapsed");

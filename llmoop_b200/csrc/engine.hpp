@@ -48,6 +48,18 @@ struct DeviceBuffer {
     size_t bytes = 0;
 };
 
+// Tile-major INT4 copies and per-layer descriptors of a layer stack the persistent decode kernel can run
+// (kernels_stack.cu); `available` is false when the stack does not have the dense INT4 Llama layer shape.
+struct StackPlan {
+    bool available = false;
+    std::string reason;                 // why not, for diagnostics
+    StackShape shape{};
+    std::vector<StackLayer> layers;     // host copy of the device array
+    DeviceBuffer device_layers;
+    std::vector<DeviceBuffer> storage;  // tile-major weights and scales
+    uint64_t weight_bytes = 0;          // bytes one pass over the stack streams
+};
+
 struct ExecCounters {
     uint64_t kernel_launches = 0;
     uint64_t graph_launches = 0;
@@ -81,11 +93,14 @@ public:
     uint64_t target_step_weight_bytes() const { return target_step_bytes_; }
     uint64_t draft_step_weight_bytes() const { return draft_step_bytes_; }
     uint64_t kv_bytes_per_token() const { return kv_bytes_per_token_; }
+    const StackPlan &target_stack() const { return target_stack_; }
+    const StackPlan &draft_stack() const { return draft_stack_; }
 
 private:
     MountedModel() = default;
     void upload_tensors();
     void build_rope_tables();
+    void build_stack(const std::vector<ComponentPlan> &layers, int first_kv_index, StackPlan &out);
 
     std::shared_ptr<HostPackage> package_;
     MountOptions options_;
@@ -98,6 +113,7 @@ private:
     int pages_per_stream_ = 0, physical_pages_ = 0;
     std::map<std::pair<uint32_t, int>, DeviceBuffer> rope_tables_;  // (theta bits, rotary) -> table
     uint32_t rope_positions_ = 0;
+    StackPlan target_stack_, draft_stack_;
 };
 
 struct SamplerConfig {
@@ -171,6 +187,12 @@ public:
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
     void set_cycle_logging(bool enabled) { log_cycles_ = enabled; }
     void set_use_graphs(bool enabled) { use_graphs_ = enabled; }
+    // The persistent decode stack kernel serves batches of at most 8 lanes of dense INT4 stacks; off (the
+    // default until it is the faster of the two) = the kernel-per-operator path for everything.
+    void set_decode_stack(bool enabled) { stack_enabled_ = enabled; }
+    // Profiling aid: nanosecond stamps CTA 0 took at the phase boundaries of the target stack's last launch
+    // ([layers][8]; stamp 0 = layer start, 1..6 = after each grid barrier).  Empty when the stack kernel is not in use.
+    std::vector<unsigned long long> decode_stack_timing();
     void set_prefill_chunk(int tokens) { prefill_chunk_ = tokens; }
 
     // Test hook: run the target over `tokens` at consecutive ticks starting at the stream's next tick WITHOUT
@@ -256,6 +278,10 @@ private:
     DeviceBuffer pending_hidden_;           // [max_streams][hidden]
     DeviceBuffer attention_scratch_;
     DeviceBuffer kernel_error_;             // device word set by pipelined kernels whose bounded waits expired
+    // persistent decode stack workspaces ([8 lanes][width]) and its two barrier words
+    DeviceBuffer stack_q_, stack_attention_out_, stack_activation_, stack_barrier_, stack_timing_;
+    bool stack_enabled_ = false;
+    bool run_stack(const StackPlan &stack, int lanes, void *hidden);
     DeviceBuffer cycle_state_;              // device-side per-batch cycle arrays (see engine.cu)
     // Pinned staging arena for host->device uploads: every upload between two host synchronisations gets its
     // own region (an asynchronous copy reads the pinned source when it executes, not when it is enqueued).

@@ -120,6 +120,55 @@ void set_int4_error_flag(int *device_word);
 // 0 = register-prefetch kernel (default), 1 = bulk-copy pipelined kernel; NERVE_B200_INT4_STREAM=1 selects the latter.
 void set_int4_stream_enabled(int enabled);
 
+// ---- persistent decode stack (kernels_stack.cu) ----
+// One cooperative launch runs a whole stack of dense INT4 g128 Llama-style layers for a batch of at most 8 lanes:
+// every CTA (one per SM) streams its share of each weight matrix while grid-wide barriers separate the phases
+// of a layer.  Weights are read from a tile-major copy made at mount (see launch_int4_tile_major).
+struct TiledInt4 {
+    const uint4 *weights;     // [tile][group][rt][half][32] uint4: 16 rows x 128 columns per (tile, group, rt)
+    const uint32_t *scales;   // [tile][group][rt][8]: bf16 scale of row g | scale of row g + 8 << 16
+    int tiles;                // 16-row tiles (tiles of a gate/up pair hold 16 gate rows and the same 16 up rows)
+    int groups;               // K / 128
+};
+struct StackLayer {
+    TiledInt4 qkv, o, gate_up, down;
+    const uint16_t *input_norm, *post_norm;
+    KvLayer kv;
+};
+struct StackShape {
+    int hidden, q_heads, kv_heads, head_width, ffn;
+    float eps, norm_offset, attention_scale;
+    const uint32_t *rope_table;  // [position][head_width / 2] packed (sin << 16 | cos) bf16
+    uint32_t rope_positions;
+};
+struct StackBuffers {
+    uint16_t *hidden;            // [lanes][hidden] residual stream, updated in place
+    uint16_t *q;                 // [lanes][q_heads * head_width]
+    float *attention_scratch;    // split partials, attention_scratch_bytes()
+    uint16_t *attention_out;     // [lanes][q_heads * head_width]
+    uint16_t *activation;        // [lanes][ffn]
+    unsigned int *barrier;       // two words, zero before the first launch
+    int *error_flag;             // set when a bounded barrier wait expires
+    unsigned long long *timing;  // optional [layers][8] nanosecond stamps of CTA 0 (phase boundaries), or nullptr
+};
+// One source matrix of a tile-major copy.  rope_head_width > 0 orders the rows of every head so that MMA rows
+// r and r + 8 of a tile are the rotary partners (d, d + head_width / 2).
+struct RelayoutSegment {
+    const uint32_t *qweight;
+    const uint16_t *scales;
+    int rows;
+    int rope_head_width;
+};
+// Segments share K; they are laid out one after the other by tiles, or - with `pair` - segment 0 and 1 are
+// interleaved tile by tile (gate, up).  Every segment's row count must be a multiple of 16.
+cudaError_t launch_int4_tile_major(const RelayoutSegment *segments, int count, bool pair, int k, uint4 *weights_out,
+                                   uint32_t *scales_out, cudaStream_t stream);
+// Whether the stack kernel is built for this shape and batch; *smem_bytes receives its dynamic shared memory.
+bool decode_stack_supported(const StackShape &shape, int lanes, size_t *smem_bytes);
+cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count, const StackShape &shape,
+                                const StackBuffers &buffers, const LaneTable &lanes_meta, int lanes, int lanes_per_stream,
+                                int split_tokens, int max_splits, cudaStream_t stream);
+
 // ---- glue of the speculative cycle (all tiny) ----
 // dst[i] = src[index[i]] for rows of `width` bf16.
 cudaError_t launch_gather_rows(const uint16_t *src, const int32_t *index, uint16_t *dst, int rows, int width,

@@ -34,7 +34,8 @@ class _PackageInfo(ctypes.Structure):
         ("weight_bytes", ctypes.c_uint64), ("verify_step_weight_bytes", ctypes.c_uint64),
         ("draft_step_weight_bytes", ctypes.c_uint64), ("kv_bytes_per_token", ctypes.c_uint64),
         ("pages_per_stream", ctypes.c_int32), ("physical_pages", ctypes.c_int32), ("page_tokens", ctypes.c_int32),
-        ("eos_token_id", ctypes.c_uint32),
+        ("eos_token_id", ctypes.c_uint32), ("target_decode_stack", ctypes.c_int32), ("draft_decode_stack", ctypes.c_int32),
+        ("target_stack_weight_bytes", ctypes.c_uint64),
     ]
 
 
@@ -65,7 +66,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_destroy", "nerve_b200_engine_add_stream", "nerve_b200_engine_fork_stream",
     "nerve_b200_engine_reset_stream", "nerve_b200_engine_remove_stream", "nerve_b200_engine_interrupt_stream",
     "nerve_b200_engine_enqueue", "nerve_b200_engine_run_until_idle", "nerve_b200_engine_run",
-    "nerve_b200_engine_set_profiling", "nerve_b200_engine_stream_tick",
+    "nerve_b200_engine_set_profiling", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
     "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair", "nerve_b200_set_int4_kernel",
@@ -202,6 +203,19 @@ class Engine:
     def run_until_idle(self, on_output=None):
         """Returns (outputs, report): outputs is a list of (stream_id, token_id, source_stream_tick, output_index)."""
         return self.run(0, on_output)
+
+    def set_decode_stack(self, enabled: bool):
+        _check(library().nerve_b200_engine_set_decode_stack(self._handle, int(enabled)))
+
+    def decode_stack_timing(self):
+        """[layers][8] nanosecond stamps of the last profiled target-stack launch (see the header)."""
+        import numpy as np
+
+        count = ctypes.c_size_t(0)
+        _check(library().nerve_b200_engine_decode_stack_timing(self._handle, None, ctypes.c_size_t(0), ctypes.byref(count)))
+        stamps = (ctypes.c_uint64 * max(1, count.value))()
+        _check(library().nerve_b200_engine_decode_stack_timing(self._handle, stamps, ctypes.c_size_t(count.value), ctypes.byref(count)))
+        return np.array(stamps[:count.value], dtype=np.uint64).reshape(-1, 8)
 
     def set_profiling(self, enabled: bool):
         _check(library().nerve_b200_engine_set_profiling(self._handle, int(enabled)))

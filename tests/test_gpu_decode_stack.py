@@ -1,0 +1,135 @@
+"""The persistent decode stack kernel (one launch per layer stack for batches of at most 8 lanes) against the CPU
+oracle, on synthetic INT4 packages large enough to give every CTA several tiles, ragged K splits (a group count
+that is not a multiple of the 16 warps) and each built head shape.  The packages are written by the native
+package writer at test time (seeded weights), so nothing outside the repository is read.
+
+Tolerances: logits max-abs <= 2e-2 and mean-abs <= 2e-3 as for the engine tests, times the largest |logit| when
+that exceeds 1.  Token ids and acceptance
+counts are exact, except that the sequences may part where the oracle's top-2 logit gap is below 2e-2: these
+models have 10-60 times more terms per sum than the golden packages, and two f32 summation orders of the same
+layer stack (this kernel, the kernel-per-operator path, the oracle) differ by up to ~1e-2 in a logit.
+"""
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = {
+    # name: hidden, layers, q heads, kv heads, head width, ffn, vocab
+    "hd128_g4": (1024, 2, 8, 2, 128, 3584, 2048),
+    "hd64_g4": (512, 3, 8, 2, 64, 1408, 1024),
+    "hd128_g8": (1024, 1, 8, 1, 128, 2048, 1024),
+}
+
+
+@pytest.fixture(scope="module", params=sorted(SHAPES))
+def stack_package(request, tmp_path_factory):
+    from llmoop_b200.package_writer import write_package
+    from llmoop_b200.synth import ModelSpec
+
+    hidden, layers, q_heads, kv_heads, head, ffn, vocab = SHAPES[request.param]
+    spec = ModelSpec(name=f"stack_{request.param}", hidden=hidden, layers=layers, q_heads=q_heads, kv_heads=kv_heads, head_dim=head,
+                     ffn=ffn, vocab=vocab, max_positions=512, quant="int4", std=0.02, seed=7)
+    directory = tmp_path_factory.mktemp("packages") / spec.name
+    write_package(spec, directory)
+    return directory, spec
+
+
+def _oracle(directory):
+    from oracle.nerve_oracle import Oracle, OraclePackage
+
+    package = OraclePackage(directory)
+    return package, Oracle(package)
+
+
+def test_stack_kernel_logits_match_oracle(stack_package):
+    import llmoop_b200 as nb
+    from oracle.nerve_oracle import OracleStream
+
+    directory, spec = stack_package
+    opkg, oracle = _oracle(directory)
+    rng = np.random.default_rng(3)
+    context = [int(t) for t in rng.integers(0, spec.vocab, size=70)]   # more than one 64-token attention split
+    probe = [int(t) for t in rng.integers(0, spec.vocab, size=4)]
+    ostream = OracleStream(opkg, 256)
+    oracle.target_forward(ostream, context, 0, want_logits=False)
+    _, expected = oracle.target_forward(ostream, probe, len(context), want_logits=True)
+
+    package = nb.Package(directory, capacity_tokens=256, page_tokens=16, max_streams=2, max_lanes=96, verify_level=0)
+    assert package.info["target_decode_stack"] == 1 and package.info["draft_decode_stack"] == 1
+    engine = nb.Engine(package)
+    engine.set_decode_stack(True)
+    engine.add_stream(1)
+    engine.submit_input_event_until_idle(1, context, 0)
+    assert engine.stream_tick(1) == len(context)
+    logits, _ = engine.debug_target_logits(1, probe)   # 4 lanes at ticks 70..73: the stack kernel
+    engine.set_decode_stack(False)
+    plain, _ = engine.debug_target_logits(1, probe)
+    difference, reference_difference = np.abs(logits - expected), np.abs(plain - expected)
+    # the golden packages' logits stay within +-1; here they reach 2-3, so the absolute bars scale with them
+    scale = max(1.0, float(np.abs(expected).max()))
+    assert difference.max() <= 2e-2 * scale, (difference.max(), scale)
+    assert difference.mean() <= 2e-3 * scale, (difference.mean(), scale)
+    # and the kernel is as close to the oracle as the kernel-per-operator path is
+    assert difference.mean() <= 1.5 * reference_difference.mean() + 1e-4, (difference.mean(), reference_difference.mean())
+    engine.close()
+    package.unmount()
+
+
+@pytest.mark.parametrize("drafts", [0, 3])
+def test_stack_kernel_generation_matches_oracle(stack_package, drafts):
+    import llmoop_b200 as nb
+    from oracle.nerve_oracle import OracleStream
+
+    directory, spec = stack_package
+    opkg, oracle = _oracle(directory)
+    prompt = [int(t) for t in np.random.default_rng(5).integers(0, spec.vocab, size=6)]  # prefill chunk of 6 lanes: stack kernel
+    ostream = OracleStream(opkg, 128)
+    expected = oracle.generate(ostream, prompt, 24, drafts, collect_logits=True)
+
+    package = nb.Package(directory, capacity_tokens=128, page_tokens=16, max_streams=2, max_lanes=64, verify_level=0)
+    engine = nb.Engine(package)
+    engine.set_decode_stack(True)
+    engine.set_cycle_logging(True)
+    engine.add_stream(7, speculative_draft_tokens=drafts)
+    tokens, report = engine.submit_input_event_until_idle(7, prompt, 24)
+    for index, (got, want) in enumerate(zip(tokens, expected["tokens"])):
+        if got != want:
+            gap = oracle.top2_gap(expected["logits"][index])
+            assert gap < 2e-2, f"token {index}: cuda {got} != oracle {want} with top-2 gap {gap}"
+            break
+    else:
+        assert len(tokens) == len(expected["tokens"])
+        cycles = engine.cycle_log()
+        assert [c["accepted"] for c in cycles] == [c["accepted"] for c in expected["cycles"]]
+        assert [c["emitted"] for c in cycles] == [c["emitted"] for c in expected["cycles"]]
+    engine.close()
+    package.unmount()
+
+
+def test_stack_kernel_is_deterministic_and_batch_independent(stack_package):
+    """A stream's tokens do not depend on what shares its batches (2 streams x 4 lanes = 8 lanes, still the stack
+    kernel), nor on the run."""
+    import llmoop_b200 as nb
+
+    directory, spec = stack_package
+    rng = np.random.default_rng(9)
+    prompts = [[int(t) for t in rng.integers(0, spec.vocab, size=5 + i)] for i in range(2)]
+    package = nb.Package(directory, capacity_tokens=128, page_tokens=16, max_streams=4, max_lanes=64, verify_level=0)
+    engine = nb.Engine(package)
+    engine.set_decode_stack(True)
+    alone = []
+    for i, prompt in enumerate(prompts):
+        engine.add_stream(10 + i, speculative_draft_tokens=3)
+        tokens, _ = engine.submit_input_event_until_idle(10 + i, prompt, 20)
+        alone.append(tokens)
+        engine.remove_stream(10 + i)
+    for i, prompt in enumerate(prompts):
+        engine.add_stream(i, speculative_draft_tokens=3)
+        engine.enqueue_input_event(i, prompt, 20)
+    outputs, report = engine.run_until_idle()
+    together = [[t for sid, t, _, _ in outputs if sid == i] for i in range(2)]
+    assert together == alone
+    engine.close()
+    package.unmount()

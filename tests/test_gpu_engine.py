@@ -73,12 +73,15 @@ def test_greedy_generation_matches_oracle(name, drafts):
 
 
 @pytest.mark.parametrize("name", PACKAGES)
-def test_target_logits_within_tolerance(name):
+@pytest.mark.parametrize("count", [24, 7])
+def test_target_logits_within_tolerance(name, count):
+    """24 lanes run kernel by kernel; 7 lanes go through the persistent decode stack kernel where the package's
+    layers have its form (the INT4 packages)."""
     import llmoop_b200 as nb
     from oracle.nerve_oracle import OracleStream
 
     opkg, oracle = _oracle(name)
-    tokens = _prompt(opkg.vocab, 24, seed=5)
+    tokens = _prompt(opkg.vocab, count, seed=5)
     ostream = OracleStream(opkg, 128)
     _, expected = oracle.target_forward(ostream, tokens, 0, want_logits=True)
 
@@ -139,15 +142,21 @@ def test_stop_token_truncates_and_closes():
     package.unmount()
 
 
-def test_multi_stream_batched_verify_matches_single_stream_runs():
-    """Several streams decoding together (one batched verify per cycle) must emit what each emits alone."""
+@pytest.mark.parametrize("streams,decode_stack", [(4, False), (2, True), (2, False)])
+def test_multi_stream_batched_verify_matches_single_stream_runs(streams, decode_stack):
+    """Several streams decoding together (one batched verify per cycle) must emit what each emits alone.
+    Batches of more than 8 lanes run kernel by kernel and smaller ones in the persistent stack kernel, whose
+    sums are ordered differently, so each case keeps its batches on one side of that line: 4 streams x 3 lanes
+    with the stack kernel off, 2 streams x 3 lanes with it on (and off)."""
     import llmoop_b200 as nb
 
     name = "tiny_int4_mtp"
     opkg, _ = _oracle(name)
-    prompts = [_prompt(opkg.vocab, 8 + 3 * i, seed=20 + i) for i in range(4)]
+    prompts = [_prompt(opkg.vocab, 5 + i, seed=20 + i) for i in range(streams)]
     package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=5, max_lanes=64)
+    assert package.info["target_decode_stack"] == 1 and package.info["draft_decode_stack"] == 1
     engine = nb.Engine(package)
+    engine.set_decode_stack(decode_stack)
     alone = []
     for i, prompt in enumerate(prompts):
         engine.add_stream(100 + i, speculative_draft_tokens=2)
@@ -158,9 +167,9 @@ def test_multi_stream_batched_verify_matches_single_stream_runs():
         engine.add_stream(i, speculative_draft_tokens=2)
         engine.enqueue_input_event(i, prompt, 16)
     outputs, report = engine.run_until_idle()
-    together = [[t for sid, t, _, _ in outputs if sid == i] for i in range(4)]
+    together = [[t for sid, t, _, _ in outputs if sid == i] for i in range(streams)]
     assert together == alone
-    assert report.max_batch_width == 4
+    assert report.max_batch_width == streams
     engine.close()
     package.unmount()
 
