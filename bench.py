@@ -36,6 +36,7 @@ EVENT_TOKENS = 256
 DRAFTS = 3
 METRIC = "accepted tokens/s (8B INT4, MTP k=3)"
 UNIT = "tokens/s"
+INT4_TRAFFIC_RATIO = 1.008
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -350,8 +351,13 @@ def main():
         },
         "verify_step": {"ms": verify_ms, "algorithmic_bytes": verify_bytes, "gbs": verify_gbs,
                         "frac_of_nominal_8tbs": verify_gbs / NOMINAL_HBM_GBS, "frac_of_measured_copy": verify_gbs / peak},
+        # traffic: DRAM bytes per launch = algorithmic bytes x 1.008, the ratio ncu measured for this kernel
+        # (dram__bytes_read.sum + dram__bytes_write.sum over packed weights + scales, gate/up pair capture in
+        # profiles/linear_int4_mma_kernel_gate_up_pair_14336x4096.md; traffic grows in proportion to the rows)
         "roofline": {"kernel": "linear_int4_mma_kernel", "bound": "hbm", "achieved": int4_gbs, "peak": peak, "peak_kind": peak_kind,
-                     "unit": "GB/s", "frac": int4_gbs / peak, "traffic": None, "launches_timed": profiled.int4_launches,
+                     "unit": "GB/s", "frac": int4_gbs / peak,
+                     "traffic": INT4_TRAFFIC_RATIO * profiled.int4_bytes / max(1, profiled.int4_launches),
+                     "launches_timed": profiled.int4_launches,
                      "bytes_per_launch": profiled.int4_bytes / max(1, profiled.int4_launches)},
         "e2e": {"value": e2e_natural, "unit": UNIT,
                 "h2d_bytes_per_step": natural_report.h2d_bytes / max(1, natural_report.cycle_count),

@@ -156,8 +156,9 @@ int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabl
  * runtime always records one dispatch per kernel (placed_stream_processor/temporal_prompt.rs:480-657). */
 int32_t nerve_b200_engine_set_decode_stack(nerve_b200_engine *engine, int32_t enabled);
 /* Profiling aid (no reference counterpart): with profiling on, CTA 0 of the persistent kernel stamps the GPU's
- * nanosecond timer at each layer's start and after each of its six grid barriers; this copies the stamps of the
- * last target-stack launch, [layers][8] (entries 7 unused).  *out_count = stamps available. */
+ * nanosecond timer at each layer's start and after each staging step, matrix or attention step and grid barrier
+ * of the layer, in program order; this copies the stamps of the last target-stack launch, [layers][32].
+ * *out_count = stamps available. */
 int32_t nerve_b200_engine_decode_stack_timing(nerve_b200_engine *engine, uint64_t *out_stamps, size_t max_stamps, size_t *out_count);
 /* Cycle log rows: {stream_id, start_tick, accepted, committed, emitted_count, width, emitted[8], targets[8]} as u64. */
 int32_t nerve_b200_engine_cycle_log(const nerve_b200_engine *engine, uint64_t *out_rows, size_t max_rows,

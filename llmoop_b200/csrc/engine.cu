@@ -394,7 +394,7 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
             stack_attention_out_ = device_alloc(8 * q_width * 2);
             stack_activation_ = device_alloc(8 * ffn * 2);
             stack_barrier_ = device_alloc(2 * sizeof(unsigned int));
-            stack_timing_ = device_alloc(std::max<size_t>(1, plan.layers.size()) * 8 * sizeof(unsigned long long));
+            stack_timing_ = device_alloc(std::max<size_t>(1, plan.layers.size()) * 32 * sizeof(unsigned long long));
         }
         const char *value = getenv("NERVE_B200_DECODE_STACK");
         if (value != nullptr) stack_enabled_ = value[0] == '1';
@@ -952,7 +952,7 @@ bool Engine::run_stack(const StackPlan &stack, int lanes, void *hidden) {
 std::vector<unsigned long long> Engine::decode_stack_timing() {
     std::vector<unsigned long long> stamps;
     if (!stack_timing_.ptr || !model_->target_stack().available) return stamps;
-    stamps.resize(model_->target_stack().layers.size() * 8);
+    stamps.resize(model_->target_stack().layers.size() * 32);
     cuda_check(cudaStreamSynchronize(cuda_stream_), "stream synchronize");
     cuda_check(cudaMemcpy(stamps.data(), stack_timing_.ptr, stamps.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost), "timing readback");
     return stamps;

@@ -191,7 +191,8 @@ public:
     // default until it is the faster of the two) = the kernel-per-operator path for everything.
     void set_decode_stack(bool enabled) { stack_enabled_ = enabled; }
     // Profiling aid: nanosecond stamps CTA 0 took at the phase boundaries of the target stack's last launch
-    // ([layers][8]; stamp 0 = layer start, 1..6 = after each grid barrier).  Empty when the stack kernel is not in use.
+    // ([layers][32]: layer start, then after each staging step, matrix or attention step and grid barrier, in
+    // program order).  Empty when the stack kernel is not in use.
     std::vector<unsigned long long> decode_stack_timing();
     void set_prefill_chunk(int tokens) { prefill_chunk_ = tokens; }
 

@@ -149,7 +149,7 @@ struct StackBuffers {
     uint16_t *activation;        // [lanes][ffn]
     unsigned int *barrier;       // two words, zero before the first launch
     int *error_flag;             // set when a bounded barrier wait expires
-    unsigned long long *timing;  // optional [layers][8] nanosecond stamps of CTA 0 (phase boundaries), or nullptr
+    unsigned long long *timing;  // optional [layers][32] nanosecond stamps of CTA 0 (phase boundaries), or nullptr
 };
 // One source matrix of a tile-major copy.  rope_head_width > 0 orders the rows of every head so that MMA rows
 // r and r + 8 of a tile are the rotary partners (d, d + head_width / 2).

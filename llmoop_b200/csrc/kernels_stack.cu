@@ -5,10 +5,10 @@
 //
 // Why one launch: at these batch sizes a layer is ~136 MB of weights (~21 us of HBM time) cut into a dozen
 // dependent steps; as separate kernels every step pays a launch, a pipeline fill and a drain (~6 us each,
-// measured), which is several times the streaming time.  Here one CTA per SM stays resident, keeps a register
-// ring of packed weights in flight across step boundaries (weights do not depend on activations, so the next
-// matrix is already streaming while the grid waits at a barrier), and the steps are separated by grid-wide
-// barriers (bounded spins on one global counter).
+// measured), which is several times the streaming time.  Here one CTA per SM stays resident, keeps a ring of
+// asynchronous copies of packed weights in flight across step boundaries (weights do not depend on activations,
+// so the next matrix is already streaming while the grid waits at a barrier), and the steps are separated by
+// grid-wide barriers (bounded spins on one global counter).
 //
 // Data layout:
 //  * weights: a tile-major copy made at mount - [tile of 16 rows][group of 128 columns][rt][half][lane] uint4,
@@ -16,10 +16,14 @@
 //    bytes; a tile is K/128 contiguous KB).  q and k tiles pair row d with row d + head_width/2, so RoPE runs in
 //    the q/k/v epilogue and K, V go straight into the KV pages.
 //  * activations of a step: staged once per CTA in shared memory in mma.sync B-fragment order, together with
-//    136 * sum(x) per (lane, group): the nibbles are fed to the tensor cores as bf16 128+q (one lop3 per pair,
+//    24 * sum(x) per (lane, group): the nibbles are fed to the tensor cores as bf16 128+q (one lop3 per pair,
 //    no subtract) and the bias 128+8 is taken out per group with that sum.
 //  * a matrix tile is computed by all 16 warps of a CTA (each takes every 16th group of K), reduced through
-//    shared memory, and finished by 64 epilogue threads.
+//    shared memory, and finished by 128 epilogue threads (one per row and lane).
+//  * attention: one warp per (kv head, 64-token split, lane group) on the tensor cores, partials merged per
+//    (lane, head) by one warp after a barrier.
+// The per-layer code is one loop over the four matrix steps with run-time matrix / epilogue selection: the
+// straight-line form of the same steps did not fit the instruction cache and spent most of its time refetching.
 #include "attention_body.cuh"
 #include "common.cuh"
 #include "kernels.cuh"
@@ -30,9 +34,7 @@ namespace {
 
 constexpr int STACK_WARPS = 16;
 constexpr int STACK_THREADS = STACK_WARPS * 32;
-constexpr int RING_UNITS = 4;          // 16x128 weight blocks a warp keeps in flight
-constexpr int ATTENTION_TEAMS = 4;     // 128-thread teams per CTA in the attention phase
-constexpr int ATTENTION_QL = 4;        // lanes of one stream served by one team
+constexpr int RING_UNITS = 4;          // 16x128 weight blocks (1 KB + scales) a warp keeps in flight
 constexpr unsigned int BARRIER_SPIN_LIMIT = 1u << 20;
 
 // ------------------------------------------------------------------------------------------ tile-major copy
@@ -94,12 +96,17 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Nibbles at bits s..s+3 and s+16..s+19 of `word` -> bf16x2 (128 + q, 128 + q'): 0x4300 | q is exactly 128 + q.
-__device__ __forceinline__ uint32_t biased_pair(uint32_t word, int shift) {
+// Nibble pair k of `word` (bits 4k..4k+3 and 16+4k..16+4k+3) -> bf16x2 (16 + q, 16 + q'): with the nibble in
+// mantissa bits 3..6 under exponent 2^4, 0x4180 | q << 3 is exactly 16 + q.  One shift and one lop3 per pair; the
+// offset 16 (+ 8 of the symmetric INT4 code) leaves the accumulator as 24 * sum(x) per group, taken out afterwards.
+template <int PAIR>
+__device__ __forceinline__ uint32_t biased_pair(uint32_t word) {
     uint32_t out;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(out) : "r"(word >> shift), "n"(0x000F000F), "n"(0x43004300));
+    const uint32_t aligned = PAIR == 0 ? word << 3 : word >> (4 * PAIR - 3);
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(out) : "r"(aligned), "n"(0x00780078), "n"(0x41804180));
     return out;
 }
+constexpr float NIBBLE_BIAS = 24.0f;
 
 __device__ __forceinline__ uint32_t load_acquire(const unsigned int *address) {
     uint32_t value;
@@ -130,28 +137,154 @@ __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int
     __syncthreads();
 }
 
-struct Ring {
-    uint4 w[RING_UNITS][2];    // rows g and g + 8 of a 16x128 block (this thread's 32 nibbles of each)
-    uint32_t s[RING_UNITS];    // their two bf16 scales
-};
-
-// Shared-memory carve-up of the matrix phases (the attention phase reuses the same bytes for its teams).
+// Shared-memory carve-up of the matrix phases.
 struct StackSmem {
     uint4 *fragments;    // [groups][4 words][staged lanes][4] activations in B-fragment order
     uint16_t *rows;      // [staged lanes][hidden] normalised rows before they are permuted
-    float *correction;   // [groups][8] 136 * sum(x) per lane
+    float *correction;   // [groups][8] 24 * sum(x) per lane
     float *reduce;       // [2][warps][32 rows][8]
-    float *partial;      // [32]
+    float *partial;      // [8 lanes][warps]
+    uint8_t *ring;       // [warps][RING_UNITS][RING_UNIT_BYTES] packed weights in flight (asynchronous copies)
 };
+
+// ------------------------------------------------------------------------------------------ weight stream
+// Every thread copies its own 2 x 16 bytes of packed weights and its 4-byte scale pair of a 16x128 block with
+// cp.async and later reads back exactly those bytes, so no thread waits on another: cp.async.wait_group is the
+// only synchronisation.  Copy groups complete in issue order and blocks are consumed in issue order, also
+// across matrices, so "all but the newest n groups" is always the right thing to wait for.  A warp's producer
+// cursor runs ahead of its consumer by up to RING_UNITS blocks and crosses into the next matrix as soon as the
+// current one is fully requested: the next phase's first weights are in flight while the grid is still at the
+// barrier in front of it.
+
+constexpr int RING_UNIT_BYTES = 2 * 512 + 128;
+
+__device__ __forceinline__ void async_copy16(void *shared_destination, const void *source) {
+    const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(address), "l"(source) : "memory");
+}
+__device__ __forceinline__ void async_copy4(void *shared_destination, const void *source) {
+    const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(address), "l"(source) : "memory");
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most `newer` of this thread's copy groups are still in flight.
+__device__ __forceinline__ void async_wait(int newer) {
+    switch (newer) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    }
+}
+
+// One matrix as a warp sees it: for each of the CTA's tiles (blockIdx.x, += gridDim.x) the warp's groups
+// (warp, += 16); an item is `rt` ring units (rt = 2 for a gate/up pair).
+struct MatrixWalk {
+    TiledInt4 matrix;
+    int rt, per_tile, tiles, total;
+};
+__device__ __forceinline__ MatrixWalk walk_of(const TiledInt4 &matrix, int rt) {
+    const int warp = threadIdx.x >> 5;
+    MatrixWalk walk;
+    walk.matrix = matrix;
+    walk.rt = rt;
+    walk.per_tile = matrix.groups > warp ? (matrix.groups - warp + STACK_WARPS - 1) / STACK_WARPS : 0;
+    walk.tiles = matrix.tiles > static_cast<int>(blockIdx.x)
+                     ? (matrix.tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
+                     : 0;
+    walk.total = walk.per_tile * walk.tiles;
+    return walk;
+}
+
+struct WeightStream {
+    uint8_t *base;          // this warp's RING_UNITS units
+    uint32_t head, tail;    // units consumed / requested so far
+    int in_flight;          // items (copy groups) requested and not yet consumed
+    MatrixWalk source;      // the matrix the producer is requesting from
+    int source_phase;       // its phase number
+    int remaining, gi;      // items of it still to request; position inside the current tile
+    const uint4 *weights;   // this thread's 16 bytes of the next block to request
+    const uint32_t *scales; // and its scale pair
+    MatrixWalk following;   // the matrix after it (valid when has_following)
+    bool has_following;
+};
+
+__device__ __forceinline__ void stream_start(WeightStream &stream, const MatrixWalk &walk, int phase) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    stream.source = walk;
+    stream.source_phase = phase;
+    stream.remaining = walk.total;
+    stream.gi = 0;
+    const size_t block = (static_cast<size_t>(blockIdx.x) * walk.matrix.groups + warp) * walk.rt;
+    stream.weights = walk.matrix.weights + block * 64 + lane;
+    stream.scales = walk.matrix.scales + block * 8 + (lane >> 2);
+}
+
+// Requests as many blocks as the ring has room for.
+__device__ __forceinline__ void stream_advance(WeightStream &stream) {
+    const int lane = threadIdx.x & 31;
+    while (true) {
+        if (stream.remaining == 0) {
+            if (!stream.has_following) break;
+            stream_start(stream, stream.following, stream.source_phase + 1);
+            stream.has_following = false;
+            continue;
+        }
+        const int rt = stream.source.rt;
+        if (RING_UNITS - static_cast<int>(stream.tail - stream.head) < rt) break;
+        for (int r = 0; r < rt; r++) {
+            uint8_t *unit = stream.base + ((stream.tail + r) % RING_UNITS) * RING_UNIT_BYTES;
+            async_copy16(unit + lane * 16, stream.weights + r * 64);
+            async_copy16(unit + 512 + lane * 16, stream.weights + r * 64 + 32);
+            async_copy4(unit + 1024 + lane * 4, stream.scales + r * 8);
+        }
+        async_commit();
+        stream.tail += rt;
+        stream.in_flight++;
+        stream.remaining--;
+        // next block of this warp: 16 groups on, or the first group of the CTA's next tile
+        int blocks = STACK_WARPS;
+        if (++stream.gi == stream.source.per_tile) {
+            stream.gi = 0;
+            blocks = static_cast<int>(gridDim.x) * stream.source.matrix.groups - (stream.source.per_tile - 1) * STACK_WARPS;
+        }
+        stream.weights += static_cast<size_t>(blocks) * rt * 64;
+        stream.scales += static_cast<size_t>(blocks) * rt * 8;
+    }
+}
+
+// Asks the memory system to bring the CTA's tiles of a matrix into L2 (no registers or shared memory are tied
+// up, nothing waits on it): issued one step ahead, so that HBM keeps streaming through the barriers, the staging
+// and the attention of the step in between and the ring's copies then find their bytes in L2.
+__device__ __forceinline__ void prefetch_l2(const void *address, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(address)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void prefetch_matrix_l2(const TiledInt4 &matrix, int rt) {
+    constexpr uint32_t PIECE = 16384;
+    const uint32_t tile_bytes = static_cast<uint32_t>(matrix.groups) * rt * 1024u, pieces = (tile_bytes + PIECE - 1) / PIECE;
+    const int tiles = matrix.tiles > static_cast<int>(blockIdx.x)
+                          ? (matrix.tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
+                          : 0;
+    for (uint32_t index = threadIdx.x; index < tiles * (pieces + 1); index += STACK_THREADS) {
+        const uint32_t t = index / (pieces + 1), piece = index % (pieces + 1);
+        const size_t tile = blockIdx.x + static_cast<size_t>(t) * gridDim.x;
+        if (piece == pieces) {
+            prefetch_l2(matrix.scales + tile * matrix.groups * rt * 8, static_cast<uint32_t>(matrix.groups) * rt * 32u);
+        } else {
+            const uint32_t offset = piece * PIECE, bytes = tile_bytes - offset < PIECE ? tile_bytes - offset : PIECE;
+            prefetch_l2(reinterpret_cast<const uint8_t *>(matrix.weights + tile * matrix.groups * rt * 64) + offset, bytes);
+        }
+    }
+}
 
 // ------------------------------------------------------------------------------------------ activation staging
 
-// 16 consecutive chunks (uint4 = 8 bf16) are one (lane, group); chunk -> fragment slot of thread (g = lane, j)
-// for word w is ((group * 4 + w) * staged + lane) * 4 + j, holding (v0,v4) (v1,v5) (v2,v6) (v3,v7): the B operands
-// of the two MMAs that consume nibble pairs (0,4) (1,5) and (2,6) (3,7) of the matching weight word.
-__device__ __forceinline__ void stage_chunk(const StackSmem &sm, uint4 raw, bool active, int chunk, int groups, int staged) {
-    const int m = chunk / (groups * 16), rem = chunk - m * groups * 16, group = rem >> 4, part = rem & 15, j = part >> 2,
-              word = part & 3;
+// A chunk is a uint4 of 8 consecutive bf16 of one lane; 16 consecutive chunks are one group of 128 columns.
+// Chunk c of lane m -> fragment slot of thread (g = m, j) for word w, with group = c / 16, j = (c / 4) % 4,
+// w = c % 4, is ((group * 4 + w) * staged + m) * 4 + j and holds (v0,v4) (v1,v5) (v2,v6) (v3,v7): the B operands of
+// the two MMAs that consume nibble pairs (0,4) (1,5) and (2,6) (3,7) of the matching weight word.
+__device__ __forceinline__ void stage_chunk(const StackSmem &sm, uint4 raw, bool active, int m, int chunk, int staged) {
+    const int group = chunk >> 4, j = (chunk >> 2) & 3, word = chunk & 3;
     float sum = 0.0f;
     if (active) {
         uint4 out;
@@ -167,311 +300,346 @@ __device__ __forceinline__ void stage_chunk(const StackSmem &sm, uint4 raw, bool
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);
     sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-    if (active && part == 0) sm.correction[group * 8 + m] = 136.0f * sum;
+    if (active && (chunk & 15) == 0) sm.correction[group * 8 + m] = NIBBLE_BIAS * sum;
 }
 
-__device__ __forceinline__ void clear_unused_corrections(const StackSmem &sm, int groups, int staged) {
-    for (int c = threadIdx.x; c < groups * 8; c += STACK_THREADS)
-        if ((c & 7) >= staged) sm.correction[c] = 0.0f;
-}
-
-// Rows written by other CTAs of this launch ([lanes][width] bf16 in global memory, read through L2).
-__device__ __forceinline__ void stage_global_rows(const StackSmem &sm, const uint16_t *x, int width, int staged) {
-    const int groups = width >> 7, chunks = staged * groups * 16;
-    for (int base = 0; base < chunks; base += STACK_THREADS) {
-        const int chunk = base + threadIdx.x;
-        const bool active = chunk < chunks;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (active) raw = __ldcg(reinterpret_cast<const uint4 *>(x) + chunk);  // chunk order == row-major order
-        stage_chunk(sm, raw, active, active ? chunk : 0, groups, staged);
+// Permutes [staged][width] bf16 rows into fragment order.  from_global: the rows were written by other CTAs of
+// this launch and are read through L2; otherwise they are sm.rows.  Loads go out in batches of eight (two chunks of
+// four lanes) before any of them is used: a pass costs one memory latency per batch, not one per chunk.
+__device__ __forceinline__ void stage_rows(const StackSmem &sm, const uint16_t *x, bool from_global, int width, int staged) {
+    const int per_lane = width >> 3;  // chunks of a lane, a multiple of 16
+    const uint4 *source = from_global ? reinterpret_cast<const uint4 *>(x) : reinterpret_cast<const uint4 *>(sm.rows);
+    for (int m0 = 0; m0 < staged; m0 += 4) {
+        for (int base = 0; base < per_lane; base += STACK_THREADS * 2) {
+            uint4 raw[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int mm = 0; mm < 4; mm++) {
+                    const int chunk = base + i * STACK_THREADS + threadIdx.x;
+                    raw[i][mm] = make_uint4(0, 0, 0, 0);
+                    if (chunk < per_lane && m0 + mm < staged) {
+                        const uint4 *address = source + static_cast<size_t>(m0 + mm) * per_lane + chunk;
+                        raw[i][mm] = from_global ? __ldcg(address) : *address;
+                    }
+                }
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int mm = 0; mm < 4; mm++) {
+                    const int chunk = base + i * STACK_THREADS + threadIdx.x;
+                    // uniform over the CTA: whole warps take part in the shuffles
+                    if (base + i * STACK_THREADS < per_lane && m0 + mm < staged)
+                        stage_chunk(sm, raw[i][mm], chunk < per_lane, m0 + mm, chunk < per_lane ? chunk : 0, staged);
+                }
+        }
     }
-    clear_unused_corrections(sm, groups, staged);
+    for (int c = threadIdx.x; c < (width >> 7) * 8; c += STACK_THREADS)
+        if ((c & 7) >= staged) sm.correction[c] = 0.0f;
     __syncthreads();
 }
 
-// rms_norm_bf16.comp.template:49-72 of every staged lane (each CTA repeats it: 8 KB per lane from L2), then the
-// normalised bf16 rows are permuted into fragment order.
-__device__ __forceinline__ void stage_normalised_rows(const StackSmem &sm, const uint16_t *x, const uint16_t *weight, int width,
-                                                      int staged, float eps, float offset) {
+// rms_norm_bf16.comp.template:49-72 of every staged lane into sm.rows (each CTA repeats it: 8 KB per lane from
+// L2).  Four lanes are loaded at once and kept in registers; width <= NORM_WORDS * 2 * STACK_THREADS.
+constexpr int NORM_WORDS = 4;
+__device__ __forceinline__ void normalise_rows(const StackSmem &sm, const uint16_t *x, const uint16_t *weight, int width, int staged,
+                                               float eps, float offset) {
     const int words = width >> 1, warp = threadIdx.x >> 5;
     const uint32_t *weight_words = reinterpret_cast<const uint32_t *>(weight);
     uint32_t *row_words = reinterpret_cast<uint32_t *>(sm.rows);
-    for (int m = 0; m < staged; m++) {
-        const uint32_t *row = reinterpret_cast<const uint32_t *>(x) + static_cast<size_t>(m) * words;
-        float sum = 0.0f;
-        for (int word = threadIdx.x; word < words; word += STACK_THREADS) {
-            uint32_t packed = __ldcg(row + word);
-            float lo = bf16_lo(packed), hi = bf16_hi(packed);
-            sum = fmaf(lo, lo, sum);
-            sum = fmaf(hi, hi, sum);
-        }
-        sum = warp_sum(sum);
-        __syncthreads();  // sm.partial of the previous lane has been read
-        if ((threadIdx.x & 31) == 0) sm.partial[warp] = sum;
-        __syncthreads();
-        float total = 0.0f;
-        for (int w = 0; w < STACK_WARPS; w++) total += sm.partial[w];
-        const float inv_rms = 1.0f / sqrtf(total * (1.0f / static_cast<float>(width)) + eps);
-        for (int word = threadIdx.x; word < words; word += STACK_THREADS) {
-            uint32_t packed = __ldcg(row + word), w = __ldg(weight_words + word);
-            float lo = bf16_lo(packed) * inv_rms * (bf16_lo(w) + offset);
-            float hi = bf16_hi(packed) * inv_rms * (bf16_hi(w) + offset);
-            row_words[static_cast<size_t>(m) * words + word] = pack_bf16(lo, hi);
-        }
-    }
-    __syncthreads();
-    const int groups = width >> 7, chunks = staged * groups * 16;
-    for (int base = 0; base < chunks; base += STACK_THREADS) {
-        const int chunk = base + threadIdx.x;
-        const bool active = chunk < chunks;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (active) raw = reinterpret_cast<const uint4 *>(sm.rows)[chunk];
-        stage_chunk(sm, raw, active, active ? chunk : 0, groups, staged);
-    }
-    clear_unused_corrections(sm, groups, staged);
-    __syncthreads();
-}
-
-// ------------------------------------------------------------------------------------------ weight ring
-
-template <int RT>
-__device__ __forceinline__ void issue_item(Ring &ring, int first_unit, const TiledInt4 &matrix, int tile, int group) {
-    const int lane = threadIdx.x & 31;
-    const size_t block = (static_cast<size_t>(tile) * matrix.groups + group) * RT;
+    uint32_t scale_words[NORM_WORDS];
 #pragma unroll
-    for (int rt = 0; rt < RT; rt++) {
-        const uint4 *src = matrix.weights + (block + rt) * 64 + lane;
-        ring.w[first_unit + rt][0] = __ldg(src);
-        ring.w[first_unit + rt][1] = __ldg(src + 32);
-        ring.s[first_unit + rt] = __ldg(matrix.scales + (block + rt) * 8 + (lane >> 2));
+    for (int i = 0; i < NORM_WORDS; i++) {
+        const int word = threadIdx.x + i * STACK_THREADS;
+        scale_words[i] = word < words ? __ldg(weight_words + word) : 0u;
     }
-}
-
-// A warp's items of one matrix: for each of the CTA's tiles (blockIdx.x, += gridDim.x) its groups (warp, += 16).
-struct WarpItems {
-    int per_tile, tiles, total;
-};
-__device__ __forceinline__ WarpItems warp_items(const TiledInt4 &matrix) {
-    const int warp = threadIdx.x >> 5;
-    WarpItems items;
-    items.per_tile = matrix.groups > warp ? (matrix.groups - warp + STACK_WARPS - 1) / STACK_WARPS : 0;
-    items.tiles = matrix.tiles > static_cast<int>(blockIdx.x) ? (matrix.tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) : 0;
-    items.total = items.per_tile * items.tiles;
-    return items;
-}
-__device__ __forceinline__ void issue_numbered(Ring &ring, int first_unit, const TiledInt4 &matrix, const WarpItems &items, int number,
-                                               int rt_count) {
-    int tile_index = 0;
-    while (number >= items.per_tile) {
-        number -= items.per_tile;
-        tile_index++;
-    }
-    const int tile = blockIdx.x + tile_index * gridDim.x, group = (threadIdx.x >> 5) + number * STACK_WARPS;
-    if (rt_count == 2) issue_item<2>(ring, first_unit, matrix, tile, group);
-    else issue_item<1>(ring, first_unit, matrix, tile, group);
-}
-
-// Before a matrix phase: whatever of the warp's first RING_UNITS / RT items the previous phase did not already
-// request (bit i of `mask`) is requested now, ahead of the activation staging.
-template <int RT>
-__device__ __forceinline__ void prefetch_entry(Ring &ring, uint32_t &mask, const TiledInt4 &matrix) {
-    constexpr int SLOTS = RING_UNITS / RT;
-    const WarpItems items = warp_items(matrix);
+    for (int m0 = 0; m0 < staged; m0 += 4) {
+        uint32_t held[4][NORM_WORDS];
 #pragma unroll
-    for (int slot = 0; slot < SLOTS; slot++)
-        if (!((mask >> slot) & 1u) && slot < items.total) issue_numbered(ring, slot * RT, matrix, items, slot, RT);
-    mask = 0;
-}
-
-// ------------------------------------------------------------------------------------------ matrix phase
-
-// Streams the CTA's tiles of `current` (its first RING_UNITS / RT items per warp already requested).  While the
-// last items are consumed the freed ring units are refilled with the first items of `next` (NRT = its rt count,
-// 0 = none); `mask` returns which of them were requested.  epilogue(tile, r, m, sums) gets, for lane m, the
-// results of MMA rows r and r + 8 of the tile (sums[rt][0], sums[rt][1]) and is run by 64 threads.
-template <int RT, int NRT, class Epilogue>
-__device__ __forceinline__ void matrix_phase(const TiledInt4 current, const TiledInt4 next, Ring &ring, uint32_t &mask,
-                                             const StackSmem &sm, int staged, int lanes, int &parity, Epilogue epilogue) {
-    constexpr int SLOTS = RING_UNITS / RT;
-    constexpr int NSLOTS = NRT > 0 ? RING_UNITS / NRT : 0;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
-    const WarpItems items = warp_items(current);
-    WarpItems next_items = items;
-    if (NRT > 0) next_items = warp_items(next);
-    const int tiles_of_cta = items.tiles;
-
-    int issued = items.total < SLOTS ? items.total : SLOTS;
-    int issue_gi = issued, issue_tile = blockIdx.x;
-    while (items.per_tile > 0 && issue_gi >= items.per_tile) {
-        issue_gi -= items.per_tile;
-        issue_tile += gridDim.x;
-    }
-    uint32_t freed = 0, requested = 0;
-
-    const int ge = g < staged ? g : 0;  // lanes beyond the batch recompute lane 0; their results are dropped
-    const uint4 *xlane = sm.fragments + ge * 4 + j;
-    float acc[RT][4];
+        for (int mm = 0; mm < 4; mm++)
 #pragma unroll
-    for (int rt = 0; rt < RT; rt++)
+            for (int i = 0; i < NORM_WORDS; i++) {
+                const int word = threadIdx.x + i * STACK_THREADS;
+                held[mm][i] = (m0 + mm < staged && word < words)
+                                  ? __ldcg(reinterpret_cast<const uint32_t *>(x) + static_cast<size_t>(m0 + mm) * words + word)
+                                  : 0u;
+            }
 #pragma unroll
-        for (int i = 0; i < 4; i++) acc[rt][i] = 0.0f;
-    int cur_tile = blockIdx.x, cur_gi = 0;
-
-    auto finish_tile = [&]() {
-        float *mine = sm.reduce + static_cast<size_t>((parity * STACK_WARPS + warp) * 32) * 8;
+        for (int mm = 0; mm < 4; mm++) {
+            float sum = 0.0f;
 #pragma unroll
-        for (int rt = 0; rt < RT; rt++) {
-            *reinterpret_cast<float2 *>(mine + (rt * 16 + g) * 8 + 2 * j) = make_float2(acc[rt][0], acc[rt][1]);
-            *reinterpret_cast<float2 *>(mine + (rt * 16 + g + 8) * 8 + 2 * j) = make_float2(acc[rt][2], acc[rt][3]);
-            acc[rt][0] = acc[rt][1] = acc[rt][2] = acc[rt][3] = 0.0f;
+            for (int i = 0; i < NORM_WORDS; i++) {
+                const float lo = bf16_lo(held[mm][i]), hi = bf16_hi(held[mm][i]);
+                sum = fmaf(lo, lo, sum);
+                sum = fmaf(hi, hi, sum);
+            }
+            sum = warp_sum(sum);
+            if ((threadIdx.x & 31) == 0) sm.partial[(m0 + mm) * STACK_WARPS + warp] = sum;
         }
         __syncthreads();
-        if (threadIdx.x < 64) {
-            const int r = threadIdx.x >> 3, m = threadIdx.x & 7;
-            if (m < lanes) {
-                const float *src = sm.reduce + static_cast<size_t>(parity * STACK_WARPS * 32 + r) * 8 + m;
-                float sums[RT][2];
 #pragma unroll
-                for (int rt = 0; rt < RT; rt++) sums[rt][0] = sums[rt][1] = 0.0f;
+        for (int mm = 0; mm < 4; mm++) {
+            if (m0 + mm < staged) {
+                float total = 0.0f;
 #pragma unroll
-                for (int w = 0; w < STACK_WARPS; w++)
+                for (int w = 0; w < STACK_WARPS; w++) total += sm.partial[(m0 + mm) * STACK_WARPS + w];
+                // IEEE sqrt and divide, as a CPU evaluates 1/sqrt(v)
+                const float inv_rms = 1.0f / sqrtf(total * (1.0f / static_cast<float>(width)) + eps);
 #pragma unroll
-                    for (int rt = 0; rt < RT; rt++) {
-                        sums[rt][0] += src[(w * 32 + rt * 16) * 8];
-                        sums[rt][1] += src[(w * 32 + rt * 16 + 8) * 8];
+                for (int i = 0; i < NORM_WORDS; i++) {
+                    const int word = threadIdx.x + i * STACK_THREADS;
+                    if (word < words) {
+                        const float lo = bf16_lo(held[mm][i]) * inv_rms * (bf16_lo(scale_words[i]) + offset);
+                        const float hi = bf16_hi(held[mm][i]) * inv_rms * (bf16_hi(scale_words[i]) + offset);
+                        row_words[static_cast<size_t>(m0 + mm) * words + word] = pack_bf16(lo, hi);
                     }
-                epilogue(cur_tile, r, m, sums);
+                }
             }
         }
-        parity ^= 1;
-        cur_gi = 0;
-        cur_tile += gridDim.x;
+    }
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------ attention
+// One warp serves one context split (64 tokens) of one kv head for the Q = QL * GROUP <= 16 query vectors of QL
+// consecutive lanes of a stream (append_gqa_attention_bf16.comp.template:217-339: f32 scores of bf16 q.k, f32
+// softmax, f32 p.v).  Scores and p.v run on the tensor cores: q rows are the A operand of S = Q K^T, K rows the
+// B operand (both read with 16-byte loads; the head dimension is permuted identically on both sides); the
+// probabilities are re-used from the accumulator registers as the A operand of O = P V, split into a bf16 high
+// and low part (p = hi + lo to 2^-17), and V is the B operand, its token pairs assembled with byte permutes.
+// The partial (unnormalised output, running maximum, sum) goes to the scratch the merge step reads.
+
+__device__ __forceinline__ uint32_t pack_bf16_pair(float low, float high) { return pack_bf16(low, high); }
+
+template <int HD, int GROUP, int QL>
+__device__ __forceinline__ void attention_warp_item(const uint16_t *__restrict__ q, const KvLayer &kv, const LaneTable &lanes_meta,
+                                                    int lanes, int lanes_per_stream, int q_heads, float scale, int max_splits,
+                                                    float *__restrict__ scratch, int kv_head, int split, int group_slot) {
+    constexpr int Q = QL * GROUP;
+    constexpr int QW = HD / 32;                    // 16-byte pieces of a q / k row per thread
+    constexpr int HALF = HD < 64 ? HD : 64;        // head dims handled per output pass
+    constexpr int DPT = HALF / 8;                  // of which one thread column owns this many
+    static_assert(Q <= 16 && HD % 32 == 0, "attention team shape");
+    const int lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
+    const int groups_per_stream = (lanes_per_stream + QL - 1) / QL;
+    const int stream_index = group_slot / groups_per_stream, group_index = group_slot % groups_per_stream;
+    const int lane0 = stream_index * lanes_per_stream + group_index * QL;
+    if (lane0 >= lanes) return;
+    const int slot = lanes_meta.slot[lane0];
+    if (slot < 0) return;
+    const uint32_t capacity = kv.capacity;
+
+    uint32_t newest = 0, tick_row[2] = {0xffffffffu, 0xffffffffu};
+#pragma unroll
+    for (int i = 0; i < QL; i++) {
+        const bool valid = lane0 + i < lanes && group_index * QL + i < lanes_per_stream;
+        const uint32_t tick = valid ? lanes_meta.position[lane0 + i] : 0xffffffffu;
+        if (valid && tick > newest) newest = tick;
+        if (g < Q && g / GROUP == i) tick_row[0] = tick;
+        if (g + 8 < Q && (g + 8) / GROUP == i) tick_row[1] = tick;
+    }
+    const uint32_t tokens = newest + 1u < capacity ? newest + 1u : capacity;  // attended window of the newest lane
+    const uint32_t first_tick = newest + 1u - tokens;
+    const uint32_t begin = static_cast<uint32_t>(split) * 64u;
+    if (begin >= tokens) return;
+    const int count = static_cast<int>(tokens - begin < 64u ? tokens - begin : 64u);
+    // ring index of the split's first token; element offset of token t's K (or V) row of this kv head
+    const uint32_t ring_base = (first_tick + begin) % capacity;
+    const int page_shift = (kv.page_tokens & (kv.page_tokens - 1)) == 0 ? __ffs(kv.page_tokens) - 1 : -1;
+    const size_t half_page = static_cast<size_t>(kv.kv_heads) * kv.page_tokens * HD;
+    auto row_offset = [&](int token, bool value) {
+        uint32_t ring = ring_base + static_cast<uint32_t>(token);
+        if (ring >= capacity) ring -= capacity;
+        const int page = page_shift >= 0 ? static_cast<int>(ring >> page_shift) : static_cast<int>(ring / kv.page_tokens);
+        const int within = page_shift >= 0 ? static_cast<int>(ring & (kv.page_tokens - 1)) : static_cast<int>(ring % kv.page_tokens);
+        const int physical = kv.block_table[static_cast<size_t>(slot) * kv.pages_per_slot + page];
+        return static_cast<size_t>(physical) * (2 * half_page) + (value ? half_page : 0) +
+               (static_cast<size_t>(kv_head) * kv.page_tokens + within) * HD;
     };
 
-    if (items.per_tile == 0) {
-        // a warp without groups of this K still takes part in every tile's reduction
-        for (int t = 0; t < tiles_of_cta; t++) finish_tile();
+    // ---- S = Q K^T
+    uint4 qf[2][QW];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const int row = g + 8 * r;
+        const bool valid = tick_row[r] != 0xffffffffu;
+        const uint16_t *source = q + (static_cast<size_t>(lane0 + row / GROUP) * q_heads + kv_head * GROUP + row % GROUP) * HD + j * (HD / 4);
+#pragma unroll
+        for (int w = 0; w < QW; w++) qf[r][w] = valid ? __ldcg(reinterpret_cast<const uint4 *>(source) + w) : make_uint4(0, 0, 0, 0);
     }
-    for (int it = 0; it < items.total;) {
+    float s[8][4];
 #pragma unroll
-        for (int slot = 0; slot < SLOTS; slot++) {
-            if (it >= items.total) break;
-            const int group = warp + cur_gi * STACK_WARPS;
-            uint4 b[4];
+    for (int nt = 0; nt < 8; nt++) {
+        const int token = nt * 8 + g;
+        uint4 kf[QW];
+        if (token < count) {
+            const uint16_t *krow = kv.pool + row_offset(token, false) + j * (HD / 4);
 #pragma unroll
-            for (int word = 0; word < 4; word++) b[word] = xlane[(group * 4 + word) * staged * 4];
-            const float2 bias = *reinterpret_cast<const float2 *>(sm.correction + group * 8 + 2 * j);
+            for (int w = 0; w < QW; w++) kf[w] = __ldcg(reinterpret_cast<const uint4 *>(krow) + w);
+        } else {
 #pragma unroll
-            for (int rt = 0; rt < RT; rt++) {
-                const int unit = slot * RT + rt;
-                float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                const uint32_t wa[4] = {ring.w[unit][0].x, ring.w[unit][0].y, ring.w[unit][0].z, ring.w[unit][0].w};
-                const uint32_t wb[4] = {ring.w[unit][1].x, ring.w[unit][1].y, ring.w[unit][1].z, ring.w[unit][1].w};
+            for (int w = 0; w < QW; w++) kf[w] = make_uint4(0, 0, 0, 0);
+        }
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
 #pragma unroll
-                for (int word = 0; word < 4; word++) {
-                    mma_bf16_16816(c, biased_pair(wa[word], 0), biased_pair(wb[word], 0), biased_pair(wa[word], 4),
-                                   biased_pair(wb[word], 4), b[word].x, b[word].y);
-                    mma_bf16_16816(c, biased_pair(wa[word], 8), biased_pair(wb[word], 8), biased_pair(wa[word], 12),
-                                   biased_pair(wb[word], 12), b[word].z, b[word].w);
-                }
-                const float sa = __uint_as_float(ring.s[unit] << 16), sb = __uint_as_float(ring.s[unit] & 0xffff0000u);
-                acc[rt][0] = fmaf(sa, c[0] - bias.x, acc[rt][0]);
-                acc[rt][1] = fmaf(sa, c[1] - bias.y, acc[rt][1]);
-                acc[rt][2] = fmaf(sb, c[2] - bias.x, acc[rt][2]);
-                acc[rt][3] = fmaf(sb, c[3] - bias.y, acc[rt][3]);
-            }
-            if (issued < items.total) {
-                issue_item<RT>(ring, slot * RT, current, issue_tile, warp + issue_gi * STACK_WARPS);
-                issued++;
-                if (++issue_gi == items.per_tile) {
-                    issue_gi = 0;
-                    issue_tile += gridDim.x;
-                }
-            } else if (NRT > 0) {
-                freed |= ((1u << RT) - 1u) << (slot * RT);
-#pragma unroll
-                for (int ns = 0; ns < NSLOTS; ns++) {
-                    const uint32_t need = ((1u << NRT) - 1u) << (ns * NRT);
-                    if (!((requested >> ns) & 1u) && (freed & need) == need && ns < next_items.total) {
-                        issue_numbered(ring, ns * NRT, next, next_items, ns, NRT);
-                        requested |= 1u << ns;
-                    }
-                }
-            }
-            it++;
-            if (++cur_gi == items.per_tile) finish_tile();
+        for (int w = 0; w < QW; w++) {
+            mma_bf16_16816(s[nt], qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, kf[w].x, kf[w].y);
+            mma_bf16_16816(s[nt], qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, kf[w].z, kf[w].w);
         }
     }
-    mask = NRT > 0 ? requested : 0u;
+
+    // ---- causal / ring mask, scale, softmax of the split (rows g and g + 8; columns 2j, 2j + 1 of every 8 tokens)
+    float row_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int token = nt * 8 + 2 * j + (c & 1);
+            const uint32_t tick = tick_row[c >> 1], token_tick = first_tick + begin + token;
+            const bool visible = token < count && tick != 0xffffffffu && token_tick <= tick && token_tick + capacity > tick;
+            s[nt][c] = visible ? s[nt][c] * scale : -INFINITY;
+            row_max[c >> 1] = fmaxf(row_max[c >> 1], s[nt][c]);
+        }
+    float row_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 1));
+        row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 2));
+        row_max[r] = fmaxf(row_max[r], -3.4028234663852886e38f);
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            s[nt][c] = s[nt][c] == -INFINITY ? 0.0f : expf(s[nt][c] - row_max[c >> 1]);
+            row_sum[c >> 1] += s[nt][c];
+        }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
+        row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+    }
+    // probabilities as A fragments of 16 tokens per step: high and low bf16 parts
+    uint32_t ph[4][4], pl[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ks++)
+#pragma unroll
+        for (int f = 0; f < 4; f++) {
+            const float first = s[2 * ks + (f >> 1)][2 * (f & 1)], second = s[2 * ks + (f >> 1)][2 * (f & 1) + 1];
+            ph[ks][f] = pack_bf16_pair(first, second);
+            pl[ks][f] = pack_bf16_pair(first - bf16_lo(ph[ks][f]), second - bf16_hi(ph[ks][f]));
+        }
+
+    // ---- O = P V, HALF head dims per pass; thread column g owns dims DPT*g .. DPT*g + DPT - 1 of the pass
+    float *out_row[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const int row = g + 8 * r;
+        out_row[r] = scratch + ((static_cast<size_t>(lane0 + row / GROUP) * q_heads + kv_head * GROUP + row % GROUP) * max_splits + split) * (HD + 2);
+    }
+#pragma unroll
+    for (int pass = 0; pass < HD / HALF; pass++) {
+        float o[DPT][4];
+#pragma unroll
+        for (int i = 0; i < DPT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            uint32_t v[4][DPT / 2];  // tokens 16ks + 2j, +1, +8, +9
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const int token = 16 * ks + 2 * j + (t & 1) + 8 * (t >> 1);
+                if (token < count) {
+                    const uint16_t *vrow = kv.pool + row_offset(token, true) + pass * HALF + DPT * g;
+                    if (DPT == 8) {
+                        const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(vrow));
+                        v[t][0] = raw.x;
+                        v[t][1] = raw.y;
+                        v[t][DPT / 2 - 2] = raw.z;
+                        v[t][DPT / 2 - 1] = raw.w;
+                    } else {
+                        const uint2 raw = __ldcg(reinterpret_cast<const uint2 *>(vrow));
+                        v[t][0] = raw.x;
+                        v[t][DPT / 2 - 1] = raw.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int w = 0; w < DPT / 2; w++) v[t][w] = 0u;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < DPT; i++) {
+                const uint32_t selector = (i & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(v[0][i >> 1], v[1][i >> 1], selector), b1 = __byte_perm(v[2][i >> 1], v[3][i >> 1], selector);
+                mma_bf16_16816(o[i], ph[ks][0], ph[ks][1], ph[ks][2], ph[ks][3], b0, b1);
+                mma_bf16_16816(o[i], pl[ks][0], pl[ks][1], pl[ks][2], pl[ks][3], b0, b1);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+            if (tick_row[r] != 0xffffffffu) {
+#pragma unroll
+                for (int i = 0; i < DPT; i++) {
+                    out_row[r][pass * HALF + DPT * (2 * j) + i] = o[i][2 * r];
+                    out_row[r][pass * HALF + DPT * (2 * j + 1) + i] = o[i][2 * r + 1];
+                }
+            }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++)
+        if (tick_row[r] != 0xffffffffu && j == 0) {
+            out_row[r][HD] = row_max[r];
+            out_row[r][HD + 1] = row_sum[r];
+        }
 }
 
-// ------------------------------------------------------------------------------------------ epilogues
-
-// q/k/v: tiles [0, q_tiles) are q, the next k_tiles are k, the rest v.  q and k rows arrive as rotary partners
-// (rotary_bf16.comp.template:99-109, non-interleaved, rotary width = head width: five bf16 roundings); k and v
-// are written into the lane's KV page (append_gqa_attention_bf16.comp.template:189-215), q into the q buffer.
-struct QkvEpilogue {
-    int q_tiles, k_tiles, head_width, q_heads;
-    uint16_t *q;
-    KvLayer kv;
-    LaneTable lanes_meta;
-    const uint32_t *rope_table;
-    uint32_t rope_positions;
-
-    __device__ __forceinline__ void operator()(int tile, int r, int m, const float (&sums)[1][2]) const {
-        const float low = round_bf16(sums[0][0]), high = round_bf16(sums[0][1]);
-        const uint32_t position = lanes_meta.position[m];
-        const int slot = lanes_meta.slot[m];
-        if (tile < q_tiles + k_tiles) {
-            const bool is_q = tile < q_tiles;
-            const int local = is_q ? tile : tile - q_tiles;
-            const int tiles_per_head = head_width >> 4, half = head_width >> 1;
-            const int head = local / tiles_per_head, d = 8 * (local % tiles_per_head) + r;
-            const uint32_t packed = __ldg(rope_table + static_cast<size_t>(position % rope_positions) * half + d);
-            const float cosine = bf16_lo(packed), sine = bf16_hi(packed);
-            const uint16_t out_low = static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(low * cosine) + round_bf16(-high * sine)));
-            const uint16_t out_high = static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(high * cosine) + round_bf16(low * sine)));
-            if (is_q) {
-                uint16_t *dst = q + (static_cast<size_t>(m) * q_heads + head) * head_width + d;
-                dst[0] = out_low;
-                dst[half] = out_high;
-            } else if (slot >= 0 && kv.capacity != 0) {
-                uint16_t *dst = kv.pool + kv_token_offset(kv, slot, position % kv.capacity, head, false) + d;
-                dst[0] = out_low;
-                dst[half] = out_high;
+// Log-sum-exp merge of the split partials of one (lane, q head) pair by one warp: lane s of the warp weighs
+// split s (s + 32, ...), every lane owns HD / 32 consecutive output dims, and the weighted rows are summed in
+// split order with four vector loads in flight.
+template <int HD>
+__device__ __forceinline__ void attention_merge_warp(const float *__restrict__ scratch, uint16_t *__restrict__ out, const KvLayer &kv,
+                                                     const LaneTable &lanes_meta, int pair, int q_heads, int max_splits) {
+    constexpr int VEC = HD / 32, STRIDE = HD + 2;
+    const int lane_id = threadIdx.x & 31, lane = pair / q_heads;
+    if (lanes_meta.slot[lane] < 0) return;
+    const uint32_t tick = lanes_meta.position[lane];
+    const uint32_t tokens = tick + 1u < kv.capacity ? tick + 1u : kv.capacity;
+    int splits = static_cast<int>((tokens + 63u) / 64u);
+    if (splits > max_splits) splits = max_splits;
+    const float *base = scratch + static_cast<size_t>(pair) * max_splits * STRIDE;
+    float maximum = -3.4028234663852886e38f;
+    for (int s = lane_id; s < splits; s += 32) maximum = fmaxf(maximum, __ldcg(base + static_cast<size_t>(s) * STRIDE + HD));
+    maximum = warp_max(maximum);
+    float denominator = 0.0f, acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; v++) acc[v] = 0.0f;
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        float weight = 0.0f;
+        if (s0 + lane_id < splits) {
+            weight = expf(__ldcg(base + static_cast<size_t>(s0 + lane_id) * STRIDE + HD) - maximum);
+            denominator += __ldcg(base + static_cast<size_t>(s0 + lane_id) * STRIDE + HD + 1) * weight;
+        }
+        const int end = splits - s0 < 32 ? splits - s0 : 32;
+        for (int s = 0; s < end; s += 4) {
+            float part[4][VEC];
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+#pragma unroll
+                for (int v = 0; v < VEC; v++)
+                    part[u][v] = s + u < end ? __ldcg(base + static_cast<size_t>(s0 + s + u) * STRIDE + lane_id * VEC + v) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float w = __shfl_sync(0xffffffffu, weight, (s + u) & 31);
+#pragma unroll
+                for (int v = 0; v < VEC; v++) acc[v] += part[u][v] * (s + u < end ? w : 0.0f);
             }
-        } else if (slot >= 0 && kv.capacity != 0) {
-            const int row = (tile - q_tiles - k_tiles) * 16 + r;
-            const int head = row / head_width, d = row % head_width;
-            uint16_t *dst = kv.pool + kv_token_offset(kv, slot, position % kv.capacity, head, true) + d;
-            dst[0] = static_cast<uint16_t>(f32_to_bf16_bits(sums[0][0]));
-            dst[8] = static_cast<uint16_t>(f32_to_bf16_bits(sums[0][1]));
         }
     }
-};
-
-// linear + residual_add (add_bf16.comp.template:17-24): bf16(bf16(product) + residual), in place.
-struct ResidualEpilogue {
-    uint16_t *hidden;
-    int width;
-    __device__ __forceinline__ void operator()(int tile, int r, int m, const float (&sums)[1][2]) const {
-        uint16_t *dst = hidden + static_cast<size_t>(m) * width + tile * 16 + r;
-        const float first = bf16_bits_to_f32(__ldcg(dst)), second = bf16_bits_to_f32(__ldcg(dst + 8));
-        dst[0] = static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(sums[0][0]) + first));
-        dst[8] = static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(sums[0][1]) + second));
-    }
-};
-
-// gate/up pair: bf16(silu_bf16(bf16 gate) * bf16 up) (silu_multiply_bf16.comp.template:30-52).
-struct SiluEpilogue {
-    uint16_t *activation;
-    int width;
-    __device__ __forceinline__ void operator()(int tile, int r, int m, const float (&sums)[2][2]) const {
-        uint16_t *dst = activation + static_cast<size_t>(m) * width + tile * 16 + r;
-        dst[0] = static_cast<uint16_t>(f32_to_bf16_bits(rounded_silu(round_bf16(sums[0][0])) * round_bf16(sums[1][0])));
-        dst[8] = static_cast<uint16_t>(f32_to_bf16_bits(rounded_silu(round_bf16(sums[0][1])) * round_bf16(sums[1][1])));
-    }
-};
+    denominator = warp_sum(denominator);
+#pragma unroll
+    for (int v = 0; v < VEC; v++)
+        out[static_cast<size_t>(pair) * HD + lane_id * VEC + v] =
+            static_cast<uint16_t>(f32_to_bf16_bits(denominator == 0.0f ? 0.0f : acc[v] / denominator));
+}
 
 // ------------------------------------------------------------------------------------------ the kernel
 
@@ -485,9 +653,9 @@ struct StackArgs {
 };
 
 struct StackSmemLayout {
-    size_t fragments, rows, correction, reduce, partial, total;
+    size_t fragments, rows, correction, reduce, partial, ring, total;
 };
-__host__ __device__ inline StackSmemLayout stack_smem_layout(const StackShape &shape, int staged, size_t attention_bytes) {
+__host__ __device__ inline StackSmemLayout stack_smem_layout(const StackShape &shape, int staged) {
     const size_t q_width = static_cast<size_t>(shape.q_heads) * shape.head_width;
     size_t widest = shape.hidden > shape.ffn ? shape.hidden : shape.ffn;
     if (q_width > widest) widest = q_width;
@@ -500,14 +668,38 @@ __host__ __device__ inline StackSmemLayout stack_smem_layout(const StackShape &s
     layout.correction = region;
     layout.reduce = layout.correction + (widest >> 7) * 8 * sizeof(float);
     layout.partial = layout.reduce + static_cast<size_t>(2) * STACK_WARPS * 32 * 8 * sizeof(float);
-    layout.total = layout.partial + 32 * sizeof(float);
-    if (attention_bytes > layout.total) layout.total = attention_bytes;
+    layout.ring = layout.partial + 8 * STACK_WARPS * sizeof(float);
+    layout.total = layout.ring + static_cast<size_t>(STACK_WARPS) * RING_UNITS * RING_UNIT_BYTES;
     return layout;
+}
+
+// One 16x128 block of the ring against the staged activations: eight MMAs over bf16 (16 + q), the block's two
+// scales, and the 24 * sum(x) bias of the group.
+__device__ __forceinline__ void consume_unit(const uint8_t *unit, const uint4 (&b)[4], float2 bias, float (&acc)[4]) {
+    const int lane = threadIdx.x & 31;
+    const uint4 first = *reinterpret_cast<const uint4 *>(unit + lane * 16);
+    const uint4 second = *reinterpret_cast<const uint4 *>(unit + 512 + lane * 16);
+    const uint32_t scales = *reinterpret_cast<const uint32_t *>(unit + 1024 + lane * 4);
+    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const uint32_t wa[4] = {first.x, first.y, first.z, first.w};
+    const uint32_t wb[4] = {second.x, second.y, second.z, second.w};
+#pragma unroll
+    for (int word = 0; word < 4; word++) {
+        mma_bf16_16816(c, biased_pair<0>(wa[word]), biased_pair<0>(wb[word]), biased_pair<1>(wa[word]), biased_pair<1>(wb[word]), b[word].x,
+                       b[word].y);
+        mma_bf16_16816(c, biased_pair<2>(wa[word]), biased_pair<2>(wb[word]), biased_pair<3>(wa[word]), biased_pair<3>(wb[word]), b[word].z,
+                       b[word].w);
+    }
+    const float sa = __uint_as_float(scales << 16), sb = __uint_as_float(scales & 0xffff0000u);
+    acc[0] = fmaf(sa, c[0] - bias.x, acc[0]);
+    acc[1] = fmaf(sa, c[1] - bias.y, acc[1]);
+    acc[2] = fmaf(sb, c[2] - bias.x, acc[2]);
+    acc[3] = fmaf(sb, c[3] - bias.y, acc[3]);
 }
 
 template <int GROUP>
 struct AttentionTeam {
-    static constexpr int QL = GROUP >= 8 ? 2 : ATTENTION_QL;
+    static constexpr int QL = GROUP >= 8 ? 2 : (GROUP >= 4 ? 4 : (16 / GROUP > 8 ? 8 : 16 / GROUP));
 };
 
 template <int HD, int GROUP>
@@ -516,106 +708,215 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     constexpr int QL = AttentionTeam<GROUP>::QL;
     const StackShape &shape = a.shape;
     const int lanes = a.lanes, staged = lanes < 8 ? lanes : 8;
-    const StackSmemLayout layout = stack_smem_layout(shape, staged, 0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
+    const StackSmemLayout layout = stack_smem_layout(shape, staged);
     StackSmem sm;
     sm.fragments = reinterpret_cast<uint4 *>(smem_raw + layout.fragments);
     sm.rows = reinterpret_cast<uint16_t *>(smem_raw + layout.rows);
     sm.correction = reinterpret_cast<float *>(smem_raw + layout.correction);
     sm.reduce = reinterpret_cast<float *>(smem_raw + layout.reduce);
     sm.partial = reinterpret_cast<float *>(smem_raw + layout.partial);
+    sm.ring = smem_raw + layout.ring;
 
-    const int q_width = shape.q_heads * HD;
+    const int q_width = shape.q_heads * HD, q_tiles = q_width >> 4, k_tiles = (shape.kv_heads * HD) >> 4;
     unsigned int target = 0;
     unsigned int *counter = a.buffers.barrier;
     int *error_flag = a.buffers.error_flag;
-    int parity = 0;
-    uint32_t mask = 0;
-    Ring ring;
+    int parity = 0, phase = 0;
+    WeightStream stream;
+    stream.base = sm.ring + static_cast<size_t>(warp) * RING_UNITS * RING_UNIT_BYTES;
+    stream.head = stream.tail = 0;
+    stream.in_flight = 0;
+    stream.has_following = false;
+    stream.source_phase = -1;
+    stream.remaining = 0;
 
-    auto stamp = [&](int layer, int phase) {
+    auto stamp = [&](int layer, int index) {
         if (a.buffers.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
             unsigned long long now;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            a.buffers.timing[layer * 8 + phase] = now;
+            a.buffers.timing[layer * 32 + index] = now;
         }
     };
+    // epilogue thread t < 128: high = t & 1, lane m = (t >> 1) & 7, row = (t >> 4) + 8 * high: the rotary partner
+    // rows r and r + 8 of a lane sit in neighbouring threads
+    const int epilogue_m = (threadIdx.x >> 1) & 7, epilogue_row = (threadIdx.x >> 4) + 8 * (threadIdx.x & 1);
+    const bool epilogue_active = threadIdx.x < 128 && epilogue_m < lanes;
+    const int ge = g < staged ? g : 0;  // lanes beyond the batch recompute lane 0; their results are dropped
+    const uint4 *xlane = sm.fragments + ge * 4 + j;
+
     for (int layer = 0; layer < a.layer_count; layer++) {
         const StackLayer *spec = a.layers + layer;
-        stamp(layer, 0);
-        const TiledInt4 qkv = spec->qkv, o = spec->o, gate_up = spec->gate_up, down = spec->down;
         const KvLayer kv = spec->kv;
+        for (int step = 0; step < 4; step++, phase++) {
+            // ---- the matrix of this step, and the one whose first blocks may be requested while this one drains
+            TiledInt4 matrix, next_matrix;
+            int rt = 1, next_rt = 1;
+            bool has_next = true;
+            if (step == 0) {
+                matrix = spec->qkv;
+                next_matrix = matrix;
+                has_next = false;  // attention sits in between; the o projection is requested after it
+            } else if (step == 1) {
+                matrix = spec->o;
+                next_matrix = spec->gate_up;
+                next_rt = 2;
+            } else if (step == 2) {
+                matrix = spec->gate_up;
+                rt = 2;
+                next_matrix = spec->down;
+            } else {
+                matrix = spec->down;
+                has_next = layer + 1 < a.layer_count;
+                next_matrix = has_next ? a.layers[layer + 1].qkv : matrix;
+            }
+            const MatrixWalk walk = walk_of(matrix, rt);
+            if (stream.source_phase != phase) stream_start(stream, walk, phase);
+            stream.has_following = has_next;
+            if (has_next) stream.following = walk_of(next_matrix, next_rt);
+            stream_advance(stream);
+            // the matrix after this one goes to L2 now (the gate/up pair already while attention runs)
+            if (step == 0) {
+                prefetch_matrix_l2(spec->o, 1);
+                prefetch_matrix_l2(spec->gate_up, 2);
+            } else if (step == 2) {
+                prefetch_matrix_l2(spec->down, 1);
+            } else if (step == 3 && layer + 1 < a.layer_count) {
+                prefetch_matrix_l2(a.layers[layer + 1].qkv, 1);
+            }
+            stamp(layer, 4 * step);
 
-        // ---- rms_norm + q/k/v + RoPE + KV append
-        prefetch_entry<1>(ring, mask, qkv);
-        stage_normalised_rows(sm, a.buffers.hidden, spec->input_norm, shape.hidden, staged, shape.eps, shape.norm_offset);
-        {
-            QkvEpilogue epilogue;
-            epilogue.q_tiles = q_width >> 4;
-            epilogue.k_tiles = (shape.kv_heads * HD) >> 4;
-            epilogue.head_width = HD;
-            epilogue.q_heads = shape.q_heads;
-            epilogue.q = a.buffers.q;
-            epilogue.kv = kv;
-            epilogue.lanes_meta = a.lanes_meta;
-            epilogue.rope_table = shape.rope_table;
-            epilogue.rope_positions = shape.rope_positions;
-            matrix_phase<1, 0>(qkv, qkv, ring, mask, sm, staged, lanes, parity, epilogue);
-        }
-        grid_barrier(counter, target, error_flag);
-        stamp(layer, 1);
+            // ---- activations of this step into fragment order
+            if (step == 0 || step == 2) {
+                normalise_rows(sm, a.buffers.hidden, step == 0 ? spec->input_norm : spec->post_norm, shape.hidden, staged, shape.eps,
+                               shape.norm_offset);
+                if (step == 2) stamp(layer, 16);
+                stage_rows(sm, nullptr, false, shape.hidden, staged);
+            } else if (step == 1) {
+                stage_rows(sm, a.buffers.attention_out, true, q_width, staged);
+            } else {
+                stage_rows(sm, a.buffers.activation, true, shape.ffn, staged);
+            }
+            stamp(layer, 4 * step + 1);
 
-        // ---- attention: (kv head, split, stream x lane group) items over all teams of the grid
-        {
-            const int team = threadIdx.x >> 7, team_tid = threadIdx.x & 127;
-            const int streams = lanes / a.lanes_per_stream;
-            const int group_slots = streams * ((a.lanes_per_stream + QL - 1) / QL);
-            const int total = shape.kv_heads * a.max_splits * group_slots;
-            uint8_t *team_smem = smem_raw + static_cast<size_t>(team) * attention_team_smem<HD, GROUP, QL>();
-            for (int item = blockIdx.x * ATTENTION_TEAMS + team; item < total; item += gridDim.x * ATTENTION_TEAMS) {
-                const int kv_head = item % shape.kv_heads, rest = item / shape.kv_heads;
-                const int split = rest % a.max_splits, group_slot = rest / a.max_splits;
-                attention_tile_body<HD, GROUP, QL, true>(a.buffers.q, kv, a.lanes_meta, lanes, a.lanes_per_stream, shape.q_heads,
-                                                         shape.attention_scale, a.split_tokens, a.max_splits,
-                                                         a.buffers.attention_scratch, kv_head, split, group_slot, team_smem, team_tid,
-                                                         1 + team);
+            // ---- the CTA's tiles: every warp takes each 16th group of K, then the tile is reduced and finished
+            float acc[2][4];
+#pragma unroll
+            for (int r = 0; r < 2; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+            int tile = blockIdx.x;
+            for (int t = 0; t < walk.tiles; t++, tile += gridDim.x) {
+                // what the epilogue needs from memory is requested before the tile's arithmetic
+                uint32_t payload = 0;
+                if (epilogue_active) {
+                    if (step == 0) {
+                        if (tile < q_tiles + k_tiles) {
+                            const int local = tile < q_tiles ? tile : tile - q_tiles;
+                            const int d = 8 * (local % (HD >> 4)) + (epilogue_row & 7);
+                            payload = __ldg(shape.rope_table + static_cast<size_t>(a.lanes_meta.position[epilogue_m] % shape.rope_positions) * (HD >> 1) + d);
+                        }
+                    } else if (step != 2) {
+                        payload = __ldcg(a.buffers.hidden + static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row);
+                    }
+                }
+                for (int gi = 0; gi < walk.per_tile; gi++) {
+                    const int group = warp + gi * STACK_WARPS;
+                    uint4 b[4];
+#pragma unroll
+                    for (int word = 0; word < 4; word++) b[word] = xlane[(group * 4 + word) * staged * 4];
+                    const float2 bias = *reinterpret_cast<const float2 *>(sm.correction + group * 8 + 2 * j);
+                    async_wait(stream.in_flight - 1);  // everything but the groups requested after this item's
+                    stream.in_flight--;
+                    consume_unit(stream.base + (stream.head % RING_UNITS) * RING_UNIT_BYTES, b, bias, acc[0]);
+                    if (rt == 2) consume_unit(stream.base + ((stream.head + 1) % RING_UNITS) * RING_UNIT_BYTES, b, bias, acc[1]);
+                    stream.head += rt;
+                    stream_advance(stream);
+                }
+                float *mine = sm.reduce + static_cast<size_t>((parity * STACK_WARPS + warp) * 32) * 8;
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    if (r < rt) {
+                        *reinterpret_cast<float2 *>(mine + (r * 16 + g) * 8 + 2 * j) = make_float2(acc[r][0], acc[r][1]);
+                        *reinterpret_cast<float2 *>(mine + (r * 16 + g + 8) * 8 + 2 * j) = make_float2(acc[r][2], acc[r][3]);
+                    }
+                    acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+                }
+                __syncthreads();
+                if (threadIdx.x < 128) {  // whole warps: the q/k epilogue exchanges partner rows by shuffle
+                    const float *src = sm.reduce + static_cast<size_t>(parity * STACK_WARPS * 32 + epilogue_row) * 8 + epilogue_m;
+                    float first = 0.0f, second = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < STACK_WARPS; w++) {
+                        first += src[w * 32 * 8];
+                        if (rt == 2) second += src[(w * 32 + 16) * 8];
+                    }
+                    if (step == 0) {
+                        // q / k: rotary_bf16.comp.template:99-109 (non-interleaved, rotary width = head width, five bf16
+                        // roundings); k and v go into the lane's KV page (append_gqa_attention_bf16.comp.template:189-215)
+                        const float mine_value = round_bf16(first);
+                        const float partner = __shfl_xor_sync(0xffffffffu, mine_value, 1);  // the row 8 further (or 8 back)
+                        if (epilogue_active) {
+                            const uint32_t position = a.lanes_meta.position[epilogue_m];
+                            const int slot = a.lanes_meta.slot[epilogue_m];
+                            if (tile < q_tiles + k_tiles) {
+                                const bool is_q = tile < q_tiles, high = epilogue_row >= 8;
+                                const int local = is_q ? tile : tile - q_tiles;
+                                const int head = local / (HD >> 4), d = 8 * (local % (HD >> 4)) + (epilogue_row & 7) + (high ? HD / 2 : 0);
+                                const float cosine = bf16_lo(payload), sine = bf16_hi(payload);
+                                // d < half: x cos + (-x[d + half]) sin;  d >= half: x cos + x[d - half] sin
+                                const float other = high ? partner : -partner;
+                                const uint16_t value = static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(mine_value * cosine) + round_bf16(other * sine)));
+                                if (is_q) a.buffers.q[(static_cast<size_t>(epilogue_m) * shape.q_heads + head) * HD + d] = value;
+                                else if (slot >= 0 && kv.capacity != 0) kv.pool[kv_token_offset(kv, slot, position % kv.capacity, head, false) + d] = value;
+                            } else if (slot >= 0 && kv.capacity != 0) {
+                                const int index = (tile - q_tiles - k_tiles) * 16 + epilogue_row;
+                                kv.pool[kv_token_offset(kv, slot, position % kv.capacity, index / HD, true) + index % HD] =
+                                    static_cast<uint16_t>(f32_to_bf16_bits(first));
+                            }
+                        }
+                    } else if (epilogue_active) {
+                        if (step == 2) {
+                            // silu_multiply_bf16.comp.template:30-52: bf16(silu_bf16(bf16 gate) * bf16 up)
+                            a.buffers.activation[static_cast<size_t>(epilogue_m) * shape.ffn + tile * 16 + epilogue_row] =
+                                static_cast<uint16_t>(f32_to_bf16_bits(rounded_silu(round_bf16(first)) * round_bf16(second)));
+                        } else {
+                            // linear + residual_add (add_bf16.comp.template:17-24): bf16(bf16(product) + residual), in place
+                            a.buffers.hidden[static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row] =
+                                static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(first) + bf16_bits_to_f32(payload)));
+                        }
+                    }
+                }
+                parity ^= 1;
+            }
+            stamp(layer, 4 * step + 2);
+            grid_barrier(counter, target, error_flag);
+            stamp(layer, 4 * step + 3);
+
+            if (step == 0) {
+                // ---- attention: (kv head, split, stream x lane group) items, one warp each, spread over the SMs first
+                const int streams = lanes / a.lanes_per_stream;
+                const int group_slots = streams * ((a.lanes_per_stream + QL - 1) / QL);
+                const int total = shape.kv_heads * a.max_splits * group_slots;
+                for (int item = blockIdx.x + gridDim.x * warp; item < total; item += gridDim.x * STACK_WARPS) {
+                    const int kv_head = item % shape.kv_heads, rest = item / shape.kv_heads;
+                    attention_warp_item<HD, GROUP, QL>(a.buffers.q, kv, a.lanes_meta, lanes, a.lanes_per_stream, shape.q_heads,
+                                                       shape.attention_scale, a.max_splits, a.buffers.attention_scratch, kv_head,
+                                                       rest % a.max_splits, rest / a.max_splits);
+                }
+                stamp(layer, 17);
+                // the o projection's first blocks stream while the grid meets and merges
+                stream_start(stream, walk_of(spec->o, 1), phase + 1);
+                stream.has_following = false;
+                stream_advance(stream);
+                grid_barrier(counter, target, error_flag);
+                stamp(layer, 18);
+                const int pairs = lanes * shape.q_heads;
+                for (int pair = blockIdx.x + gridDim.x * warp; pair < pairs; pair += gridDim.x * STACK_WARPS)
+                    attention_merge_warp<HD>(a.buffers.attention_scratch, a.buffers.attention_out, kv, a.lanes_meta, pair, shape.q_heads,
+                                             a.max_splits);
+                stamp(layer, 19);
+                grid_barrier(counter, target, error_flag);
             }
         }
-        prefetch_entry<1>(ring, mask, o);
-        grid_barrier(counter, target, error_flag);
-        stamp(layer, 2);
-        {
-            const int pairs = lanes * shape.q_heads;
-            for (int pair = blockIdx.x * STACK_WARPS + (threadIdx.x >> 5); pair < pairs; pair += gridDim.x * STACK_WARPS)
-                attention_merge_pair<true>(a.buffers.attention_scratch, a.buffers.attention_out, kv, a.lanes_meta, pair, threadIdx.x & 31,
-                                           shape.q_heads, HD, a.split_tokens, a.max_splits);
-        }
-        grid_barrier(counter, target, error_flag);
-        stamp(layer, 3);
-
-        // ---- o projection + residual
-        stage_global_rows(sm, a.buffers.attention_out, q_width, staged);
-        matrix_phase<1, 2>(o, gate_up, ring, mask, sm, staged, lanes, parity, ResidualEpilogue{a.buffers.hidden, shape.hidden});
-        grid_barrier(counter, target, error_flag);
-        stamp(layer, 4);
-
-        // ---- rms_norm + gate/up + SiLU multiply
-        prefetch_entry<2>(ring, mask, gate_up);
-        stage_normalised_rows(sm, a.buffers.hidden, spec->post_norm, shape.hidden, staged, shape.eps, shape.norm_offset);
-        matrix_phase<2, 1>(gate_up, down, ring, mask, sm, staged, lanes, parity, SiluEpilogue{a.buffers.activation, shape.ffn});
-        grid_barrier(counter, target, error_flag);
-        stamp(layer, 5);
-
-        // ---- down projection + residual
-        prefetch_entry<1>(ring, mask, down);
-        stage_global_rows(sm, a.buffers.activation, shape.ffn, staged);
-        if (layer + 1 < a.layer_count) {
-            const TiledInt4 following = a.layers[layer + 1].qkv;
-            matrix_phase<1, 1>(down, following, ring, mask, sm, staged, lanes, parity, ResidualEpilogue{a.buffers.hidden, shape.hidden});
-        } else {
-            matrix_phase<1, 0>(down, down, ring, mask, sm, staged, lanes, parity, ResidualEpilogue{a.buffers.hidden, shape.hidden});
-        }
-        grid_barrier(counter, target, error_flag);
-        stamp(layer, 6);
     }
 
     // The last CTA to leave rearms the barrier words for the next launch (every CTA has passed its last barrier
@@ -656,20 +957,12 @@ cudaError_t launch_instance(const StackArgs &args, size_t smem, cudaStream_t str
     return cudaLaunchKernelEx(&config, decode_stack_kernel<HD, GROUP>, args);
 }
 
-template <int HD, int GROUP>
-size_t attention_bytes_of() {
-    return ATTENTION_TEAMS * attention_team_smem<HD, GROUP, AttentionTeam<GROUP>::QL>();
-}
-
 bool instance_smem(const StackShape &shape, int lanes, size_t *bytes) {
     const int group = shape.kv_heads > 0 ? shape.q_heads / shape.kv_heads : 0;
-    size_t attention = 0;
-    if (shape.head_width == 128 && group == 4) attention = attention_bytes_of<128, 4>();
-    else if (shape.head_width == 128 && group == 8) attention = attention_bytes_of<128, 8>();
-    else if (shape.head_width == 64 && group == 4) attention = attention_bytes_of<64, 4>();
-    else if (shape.head_width == 32 && group == 2) attention = attention_bytes_of<32, 2>();
-    else return false;
-    *bytes = stack_smem_layout(shape, lanes < 8 ? lanes : 8, attention).total;
+    const bool built = (shape.head_width == 128 && (group == 4 || group == 8)) || (shape.head_width == 64 && group == 4) ||
+                       (shape.head_width == 32 && group == 2);
+    if (!built) return false;
+    *bytes = stack_smem_layout(shape, lanes < 8 ? lanes : 8).total;
     return true;
 }
 
@@ -701,7 +994,7 @@ cudaError_t launch_int4_tile_major(const RelayoutSegment *segments, int count, b
 bool decode_stack_supported(const StackShape &shape, int lanes, size_t *smem_bytes) {
     size_t bytes = 0;
     if (lanes < 1 || lanes > 8) return false;
-    if (shape.hidden % 128 != 0 || shape.ffn % 128 != 0 || (shape.q_heads * shape.head_width) % 128 != 0) return false;
+    if (shape.hidden > NORM_WORDS * 2 * STACK_THREADS || shape.hidden % 128 != 0 || shape.ffn % 128 != 0 || (shape.q_heads * shape.head_width) % 128 != 0) return false;
     if (!instance_smem(shape, lanes, &bytes)) return false;
     if (bytes > 227 * 1024) return false;
     if (smem_bytes) *smem_bytes = bytes;

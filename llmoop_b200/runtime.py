@@ -208,14 +208,14 @@ class Engine:
         _check(library().nerve_b200_engine_set_decode_stack(self._handle, int(enabled)))
 
     def decode_stack_timing(self):
-        """[layers][8] nanosecond stamps of the last profiled target-stack launch (see the header)."""
+        """[layers][32] nanosecond stamps of the last profiled target-stack launch (see the header)."""
         import numpy as np
 
         count = ctypes.c_size_t(0)
         _check(library().nerve_b200_engine_decode_stack_timing(self._handle, None, ctypes.c_size_t(0), ctypes.byref(count)))
         stamps = (ctypes.c_uint64 * max(1, count.value))()
         _check(library().nerve_b200_engine_decode_stack_timing(self._handle, stamps, ctypes.c_size_t(count.value), ctypes.byref(count)))
-        return np.array(stamps[:count.value], dtype=np.uint64).reshape(-1, 8)
+        return np.array(stamps[:count.value], dtype=np.uint64).reshape(-1, 32)
 
     def set_profiling(self, enabled: bool):
         _check(library().nerve_b200_engine_set_profiling(self._handle, int(enabled)))
