@@ -199,6 +199,23 @@ int32_t nerve_b200_op_linear_fp8(const void *x_device, const void *w_device, con
 int32_t nerve_b200_op_greedy(const void *logits_device, void *records_device, void *scratch_device, int32_t lanes,
                              int32_t vocab, void *stream);
 uint64_t nerve_b200_op_greedy_scratch_bytes(int32_t lanes);
+/* The same arg-max for callers that must not allocate device memory and have none to lend: the partial winners
+ * of the two-stage reduction live in a 32 KB device array built into the library, so neither this call nor the
+ * caller ever allocates or frees anything.  No counterpart in the reference (its sampler dispatch always binds a
+ * buffer the runtime allocated at mount).
+ * Who needs it: a sampler thread inside a serving process whose device memory was carved up once at start-up
+ * (a later cudaMalloc may fail under fragmentation, and it synchronises the whole device, stalling every other
+ * stream's decode step), or code that runs where allocation is forbidden outright, such as a host callback
+ * enqueued on a stream.
+ * Limits and rules:
+ *  - at most 64 lanes per call; more is rejected with an error naming the limit (use nerve_b200_op_greedy);
+ *  - the first call on each device looks up the array's device address (with that device current) and caches
+ *    it: make that first call during set-up, before any stream capture is begun;
+ *  - the array is shared by every caller in the process and keeps the last call's partials.  A call overwrites
+ *    every slot it later reads, so nothing has to be cleared, but two calls that overlap in time on one device
+ *    (two streams, two threads) race: issue them on one stream or order them yourself. */
+int32_t nerve_b200_op_greedy_static(const void *logits_device, void *records_device, int32_t lanes, int32_t vocab,
+                                    void *stream);
 /* Kernel-ABI byte layouts of the reference (pure host functions): the 20-byte stream-control record
  * (stream_control_bytes.rs:8-18) and the transient-state header + page table
  * (transient_state_buffer_layout.rs:24-154; out_layout = {block capacity, page count, page bytes, page-table

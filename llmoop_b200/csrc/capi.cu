@@ -405,6 +405,21 @@ int32_t nerve_b200_op_greedy(const void *logits, void *records, void *scratch, i
 
 uint64_t nerve_b200_op_greedy_scratch_bytes(int32_t lanes) { return argmax_scratch_bytes(lanes); }
 
+int32_t nerve_b200_op_greedy_static(const void *logits, void *records, int32_t lanes, int32_t vocab, void *stream) {
+    if (lanes < 0 || vocab <= 0 || logits == nullptr || records == nullptr) {
+        last_error = "nerve_b200_op_greedy_static: null pointer or non-positive size";
+        return NERVE_B200_ERROR;
+    }
+    if (lanes > argmax_static_max_lanes()) {
+        last_error = "nerve_b200_op_greedy_static: " + std::to_string(lanes) + " lanes exceed the built-in scratch of " +
+                     std::to_string(argmax_static_max_lanes()) + " lanes; use nerve_b200_op_greedy with a caller-provided scratch buffer";
+        return NERVE_B200_ERROR;
+    }
+    return cuda_status(launch_argmax_static(static_cast<const float *>(logits), static_cast<uint32_t *>(records), lanes, vocab,
+                                            static_cast<cudaStream_t>(stream)),
+                       "nerve_b200_op_greedy_static");
+}
+
 int32_t nerve_b200_stream_control_bytes(uint32_t token_id, uint64_t stream_tick, uint32_t control_flags, uint32_t capacity,
                                         uint8_t *out_20_bytes) {
     return guarded([&] {

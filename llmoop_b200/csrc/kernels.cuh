@@ -192,5 +192,9 @@ cudaError_t launch_accept(const uint32_t *verify_tokens, const uint32_t *target_
 // `scratch` holds argmax_scratch_bytes(lanes) bytes of per-chunk partial winners.
 size_t argmax_scratch_bytes(int lanes);
 cudaError_t launch_argmax(const float *logits, uint32_t *records, int lanes, int vocab, void *scratch, cudaStream_t stream);
+// The same with the partial winners in a fixed device array of the library (no allocation anywhere); at most
+// argmax_static_max_lanes() lanes, one call at a time per device.
+int argmax_static_max_lanes();
+cudaError_t launch_argmax_static(const float *logits, uint32_t *records, int lanes, int vocab, cudaStream_t stream);
 
 }  // namespace nerve

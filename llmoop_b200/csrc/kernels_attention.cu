@@ -261,4 +261,35 @@ cudaError_t launch_argmax(const float *logits, uint32_t *records, int lanes, int
     return cudaGetLastError();
 }
 
+// ---- greedy arg-max without a caller-provided scratch buffer -------------------------------------------------
+// Same two kernels as launch_argmax, with the per-chunk partial winners kept in a fixed device array that is part
+// of the library image (32 KB, enough for STATIC_ARGMAX_MAX_LANES lanes).  Nothing is allocated, by this function
+// or on its behalf: the array's device address is looked up once per device (cudaGetSymbolAddress; the array's
+// name on the host side is not a device pointer) with that device current, and cached.
+// Every partial slot the second kernel reads is written by the first kernel of the same call, so nothing needs
+// clearing between calls; the array does keep the previous call's partials and is shared by all callers in the
+// process, so two calls that overlap in time on one device (different streams or threads) race on it.
+constexpr int STATIC_ARGMAX_MAX_LANES = 64;
+constexpr int STATIC_ARGMAX_MAX_DEVICES = 64;
+static __device__ __align__(256) unsigned char static_argmax_scratch[STATIC_ARGMAX_MAX_LANES * ARGMAX_CHUNKS * 8];
+
+int argmax_static_max_lanes() { return STATIC_ARGMAX_MAX_LANES; }
+
+cudaError_t launch_argmax_static(const float *logits, uint32_t *records, int lanes, int vocab, cudaStream_t stream) {
+    if (lanes <= 0) return cudaSuccess;
+    if (lanes > STATIC_ARGMAX_MAX_LANES) return cudaErrorInvalidValue;
+    static void *device_address[STATIC_ARGMAX_MAX_DEVICES] = {};
+    int device = 0;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status != cudaSuccess) return status;
+    if (device < 0 || device >= STATIC_ARGMAX_MAX_DEVICES) return cudaErrorInvalidDevice;
+    if (device_address[device] == nullptr) {
+        void *address = nullptr;
+        status = cudaGetSymbolAddress(&address, static_argmax_scratch);
+        if (status != cudaSuccess) return status;
+        device_address[device] = address;
+    }
+    return launch_argmax(logits, records, lanes, vocab, device_address[device], stream);
+}
+
 }  // namespace nerve

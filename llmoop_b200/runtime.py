@@ -71,7 +71,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair", "nerve_b200_set_int4_kernel",
     "nerve_b200_op_linear_bf16", "nerve_b200_op_rms_norm", "nerve_b200_op_linear_fp8",
-    "nerve_b200_op_greedy", "nerve_b200_op_greedy_scratch_bytes", "nerve_b200_verify_prefix",
+    "nerve_b200_op_greedy", "nerve_b200_op_greedy_scratch_bytes", "nerve_b200_op_greedy_static", "nerve_b200_verify_prefix",
     "nerve_b200_stream_control_bytes", "nerve_b200_state_page_table_bytes",
 )
 
