@@ -24,6 +24,8 @@
 //    (lane, head) by one warp after a barrier.
 // The per-layer code is one loop over the four matrix steps with run-time matrix / epilogue selection: the
 // straight-line form of the same steps did not fit the instruction cache and spent most of its time refetching.
+#include <cstdlib>
+
 #include "attention_body.cuh"
 #include "common.cuh"
 #include "kernels.cuh"
@@ -34,7 +36,7 @@ namespace {
 
 constexpr int STACK_WARPS = 16;
 constexpr int STACK_THREADS = STACK_WARPS * 32;
-constexpr int RING_UNITS = 4;          // 16x128 weight blocks (1 KB + scales) a warp keeps in flight
+constexpr int MAX_RING_UNITS = 8;      // 16x128 weight blocks (1 KB + scales) a warp keeps in flight, at most
 constexpr unsigned int BARRIER_SPIN_LIMIT = 1u << 20;
 
 // ------------------------------------------------------------------------------------------ tile-major copy
@@ -158,13 +160,14 @@ struct StackSmem {
 
 constexpr int RING_UNIT_BYTES = 2 * 512 + 128;
 
-__device__ __forceinline__ void async_copy16(void *shared_destination, const void *source) {
-    const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination));
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(address), "l"(source) : "memory");
+// cp.async with shared-space destination addresses and byte offsets folded into the instruction.
+template <int DST_OFFSET, int SRC_OFFSET>
+__device__ __forceinline__ void async_copy16(uint32_t shared_address, const void *source) {
+    asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;" ::"r"(shared_address), "l"(source), "n"(DST_OFFSET), "n"(SRC_OFFSET) : "memory");
 }
-__device__ __forceinline__ void async_copy4(void *shared_destination, const void *source) {
-    const uint32_t address = static_cast<uint32_t>(__cvta_generic_to_shared(shared_destination));
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(address), "l"(source) : "memory");
+template <int SRC_OFFSET>
+__device__ __forceinline__ void async_copy4(uint32_t shared_address, const void *source) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1+%2], 4;" ::"r"(shared_address), "l"(source), "n"(SRC_OFFSET) : "memory");
 }
 __device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 // Waits until at most `newer` of this thread's copy groups are still in flight.
@@ -173,7 +176,11 @@ __device__ __forceinline__ void async_wait(int newer) {
     case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
     case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
     case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
     }
 }
 
@@ -197,32 +204,68 @@ __device__ __forceinline__ MatrixWalk walk_of(const TiledInt4 &matrix, int rt) {
 }
 
 struct WeightStream {
-    uint8_t *base;          // this warp's RING_UNITS units
-    uint32_t head, tail;    // units consumed / requested so far
+    const uint8_t *ring;    // this thread's 16 bytes (first half) of ring unit 0; the scale word is at scale_offset from it
+    uint32_t ring_shared;   // the same position as a shared-space address, for the copies
+    int scale_offset;       // 1024 + lane * 4 - lane * 16
+    int units;              // ring units of this warp (2..MAX_RING_UNITS, as shared memory allows)
+    int head, tail;         // ring positions (unit index) of the next block to consume / to request
+    int used;               // units requested and not yet consumed
     int in_flight;          // items (copy groups) requested and not yet consumed
-    MatrixWalk source;      // the matrix the producer is requesting from
-    int source_phase;       // its phase number
-    int remaining, gi;      // items of it still to request; position inside the current tile
+    // producer: the matrix being requested from, and the position in it
+    int source_phase, rt, per_tile, remaining, gi;
     const uint4 *weights;   // this thread's 16 bytes of the next block to request
     const uint32_t *scales; // and its scale pair
+    long long step, tile_step;  // blocks to move on by inside a tile / to the first block of the CTA's next tile
     MatrixWalk following;   // the matrix after it (valid when has_following)
     bool has_following;
 };
 
 __device__ __forceinline__ void stream_start(WeightStream &stream, const MatrixWalk &walk, int phase) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    stream.source = walk;
     stream.source_phase = phase;
+    stream.rt = walk.rt;
+    stream.per_tile = walk.per_tile;
     stream.remaining = walk.total;
     stream.gi = 0;
     const size_t block = (static_cast<size_t>(blockIdx.x) * walk.matrix.groups + warp) * walk.rt;
     stream.weights = walk.matrix.weights + block * 64 + lane;
     stream.scales = walk.matrix.scales + block * 8 + (lane >> 2);
+    stream.step = static_cast<long long>(STACK_WARPS) * walk.rt;
+    stream.tile_step = (static_cast<long long>(gridDim.x) * walk.matrix.groups - (walk.per_tile - 1) * STACK_WARPS) * walk.rt;
 }
 
-// Requests as many blocks as the ring has room for.
+// Requests the producer's next item (the ring has room and the matrix has items left).
+__device__ __forceinline__ void stream_issue(WeightStream &stream) {
+    {
+        const uint32_t unit = stream.ring_shared + stream.tail * RING_UNIT_BYTES;
+        async_copy16<0, 0>(unit, stream.weights);
+        async_copy16<512, 512>(unit, stream.weights);
+        async_copy4<0>(unit + stream.scale_offset, stream.scales);
+        stream.tail = stream.tail + 1 == stream.units ? 0 : stream.tail + 1;
+    }
+    if (stream.rt == 2) {
+        const uint32_t unit = stream.ring_shared + stream.tail * RING_UNIT_BYTES;
+        async_copy16<0, 1024>(unit, stream.weights);
+        async_copy16<512, 1536>(unit, stream.weights);
+        async_copy4<32>(unit + stream.scale_offset, stream.scales);
+        stream.tail = stream.tail + 1 == stream.units ? 0 : stream.tail + 1;
+    }
+    async_commit();
+    stream.used += stream.rt;
+    stream.in_flight++;
+    stream.remaining--;
+    // next block of this warp: 16 groups on, or the first group of the CTA's next tile
+    long long blocks = stream.step;
+    if (++stream.gi == stream.per_tile) {
+        stream.gi = 0;
+        blocks = stream.tile_step;
+    }
+    stream.weights += blocks * 64;
+    stream.scales += blocks * 8;
+}
+
+// Requests as many blocks as the ring has room for, moving on to the following matrix when this one is done.
 __device__ __forceinline__ void stream_advance(WeightStream &stream) {
-    const int lane = threadIdx.x & 31;
     while (true) {
         if (stream.remaining == 0) {
             if (!stream.has_following) break;
@@ -230,26 +273,8 @@ __device__ __forceinline__ void stream_advance(WeightStream &stream) {
             stream.has_following = false;
             continue;
         }
-        const int rt = stream.source.rt;
-        if (RING_UNITS - static_cast<int>(stream.tail - stream.head) < rt) break;
-        for (int r = 0; r < rt; r++) {
-            uint8_t *unit = stream.base + ((stream.tail + r) % RING_UNITS) * RING_UNIT_BYTES;
-            async_copy16(unit + lane * 16, stream.weights + r * 64);
-            async_copy16(unit + 512 + lane * 16, stream.weights + r * 64 + 32);
-            async_copy4(unit + 1024 + lane * 4, stream.scales + r * 8);
-        }
-        async_commit();
-        stream.tail += rt;
-        stream.in_flight++;
-        stream.remaining--;
-        // next block of this warp: 16 groups on, or the first group of the CTA's next tile
-        int blocks = STACK_WARPS;
-        if (++stream.gi == stream.source.per_tile) {
-            stream.gi = 0;
-            blocks = static_cast<int>(gridDim.x) * stream.source.matrix.groups - (stream.source.per_tile - 1) * STACK_WARPS;
-        }
-        stream.weights += static_cast<size_t>(blocks) * rt * 64;
-        stream.scales += static_cast<size_t>(blocks) * rt * 8;
+        if (stream.units - stream.used < stream.rt) break;
+        stream_issue(stream);
     }
 }
 
@@ -401,26 +426,37 @@ __device__ __forceinline__ void normalise_rows(const StackSmem &sm, const uint16
 }
 
 // ------------------------------------------------------------------------------------------ attention
-// One warp serves one context split (64 tokens) of one kv head for the Q = QL * GROUP <= 16 query vectors of QL
-// consecutive lanes of a stream (append_gqa_attention_bf16.comp.template:217-339: f32 scores of bf16 q.k, f32
-// softmax, f32 p.v).  Scores and p.v run on the tensor cores: q rows are the A operand of S = Q K^T, K rows the
-// B operand (both read with 16-byte loads; the head dimension is permuted identically on both sides); the
-// probabilities are re-used from the accumulator registers as the A operand of O = P V, split into a bf16 high
-// and low part (p = hi + lo to 2^-17), and V is the B operand, its token pairs assembled with byte permutes.
-// The partial (unnormalised output, running maximum, sum) goes to the scratch the merge step reads.
+// A team of four warps serves one context split (64 tokens) of one kv head for the Q = QL * GROUP <= 16 query
+// vectors of QL consecutive lanes of a stream (append_gqa_attention_bf16.comp.template:217-339: f32 scores of
+// bf16 q.k, f32 softmax, f32 p.v); warp w of the team takes tokens 16w .. 16w + 15 of the split.  Scores and p.v
+// run on the tensor cores: q rows are the A operand of S = Q K^T, K rows the B operand (both read with 16-byte
+// loads; the head dimension is permuted identically on both sides); the probabilities are re-used from the
+// accumulator registers as the A operand of O = P V, split into a bf16 high and low part (p = hi + lo to 2^-17),
+// and V is the B operand, its token pairs assembled with byte permutes.  The warps agree on the split's row
+// maxima through shared memory, add up their partial outputs there, and the team writes one partial
+// (unnormalised output, maximum, sum) to the scratch the merge step reads.
 
-__device__ __forceinline__ uint32_t pack_bf16_pair(float low, float high) { return pack_bf16(low, high); }
+__device__ __forceinline__ void team_barrier(int barrier_id) { asm volatile("bar.sync %0, 128;" ::"r"(barrier_id) : "memory"); }
+
+template <int HD>
+__host__ __device__ constexpr size_t attention_team_bytes() {
+    return (4 * 16 * HD + 2 * 4 * 16) * sizeof(float);  // partial outputs [warp][row][dim], maxima and sums [warp][row]
+}
 
 template <int HD, int GROUP, int QL>
-__device__ __forceinline__ void attention_warp_item(const uint16_t *__restrict__ q, const KvLayer &kv, const LaneTable &lanes_meta,
+__device__ __forceinline__ void attention_team_item(const uint16_t *__restrict__ q, const KvLayer &kv, const LaneTable &lanes_meta,
                                                     int lanes, int lanes_per_stream, int q_heads, float scale, int max_splits,
-                                                    float *__restrict__ scratch, int kv_head, int split, int group_slot) {
+                                                    float *__restrict__ scratch, int kv_head, int split, int group_slot,
+                                                    float *team_smem, int team_warp, int barrier_id) {
     constexpr int Q = QL * GROUP;
     constexpr int QW = HD / 32;                    // 16-byte pieces of a q / k row per thread
     constexpr int HALF = HD < 64 ? HD : 64;        // head dims handled per output pass
     constexpr int DPT = HALF / 8;                  // of which one thread column owns this many
     static_assert(Q <= 16 && HD % 32 == 0, "attention team shape");
     const int lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
+    float *partial_out = team_smem;                       // [4][16][HD]
+    float *team_max = team_smem + 4 * 16 * HD;            // [4][16]
+    float *team_sum = team_max + 4 * 16;                  // [4][16]
     const int groups_per_stream = (lanes_per_stream + QL - 1) / QL;
     const int stream_index = group_slot / groups_per_stream, group_index = group_slot % groups_per_stream;
     const int lane0 = stream_index * lanes_per_stream + group_index * QL;
@@ -441,8 +477,9 @@ __device__ __forceinline__ void attention_warp_item(const uint16_t *__restrict__
     const uint32_t tokens = newest + 1u < capacity ? newest + 1u : capacity;  // attended window of the newest lane
     const uint32_t first_tick = newest + 1u - tokens;
     const uint32_t begin = static_cast<uint32_t>(split) * 64u;
-    if (begin >= tokens) return;
+    if (begin >= tokens) return;  // the whole team leaves: nobody waits at the team barrier
     const int count = static_cast<int>(tokens - begin < 64u ? tokens - begin : 64u);
+    const int token0 = 16 * team_warp;  // this warp's tokens of the split
     // ring index of the split's first token; element offset of token t's K (or V) row of this kv head
     const uint32_t ring_base = (first_tick + begin) % capacity;
     const int page_shift = (kv.page_tokens & (kv.page_tokens - 1)) == 0 ? __ffs(kv.page_tokens) - 1 : -1;
@@ -457,7 +494,7 @@ __device__ __forceinline__ void attention_warp_item(const uint16_t *__restrict__
                (static_cast<size_t>(kv_head) * kv.page_tokens + within) * HD;
     };
 
-    // ---- S = Q K^T
+    // ---- S = Q K^T for 16 tokens
     uint4 qf[2][QW];
 #pragma unroll
     for (int r = 0; r < 2; r++) {
@@ -467,10 +504,10 @@ __device__ __forceinline__ void attention_warp_item(const uint16_t *__restrict__
 #pragma unroll
         for (int w = 0; w < QW; w++) qf[r][w] = valid ? __ldcg(reinterpret_cast<const uint4 *>(source) + w) : make_uint4(0, 0, 0, 0);
     }
-    float s[8][4];
+    float s[2][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; nt++) {
-        const int token = nt * 8 + g;
+    for (int nt = 0; nt < 2; nt++) {
+        const int token = token0 + nt * 8 + g;
         uint4 kf[QW];
         if (token < count) {
             const uint16_t *krow = kv.pool + row_offset(token, false) + j * (HD / 4);
@@ -487,28 +524,42 @@ __device__ __forceinline__ void attention_warp_item(const uint16_t *__restrict__
             mma_bf16_16816(s[nt], qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, kf[w].z, kf[w].w);
         }
     }
+    // V rows of this warp's tokens 2j, 2j+1, 2j+8, 2j+9 (requested now, used after the softmax)
+    size_t v_offset[4];
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+        const int token = token0 + 2 * j + (t & 1) + 8 * (t >> 1);
+        v_offset[t] = token < count ? row_offset(token, true) : static_cast<size_t>(-1);
+    }
 
-    // ---- causal / ring mask, scale, softmax of the split (rows g and g + 8; columns 2j, 2j + 1 of every 8 tokens)
+    // ---- causal / ring mask, scale; the team's row maxima; probabilities
     float row_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int nt = 0; nt < 8; nt++)
+    for (int nt = 0; nt < 2; nt++)
 #pragma unroll
         for (int c = 0; c < 4; c++) {
-            const int token = nt * 8 + 2 * j + (c & 1);
+            const int token = token0 + nt * 8 + 2 * j + (c & 1);
             const uint32_t tick = tick_row[c >> 1], token_tick = first_tick + begin + token;
             const bool visible = token < count && tick != 0xffffffffu && token_tick <= tick && token_tick + capacity > tick;
             s[nt][c] = visible ? s[nt][c] * scale : -INFINITY;
             row_max[c >> 1] = fmaxf(row_max[c >> 1], s[nt][c]);
         }
-    float row_sum[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int r = 0; r < 2; r++) {
         row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 1));
         row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 2));
+        if (j == 0) team_max[team_warp * 16 + g + 8 * r] = row_max[r];
+    }
+    team_barrier(barrier_id);
+    float row_sum[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        const int row = g + 8 * r;
+        row_max[r] = fmaxf(fmaxf(team_max[row], team_max[16 + row]), fmaxf(team_max[32 + row], team_max[48 + row]));
         row_max[r] = fmaxf(row_max[r], -3.4028234663852886e38f);
     }
 #pragma unroll
-    for (int nt = 0; nt < 8; nt++)
+    for (int nt = 0; nt < 2; nt++)
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             s[nt][c] = s[nt][c] == -INFINITY ? 0.0f : expf(s[nt][c] - row_max[c >> 1]);
@@ -518,78 +569,78 @@ __device__ __forceinline__ void attention_warp_item(const uint16_t *__restrict__
     for (int r = 0; r < 2; r++) {
         row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 1);
         row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
+        if (j == 0) team_sum[team_warp * 16 + g + 8 * r] = row_sum[r];
     }
-    // probabilities as A fragments of 16 tokens per step: high and low bf16 parts
-    uint32_t ph[4][4], pl[4][4];
+    // probabilities as the A fragment of this warp's 16 tokens: high and low bf16 parts
+    uint32_t ph[4], pl[4];
 #pragma unroll
-    for (int ks = 0; ks < 4; ks++)
-#pragma unroll
-        for (int f = 0; f < 4; f++) {
-            const float first = s[2 * ks + (f >> 1)][2 * (f & 1)], second = s[2 * ks + (f >> 1)][2 * (f & 1) + 1];
-            ph[ks][f] = pack_bf16_pair(first, second);
-            pl[ks][f] = pack_bf16_pair(first - bf16_lo(ph[ks][f]), second - bf16_hi(ph[ks][f]));
-        }
+    for (int f = 0; f < 4; f++) {
+        const float first = s[f >> 1][2 * (f & 1)], second = s[f >> 1][2 * (f & 1) + 1];
+        ph[f] = pack_bf16(first, second);
+        pl[f] = pack_bf16(first - bf16_lo(ph[f]), second - bf16_hi(ph[f]));
+    }
 
-    // ---- O = P V, HALF head dims per pass; thread column g owns dims DPT*g .. DPT*g + DPT - 1 of the pass
-    float *out_row[2];
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        const int row = g + 8 * r;
-        out_row[r] = scratch + ((static_cast<size_t>(lane0 + row / GROUP) * q_heads + kv_head * GROUP + row % GROUP) * max_splits + split) * (HD + 2);
-    }
+    // ---- O = P V over the warp's tokens, HALF head dims per pass; thread column g owns dims DPT*g .. DPT*g+DPT-1
+    float *mine = partial_out + static_cast<size_t>(team_warp) * 16 * HD;
 #pragma unroll
     for (int pass = 0; pass < HD / HALF; pass++) {
         float o[DPT][4];
 #pragma unroll
         for (int i = 0; i < DPT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+        uint32_t v[4][DPT / 2];
 #pragma unroll
-        for (int ks = 0; ks < 4; ks++) {
-            uint32_t v[4][DPT / 2];  // tokens 16ks + 2j, +1, +8, +9
-#pragma unroll
-            for (int t = 0; t < 4; t++) {
-                const int token = 16 * ks + 2 * j + (t & 1) + 8 * (t >> 1);
-                if (token < count) {
-                    const uint16_t *vrow = kv.pool + row_offset(token, true) + pass * HALF + DPT * g;
-                    if (DPT == 8) {
-                        const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(vrow));
-                        v[t][0] = raw.x;
-                        v[t][1] = raw.y;
-                        v[t][DPT / 2 - 2] = raw.z;
-                        v[t][DPT / 2 - 1] = raw.w;
-                    } else {
-                        const uint2 raw = __ldcg(reinterpret_cast<const uint2 *>(vrow));
-                        v[t][0] = raw.x;
-                        v[t][DPT / 2 - 1] = raw.y;
-                    }
+        for (int t = 0; t < 4; t++) {
+            if (v_offset[t] != static_cast<size_t>(-1)) {
+                const uint16_t *vrow = kv.pool + v_offset[t] + pass * HALF + DPT * g;
+                if (DPT == 8) {
+                    const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(vrow));
+                    v[t][0] = raw.x;
+                    v[t][1] = raw.y;
+                    v[t][DPT / 2 - 2] = raw.z;
+                    v[t][DPT / 2 - 1] = raw.w;
                 } else {
-#pragma unroll
-                    for (int w = 0; w < DPT / 2; w++) v[t][w] = 0u;
+                    const uint2 raw = __ldcg(reinterpret_cast<const uint2 *>(vrow));
+                    v[t][0] = raw.x;
+                    v[t][DPT / 2 - 1] = raw.y;
                 }
-            }
+            } else {
 #pragma unroll
-            for (int i = 0; i < DPT; i++) {
-                const uint32_t selector = (i & 1) ? 0x7632u : 0x5410u;
-                const uint32_t b0 = __byte_perm(v[0][i >> 1], v[1][i >> 1], selector), b1 = __byte_perm(v[2][i >> 1], v[3][i >> 1], selector);
-                mma_bf16_16816(o[i], ph[ks][0], ph[ks][1], ph[ks][2], ph[ks][3], b0, b1);
-                mma_bf16_16816(o[i], pl[ks][0], pl[ks][1], pl[ks][2], pl[ks][3], b0, b1);
+                for (int w = 0; w < DPT / 2; w++) v[t][w] = 0u;
             }
         }
+#pragma unroll
+        for (int i = 0; i < DPT; i++) {
+            const uint32_t selector = (i & 1) ? 0x7632u : 0x5410u;
+            const uint32_t b0 = __byte_perm(v[0][i >> 1], v[1][i >> 1], selector), b1 = __byte_perm(v[2][i >> 1], v[3][i >> 1], selector);
+            mma_bf16_16816(o[i], ph[0], ph[1], ph[2], ph[3], b0, b1);
+            mma_bf16_16816(o[i], pl[0], pl[1], pl[2], pl[3], b0, b1);
+        }
+        // accumulator column 2j (+1) of output tile i is head dim DPT * (2j (+1)) + i of the pass
 #pragma unroll
         for (int r = 0; r < 2; r++)
-            if (tick_row[r] != 0xffffffffu) {
 #pragma unroll
-                for (int i = 0; i < DPT; i++) {
-                    out_row[r][pass * HALF + DPT * (2 * j) + i] = o[i][2 * r];
-                    out_row[r][pass * HALF + DPT * (2 * j + 1) + i] = o[i][2 * r + 1];
-                }
+            for (int i = 0; i < DPT; i++) {
+                mine[(g + 8 * r) * HD + pass * HALF + DPT * (2 * j) + i] = o[i][2 * r];
+                mine[(g + 8 * r) * HD + pass * HALF + DPT * (2 * j + 1) + i] = o[i][2 * r + 1];
             }
     }
-#pragma unroll
-    for (int r = 0; r < 2; r++)
-        if (tick_row[r] != 0xffffffffu && j == 0) {
-            out_row[r][HD] = row_max[r];
-            out_row[r][HD + 1] = row_sum[r];
+    team_barrier(barrier_id);
+    // ---- the four partial outputs add up; warp w writes head dims [w * HD / 4, (w + 1) * HD / 4) of every row
+    for (int index = lane; index < 16 * (HD / 4); index += 32) {
+        const int row = index / (HD / 4), d = team_warp * (HD / 4) + index % (HD / 4);
+        const int query_lane = lane0 + row / GROUP;  // rows beyond Q are padding
+        const bool valid = row < Q && query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream;
+        if (!valid) continue;
+        const float sum = partial_out[row * HD + d] + partial_out[(16 + row) * HD + d] + partial_out[(32 + row) * HD + d] +
+                          partial_out[(48 + row) * HD + d];
+        float *out = scratch + ((static_cast<size_t>(query_lane) * q_heads + kv_head * GROUP + row % GROUP) * max_splits + split) * (HD + 2);
+        out[d] = sum;
+        if (d == 0) {
+            out[HD] = fmaxf(fmaxf(fmaxf(team_max[row], team_max[16 + row]), fmaxf(team_max[32 + row], team_max[48 + row])), -3.4028234663852886e38f);
+            out[HD + 1] = team_sum[row] + team_sum[16 + row] + team_sum[32 + row] + team_sum[48 + row];
         }
+    }
+    team_barrier(barrier_id);  // the team's shared arrays are free for its next item
 }
 
 // Log-sum-exp merge of the split partials of one (lane, q head) pair by one warp: lane s of the warp weighs
@@ -650,12 +701,13 @@ struct StackArgs {
     StackBuffers buffers;
     LaneTable lanes_meta;
     int lanes, lanes_per_stream, split_tokens, max_splits;
+    int ring_units, l2_prefetch;
 };
 
 struct StackSmemLayout {
     size_t fragments, rows, correction, reduce, partial, ring, total;
 };
-__host__ __device__ inline StackSmemLayout stack_smem_layout(const StackShape &shape, int staged) {
+__host__ __device__ inline StackSmemLayout stack_smem_layout(const StackShape &shape, int staged, int ring_units) {
     const size_t q_width = static_cast<size_t>(shape.q_heads) * shape.head_width;
     size_t widest = shape.hidden > shape.ffn ? shape.hidden : shape.ffn;
     if (q_width > widest) widest = q_width;
@@ -669,27 +721,30 @@ __host__ __device__ inline StackSmemLayout stack_smem_layout(const StackShape &s
     layout.reduce = layout.correction + (widest >> 7) * 8 * sizeof(float);
     layout.partial = layout.reduce + static_cast<size_t>(2) * STACK_WARPS * 32 * 8 * sizeof(float);
     layout.ring = layout.partial + 8 * STACK_WARPS * sizeof(float);
-    layout.total = layout.ring + static_cast<size_t>(STACK_WARPS) * RING_UNITS * RING_UNIT_BYTES;
+    layout.total = layout.ring + static_cast<size_t>(STACK_WARPS) * ring_units * RING_UNIT_BYTES;
+    const size_t attention = 4 * (4 * 16 * static_cast<size_t>(shape.head_width) + 2 * 4 * 16) * sizeof(float);  // four attention teams
+    if (attention > layout.total) layout.total = attention;
     return layout;
 }
 
 // One 16x128 block of the ring against the staged activations: eight MMAs over bf16 (16 + q), the block's two
 // scales, and the 24 * sum(x) bias of the group.
-__device__ __forceinline__ void consume_unit(const uint8_t *unit, const uint4 (&b)[4], float2 bias, float (&acc)[4]) {
-    const int lane = threadIdx.x & 31;
-    const uint4 first = *reinterpret_cast<const uint4 *>(unit + lane * 16);
-    const uint4 second = *reinterpret_cast<const uint4 *>(unit + 512 + lane * 16);
-    const uint32_t scales = *reinterpret_cast<const uint32_t *>(unit + 1024 + lane * 4);
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+__device__ __forceinline__ void consume_unit(const uint8_t *mine, int scale_offset, const uint4 (&b)[4], float2 bias, float (&acc)[4]) {
+    const uint4 first = *reinterpret_cast<const uint4 *>(mine);
+    const uint4 second = *reinterpret_cast<const uint4 *>(mine + 512);
+    const uint32_t scales = *reinterpret_cast<const uint32_t *>(mine + scale_offset);
+    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, d[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // two accumulation chains of four MMAs
     const uint32_t wa[4] = {first.x, first.y, first.z, first.w};
     const uint32_t wb[4] = {second.x, second.y, second.z, second.w};
 #pragma unroll
     for (int word = 0; word < 4; word++) {
         mma_bf16_16816(c, biased_pair<0>(wa[word]), biased_pair<0>(wb[word]), biased_pair<1>(wa[word]), biased_pair<1>(wb[word]), b[word].x,
                        b[word].y);
-        mma_bf16_16816(c, biased_pair<2>(wa[word]), biased_pair<2>(wb[word]), biased_pair<3>(wa[word]), biased_pair<3>(wb[word]), b[word].z,
+        mma_bf16_16816(d, biased_pair<2>(wa[word]), biased_pair<2>(wb[word]), biased_pair<3>(wa[word]), biased_pair<3>(wb[word]), b[word].z,
                        b[word].w);
     }
+#pragma unroll
+    for (int i = 0; i < 4; i++) c[i] += d[i];
     const float sa = __uint_as_float(scales << 16), sb = __uint_as_float(scales & 0xffff0000u);
     acc[0] = fmaf(sa, c[0] - bias.x, acc[0]);
     acc[1] = fmaf(sa, c[1] - bias.y, acc[1]);
@@ -709,7 +764,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     const StackShape &shape = a.shape;
     const int lanes = a.lanes, staged = lanes < 8 ? lanes : 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
-    const StackSmemLayout layout = stack_smem_layout(shape, staged);
+    const StackSmemLayout layout = stack_smem_layout(shape, staged, a.ring_units);
     StackSmem sm;
     sm.fragments = reinterpret_cast<uint4 *>(smem_raw + layout.fragments);
     sm.rows = reinterpret_cast<uint16_t *>(smem_raw + layout.rows);
@@ -724,12 +779,22 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     int *error_flag = a.buffers.error_flag;
     int parity = 0, phase = 0;
     WeightStream stream;
-    stream.base = sm.ring + static_cast<size_t>(warp) * RING_UNITS * RING_UNIT_BYTES;
+    stream.ring = sm.ring + static_cast<size_t>(warp) * a.ring_units * RING_UNIT_BYTES + lane * 16;
+    stream.ring_shared = static_cast<uint32_t>(__cvta_generic_to_shared(stream.ring));
+    stream.scale_offset = 1024 + lane * 4 - lane * 16;
+    stream.units = a.ring_units;
     stream.head = stream.tail = 0;
+    stream.used = 0;
+    stream.rt = 1;
+    stream.per_tile = 0;
+    stream.gi = 0;
     stream.in_flight = 0;
     stream.has_following = false;
     stream.source_phase = -1;
     stream.remaining = 0;
+    stream.weights = nullptr;
+    stream.scales = nullptr;
+    stream.step = stream.tile_step = 0;
 
     auto stamp = [&](int layer, int index) {
         if (a.buffers.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -776,7 +841,8 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
             if (has_next) stream.following = walk_of(next_matrix, next_rt);
             stream_advance(stream);
             // the matrix after this one goes to L2 now (the gate/up pair already while attention runs)
-            if (step == 0) {
+            if (!a.l2_prefetch) {
+            } else if (step == 0) {
                 prefetch_matrix_l2(spec->o, 1);
                 prefetch_matrix_l2(spec->gate_up, 2);
             } else if (step == 2) {
@@ -818,18 +884,26 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                         payload = __ldcg(a.buffers.hidden + static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row);
                     }
                 }
+                const uint4 *xitem = xlane + warp * 4 * staged * 4;   // fragments of group `warp`, then 16 groups on per item
+                const float *bias_item = sm.correction + warp * 8 + 2 * j;
                 for (int gi = 0; gi < walk.per_tile; gi++) {
-                    const int group = warp + gi * STACK_WARPS;
                     uint4 b[4];
 #pragma unroll
-                    for (int word = 0; word < 4; word++) b[word] = xlane[(group * 4 + word) * staged * 4];
-                    const float2 bias = *reinterpret_cast<const float2 *>(sm.correction + group * 8 + 2 * j);
+                    for (int word = 0; word < 4; word++) b[word] = xitem[word * staged * 4];
+                    const float2 bias = *reinterpret_cast<const float2 *>(bias_item);
+                    xitem += STACK_WARPS * 4 * staged * 4;
+                    bias_item += STACK_WARPS * 8;
                     async_wait(stream.in_flight - 1);  // everything but the groups requested after this item's
                     stream.in_flight--;
-                    consume_unit(stream.base + (stream.head % RING_UNITS) * RING_UNIT_BYTES, b, bias, acc[0]);
-                    if (rt == 2) consume_unit(stream.base + ((stream.head + 1) % RING_UNITS) * RING_UNIT_BYTES, b, bias, acc[1]);
-                    stream.head += rt;
-                    stream_advance(stream);
+                    consume_unit(stream.ring + stream.head * RING_UNIT_BYTES, stream.scale_offset, b, bias, acc[0]);
+                    stream.head = stream.head + 1 == stream.units ? 0 : stream.head + 1;
+                    if (rt == 2) {
+                        consume_unit(stream.ring + stream.head * RING_UNIT_BYTES, stream.scale_offset, b, bias, acc[1]);
+                        stream.head = stream.head + 1 == stream.units ? 0 : stream.head + 1;
+                    }
+                    stream.used -= rt;
+                    if (stream.remaining > 0 && stream.rt == rt) stream_issue(stream);  // the freed units go straight back to work
+                    else stream_advance(stream);
                 }
                 float *mine = sm.reduce + static_cast<size_t>((parity * STACK_WARPS + warp) * 32) * 8;
 #pragma unroll
@@ -892,16 +966,20 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
             stamp(layer, 4 * step + 3);
 
             if (step == 0) {
-                // ---- attention: (kv head, split, stream x lane group) items, one warp each, spread over the SMs first
+                // ---- attention: (kv head, split, stream x lane group) items, one team of four warps each, spread
+                // over the SMs first; the teams' shared arrays reuse the staging area (nothing is staged right now)
                 const int streams = lanes / a.lanes_per_stream;
                 const int group_slots = streams * ((a.lanes_per_stream + QL - 1) / QL);
                 const int total = shape.kv_heads * a.max_splits * group_slots;
-                for (int item = blockIdx.x + gridDim.x * warp; item < total; item += gridDim.x * STACK_WARPS) {
+                const int team = warp >> 2;
+                float *team_smem = reinterpret_cast<float *>(smem_raw + static_cast<size_t>(team) * attention_team_bytes<HD>());
+                for (int item = blockIdx.x + gridDim.x * team; item < total; item += gridDim.x * 4) {
                     const int kv_head = item % shape.kv_heads, rest = item / shape.kv_heads;
-                    attention_warp_item<HD, GROUP, QL>(a.buffers.q, kv, a.lanes_meta, lanes, a.lanes_per_stream, shape.q_heads,
+                    attention_team_item<HD, GROUP, QL>(a.buffers.q, kv, a.lanes_meta, lanes, a.lanes_per_stream, shape.q_heads,
                                                        shape.attention_scale, a.max_splits, a.buffers.attention_scratch, kv_head,
-                                                       rest % a.max_splits, rest / a.max_splits);
+                                                       rest % a.max_splits, rest / a.max_splits, team_smem, warp & 3, 1 + team);
                 }
+                __syncthreads();  // the ring shares bytes with the teams' arrays
                 stamp(layer, 17);
                 // the o projection's first blocks stream while the grid meets and merges
                 stream_start(stream, walk_of(spec->o, 1), phase + 1);
@@ -957,12 +1035,18 @@ cudaError_t launch_instance(const StackArgs &args, size_t smem, cudaStream_t str
     return cudaLaunchKernelEx(&config, decode_stack_kernel<HD, GROUP>, args);
 }
 
-bool instance_smem(const StackShape &shape, int lanes, size_t *bytes) {
+bool instance_smem(const StackShape &shape, int lanes, size_t *bytes, int *ring_units) {
     const int group = shape.kv_heads > 0 ? shape.q_heads / shape.kv_heads : 0;
     const bool built = (shape.head_width == 128 && (group == 4 || group == 8)) || (shape.head_width == 64 && group == 4) ||
                        (shape.head_width == 32 && group == 2);
     if (!built) return false;
-    *bytes = stack_smem_layout(shape, lanes < 8 ? lanes : 8).total;
+    // the deepest ring the 227 KB of shared memory leave room for (an even count: a gate/up item takes two units)
+    int units = MAX_RING_UNITS;
+    static const char *forced = getenv("NERVE_B200_STACK_RING");
+    if (forced != nullptr && atoi(forced) >= 2 && atoi(forced) <= MAX_RING_UNITS) units = atoi(forced) & ~1;
+    while (units > 2 && stack_smem_layout(shape, lanes < 8 ? lanes : 8, units).total > 227 * 1024) units -= 2;
+    *bytes = stack_smem_layout(shape, lanes < 8 ? lanes : 8, units).total;
+    if (ring_units) *ring_units = units;
     return true;
 }
 
@@ -995,7 +1079,7 @@ bool decode_stack_supported(const StackShape &shape, int lanes, size_t *smem_byt
     size_t bytes = 0;
     if (lanes < 1 || lanes > 8) return false;
     if (shape.hidden > NORM_WORDS * 2 * STACK_THREADS || shape.hidden % 128 != 0 || shape.ffn % 128 != 0 || (shape.q_heads * shape.head_width) % 128 != 0) return false;
-    if (!instance_smem(shape, lanes, &bytes)) return false;
+    if (!instance_smem(shape, lanes, &bytes, nullptr)) return false;
     if (bytes > 227 * 1024) return false;
     if (smem_bytes) *smem_bytes = bytes;
     return true;
@@ -1017,6 +1101,9 @@ cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count
     args.lanes_per_stream = lanes_per_stream;
     args.split_tokens = split_tokens;
     args.max_splits = max_splits;
+    instance_smem(shape, lanes, &smem, &args.ring_units);
+    static const char *prefetch = getenv("NERVE_B200_STACK_L2_PREFETCH");
+    args.l2_prefetch = (prefetch != nullptr && prefetch[0] == '0') ? 0 : 1;
     const int group = shape.q_heads / shape.kv_heads;
     if (shape.head_width == 128 && group == 4) return launch_instance<128, 4>(args, smem, stream);
     if (shape.head_width == 128 && group == 8) return launch_instance<128, 8>(args, smem, stream);
