@@ -364,64 +364,75 @@ __device__ __forceinline__ void stage_rows(const StackSmem &sm, const uint16_t *
     __syncthreads();
 }
 
-// rms_norm_bf16.comp.template:49-72 of every staged lane into sm.rows (each CTA repeats it: 8 KB per lane from
-// L2).  Four lanes are loaded at once and kept in registers; width <= NORM_WORDS * 2 * STACK_THREADS.
-constexpr int NORM_WORDS = 4;
-__device__ __forceinline__ void normalise_rows(const StackSmem &sm, const uint16_t *x, const uint16_t *weight, int width, int staged,
-                                               float eps, float offset) {
-    const int words = width >> 1, warp = threadIdx.x >> 5;
-    const uint32_t *weight_words = reinterpret_cast<const uint32_t *>(weight);
-    uint32_t *row_words = reinterpret_cast<uint32_t *>(sm.rows);
-    uint32_t scale_words[NORM_WORDS];
+// rms_norm_bf16.comp.template:49-72 of every staged lane, straight into fragment order (each CTA repeats it:
+// 8 KB per lane from L2).  A thread owns chunk t (and t + 512 when CHUNKS = 2) of each lane, four lanes at a time:
+// one pass over registers for the sums of squares, one block-wide exchange, then normalise, round and permute.
+template <int CHUNKS>  // chunks per thread and lane: width <= CHUNKS * 8 * STACK_THREADS
+__device__ __forceinline__ void stage_normalised(const StackSmem &sm, const uint16_t *x, const uint16_t *weight, int width, int staged,
+                                                 float eps, float offset) {
+    const int per_lane = width >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint4 *source = reinterpret_cast<const uint4 *>(x);
+    uint4 scale_words[CHUNKS];
 #pragma unroll
-    for (int i = 0; i < NORM_WORDS; i++) {
-        const int word = threadIdx.x + i * STACK_THREADS;
-        scale_words[i] = word < words ? __ldg(weight_words + word) : 0u;
+    for (int c = 0; c < CHUNKS; c++) {
+        const int chunk = threadIdx.x + c * STACK_THREADS;
+        scale_words[c] = chunk < per_lane ? __ldg(reinterpret_cast<const uint4 *>(weight) + chunk) : make_uint4(0, 0, 0, 0);
     }
     for (int m0 = 0; m0 < staged; m0 += 4) {
-        uint32_t held[4][NORM_WORDS];
+        uint4 raw[4][CHUNKS];
 #pragma unroll
         for (int mm = 0; mm < 4; mm++)
 #pragma unroll
-            for (int i = 0; i < NORM_WORDS; i++) {
-                const int word = threadIdx.x + i * STACK_THREADS;
-                held[mm][i] = (m0 + mm < staged && word < words)
-                                  ? __ldcg(reinterpret_cast<const uint32_t *>(x) + static_cast<size_t>(m0 + mm) * words + word)
-                                  : 0u;
+            for (int c = 0; c < CHUNKS; c++) {
+                const int chunk = threadIdx.x + c * STACK_THREADS;
+                raw[mm][c] = (m0 + mm < staged && chunk < per_lane) ? __ldcg(source + static_cast<size_t>(m0 + mm) * per_lane + chunk)
+                                                                    : make_uint4(0, 0, 0, 0);
             }
 #pragma unroll
         for (int mm = 0; mm < 4; mm++) {
             float sum = 0.0f;
 #pragma unroll
-            for (int i = 0; i < NORM_WORDS; i++) {
-                const float lo = bf16_lo(held[mm][i]), hi = bf16_hi(held[mm][i]);
-                sum = fmaf(lo, lo, sum);
-                sum = fmaf(hi, hi, sum);
+            for (int c = 0; c < CHUNKS; c++) {
+                const uint32_t words[4] = {raw[mm][c].x, raw[mm][c].y, raw[mm][c].z, raw[mm][c].w};
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const float lo = bf16_lo(words[w]), hi = bf16_hi(words[w]);
+                    sum = fmaf(lo, lo, sum);
+                    sum = fmaf(hi, hi, sum);
+                }
             }
             sum = warp_sum(sum);
-            if ((threadIdx.x & 31) == 0) sm.partial[(m0 + mm) * STACK_WARPS + warp] = sum;
+            if (lane == 0) sm.partial[mm * STACK_WARPS + warp] = sum;
         }
         __syncthreads();
+        // every warp adds up the 16 partials of the four lanes: lanes 8k .. 8k+7 of the warp take lane m0 + k
+        float total = sm.partial[(lane >> 3) * STACK_WARPS + (lane & 7) * 2] + sm.partial[(lane >> 3) * STACK_WARPS + (lane & 7) * 2 + 1];
+        total += __shfl_xor_sync(0xffffffffu, total, 1);
+        total += __shfl_xor_sync(0xffffffffu, total, 2);
+        total += __shfl_xor_sync(0xffffffffu, total, 4);
+        // IEEE sqrt and divide, as a CPU evaluates 1/sqrt(v)
+        const float my_inverse = 1.0f / sqrtf(total * (1.0f / static_cast<float>(width)) + eps);
 #pragma unroll
         for (int mm = 0; mm < 4; mm++) {
-            if (m0 + mm < staged) {
-                float total = 0.0f;
+            const float inv_rms = __shfl_sync(0xffffffffu, my_inverse, mm * 8);
 #pragma unroll
-                for (int w = 0; w < STACK_WARPS; w++) total += sm.partial[(m0 + mm) * STACK_WARPS + w];
-                // IEEE sqrt and divide, as a CPU evaluates 1/sqrt(v)
-                const float inv_rms = 1.0f / sqrtf(total * (1.0f / static_cast<float>(width)) + eps);
+            for (int c = 0; c < CHUNKS; c++) {
+                const int chunk = threadIdx.x + c * STACK_THREADS;
+                if (c * STACK_THREADS < per_lane && m0 + mm < staged) {  // uniform over the CTA
+                    const uint32_t in[4] = {raw[mm][c].x, raw[mm][c].y, raw[mm][c].z, raw[mm][c].w};
+                    const uint32_t sc[4] = {scale_words[c].x, scale_words[c].y, scale_words[c].z, scale_words[c].w};
+                    uint32_t out[4];
 #pragma unroll
-                for (int i = 0; i < NORM_WORDS; i++) {
-                    const int word = threadIdx.x + i * STACK_THREADS;
-                    if (word < words) {
-                        const float lo = bf16_lo(held[mm][i]) * inv_rms * (bf16_lo(scale_words[i]) + offset);
-                        const float hi = bf16_hi(held[mm][i]) * inv_rms * (bf16_hi(scale_words[i]) + offset);
-                        row_words[static_cast<size_t>(m0 + mm) * words + word] = pack_bf16(lo, hi);
-                    }
+                    for (int w = 0; w < 4; w++)
+                        out[w] = pack_bf16(bf16_lo(in[w]) * inv_rms * (bf16_lo(sc[w]) + offset), bf16_hi(in[w]) * inv_rms * (bf16_hi(sc[w]) + offset));
+                    stage_chunk(sm, make_uint4(out[0], out[1], out[2], out[3]), chunk < per_lane, m0 + mm, chunk < per_lane ? chunk : 0, staged);
                 }
             }
         }
+        if (m0 + 4 < staged) __syncthreads();  // sm.partial is rewritten for the next four lanes
     }
+    for (int c = threadIdx.x; c < (width >> 7) * 8; c += STACK_THREADS)
+        if ((c & 7) >= staged) sm.correction[c] = 0.0f;
     __syncthreads();
 }
 
@@ -803,10 +814,29 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
             a.buffers.timing[layer * 32 + index] = now;
         }
     };
-    // epilogue thread t < 128: high = t & 1, lane m = (t >> 1) & 7, row = (t >> 4) + 8 * high: the rotary partner
-    // rows r and r + 8 of a lane sit in neighbouring threads
+    // Epilogue roles: thread t < 128 finishes output (high = t & 1, lane m = (t >> 1) & 7, row = (t >> 4) + 8 * high)
+    // of a tile's 16 rows x 8 lanes, so the rotary partner rows r and r + 8 of a lane sit in neighbouring threads.
+    // Only four warps do this; the other twelve go straight on to the next tile's blocks.
     const int epilogue_m = (threadIdx.x >> 1) & 7, epilogue_row = (threadIdx.x >> 4) + 8 * (threadIdx.x & 1);
     const bool epilogue_active = threadIdx.x < 128 && epilogue_m < lanes;
+    // per-lane constants of the epilogue: position, rotary table row, and the lane's KV row inside a page (the
+    // block table is shared by all layers)
+    uint32_t lane_position = 0;
+    const uint32_t *rope_row = shape.rope_table;
+    size_t kv_token_base = 0;
+    bool kv_writable = false;
+    if (threadIdx.x < 128 && epilogue_m < lanes) {
+        lane_position = a.lanes_meta.position[epilogue_m];
+        rope_row = shape.rope_table + static_cast<size_t>(lane_position % shape.rope_positions) * (HD >> 1);
+        const KvLayer &kv0 = a.layers[0].kv;
+        const int slot = a.lanes_meta.slot[epilogue_m];
+        if (slot >= 0 && kv0.capacity != 0) {
+            const uint32_t ring = lane_position % kv0.capacity;
+            const int physical = kv0.block_table[static_cast<size_t>(slot) * kv0.pages_per_slot + ring / kv0.page_tokens];
+            kv_token_base = static_cast<size_t>(physical) * 2 * kv0.kv_heads * kv0.page_tokens * HD + static_cast<size_t>(ring % kv0.page_tokens) * HD;
+            kv_writable = true;
+        }
+    }
     const int ge = g < staged ? g : 0;  // lanes beyond the batch recompute lane 0; their results are dropped
     const uint4 *xlane = sm.fragments + ge * 4 + j;
 
@@ -854,10 +884,12 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
 
             // ---- activations of this step into fragment order
             if (step == 0 || step == 2) {
-                normalise_rows(sm, a.buffers.hidden, step == 0 ? spec->input_norm : spec->post_norm, shape.hidden, staged, shape.eps,
-                               shape.norm_offset);
+                const uint16_t *norm_weight = step == 0 ? spec->input_norm : spec->post_norm;
+                if (shape.hidden <= 8 * STACK_THREADS)
+                    stage_normalised<1>(sm, a.buffers.hidden, norm_weight, shape.hidden, staged, shape.eps, shape.norm_offset);
+                else
+                    stage_normalised<2>(sm, a.buffers.hidden, norm_weight, shape.hidden, staged, shape.eps, shape.norm_offset);
                 if (step == 2) stamp(layer, 16);
-                stage_rows(sm, nullptr, false, shape.hidden, staged);
             } else if (step == 1) {
                 stage_rows(sm, a.buffers.attention_out, true, q_width, staged);
             } else {
@@ -877,8 +909,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                     if (step == 0) {
                         if (tile < q_tiles + k_tiles) {
                             const int local = tile < q_tiles ? tile : tile - q_tiles;
-                            const int d = 8 * (local % (HD >> 4)) + (epilogue_row & 7);
-                            payload = __ldg(shape.rope_table + static_cast<size_t>(a.lanes_meta.position[epilogue_m] % shape.rope_positions) * (HD >> 1) + d);
+                            payload = __ldg(rope_row + 8 * (local % (HD >> 4)) + (epilogue_row & 7));
                         }
                     } else if (step != 2) {
                         payload = __ldcg(a.buffers.hidden + static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row);
@@ -929,8 +960,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                         const float mine_value = round_bf16(first);
                         const float partner = __shfl_xor_sync(0xffffffffu, mine_value, 1);  // the row 8 further (or 8 back)
                         if (epilogue_active) {
-                            const uint32_t position = a.lanes_meta.position[epilogue_m];
-                            const int slot = a.lanes_meta.slot[epilogue_m];
+                            const size_t kv_half = static_cast<size_t>(kv.kv_heads) * kv.page_tokens * HD;
                             if (tile < q_tiles + k_tiles) {
                                 const bool is_q = tile < q_tiles, high = epilogue_row >= 8;
                                 const int local = is_q ? tile : tile - q_tiles;
@@ -940,10 +970,10 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                                 const float other = high ? partner : -partner;
                                 const uint16_t value = static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(mine_value * cosine) + round_bf16(other * sine)));
                                 if (is_q) a.buffers.q[(static_cast<size_t>(epilogue_m) * shape.q_heads + head) * HD + d] = value;
-                                else if (slot >= 0 && kv.capacity != 0) kv.pool[kv_token_offset(kv, slot, position % kv.capacity, head, false) + d] = value;
-                            } else if (slot >= 0 && kv.capacity != 0) {
+                                else if (kv_writable) kv.pool[kv_token_base + static_cast<size_t>(head) * kv.page_tokens * HD + d] = value;
+                            } else if (kv_writable) {
                                 const int index = (tile - q_tiles - k_tiles) * 16 + epilogue_row;
-                                kv.pool[kv_token_offset(kv, slot, position % kv.capacity, index / HD, true) + index % HD] =
+                                kv.pool[kv_token_base + kv_half + static_cast<size_t>(index / HD) * kv.page_tokens * HD + index % HD] =
                                     static_cast<uint16_t>(f32_to_bf16_bits(first));
                             }
                         }
@@ -1078,7 +1108,7 @@ cudaError_t launch_int4_tile_major(const RelayoutSegment *segments, int count, b
 bool decode_stack_supported(const StackShape &shape, int lanes, size_t *smem_bytes) {
     size_t bytes = 0;
     if (lanes < 1 || lanes > 8) return false;
-    if (shape.hidden > NORM_WORDS * 2 * STACK_THREADS || shape.hidden % 128 != 0 || shape.ffn % 128 != 0 || (shape.q_heads * shape.head_width) % 128 != 0) return false;
+    if (shape.hidden > 2 * 8 * STACK_THREADS || shape.hidden % 128 != 0 || shape.ffn % 128 != 0 || (shape.q_heads * shape.head_width) % 128 != 0) return false;
     if (!instance_smem(shape, lanes, &bytes, nullptr)) return false;
     if (bytes > 227 * 1024) return false;
     if (smem_bytes) *smem_bytes = bytes;
@@ -1103,7 +1133,7 @@ cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count
     args.max_splits = max_splits;
     instance_smem(shape, lanes, &smem, &args.ring_units);
     static const char *prefetch = getenv("NERVE_B200_STACK_L2_PREFETCH");
-    args.l2_prefetch = (prefetch != nullptr && prefetch[0] == '0') ? 0 : 1;
+    args.l2_prefetch = (prefetch != nullptr && prefetch[0] == '1') ? 1 : 0;  // off: the tile loops are not HBM-bound (yet)
     const int group = shape.q_heads / shape.kv_heads;
     if (shape.head_width == 128 && group == 4) return launch_instance<128, 4>(args, smem, stream);
     if (shape.head_width == 128 && group == 8) return launch_instance<128, 8>(args, smem, stream);
