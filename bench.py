@@ -37,6 +37,7 @@ DRAFTS = 3
 METRIC = "accepted tokens/s (8B INT4, MTP k=3)"
 UNIT = "tokens/s"
 INT4_TRAFFIC_RATIO = 1.008
+STACK_TRAFFIC_RATIO = 1.06
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -310,6 +311,8 @@ def main():
     profiled, _ = timed_cycles(engine, 0, prompt, budget, warmup, min(steps, 16), None, barrier)
     engine.set_profiling(False)
 
+    stack_kernel = bool(info["target_decode_stack"]) and os.environ.get("NERVE_B200_DECODE_STACK", "1") != "0"
+
     def reduce_max(value):
         if world == 1:
             return value
@@ -351,12 +354,14 @@ def main():
         },
         "verify_step": {"ms": verify_ms, "algorithmic_bytes": verify_bytes, "gbs": verify_gbs,
                         "frac_of_nominal_8tbs": verify_gbs / NOMINAL_HBM_GBS, "frac_of_measured_copy": verify_gbs / peak},
-        # traffic: DRAM bytes per launch = algorithmic bytes x 1.008, the ratio ncu measured for this kernel
-        # (dram__bytes_read.sum + dram__bytes_write.sum over packed weights + scales, gate/up pair capture in
-        # profiles/linear_int4_mma_kernel_gate_up_pair_14336x4096.md; traffic grows in proportion to the rows)
-        "roofline": {"kernel": "linear_int4_mma_kernel", "bound": "hbm", "achieved": int4_gbs, "peak": peak, "peak_kind": peak_kind,
+        # The dominant kernel is the persistent decode stack kernel (all layers of a stack in one launch; its
+        # algorithmic bytes are the tile-major INT4 weights + scales + norm weights of the stack), or - with it
+        # switched off - the per-matrix INT4 kernel.  traffic: DRAM bytes per launch = algorithmic bytes x the
+        # ratio ncu measured (dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes; captures of a
+        # one-layer stack launch and of the gate/up pair in profiles/; traffic grows in proportion to layers and rows).
+        "roofline": {"kernel": "decode_stack_kernel" if stack_kernel else "linear_int4_mma_kernel", "bound": "hbm", "achieved": int4_gbs, "peak": peak, "peak_kind": peak_kind,
                      "unit": "GB/s", "frac": int4_gbs / peak,
-                     "traffic": INT4_TRAFFIC_RATIO * profiled.int4_bytes / max(1, profiled.int4_launches),
+                     "traffic": (STACK_TRAFFIC_RATIO if stack_kernel else INT4_TRAFFIC_RATIO) * profiled.int4_bytes / max(1, profiled.int4_launches),
                      "launches_timed": profiled.int4_launches,
                      "bytes_per_launch": profiled.int4_bytes / max(1, profiled.int4_launches)},
         "e2e": {"value": e2e_natural, "unit": UNIT,

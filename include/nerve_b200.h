@@ -151,8 +151,8 @@ int32_t nerve_b200_engine_set_cycle_logging(nerve_b200_engine *engine, int32_t e
 /* Records CUDA events around every INT4 linear launch (adds launch overhead; for roofline measurement only). */
 int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabled);
 /* Batches of at most 8 lanes of a dense INT4 g128 layer stack (the verify batch, draft and single-tick steps) run
- * as one persistent kernel per stack; 0 selects the kernel-per-operator path for them as well.  Default: the
- * value of NERVE_B200_DECODE_STACK in the environment (1 = on), else off.  No counterpart in the reference: its Vulkan
+ * as one persistent kernel per stack; 0 selects the kernel-per-operator path for them as well.  Default on
+ * (NERVE_B200_DECODE_STACK=0 in the environment turns it off).  No counterpart in the reference: its Vulkan
  * runtime always records one dispatch per kernel (placed_stream_processor/temporal_prompt.rs:480-657). */
 int32_t nerve_b200_engine_set_decode_stack(nerve_b200_engine *engine, int32_t enabled);
 /* Profiling aid (no reference counterpart): with profiling on, CTA 0 of the persistent kernel stamps the GPU's

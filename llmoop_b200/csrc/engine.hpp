@@ -187,8 +187,8 @@ public:
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
     void set_cycle_logging(bool enabled) { log_cycles_ = enabled; }
     void set_use_graphs(bool enabled) { use_graphs_ = enabled; }
-    // The persistent decode stack kernel serves batches of at most 8 lanes of dense INT4 stacks; off (the
-    // default until it is the faster of the two) = the kernel-per-operator path for everything.
+    // The persistent decode stack kernel serves batches of at most 8 lanes of dense INT4 stacks; off = the
+    // kernel-per-operator path for everything.
     void set_decode_stack(bool enabled) { stack_enabled_ = enabled; }
     // Profiling aid: nanosecond stamps CTA 0 took at the phase boundaries of the target stack's last launch
     // ([layers][32]: layer start, then after each staging step, matrix or attention step and grid barrier, in
@@ -281,7 +281,7 @@ private:
     DeviceBuffer kernel_error_;             // device word set by pipelined kernels whose bounded waits expired
     // persistent decode stack workspaces ([8 lanes][width]) and its two barrier words
     DeviceBuffer stack_q_, stack_attention_out_, stack_activation_, stack_barrier_, stack_timing_;
-    bool stack_enabled_ = false;
+    bool stack_enabled_ = true;
     bool run_stack(const StackPlan &stack, int lanes, void *hidden);
     DeviceBuffer cycle_state_;              // device-side per-batch cycle arrays (see engine.cu)
     // Pinned staging arena for host->device uploads: every upload between two host synchronisations gets its
