@@ -88,7 +88,7 @@ int32_t nerve_b200_engine_create(nerve_b200_package *package, nerve_b200_engine 
 int32_t nerve_b200_engine_destroy(nerve_b200_engine *engine);
 
 typedef struct nerve_b200_sampler_config {
-    int32_t method; /* 0 = greedy */
+    int32_t method; /* 0 = greedy, 1 = temperature_top_k_top_p (seeded; top_k 1..64, temperature > 0) */
     float temperature, top_p, min_p;
     int32_t top_k;
 } nerve_b200_sampler_config;
@@ -199,6 +199,17 @@ int32_t nerve_b200_op_linear_fp8(const void *x_device, const void *w_device, con
 int32_t nerve_b200_op_greedy(const void *logits_device, void *records_device, void *scratch_device, int32_t lanes,
                              int32_t vocab, void *stream);
 uint64_t nerve_b200_op_greedy_scratch_bytes(int32_t lanes);
+/* Seeded temperature / top-k / top-p / min-p sampler (sampler.rs:748-873;
+ * temperature_top_k_candidates_f32.comp.template:48-127 + temperature_top_k_top_p_sampler_f32.comp.template:56-216):
+ * exact top-k (ties -> lower id, NaNs skipped), weights exp(l/T - max/T), min-p cut, top-p nucleus, uniform
+ * u = (hash_u32(seed ^ tick) >> 8) * 2^-24 with the shader's hash, first index whose cumulative weight exceeds
+ * u * nucleus weight.  records u32[lanes][4] = {token, logit bits, 1, 0}; lane l draws for stream tick
+ * ticks_device[l] (0 when NULL).  scratch_device: nerve_b200_op_sample_scratch_bytes(lanes) bytes;
+ * params_device: 32 bytes the call fills with the parameters.  top_k <= 64. */
+int32_t nerve_b200_op_sample_top_k_top_p(const void *logits_device, void *records_device, void *scratch_device, int32_t lanes,
+                                         int32_t vocab, int32_t top_k, float temperature, float top_p, float min_p, uint32_t seed,
+                                         const uint32_t *ticks_device, void *params_device, void *stream);
+uint64_t nerve_b200_op_sample_scratch_bytes(int32_t lanes);
 /* The same arg-max for callers that must not allocate device memory and have none to lend: the partial winners
  * of the two-stage reduction live in a 32 KB device array built into the library, so neither this call nor the
  * caller ever allocates or frees anything.  No counterpart in the reference (its sampler dispatch always binds a

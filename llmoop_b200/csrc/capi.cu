@@ -405,6 +405,31 @@ int32_t nerve_b200_op_greedy(const void *logits, void *records, void *scratch, i
 
 uint64_t nerve_b200_op_greedy_scratch_bytes(int32_t lanes) { return argmax_scratch_bytes(lanes); }
 
+int32_t nerve_b200_op_sample_top_k_top_p(const void *logits, void *records, void *scratch, int32_t lanes, int32_t vocab, int32_t top_k,
+                                         float temperature, float top_p, float min_p, uint32_t seed, const uint32_t *ticks_device,
+                                         void *params_device, void *stream) {
+    return guarded([&] {
+        require(logits && records && scratch && params_device, "nerve_b200_op_sample_top_k_top_p: null pointer");
+        require(top_k >= 1 && top_k <= SAMPLER_MAX_TOP_K, "top_k must be between 1 and 64");
+        require(temperature > 0.0f && top_p > 0.0f && top_p <= 1.0f && min_p >= 0.0f && min_p <= 1.0f, "sampler parameters out of range");
+        SamplerParams params{};
+        params.method = 1;
+        params.top_k = static_cast<uint32_t>(top_k);
+        params.seed = seed;
+        params.temperature = temperature;
+        params.top_p = top_p;
+        params.min_p = min_p;
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        cudaError_t status = cudaMemcpyAsync(params_device, &params, sizeof(params), cudaMemcpyHostToDevice, st);
+        if (status == cudaSuccess)
+            status = launch_sample(static_cast<const float *>(logits), static_cast<uint32_t *>(records), lanes, vocab,
+                                   static_cast<const SamplerParams *>(params_device), nullptr, ticks_device, scratch, st);
+        if (status != cudaSuccess) throw std::runtime_error(std::string("nerve_b200_op_sample_top_k_top_p: ") + cudaGetErrorString(status));
+    });
+}
+
+uint64_t nerve_b200_op_sample_scratch_bytes(int32_t lanes) { return sampler_scratch_bytes(lanes); }
+
 int32_t nerve_b200_op_greedy_static(const void *logits, void *records, int32_t lanes, int32_t vocab, void *stream) {
     if (lanes < 0 || vocab <= 0 || logits == nullptr || records == nullptr) {
         last_error = "nerve_b200_op_greedy_static: null pointer or non-positive size";

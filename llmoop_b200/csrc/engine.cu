@@ -355,6 +355,7 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     logits_ = device_alloc(lanes * static_cast<size_t>(plan.vocab) * sizeof(float));
     records_ = device_alloc(lanes * 4 * sizeof(uint32_t));
     argmax_scratch_ = device_alloc(argmax_scratch_bytes(options.max_lanes));
+    sampler_table_ = device_alloc(static_cast<size_t>(options.max_streams) * sizeof(SamplerParams));
     lane_tokens_ = device_alloc(lanes * sizeof(uint32_t));
     lane_positions_ = device_alloc(lanes * sizeof(uint32_t));
     lane_slots_ = device_alloc(lanes * sizeof(int32_t));
@@ -411,7 +412,7 @@ Engine::~Engine() {
     set_int4_error_flag(nullptr);
     for (auto &entry : signals_) cudaFree(entry.second.ptr);
     for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
-                                 &records_, &argmax_scratch_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
+                                 &records_, &argmax_scratch_, &sampler_scratch_, &sampler_table_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
                                  &cycle_state_, &kernel_error_, &stack_q_, &stack_attention_out_, &stack_activation_, &stack_barrier_, &stack_timing_})
         cudaFree(buffer->ptr);
     cudaFreeHost(staging_);
@@ -445,7 +446,14 @@ uint64_t Engine::stream_tick(int64_t id) const { return stream(id).next_tick; }
 void Engine::add_stream(int64_t id, uint32_t seed, int speculative_draft_tokens, const SamplerConfig &sampler) {
     if (streams_.count(id)) fail("stream " + std::to_string(id) + " already exists");
     if (free_slots_.empty()) fail("no free stream slot (max_streams = " + std::to_string(model_->options().max_streams) + ")");
-    if (sampler.method != 0) fail("only the greedy sampler is mounted in this build");
+    if (sampler.method != 0 && sampler.method != 1) fail("sampler method must be 0 (greedy) or 1 (temperature_top_k_top_p)");
+    if (sampler.method == 1) {
+        if (!(sampler.temperature > 0.0f)) fail("sampler temperature must be positive");
+        if (sampler.top_k < 1 || sampler.top_k > SAMPLER_MAX_TOP_K)
+            fail("sampler top_k must be between 1 and " + std::to_string(SAMPLER_MAX_TOP_K));
+        if (!(sampler.top_p > 0.0f) || sampler.top_p > 1.0f || sampler.min_p < 0.0f || sampler.min_p > 1.0f)
+            fail("sampler top_p must be in (0, 1] and min_p in [0, 1]");
+    }
     if (speculative_draft_tokens < 0) fail("speculative_draft_tokens must be >= 0");
     if (speculative_draft_tokens > 0 && !model_->plan().has_draft)
         fail("resident model package has no mounted speculative decoder");
@@ -456,6 +464,21 @@ void Engine::add_stream(int64_t id, uint32_t seed, int speculative_draft_tokens,
     s.seed = seed;
     s.k = speculative_draft_tokens;
     s.sampler = sampler;
+    {
+        SamplerParams params{};
+        params.method = static_cast<uint32_t>(sampler.method);
+        params.top_k = static_cast<uint32_t>(sampler.method == 1 ? sampler.top_k : 1);
+        params.seed = seed;
+        params.temperature = sampler.temperature;
+        params.top_p = sampler.top_p;
+        params.min_p = sampler.min_p;
+        upload(static_cast<uint8_t *>(sampler_table_.ptr) + static_cast<size_t>(s.slot) * sizeof(SamplerParams), &params, sizeof(params),
+               "sampler parameters upload");
+        if (sampler.method != 0) {
+            stochastic_streams_++;
+            if (sampler_scratch_.ptr == nullptr) sampler_scratch_ = device_alloc(sampler_scratch_bytes(model_->options().max_lanes), false);
+        }
+    }
     s.pages.assign(model_->pages_per_stream(), -1);
     const size_t frame = static_cast<size_t>(model_->plan().hidden) * 2;
     cuda_check(cudaMemsetAsync(static_cast<uint8_t *>(pending_hidden_.ptr) + s.slot * frame, 0, frame, cuda_stream_), "pending reset");
@@ -470,9 +493,23 @@ void Engine::release_pages(Stream &s) {
     s.block_table_dirty = true;
 }
 
+void Engine::sample_lanes(const float *logits, uint32_t *records, int lanes, const int32_t *slots, const uint32_t *ticks, const char *what) {
+    const int vocab = static_cast<int>(model_->plan().vocab);
+    if (stochastic_streams_ == 0) {
+        check(launch_argmax(logits, records, lanes, vocab, argmax_scratch_.ptr, cuda_stream_), what);
+        counters_.kernel_launches++;
+        return;
+    }
+    check(launch_sample(logits, records, lanes, vocab, static_cast<const SamplerParams *>(sampler_table_.ptr), slots, ticks,
+                        sampler_scratch_.ptr, cuda_stream_),
+          what);
+    counters_.kernel_launches++;
+}
+
 void Engine::remove_stream(int64_t id) {
     Stream &s = stream(id);
     release_pages(s);
+    if (s.sampler.method != 0) stochastic_streams_--;
     free_slots_.push_back(s.slot);
     streams_.erase(id);
 }
@@ -984,9 +1021,8 @@ void Engine::target_forward(int lanes, bool want_logits) {
                                  static_cast<int>(plan.vocab), static_cast<int>(plan.hidden), EPILOGUE_F32_SCALED, plan.output.logits_scale,
                                  cuda_stream_),
               "output projection");
-        check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, static_cast<int>(plan.vocab),
-                            argmax_scratch_.ptr, cuda_stream_),
-              "greedy sampler");
+        sample_lanes(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, current_lanes_.slot,
+                     current_lanes_.position, "sampler");
     }
 }
 
@@ -1020,9 +1056,8 @@ void Engine::draft_forward(int lanes, const uint16_t *hidden_in, bool want_logit
                              static_cast<int>(plan.vocab), static_cast<int>(plan.hidden), EPILOGUE_F32_SCALED, plan.draft_output.logits_scale,
                              cuda_stream_),
           "draft output projection");
-    check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, static_cast<int>(plan.vocab),
-                        argmax_scratch_.ptr, cuda_stream_),
-          "draft greedy sampler");
+    sample_lanes(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, current_lanes_.slot,
+                 current_lanes_.position, "draft sampler");
 }
 
 // ---------------------------------------------------------------------------- prefill (temporal_prompt.rs:298-478)
@@ -1058,9 +1093,8 @@ void Engine::run_prefill_chunk(Stream &s, const uint32_t *tokens, int count, boo
                                  static_cast<int>(plan.vocab), static_cast<int>(plan.hidden), EPILOGUE_F32_SCALED, plan.output.logits_scale,
                                  cuda_stream_),
               "prefill output projection");
-        check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), 1, static_cast<int>(plan.vocab),
-                            argmax_scratch_.ptr, cuda_stream_),
-              "prefill sampler");
+        sample_lanes(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), 1, current_lanes_.slot + (count - 1),
+                     current_lanes_.position + (count - 1), "prefill sampler");
         cuda_check(cudaMemcpyAsync(host_records_, records_.ptr, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, cuda_stream_), "record readback");
         synchronize("prefill synchronize");
         counters_.d2h_bytes += 16;
@@ -1196,7 +1230,7 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
 
     uint64_t t0 = now_ns();
     // ---- draft loop: `drafts` serial steps over `streams` lanes
-    run_phase({0, streams, drafts, splits}, [&] {
+    run_phase({0, streams, drafts, splits, stochastic_streams_ != 0 ? 1 : 0, stack_enabled_ ? 1 : 0}, [&] {
         for (int j = 0; j < drafts; j++) {
             current_lanes_ = LaneTable{draft_positions + static_cast<size_t>(j) * streams, stream_slots};
             current_tokens_ = draft_tokens;
@@ -1217,7 +1251,7 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
     cuda_check(cudaEventRecord(event_a_, cuda_stream_), "event record");
 
     // ---- verify: all candidates of all streams in one batch of lanes
-    run_phase({1, streams, drafts, splits}, [&] {
+    run_phase({1, streams, drafts, splits, stochastic_streams_ != 0 ? 1 : 0, stack_enabled_ ? 1 : 0}, [&] {
         current_lanes_ = LaneTable{verify_positions, verify_slots};
         current_tokens_ = verify_tokens;
         current_width_ = width;
@@ -1229,7 +1263,7 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
     // with the target's hidden states.  Lanes beyond the committed prefix write slots that the next cycle
     // overwrites before reading (like the draft loop's own tentative writes in the reference).
     const size_t row_words = 4 + 2 * width;
-    run_phase({2, streams, drafts, splits}, [&] {
+    run_phase({2, streams, drafts, splits, stochastic_streams_ != 0 ? 1 : 0, stack_enabled_ ? 1 : 0}, [&] {
         current_lanes_ = LaneTable{verify_positions, verify_slots};
         current_tokens_ = verify_tokens;
         current_width_ = width;

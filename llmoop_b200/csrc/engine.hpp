@@ -275,6 +275,10 @@ private:
     DeviceBuffer logits_;                   // f32 [max_lanes][vocab]
     DeviceBuffer records_;                  // u32 [max_lanes][4]
     DeviceBuffer argmax_scratch_;
+    DeviceBuffer sampler_scratch_, sampler_table_;   // stochastic sampler: candidate lists, per-slot parameters
+    int stochastic_streams_ = 0;                     // streams whose sampler is not greedy
+    // arg-max for all-greedy engines, else the seeded sampler (greedy lanes take its first entry)
+    void sample_lanes(const float *logits, uint32_t *records, int lanes, const int32_t *slots, const uint32_t *ticks, const char *what);
     DeviceBuffer lane_tokens_, lane_positions_, lane_slots_;
     DeviceBuffer pending_hidden_;           // [max_streams][hidden]
     DeviceBuffer attention_scratch_;

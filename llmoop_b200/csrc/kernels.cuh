@@ -197,4 +197,18 @@ cudaError_t launch_argmax(const float *logits, uint32_t *records, int lanes, int
 int argmax_static_max_lanes();
 cudaError_t launch_argmax_static(const float *logits, uint32_t *records, int lanes, int vocab, cudaStream_t stream);
 
+// ---- seeded temperature / top-k / top-p / min-p sampler (kernels_sampler.cu) ----
+constexpr int SAMPLER_MAX_TOP_K = 64;
+struct SamplerParams {   // one per stream slot
+    uint32_t method;     // 0 greedy (arg-max, record flags 0), 1 temperature_top_k_top_p
+    uint32_t top_k;      // 1..SAMPLER_MAX_TOP_K
+    uint32_t seed;
+    float temperature, top_p, min_p;
+};
+size_t sampler_scratch_bytes(int lanes);
+// One record {token, logit bits, sampled flag, 0} per lane; lane l uses table[slots[l]] (slot 0 when slots is
+// NULL) and the uniform of stream tick ticks[l].
+cudaError_t launch_sample(const float *logits, uint32_t *records, int lanes, int vocab, const SamplerParams *table, const int32_t *slots,
+                          const uint32_t *ticks, void *scratch, cudaStream_t stream);
+
 }  // namespace nerve

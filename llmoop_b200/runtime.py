@@ -71,7 +71,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair", "nerve_b200_set_int4_kernel",
     "nerve_b200_op_linear_bf16", "nerve_b200_op_rms_norm", "nerve_b200_op_linear_fp8",
-    "nerve_b200_op_greedy", "nerve_b200_op_greedy_scratch_bytes", "nerve_b200_op_greedy_static", "nerve_b200_verify_prefix",
+    "nerve_b200_op_greedy", "nerve_b200_op_greedy_scratch_bytes", "nerve_b200_op_greedy_static", "nerve_b200_op_sample_top_k_top_p", "nerve_b200_op_sample_scratch_bytes", "nerve_b200_verify_prefix",
     "nerve_b200_stream_control_bytes", "nerve_b200_state_page_table_bytes",
 )
 
@@ -90,6 +90,7 @@ def library() -> ctypes.CDLL:
             if name != "nerve_b200_last_error":
                 getattr(lib, name).restype = ctypes.c_int32
         lib.nerve_b200_op_greedy_scratch_bytes.restype = ctypes.c_uint64
+        lib.nerve_b200_op_sample_scratch_bytes.restype = ctypes.c_uint64
         _library = lib
     return _library
 

@@ -64,6 +64,11 @@ def lib():
         _lib.orc_f32_to_e4m3.argtypes = [ctypes.c_float]
         _lib.orc_top2_gap.restype = ctypes.c_float
         _lib.orc_greedy.restype = ctypes.c_uint32
+        _lib.orc_hash_u32.restype = ctypes.c_uint32
+        _lib.orc_hash_u32.argtypes = [ctypes.c_uint32]
+        _lib.orc_sample_top_k_top_p.restype = ctypes.c_uint32
+        _lib.orc_sample_top_k_top_p.argtypes = [_f32p, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float,
+                                                ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, _u32p]
     return _lib
 
 
@@ -423,6 +428,24 @@ class Oracle:
             tokens[lane] = lib().orc_greedy(_p(row, _f32p), row.shape[0], None)
         return tokens
 
+    # sampler.rs:748-873: `sampler` = None (greedy) or dict(top_k, temperature, top_p, min_p, seed); draft and
+    # target draw with the same hash(seed ^ tick) at the same tick
+    sampler = None
+
+    def sample(self, logits, first_tick):
+        """One token per logits row; row i belongs to stream tick first_tick + i."""
+        if self.sampler is None:
+            return self.greedy(logits)
+        cfg = self.sampler
+        tokens = np.empty(logits.shape[0], dtype=np.uint32)
+        for lane in range(logits.shape[0]):
+            row = np.ascontiguousarray(logits[lane], dtype=np.float32)
+            tick = int(first_tick) + lane
+            tokens[lane] = lib().orc_sample_top_k_top_p(_p(row, _f32p), row.shape[0], int(cfg["top_k"]), float(cfg["temperature"]),
+                                                        float(cfg["top_p"]), float(cfg["min_p"]), int(cfg["seed"]) & 0xffffffff,
+                                                        tick & 0xffffffff, (tick >> 32) & 0xffffffff, None)
+        return tokens
+
     @staticmethod
     def top2_gap(logits_row):
         row = np.ascontiguousarray(logits_row, dtype=np.float32)
@@ -496,7 +519,7 @@ class Oracle:
                 stream.pending_hidden = normalized[-1:].copy()
             if is_last and sample_last:
                 last_logits = self.project(normalized[-1:])
-                sampled = int(self.greedy(last_logits)[0])
+                sampled = int(self.sample(last_logits, start + len(piece) - 1)[0])
             stream.next_tick += len(piece)
         return sampled, last_logits
 
@@ -508,7 +531,7 @@ class Oracle:
             self.draft_forward(stream, [token], stream.pending_hidden, tick, want_logits=False)
             stream.pending_hidden = normalized.copy()
         stream.next_tick += 1
-        return (int(self.greedy(logits)[0]), logits) if emit else (None, None)
+        return (int(self.sample(logits, tick)[0]), logits) if emit else (None, None)
 
     # -- one speculative cycle: feedback_generation.rs:66-194 ---------------------------------------------
     def speculative_cycle(self, stream, initial_token, draft_count, stop_tokens=(), forced_drafts=None):
@@ -518,7 +541,7 @@ class Oracle:
         draft_logits = []
         for j in range(draft_count):
             normalized, logits = self.draft_forward(stream, [token], hidden, start + j, want_logits=True)
-            token = int(self.greedy(logits)[0])
+            token = int(self.sample(logits, start + j)[0])
             draft_logits.append(logits[0])
             if forced_drafts is not None:
                 token = int(forced_drafts[j])
@@ -526,7 +549,7 @@ class Oracle:
             hidden = normalized
         inputs = [initial_token] + drafts
         normalized, logits = self.target_forward(stream, inputs, start, want_logits=True)
-        targets = [int(t) for t in self.greedy(logits)]
+        targets = [int(t) for t in self.sample(logits, start)]
         accepted, committed, emitted = verify_prefix(drafts, targets, stop_tokens)
         # draft catch-up: state steps for the committed inputs with hidden = pending / target frame i-1
         hidden = np.concatenate([stream.pending_hidden, normalized[:committed - 1]], axis=0)

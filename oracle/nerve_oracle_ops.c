@@ -389,6 +389,89 @@ ORC_API uint32_t orc_greedy(const float *logits, int vocab, uint32_t *record) {
     return best;
 }
 
+/* temperature_top_k_candidates_f32.comp.template:48-127 + temperature_top_k_top_p_sampler_f32.comp.template:
+ * 56-72,100-216: exact top-k of the logits (NaNs skipped; order: larger logit first, ties -> lower id), then
+ *   max_scaled = top[0]/T;  min_logit = min_p > 0 ? top[0] + T*log(min_p) : lowest float
+ *   total   = sum of exp(l/T - max_scaled) over the list until an entry falls below min_logit
+ *   nucleus = the shortest prefix whose weight reaches top_p * total
+ *   u       = (hash_u32(seed ^ tick_lo ^ tick_hi*0x9e3779b9) >> 8) * 2^-24;  target = u * nucleus weight
+ *   pick the first index whose cumulative weight exceeds target (else the last of the nucleus)
+ * record = {token, logit bits, 1, 0}.  All sums in f32 and in list order, as the single shader thread does. */
+ORC_API uint32_t orc_hash_u32(uint32_t value) {
+    value ^= value >> 16;
+    value *= 0x7feb352du;
+    value ^= value >> 15;
+    value *= 0x846ca68bu;
+    value ^= value >> 16;
+    return value;
+}
+
+ORC_API uint32_t orc_sample_top_k_top_p(const float *logits, int vocab, int top_k, float temperature, float top_p,
+                                        float min_p, uint32_t seed, uint32_t tick_lo, uint32_t tick_hi, uint32_t *record) {
+    const float lowest = -3.4028234663852886e38f;
+    if (top_k < 1) top_k = 1;
+    float *top_logit = (float *)malloc(sizeof(float) * (size_t)top_k);
+    uint32_t *top_token = (uint32_t *)malloc(sizeof(uint32_t) * (size_t)top_k);
+    float previous_logit = 0.0f;
+    uint32_t previous_token = 0;
+    for (int rank = 0; rank < top_k; rank++) {
+        float best = lowest;
+        uint32_t best_token = 0xffffffffu;
+        for (int token = 0; token < vocab; token++) {
+            float candidate = logits[token];
+            if (isnan(candidate)) continue;
+            if (rank != 0 && !(candidate < previous_logit || (candidate == previous_logit && (uint32_t)token > previous_token)))
+                continue;
+            if (candidate > best || (candidate == best && (uint32_t)token < best_token)) {
+                best = candidate;
+                best_token = (uint32_t)token;
+            }
+        }
+        top_logit[rank] = best;
+        top_token[rank] = best_token;
+        previous_logit = best;
+        previous_token = best_token;
+    }
+    const float max_scaled = top_logit[0] / temperature;
+    const float min_logit = min_p > 0.0f ? top_logit[0] + temperature * logf(min_p) : lowest;
+    float total = 0.0f;
+    for (int i = 0; i < top_k; i++) {
+        if (top_logit[i] < min_logit) break;
+        total += expf(top_logit[i] / temperature - max_scaled);
+    }
+    const float threshold = top_p * total;
+    float nucleus = 0.0f;
+    int count = 0;
+    for (int i = 0; i < top_k; i++) {
+        if (top_logit[i] < min_logit) break;
+        nucleus += expf(top_logit[i] / temperature - max_scaled);
+        count = i + 1;
+        if (nucleus >= threshold) break;
+    }
+    const uint32_t bits = orc_hash_u32(seed ^ tick_lo ^ (tick_hi * 0x9e3779b9u));
+    const float target = (float)(bits >> 8) * (1.0f / 16777216.0f) * nucleus;
+    float cumulative = 0.0f;
+    int selected = count - 1;
+    for (int i = 0; i < count; i++) {
+        cumulative += expf(top_logit[i] / temperature - max_scaled);
+        if (target < cumulative) {
+            selected = i;
+            break;
+        }
+    }
+    if (selected < 0) selected = 0;
+    const uint32_t token = top_token[selected];
+    if (record) {
+        record[0] = token;
+        memcpy(&record[1], &top_logit[selected], 4);
+        record[2] = 1;
+        record[3] = 0;
+    }
+    free(top_logit);
+    free(top_token);
+    return token;
+}
+
 /* Top-2 gap of a logits row (used by the parity rule "divergence allowed only
  * where the oracle's top-2 gap is below 1e-3"). */
 ORC_API float orc_top2_gap(const float *logits, int vocab) {

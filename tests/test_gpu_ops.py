@@ -208,3 +208,44 @@ def test_linear_fp8_matches_oracle(lanes):
     got = dy.cpu().numpy().view(np.uint16).reshape(lanes, n)
     exact, worst = _ulp_report(got, want)
     assert worst <= 1.01 and exact > 0.97, (exact, worst)
+
+
+@pytest.mark.parametrize("lanes,vocab,top_k", [(1, 64, 4), (5, 4099, 40), (3, 128256, 64)])
+def test_seeded_sampler_matches_oracle(lanes, vocab, top_k):
+    """nerve_b200_op_sample_top_k_top_p against the oracle (and, for the first case, the reference's known-answer
+    vector: tokens 7, 8, 19, 51 at logit 2.0 in a vocabulary of 64, seed 0x5eed1234)."""
+    import torch
+
+    import llmoop_b200 as nb
+    from oracle import nerve_oracle as orc
+
+    lib = nb.library()
+    rng = np.random.default_rng(vocab + top_k)
+    if vocab == 64:
+        logits = np.full((lanes, vocab), -100.0, dtype=np.float32)
+        logits[:, [7, 8, 19, 51]] = 2.0
+        temperature, top_p, min_p, seed = 1.0, 1.0, 0.0, 0x5EED1234
+    else:
+        logits = (rng.standard_normal((lanes, vocab)) * 2.0).astype(np.float32)
+        logits[0, 5] = np.nan
+        logits[-1, 100] = logits[-1, 17] = logits[-1].max() + 1.0  # a tie at the top
+        temperature, top_p, min_p, seed = 0.8, 0.9, 0.02, 1234567
+    d_logits = torch.from_numpy(logits).cuda()
+    scratch = torch.zeros(int(lib.nerve_b200_op_sample_scratch_bytes(lanes)), dtype=torch.uint8, device="cuda")
+    params = torch.zeros(32, dtype=torch.uint8, device="cuda")
+    for first_tick in (0, 9, 1000):
+        ticks = np.arange(first_tick, first_tick + lanes, dtype=np.uint32)
+        d_ticks = torch.from_numpy(ticks.view(np.int32)).cuda()
+        records = torch.zeros(lanes, 4, dtype=torch.int32, device="cuda")
+        status = lib.nerve_b200_op_sample_top_k_top_p(_ptr(d_logits), _ptr(records), _ptr(scratch), lanes, vocab, top_k,
+                                                      ctypes.c_float(temperature), ctypes.c_float(top_p), ctypes.c_float(min_p),
+                                                      ctypes.c_uint32(seed), _ptr(d_ticks), _ptr(params), None)
+        assert status == 0, lib.nerve_b200_last_error()
+        torch.cuda.synchronize()
+        got = records.cpu().numpy().view(np.uint32)
+        for lane in range(lanes):
+            want = np.zeros(4, dtype=np.uint32)
+            row = np.ascontiguousarray(logits[lane])
+            orc.lib().orc_sample_top_k_top_p(orc._p(row, orc._f32p), vocab, top_k, temperature, top_p, min_p, seed, int(ticks[lane]), 0,
+                                             orc._p(want, orc._u32p))
+            assert list(got[lane]) == list(want), (lane, first_tick, got[lane], want)

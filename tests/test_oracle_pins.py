@@ -174,3 +174,55 @@ def test_shader_float_round_trips_through_nine_significant_digits():
     assert orc.shader_float(0.3535533905932738) == np.float32(0.353553391)
     assert orc.shader_float(1e-5) == np.float32(1e-05)
     assert orc.attention_tile_tokens(8) == 112 and orc.attention_tile_tokens(128) == 56
+
+
+# ---- seeded top-k / top-p sampler ---------------------------------------------------------------------------
+def test_seeded_sampler_matches_the_reference_known_answer():
+    """component_transducer_sampler_tests.rs:409-533: vocabulary 64, logits -100 except tokens 7, 8, 19, 51 at 2.0,
+    temperature 1, top_k 4, top_p 1, min_p 0, seed 0x5eed1234; at stream tick t the sampler must pick
+    TOP_TOKENS[((hash(seed ^ t) >> 8) * 4) >> 24] with logit bits of 2.0 and record flags 1, and all four tokens
+    must appear over ticks 0..15."""
+    top_tokens = [7, 8, 19, 51]
+    logits = np.full(64, -100.0, dtype=np.float32)
+    logits[top_tokens] = 2.0
+    seen = set()
+    for tick in range(16):
+        bits = orc.lib().orc_hash_u32(ctypes.c_uint32(0x5EED1234 ^ tick))
+        expected = top_tokens[((bits >> 8) * 4) >> 24]
+        record = np.zeros(4, dtype=np.uint32)
+        token = orc.lib().orc_sample_top_k_top_p(orc._p(logits, orc._f32p), 64, 4, 1.0, 1.0, 0.0, 0x5EED1234, tick, 0,
+                                                 orc._p(record, orc._u32p))
+        assert token == expected
+        assert list(record) == [expected, int(np.float32(2.0).view(np.uint32)), 1, 0]
+        seen.add(token)
+    assert seen == set(top_tokens)
+
+
+def test_sampler_hash_is_the_shader_hash():
+    """temperature_top_k_top_p_sampler_f32.comp.template:56-63, evaluated by hand for two inputs."""
+    def reference(value):
+        value ^= value >> 16
+        value = (value * 0x7FEB352D) & 0xFFFFFFFF
+        value ^= value >> 15
+        value = (value * 0x846CA68B) & 0xFFFFFFFF
+        value ^= value >> 16
+        return value
+
+    for value in (0, 1, 0x5EED1234, 0xFFFFFFFF, 123456789):
+        assert orc.lib().orc_hash_u32(ctypes.c_uint32(value)) == reference(value)
+
+
+def test_sampler_min_p_top_p_and_nan_rules():
+    """min-p cuts entries below top + T*log(min_p); top-p keeps the shortest prefix reaching p of the weight; NaN
+    logits never enter the list; ties go to the lower token id."""
+    logits = np.array([1.0, np.nan, 3.0, 3.0, 0.5, -2.0, 2.9, np.nan], dtype=np.float32)
+    picks = set()
+    for tick in range(64):
+        picks.add(int(orc.lib().orc_sample_top_k_top_p(orc._p(logits, orc._f32p), 8, 8, 1.0, 1.0, 0.0, 7, tick, 0, None)))
+    assert picks <= {0, 2, 3, 4, 5, 6} and {2, 3, 6} <= picks          # NaN tokens 1 and 7 never drawn
+    # min_p 0.5: only logits >= 3 + log(0.5) = 2.307 survive -> tokens 2, 3, 6
+    picks = {int(orc.lib().orc_sample_top_k_top_p(orc._p(logits, orc._f32p), 8, 8, 1.0, 1.0, 0.5, 7, tick, 0, None)) for tick in range(64)}
+    assert picks == {2, 3, 6}
+    # top_p tiny: the nucleus is the first entry alone, and the tie between tokens 2 and 3 goes to token 2
+    picks = {int(orc.lib().orc_sample_top_k_top_p(orc._p(logits, orc._f32p), 8, 8, 1.0, 0.01, 0.0, 7, tick, 0, None)) for tick in range(64)}
+    assert picks == {2}
