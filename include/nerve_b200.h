@@ -150,6 +150,21 @@ int32_t nerve_b200_engine_set_prefill_chunk(nerve_b200_engine *engine, int32_t t
 int32_t nerve_b200_engine_set_cycle_logging(nerve_b200_engine *engine, int32_t enabled);
 /* Records CUDA events around every INT4 linear launch (adds launch overhead; for roofline measurement only). */
 int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabled);
+/* Tensor parallelism (the reference's sharding plan: vulkan_distributed/planning.rs:180-528).  A package mounted
+ * with tp_size > 1 holds rank tp_rank's shard of every dense layer: q/k/v and gate/up by output rows (whole
+ * heads), o and down by input columns (whole groups of 128); norms, embedding and output projection are
+ * replicated.  Every rank runs the same streams with the same calls; after each o and down projection the ranks'
+ * f32 partial sums meet in one NCCL all-reduce, then the bf16 rounding and the residual add follow.
+ * nerve_b200_tp_unique_id: rank 0 obtains the 128-byte NCCL id and hands it to the other ranks (any transport);
+ * nerve_b200_engine_init_tp: every rank joins the group before its first run.  nccl_library_path: libnccl.so.2,
+ * loaded at run time (the library does not link NCCL). */
+int32_t nerve_b200_tp_unique_id(const char *nccl_library_path, uint8_t *out_128_bytes);
+/* The shard rule of the mount (pure host function): rank's [begin, begin + count) of `total` rows or columns kept
+ * in whole units (head width for q/k/v rows, 16 for gate/up rows, 128 for o/down columns); an error when total is
+ * not a multiple of unit x size. */
+int32_t nerve_b200_tp_shard_range(int64_t total, int64_t unit, int32_t rank, int32_t size, int64_t *out_begin, int64_t *out_count);
+int32_t nerve_b200_engine_init_tp(nerve_b200_engine *engine, const char *nccl_library_path, int32_t rank, int32_t size,
+                                  const uint8_t *unique_id_128_bytes);
 /* Batches of at most 8 lanes of a dense INT4 g128 layer stack (the verify batch, draft and single-tick steps) run
  * as one persistent kernel per stack; 0 selects the kernel-per-operator path for them as well.  Default on
  * (NERVE_B200_DECODE_STACK=0 in the environment turns it off).  No counterpart in the reference: its Vulkan

@@ -11,6 +11,9 @@ from .runtime import (  # noqa: F401
     Package,
     RunReport,
     library,
+    nccl_library_path,
+    tensor_parallel_unique_id,
+    tp_shard_range,
     validate_package,
     verify_prefix,
 )

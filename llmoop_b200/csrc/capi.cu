@@ -67,7 +67,7 @@ int32_t nerve_b200_package_mount(const char *path, const nerve_b200_mount_option
         mount.tp_rank = options->tp_rank;
         mount.tp_size = options->tp_size > 0 ? options->tp_size : 1;
         mount.extra_pages = options->extra_pages;
-        require(mount.tp_size == 1, "tensor-parallel mounts are not available in this build");
+        require(mount.tp_rank >= 0 && mount.tp_rank < mount.tp_size, "tp_rank must be in [0, tp_size)");
         auto package = new nerve_b200_package();
         try {
             package->model = MountedModel::mount(path, mount);
@@ -217,6 +217,28 @@ int32_t nerve_b200_engine_enqueue(nerve_b200_engine *engine, int64_t stream_id, 
 int32_t nerve_b200_engine_run_until_idle(nerve_b200_engine *engine, nerve_b200_output_callback on_output, void *user,
                                          nerve_b200_run_report *out) {
     return nerve_b200_engine_run(engine, 0, on_output, user, out);
+}
+
+int32_t nerve_b200_tp_shard_range(int64_t total, int64_t unit, int32_t rank, int32_t size, int64_t *out_begin, int64_t *out_count) {
+    return guarded([&] {
+        require(out_begin && out_count, "null output");
+        tp_shard_range(total, unit, rank, size, *out_begin, *out_count);
+    });
+}
+
+int32_t nerve_b200_tp_unique_id(const char *nccl_library_path, uint8_t *out_128_bytes) {
+    return guarded([&] {
+        require(nccl_library_path && out_128_bytes, "null argument");
+        Engine::tensor_parallel_unique_id(nccl_library_path, out_128_bytes);
+    });
+}
+
+int32_t nerve_b200_engine_init_tp(nerve_b200_engine *engine, const char *nccl_library_path, int32_t rank, int32_t size,
+                                  const uint8_t *unique_id_128_bytes) {
+    return guarded([&] {
+        require(engine && nccl_library_path && unique_id_128_bytes, "null argument");
+        engine->engine->init_tensor_parallel(nccl_library_path, rank, size, unique_id_128_bytes);
+    });
 }
 
 int32_t nerve_b200_engine_set_decode_stack(nerve_b200_engine *engine, int32_t enabled) {

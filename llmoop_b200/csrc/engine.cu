@@ -1,4 +1,7 @@
 #include "engine.hpp"
+#include "state_abi.hpp"
+
+#include <dlfcn.h>
 
 #include <algorithm>
 #include <chrono>
@@ -55,6 +58,98 @@ void collect_component_tensors(const ComponentPlan &plan, std::set<std::string> 
 
 }  // namespace
 
+// ---- tensor parallelism (vulkan_distributed/planning.rs:180-528 is the reference's only sharding; here the
+// Megatron split of a dense layer: q/k/v and gate/up by output rows (whole heads), o and down by input columns
+// (whole groups of 128), one all-reduce of f32 partial sums after o and after down; norms, embedding and the
+// output projection are replicated).
+void shard_linear_rows(WeightRef &w, int rank, int size, int64_t unit, const std::string &what) {
+    w.full_n = w.n;
+    w.full_k = w.k;
+    try {
+        tp_shard_range(w.full_n, unit, rank, size, w.row_begin, w.n);
+    } catch (const std::exception &error) {
+        fail("tensor-parallel mount: rows of the " + what + ": " + error.what());
+    }
+}
+void shard_linear_columns(WeightRef &w, int rank, int size, const std::string &what) {
+    w.full_n = w.n;
+    w.full_k = w.k;
+    try {
+        tp_shard_range(w.full_k, 128, rank, size, w.col_begin, w.k);
+    } catch (const std::exception &error) {
+        fail("tensor-parallel mount: columns of the " + what + ": " + error.what());
+    }
+}
+
+void shard_component(ComponentPlan &layer, int rank, int size) {
+    static const OpKind expected[15] = {OpKind::RmsNorm, OpKind::Linear, OpKind::Linear, OpKind::Linear, OpKind::Rope, OpKind::Rope,
+                                        OpKind::AppendAttention, OpKind::Linear, OpKind::ResidualAdd, OpKind::RmsNorm, OpKind::Linear,
+                                        OpKind::Linear, OpKind::SiluMultiply, OpKind::Linear, OpKind::ResidualAdd};
+    if (layer.ops.size() != 15) fail("tensor-parallel mount: component " + layer.id + " is not a dense layer of 15 kernels");
+    for (int i = 0; i < 15; i++)
+        if (layer.ops[i].kind != expected[i] || (layer.ops[i].kind == OpKind::Linear && layer.ops[i].weights.size() != 1))
+            fail("tensor-parallel mount: component " + layer.id + " is not a dense layer of 15 kernels");
+    for (int i : {1, 2, 3, 7, 10, 11, 13}) {
+        TensorStorage storage = layer.ops[i].weights[0].storage;
+        if (storage != TensorStorage::INT4_CT && storage != TensorStorage::BF16)
+            fail("tensor-parallel mount: only INT4 and BF16 linears are sharded");
+    }
+    OpSpec &q = layer.ops[1], &k = layer.ops[2], &v = layer.ops[3], &rope_q = layer.ops[4], &rope_k = layer.ops[5], &attention = layer.ops[6],
+           &o = layer.ops[7], &gate = layer.ops[10], &up = layer.ops[11], &silu = layer.ops[12], &down = layer.ops[13];
+    const int head = attention.head_width;
+    if (attention.q_heads % size != 0 || attention.kv_heads % size != 0)
+        fail("tensor-parallel mount: " + std::to_string(attention.q_heads) + " query / " + std::to_string(attention.kv_heads) +
+             " key-value heads do not divide over " + std::to_string(size) + " ranks");
+    shard_linear_rows(q.weights[0], rank, size, head, "q projection");
+    shard_linear_rows(k.weights[0], rank, size, head, "k projection");
+    shard_linear_rows(v.weights[0], rank, size, head, "v projection");
+    shard_linear_columns(o.weights[0], rank, size, "o projection");
+    shard_linear_rows(gate.weights[0], rank, size, 16, "gate projection");
+    shard_linear_rows(up.weights[0], rank, size, 16, "up projection");
+    shard_linear_columns(down.weights[0], rank, size, "down projection");
+    o.tp_partial = true;
+    down.tp_partial = true;
+    attention.q_heads /= size;
+    attention.kv_heads /= size;
+    for (OpSpec *rope : {&rope_q, &rope_k})
+        for (RopeAttrs &attrs : rope->rope) attrs.heads /= size;
+    layer.q_heads = attention.q_heads;
+    layer.kv_heads = attention.kv_heads;
+    auto set_width = [&](const std::string &signal, int64_t width) { layer.signals[signal].width = width; };
+    set_width(q.outputs[0], q.weights[0].n);
+    set_width(k.outputs[0], k.weights[0].n);
+    set_width(v.outputs[0], v.weights[0].n);
+    set_width(rope_q.outputs[0], q.weights[0].n);
+    set_width(rope_k.outputs[0], k.weights[0].n);
+    set_width(attention.outputs[0], q.weights[0].n);
+    set_width(gate.outputs[0], gate.weights[0].n);
+    set_width(up.outputs[0], up.weights[0].n);
+    set_width(silu.outputs[0], gate.weights[0].n);
+}
+
+ModelPlan shard_plan(const ModelPlan &full, int rank, int size) {
+    ModelPlan plan = full;
+    if (size <= 1) return plan;
+    if (rank < 0 || rank >= size) fail("tensor-parallel rank " + std::to_string(rank) + " outside 0.." + std::to_string(size - 1));
+    for (ComponentPlan &layer : plan.layers) shard_component(layer, rank, size);
+    for (ComponentPlan &layer : plan.draft_layers) shard_component(layer, rank, size);
+    return plan;
+}
+
+// Rows [row_begin, row_begin + n) and columns [col_begin, col_begin + k) of a row-major [full_n][full_k] weight whose
+// rows take `row_bytes` bytes; `per_column_num / per_column_den` bytes per column (INT4: 1/2, bf16: 2, a group
+// scale: 2/128).
+std::vector<uint8_t> slice_tensor(const std::vector<uint8_t> &data, const WeightRef &w, int64_t num, int64_t den) {
+    if (w.full_n == 0) return data;
+    const size_t full_row = static_cast<size_t>(w.full_k) * num / den, row = static_cast<size_t>(w.k) * num / den,
+                 offset = static_cast<size_t>(w.col_begin) * num / den;
+    if (data.size() != full_row * static_cast<size_t>(w.full_n)) fail("tensor-parallel mount: tensor " + w.tensor + " has an unexpected size");
+    std::vector<uint8_t> out(row * static_cast<size_t>(w.n));
+    for (int64_t r = 0; r < w.n; r++)
+        std::memcpy(out.data() + static_cast<size_t>(r) * row, data.data() + static_cast<size_t>(w.row_begin + r) * full_row + offset, row);
+    return out;
+}
+
 // ============================================================================ MountedModel
 
 std::shared_ptr<MountedModel> MountedModel::mount(const std::string &path, const MountOptions &options) {
@@ -70,7 +165,8 @@ std::shared_ptr<MountedModel> MountedModel::mount(const std::string &path, const
     model->options_ = options;
     VerifyLevel level = options.verify_level >= 2 ? VerifyLevel::All : (options.verify_level == 1 ? VerifyLevel::Used : VerifyLevel::None);
     model->package_ = HostPackage::open(path, level);
-    const ModelPlan &plan = model->package_->plan();
+    model->plan_ = shard_plan(model->package_->plan(), options.tp_rank, options.tp_size);
+    const ModelPlan &plan = model->plan_;
     if (plan.max_context > 0 && options.capacity_tokens > plan.max_context)
         fail("requested context " + std::to_string(options.capacity_tokens) + " exceeds the package's max_context_activations " +
              std::to_string(plan.max_context));
@@ -121,7 +217,23 @@ const void *MountedModel::tensor(const std::string &name) const {
 }
 
 void MountedModel::upload_tensors() {
-    const ModelPlan &plan = package_->plan();
+    const ModelPlan &plan = plan_;
+    // which linears hold only a tensor-parallel shard of their weight (and scales)
+    std::map<std::string, std::pair<WeightRef, std::pair<int64_t, int64_t>>> shards;  // tensor -> (ref, bytes per column as a fraction)
+    auto note = [&](const ComponentPlan &component) {
+        for (const OpSpec &op : component.ops)
+            for (const WeightRef &w : op.weights)
+                if (w.full_n != 0) {
+                    if (w.storage == TensorStorage::INT4_CT) {
+                        shards[w.tensor] = {w, {1, 2}};
+                        shards[w.scale] = {w, {2, 128}};
+                    } else {
+                        shards[w.tensor] = {w, {2, 1}};
+                    }
+                }
+    };
+    for (const ComponentPlan &layer : plan.layers) note(layer);
+    for (const ComponentPlan &layer : plan.draft_layers) note(layer);
     std::set<std::string> target, draft, shared;
     for (const ComponentPlan &layer : plan.layers) collect_component_tensors(layer, target);
     target.insert(plan.output.norm_tensor);
@@ -139,17 +251,19 @@ void MountedModel::upload_tensors() {
     const bool verify = options_.verify_level >= 1;
     for (const std::string &name : all) {
         std::vector<uint8_t> data = package_->read_tensor(name, verify);
+        auto shard = shards.find(name);
+        if (shard != shards.end()) data = slice_tensor(data, shard->second.first, shard->second.second.first, shard->second.second.second);
         DeviceBuffer buffer = device_alloc(data.size(), false);
         cuda_check(cudaMemcpy(buffer.ptr, data.data(), data.size(), cudaMemcpyHostToDevice), "weight upload");
         tensors_[name] = buffer;
         weight_bytes_ += data.size();
     }
-    for (const std::string &name : target) target_step_bytes_ += package_->tensor(name).byte_count();
-    for (const std::string &name : draft) draft_step_bytes_ += package_->tensor(name).byte_count();
+    for (const std::string &name : target) target_step_bytes_ += tensors_.at(name).bytes;
+    for (const std::string &name : draft) draft_step_bytes_ += tensors_.at(name).bytes;
 }
 
 void MountedModel::build_rope_tables() {
-    const ModelPlan &plan = package_->plan();
+    const ModelPlan &plan = plan_;
     rope_positions_ = static_cast<uint32_t>(std::max<int64_t>(plan.max_context, options_.capacity_tokens)) + 64;
     auto add = [&](const ComponentPlan &component) {
         for (const OpSpec &op : component.ops)
@@ -321,6 +435,36 @@ namespace {
 constexpr int MAX_STOP_TOKENS = 8;
 }
 
+// ---- NCCL through its C ABI, loaded at run time (ncclUniqueId is 128 bytes; ncclFloat32 = 7, ncclSum = 0)
+namespace {
+struct NcclApi {
+    int (*get_unique_id)(void *id);
+    int (*comm_init_rank)(void **comm, int size, const void *id_by_value_128, int rank);
+    int (*all_reduce)(const void *send, void *recv, size_t count, int datatype, int op, void *comm, cudaStream_t stream);
+    int (*comm_destroy)(void *comm);
+    const char *(*get_error_string)(int result);
+};
+struct NcclId {
+    char bytes[128];
+};
+void *open_nccl(const std::string &library, NcclApi &api) {
+    void *handle = dlopen(library.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (handle == nullptr) fail("cannot load NCCL from " + library + ": " + dlerror());
+    auto need = [&](const char *name) {
+        void *symbol = dlsym(handle, name);
+        if (symbol == nullptr) fail(std::string("NCCL library lacks ") + name);
+        return symbol;
+    };
+    api.get_unique_id = reinterpret_cast<int (*)(void *)>(need("ncclGetUniqueId"));
+    api.comm_init_rank = reinterpret_cast<int (*)(void **, int, const void *, int)>(need("ncclCommInitRank"));
+    api.all_reduce = reinterpret_cast<int (*)(const void *, void *, size_t, int, int, void *, cudaStream_t)>(need("ncclAllReduce"));
+    api.comm_destroy = reinterpret_cast<int (*)(void *)>(need("ncclCommDestroy"));
+    api.get_error_string = reinterpret_cast<const char *(*)(int)>(need("ncclGetErrorString"));
+    return handle;
+}
+NcclApi g_nccl{};
+}  // namespace
+
 Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     const MountOptions &options = model_->options();
     const ModelPlan &plan = model_->plan();
@@ -383,6 +527,7 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
 
     kernel_error_ = device_alloc(sizeof(int));
     set_int4_error_flag(static_cast<int *>(kernel_error_.ptr));
+    if (options.tp_size > 1) tp_partial_ = device_alloc(lanes * static_cast<size_t>(plan.hidden) * sizeof(float));
     {
         size_t q_width = 0, ffn = 0;
         for (const StackPlan *stack : {&model_->target_stack(), &model_->draft_stack()})
@@ -409,11 +554,12 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
 
 Engine::~Engine() {
     cudaStreamSynchronize(cuda_stream_);
+    if (nccl_comm_ != nullptr) g_nccl.comm_destroy(nccl_comm_);
     set_int4_error_flag(nullptr);
     for (auto &entry : signals_) cudaFree(entry.second.ptr);
     for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
                                  &records_, &argmax_scratch_, &sampler_scratch_, &sampler_table_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
-                                 &cycle_state_, &kernel_error_, &stack_q_, &stack_attention_out_, &stack_activation_, &stack_barrier_, &stack_timing_})
+                                 &cycle_state_, &kernel_error_, &tp_partial_, &stack_q_, &stack_attention_out_, &stack_activation_, &stack_barrier_, &stack_timing_})
         cudaFree(buffer->ptr);
     cudaFreeHost(staging_);
     cudaFreeHost(host_records_);
@@ -423,6 +569,39 @@ Engine::~Engine() {
     cudaEventDestroy(event_a_);
     cudaEventDestroy(event_b_);
     cudaStreamDestroy(cuda_stream_);
+}
+
+void Engine::tensor_parallel_unique_id(const std::string &library, uint8_t *out_128_bytes) {
+    NcclApi api{};
+    open_nccl(library, api);  // stays loaded: the communicator is made from the same library
+    NcclId id{};
+    int result = api.get_unique_id(&id);
+    if (result != 0) fail(std::string("ncclGetUniqueId: ") + api.get_error_string(result));
+    std::memcpy(out_128_bytes, id.bytes, 128);
+}
+
+void Engine::init_tensor_parallel(const std::string &library, int rank, int size, const uint8_t *unique_id_128_bytes) {
+    const MountOptions &options = model_->options();
+    if (size != options.tp_size || rank != options.tp_rank)
+        fail("tensor-parallel group (" + std::to_string(rank) + " of " + std::to_string(size) + ") differs from the mounted shard (" +
+             std::to_string(options.tp_rank) + " of " + std::to_string(options.tp_size) + ")");
+    if (size <= 1) return;
+    if (nccl_comm_ != nullptr) fail("tensor parallelism is already initialised");
+    cuda_check(cudaSetDevice(options.device), "cudaSetDevice");
+    nccl_library_ = open_nccl(library, g_nccl);
+    NcclId id{};
+    std::memcpy(id.bytes, unique_id_128_bytes, 128);
+    // ncclCommInitRank takes the id by value: a 128-byte struct is passed in memory, which is how this call passes it
+    using InitByValue = int (*)(void **, int, NcclId, int);
+    int result = reinterpret_cast<InitByValue>(g_nccl.comm_init_rank)(&nccl_comm_, size, id, rank);
+    if (result != 0) fail(std::string("ncclCommInitRank: ") + g_nccl.get_error_string(result));
+}
+
+void Engine::tp_all_reduce(float *values, size_t count) {
+    if (nccl_comm_ == nullptr) fail("this package was mounted as a tensor-parallel shard: call init_tensor_parallel before running");
+    int result = g_nccl.all_reduce(values, values, count, 7 /* ncclFloat32 */, 0 /* ncclSum */, nccl_comm_, cuda_stream_);
+    if (result != 0) fail(std::string("ncclAllReduce: ") + g_nccl.get_error_string(result));
+    counters_.kernel_launches++;
 }
 
 void Engine::check(cudaError_t status, const char *what) {
@@ -655,6 +834,37 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                   "rms_norm");
             break;
         case OpKind::Linear: {
+            if (op.tp_partial) {
+                // row-parallel linear: f32 partial sums of this rank's columns -> all-reduce -> the linear's bf16 rounding
+                // (and, when a residual_add of its output follows, that add with its second rounding)
+                const WeightRef &w = op.weights[0];
+                float *partial = static_cast<float *>(tp_partial_.ptr);
+                if (w.storage == TensorStorage::INT4_CT) {
+                    profile_begin(static_cast<uint64_t>(w.n) * (w.k / 2 + w.k / 64));
+                    check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(w.tensor)),
+                                             static_cast<const uint16_t *>(weight(w.scale)), reinterpret_cast<uint16_t *>(partial), nullptr, lanes,
+                                             static_cast<int>(w.n), static_cast<int>(w.k), w.group, EPILOGUE_F32_SCALED, st),
+                          "linear_int4 (row-parallel)");
+                    profile_end();
+                } else {
+                    check(launch_linear_bf16(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(w.tensor)), partial, nullptr, lanes,
+                                             static_cast<int>(w.n), static_cast<int>(w.k), EPILOGUE_F32_SCALED, 1.0f, st),
+                          "linear_bf16 (row-parallel)");
+                }
+                tp_all_reduce(partial, static_cast<size_t>(lanes) * w.n);
+                const bool fold = index + 1 < plan.ops.size() && plan.ops[index + 1].kind == OpKind::ResidualAdd &&
+                                  consumers(op.outputs[0], index + 2) == 0 &&
+                                  (plan.ops[index + 1].inputs[0] == op.outputs[0] || plan.ops[index + 1].inputs[1] == op.outputs[0]);
+                if (fold) {
+                    const OpSpec &add = plan.ops[index + 1];
+                    const std::string &residual = add.inputs[0] == op.outputs[0] ? add.inputs[1] : add.inputs[0];
+                    check(launch_round_add(partial, u16(residual), u16(add.outputs[0]), static_cast<size_t>(lanes) * w.n, st), "round + residual");
+                    index += 1;
+                } else {
+                    check(launch_round_add(partial, nullptr, u16(op.outputs[0]), static_cast<size_t>(lanes) * w.n, st), "round");
+                }
+                break;
+            }
             if (is_int4_single(op)) {
                 // gate/up + SiLU*up in one launch
                 if (index + 2 < plan.ops.size() && is_int4_single(plan.ops[index + 1]) && plan.ops[index + 2].kind == OpKind::SiluMultiply &&
@@ -932,7 +1142,8 @@ int Engine::splits_for(uint64_t newest_tick) const {
 // Runs `body` (stream-ordered launches only: no uploads, read-backs or synchronisation) directly the first time a
 // key is seen, then captures it into a CUDA graph and replays the graph from the third call on.
 void Engine::run_phase(const std::vector<int> &key, const std::function<void()> &body) {
-    if (!use_graphs_ || profile_) {
+    // tensor-parallel engines launch directly: the all-reduces are not replayed from a captured graph
+    if (!use_graphs_ || profile_ || model_->options().tp_size > 1) {
         body();
         return;
     }
@@ -966,6 +1177,7 @@ void Engine::run_phase(const std::vector<int> &key, const std::function<void()> 
 // Runs a whole layer stack over `hidden` ([lanes][hidden], in place) with the persistent decode kernel when the
 // stack and the batch qualify; false = the caller runs the layers kernel by kernel.
 bool Engine::run_stack(const StackPlan &stack, int lanes, void *hidden) {
+    if (model_->options().tp_size > 1) return false;  // the persistent kernel has no all-reduce inside (yet)
     if (!stack_enabled_ || !stack.available || lanes < 1 || lanes > 8 || current_width_ <= 0 || lanes % current_width_ != 0) return false;
     size_t smem = 0;
     if (!decode_stack_supported(stack.shape, lanes, &smem)) return false;

@@ -72,7 +72,7 @@ public:
     static std::shared_ptr<MountedModel> mount(const std::string &path, const MountOptions &options);
     ~MountedModel();
 
-    const ModelPlan &plan() const { return package_->plan(); }
+    const ModelPlan &plan() const { return plan_; }  // the package's plan, cut down to this process's tensor-parallel shard
     const HostPackage &package() const { return *package_; }
     const MountOptions &options() const { return options_; }
     const void *tensor(const std::string &name) const;
@@ -103,6 +103,7 @@ private:
     void build_stack(const std::vector<ComponentPlan> &layers, int first_kv_index, StackPlan &out);
 
     std::shared_ptr<HostPackage> package_;
+    ModelPlan plan_;
     MountOptions options_;
     std::map<std::string, DeviceBuffer> tensors_;
     uint64_t weight_bytes_ = 0, target_step_bytes_ = 0, draft_step_bytes_ = 0, kv_bytes_per_token_ = 0;
@@ -182,6 +183,12 @@ public:
     // batches (speculative cycles or single-tick batches); 0 = unbounded.
     RunReport run(uint64_t max_batches, const std::function<void(const OutputEvent &)> &on_output);
     void set_profiling(bool enabled) { profile_ = enabled; }
+    // Tensor parallelism: every rank of the group runs the same streams in lock step on its shard of the weights and
+    // meets the others in one NCCL all-reduce of f32 partial sums after each o and down projection.  `library` is the
+    // path of libnccl.so.2 (loaded at run time, the engine does not link it); `unique_id` the 128 bytes rank 0 got
+    // from tensor_parallel_unique_id and passed to the other ranks.
+    static void tensor_parallel_unique_id(const std::string &library, uint8_t *out_128_bytes);
+    void init_tensor_parallel(const std::string &library, int rank, int size, const uint8_t *unique_id_128_bytes);
 
     uint64_t stream_tick(int64_t id) const;
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
@@ -283,6 +290,9 @@ private:
     DeviceBuffer pending_hidden_;           // [max_streams][hidden]
     DeviceBuffer attention_scratch_;
     DeviceBuffer kernel_error_;             // device word set by pipelined kernels whose bounded waits expired
+    DeviceBuffer tp_partial_;               // f32 [max_lanes][hidden] partial sums of row-parallel linears
+    void *nccl_library_ = nullptr, *nccl_comm_ = nullptr;
+    void tp_all_reduce(float *values, size_t count);
     // persistent decode stack workspaces ([8 lanes][width]) and its two barrier words
     DeviceBuffer stack_q_, stack_attention_out_, stack_activation_, stack_barrier_, stack_timing_;
     bool stack_enabled_ = true;

@@ -50,7 +50,7 @@ enum LinearEpilogue {
     EPILOGUE_BF16 = 0,            // y = bf16(sum)
     EPILOGUE_RESIDUAL_ROUNDED = 1,  // y = bf16(bf16(sum) + residual)        (BF16 / INT4 packages)
     EPILOGUE_RESIDUAL_F32 = 2,    // y = bf16(sum + residual)                (FP8 packages)
-    EPILOGUE_F32_SCALED = 3,      // y_f32 = sum * scale                     (logits)
+    EPILOGUE_F32_SCALED = 3,      // y_f32 = sum * scale                     (logits; tensor-parallel partial sums)
 };
 
 // y[m][n] = sum_k x[m][k] * W[n][k], bf16 weights.
@@ -168,6 +168,10 @@ bool decode_stack_supported(const StackShape &shape, int lanes, size_t *smem_byt
 cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count, const StackShape &shape,
                                 const StackBuffers &buffers, const LaneTable &lanes_meta, int lanes, int lanes_per_stream,
                                 int split_tokens, int max_splits, cudaStream_t stream);
+
+// Tensor-parallel row-parallel linears: out = bf16(bf16(sum) + residual) (or bf16(sum) without residual) from the
+// all-reduced f32 sums [count].
+cudaError_t launch_round_add(const float *sums, const uint16_t *residual, uint16_t *out, size_t count, cudaStream_t stream);
 
 // ---- glue of the speculative cycle (all tiny) ----
 // dst[i] = src[index[i]] for rows of `width` bf16.

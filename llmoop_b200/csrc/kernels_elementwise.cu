@@ -91,6 +91,26 @@ cudaError_t launch_add(const uint16_t *a, const uint16_t *b, uint16_t *y, size_t
     return cudaGetLastError();
 }
 
+// After the tensor-parallel all-reduce of a row-parallel linear: the reference's linear rounds its f32 sum to bf16
+// and its residual_add rounds again (add_bf16.comp.template:17-24).
+__global__ void round_add_kernel(const float *__restrict__ sums, const uint16_t *__restrict__ residual, uint16_t *__restrict__ out,
+                                 size_t count) {
+    for (size_t index = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; index < count;
+         index += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float value = round_bf16(sums[index]);
+        if (residual != nullptr) value += bf16_bits_to_f32(residual[index]);
+        out[index] = static_cast<uint16_t>(f32_to_bf16_bits(value));
+    }
+}
+
+cudaError_t launch_round_add(const float *sums, const uint16_t *residual, uint16_t *out, size_t count, cudaStream_t stream) {
+    int blocks = static_cast<int>((count + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    round_add_kernel<<<blocks, 256, 0, stream>>>(sums, residual, out, count);
+    return cudaGetLastError();
+}
+
 // silu_multiply_bf16.comp.template:30-52: bf16(bf16(silu(gate)) * up)
 __global__ void silu_multiply_kernel(const uint32_t *__restrict__ gate, const uint32_t *__restrict__ up,
                                      uint32_t *__restrict__ y, size_t words) {

@@ -352,6 +352,10 @@ linear_int4_mma_kernel(const Int4Launch p) {
 #pragma unroll
             for (int w = 0; w < INT4_WARPS; w++) sum += reduce[w][local_row][m];
             size_t out = static_cast<size_t>(m0 + m) * br.n + row;
+            if (p.epilogue == EPILOGUE_F32_SCALED) {  // f32 partial sums (tensor-parallel row split)
+                reinterpret_cast<float *>(br.y)[out] = sum;
+                continue;
+            }
             if (p.epilogue == EPILOGUE_RESIDUAL_ROUNDED) sum = round_bf16(sum) + bf16_bits_to_f32(p.residual[out]);
             else if (p.epilogue == EPILOGUE_RESIDUAL_F32) sum = sum + bf16_bits_to_f32(p.residual[out]);
             br.y[out] = static_cast<uint16_t>(f32_to_bf16_bits(sum));
@@ -395,7 +399,7 @@ cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint
                                      const uint16_t *residual, int lanes, int k, int epilogue, cudaStream_t stream) {
     if (lanes <= 0) return cudaSuccess;
     if (k % 128 != 0 || branches < 1 || branches > 3) return cudaErrorInvalidValue;
-    if (use_stream_kernel(k))
+    if (use_stream_kernel(k) && epilogue != EPILOGUE_F32_SCALED)
         return launch_linear_int4_stream(x, branches, qweights, scales, ys, ns, residual, lanes, k, epilogue, g_int4_error_flag, stream);
     Int4Launch params = {};
     params.branches = branches;

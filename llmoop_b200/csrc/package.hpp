@@ -63,6 +63,8 @@ struct WeightRef {
     TensorStorage storage = TensorStorage::BF16;
     int64_t n = 0, k = 0;     // logical [out, in]
     int group = 0;            // INT4 group size along K, FP8 block columns
+    // tensor-parallel shard held by this process (n, k above are the shard's; the full tensor is full_n x full_k)
+    int64_t full_n = 0, full_k = 0, row_begin = 0, col_begin = 0;
 };
 
 struct RopeAttrs {
@@ -87,6 +89,7 @@ struct OpSpec {
     bool residual_rounds_product = false;  // BF16 linear_residual rounds the product before the add
     std::string residual_input;
     bool prequantized_input = false;       // FP8 linears fed by a QuantizeFp8 op
+    bool tp_partial = false;               // row-parallel linear: the output is a partial sum to all-reduce over the TP group
 };
 
 struct SignalInfo {

@@ -69,4 +69,14 @@ inline std::vector<uint8_t> state_page_table_bytes(const StateLayout &layout, co
     return bytes;
 }
 
+// Tensor-parallel shard of `total` rows (or columns) that must stay in whole units (a head, 16 rows, a group of 128
+// columns): rank r of `size` holds [begin, begin + count).  Throws when total is not a multiple of unit * size.
+inline void tp_shard_range(int64_t total, int64_t unit, int rank, int size, int64_t &begin, int64_t &count) {
+    if (size < 1 || rank < 0 || rank >= size || unit < 1) throw std::runtime_error("tensor-parallel rank/size/unit out of range");
+    if (total % (unit * size) != 0)
+        throw std::runtime_error(std::to_string(total) + " is not a multiple of " + std::to_string(unit) + " x " + std::to_string(size) + " ranks");
+    count = total / size;
+    begin = count * rank;
+}
+
 }  // namespace nerve

@@ -66,7 +66,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_destroy", "nerve_b200_engine_add_stream", "nerve_b200_engine_fork_stream",
     "nerve_b200_engine_reset_stream", "nerve_b200_engine_remove_stream", "nerve_b200_engine_interrupt_stream",
     "nerve_b200_engine_enqueue", "nerve_b200_engine_run_until_idle", "nerve_b200_engine_run",
-    "nerve_b200_engine_set_profiling", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
+    "nerve_b200_engine_set_profiling", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_init_tp", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
     "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair", "nerve_b200_set_int4_kernel",
@@ -156,6 +156,34 @@ class Package:
             pass
 
 
+def nccl_library_path() -> str:
+    """libnccl.so.2 as shipped with torch's CUDA wheels, or the system's."""
+    import importlib.util
+    from pathlib import Path
+
+    spec = importlib.util.find_spec("nvidia.nccl")
+    if spec is not None and spec.submodule_search_locations:
+        for base in spec.submodule_search_locations:
+            candidate = Path(base) / "lib" / "libnccl.so.2"
+            if candidate.exists():
+                return str(candidate)
+    return "libnccl.so.2"
+
+
+def tp_shard_range(total: int, unit: int, rank: int, size: int):
+    """(begin, count) of rank's tensor-parallel shard; raises NerveError when total is not a multiple of unit x size."""
+    begin, count = ctypes.c_int64(0), ctypes.c_int64(0)
+    _check(library().nerve_b200_tp_shard_range(ctypes.c_int64(total), ctypes.c_int64(unit), rank, size, ctypes.byref(begin), ctypes.byref(count)))
+    return begin.value, count.value
+
+
+def tensor_parallel_unique_id() -> bytes:
+    """The 128-byte NCCL id rank 0 creates and passes to the other ranks."""
+    buffer = (ctypes.c_uint8 * 128)()
+    _check(library().nerve_b200_tp_unique_id(nccl_library_path().encode(), buffer))
+    return bytes(buffer)
+
+
 class Engine:
     def __init__(self, package: Package):
         self.package = package
@@ -204,6 +232,10 @@ class Engine:
     def run_until_idle(self, on_output=None):
         """Returns (outputs, report): outputs is a list of (stream_id, token_id, source_stream_tick, output_index)."""
         return self.run(0, on_output)
+
+    def init_tensor_parallel(self, rank: int, size: int, unique_id: bytes):
+        buffer = (ctypes.c_uint8 * 128).from_buffer_copy(unique_id)
+        _check(library().nerve_b200_engine_init_tp(self._handle, nccl_library_path().encode(), rank, size, buffer))
 
     def set_decode_stack(self, enabled: bool):
         _check(library().nerve_b200_engine_set_decode_stack(self._handle, int(enabled)))

@@ -1,0 +1,95 @@
+"""Tensor-parallel engine on two GPUs of one box (skipped where fewer are visible): each rank mounts its shard of a
+synthetic INT4 package, joins the NCCL group through the C ABI and runs the same stream; the ranks must emit the
+same tokens, and those must be the oracle's (sequences may part where the oracle's top-2 logit gap is below 2e-2:
+the ranks' partial sums are added in another order than one GPU's)."""
+
+import os
+import pickle
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, size, port, directory, prompt, drafts, out):
+    import torch
+    import torch.distributed as dist
+
+    import llmoop_b200 as nb
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("gloo", rank=rank, world_size=size)
+    torch.cuda.set_device(rank)
+    holder = [nb.tensor_parallel_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(holder, src=0)
+    package = nb.Package(directory, device=rank, capacity_tokens=128, page_tokens=16, max_streams=2, max_lanes=64, verify_level=0,
+                         tp_rank=rank, tp_size=size)
+    engine = nb.Engine(package)
+    engine.init_tensor_parallel(rank, size, holder[0])
+    engine.set_cycle_logging(True)
+    engine.add_stream(1, speculative_draft_tokens=drafts)
+    tokens, report = engine.submit_input_event_until_idle(1, prompt, 20)
+    accepted = [c["accepted"] for c in engine.cycle_log()]
+    gathered = [None] * size
+    dist.all_gather_object(gathered, (tokens, accepted))
+    if rank == 0:
+        out.put(pickle.dumps(gathered))
+    engine.close()
+    package.unmount()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("drafts", [0, 3])
+def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, drafts):
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from llmoop_b200.package_writer import write_package
+    from llmoop_b200.synth import ModelSpec
+    from oracle.nerve_oracle import Oracle, OraclePackage, OracleStream
+
+    spec = ModelSpec(name="tp_int4", hidden=1024, layers=2, q_heads=8, kv_heads=2, head_dim=128, ffn=3584, vocab=1024,
+                     max_positions=512, quant="int4", std=0.02, seed=21)
+    directory = tmp_path / spec.name
+    write_package(spec, directory)
+    prompt = [int(t) for t in np.random.default_rng(4).integers(0, spec.vocab, size=11)]
+    opkg = OraclePackage(directory)
+    oracle = Oracle(opkg)
+    expected = oracle.generate(OracleStream(opkg, 128), prompt, 20, drafts, collect_logits=True)
+
+    context = mp.get_context("spawn")
+    out = context.Queue()
+    port = _free_port()
+    processes = [context.Process(target=_worker, args=(rank, 2, port, str(directory), prompt, drafts, out)) for rank in range(2)]
+    for process in processes:
+        process.start()
+    try:
+        for process in processes:
+            process.join(timeout=150)
+            assert process.exitcode == 0, "a tensor-parallel rank failed or did not finish"
+    finally:
+        for process in processes:
+            if process.is_alive():
+                process.kill()
+    gathered = pickle.loads(out.get(timeout=10))
+    assert gathered[0] == gathered[1]  # the ranks agree token for token
+    tokens, accepted = gathered[0]
+    for index, (got, want) in enumerate(zip(tokens, expected["tokens"])):
+        if got != want:
+            gap = oracle.top2_gap(expected["logits"][index])
+            assert gap < 2e-2, f"token {index}: tensor-parallel {got} != oracle {want} with top-2 gap {gap}"
+            break
+    else:
+        assert len(tokens) == len(expected["tokens"])
+        assert accepted == [c["accepted"] for c in expected["cycles"]]
