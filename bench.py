@@ -237,7 +237,7 @@ def main():
         line = {
             "impl": "reference", "metric": METRIC, "value": sample["tokens_per_s"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": sample["cycles"], "steps_requested": steps, "warmup": 0, "ms_per_step": sample["ms_per_cycle"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights, bf16 activations, f32 accumulate",
+            "higher_is_better": True, "scaling": "strong" if tensor_parallel else "weak", "vs_baseline": None, "dtype": "int4 weights, bf16 activations, f32 accumulate",
             "data": "synthetic", "config": config,
             "cpu_baseline": {"value": sample["tokens_per_s"], "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"{sample['cycles']} speculative cycles (k=3) at a 16-token context, OpenMP over output rows"},
@@ -267,15 +267,26 @@ def main():
         directory = ensure_package(spec, f"cuda:{local_rank}")
     barrier()
     directory = package_dir(spec.name)
-    prompt = prompt_tokens(spec.vocab, seed=rank)
+    # Several GPUs: one stream, the weights sharded tensor-parallel over the ranks (strong scaling; every rank runs
+    # the same calls and meets the others in the all-reduces).  NERVE_B200_BENCH_REPLICAS=1 instead runs one
+    # independent stream per GPU on replicated weights (weak scaling, no collective on the data path).
+    tensor_parallel = world > 1 and os.environ.get("NERVE_B200_BENCH_REPLICAS", "0") != "1"
+    prompt = prompt_tokens(spec.vocab, seed=0 if tensor_parallel else rank)
 
     # natural-mode budget: one token per cycle when no draft is accepted, up to k+1 when all are
     budget = (warmup + steps) * (DRAFTS + 1) + 8
     capacity = PROMPT_TOKENS + max(budget, EVENT_TOKENS + 8) + 64  # the context ring never wraps in this workload
     package = nb.Package(directory, device=local_rank, capacity_tokens=capacity, page_tokens=16, max_streams=1,
-                         max_lanes=PROMPT_TOKENS, verify_level=0)
+                         max_lanes=PROMPT_TOKENS, verify_level=0, tp_rank=rank if tensor_parallel else 0,
+                         tp_size=world if tensor_parallel else 1)
     info = package.info
     engine = nb.Engine(package)
+    if tensor_parallel:
+        unique_id = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            unique_id.copy_(torch.frombuffer(bytearray(nb.tensor_parallel_unique_id()), dtype=torch.uint8))
+        dist.broadcast(unique_id, src=0)
+        engine.init_tensor_parallel(rank, world, bytes(unique_id.cpu().numpy().tobytes()))
     engine.set_prefill_chunk(PROMPT_TOKENS)
     engine.add_stream(0, seed=0, speculative_draft_tokens=DRAFTS)
 
@@ -311,7 +322,7 @@ def main():
     profiled, _ = timed_cycles(engine, 0, prompt, budget, warmup, min(steps, 16), None, barrier)
     engine.set_profiling(False)
 
-    stack_kernel = bool(info["target_decode_stack"]) and os.environ.get("NERVE_B200_DECODE_STACK", "1") != "0"
+    stack_kernel = bool(info["target_decode_stack"]) and os.environ.get("NERVE_B200_DECODE_STACK", "1") != "0" and not tensor_parallel
 
     def reduce_max(value):
         if world == 1:
@@ -321,7 +332,7 @@ def main():
         return float(tensor.item())
 
     def reduce_sum(value):
-        if world == 1:
+        if world == 1 or tensor_parallel:  # tensor-parallel ranks all carry the one stream: nothing to add up
             return value
         tensor = torch.tensor([value], dtype=torch.float64, device="cuda")
         dist.all_reduce(tensor, op=dist.ReduceOp.SUM)
@@ -341,9 +352,10 @@ def main():
     int4_gbs = profiled.int4_bytes / (profiled.int4_ms * 1e-3) / 1e9 if profiled.int4_ms > 0 else 0.0
     line = {
         "metric": METRIC, "value": tokens / seconds, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": 1e3 * seconds / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": 1e3 * seconds / steps, "higher_is_better": True, "scaling": "strong" if tensor_parallel else "weak", "vs_baseline": None,
         "dtype": "int4 weights, bf16 activations, f32 accumulate", "data": "synthetic",
-        "config": {**config, "parallelism": "replicated streams (one per GPU)" if world > 1 else "single GPU",
+        "config": {**config, "parallelism": (f"tp{world}: dense layers sharded by rows / columns, 2 NCCL all-reduces per layer" if tensor_parallel
+                                              else "replicated streams (one per GPU)") if world > 1 else "single GPU",
                    "capacity_tokens": capacity},
         "modes": {
             "natural": {"tokens_per_s": tokens / seconds, "acceptance": natural_timed.accepted_draft_token_count /
