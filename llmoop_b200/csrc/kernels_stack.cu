@@ -98,6 +98,15 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The same with a zero accumulator coming in (starts a chain without clearing registers first).
+__device__ __forceinline__ void mma_bf16_16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                     uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 // Nibble pair k of `word` (bits 4k..4k+3 and 16+4k..16+4k+3) -> bf16x2 (16 + q, 16 + q'): with the nibble in
 // mantissa bits 3..6 under exponent 2^4, 0x4180 | q << 3 is exactly 16 + q.  One shift and one lop3 per pair; the
 // offset 16 (+ 8 of the symmetric INT4 code) leaves the accumulator as 24 * sum(x) per group, taken out afterwards.
@@ -143,7 +152,7 @@ __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int
 struct StackSmem {
     uint4 *fragments;    // [groups][4 words][staged lanes][4] activations in B-fragment order
     uint16_t *rows;      // [staged lanes][hidden] normalised rows before they are permuted
-    float *correction;   // [groups][8] 24 * sum(x) per lane
+    float *correction;   // [groups][8] -24 * sum(x) per lane
     float *reduce;       // [2][warps][32 rows][8]
     float *partial;      // [8 lanes][warps]
     uint8_t *ring;       // [warps][RING_UNITS][RING_UNIT_BYTES] packed weights in flight (asynchronous copies)
@@ -184,6 +193,30 @@ __device__ __forceinline__ void async_wait(int newer) {
     }
 }
 
+// Waits for the oldest of this thread's `in_flight` (>= 1) copy groups; the usual depths are tested first.
+__device__ __forceinline__ void async_wait_oldest(int in_flight) {
+    if (in_flight == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
+    else if (in_flight == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
+    else async_wait(in_flight - 1);
+}
+// Shared-memory loads by shared-space address (32-bit address arithmetic, offsets folded into the instruction).
+template <int OFFSET>
+__device__ __forceinline__ uint4 shared_load16(uint32_t address) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address), "n"(OFFSET) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t shared_load4(uint32_t address) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 shared_load_float2(uint32_t address) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(address) : "memory");
+    return v;
+}
+
 // One matrix as a warp sees it: for each of the CTA's tiles (blockIdx.x, += gridDim.x) the warp's groups
 // (warp, += 16); an item is `rt` ring units (rt = 2 for a gate/up pair).
 struct MatrixWalk {
@@ -204,19 +237,19 @@ __device__ __forceinline__ MatrixWalk walk_of(const TiledInt4 &matrix, int rt) {
 }
 
 struct WeightStream {
-    const uint8_t *ring;    // this thread's 16 bytes (first half) of ring unit 0; the scale word is at scale_offset from it
-    uint32_t ring_shared;   // the same position as a shared-space address, for the copies
-    int scale_offset;       // 1024 + lane * 4 - lane * 16
-    int units;              // ring units of this warp (2..MAX_RING_UNITS, as shared memory allows)
-    int head, tail;         // ring positions (unit index) of the next block to consume / to request
-    int used;               // units requested and not yet consumed
-    int in_flight;          // items (copy groups) requested and not yet consumed
+    uint32_t ring_begin, ring_end;  // shared-space address of this thread's 16 bytes (first half) of ring unit 0 / one past the last unit
+    uint32_t head, tail;            // the same position in the unit to consume next / to request next
+    uint32_t scale_offset;          // from there to this thread's scale word: 1024 + lane * 4 - lane * 16
+    int units;                      // ring units of this warp (2..MAX_RING_UNITS, as shared memory allows)
+    int used;                       // units requested and not yet consumed
+    int in_flight;                  // items (copy groups) requested and not yet consumed
     // producer: the matrix being requested from, and the position in it
     int source_phase, rt, per_tile, remaining, gi;
-    const uint4 *weights;   // this thread's 16 bytes of the next block to request
-    const uint32_t *scales; // and its scale pair
-    long long step, tile_step;  // blocks to move on by inside a tile / to the first block of the CTA's next tile
-    MatrixWalk following;   // the matrix after it (valid when has_following)
+    const uint4 *weights;           // the matrix, moved on by this thread's lane: + offset = its 16 bytes of the next block
+    const uint32_t *scales;         // the scale pairs, moved on by lane / 4: + (offset >> 3) = this thread's pair of that block
+    uint32_t offset;                // in 16-byte words; one block is 64 of them
+    uint32_t step, tile_step;       // to the warp's next block inside a tile / to its first block of the CTA's next tile
+    MatrixWalk following;           // the matrix after it (valid when has_following)
     bool has_following;
 };
 
@@ -227,41 +260,47 @@ __device__ __forceinline__ void stream_start(WeightStream &stream, const MatrixW
     stream.per_tile = walk.per_tile;
     stream.remaining = walk.total;
     stream.gi = 0;
-    const size_t block = (static_cast<size_t>(blockIdx.x) * walk.matrix.groups + warp) * walk.rt;
-    stream.weights = walk.matrix.weights + block * 64 + lane;
-    stream.scales = walk.matrix.scales + block * 8 + (lane >> 2);
-    stream.step = static_cast<long long>(STACK_WARPS) * walk.rt;
-    stream.tile_step = (static_cast<long long>(gridDim.x) * walk.matrix.groups - (walk.per_tile - 1) * STACK_WARPS) * walk.rt;
+    stream.weights = walk.matrix.weights + lane;
+    stream.scales = walk.matrix.scales + (lane >> 2);
+    stream.offset = (blockIdx.x * static_cast<uint32_t>(walk.matrix.groups) + warp) * walk.rt * 64u;
+    stream.step = static_cast<uint32_t>(STACK_WARPS) * walk.rt * 64u;
+    stream.tile_step = (gridDim.x * static_cast<uint32_t>(walk.matrix.groups) - (walk.per_tile - 1) * STACK_WARPS) * walk.rt * 64u;
 }
 
-// Requests the producer's next item (the ring has room and the matrix has items left).
-__device__ __forceinline__ void stream_issue(WeightStream &stream) {
-    {
-        const uint32_t unit = stream.ring_shared + stream.tail * RING_UNIT_BYTES;
-        async_copy16<0, 0>(unit, stream.weights);
-        async_copy16<512, 512>(unit, stream.weights);
-        async_copy4<0>(unit + stream.scale_offset, stream.scales);
-        stream.tail = stream.tail + 1 == stream.units ? 0 : stream.tail + 1;
-    }
-    if (stream.rt == 2) {
-        const uint32_t unit = stream.ring_shared + stream.tail * RING_UNIT_BYTES;
-        async_copy16<0, 1024>(unit, stream.weights);
-        async_copy16<512, 1536>(unit, stream.weights);
-        async_copy4<32>(unit + stream.scale_offset, stream.scales);
-        stream.tail = stream.tail + 1 == stream.units ? 0 : stream.tail + 1;
+// Requests the producer's next item of RT units (the ring has room and the matrix has items left).
+template <int RT>
+__device__ __forceinline__ void stream_issue_item(WeightStream &stream) {
+    const uint4 *source = stream.weights + stream.offset;
+    const uint32_t *scale_source = stream.scales + (stream.offset >> 3);
+#pragma unroll
+    for (int r = 0; r < RT; r++) {
+        if (r == 0) {
+            async_copy16<0, 0>(stream.tail, source);
+            async_copy16<512, 512>(stream.tail, source);
+            async_copy4<0>(stream.tail + stream.scale_offset, scale_source);
+        } else {
+            async_copy16<0, 1024>(stream.tail, source);
+            async_copy16<512, 1536>(stream.tail, source);
+            async_copy4<32>(stream.tail + stream.scale_offset, scale_source);
+        }
+        stream.tail += RING_UNIT_BYTES;
+        if (stream.tail == stream.ring_end) stream.tail = stream.ring_begin;
     }
     async_commit();
-    stream.used += stream.rt;
+    stream.used += RT;
     stream.in_flight++;
     stream.remaining--;
     // next block of this warp: 16 groups on, or the first group of the CTA's next tile
-    long long blocks = stream.step;
+    uint32_t advance = stream.step;
     if (++stream.gi == stream.per_tile) {
         stream.gi = 0;
-        blocks = stream.tile_step;
+        advance = stream.tile_step;
     }
-    stream.weights += blocks * 64;
-    stream.scales += blocks * 8;
+    stream.offset += advance;
+}
+__device__ __forceinline__ void stream_issue(WeightStream &stream) {
+    if (stream.rt == 2) stream_issue_item<2>(stream);
+    else stream_issue_item<1>(stream);
 }
 
 // Requests as many blocks as the ring has room for, moving on to the following matrix when this one is done.
@@ -325,7 +364,7 @@ __device__ __forceinline__ void stage_chunk(const StackSmem &sm, uint4 raw, bool
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);
     sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-    if (active && (chunk & 15) == 0) sm.correction[group * 8 + m] = NIBBLE_BIAS * sum;
+    if (active && (chunk & 15) == 0) sm.correction[group * 8 + m] = -NIBBLE_BIAS * sum;  // the accumulation chains start from it
 }
 
 // Permutes [staged][width] bf16 rows into fragment order.  from_global: the rows were written by other CTAs of
@@ -738,29 +777,72 @@ __host__ __device__ inline StackSmemLayout stack_smem_layout(const StackShape &s
     return layout;
 }
 
-// One 16x128 block of the ring against the staged activations: eight MMAs over bf16 (16 + q), the block's two
-// scales, and the 24 * sum(x) bias of the group.
-__device__ __forceinline__ void consume_unit(const uint8_t *mine, int scale_offset, const uint4 (&b)[4], float2 bias, float (&acc)[4]) {
-    const uint4 first = *reinterpret_cast<const uint4 *>(mine);
-    const uint4 second = *reinterpret_cast<const uint4 *>(mine + 512);
-    const uint32_t scales = *reinterpret_cast<const uint32_t *>(mine + scale_offset);
-    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f}, d[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // two accumulation chains of four MMAs
+// One 16x128 block of the ring against the staged activations: eight MMAs over bf16 (16 + q) in two accumulation
+// chains.  The first chain starts from -24 * sum(x) of the group (`negative_bias`, per lane), which takes the
+// 16 + 8 offset of the nibbles out again; the sum of the chains is the block's product.
+__device__ __forceinline__ void unit_products(uint32_t mine, const uint4 (&b)[4], float2 negative_bias, float (&c)[4]) {
+    const uint4 first = shared_load16<0>(mine);
+    const uint4 second = shared_load16<512>(mine);
     const uint32_t wa[4] = {first.x, first.y, first.z, first.w};
     const uint32_t wb[4] = {second.x, second.y, second.z, second.w};
+    float even[4] = {negative_bias.x, negative_bias.y, negative_bias.x, negative_bias.y}, odd[4];
 #pragma unroll
     for (int word = 0; word < 4; word++) {
-        mma_bf16_16816(c, biased_pair<0>(wa[word]), biased_pair<0>(wb[word]), biased_pair<1>(wa[word]), biased_pair<1>(wb[word]), b[word].x,
+        mma_bf16_16816(even, biased_pair<0>(wa[word]), biased_pair<0>(wb[word]), biased_pair<1>(wa[word]), biased_pair<1>(wb[word]), b[word].x,
                        b[word].y);
-        mma_bf16_16816(d, biased_pair<2>(wa[word]), biased_pair<2>(wb[word]), biased_pair<3>(wa[word]), biased_pair<3>(wb[word]), b[word].z,
-                       b[word].w);
+        if (word == 0)
+            mma_bf16_16816_first(odd, biased_pair<2>(wa[word]), biased_pair<2>(wb[word]), biased_pair<3>(wa[word]), biased_pair<3>(wb[word]),
+                                 b[word].z, b[word].w);
+        else
+            mma_bf16_16816(odd, biased_pair<2>(wa[word]), biased_pair<2>(wb[word]), biased_pair<3>(wa[word]), biased_pair<3>(wb[word]), b[word].z,
+                           b[word].w);
     }
 #pragma unroll
-    for (int i = 0; i < 4; i++) c[i] += d[i];
+    for (int i = 0; i < 4; i++) c[i] = even[i] + odd[i];
+}
+
+// The block's two scales (rows g and g + 8).
+__device__ __forceinline__ void unit_accumulate(uint32_t scales, const float (&c)[4], float (&acc)[4]) {
     const float sa = __uint_as_float(scales << 16), sb = __uint_as_float(scales & 0xffff0000u);
-    acc[0] = fmaf(sa, c[0] - bias.x, acc[0]);
-    acc[1] = fmaf(sa, c[1] - bias.y, acc[1]);
-    acc[2] = fmaf(sb, c[2] - bias.x, acc[2]);
-    acc[3] = fmaf(sb, c[3] - bias.y, acc[3]);
+    acc[0] = fmaf(sa, c[0], acc[0]);
+    acc[1] = fmaf(sa, c[1], acc[1]);
+    acc[2] = fmaf(sb, c[2], acc[2]);
+    acc[3] = fmaf(sb, c[3], acc[3]);
+}
+
+// A tile's items of this warp (RT ring units each): wait for the item's copies, issue its MMAs, put the freed ring
+// units back to work while the tensor pipe runs, then fold the products into the tile's accumulators.
+// xitem / bias_item: shared-space addresses of the thread's fragments and bias pair of the warp's first group.
+template <int RT>
+__device__ __forceinline__ void tile_items(WeightStream &stream, int items, uint32_t xitem, uint32_t bias_item, uint32_t word_stride,
+                                           float (&acc)[2][4]) {
+    const uint32_t item_stride = STACK_WARPS * 4 * word_stride;
+    for (int gi = 0; gi < items; gi++) {
+        uint4 b[4];
+        b[0] = shared_load16<0>(xitem);
+        b[1] = shared_load16<0>(xitem + word_stride);
+        b[2] = shared_load16<0>(xitem + 2 * word_stride);
+        b[3] = shared_load16<0>(xitem + 3 * word_stride);
+        const float2 negative_bias = shared_load_float2(bias_item);
+        xitem += item_stride;
+        bias_item += STACK_WARPS * 8 * sizeof(float);
+        async_wait_oldest(stream.in_flight);
+        stream.in_flight--;
+        float c[RT][4];
+        uint32_t scales[RT];
+#pragma unroll
+        for (int r = 0; r < RT; r++) {
+            scales[r] = shared_load4(stream.head + stream.scale_offset);
+            unit_products(stream.head, b, negative_bias, c[r]);
+            stream.head += RING_UNIT_BYTES;
+            if (stream.head == stream.ring_end) stream.head = stream.ring_begin;
+        }
+        stream.used -= RT;
+        if (stream.remaining > 0 && stream.rt == RT) stream_issue_item<RT>(stream);  // the freed units go straight back to work
+        else stream_advance(stream);
+#pragma unroll
+        for (int r = 0; r < RT; r++) unit_accumulate(scales[r], c[r], acc[r]);
+    }
 }
 
 template <int GROUP>
@@ -790,11 +872,11 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     int *error_flag = a.buffers.error_flag;
     int parity = 0, phase = 0;
     WeightStream stream;
-    stream.ring = sm.ring + static_cast<size_t>(warp) * a.ring_units * RING_UNIT_BYTES + lane * 16;
-    stream.ring_shared = static_cast<uint32_t>(__cvta_generic_to_shared(stream.ring));
+    stream.ring_begin = static_cast<uint32_t>(__cvta_generic_to_shared(sm.ring + static_cast<size_t>(warp) * a.ring_units * RING_UNIT_BYTES + lane * 16));
+    stream.ring_end = stream.ring_begin + a.ring_units * RING_UNIT_BYTES;
+    stream.head = stream.tail = stream.ring_begin;
     stream.scale_offset = 1024 + lane * 4 - lane * 16;
     stream.units = a.ring_units;
-    stream.head = stream.tail = 0;
     stream.used = 0;
     stream.rt = 1;
     stream.per_tile = 0;
@@ -805,7 +887,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     stream.remaining = 0;
     stream.weights = nullptr;
     stream.scales = nullptr;
-    stream.step = stream.tile_step = 0;
+    stream.offset = stream.step = stream.tile_step = 0;
 
     auto stamp = [&](int layer, int index) {
         if (a.buffers.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -838,7 +920,9 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
         }
     }
     const int ge = g < staged ? g : 0;  // lanes beyond the batch recompute lane 0; their results are dropped
-    const uint4 *xlane = sm.fragments + ge * 4 + j;
+    const uint32_t xlane = static_cast<uint32_t>(__cvta_generic_to_shared(sm.fragments + ge * 4 + j));
+    const uint32_t bias_lane = static_cast<uint32_t>(__cvta_generic_to_shared(sm.correction + 2 * j));
+    const uint32_t word_stride = static_cast<uint32_t>(staged) * 4 * sizeof(uint4);
 
     for (int layer = 0; layer < a.layer_count; layer++) {
         const StackLayer *spec = a.layers + layer;
@@ -915,27 +999,10 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                         payload = __ldcg(a.buffers.hidden + static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row);
                     }
                 }
-                const uint4 *xitem = xlane + warp * 4 * staged * 4;   // fragments of group `warp`, then 16 groups on per item
-                const float *bias_item = sm.correction + warp * 8 + 2 * j;
-                for (int gi = 0; gi < walk.per_tile; gi++) {
-                    uint4 b[4];
-#pragma unroll
-                    for (int word = 0; word < 4; word++) b[word] = xitem[word * staged * 4];
-                    const float2 bias = *reinterpret_cast<const float2 *>(bias_item);
-                    xitem += STACK_WARPS * 4 * staged * 4;
-                    bias_item += STACK_WARPS * 8;
-                    async_wait(stream.in_flight - 1);  // everything but the groups requested after this item's
-                    stream.in_flight--;
-                    consume_unit(stream.ring + stream.head * RING_UNIT_BYTES, stream.scale_offset, b, bias, acc[0]);
-                    stream.head = stream.head + 1 == stream.units ? 0 : stream.head + 1;
-                    if (rt == 2) {
-                        consume_unit(stream.ring + stream.head * RING_UNIT_BYTES, stream.scale_offset, b, bias, acc[1]);
-                        stream.head = stream.head + 1 == stream.units ? 0 : stream.head + 1;
-                    }
-                    stream.used -= rt;
-                    if (stream.remaining > 0 && stream.rt == rt) stream_issue(stream);  // the freed units go straight back to work
-                    else stream_advance(stream);
-                }
+                const uint32_t xitem = xlane + warp * 4 * word_stride;  // fragments of group `warp`, then 16 groups on per item
+                const uint32_t bias_item = bias_lane + warp * 8 * sizeof(float);
+                if (rt == 2) tile_items<2>(stream, walk.per_tile, xitem, bias_item, word_stride, acc);
+                else tile_items<1>(stream, walk.per_tile, xitem, bias_item, word_stride, acc);
                 float *mine = sm.reduce + static_cast<size_t>((parity * STACK_WARPS + warp) * 32) * 8;
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
