@@ -257,6 +257,81 @@ int32_t nerve_b200_verify_prefix(const uint32_t *draft, size_t draft_count, cons
                                  size_t target_count, const uint32_t *stop, size_t stop_count, uint32_t *out_counts,
                                  uint32_t *out_emitted, size_t *out_emitted_count);
 
+
+/* ---- stream scheduler and transient-state arena (host only, no GPU) -------------------------------------------
+ * The reference's RuntimeStreamScheduler (stream_runtime.rs:426-1433) over its TransientStateArena / Table
+ * (stream_state.rs:122-633), without the prefix-state cache: input events are cut into prefill chunks that end at
+ * state-page boundaries and into decode feedback windows; each activation reserves its state slots (KV pages)
+ * ahead of execution and gives back the ones it did not use when it completes; interrupt, close-after-current,
+ * reset, remove and fork follow the reference.  Strings written into the structs below are NUL-terminated and cut
+ * at 63 bytes. */
+typedef struct nerve_b200_scheduler nerve_b200_scheduler;
+typedef struct {
+    const char *node_instance_id, *state_id;
+    uint64_t bytes_per_activation, activation_capacity;
+    uint64_t maximum_activation_count; /* 0 = unbounded; else the state is a ring of that many activations */
+    int32_t retention;                 /* 0 = append, 1 = mutable singleton (activation_capacity is ignored) */
+} nerve_b200_state_declaration;
+typedef struct {
+    uint64_t max_activations, max_prefill_tokens_per_activation, max_decode_tokens_per_activation, max_work_units;
+} nerve_b200_scheduler_budget;
+typedef struct {
+    int32_t status; /* 0 idle, 1 active, 2 interrupted, 3 closing (stream_runtime.rs:15-21) */
+    uint64_t queued_input_event_count, in_flight_activation_count, completed_input_event_count, scheduled_activation_count,
+        generated_token_count, transient_state_entry_count, transient_state_block_count, transient_state_logical_activation_count;
+    char current_input_event_id[64]; /* empty = none */
+} nerve_b200_stream_snapshot;
+typedef struct {
+    uint64_t stream_count, active_stream_count, in_flight_activation_count, allocated_block_count, free_block_count, live_block_count;
+} nerve_b200_scheduler_counts;
+typedef struct {
+    uint64_t id;
+    int32_t kind; /* 0 = prefill chunk, 1 = decode feedback (stream_runtime.rs:44-55) */
+    uint64_t token_offset, token_count, remaining_prompt_token_count; /* prefill chunk */
+    uint64_t feedback_depth, max_tokens;                              /* decode feedback */
+    uint64_t max_state_activation_count, reservation_count;
+    char stream_id[64], execution_class_id[64], input_event_id[64];
+} nerve_b200_activation;
+typedef struct {
+    uint64_t logical_activation_index, block_id, block_activation_offset, block_activation_capacity;
+    int32_t allocated_block;
+    int64_t copy_from_block_id; /* -1 = none; else copy that block into block_id before the write */
+} nerve_b200_state_slot;
+
+int32_t nerve_b200_scheduler_create(nerve_b200_scheduler **out);
+int32_t nerve_b200_scheduler_destroy(nerve_b200_scheduler *scheduler);
+/* add_stream_with_state_declarations_and_execution_class (stream_runtime.rs:482-515); execution_class_id NULL = "default". */
+int32_t nerve_b200_scheduler_add_stream(nerve_b200_scheduler *scheduler, const char *stream_id, const char *execution_class_id,
+                                        const nerve_b200_state_declaration *declarations, size_t declaration_count,
+                                        nerve_b200_stream_snapshot *out);
+int32_t nerve_b200_scheduler_fork_stream(nerve_b200_scheduler *scheduler, const char *source_stream_id, const char *target_stream_id,
+                                         const char *execution_class_id, nerve_b200_stream_snapshot *out);
+int32_t nerve_b200_scheduler_enqueue(nerve_b200_scheduler *scheduler, const char *stream_id, const char *event_id,
+                                     const uint32_t *token_ids, size_t token_count, uint64_t max_public_tokens,
+                                     nerve_b200_stream_snapshot *out);
+int32_t nerve_b200_scheduler_interrupt(nerve_b200_scheduler *scheduler, const char *stream_id, const char *reason,
+                                       nerve_b200_stream_snapshot *out);
+int32_t nerve_b200_scheduler_reset_stream_state(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out);
+int32_t nerve_b200_scheduler_remove_stream(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out);
+int32_t nerve_b200_scheduler_close_after_current(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out);
+/* schedule_step (stream_runtime.rs:833-889).  The step stays inside the scheduler until the next schedule call;
+ * out_flags: bit 0 activation budget exhausted, bit 1 work budget exhausted, bit 2 idle. */
+int32_t nerve_b200_scheduler_schedule_step(nerve_b200_scheduler *scheduler, const nerve_b200_scheduler_budget *budget,
+                                           size_t *out_activation_count, int32_t *out_flags);
+/* Activation `index` of the last step; its prefill tokens go to out_token_ids (may be NULL). */
+int32_t nerve_b200_scheduler_step_activation(nerve_b200_scheduler *scheduler, size_t index, nerve_b200_activation *out,
+                                             uint32_t *out_token_ids, size_t max_token_ids);
+/* State reservation `reservation_index` of that activation: the state's key (two 64-byte buffers) and its slots. */
+int32_t nerve_b200_scheduler_step_reservation(nerve_b200_scheduler *scheduler, size_t activation_index, size_t reservation_index,
+                                              char *out_node_instance_id, char *out_state_id, nerve_b200_state_slot *out_slots,
+                                              size_t max_slots, size_t *out_slot_count);
+/* complete_activation (stream_runtime.rs:1032-1175).  processed_state_activation_count -1 = the activation's work units. */
+int32_t nerve_b200_scheduler_complete(nerve_b200_scheduler *scheduler, uint64_t activation_id, const uint32_t *generated_token_ids,
+                                      size_t generated_count, int32_t continue_generation, int64_t processed_state_activation_count,
+                                      nerve_b200_stream_snapshot *out);
+int32_t nerve_b200_scheduler_snapshot(nerve_b200_scheduler *scheduler, nerve_b200_scheduler_counts *out);
+int32_t nerve_b200_scheduler_stream_snapshot(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out);
+
 #ifdef __cplusplus
 }
 #endif

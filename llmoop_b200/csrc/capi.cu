@@ -6,6 +6,7 @@
 #include "../../include/nerve_b200.h"
 #include "engine.hpp"
 #include "state_abi.hpp"
+#include "stream_runtime.hpp"
 
 using namespace nerve;
 
@@ -17,6 +18,11 @@ struct nerve_b200_package {
 struct nerve_b200_engine {
     nerve_b200_package *package;
     std::unique_ptr<Engine> engine;
+};
+
+struct nerve_b200_scheduler {
+    nerve::runtime::StreamScheduler scheduler;
+    nerve::runtime::SchedulerStep step;  // the last schedule_step, read back by index
 };
 
 namespace {
@@ -44,6 +50,26 @@ int32_t cuda_status(cudaError_t status, const char *what) {
     if (status == cudaSuccess) return NERVE_B200_OK;
     last_error = std::string(what) + ": " + cudaGetErrorString(status);
     return NERVE_B200_ERROR;
+}
+
+void copy_text(char (&out)[64], const std::string &text) {
+    const size_t count = text.size() < 63 ? text.size() : 63;
+    std::memcpy(out, text.data(), count);
+    out[count] = 0;
+}
+
+void fill_snapshot(nerve_b200_stream_snapshot *out, const nerve::runtime::StreamSnapshot &snapshot) {
+    if (out == nullptr) return;
+    out->status = static_cast<int32_t>(snapshot.status);
+    out->queued_input_event_count = snapshot.queued_input_event_count;
+    out->in_flight_activation_count = snapshot.in_flight_activation_count;
+    out->completed_input_event_count = snapshot.completed_input_event_count;
+    out->scheduled_activation_count = snapshot.scheduled_activation_count;
+    out->generated_token_count = snapshot.generated_token_count;
+    out->transient_state_entry_count = snapshot.transient_state_entry_count;
+    out->transient_state_block_count = snapshot.transient_state_block_count;
+    out->transient_state_logical_activation_count = snapshot.transient_state_logical_activation_count;
+    copy_text(out->current_input_event_id, snapshot.current_input_event_id.value_or(""));
 }
 
 }  // namespace
@@ -521,6 +547,204 @@ int32_t nerve_b200_verify_prefix(const uint32_t *draft, size_t draft_count, cons
         out_counts[0] = static_cast<uint32_t>(accepted);
         out_counts[1] = static_cast<uint32_t>(committed);
         *out_emitted_count = count;
+    });
+}
+
+// ---- stream scheduler (host only) ----------------------------------------------------------------------------
+
+int32_t nerve_b200_scheduler_create(nerve_b200_scheduler **out) {
+    return guarded([&] {
+        require(out != nullptr, "out must not be NULL");
+        *out = new nerve_b200_scheduler();
+    });
+}
+
+int32_t nerve_b200_scheduler_destroy(nerve_b200_scheduler *scheduler) {
+    return guarded([&] { delete scheduler; });
+}
+
+int32_t nerve_b200_scheduler_add_stream(nerve_b200_scheduler *scheduler, const char *stream_id, const char *execution_class_id,
+                                        const nerve_b200_state_declaration *declarations, size_t declaration_count,
+                                        nerve_b200_stream_snapshot *out) {
+    return guarded([&] {
+        require(scheduler != nullptr && stream_id != nullptr, "scheduler and stream_id must not be NULL");
+        require(declaration_count == 0 || declarations != nullptr, "declarations must not be NULL");
+        nerve::runtime::StreamScheduler::Declarations list;
+        for (size_t i = 0; i < declaration_count; i++) {
+            const nerve_b200_state_declaration &d = declarations[i];
+            require(d.node_instance_id != nullptr && d.state_id != nullptr, "state key strings must not be NULL");
+            nerve::runtime::BlockShape shape = d.retention == 1 ? nerve::runtime::BlockShape::mutable_singleton(d.bytes_per_activation)
+                                                                : nerve::runtime::BlockShape::append(d.bytes_per_activation, d.activation_capacity);
+            require(d.retention == 0 || d.retention == 1, "retention must be 0 (append) or 1 (mutable singleton)");
+            if (d.maximum_activation_count != 0) shape = shape.with_maximum_activation_count(d.maximum_activation_count);
+            list.emplace_back(nerve::runtime::StateKey{d.node_instance_id, d.state_id}, shape);
+        }
+        fill_snapshot(out, scheduler->scheduler.add_stream(stream_id, execution_class_id ? execution_class_id : "default", list));
+    });
+}
+
+int32_t nerve_b200_scheduler_fork_stream(nerve_b200_scheduler *scheduler, const char *source_stream_id, const char *target_stream_id,
+                                         const char *execution_class_id, nerve_b200_stream_snapshot *out) {
+    return guarded([&] {
+        require(scheduler != nullptr && source_stream_id != nullptr && target_stream_id != nullptr && execution_class_id != nullptr,
+                "scheduler and ids must not be NULL");
+        fill_snapshot(out, scheduler->scheduler.fork_stream_transient_state(source_stream_id, target_stream_id, execution_class_id));
+    });
+}
+
+int32_t nerve_b200_scheduler_enqueue(nerve_b200_scheduler *scheduler, const char *stream_id, const char *event_id,
+                                     const uint32_t *token_ids, size_t token_count, uint64_t max_public_tokens,
+                                     nerve_b200_stream_snapshot *out) {
+    return guarded([&] {
+        require(scheduler != nullptr && stream_id != nullptr && event_id != nullptr, "scheduler and ids must not be NULL");
+        require(token_count == 0 || token_ids != nullptr, "token_ids must not be NULL");
+        nerve::runtime::InputEvent event;
+        event.id = event_id;
+        event.token_ids.assign(token_ids, token_ids + token_count);
+        event.max_public_tokens = max_public_tokens;
+        fill_snapshot(out, scheduler->scheduler.enqueue_input_event(stream_id, event));
+    });
+}
+
+int32_t nerve_b200_scheduler_interrupt(nerve_b200_scheduler *scheduler, const char *stream_id, const char *reason,
+                                       nerve_b200_stream_snapshot *out) {
+    return guarded([&] {
+        require(scheduler != nullptr && stream_id != nullptr && reason != nullptr, "scheduler, stream_id and reason must not be NULL");
+        fill_snapshot(out, scheduler->scheduler.interrupt_stream(stream_id, reason));
+    });
+}
+
+int32_t nerve_b200_scheduler_reset_stream_state(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out) {
+    return guarded([&] {
+        require(scheduler != nullptr && stream_id != nullptr, "scheduler and stream_id must not be NULL");
+        fill_snapshot(out, scheduler->scheduler.reset_stream_transient_state(stream_id));
+    });
+}
+
+int32_t nerve_b200_scheduler_remove_stream(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out) {
+    return guarded([&] {
+        require(scheduler != nullptr && stream_id != nullptr, "scheduler and stream_id must not be NULL");
+        fill_snapshot(out, scheduler->scheduler.remove_stream(stream_id));
+    });
+}
+
+int32_t nerve_b200_scheduler_close_after_current(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out) {
+    return guarded([&] {
+        require(scheduler != nullptr && stream_id != nullptr, "scheduler and stream_id must not be NULL");
+        fill_snapshot(out, scheduler->scheduler.close_stream_after_current(stream_id));
+    });
+}
+
+int32_t nerve_b200_scheduler_schedule_step(nerve_b200_scheduler *scheduler, const nerve_b200_scheduler_budget *budget,
+                                           size_t *out_activation_count, int32_t *out_flags) {
+    return guarded([&] {
+        require(scheduler != nullptr && budget != nullptr, "scheduler and budget must not be NULL");
+        nerve::runtime::SchedulerBudget limits(budget->max_activations, budget->max_prefill_tokens_per_activation, budget->max_work_units);
+        limits.max_decode_tokens_per_activation = budget->max_decode_tokens_per_activation;
+        scheduler->step = scheduler->scheduler.schedule_step(limits);
+        if (out_activation_count) *out_activation_count = scheduler->step.activations.size();
+        if (out_flags)
+            *out_flags = (scheduler->step.exhausted_activation_budget ? 1 : 0) | (scheduler->step.exhausted_work_budget ? 2 : 0) |
+                         (scheduler->step.idle ? 4 : 0);
+    });
+}
+
+int32_t nerve_b200_scheduler_step_activation(nerve_b200_scheduler *scheduler, size_t index, nerve_b200_activation *out,
+                                             uint32_t *out_token_ids, size_t max_token_ids) {
+    return guarded([&] {
+        require(scheduler != nullptr && out != nullptr, "scheduler and out must not be NULL");
+        require(index < scheduler->step.activations.size(), "activation index is outside the last step");
+        const nerve::runtime::Activation &activation = scheduler->step.activations[index];
+        out->id = activation.id;
+        out->kind = static_cast<int32_t>(activation.kind);
+        out->token_offset = activation.token_offset;
+        out->token_count = activation.token_ids.size();
+        out->remaining_prompt_token_count = activation.remaining_prompt_token_count;
+        out->feedback_depth = activation.feedback_depth;
+        out->max_tokens = activation.max_tokens;
+        out->max_state_activation_count = activation.max_state_activation_count;
+        out->reservation_count = activation.state_reservations.size();
+        copy_text(out->stream_id, activation.stream_id);
+        copy_text(out->execution_class_id, activation.execution_class_id);
+        copy_text(out->input_event_id, activation.input_event_id);
+        if (out_token_ids != nullptr) {
+            require(max_token_ids >= activation.token_ids.size(), "out_token_ids is too small for the chunk");
+            std::memcpy(out_token_ids, activation.token_ids.data(), activation.token_ids.size() * sizeof(uint32_t));
+        }
+    });
+}
+
+int32_t nerve_b200_scheduler_step_reservation(nerve_b200_scheduler *scheduler, size_t activation_index, size_t reservation_index,
+                                              char *out_node_instance_id, char *out_state_id, nerve_b200_state_slot *out_slots,
+                                              size_t max_slots, size_t *out_slot_count) {
+    return guarded([&] {
+        require(scheduler != nullptr, "scheduler must not be NULL");
+        require(activation_index < scheduler->step.activations.size(), "activation index is outside the last step");
+        const nerve::runtime::Activation &activation = scheduler->step.activations[activation_index];
+        require(reservation_index < activation.state_reservations.size(), "reservation index is outside the activation");
+        const nerve::runtime::StateReservation &reservation = activation.state_reservations[reservation_index];
+        char text[64];
+        if (out_node_instance_id) {
+            copy_text(text, reservation.key.node_instance_id);
+            std::memcpy(out_node_instance_id, text, 64);
+        }
+        if (out_state_id) {
+            copy_text(text, reservation.key.state_id);
+            std::memcpy(out_state_id, text, 64);
+        }
+        if (out_slot_count) *out_slot_count = reservation.slots.size();
+        if (out_slots != nullptr) {
+            require(max_slots >= reservation.slots.size(), "out_slots is too small for the reservation");
+            for (size_t i = 0; i < reservation.slots.size(); i++) {
+                const nerve::runtime::StateSlot &slot = reservation.slots[i];
+                out_slots[i].logical_activation_index = slot.logical_activation_index;
+                out_slots[i].block_id = slot.block_id;
+                out_slots[i].block_activation_offset = slot.block_activation_offset;
+                out_slots[i].block_activation_capacity = slot.block_activation_capacity;
+                out_slots[i].allocated_block = slot.allocated_block ? 1 : 0;
+                out_slots[i].copy_from_block_id = slot.copy_from_block_id ? static_cast<int64_t>(*slot.copy_from_block_id) : -1;
+            }
+        }
+    });
+}
+
+int32_t nerve_b200_scheduler_complete(nerve_b200_scheduler *scheduler, uint64_t activation_id, const uint32_t *generated_token_ids,
+                                      size_t generated_count, int32_t continue_generation, int64_t processed_state_activation_count,
+                                      nerve_b200_stream_snapshot *out) {
+    return guarded([&] {
+        require(scheduler != nullptr, "scheduler must not be NULL");
+        require(generated_count == 0 || generated_token_ids != nullptr, "generated_token_ids must not be NULL");
+        nerve::runtime::ActivationOutcome outcome;
+        outcome.generated_token_ids.assign(generated_token_ids, generated_token_ids + generated_count);
+        outcome.continue_generation = continue_generation != 0;
+        if (processed_state_activation_count >= 0) outcome.processed_state_activation_count = static_cast<size_t>(processed_state_activation_count);
+        fill_snapshot(out, scheduler->scheduler.complete_activation(activation_id, outcome));
+    });
+}
+
+int32_t nerve_b200_scheduler_snapshot(nerve_b200_scheduler *scheduler, nerve_b200_scheduler_counts *out) {
+    return guarded([&] {
+        require(scheduler != nullptr && out != nullptr, "scheduler and out must not be NULL");
+        const nerve::runtime::SchedulerSnapshot snapshot = scheduler->scheduler.snapshot();
+        out->stream_count = snapshot.stream_count;
+        out->active_stream_count = snapshot.active_stream_count;
+        out->in_flight_activation_count = snapshot.in_flight_activation_count;
+        out->allocated_block_count = snapshot.transient_state_arena.allocated_block_count;
+        out->free_block_count = snapshot.transient_state_arena.free_block_count;
+        out->live_block_count = snapshot.transient_state_arena.live_block_count;
+    });
+}
+
+int32_t nerve_b200_scheduler_stream_snapshot(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out) {
+    return guarded([&] {
+        require(scheduler != nullptr && stream_id != nullptr && out != nullptr, "scheduler, stream_id and out must not be NULL");
+        const nerve::runtime::SchedulerSnapshot snapshot = scheduler->scheduler.snapshot();
+        for (const nerve::runtime::StreamSnapshot &stream : snapshot.streams)
+            if (stream.stream_id == stream_id) {
+                fill_snapshot(out, stream);
+                return;
+            }
+        throw std::runtime_error(std::string("unknown stream \"") + stream_id + "\"");
     });
 }
 

@@ -73,6 +73,12 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_op_linear_bf16", "nerve_b200_op_rms_norm", "nerve_b200_op_linear_fp8",
     "nerve_b200_op_greedy", "nerve_b200_op_greedy_scratch_bytes", "nerve_b200_op_greedy_static", "nerve_b200_op_sample_top_k_top_p", "nerve_b200_op_sample_scratch_bytes", "nerve_b200_verify_prefix",
     "nerve_b200_stream_control_bytes", "nerve_b200_state_page_table_bytes",
+    "nerve_b200_scheduler_create", "nerve_b200_scheduler_destroy", "nerve_b200_scheduler_add_stream",
+    "nerve_b200_scheduler_fork_stream", "nerve_b200_scheduler_enqueue", "nerve_b200_scheduler_interrupt",
+    "nerve_b200_scheduler_reset_stream_state", "nerve_b200_scheduler_remove_stream",
+    "nerve_b200_scheduler_close_after_current", "nerve_b200_scheduler_schedule_step",
+    "nerve_b200_scheduler_step_activation", "nerve_b200_scheduler_step_reservation", "nerve_b200_scheduler_complete",
+    "nerve_b200_scheduler_snapshot", "nerve_b200_scheduler_stream_snapshot",
 )
 
 _library = None
