@@ -271,6 +271,7 @@ def main():
     # the same calls and meets the others in the all-reduces).  NERVE_B200_BENCH_REPLICAS=1 instead runs one
     # independent stream per GPU on replicated weights (weak scaling, no collective on the data path).
     tensor_parallel = world > 1 and os.environ.get("NERVE_B200_BENCH_REPLICAS", "0") != "1"
+    peer_exchange = tensor_parallel and os.environ.get("NERVE_B200_TP_EXCHANGE", "1") != "0"
     prompt = prompt_tokens(spec.vocab, seed=0 if tensor_parallel else rank)
 
     # natural-mode budget: one token per cycle when no draft is accepted, up to k+1 when all are
@@ -287,6 +288,11 @@ def main():
             unique_id.copy_(torch.frombuffer(bytearray(nb.tensor_parallel_unique_id()), dtype=torch.uint8))
         dist.broadcast(unique_id, src=0)
         engine.init_tensor_parallel(rank, world, bytes(unique_id.cpu().numpy().tobytes()))
+        if peer_exchange:  # the persistent kernel's exchange over peer memory: handles travel through the process group
+            mine = torch.frombuffer(bytearray(engine.tp_exchange_handle()), dtype=torch.uint8).cuda()
+            handles = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
+            dist.all_gather(handles, mine)
+            engine.tp_connect([bytes(handle.cpu().numpy().tobytes()) for handle in handles])
     engine.set_prefill_chunk(PROMPT_TOKENS)
     engine.add_stream(0, seed=0, speculative_draft_tokens=DRAFTS)
 
@@ -322,7 +328,7 @@ def main():
     profiled, _ = timed_cycles(engine, 0, prompt, budget, warmup, min(steps, 16), None, barrier)
     engine.set_profiling(False)
 
-    stack_kernel = bool(info["target_decode_stack"]) and os.environ.get("NERVE_B200_DECODE_STACK", "1") != "0" and not tensor_parallel
+    stack_kernel = bool(info["target_decode_stack"]) and os.environ.get("NERVE_B200_DECODE_STACK", "1") != "0" and (not tensor_parallel or peer_exchange)
 
     def reduce_max(value):
         if world == 1:
@@ -354,7 +360,8 @@ def main():
         "metric": METRIC, "value": tokens / seconds, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": 1e3 * seconds / steps, "higher_is_better": True, "scaling": "strong" if tensor_parallel else "weak", "vs_baseline": None,
         "dtype": "int4 weights, bf16 activations, f32 accumulate", "data": "synthetic",
-        "config": {**config, "parallelism": (f"tp{world}: dense layers sharded by rows / columns, 2 NCCL all-reduces per layer" if tensor_parallel
+        "config": {**config, "parallelism": ((f"tp{world}: dense layers sharded by rows / columns, partial sums exchanged over peer memory inside the persistent kernel"
+                                               if peer_exchange else f"tp{world}: dense layers sharded by rows / columns, 2 NCCL all-reduces per layer") if tensor_parallel
                                               else "replicated streams (one per GPU)") if world > 1 else "single GPU",
                    "capacity_tokens": capacity},
         "modes": {

@@ -165,6 +165,18 @@ int32_t nerve_b200_tp_unique_id(const char *nccl_library_path, uint8_t *out_128_
 int32_t nerve_b200_tp_shard_range(int64_t total, int64_t unit, int32_t rank, int32_t size, int64_t *out_begin, int64_t *out_count);
 int32_t nerve_b200_engine_init_tp(nerve_b200_engine *engine, const char *nccl_library_path, int32_t rank, int32_t size,
                                   const uint8_t *unique_id_128_bytes);
+/* Exchange inside the persistent decode kernel (no reference counterpart; the reference shards through shared host
+ * memory, vulkan_distributed/planning.rs:180-528).  Every rank calls ..._tp_exchange_handle (allocates its exchange
+ * buffer, returns the 64-byte inter-process memory handle), the handles travel to every rank by any transport, and
+ * ..._tp_connect(handles of ranks 0..size-1, in rank order, own included) maps the peers' buffers over NVLink.  From
+ * then on batches of at most 8 lanes run the persistent kernel on every rank: the o and down projections write their
+ * f32 partial sums into every rank's buffer with plain peer stores, all CTAs of all ranks meet at a barrier of
+ * system-scope atomics with bounded waits, and each rank adds the partials up in rank order.  Larger batches keep
+ * the NCCL path of nerve_b200_engine_init_tp, which is still required.  The ranks must issue the same calls in the
+ * same order; a rank that stays away ends the others' launches with the barrier-timeout error, after which the
+ * engines of the group have to be created anew. */
+int32_t nerve_b200_engine_tp_exchange_handle(nerve_b200_engine *engine, uint8_t *out_64_bytes);
+int32_t nerve_b200_engine_tp_connect(nerve_b200_engine *engine, const uint8_t *handles_64_bytes_each, int32_t count);
 /* Batches of at most 8 lanes of a dense INT4 g128 layer stack (the verify batch, draft and single-tick steps) run
  * as one persistent kernel per stack; 0 selects the kernel-per-operator path for them as well.  Default on
  * (NERVE_B200_DECODE_STACK=0 in the environment turns it off).  No counterpart in the reference: its Vulkan

@@ -267,6 +267,20 @@ int32_t nerve_b200_engine_init_tp(nerve_b200_engine *engine, const char *nccl_li
     });
 }
 
+int32_t nerve_b200_engine_tp_exchange_handle(nerve_b200_engine *engine, uint8_t *out_64_bytes) {
+    return guarded([&] {
+        require(engine && out_64_bytes, "null argument");
+        engine->engine->tp_exchange_handle(out_64_bytes);
+    });
+}
+
+int32_t nerve_b200_engine_tp_connect(nerve_b200_engine *engine, const uint8_t *handles_64_bytes_each, int32_t count) {
+    return guarded([&] {
+        require(engine && handles_64_bytes_each, "null argument");
+        engine->engine->tp_connect(handles_64_bytes_each, count);
+    });
+}
+
 int32_t nerve_b200_engine_set_decode_stack(nerve_b200_engine *engine, int32_t enabled) {
     return guarded([&] {
         require(engine != nullptr, "null engine");

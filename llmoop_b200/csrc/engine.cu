@@ -555,11 +555,12 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
 Engine::~Engine() {
     cudaStreamSynchronize(cuda_stream_);
     if (nccl_comm_ != nullptr) g_nccl.comm_destroy(nccl_comm_);
+    for (void *mapping : tp_peer_mappings_) cudaIpcCloseMemHandle(mapping);
     set_int4_error_flag(nullptr);
     for (auto &entry : signals_) cudaFree(entry.second.ptr);
     for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
                                  &records_, &argmax_scratch_, &sampler_scratch_, &sampler_table_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
-                                 &cycle_state_, &kernel_error_, &tp_partial_, &stack_q_, &stack_attention_out_, &stack_activation_, &stack_barrier_, &stack_timing_})
+                                 &cycle_state_, &kernel_error_, &tp_partial_, &tp_exchange_, &tp_description_, &stack_q_, &stack_attention_out_, &stack_activation_, &stack_barrier_, &stack_timing_})
         cudaFree(buffer->ptr);
     cudaFreeHost(staging_);
     cudaFreeHost(host_records_);
@@ -595,6 +596,48 @@ void Engine::init_tensor_parallel(const std::string &library, int rank, int size
     using InitByValue = int (*)(void **, int, NcclId, int);
     int result = reinterpret_cast<InitByValue>(g_nccl.comm_init_rank)(&nccl_comm_, size, id, rank);
     if (result != 0) fail(std::string("ncclCommInitRank: ") + g_nccl.get_error_string(result));
+}
+
+namespace {
+size_t tp_exchange_bytes(int size, size_t hidden) { return stack_tp_exchange_floats(size, static_cast<int>(hidden)) * sizeof(float); }
+}  // namespace
+
+void Engine::tp_exchange_handle(uint8_t *out_64_bytes) {
+    const MountOptions &options = model_->options();
+    if (options.tp_size <= 1) fail("this package was not mounted as a tensor-parallel shard");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "inter-process memory handles are 64 bytes");
+    cuda_check(cudaSetDevice(options.device), "cudaSetDevice");
+    if (!tp_exchange_.ptr) tp_exchange_ = device_alloc(tp_exchange_bytes(options.tp_size, model_->plan().hidden) + 256);  // zeroed
+    cudaIpcMemHandle_t handle;
+    cuda_check(cudaIpcGetMemHandle(&handle, tp_exchange_.ptr), "cudaIpcGetMemHandle");
+    std::memcpy(out_64_bytes, &handle, sizeof(handle));
+}
+
+void Engine::tp_connect(const uint8_t *handles_64_bytes_each, int count) {
+    const MountOptions &options = model_->options();
+    if (count != options.tp_size || count > STACK_TP_MAX_RANKS) fail("tp_connect needs one handle per rank of the mounted group (at most 8)");
+    if (!tp_exchange_.ptr) fail("call tp_exchange_handle before tp_connect");
+    if (tp_connected_) fail("the tensor-parallel exchange is already connected");
+    cuda_check(cudaSetDevice(options.device), "cudaSetDevice");
+    const size_t floats = stack_tp_exchange_floats(options.tp_size, static_cast<int>(model_->plan().hidden));
+    StackTp description;
+    description.rank = options.tp_rank;
+    description.size = options.tp_size;
+    for (int r = 0; r < count; r++) {
+        void *base = tp_exchange_.ptr;
+        if (r != options.tp_rank) {
+            cudaIpcMemHandle_t handle;
+            std::memcpy(&handle, handles_64_bytes_each + static_cast<size_t>(r) * 64, sizeof(handle));
+            cuda_check(cudaIpcOpenMemHandle(&base, handle, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle (is peer access between the GPUs available?)");
+            tp_peer_mappings_.push_back(base);
+        }
+        description.exchange[r] = static_cast<float *>(base);
+        description.counter[r] = reinterpret_cast<unsigned long long *>(static_cast<float *>(base) + floats);
+    }
+    description.base = description.counter[options.tp_rank] + 1;
+    tp_description_ = device_alloc(sizeof(StackTp));
+    cuda_check(cudaMemcpy(tp_description_.ptr, &description, sizeof(description), cudaMemcpyHostToDevice), "exchange description upload");
+    tp_connected_ = true;
 }
 
 void Engine::tp_all_reduce(float *values, size_t count) {
@@ -1177,7 +1220,8 @@ void Engine::run_phase(const std::vector<int> &key, const std::function<void()> 
 // Runs a whole layer stack over `hidden` ([lanes][hidden], in place) with the persistent decode kernel when the
 // stack and the batch qualify; false = the caller runs the layers kernel by kernel.
 bool Engine::run_stack(const StackPlan &stack, int lanes, void *hidden) {
-    if (model_->options().tp_size > 1) return false;  // the persistent kernel has no all-reduce inside (yet)
+    const int tp_size = model_->options().tp_size;
+    if (tp_size > 1 && !tp_connected_) return false;  // without the peer exchange the shards meet in NCCL all-reduces, kernel by kernel
     if (!stack_enabled_ || !stack.available || lanes < 1 || lanes > 8 || current_width_ <= 0 || lanes % current_width_ != 0) return false;
     size_t smem = 0;
     if (!decode_stack_supported(stack.shape, lanes, &smem)) return false;
@@ -1192,7 +1236,8 @@ bool Engine::run_stack(const StackPlan &stack, int lanes, void *hidden) {
     buffers.timing = (profile_ && &stack == &model_->target_stack()) ? static_cast<unsigned long long *>(stack_timing_.ptr) : nullptr;
     profile_begin(stack.weight_bytes);
     check(launch_decode_stack(static_cast<const StackLayer *>(stack.device_layers.ptr), static_cast<int>(stack.layers.size()), stack.shape,
-                              buffers, current_lanes_, lanes, current_width_, split_tokens_, current_splits_, cuda_stream_),
+                              buffers, current_lanes_, lanes, current_width_, split_tokens_, current_splits_, cuda_stream_,
+                              static_cast<const StackTp *>(tp_description_.ptr), tp_size),
           "decode stack");
     profile_end();
     return true;

@@ -189,6 +189,13 @@ public:
     // from tensor_parallel_unique_id and passed to the other ranks.
     static void tensor_parallel_unique_id(const std::string &library, uint8_t *out_128_bytes);
     void init_tensor_parallel(const std::string &library, int rank, int size, const uint8_t *unique_id_128_bytes);
+    // Exchange inside the persistent decode kernel (no NCCL on that path): every rank allocates an exchange buffer
+    // and hands out its 64-byte inter-process memory handle (tp_exchange_handle); once it has everybody's handles
+    // (rank order, its own included) tp_connect maps the peers' buffers and the decode stack kernel then adds the
+    // partial sums of the o and down projections up over peer memory.  Without it tensor-parallel batches run kernel
+    // by kernel with NCCL all-reduces.
+    void tp_exchange_handle(uint8_t *out_64_bytes);
+    void tp_connect(const uint8_t *handles_64_bytes_each, int count);
 
     uint64_t stream_tick(int64_t id) const;
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
@@ -292,6 +299,10 @@ private:
     DeviceBuffer kernel_error_;             // device word set by pipelined kernels whose bounded waits expired
     DeviceBuffer tp_partial_;               // f32 [max_lanes][hidden] partial sums of row-parallel linears
     void *nccl_library_ = nullptr, *nccl_comm_ = nullptr;
+    DeviceBuffer tp_exchange_;              // this rank's exchange buffer + arrival counter + consumed-arrivals word
+    DeviceBuffer tp_description_;           // StackTp in device memory
+    std::vector<void *> tp_peer_mappings_;  // opened peer handles
+    bool tp_connected_ = false;
     void tp_all_reduce(float *values, size_t count);
     // persistent decode stack workspaces ([8 lanes][width]) and its two barrier words
     DeviceBuffer stack_q_, stack_attention_out_, stack_activation_, stack_barrier_, stack_timing_;

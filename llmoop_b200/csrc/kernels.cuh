@@ -151,6 +151,20 @@ struct StackBuffers {
     int *error_flag;             // set when a bounded barrier wait expires
     unsigned long long *timing;  // optional [layers][32] nanosecond stamps of CTA 0 (phase boundaries), or nullptr
 };
+// Tensor-parallel exchange of the persistent kernel: every rank holds the same residual stream and its shard of
+// each layer; the o and down projections leave f32 partial sums that every rank writes into every rank's exchange
+// buffer (peer memory, plain stores), all CTAs of all ranks meet at a barrier made of one counter per GPU that the
+// others bump with system-scope atomics, and every rank adds the partials up in rank order.
+// Exchange buffer of a rank: [2 parities][size sources][8 lanes][hidden] f32.
+constexpr int STACK_TP_MAX_RANKS = 8;
+struct StackTp {
+    int rank = 0, size = 1;                            // size 1: no exchange
+    float *exchange[STACK_TP_MAX_RANKS] = {};          // every rank's buffer as seen from this GPU (own entry: local memory)
+    unsigned long long *counter[STACK_TP_MAX_RANKS] = {};  // every rank's arrival counter, only ever added to
+    unsigned long long *base = nullptr;                // this rank's count of arrivals consumed by earlier launches
+};
+inline size_t stack_tp_exchange_floats(int size, int hidden) { return static_cast<size_t>(2) * size * 8 * hidden; }
+
 // One source matrix of a tile-major copy.  rope_head_width > 0 orders the rows of every head so that MMA rows
 // r and r + 8 of a tile are the rotary partners (d, d + head_width / 2).
 struct RelayoutSegment {
@@ -167,7 +181,7 @@ cudaError_t launch_int4_tile_major(const RelayoutSegment *segments, int count, b
 bool decode_stack_supported(const StackShape &shape, int lanes, size_t *smem_bytes);
 cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count, const StackShape &shape,
                                 const StackBuffers &buffers, const LaneTable &lanes_meta, int lanes, int lanes_per_stream,
-                                int split_tokens, int max_splits, cudaStream_t stream);
+                                int split_tokens, int max_splits, cudaStream_t stream, const StackTp *tp_device = nullptr, int tp_size = 1);
 
 // Tensor-parallel row-parallel linears: out = bf16(bf16(sum) + residual) (or bf16(sum) without residual) from the
 // all-reduced f32 sums [count].

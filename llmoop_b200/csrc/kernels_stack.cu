@@ -148,6 +148,66 @@ __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int
     __syncthreads();
 }
 
+// All CTAs of all tensor-parallel ranks meet here.  Every CTA bumps the arrival counter of every rank (its own and,
+// through peer memory, the others'); the counters only grow, `target` is the value this rank's counter reaches when
+// every CTA of every rank has arrived.  What the CTA wrote into the peers' exchange buffers before the call is
+// visible to them after it.  The wait is bounded like the grid barrier's; a rank that never shows up ends the
+// launch with the error flag set.
+constexpr unsigned int EXCHANGE_SPIN_LIMIT = 1u << 22;
+__device__ __noinline__ void exchange_barrier(const StackTp &tp, unsigned long long &target, int *error_flag) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        target += static_cast<unsigned long long>(gridDim.x) * tp.size;
+        __threadfence_system();
+        for (int r = 0; r < tp.size; r++)
+            asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(tp.counter[r]) : "memory");
+        unsigned int spins = 0;
+        while (true) {
+            unsigned long long seen;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(tp.counter[tp.rank]) : "memory");
+            if (seen >= target) break;
+            if (++spins > EXCHANGE_SPIN_LIMIT) {
+                atomicExch(error_flag, 2);
+                break;
+            }
+            if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) break;
+            __nanosleep(64);
+        }
+        __threadfence_system();
+    }
+    __syncthreads();
+}
+
+// After an exchange: hidden = bf16(bf16(sum over ranks of the partial sums) + hidden) for this CTA's share of the
+// [lanes][width] elements, four at a time (add_bf16.comp.template:17-24 on the all-reduced linear output).  The
+// partials are added in rank order on every rank, so the replicated residual streams stay bit-identical.
+__device__ __noinline__ void reduce_exchanged(const StackTp &tp, int parity, uint16_t *hidden, int lanes, int width) {
+    const int per_lane = width >> 2, items = lanes * per_lane;
+    const float4 *mine = reinterpret_cast<const float4 *>(tp.exchange[tp.rank]) + static_cast<size_t>(parity) * tp.size * 8 * per_lane;
+    for (int item = blockIdx.x * STACK_THREADS + threadIdx.x; item < items; item += gridDim.x * STACK_THREADS) {
+        const int m = item / per_lane, quad = item - m * per_lane;
+        float4 part[STACK_TP_MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < STACK_TP_MAX_RANKS; r++)
+            if (r < tp.size) part[r] = __ldcg(mine + (static_cast<size_t>(r) * 8 + m) * per_lane + quad);
+        uint2 *destination = reinterpret_cast<uint2 *>(hidden) + static_cast<size_t>(m) * per_lane + quad;
+        const uint2 residual = __ldcg(destination);
+        float4 sum = part[0];
+#pragma unroll
+        for (int r = 1; r < STACK_TP_MAX_RANKS; r++)
+            if (r < tp.size) {
+                sum.x += part[r].x;
+                sum.y += part[r].y;
+                sum.z += part[r].z;
+                sum.w += part[r].w;
+            }
+        uint2 out;
+        out.x = pack_bf16(round_bf16(sum.x) + bf16_lo(residual.x), round_bf16(sum.y) + bf16_hi(residual.x));
+        out.y = pack_bf16(round_bf16(sum.z) + bf16_lo(residual.y), round_bf16(sum.w) + bf16_hi(residual.y));
+        *destination = out;
+    }
+}
+
 // Shared-memory carve-up of the matrix phases.
 struct StackSmem {
     uint4 *fragments;    // [groups][4 words][staged lanes][4] activations in B-fragment order
@@ -752,6 +812,8 @@ struct StackArgs {
     LaneTable lanes_meta;
     int lanes, lanes_per_stream, split_tokens, max_splits;
     int ring_units, l2_prefetch;
+    const StackTp *tp;  // device copy of the exchange description, or nullptr (single GPU)
+    int tp_size;
 };
 
 struct StackSmemLayout {
@@ -850,7 +912,8 @@ struct AttentionTeam {
     static constexpr int QL = GROUP >= 8 ? 2 : (GROUP >= 4 ? 4 : (16 / GROUP > 8 ? 8 : 16 / GROUP));
 };
 
-template <int HD, int GROUP>
+// EXCHANGE: the tensor-parallel form (o and down leave partial sums that are exchanged between the ranks).
+template <int HD, int GROUP, bool EXCHANGE>
 __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const StackArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     constexpr int QL = AttentionTeam<GROUP>::QL;
@@ -868,6 +931,10 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
 
     const int q_width = shape.q_heads * HD, q_tiles = q_width >> 4, k_tiles = (shape.kv_heads * HD) >> 4;
     unsigned int target = 0;
+    constexpr bool exchanging = EXCHANGE;
+    unsigned long long exchange_target = 0ull;  // arrivals that earlier launches consumed
+    if constexpr (EXCHANGE) exchange_target = *a.tp->base;
+    int exchange_parity = 0;
     unsigned int *counter = a.buffers.barrier;
     int *error_flag = a.buffers.error_flag;
     int parity = 0, phase = 0;
@@ -995,7 +1062,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                             const int local = tile < q_tiles ? tile : tile - q_tiles;
                             payload = __ldg(rope_row + 8 * (local % (HD >> 4)) + (epilogue_row & 7));
                         }
-                    } else if (step != 2) {
+                    } else if (step != 2 && !exchanging) {
                         payload = __ldcg(a.buffers.hidden + static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row);
                     }
                 }
@@ -1049,6 +1116,11 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                             // silu_multiply_bf16.comp.template:30-52: bf16(silu_bf16(bf16 gate) * bf16 up)
                             a.buffers.activation[static_cast<size_t>(epilogue_m) * shape.ffn + tile * 16 + epilogue_row] =
                                 static_cast<uint16_t>(f32_to_bf16_bits(rounded_silu(round_bf16(first)) * round_bf16(second)));
+                        } else if constexpr (EXCHANGE) {
+                            // this rank's share of the sum over K, unrounded, into every rank's exchange buffer
+                            const size_t slot = ((static_cast<size_t>(exchange_parity) * a.tp_size + a.tp->rank) * 8 + epilogue_m) * shape.hidden +
+                                                tile * 16 + epilogue_row;
+                            for (int r = 0; r < a.tp_size; r++) a.tp->exchange[r][slot] = first;
                         } else {
                             // linear + residual_add (add_bf16.comp.template:17-24): bf16(bf16(product) + residual), in place
                             a.buffers.hidden[static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row] =
@@ -1059,6 +1131,13 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                 parity ^= 1;
             }
             stamp(layer, 4 * step + 2);
+            if constexpr (EXCHANGE) {
+              if (step == 1 || step == 3) {
+                exchange_barrier(*a.tp, exchange_target, error_flag);
+                reduce_exchanged(*a.tp, exchange_parity, a.buffers.hidden, lanes, shape.hidden);
+                exchange_parity ^= 1;
+              }
+            }
             grid_barrier(counter, target, error_flag);
             stamp(layer, 4 * step + 3);
 
@@ -1101,19 +1180,20 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
         if (gone == gridDim.x - 1) {
             counter[0] = 0u;
             counter[1] = 0u;
+            if constexpr (EXCHANGE) *a.tp->base = exchange_target;  // the next launch counts on from here
             __threadfence();
         }
     }
 }
 
-template <int HD, int GROUP>
-cudaError_t launch_instance(const StackArgs &args, size_t smem, cudaStream_t stream) {
+template <int HD, int GROUP, bool EXCHANGE>
+cudaError_t launch_instance_of(const StackArgs &args, size_t smem, cudaStream_t stream) {
     static int configured_device = -1, sm_count = 0;
     int device = 0;
     cudaError_t status = cudaGetDevice(&device);
     if (status != cudaSuccess) return status;
     if (configured_device != device) {
-        status = cudaFuncSetAttribute(decode_stack_kernel<HD, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        status = cudaFuncSetAttribute(decode_stack_kernel<HD, GROUP, EXCHANGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (status != cudaSuccess) return status;
         status = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
         if (status != cudaSuccess) return status;
@@ -1129,7 +1209,12 @@ cudaError_t launch_instance(const StackArgs &args, size_t smem, cudaStream_t str
     attribute[0].val.cooperative = 1;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, decode_stack_kernel<HD, GROUP>, args);
+    return cudaLaunchKernelEx(&config, decode_stack_kernel<HD, GROUP, EXCHANGE>, args);
+}
+
+template <int HD, int GROUP>
+cudaError_t launch_instance(const StackArgs &args, size_t smem, cudaStream_t stream) {
+    return args.tp_size > 1 ? launch_instance_of<HD, GROUP, true>(args, smem, stream) : launch_instance_of<HD, GROUP, false>(args, smem, stream);
 }
 
 bool instance_smem(const StackShape &shape, int lanes, size_t *bytes, int *ring_units) {
@@ -1184,7 +1269,7 @@ bool decode_stack_supported(const StackShape &shape, int lanes, size_t *smem_byt
 
 cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count, const StackShape &shape,
                                 const StackBuffers &buffers, const LaneTable &lanes_meta, int lanes, int lanes_per_stream,
-                                int split_tokens, int max_splits, cudaStream_t stream) {
+                                int split_tokens, int max_splits, cudaStream_t stream, const StackTp *tp_device, int tp_size) {
     size_t smem = 0;
     if (!decode_stack_supported(shape, lanes, &smem) || lanes_per_stream <= 0 || lanes % lanes_per_stream != 0 || layer_count < 1)
         return cudaErrorInvalidValue;
@@ -1198,6 +1283,9 @@ cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count
     args.lanes_per_stream = lanes_per_stream;
     args.split_tokens = split_tokens;
     args.max_splits = max_splits;
+    if (tp_size < 1 || tp_size > STACK_TP_MAX_RANKS || (tp_size > 1 && (tp_device == nullptr || shape.hidden % 4 != 0))) return cudaErrorInvalidValue;
+    args.tp = tp_size > 1 ? tp_device : nullptr;
+    args.tp_size = tp_size;
     instance_smem(shape, lanes, &smem, &args.ring_units);
     static const char *prefetch = getenv("NERVE_B200_STACK_L2_PREFETCH");
     args.l2_prefetch = (prefetch != nullptr && prefetch[0] == '1') ? 1 : 0;  // off: the tile loops are not HBM-bound (yet)

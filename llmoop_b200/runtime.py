@@ -66,7 +66,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_destroy", "nerve_b200_engine_add_stream", "nerve_b200_engine_fork_stream",
     "nerve_b200_engine_reset_stream", "nerve_b200_engine_remove_stream", "nerve_b200_engine_interrupt_stream",
     "nerve_b200_engine_enqueue", "nerve_b200_engine_run_until_idle", "nerve_b200_engine_run",
-    "nerve_b200_engine_set_profiling", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_init_tp", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
+    "nerve_b200_engine_set_profiling", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_init_tp", "nerve_b200_engine_tp_exchange_handle", "nerve_b200_engine_tp_connect", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
     "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair", "nerve_b200_set_int4_kernel",
@@ -242,6 +242,18 @@ class Engine:
     def init_tensor_parallel(self, rank: int, size: int, unique_id: bytes):
         buffer = (ctypes.c_uint8 * 128).from_buffer_copy(unique_id)
         _check(library().nerve_b200_engine_init_tp(self._handle, nccl_library_path().encode(), rank, size, buffer))
+
+    def tp_exchange_handle(self) -> bytes:
+        """This rank's 64-byte inter-process handle of its exchange buffer (see nerve_b200_engine_tp_connect)."""
+        buffer = (ctypes.c_uint8 * 64)()
+        _check(library().nerve_b200_engine_tp_exchange_handle(self._handle, buffer))
+        return bytes(buffer)
+
+    def tp_connect(self, handles) -> None:
+        """handles: every rank's tp_exchange_handle() in rank order (own included)."""
+        joined = b"".join(handles)
+        buffer = (ctypes.c_uint8 * len(joined)).from_buffer_copy(joined)
+        _check(library().nerve_b200_engine_tp_connect(self._handle, buffer, len(handles)))
 
     def set_decode_stack(self, enabled: bool):
         _check(library().nerve_b200_engine_set_decode_stack(self._handle, int(enabled)))

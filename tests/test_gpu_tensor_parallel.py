@@ -1,7 +1,8 @@
 """Tensor-parallel engine on two GPUs of one box (skipped where fewer are visible): each rank mounts its shard of a
 synthetic INT4 package, joins the NCCL group through the C ABI and runs the same stream; the ranks must emit the
 same tokens, and those must be the oracle's (sequences may part where the oracle's top-2 logit gap is below 2e-2:
-the ranks' partial sums are added in another order than one GPU's)."""
+the ranks' partial sums are added in another order than one GPU's).  Two forms: kernel by kernel with NCCL
+all-reduces, and the persistent decode kernel with its exchange over peer memory (far fewer launches)."""
 
 import os
 import pickle
@@ -13,13 +14,16 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
+LAUNCH_BOUND = {0: 700, 3: 1800}  # between the two forms' launch counts for the 20-token run below
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
 
 
-def _worker(rank, size, port, directory, prompt, drafts, out):
+def _worker(rank, size, port, directory, prompt, drafts, exchange, out):
     import torch
     import torch.distributed as dist
 
@@ -35,12 +39,16 @@ def _worker(rank, size, port, directory, prompt, drafts, out):
                          tp_rank=rank, tp_size=size)
     engine = nb.Engine(package)
     engine.init_tensor_parallel(rank, size, holder[0])
+    if exchange:
+        handles = [None] * size
+        dist.all_gather_object(handles, engine.tp_exchange_handle())
+        engine.tp_connect(handles)
     engine.set_cycle_logging(True)
     engine.add_stream(1, speculative_draft_tokens=drafts)
     tokens, report = engine.submit_input_event_until_idle(1, prompt, 20)
     accepted = [c["accepted"] for c in engine.cycle_log()]
     gathered = [None] * size
-    dist.all_gather_object(gathered, (tokens, accepted))
+    dist.all_gather_object(gathered, (tokens, accepted, report.kernel_launches))
     if rank == 0:
         out.put(pickle.dumps(gathered))
     engine.close()
@@ -48,8 +56,9 @@ def _worker(rank, size, port, directory, prompt, drafts, out):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", [False, True], ids=["nccl", "peer_exchange"])
 @pytest.mark.parametrize("drafts", [0, 3])
-def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, drafts):
+def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, drafts, exchange):
     import torch
     import torch.multiprocessing as mp
 
@@ -71,7 +80,7 @@ def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, drafts):
     context = mp.get_context("spawn")
     out = context.Queue()
     port = _free_port()
-    processes = [context.Process(target=_worker, args=(rank, 2, port, str(directory), prompt, drafts, out)) for rank in range(2)]
+    processes = [context.Process(target=_worker, args=(rank, 2, port, str(directory), prompt, drafts, exchange, out)) for rank in range(2)]
     for process in processes:
         process.start()
     try:
@@ -83,8 +92,11 @@ def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, drafts):
             if process.is_alive():
                 process.kill()
     gathered = pickle.loads(out.get(timeout=10))
-    assert gathered[0] == gathered[1]  # the ranks agree token for token
-    tokens, accepted = gathered[0]
+    assert gathered[0][:2] == gathered[1][:2]  # the ranks agree token for token
+    tokens, accepted, launches = gathered[0]
+    print(f"kernel launches: {launches}")
+    # kernel by kernel every layer is ~20 launches per forward; the persistent kernel is one per stack
+    assert (launches < LAUNCH_BOUND[drafts]) == exchange, launches
     for index, (got, want) in enumerate(zip(tokens, expected["tokens"])):
         if got != want:
             gap = oracle.top2_gap(expected["logits"][index])
