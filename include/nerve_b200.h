@@ -169,9 +169,9 @@ int32_t nerve_b200_engine_init_tp(nerve_b200_engine *engine, const char *nccl_li
  * memory, vulkan_distributed/planning.rs:180-528).  Every rank calls ..._tp_exchange_handle (allocates its exchange
  * buffer, returns the 64-byte inter-process memory handle), the handles travel to every rank by any transport, and
  * ..._tp_connect(handles of ranks 0..size-1, in rank order, own included) maps the peers' buffers over NVLink.  From
- * then on batches of at most 8 lanes run the persistent kernel on every rank: the o and down projections write their
- * f32 partial sums into every rank's buffer with plain peer stores, all CTAs of all ranks meet at a barrier of
- * system-scope atomics with bounded waits, and each rank adds the partials up in rank order.  Larger batches keep
+ * then on batches of at most 8 lanes run the persistent kernel on every rank: the o and down projections leave their
+ * f32 partial sums in the rank's own buffer, all CTAs of all ranks meet at a two-level barrier (local arrivals, one system-scope
+ * store per peer) with bounded waits, and each rank reads everybody's partials with plain peer loads and adds them up in rank order.  Larger batches keep
  * the NCCL path of nerve_b200_engine_init_tp, which is still required.  The ranks must issue the same calls in the
  * same order; a rank that stays away ends the others' launches with the barrier-timeout error, after which the
  * engines of the group have to be created anew. */

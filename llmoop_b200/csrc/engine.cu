@@ -599,7 +599,7 @@ void Engine::init_tensor_parallel(const std::string &library, int rank, int size
 }
 
 namespace {
-size_t tp_exchange_bytes(int size, size_t hidden) { return stack_tp_exchange_floats(size, static_cast<int>(hidden)) * sizeof(float); }
+size_t tp_exchange_bytes(size_t hidden) { return stack_tp_exchange_floats(static_cast<int>(hidden)) * sizeof(float); }
 }  // namespace
 
 void Engine::tp_exchange_handle(uint8_t *out_64_bytes) {
@@ -607,7 +607,7 @@ void Engine::tp_exchange_handle(uint8_t *out_64_bytes) {
     if (options.tp_size <= 1) fail("this package was not mounted as a tensor-parallel shard");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "inter-process memory handles are 64 bytes");
     cuda_check(cudaSetDevice(options.device), "cudaSetDevice");
-    if (!tp_exchange_.ptr) tp_exchange_ = device_alloc(tp_exchange_bytes(options.tp_size, model_->plan().hidden) + 256);  // zeroed
+    if (!tp_exchange_.ptr) tp_exchange_ = device_alloc(tp_exchange_bytes(model_->plan().hidden) + STACK_TP_CONTROL_BYTES);  // zeroed
     cudaIpcMemHandle_t handle;
     cuda_check(cudaIpcGetMemHandle(&handle, tp_exchange_.ptr), "cudaIpcGetMemHandle");
     std::memcpy(out_64_bytes, &handle, sizeof(handle));
@@ -619,7 +619,7 @@ void Engine::tp_connect(const uint8_t *handles_64_bytes_each, int count) {
     if (!tp_exchange_.ptr) fail("call tp_exchange_handle before tp_connect");
     if (tp_connected_) fail("the tensor-parallel exchange is already connected");
     cuda_check(cudaSetDevice(options.device), "cudaSetDevice");
-    const size_t floats = stack_tp_exchange_floats(options.tp_size, static_cast<int>(model_->plan().hidden));
+    const size_t floats = stack_tp_exchange_floats(static_cast<int>(model_->plan().hidden));
     StackTp description;
     description.rank = options.tp_rank;
     description.size = options.tp_size;
@@ -634,7 +634,6 @@ void Engine::tp_connect(const uint8_t *handles_64_bytes_each, int count) {
         description.exchange[r] = static_cast<float *>(base);
         description.counter[r] = reinterpret_cast<unsigned long long *>(static_cast<float *>(base) + floats);
     }
-    description.base = description.counter[options.tp_rank] + 1;
     tp_description_ = device_alloc(sizeof(StackTp));
     cuda_check(cudaMemcpy(tp_description_.ptr, &description, sizeof(description), cudaMemcpyHostToDevice), "exchange description upload");
     tp_connected_ = true;

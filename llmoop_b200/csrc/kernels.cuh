@@ -152,18 +152,18 @@ struct StackBuffers {
     unsigned long long *timing;  // optional [layers][32] nanosecond stamps of CTA 0 (phase boundaries), or nullptr
 };
 // Tensor-parallel exchange of the persistent kernel: every rank holds the same residual stream and its shard of
-// each layer; the o and down projections leave f32 partial sums that every rank writes into every rank's exchange
-// buffer (peer memory, plain stores), all CTAs of all ranks meet at a barrier made of one counter per GPU that the
-// others bump with system-scope atomics, and every rank adds the partials up in rank order.
-// Exchange buffer of a rank: [2 parities][size sources][8 lanes][hidden] f32.
+// each layer; the o and down projections leave f32 partial sums in the rank's own exchange buffer, all CTAs of all
+// ranks meet at a two-level barrier (local arrivals, then one system-scope store per peer over NVLink), and every
+// rank then reads everybody's partials (peer memory, plain loads) and adds them up in rank order.
+// Exchange buffer of a rank: [2 parities][8 lanes][hidden] f32.
 constexpr int STACK_TP_MAX_RANKS = 8;
 struct StackTp {
     int rank = 0, size = 1;                            // size 1: no exchange
     float *exchange[STACK_TP_MAX_RANKS] = {};          // every rank's buffer as seen from this GPU (own entry: local memory)
-    unsigned long long *counter[STACK_TP_MAX_RANKS] = {};  // every rank's arrival counter, only ever added to
-    unsigned long long *base = nullptr;                // this rank's count of arrivals consumed by earlier launches
+    unsigned long long *counter[STACK_TP_MAX_RANKS] = {};  // every rank's 16 control words (arrivals, go, consumed, peers' progress)
 };
-inline size_t stack_tp_exchange_floats(int size, int hidden) { return static_cast<size_t>(2) * size * 8 * hidden; }
+constexpr size_t STACK_TP_CONTROL_BYTES = 16 * sizeof(unsigned long long);
+inline size_t stack_tp_exchange_floats(int hidden) { return static_cast<size_t>(2) * 8 * hidden; }
 
 // One source matrix of a tile-major copy.  rope_head_width > 0 orders the rows of every head so that MMA rows
 // r and r + 8 of a tile are the rotary partners (d, d + head_width / 2).

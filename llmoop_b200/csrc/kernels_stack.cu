@@ -148,48 +148,90 @@ __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int
     __syncthreads();
 }
 
-// All CTAs of all tensor-parallel ranks meet here.  Every CTA bumps the arrival counter of every rank (its own and,
-// through peer memory, the others'); the counters only grow, `target` is the value this rank's counter reaches when
-// every CTA of every rank has arrived.  What the CTA wrote into the peers' exchange buffers before the call is
-// visible to them after it.  The wait is bounded like the grid barrier's; a rank that never shows up ends the
-// launch with the error flag set.
+// All CTAs of all tensor-parallel ranks meet here, in two levels: the CTAs of this GPU count themselves in on a
+// local word; the last one to arrive tells every peer (one system-scope store of the exchange number per peer, over
+// NVLink), waits until every peer has told it the same, and lets the local CTAs go.  One remote write per peer and
+// exchange: arrivals of 148 CTAs on one remote word would queue up on the link.  `exchange_number` counts the
+// exchanges of this and all earlier launches; all words only grow.  What the CTAs wrote into their rank's exchange
+// buffer before the call is visible to the peers after it.  Every wait is bounded; a rank that never shows up ends
+// the launch with the error flag set.
+// Control words of a rank (unsigned long long, behind its exchange buffer): [0] local arrivals, [1] go,
+// [2] exchanges consumed by earlier launches, [8 + s] the exchange number rank s has reached.
 constexpr unsigned int EXCHANGE_SPIN_LIMIT = 1u << 22;
-__device__ __noinline__ void exchange_barrier(const StackTp &tp, unsigned long long &target, int *error_flag) {
+constexpr int TP_WORD_ARRIVALS = 0, TP_WORD_GO = 1, TP_WORD_CONSUMED = 2, TP_WORD_PEER = 8;
+
+__device__ __forceinline__ unsigned long long load_acquire_sys(const unsigned long long *address) {
+    unsigned long long value;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(value) : "l"(address) : "memory");
+    return value;
+}
+__device__ __forceinline__ unsigned long long load_acquire_gpu(const unsigned long long *address) {
+    unsigned long long value;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(value) : "l"(address) : "memory");
+    return value;
+}
+
+__device__ __noinline__ void exchange_barrier(const StackTp &tp, unsigned long long &exchange_number, int *error_flag) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        target += static_cast<unsigned long long>(gridDim.x) * tp.size;
-        __threadfence_system();
-        for (int r = 0; r < tp.size; r++)
-            asm volatile("red.release.sys.global.add.u64 [%0], 1;" ::"l"(tp.counter[r]) : "memory");
+        exchange_number += 1;
+        unsigned long long *mine = tp.counter[tp.rank];
+        __threadfence();
+        const unsigned long long before = atomicAdd(mine + TP_WORD_ARRIVALS, 1ull);
         unsigned int spins = 0;
-        while (true) {
-            unsigned long long seen;
-            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(tp.counter[tp.rank]) : "memory");
-            if (seen >= target) break;
-            if (++spins > EXCHANGE_SPIN_LIMIT) {
-                atomicExch(error_flag, 2);
-                break;
+        bool gave_up = false;
+        if (before + 1 == exchange_number * gridDim.x) {
+            // the last CTA of this GPU: everything this rank wrote for the exchange is in memory
+            __threadfence_system();
+            for (int r = 0; r < tp.size; r++)
+                if (r != tp.rank)
+                    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(tp.counter[r] + TP_WORD_PEER + tp.rank), "l"(exchange_number) : "memory");
+            for (int r = 0; r < tp.size && !gave_up; r++) {
+                if (r == tp.rank) continue;
+                while (load_acquire_sys(mine + TP_WORD_PEER + r) < exchange_number) {
+                    if (++spins > EXCHANGE_SPIN_LIMIT) {
+                        atomicExch(error_flag, 2);
+                        gave_up = true;
+                        break;
+                    }
+                    if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) {
+                        gave_up = true;
+                        break;
+                    }
+                    __nanosleep(32);
+                }
             }
-            if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) break;
-            __nanosleep(64);
+            __threadfence_system();
+            asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(mine + TP_WORD_GO), "l"(exchange_number) : "memory");
+        } else {
+            while (load_acquire_gpu(mine + TP_WORD_GO) < exchange_number) {
+                if (++spins > EXCHANGE_SPIN_LIMIT) {
+                    atomicExch(error_flag, 2);
+                    break;
+                }
+                if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) break;
+                __nanosleep(32);
+            }
         }
-        __threadfence_system();
+        __threadfence();
     }
     __syncthreads();
 }
 
 // After an exchange: hidden = bf16(bf16(sum over ranks of the partial sums) + hidden) for this CTA's share of the
-// [lanes][width] elements, four at a time (add_bf16.comp.template:17-24 on the all-reduced linear output).  The
-// partials are added in rank order on every rank, so the replicated residual streams stay bit-identical.
+// [lanes][width] elements, four at a time (add_bf16.comp.template:17-24 on the all-reduced linear output).  Every
+// rank keeps its own partial sums in its own buffer and the others read them from there (peer loads, all in flight
+// at once: one NVLink round trip).  The partials are added in rank order on every rank, so the replicated residual
+// streams stay bit-identical.
 __device__ __noinline__ void reduce_exchanged(const StackTp &tp, int parity, uint16_t *hidden, int lanes, int width) {
     const int per_lane = width >> 2, items = lanes * per_lane;
-    const float4 *mine = reinterpret_cast<const float4 *>(tp.exchange[tp.rank]) + static_cast<size_t>(parity) * tp.size * 8 * per_lane;
     for (int item = blockIdx.x * STACK_THREADS + threadIdx.x; item < items; item += gridDim.x * STACK_THREADS) {
         const int m = item / per_lane, quad = item - m * per_lane;
+        const size_t offset = (static_cast<size_t>(parity) * 8 + m) * per_lane + quad;
         float4 part[STACK_TP_MAX_RANKS];
 #pragma unroll
         for (int r = 0; r < STACK_TP_MAX_RANKS; r++)
-            if (r < tp.size) part[r] = __ldcg(mine + (static_cast<size_t>(r) * 8 + m) * per_lane + quad);
+            if (r < tp.size) part[r] = __ldcg(reinterpret_cast<const float4 *>(tp.exchange[r]) + offset);
         uint2 *destination = reinterpret_cast<uint2 *>(hidden) + static_cast<size_t>(m) * per_lane + quad;
         const uint2 residual = __ldcg(destination);
         float4 sum = part[0];
@@ -932,8 +974,12 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     const int q_width = shape.q_heads * HD, q_tiles = q_width >> 4, k_tiles = (shape.kv_heads * HD) >> 4;
     unsigned int target = 0;
     constexpr bool exchanging = EXCHANGE;
-    unsigned long long exchange_target = 0ull;  // arrivals that earlier launches consumed
-    if constexpr (EXCHANGE) exchange_target = *a.tp->base;
+    unsigned long long exchange_target = 0ull;  // exchanges done so far, earlier launches included
+    float *exchange_mine = nullptr;
+    if constexpr (EXCHANGE) {
+        exchange_target = a.tp->counter[a.tp->rank][TP_WORD_CONSUMED];
+        exchange_mine = a.tp->exchange[a.tp->rank];
+    }
     int exchange_parity = 0;
     unsigned int *counter = a.buffers.barrier;
     int *error_flag = a.buffers.error_flag;
@@ -1117,10 +1163,8 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                             a.buffers.activation[static_cast<size_t>(epilogue_m) * shape.ffn + tile * 16 + epilogue_row] =
                                 static_cast<uint16_t>(f32_to_bf16_bits(rounded_silu(round_bf16(first)) * round_bf16(second)));
                         } else if constexpr (EXCHANGE) {
-                            // this rank's share of the sum over K, unrounded, into every rank's exchange buffer
-                            const size_t slot = ((static_cast<size_t>(exchange_parity) * a.tp_size + a.tp->rank) * 8 + epilogue_m) * shape.hidden +
-                                                tile * 16 + epilogue_row;
-                            for (int r = 0; r < a.tp_size; r++) a.tp->exchange[r][slot] = first;
+                            // this rank's share of the sum over K, unrounded, into its exchange buffer (the others fetch it)
+                            exchange_mine[(static_cast<size_t>(exchange_parity) * 8 + epilogue_m) * shape.hidden + tile * 16 + epilogue_row] = first;
                         } else {
                             // linear + residual_add (add_bf16.comp.template:17-24): bf16(bf16(product) + residual), in place
                             a.buffers.hidden[static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row] =
@@ -1180,7 +1224,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
         if (gone == gridDim.x - 1) {
             counter[0] = 0u;
             counter[1] = 0u;
-            if constexpr (EXCHANGE) *a.tp->base = exchange_target;  // the next launch counts on from here
+            if constexpr (EXCHANGE) a.tp->counter[a.tp->rank][TP_WORD_CONSUMED] = exchange_target;  // the next launch counts on from here
             __threadfence();
         }
     }
