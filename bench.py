@@ -37,7 +37,7 @@ DRAFTS = 3
 METRIC = "accepted tokens/s (8B INT4, MTP k=3)"
 UNIT = "tokens/s"
 INT4_TRAFFIC_RATIO = 1.008
-STACK_TRAFFIC_RATIO = 1.06
+STACK_TRAFFIC_RATIO = 1.035
 NOMINAL_HBM_GBS = 8000.0
 
 
