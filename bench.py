@@ -217,6 +217,10 @@ def main():
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
     cores = os.cpu_count() or 1
+    # Several GPUs: one stream, the weights sharded tensor-parallel over the ranks (strong scaling; every rank runs
+    # the same calls and meets the others in the exchange).  NERVE_B200_BENCH_REPLICAS=1 instead runs one
+    # independent stream per GPU on replicated weights (weak scaling, no collective on the data path).
+    tensor_parallel = world > 1 and os.environ.get("NERVE_B200_BENCH_REPLICAS", "0") != "1"
     config = {
         "workload": "configs[1]: Llama-3-8B-shaped INT4 g128 + MTP k=3, prompt 512, batch 1, natural acceptance",
         "prompt_tokens": PROMPT_TOKENS, "draft_tokens": DRAFTS, "kv_page_tokens": 16,
@@ -267,10 +271,6 @@ def main():
         directory = ensure_package(spec, f"cuda:{local_rank}")
     barrier()
     directory = package_dir(spec.name)
-    # Several GPUs: one stream, the weights sharded tensor-parallel over the ranks (strong scaling; every rank runs
-    # the same calls and meets the others in the all-reduces).  NERVE_B200_BENCH_REPLICAS=1 instead runs one
-    # independent stream per GPU on replicated weights (weak scaling, no collective on the data path).
-    tensor_parallel = world > 1 and os.environ.get("NERVE_B200_BENCH_REPLICAS", "0") != "1"
     peer_exchange = tensor_parallel and os.environ.get("NERVE_B200_TP_EXCHANGE", "1") != "0"
     prompt = prompt_tokens(spec.vocab, seed=0 if tensor_parallel else rank)
 
