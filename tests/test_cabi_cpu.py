@@ -90,7 +90,7 @@ def test_reference_tiny_model_golden_equals_the_checked_in_fixture():
     reference ships for its own runtime tests."""
     import json
 
-    fixture = Path("/root/reference/runtime-rs/test-fixtures/tiny_model")
+    fixture = ROOT.parent / "reference" / "runtime-rs" / "test-fixtures" / "tiny_model"  # the reference checkout beside this repository
     if not fixture.exists():
         pytest.skip("reference checkout not present")
     ours = json.loads((GOLDEN / "reference_tiny_model" / "tensors.json").read_text())
