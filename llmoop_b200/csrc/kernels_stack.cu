@@ -3,7 +3,7 @@
 // the kernel list of one reference layer component, runtime-rs/shaders/*.comp.template) for a batch of at most
 // 8 lanes - the verify batch and the draft / single-tick steps of the speculative decode cycle.
 //
-// Why one launch: at these batch sizes a layer is ~136 MB of weights (~21 us of HBM time) cut into a dozen
+// Why one launch: at these batch sizes a layer is ~112 MB of weights (~17 us of HBM time) cut into a dozen
 // dependent steps; as separate kernels every step pays a launch, a pipeline fill and a drain (~6 us each,
 // measured), which is several times the streaming time.  Here one CTA per SM stays resident, keeps a ring of
 // asynchronous copies of packed weights in flight across step boundaries (weights do not depend on activations,
@@ -16,12 +16,14 @@
 //    bytes; a tile is K/128 contiguous KB).  q and k tiles pair row d with row d + head_width/2, so RoPE runs in
 //    the q/k/v epilogue and K, V go straight into the KV pages.
 //  * activations of a step: staged once per CTA in shared memory in mma.sync B-fragment order, together with
-//    24 * sum(x) per (lane, group): the nibbles are fed to the tensor cores as bf16 128+q (one lop3 per pair,
-//    no subtract) and the bias 128+8 is taken out per group with that sum.
+//    -24 * sum(x) per (lane, group): the nibbles are fed to the tensor cores as bf16 16+q (one shift and one lop3
+//    per pair, no subtract) and the bias 16+8 is taken out per group by starting the accumulation from that sum.
 //  * a matrix tile is computed by all 16 warps of a CTA (each takes every 16th group of K), reduced through
 //    shared memory, and finished by 128 epilogue threads (one per row and lane).
-//  * attention: one warp per (kv head, 64-token split, lane group) on the tensor cores, partials merged per
-//    (lane, head) by one warp after a barrier.
+//  * attention: a team of four warps per (kv head, 64-token split, lane group) on the tensor cores, partials
+//    merged per (lane, head) by one warp after a barrier.
+//  * tensor parallelism (the EXCHANGE instances): o and down leave f32 partial sums in the rank's exchange buffer;
+//    the ranks meet at a two-level barrier over NVLink and add each other's partials up from peer memory.
 // The per-layer code is one loop over the four matrix steps with run-time matrix / epilogue selection: the
 // straight-line form of the same steps did not fit the instruction cache and spent most of its time refetching.
 #include <cstdlib>
