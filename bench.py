@@ -176,6 +176,13 @@ def cpu_cycle_sample(directory, seconds_budget=150.0, max_cycles=None):
     at the benchmark's context, so the short context does not change the rate materially."""
     from oracle.nerve_oracle import Oracle, OraclePackage, OracleStream
 
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the sample is meant to use every host thread
+    try:
+        import ctypes
+
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(os.cpu_count() or 1)
+    except OSError:
+        pass
     package = OraclePackage(directory)
     oracle = Oracle(package)
     stream = OracleStream(package, 64)
@@ -292,7 +299,16 @@ def main():
             mine = torch.frombuffer(bytearray(engine.tp_exchange_handle()), dtype=torch.uint8).cuda()
             handles = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
             dist.all_gather(handles, mine)
-            engine.tp_connect([bytes(handle.cpu().numpy().tobytes()) for handle in handles])
+            connected = torch.ones(1, dtype=torch.int32, device="cuda")
+            try:
+                engine.tp_connect([bytes(handle.cpu().numpy().tobytes()) for handle in handles])
+            except nb.NerveError as error:  # e.g. no peer access between two of the GPUs
+                print(f"rank {rank}: peer exchange not available ({error}); NCCL path", file=sys.stderr)
+                connected.zero_()
+            dist.all_reduce(connected, op=dist.ReduceOp.MIN)
+            if int(connected.item()) == 0:  # all ranks or none: the others would wait for this one inside the kernel
+                engine.set_decode_stack(False)
+                peer_exchange = False
     engine.set_prefill_chunk(PROMPT_TOKENS)
     engine.add_stream(0, seed=0, speculative_draft_tokens=DRAFTS)
 
