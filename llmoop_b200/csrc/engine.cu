@@ -1607,6 +1607,12 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
             size_t left = event.input.token_ids.size() - event.next_external;
             int budget = std::min(prefill_chunk_, model_->options().max_lanes);
             int count = static_cast<int>(std::min<size_t>(left, budget));
+            // A batch appends the K/V of all its lanes before any lane attends.  Once the KV ring wraps, a later
+            // lane's slot is the one an earlier lane's window still ends in, and the reference runs the lanes one
+            // after the other (append_gqa_attention_bf16.comp.template:189-215 per tick).  So a chunk stops at the
+            // wrap, and beyond it every tick is a batch of its own.
+            const uint64_t ring = model_->capacity();
+            if (s.next_tick + static_cast<uint64_t>(count) > ring) count = s.next_tick < ring ? static_cast<int>(ring - s.next_tick) : 1;
             bool last = static_cast<size_t>(count) == left;
             bool sample = last && event.remaining > 0;
             uint32_t sampled = 0;
@@ -1630,7 +1636,10 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
             if (!s.active) continue;
             ActiveEvent &event = *s.active;
             if (event.next_external < event.input.token_ids.size() || !event.has_feedback) continue;
-            if (s.k > 0 && model_->plan().has_draft && !event.feedback_closes && event.remaining >= 2) {
+            // no speculation across or beyond the wrap of the KV ring (see the prefill chunks above): the rejected
+            // lanes of a cycle would also overwrite slots that are still inside the window
+            const bool ring_wraps = s.next_tick + static_cast<uint64_t>(s.k) + 1 > model_->capacity();
+            if (s.k > 0 && model_->plan().has_draft && !event.feedback_closes && event.remaining >= 2 && !ring_wraps) {
                 int drafts = static_cast<int>(std::min<size_t>(s.k, event.remaining - 1));
                 speculative[drafts].push_back(&s);
             } else {

@@ -132,3 +132,85 @@ def test_stack_kernel_is_deterministic_and_batch_independent(stack_package):
     assert together == alone
     engine.close()
     package.unmount()
+
+
+@pytest.fixture(scope="module")
+def long_context_package(tmp_path_factory):
+    from llmoop_b200.package_writer import write_package
+    from llmoop_b200.synth import ModelSpec
+
+    spec = ModelSpec(name="stack_long_context", hidden=512, layers=2, q_heads=8, kv_heads=2, head_dim=64, ffn=1408, vocab=512,
+                     max_positions=4096, quant="int4", std=0.02, seed=11)
+    directory = tmp_path_factory.mktemp("packages") / spec.name
+    write_package(spec, directory)
+    return directory, spec
+
+
+@pytest.mark.parametrize("capacity,context_tokens,probe_tokens", [(4096, 2100, 4), (128, 300, 1)], ids=["33_splits", "ring_wrapped_twice"])
+def test_stack_kernel_long_context_and_ring_wrap(long_context_package, capacity, context_tokens, probe_tokens):
+    """More attention splits than a warp has lanes (the merge walks them in rounds of 32), and a KV ring that has
+    wrapped: probe lanes after the context, stack kernel against the oracle and against the kernel-per-operator
+    path.  Behind the wrap a batch is one tick (all lanes of a batch append before any attends, and a later lane's
+    slot is the far end of an earlier lane's window), so the probe there is a single lane."""
+    import llmoop_b200 as nb
+    from oracle.nerve_oracle import OracleStream
+
+    directory, spec = long_context_package
+    opkg, oracle = _oracle(directory)
+    rng = np.random.default_rng(5)
+    context = [int(t) for t in rng.integers(0, spec.vocab, size=context_tokens)]
+    probe = [int(t) for t in rng.integers(0, spec.vocab, size=probe_tokens)]
+    ostream = OracleStream(opkg, capacity)
+    oracle.target_forward(ostream, context, 0, want_logits=False)
+    _, expected = oracle.target_forward(ostream, probe, len(context), want_logits=True)
+
+    package = nb.Package(directory, capacity_tokens=capacity, page_tokens=16, max_streams=1, max_lanes=96, verify_level=0)
+    engine = nb.Engine(package)
+    engine.set_decode_stack(True)
+    engine.add_stream(1)
+    engine.submit_input_event_until_idle(1, context, 0)
+    assert engine.stream_tick(1) == len(context)
+    logits, _ = engine.debug_target_logits(1, probe)
+    engine.set_decode_stack(False)
+    plain, _ = engine.debug_target_logits(1, probe)
+    scale = max(1.0, float(np.abs(expected).max()))
+    for name, got in (("stack kernel", logits), ("kernel per operator", plain)):
+        difference = np.abs(got - expected)
+        assert difference.max() <= 2e-2 * scale, (name, difference.max(), scale)
+        assert difference.mean() <= 2e-3 * scale, (name, difference.mean(), scale)
+    engine.close()
+    package.unmount()
+
+
+@pytest.mark.parametrize("decode_stack", [True, False], ids=["stack_kernel", "kernel_per_operator"])
+def test_speculative_stream_across_the_ring_wrap_equals_plain_decoding(long_context_package, decode_stack):
+    """A stream with k = 3 whose context grows past the KV capacity: up to the wrap it speculates, from there on
+    every tick runs alone; the tokens must be those of non-speculative decoding (the oracle with no drafts), which
+    keeps the full window of `capacity` ticks for every token."""
+    import llmoop_b200 as nb
+    from oracle.nerve_oracle import OracleStream
+
+    directory, spec = long_context_package
+    opkg, oracle = _oracle(directory)
+    capacity, new_tokens = 64, 40
+    prompt = [int(t) for t in np.random.default_rng(9).integers(0, spec.vocab, size=45)]
+    expected = oracle.generate(OracleStream(opkg, capacity), prompt, new_tokens, 0, collect_logits=True)
+
+    package = nb.Package(directory, capacity_tokens=capacity, page_tokens=16, max_streams=1, max_lanes=32, verify_level=0)
+    engine = nb.Engine(package)
+    engine.set_decode_stack(decode_stack)
+    engine.set_cycle_logging(True)
+    engine.add_stream(1, speculative_draft_tokens=3)
+    tokens, _ = engine.submit_input_event_until_idle(1, prompt, new_tokens)
+    cycles = engine.cycle_log()
+    assert cycles and all(c["start_tick"] + 4 <= capacity for c in cycles)  # speculation stops before the wrap
+    assert engine.stream_tick(1) > capacity
+    for index, (got, want) in enumerate(zip(tokens, expected["tokens"])):
+        if got != want:
+            gap = oracle.top2_gap(expected["logits"][index])
+            assert gap < 2e-2, f"token {index}: {got} != {want} with top-2 gap {gap}"
+            break
+    else:
+        assert len(tokens) == len(expected["tokens"])
+    engine.close()
+    package.unmount()
