@@ -302,3 +302,41 @@ def test_seeded_sampling_is_independent_of_speculation(decode_stack):
     assert len(set(runs[0])) > 3
     engine.close()
     package.unmount()
+
+
+@pytest.mark.parametrize("drafts", [0, 3])
+def test_consecutive_events_reset_and_interrupt(drafts):
+    """Stream life cycle (placed_prompt_engine.rs:48-589 as used by the chat front end): a second input event
+    continues the first one's context; after reset_stream the same events give the same tokens again (state pages
+    and the draft's state start over); an interrupted stream drops its queued work and runs again afterwards."""
+    import llmoop_b200 as nb
+    from oracle.nerve_oracle import OracleStream
+
+    name = "tiny_int4_mtp"
+    opkg, oracle = _oracle(name)
+    first, second = _prompt(opkg.vocab, 13, seed=41), _prompt(opkg.vocab, 6, seed=42)
+    ostream = OracleStream(opkg, 128)
+    expected_first = oracle.generate(ostream, first, 9, drafts)["tokens"]
+    expected_second = oracle.generate(ostream, second, 11, drafts)["tokens"]
+
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=2, max_lanes=32)
+    engine = nb.Engine(package)
+    engine.add_stream(7, speculative_draft_tokens=drafts)
+    for _ in range(2):
+        got_first, _ = engine.submit_input_event_until_idle(7, first, 9)
+        ticks_after_first = engine.stream_tick(7)
+        got_second, _ = engine.submit_input_event_until_idle(7, second, 11)
+        assert got_first == expected_first and got_second == expected_second
+        assert ticks_after_first == len(first) + 9 and engine.stream_tick(7) == ticks_after_first + len(second) + 11
+        engine.reset_stream_transient_state(7)
+        assert engine.stream_tick(7) == 0
+
+    engine.enqueue_input_event(7, first, 9)
+    engine.interrupt_stream(7)
+    outputs, _ = engine.run_until_idle()
+    assert outputs == []
+    engine.reset_stream_transient_state(7)
+    again, _ = engine.submit_input_event_until_idle(7, first, 9)
+    assert again == expected_first
+    engine.close()
+    package.unmount()
