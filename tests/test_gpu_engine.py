@@ -340,3 +340,47 @@ def test_consecutive_events_reset_and_interrupt(drafts):
     assert again == expected_first
     engine.close()
     package.unmount()
+
+
+def test_ragged_streams_with_different_draft_counts_budgets_and_stops():
+    """Streams that differ in prompt length, draft count (0, 1, 3), output budget (down to one token) and stop
+    tokens share an engine: each must emit what it emits alone (the kernel-per-operator path keeps the sums of
+    every batch composition identical)."""
+    import llmoop_b200 as nb
+
+    name = "tiny_int4_mtp"
+    opkg, oracle = _oracle(name)
+    cases = [  # prompt length, drafts, budget
+        (1, 3, 1), (9, 0, 14), (17, 1, 9), (4, 3, 20), (33, 3, 2),
+    ]
+    prompts = [_prompt(opkg.vocab, length, seed=60 + i) for i, (length, _, _) in enumerate(cases)]
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=6, max_lanes=64)
+    engine = nb.Engine(package)
+    engine.set_decode_stack(False)
+    alone, stops = [], []
+    for i, ((_, drafts, budget), prompt) in enumerate(zip(cases, prompts)):
+        engine.add_stream(100 + i, speculative_draft_tokens=drafts)
+        tokens, _ = engine.submit_input_event_until_idle(100 + i, prompt, budget)
+        engine.remove_stream(100 + i)
+        assert 1 <= len(tokens) <= budget
+        # the longest run also gets a stop token taken from the middle of its own output
+        stop = [tokens[len(tokens) // 2]] if budget == 20 else []
+        if stop:
+            engine.add_stream(200 + i, speculative_draft_tokens=drafts)
+            tokens, _ = engine.submit_input_event_until_idle(200 + i, prompt, budget, stop_token_ids=stop)
+            engine.remove_stream(200 + i)
+            assert tokens[-1] == stop[0] and stop[0] not in tokens[:-1]
+        alone.append(tokens)
+        stops.append(stop)
+    for i, ((_, drafts, budget), prompt) in enumerate(zip(cases, prompts)):
+        engine.add_stream(i, speculative_draft_tokens=drafts)
+        engine.enqueue_input_event(i, prompt, budget, stop_token_ids=stops[i])
+    outputs, _ = engine.run_until_idle()
+    together = [[t for sid, t, _, _ in outputs if sid == i] for i in range(len(cases))]
+    assert together == alone
+    # and the oracle agrees on the plain greedy case
+    from oracle.nerve_oracle import OracleStream
+
+    assert oracle.generate(OracleStream(opkg, 128), prompts[1], 14, 0)["tokens"] == alone[1]
+    engine.close()
+    package.unmount()
