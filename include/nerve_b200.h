@@ -103,6 +103,21 @@ int32_t nerve_b200_engine_fork_stream(nerve_b200_engine *engine, int64_t source_
 int32_t nerve_b200_engine_reset_stream(nerve_b200_engine *engine, int64_t stream_id);
 int32_t nerve_b200_engine_remove_stream(nerve_b200_engine *engine, int64_t stream_id);
 int32_t nerve_b200_engine_interrupt_stream(nerve_b200_engine *engine, int64_t stream_id);
+/* stop_stream_after_current (placed_prompt_engine.rs:307-331): the active event emits no more tokens, its last token is
+ * still fed back as the closing tick; queued events are dropped.  No effect on an idle stream. */
+int32_t nerve_b200_engine_stop_after_current(nerve_b200_engine *engine, int64_t stream_id);
+/* snapshot (placed_prompt_engine.rs:1238-1258, 1388-1400). */
+typedef struct {
+    uint64_t pending_input_event_count, next_stream_tick, completed_prompt_event_count, context_window_activations,
+        mapped_state_pages;
+    int32_t speculative_draft_tokens, idle;
+} nerve_b200_engine_stream_snapshot;
+typedef struct {
+    uint64_t stream_count, active_stream_count;
+    int32_t idle;
+} nerve_b200_engine_snapshot_counts;
+int32_t nerve_b200_engine_stream_snapshot_of(nerve_b200_engine *engine, int64_t stream_id, nerve_b200_engine_stream_snapshot *out);
+int32_t nerve_b200_engine_snapshot(nerve_b200_engine *engine, nerve_b200_engine_snapshot_counts *out);
 
 /* enqueue_input_event (placed_prompt_engine.rs:256-331): VulkanResidentTokenInputEvent
  * {id, token_ids, max_public_tokens, stop_token_ids}. */

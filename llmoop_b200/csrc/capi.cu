@@ -267,6 +267,37 @@ int32_t nerve_b200_engine_init_tp(nerve_b200_engine *engine, const char *nccl_li
     });
 }
 
+int32_t nerve_b200_engine_stop_after_current(nerve_b200_engine *engine, int64_t stream_id) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        engine->engine->stop_stream_after_current(stream_id);
+    });
+}
+
+int32_t nerve_b200_engine_stream_snapshot_of(nerve_b200_engine *engine, int64_t stream_id, nerve_b200_engine_stream_snapshot *out) {
+    return guarded([&] {
+        require(engine != nullptr && out != nullptr, "null argument");
+        const Engine::StreamSnapshot snapshot = engine->engine->stream_snapshot(stream_id);
+        out->pending_input_event_count = snapshot.pending_input_event_count;
+        out->next_stream_tick = snapshot.next_stream_tick;
+        out->completed_prompt_event_count = snapshot.completed_prompt_event_count;
+        out->context_window_activations = snapshot.context_window_activations;
+        out->mapped_state_pages = snapshot.mapped_state_pages;
+        out->speculative_draft_tokens = snapshot.speculative_draft_tokens;
+        out->idle = snapshot.idle ? 1 : 0;
+    });
+}
+
+int32_t nerve_b200_engine_snapshot(nerve_b200_engine *engine, nerve_b200_engine_snapshot_counts *out) {
+    return guarded([&] {
+        require(engine != nullptr && out != nullptr, "null argument");
+        const Engine::EngineSnapshot snapshot = engine->engine->snapshot();
+        out->stream_count = snapshot.stream_count;
+        out->active_stream_count = snapshot.active_stream_count;
+        out->idle = snapshot.idle ? 1 : 0;
+    });
+}
+
 int32_t nerve_b200_engine_tp_exchange_handle(nerve_b200_engine *engine, uint8_t *out_64_bytes) {
     return guarded([&] {
         require(engine && out_64_bytes, "null argument");

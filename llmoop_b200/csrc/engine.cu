@@ -751,6 +751,40 @@ void Engine::interrupt_stream(int64_t id) {
     s.active.reset();
 }
 
+// stop_stream_after_current (placed_prompt_engine.rs:307-331, placed_prompt_event.rs:320-341): the active event
+// emits nothing more; the token it emitted last is still fed back (the closing tick), so the state stays complete.
+// Queued events are dropped (stream_runtime.rs:819-831).
+void Engine::stop_stream_after_current(int64_t id) {
+    Stream &s = stream(id);
+    if (!s.active) return;
+    s.queue.clear();
+    s.active->remaining = 0;
+    if (s.active->has_feedback) s.active->feedback_closes = true;
+}
+
+Engine::StreamSnapshot Engine::stream_snapshot(int64_t id) const {
+    const Stream &s = stream(id);
+    StreamSnapshot snapshot;
+    snapshot.pending_input_event_count = s.queue.size() + (s.active ? 1 : 0);
+    snapshot.next_stream_tick = s.next_tick;
+    snapshot.completed_prompt_event_count = s.completed_events;
+    snapshot.idle = !s.active && s.queue.empty();
+    snapshot.context_window_activations = model_->capacity();
+    snapshot.speculative_draft_tokens = s.k;
+    size_t pages = 0;
+    for (int32_t page : s.pages) pages += page >= 0 ? 1 : 0;
+    snapshot.mapped_state_pages = pages;
+    return snapshot;
+}
+
+Engine::EngineSnapshot Engine::snapshot() const {
+    EngineSnapshot snapshot;
+    snapshot.stream_count = streams_.size();
+    for (const auto &entry : streams_) snapshot.active_stream_count += (entry.second.active || !entry.second.queue.empty()) ? 1 : 0;
+    snapshot.idle = snapshot.active_stream_count == 0;
+    return snapshot;
+}
+
 void Engine::fork_stream(int64_t source, int64_t destination, uint32_t seed) {
     Stream &src = stream(source);
     if (src.active) fail("cannot fork stream " + std::to_string(source) + " while an input event is active");
@@ -1426,7 +1460,10 @@ void Engine::run_single_ticks(std::vector<Stream *> &batch, const std::function<
         bool should_emit = !was_closing && event.remaining > 0;
         event.has_feedback = false;
         if (should_emit) emit(s, host_records_[i * 4], tick, on_output, report);
-        if (was_closing || !event.has_feedback) s.active.reset();
+        if (was_closing || !event.has_feedback) {
+            s.active.reset();
+            s.completed_events++;
+        }
     }
 }
 
@@ -1625,6 +1662,7 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
             else if (last) {
                 synchronize("prefill synchronize");
                 s.active.reset();  // no public outputs requested: the event ends with the prompt
+                s.completed_events++;
             }
             report.prefill_ns += now_ns() - start;
         }

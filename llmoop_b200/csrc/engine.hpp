@@ -198,6 +198,20 @@ public:
     void tp_connect(const uint8_t *handles_64_bytes_each, int count);
 
     uint64_t stream_tick(int64_t id) const;
+    void stop_stream_after_current(int64_t id);
+    // placed_prompt_engine.rs:1238-1258, 1388-1400 (the fields that exist on one device)
+    struct StreamSnapshot {
+        uint64_t pending_input_event_count = 0, next_stream_tick = 0, completed_prompt_event_count = 0, context_window_activations = 0,
+                 mapped_state_pages = 0;
+        int speculative_draft_tokens = 0;
+        bool idle = true;
+    };
+    struct EngineSnapshot {
+        uint64_t stream_count = 0, active_stream_count = 0;
+        bool idle = true;
+    };
+    StreamSnapshot stream_snapshot(int64_t id) const;
+    EngineSnapshot snapshot() const;
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
     void set_cycle_logging(bool enabled) { log_cycles_ = enabled; }
     void set_use_graphs(bool enabled) { use_graphs_ = enabled; }
@@ -238,6 +252,7 @@ private:
         std::vector<int32_t> pages;  // logical page -> physical page (-1 = unmapped)
         std::vector<uint32_t> teacher;
         bool block_table_dirty = true;
+        uint64_t completed_events = 0;
     };
 
     Stream &stream(int64_t id);

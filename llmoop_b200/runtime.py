@@ -51,6 +51,16 @@ _REPORT_U64 = (
     "kernel_launches", "graph_launches", "h2d_bytes", "d2h_bytes", "host_syncs")
 
 
+class _EngineStreamSnapshot(ctypes.Structure):
+    _fields_ = [("pending_input_event_count", ctypes.c_uint64), ("next_stream_tick", ctypes.c_uint64),
+                ("completed_prompt_event_count", ctypes.c_uint64), ("context_window_activations", ctypes.c_uint64),
+                ("mapped_state_pages", ctypes.c_uint64), ("speculative_draft_tokens", ctypes.c_int32), ("idle", ctypes.c_int32)]
+
+
+class _EngineSnapshotCounts(ctypes.Structure):
+    _fields_ = [("stream_count", ctypes.c_uint64), ("active_stream_count", ctypes.c_uint64), ("idle", ctypes.c_int32)]
+
+
 class _RunReport(ctypes.Structure):
     _fields_ = [(name, ctypes.c_uint64) for name in _REPORT_U64] + [
         ("verify_ms_sum", ctypes.c_double), ("verify_steps", ctypes.c_uint64), ("verify_bytes", ctypes.c_uint64),
@@ -66,7 +76,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_destroy", "nerve_b200_engine_add_stream", "nerve_b200_engine_fork_stream",
     "nerve_b200_engine_reset_stream", "nerve_b200_engine_remove_stream", "nerve_b200_engine_interrupt_stream",
     "nerve_b200_engine_enqueue", "nerve_b200_engine_run_until_idle", "nerve_b200_engine_run",
-    "nerve_b200_engine_set_profiling", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_init_tp", "nerve_b200_engine_tp_exchange_handle", "nerve_b200_engine_tp_connect", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
+    "nerve_b200_engine_set_profiling", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_stop_after_current", "nerve_b200_engine_stream_snapshot_of", "nerve_b200_engine_snapshot", "nerve_b200_engine_init_tp", "nerve_b200_engine_tp_exchange_handle", "nerve_b200_engine_tp_connect", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
     "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair", "nerve_b200_set_int4_kernel",
@@ -227,6 +237,21 @@ class Engine:
 
     def interrupt_stream(self, stream_id: int):
         _check(library().nerve_b200_engine_interrupt_stream(self._handle, ctypes.c_int64(stream_id)))
+
+    def stop_stream_after_current(self, stream_id: int):
+        _check(library().nerve_b200_engine_stop_after_current(self._handle, ctypes.c_int64(stream_id)))
+
+    def stream_snapshot(self, stream_id: int) -> dict:
+        raw = _EngineStreamSnapshot()
+        _check(library().nerve_b200_engine_stream_snapshot_of(self._handle, ctypes.c_int64(stream_id), ctypes.byref(raw)))
+        out = {name: getattr(raw, name) for name, _ in _EngineStreamSnapshot._fields_}
+        out["idle"] = bool(out["idle"])
+        return out
+
+    def snapshot(self) -> dict:
+        raw = _EngineSnapshotCounts()
+        _check(library().nerve_b200_engine_snapshot(self._handle, ctypes.byref(raw)))
+        return {"stream_count": raw.stream_count, "active_stream_count": raw.active_stream_count, "idle": bool(raw.idle)}
 
     def enqueue_input_event(self, stream_id: int, token_ids, max_public_tokens: int, stop_token_ids=(), event_id="event"):
         tokens = (ctypes.c_uint32 * max(1, len(token_ids)))(*[int(t) for t in token_ids])

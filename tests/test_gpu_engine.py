@@ -384,3 +384,48 @@ def test_ragged_streams_with_different_draft_counts_budgets_and_stops():
     assert oracle.generate(OracleStream(opkg, 128), prompts[1], 14, 0)["tokens"] == alone[1]
     engine.close()
     package.unmount()
+
+
+@pytest.mark.parametrize("drafts", [0, 3])
+def test_stop_after_current_and_snapshots(drafts):
+    """stop_stream_after_current (placed_prompt_engine.rs:307-331): the active event emits nothing more, its last token
+    is still fed back (the stream's tick count stays prompt + emitted), queued events are dropped and the stream can
+    be used again; snapshots report queue depth, ticks, finished events and mapped pages."""
+    import llmoop_b200 as nb
+
+    name = "tiny_int4_mtp"
+    opkg, _ = _oracle(name)
+    prompt, later = _prompt(opkg.vocab, 10, seed=71), _prompt(opkg.vocab, 4, seed=72)
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=2, max_lanes=32)
+    engine = nb.Engine(package)
+    engine.add_stream(3, speculative_draft_tokens=drafts)
+    full, _ = engine.submit_input_event_until_idle(3, prompt, 20)
+    engine.reset_stream_transient_state(3)
+    assert engine.snapshot() == {"stream_count": 1, "active_stream_count": 0, "idle": True}
+
+    engine.enqueue_input_event(3, prompt, 20)
+    engine.enqueue_input_event(3, later, 5)
+    before = engine.stream_snapshot(3)
+    assert before["pending_input_event_count"] == 2 and not before["idle"] and before["next_stream_tick"] == 0
+    assert engine.snapshot()["active_stream_count"] == 1
+    first, _ = engine.run(1)   # prompt chunk and the first decode batch
+    got = [token for sid, token, _, _ in first if sid == 3]
+    assert 1 <= len(got) < 20 and got == full[: len(got)]
+    engine.stop_stream_after_current(3)
+    rest, _ = engine.run_until_idle()
+    assert [t for sid, t, _, _ in rest if sid == 3] == []          # nothing more is emitted, the queued event is gone
+    after = engine.stream_snapshot(3)
+    assert after["idle"] and after["pending_input_event_count"] == 0 and after["completed_prompt_event_count"] == 2
+    assert after["next_stream_tick"] == len(prompt) + len(got)      # the last token was fed back: P + N ticks
+    assert after["mapped_state_pages"] == (after["next_stream_tick"] + 15) // 16
+    assert after["speculative_draft_tokens"] == drafts and after["context_window_activations"] == 128
+    # the state is complete: continuing from here equals continuing an uninterrupted run of the same length
+    engine.add_stream(4, speculative_draft_tokens=drafts)
+    engine.submit_input_event_until_idle(4, prompt, len(got))
+    expected, _ = engine.submit_input_event_until_idle(4, later, 6)
+    continued, _ = engine.submit_input_event_until_idle(3, later, 6)
+    assert continued == expected
+    engine.stop_stream_after_current(3)                             # idle stream: no effect
+    assert engine.stream_snapshot(3)["idle"]
+    engine.close()
+    package.unmount()
