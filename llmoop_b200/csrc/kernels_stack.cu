@@ -134,8 +134,7 @@ __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int
     __syncthreads();
     if (threadIdx.x == 0) {
         target += gridDim.x;
-        __threadfence();
-        atomicAdd(counter, 1u);
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");  // covers the CTA's writes before the barrier above
         unsigned int spins = 0;
         while (load_acquire(counter) < target) {
             if (++spins > BARRIER_SPIN_LIMIT) {
@@ -143,9 +142,7 @@ __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int
                 break;
             }
             if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) break;
-            __nanosleep(32);
         }
-        __threadfence();
     }
     __syncthreads();
 }
@@ -200,7 +197,6 @@ __device__ __noinline__ void exchange_barrier(const StackTp &tp, unsigned long l
                         gave_up = true;
                         break;
                     }
-                    __nanosleep(32);
                 }
             }
             __threadfence_system();
@@ -212,7 +208,6 @@ __device__ __noinline__ void exchange_barrier(const StackTp &tp, unsigned long l
                     break;
                 }
                 if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) break;
-                __nanosleep(32);
             }
         }
         __threadfence();
