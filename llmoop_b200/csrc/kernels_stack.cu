@@ -149,12 +149,12 @@ __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int
 
 // All CTAs of all tensor-parallel ranks meet here, in two levels: the CTAs of this GPU count themselves in on a
 // local word; the last one to arrive tells every peer (one system-scope store of the exchange number per peer, over
-// NVLink), waits until every peer has told it the same, and lets the local CTAs go.  One remote write per peer and
+// NVLink); every CTA then waits until all local CTAs and every peer have done so.  One remote write per peer and
 // exchange: arrivals of 148 CTAs on one remote word would queue up on the link.  `exchange_number` counts the
 // exchanges of this and all earlier launches; all words only grow.  What the CTAs wrote into their rank's exchange
 // buffer before the call is visible to the peers after it.  Every wait is bounded; a rank that never shows up ends
 // the launch with the error flag set.
-// Control words of a rank (unsigned long long, behind its exchange buffer): [0] local arrivals, [1] go,
+// Control words of a rank (unsigned long long, behind its exchange buffer): [0] local arrivals, [1] unused,
 // [2] exchanges consumed by earlier launches, [8 + s] the exchange number rank s has reached.
 constexpr unsigned int EXCHANGE_SPIN_LIMIT = 1u << 22;
 constexpr int TP_WORD_ARRIVALS = 0, TP_WORD_GO = 1, TP_WORD_CONSUMED = 2, TP_WORD_PEER = 8;
@@ -175,42 +175,43 @@ __device__ __noinline__ void exchange_barrier(const StackTp &tp, unsigned long l
     if (threadIdx.x == 0) {
         exchange_number += 1;
         unsigned long long *mine = tp.counter[tp.rank];
-        __threadfence();
-        const unsigned long long before = atomicAdd(mine + TP_WORD_ARRIVALS, 1ull);
+        // release: the CTA's writes before the barrier above; acquire: the last to arrive takes over everybody's
+        unsigned long long before;
+        asm volatile("atom.acq_rel.gpu.global.add.u64 %0, [%1], 1;" : "=l"(before) : "l"(mine + TP_WORD_ARRIVALS) : "memory");
         unsigned int spins = 0;
         bool gave_up = false;
         if (before + 1 == exchange_number * gridDim.x) {
-            // the last CTA of this GPU: everything this rank wrote for the exchange is in memory
-            __threadfence_system();
+            // the last CTA of this GPU: everything this rank wrote for the exchange is in memory; the system-scope
+            // release stores publish it to the peers
             for (int r = 0; r < tp.size; r++)
                 if (r != tp.rank)
                     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(tp.counter[r] + TP_WORD_PEER + tp.rank), "l"(exchange_number) : "memory");
-            for (int r = 0; r < tp.size && !gave_up; r++) {
-                if (r == tp.rank) continue;
-                while (load_acquire_sys(mine + TP_WORD_PEER + r) < exchange_number) {
-                    if (++spins > EXCHANGE_SPIN_LIMIT) {
-                        atomicExch(error_flag, 2);
-                        gave_up = true;
-                        break;
-                    }
-                    if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) {
-                        gave_up = true;
-                        break;
-                    }
-                }
-            }
-            __threadfence_system();
-            asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(mine + TP_WORD_GO), "l"(exchange_number) : "memory");
-        } else {
-            while (load_acquire_gpu(mine + TP_WORD_GO) < exchange_number) {
-                if (++spins > EXCHANGE_SPIN_LIMIT) {
-                    atomicExch(error_flag, 2);
-                    break;
-                }
-                if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) break;
+        }
+        // every CTA waits for the same two things itself (no hop through a go word): all CTAs of this GPU have
+        // arrived, and every peer has said so of its own
+        const unsigned long long all_here = exchange_number * gridDim.x;
+        while (!gave_up && load_acquire_gpu(mine + TP_WORD_ARRIVALS) < all_here) {
+            if (++spins > EXCHANGE_SPIN_LIMIT) {
+                atomicExch(error_flag, 2);
+                gave_up = true;
+            } else if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) {
+                gave_up = true;
             }
         }
-        __threadfence();
+        for (int r = 0; r < tp.size && !gave_up; r++) {
+            if (r == tp.rank) continue;
+            while (load_acquire_sys(mine + TP_WORD_PEER + r) < exchange_number) {
+                if (++spins > EXCHANGE_SPIN_LIMIT) {
+                    atomicExch(error_flag, 2);
+                    gave_up = true;
+                    break;
+                }
+                if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) {
+                    gave_up = true;
+                    break;
+                }
+            }
+        }
     }
     __syncthreads();
 }
