@@ -156,7 +156,7 @@ __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int
 // the launch with the error flag set.
 // Control words of a rank (unsigned long long, behind its exchange buffer): [0] local arrivals, [1] unused,
 // [2] exchanges consumed by earlier launches, [8 + s] the exchange number rank s has reached.
-constexpr unsigned int EXCHANGE_SPIN_LIMIT = 1u << 22;
+constexpr unsigned int EXCHANGE_SPIN_LIMIT = 1u << 24;  // about ten seconds of polling: ranks start their launches a host jitter apart
 constexpr int TP_WORD_ARRIVALS = 0, TP_WORD_GO = 1, TP_WORD_CONSUMED = 2, TP_WORD_PEER = 8;
 
 __device__ __forceinline__ unsigned long long load_acquire_sys(const unsigned long long *address) {
