@@ -190,6 +190,7 @@ std::shared_ptr<MountedModel> MountedModel::mount(const std::string &path, const
     for (const ComponentPlan &layer : plan.draft_layers) add_pool(layer);
     model->block_table_ = device_alloc(sizeof(int32_t) * options.max_streams * model->pages_per_stream_);
     model->build_rope_tables();
+    cuda_check(cudaDeviceGetAttribute(&model->sm_count_, cudaDevAttrMultiProcessorCount, options.device), "cudaDeviceGetAttribute");
     {
         int target_kv_layers = 0;
         for (const ComponentPlan &layer : plan.layers) target_kv_layers += layer.has_kv ? 1 : 0;
@@ -362,14 +363,15 @@ void MountedModel::build_stack(const std::vector<ComponentPlan> &layers, int fir
         if (!dims) return drop(), refuse("layer dimensions or rotary form are outside the decode stack kernel");
         here.rope_table = rope_table(rq.theta, rq.rotary_width);
         here.rope_positions = rope_positions_;
+        here.grid = sm_count_;
         if (index == 0) shape = here;
         else if (std::memcmp(&shape, &here, sizeof(StackShape)) != 0) return drop(), refuse("layers differ in shape");
         size_t unused = 0;
         if (!decode_stack_supported(shape, 1, &unused)) return drop(), refuse("no decode stack kernel instance for this head shape");
 
-        auto tiled = [&](std::initializer_list<const OpSpec *> sources, bool pair, bool rope_first_two) {
+        auto streamed = [&](std::initializer_list<const OpSpec *> sources, bool pair, bool rope_first_two) {
             RelayoutSegment segments[3];
-            int count = 0, tiles = 0;
+            int count = 0, rows = 0;
             const int kk = static_cast<int>((*sources.begin())->weights[0].k);
             for (const OpSpec *source : sources) {
                 const WeightRef &w = source->weights[0];
@@ -377,31 +379,27 @@ void MountedModel::build_stack(const std::vector<ComponentPlan> &layers, int fir
                 segments[count].scales = static_cast<const uint16_t *>(tensor(w.scale));
                 segments[count].rows = static_cast<int>(w.n);
                 segments[count].rope_head_width = (rope_first_two && count < 2) ? here.head_width : 0;
-                if (!pair || count == 0) tiles += static_cast<int>(w.n) / 16;
+                if (!pair || count == 0) rows += static_cast<int>(w.n);
                 count++;
             }
-            const int rt = pair ? 2 : 1, groups = kk / 128;
-            DeviceBuffer weights = device_alloc(static_cast<size_t>(tiles) * groups * rt * 64 * sizeof(uint4), false);
-            DeviceBuffer scales = device_alloc(static_cast<size_t>(tiles) * groups * rt * 8 * sizeof(uint32_t), false);
-            storage.push_back(weights);
-            storage.push_back(scales);
-            cuda_check(launch_int4_tile_major(segments, count, pair, kk, static_cast<uint4 *>(weights.ptr), static_cast<uint32_t *>(scales.ptr), nullptr),
-                       "tile-major INT4 copy");
-            bytes += weights.bytes + scales.bytes;
-            return TiledInt4{static_cast<const uint4 *>(weights.ptr), static_cast<const uint32_t *>(scales.ptr), tiles, groups};
+            DeviceBuffer stream = device_alloc(std::max<size_t>(16, int4_cta_stream_bytes(rows, kk, pair, here.grid)), false);
+            storage.push_back(stream);
+            cuda_check(launch_int4_cta_streams(segments, count, pair, kk, here.grid, static_cast<uint8_t *>(stream.ptr), nullptr), "per-CTA INT4 stream copy");
+            bytes += stream.bytes;
+            return static_cast<const uint8_t *>(stream.ptr);
         };
         StackLayer spec{};
-        spec.qkv = tiled({&q, &k, &v}, false, true);
-        spec.o = tiled({&o}, false, false);
-        spec.gate_up = tiled({&gate, &up}, true, false);
-        spec.down = tiled({&down}, false, false);
+        spec.qkv = streamed({&q, &k, &v}, false, true);
+        spec.o = streamed({&o}, false, false);
+        spec.gate_up = streamed({&gate, &up}, true, false);
+        spec.down = streamed({&down}, false, false);
         spec.input_norm = static_cast<const uint16_t *>(tensor(norm1.norm_weights[0]));
         spec.post_norm = static_cast<const uint16_t *>(tensor(norm2.norm_weights[0]));
         spec.kv = kv_layer(kv_index++);
         bytes += 2 * static_cast<uint64_t>(here.hidden) * 2;
         built.push_back(spec);
     }
-    cuda_check(cudaDeviceSynchronize(), "tile-major INT4 copies");
+    cuda_check(cudaDeviceSynchronize(), "per-CTA INT4 stream copies");
     out.available = true;
     out.shape = shape;
     out.layers = built;
@@ -539,7 +537,7 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
             stack_q_ = device_alloc(8 * q_width * 2);
             stack_attention_out_ = device_alloc(8 * q_width * 2);
             stack_activation_ = device_alloc(8 * ffn * 2);
-            stack_barrier_ = device_alloc(2 * sizeof(unsigned int));
+            stack_barrier_ = device_alloc(STACK_BARRIER_WORDS * sizeof(unsigned int));
             stack_timing_ = device_alloc(std::max<size_t>(1, plan.layers.size()) * 32 * sizeof(unsigned long long));
         }
         const char *value = getenv("NERVE_B200_DECODE_STACK");

@@ -114,6 +114,7 @@ private:
     int pages_per_stream_ = 0, physical_pages_ = 0;
     std::map<std::pair<uint32_t, int>, DeviceBuffer> rope_tables_;  // (theta bits, rotary) -> table
     uint32_t rope_positions_ = 0;
+    int sm_count_ = 0;  // CTAs of the persistent kernels (one per SM of the mount device)
     StackPlan target_stack_, draft_stack_;
 };
 

@@ -122,16 +122,45 @@ void set_int4_stream_enabled(int enabled);
 
 // ---- persistent decode stack (kernels_stack.cu) ----
 // One cooperative launch runs a whole stack of dense INT4 g128 Llama-style layers for a batch of at most 8 lanes:
-// every CTA (one per SM) streams its share of each weight matrix while grid-wide barriers separate the phases
-// of a layer.  Weights are read from a tile-major copy made at mount (see launch_int4_tile_major).
-struct TiledInt4 {
-    const uint4 *weights;     // [tile][group][rt][half][32] uint4: 16 rows x 128 columns per (tile, group, rt)
-    const uint32_t *scales;   // [tile][group][rt][8]: bf16 scale of row g | scale of row g + 8 << 16
-    int tiles;                // 16-row tiles (tiles of a gate/up pair hold 16 gate rows and the same 16 up rows)
-    int groups;               // K / 128
+// every CTA (one per SM) streams its share of each weight matrix while grid-wide barriers separate the steps of a
+// layer.  Weights are read from per-CTA byte streams written at mount (launch_int4_cta_streams).
+
+// How the CTAs of a grid share one matrix of `tiles` 16-row tiles (a gate/up pair tile holds 16 gate rows and the
+// same 16 up rows: rt = 2) over K = groups * 128 columns.  CTA c owns tiles c, c + grid, ...; it works on `slots`
+// of them at a time (one pass), `width` warps per tile, warp i of a tile taking units i, i + width, ... of the
+// tile's `units` = groups * rt blocks of 16x128 nibbles (unit u = group u / rt, matrix u % rt).  Step s of a pass
+// is one stage of the CTA's stream: for every present tile slot, units s * width .. s * width + width - 1
+// (1 KB of nibbles each, zero beyond `units`), followed by the same units' 32-byte scale-pair rows.
+struct MatrixSchedule {
+    int tiles, units, rt, slots, width, steps, grid;
 };
+__host__ __device__ inline MatrixSchedule stack_schedule(int tiles, int groups, int rt, int grid) {
+    MatrixSchedule s;
+    s.tiles = tiles;
+    s.rt = rt;
+    s.units = groups * rt;
+    s.grid = grid;
+    const int most = (tiles + grid - 1) / grid;
+    int slots = 1;
+    while (slots < most && slots * 2 <= 16 / rt) slots *= 2;
+    int width = 16 / slots;
+    while (width / 2 >= rt && width / 2 >= s.units) width /= 2;
+    s.slots = slots;
+    s.width = width;
+    s.steps = (s.units + width - 1) / width;
+    return s;
+}
+__host__ __device__ inline int stack_cta_tiles(const MatrixSchedule &s, int cta) { return s.tiles / s.grid + (cta < s.tiles % s.grid ? 1 : 0); }
+// Bytes of the stream in front of CTA `cta`'s share (every tile costs width * steps units of 1056 bytes).
+__host__ __device__ inline size_t stack_cta_offset(const MatrixSchedule &s, int cta) {
+    const int extra = s.tiles % s.grid;
+    const size_t tiles_before = static_cast<size_t>(cta) * (s.tiles / s.grid) + (cta < extra ? cta : extra);
+    return tiles_before * s.width * s.steps * 1056;
+}
+__host__ __device__ inline size_t stack_stream_bytes(const MatrixSchedule &s) { return static_cast<size_t>(s.tiles) * s.width * s.steps * 1056; }
+
 struct StackLayer {
-    TiledInt4 qkv, o, gate_up, down;
+    const uint8_t *qkv, *o, *gate_up, *down;  // per-CTA streams of the four matrix steps
     const uint16_t *input_norm, *post_norm;
     KvLayer kv;
 };
@@ -140,32 +169,36 @@ struct StackShape {
     float eps, norm_offset, attention_scale;
     const uint32_t *rope_table;  // [position][head_width / 2] packed (sin << 16 | cos) bf16
     uint32_t rope_positions;
+    int grid;                    // CTAs the streams were written for (the device's SM count at mount)
 };
 struct StackBuffers {
     uint16_t *hidden;            // [lanes][hidden] residual stream, updated in place
     uint16_t *q;                 // [lanes][q_heads * head_width]
     float *attention_scratch;    // split partials, attention_scratch_bytes()
-    uint16_t *attention_out;     // [lanes][q_heads * head_width]
-    uint16_t *activation;        // [lanes][ffn]
-    unsigned int *barrier;       // two words, zero before the first launch
-    int *error_flag;             // set when a bounded barrier wait expires
-    unsigned long long *timing;  // optional [layers][32] nanosecond stamps of CTA 0 (phase boundaries), or nullptr
+    uint16_t *attention_out;     // [lanes][q_heads * head_width] fp16 in fragment order (see kernels_stack.cu)
+    uint16_t *activation;        // [lanes][ffn] fp16 in fragment order
+    unsigned int *barrier;       // STACK_BARRIER_WORDS words, zero before the first launch
+    int *error_flag;             // set when a bounded wait expires (2: grid barrier or peer, 3: weight pipeline)
+    unsigned long long *timing;  // optional [layers][32] nanosecond stamps of CTA 0 (step boundaries), or nullptr
 };
+constexpr int STACK_BARRIER_WORDS = 1024;  // two barrier words, then the attention arrival counters (kv heads x lane groups)
 // Tensor-parallel exchange of the persistent kernel: every rank holds the same residual stream and its shard of
-// each layer; the o and down projections leave f32 partial sums in the rank's own exchange buffer, all CTAs of all
-// ranks meet at a two-level barrier (local arrivals, then one system-scope store per peer over NVLink), and every
-// rank then reads everybody's partials (peer memory, plain loads) and adds them up in rank order.
-// Exchange buffer of a rank: [2 parities][8 lanes][hidden] f32.
+// each layer.  The o and down projections push their f32 partial sums into every peer's inbox - value and exchange
+// number in one 8-byte store over NVLink - and the thread that owns an output element waits for the peers' words
+// in its own rank's inbox, then adds all shares in rank order.
+// Inbox of a rank: [2 parities][STACK_TP_MAX_RANKS sources][8 lanes][hidden] 8-byte words.
 constexpr int STACK_TP_MAX_RANKS = 8;
+constexpr int STACK_TP_WORD_CONSUMED = 2;                // control word: exchanges done by earlier launches
+constexpr unsigned int STACK_TP_SPIN_LIMIT = 1u << 25;   // polls of one inbox word: ranks start their launches a host jitter apart
 struct StackTp {
     int rank = 0, size = 1;                            // size 1: no exchange
-    float *exchange[STACK_TP_MAX_RANKS] = {};          // every rank's buffer as seen from this GPU (own entry: local memory)
-    unsigned long long *counter[STACK_TP_MAX_RANKS] = {};  // every rank's 16 control words (arrivals, go, consumed, peers' progress)
+    float *exchange[STACK_TP_MAX_RANKS] = {};          // every rank's inbox as seen from this GPU (own entry: local memory)
+    unsigned long long *counter[STACK_TP_MAX_RANKS] = {};  // every rank's 16 control words
 };
 constexpr size_t STACK_TP_CONTROL_BYTES = 16 * sizeof(unsigned long long);
-inline size_t stack_tp_exchange_floats(int hidden) { return static_cast<size_t>(2) * 8 * hidden; }
+inline size_t stack_tp_exchange_floats(int hidden) { return static_cast<size_t>(2) * STACK_TP_MAX_RANKS * 8 * hidden * 2; }
 
-// One source matrix of a tile-major copy.  rope_head_width > 0 orders the rows of every head so that MMA rows
+// One source matrix of a stream copy.  rope_head_width > 0 orders the rows of every head so that MMA rows
 // r and r + 8 of a tile are the rotary partners (d, d + head_width / 2).
 struct RelayoutSegment {
     const uint32_t *qweight;
@@ -173,10 +206,12 @@ struct RelayoutSegment {
     int rows;
     int rope_head_width;
 };
-// Segments share K; they are laid out one after the other by tiles, or - with `pair` - segment 0 and 1 are
-// interleaved tile by tile (gate, up).  Every segment's row count must be a multiple of 16.
-cudaError_t launch_int4_tile_major(const RelayoutSegment *segments, int count, bool pair, int k, uint4 *weights_out,
-                                   uint32_t *scales_out, cudaStream_t stream);
+// Segments share K; their tiles follow one another, or - with `pair` - segment 0 and 1 are interleaved unit by unit
+// (gate, up).  Every segment's row count must be a multiple of 16.  `rows` of int4_cta_stream_bytes is the sum of
+// the segments' rows (one segment's for a pair).
+size_t int4_cta_stream_bytes(int rows, int k, bool pair, int grid);
+cudaError_t launch_int4_cta_streams(const RelayoutSegment *segments, int count, bool pair, int k, int grid, uint8_t *out,
+                                    cudaStream_t stream);
 // Whether the stack kernel is built for this shape and batch; *smem_bytes receives its dynamic shared memory.
 bool decode_stack_supported(const StackShape &shape, int lanes, size_t *smem_bytes);
 cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count, const StackShape &shape,

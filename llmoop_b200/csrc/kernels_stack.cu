@@ -4,31 +4,37 @@
 // 8 lanes - the verify batch and the draft / single-tick steps of the speculative decode cycle.
 //
 // Why one launch: at these batch sizes a layer is ~112 MB of weights (~17 us of HBM time) cut into a dozen
-// dependent steps; as separate kernels every step pays a launch, a pipeline fill and a drain (~6 us each,
-// measured), which is several times the streaming time.  Here one CTA per SM stays resident, keeps a ring of
-// asynchronous copies of packed weights in flight across step boundaries (weights do not depend on activations,
-// so the next matrix is already streaming while the grid waits at a barrier), and the steps are separated by
-// grid-wide barriers (bounded spins on one global counter).
+// dependent steps; as separate kernels every step pays a launch, a pipeline fill and a drain.  Here one CTA per
+// SM stays resident and the weight stream never stops for a step boundary:
 //
-// Data layout:
-//  * weights: a tile-major copy made at mount - [tile of 16 rows][group of 128 columns][rt][half][lane] uint4,
-//    i.e. exactly the order in which a warp's two 16-byte loads consume them (each load is 512 contiguous
-//    bytes; a tile is K/128 contiguous KB).  q and k tiles pair row d with row d + head_width/2, so RoPE runs in
-//    the q/k/v epilogue and K, V go straight into the KV pages.
-//  * activations of a step: staged once per CTA in shared memory in mma.sync B-fragment order, together with
-//    -24 * sum(x) per (lane, group): the nibbles are fed to the tensor cores as bf16 16+q (one shift and one lop3
-//    per pair, no subtract) and the bias 16+8 is taken out per group by starting the accumulation from that sum.
-//  * a matrix tile is computed by all 16 warps of a CTA (each takes every 16th group of K), reduced through
-//    shared memory, and finished by 128 epilogue threads (one per row and lane).
-//  * attention: a team of four warps per (kv head, 64-token split, lane group) on the tensor cores, partials
-//    merged per (lane, head) by one warp after a barrier.
-//  * tensor parallelism (the EXCHANGE instances): o and down leave f32 partial sums in the rank's exchange buffer;
-//    the ranks meet at a two-level barrier over NVLink and add each other's partials up from peer memory.
-// The per-layer code is one loop over the four matrix steps with run-time matrix / epilogue selection: the
-// straight-line form of the same steps did not fit the instruction cache and spent most of its time refetching.
+//  * weights: at mount every matrix is rewritten as one contiguous byte stream per CTA, in exactly the order the
+//    CTA consumes it (see stack_schedule in kernels.cuh).  A stream is a sequence of stages; a stage is one
+//    16x128 block of packed nibbles (1 KB) plus its 32 bytes of scales for each of up to 16 warps.
+//  * a producer thread (warp 16) walks the CTA's stages of all matrices of all layers and brings them into a ring
+//    in shared memory with one bulk asynchronous copy per stage (mbarrier transaction counts; no cluster forms),
+//    as far ahead as the ring allows - through the grid barriers, the attention step and the epilogues - and asks
+//    L2 for the stages after those (cp.async.bulk.prefetch.L2) so that HBM keeps streaming while the SMs wait on
+//    one another.
+//  * 16 consumer warps: a CTA works on all its tiles of a matrix at once - warp w owns tile slot w / W and every
+//    W-th block of K - so a matrix costs one cross-warp reduction and one epilogue pass per CTA instead of one per
+//    tile.  Nibbles become exact fp16 (q - 8) operands (lop3 into the mantissa of 1024, one fp16 subtract or fma),
+//    eight mma.sync m16n8k16 per block accumulate in f32, the group scale multiplies the block's f32 product as in
+//    linear_int4_ct.comp.template:80-150.
+//  * activations: the inputs of q/k/v and gate/up are normalised (rms_norm_bf16.comp.template:49-72) by every CTA
+//    into shared memory in mma B-fragment order; the inputs of o and down are written by their producers
+//    (attention merge, SiLU epilogue) to global memory already in fragment order and ride the ring, one slice per
+//    stage, once the grid barrier in front of the step has opened.
+//  * attention: a team of four warps per (kv head, 64-token split, lane group) on the tensor cores; the last team
+//    to finish a kv head merges its splits, so there is no separate merge step.
+//  * tensor parallelism (the EXCHANGE instances): o and down push their f32 partial sums, tagged with the exchange
+//    number in the same 8-byte store, into every peer's inbox over NVLink; the owner of an output element waits
+//    for the peers' words in its own memory and adds them in rank order.  No barrier crosses the link.
+//
+// Every wait is bounded: when a bound expires the kernel sets the error word and leaves.
+#include <cuda_fp16.h>
+
 #include <cstdlib>
 
-#include "attention_body.cuh"
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -36,12 +42,21 @@ namespace nerve {
 
 namespace {
 
-constexpr int STACK_WARPS = 16;
-constexpr int STACK_THREADS = STACK_WARPS * 32;
-constexpr int MAX_RING_UNITS = 8;      // 16x128 weight blocks (1 KB + scales) a warp keeps in flight, at most
+constexpr int CONSUMER_WARPS = 16;
+constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
+constexpr int STACK_THREADS = CONSUMER_THREADS + 128;  // + the producer warps (registers are allotted four warps at a time)
+constexpr int UNIT_BYTES = 1024;                      // packed nibbles of a 16x128 block
+constexpr int UNIT_SCALE_BYTES = 32;                  // its eight scale pairs
+constexpr int UNIT_TOTAL = UNIT_BYTES + UNIT_SCALE_BYTES;
+constexpr int STAGE_WEIGHT_BYTES = 16 * UNIT_TOTAL;   // weight part of a ring stage (16 896 bytes)
+constexpr int MAX_STAGES = 16;
 constexpr unsigned int BARRIER_SPIN_LIMIT = 1u << 20;
+constexpr unsigned int PIPE_SPIN_LIMIT = 1u << 18;  // attempts of about 20 us each at most
+constexpr unsigned int OPEN_SPIN_LIMIT = 1u << 28;  // polls of the barrier count by the slice producer: it has to outlast the consumers' own waits
+constexpr int BARRIERS_PER_LAYER = 5;  // after q/k/v, attention, o, gate/up, down
+constexpr int ARRIVAL_WORDS_OFFSET = 16;  // attention arrival counters sit behind the two barrier words
 
-// ------------------------------------------------------------------------------------------ tile-major copy
+// ------------------------------------------------------------------------------------------ per-CTA streams
 
 struct RelayoutArgs {
     RelayoutSegment segment[3];
@@ -49,44 +64,72 @@ struct RelayoutArgs {
     int count;
     int pair;
     int k;
-    int tiles;
+    MatrixSchedule schedule;
 };
 
-__global__ void int4_tile_major_kernel(const RelayoutArgs args, uint4 *__restrict__ weights_out, uint32_t *__restrict__ scales_out) {
-    const int groups = args.k >> 7, rt_count = args.pair ? 2 : 1;
-    const size_t total = static_cast<size_t>(args.tiles) * groups * rt_count * 64;
-    for (size_t index = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; index < total;
-         index += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const int lane = static_cast<int>(index & 31), half = static_cast<int>((index >> 5) & 1);
-        size_t rest = index >> 6;
-        const int rt = static_cast<int>(rest % rt_count);
-        rest /= rt_count;
-        const int group = static_cast<int>(rest % groups), tile = static_cast<int>(rest / groups);
-        const int g = lane >> 2, j = lane & 3;
-        int which = 0, local_tile = tile;
+// Block (stage, cta) writes one stage of one CTA's stream: the present units' nibbles, then their scale pairs.
+__global__ void int4_cta_stream_kernel(const RelayoutArgs args, uint8_t *__restrict__ out) {
+    const MatrixSchedule &s = args.schedule;
+    const int cta = blockIdx.y, stage = blockIdx.x;
+    const int here = stack_cta_tiles(s, cta);
+    const int pass = stage / s.steps, step = stage % s.steps;
+    int present = here - pass * s.slots;
+    if (present <= 0) return;
+    if (present > s.slots) present = s.slots;
+    const int groups = args.k >> 7;
+    uint8_t *base = out + stack_cta_offset(s, cta) + static_cast<size_t>(pass) * s.slots * s.width * s.steps * UNIT_TOTAL +
+                    static_cast<size_t>(step) * present * s.width * UNIT_TOTAL;
+    uint4 *weights_out = reinterpret_cast<uint4 *>(base);
+    uint32_t *scales_out = reinterpret_cast<uint32_t *>(base + static_cast<size_t>(present) * s.width * UNIT_BYTES);
+    auto locate = [&](int unit_in_stage, int &group, int &which, int &local_tile) {
+        const int slot = unit_in_stage / s.width, i = unit_in_stage % s.width;
+        const int unit = step * s.width + i;
+        if (unit >= s.units) return false;  // padding of a ragged last step: zero nibbles under zero scales
+        group = unit / s.rt;
+        const int tile = cta + (pass * s.slots + slot) * s.grid;
+        which = 0;
+        local_tile = tile;
         if (args.pair) {
-            which = rt;
+            which = unit % s.rt;
         } else {
             while (which + 1 < args.count && tile >= args.first_tile[which + 1]) which++;
             local_tile = tile - args.first_tile[which];
         }
-        const RelayoutSegment &segment = args.segment[which];
-        auto source_row = [&](int mma_row) {
-            if (segment.rope_head_width > 0) {
-                const int tiles_per_head = segment.rope_head_width / 16;
-                const int head = local_tile / tiles_per_head, th = local_tile % tiles_per_head;
-                const int d = mma_row < 8 ? 8 * th + mma_row : segment.rope_head_width / 2 + 8 * th + (mma_row - 8);
-                return head * segment.rope_head_width + d;
-            }
-            return local_tile * 16 + mma_row;
-        };
-        const int row = source_row(g + 8 * half);
-        weights_out[index] = *reinterpret_cast<const uint4 *>(segment.qweight + static_cast<size_t>(row) * (args.k >> 3) + group * 16 + j * 4);
-        if (half == 0 && j == 0) {
-            const uint32_t low = segment.scales[static_cast<size_t>(row) * groups + group];
-            const uint32_t high = segment.scales[static_cast<size_t>(source_row(g + 8)) * groups + group];
-            scales_out[(static_cast<size_t>(tile) * groups + group) * rt_count * 8 + rt * 8 + g] = low | (high << 16);
+        return true;
+    };
+    auto source_row = [&](const RelayoutSegment &segment, int local_tile, int mma_row) {
+        if (segment.rope_head_width > 0) {
+            const int tiles_per_head = segment.rope_head_width / 16;
+            const int head = local_tile / tiles_per_head, th = local_tile % tiles_per_head;
+            const int d = mma_row < 8 ? 8 * th + mma_row : segment.rope_head_width / 2 + 8 * th + (mma_row - 8);
+            return head * segment.rope_head_width + d;
         }
+        return local_tile * 16 + mma_row;
+    };
+    const int units = present * s.width;
+    for (int index = threadIdx.x; index < units * 64; index += blockDim.x) {
+        const int unit_in_stage = index >> 6, half = (index >> 5) & 1, lane = index & 31;
+        const int g = lane >> 2, j = lane & 3;
+        int group = 0, which = 0, local_tile = 0;
+        uint4 value = make_uint4(0, 0, 0, 0);
+        if (locate(unit_in_stage, group, which, local_tile)) {
+            const RelayoutSegment &segment = args.segment[which];
+            const int row = source_row(segment, local_tile, g + 8 * half);
+            value = *reinterpret_cast<const uint4 *>(segment.qweight + static_cast<size_t>(row) * (args.k >> 3) + group * 16 + j * 4);
+        }
+        weights_out[index] = value;
+    }
+    for (int index = threadIdx.x; index < units * 8; index += blockDim.x) {
+        const int unit_in_stage = index >> 3, g = index & 7;
+        int group = 0, which = 0, local_tile = 0;
+        uint32_t value = 0;
+        if (locate(unit_in_stage, group, which, local_tile)) {
+            const RelayoutSegment &segment = args.segment[which];
+            const uint32_t low = segment.scales[static_cast<size_t>(source_row(segment, local_tile, g)) * groups + group];
+            const uint32_t high = segment.scales[static_cast<size_t>(source_row(segment, local_tile, g + 8)) * groups + group];
+            value = low | (high << 16);
+        }
+        scales_out[index] = value;
     }
 }
 
@@ -99,27 +142,36 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-// The same with a zero accumulator coming in (starts a chain without clearing registers first).
-__device__ __forceinline__ void mma_bf16_16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                                     uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
-        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+__device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Nibble pair k of `word` (bits 4k..4k+3 and 16+4k..16+4k+3) -> bf16x2 (16 + q, 16 + q'): with the nibble in
-// mantissa bits 3..6 under exponent 2^4, 0x4180 | q << 3 is exactly 16 + q.  One shift and one lop3 per pair; the
-// offset 16 (+ 8 of the symmetric INT4 code) leaves the accumulator as 24 * sum(x) per group, taken out afterwards.
-template <int PAIR>
-__device__ __forceinline__ uint32_t biased_pair(uint32_t word) {
-    uint32_t out;
-    const uint32_t aligned = PAIR == 0 ? word << 3 : word >> (4 * PAIR - 3);
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(out) : "r"(aligned), "n"(0x00780078), "n"(0x41804180));
+// Two nibbles of `word` (bits 0..3 and 16..19) -> fp16x2 (q - 8, q' - 8), exactly: the nibble lands in the low
+// mantissa bits of 1024.0 (0x6400), 1032 is subtracted.
+__device__ __forceinline__ uint32_t nibbles_low(uint32_t word) {
+    uint32_t biased, out;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(biased) : "r"(word), "n"(0x000F000F), "n"(0x64006400));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(out) : "r"(biased), "r"(0x64086408u));
     return out;
 }
-constexpr float NIBBLE_BIAS = 24.0f;
+// The nibbles at bits 4..7 and 20..23: 1024 + 16 q, times 1/16, minus 72 (one fused multiply-add, exact).
+__device__ __forceinline__ uint32_t nibbles_high(uint32_t word) {
+    uint32_t biased, out;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(biased) : "r"(word), "n"(0x00F000F0), "n"(0x64006400));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(out) : "r"(biased), "r"(0x2C002C00u), "r"(0xD480D480u));
+    return out;
+}
+
+// bf16 values (already rounded) as an fp16 pair: exact for magnitudes in [2^-14, 65504]; the activations of a
+// decoder layer (normalised rows, attention outputs, SiLU products) live there.
+__device__ __forceinline__ uint32_t half_pair(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
 
 __device__ __forceinline__ uint32_t load_acquire(const unsigned int *address) {
     uint32_t value;
@@ -127,11 +179,14 @@ __device__ __forceinline__ uint32_t load_acquire(const unsigned int *address) {
     return value;
 }
 
-// All CTAs of the (cooperative, co-resident) grid meet here.  `target` counts the arrivals expected so far.  A
-// wait that does not complete within the spin limit sets the error flag and lets the CTA go on (its results are
-// then garbage, the host sees the flag); once the flag is up nobody waits any more.
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
+__device__ __forceinline__ void team_barrier(int barrier_id) { asm volatile("bar.sync %0, 128;" ::"r"(barrier_id) : "memory"); }
+
+// All CTAs of the (cooperative, co-resident) grid meet here; only the consumer warps take part.  `target` counts
+// the arrivals expected so far.  A wait that does not complete within the spin limit sets the error flag and lets
+// the CTA go on (its results are then garbage, the host sees the flag); once the flag is up nobody waits any more.
 __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int &target, int *error_flag) {
-    __syncthreads();
+    consumer_sync();
     if (threadIdx.x == 0) {
         target += gridDim.x;
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");  // covers the CTA's writes before the barrier above
@@ -144,162 +199,53 @@ __device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int
             if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) break;
         }
     }
-    __syncthreads();
+    consumer_sync();
 }
 
-// All CTAs of all tensor-parallel ranks meet here, in two levels: the CTAs of this GPU count themselves in on a
-// local word; the last one to arrive tells every peer (one system-scope store of the exchange number per peer, over
-// NVLink); every CTA then waits until all local CTAs and every peer have done so.  One remote write per peer and
-// exchange: arrivals of 148 CTAs on one remote word would queue up on the link.  `exchange_number` counts the
-// exchanges of this and all earlier launches; all words only grow.  What the CTAs wrote into their rank's exchange
-// buffer before the call is visible to the peers after it.  Every wait is bounded; a rank that never shows up ends
-// the launch with the error flag set.
-// Control words of a rank (unsigned long long, behind its exchange buffer): [0] local arrivals, [1] unused,
-// [2] exchanges consumed by earlier launches, [8 + s] the exchange number rank s has reached.
-constexpr unsigned int EXCHANGE_SPIN_LIMIT = 1u << 24;  // about ten seconds of polling: ranks start their launches a host jitter apart
-constexpr int TP_WORD_ARRIVALS = 0, TP_WORD_GO = 1, TP_WORD_CONSUMED = 2, TP_WORD_PEER = 8;
-
-__device__ __forceinline__ unsigned long long load_acquire_sys(const unsigned long long *address) {
-    unsigned long long value;
-    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(value) : "l"(address) : "memory");
+// ---- mbarrier / bulk copy (shared-space addresses)
+__device__ __forceinline__ void mbarrier_init(uint32_t address, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(address), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbarrier_arrive(uint32_t address) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(address) : "memory");
+}
+__device__ __forceinline__ void mbarrier_arrive_expect(uint32_t address, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(address), "r"(bytes) : "memory");
+}
+// One attempt at waiting for the phase of the given parity: the thread is suspended by the hardware until the
+// phase completes or about `MBARRIER_SUSPEND_NS` have passed, so a waiting warp issues almost nothing.
+constexpr uint32_t MBARRIER_SUSPEND_NS = 20000;
+__device__ __forceinline__ bool mbarrier_test(uint32_t address, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(address), "r"(parity), "r"(MBARRIER_SUSPEND_NS)
+        : "memory");
+    return done != 0;
+}
+// global -> this CTA's shared memory, completion counted in bytes on `barrier`
+__device__ __forceinline__ void bulk_load(uint32_t destination, const void *source, uint32_t bytes, uint32_t barrier) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(destination),
+                 "l"(__cvta_generic_to_global(source)), "r"(bytes), "r"(barrier)
+                 : "memory");
+}
+__device__ __forceinline__ void prefetch_l2(const void *address, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(address)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t shared_load_acquire(uint32_t address) {
+    uint32_t value;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(value) : "r"(address) : "memory");
     return value;
 }
-__device__ __forceinline__ unsigned long long load_acquire_gpu(const unsigned long long *address) {
-    unsigned long long value;
-    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(value) : "l"(address) : "memory");
-    return value;
+__device__ __forceinline__ void shared_store_release(uint32_t address, uint32_t value) {
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(address), "r"(value) : "memory");
 }
-
-__device__ __noinline__ void exchange_barrier(const StackTp &tp, unsigned long long &exchange_number, int *error_flag) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        exchange_number += 1;
-        unsigned long long *mine = tp.counter[tp.rank];
-        // release: the CTA's writes before the barrier above; acquire: the last to arrive takes over everybody's
-        unsigned long long before;
-        asm volatile("atom.acq_rel.gpu.global.add.u64 %0, [%1], 1;" : "=l"(before) : "l"(mine + TP_WORD_ARRIVALS) : "memory");
-        unsigned int spins = 0;
-        bool gave_up = false;
-        if (before + 1 == exchange_number * gridDim.x) {
-            // the last CTA of this GPU: everything this rank wrote for the exchange is in memory; the system-scope
-            // release stores publish it to the peers
-            for (int r = 0; r < tp.size; r++)
-                if (r != tp.rank)
-                    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(tp.counter[r] + TP_WORD_PEER + tp.rank), "l"(exchange_number) : "memory");
-        }
-        // every CTA waits for the same two things itself (no hop through a go word): all CTAs of this GPU have
-        // arrived, and every peer has said so of its own
-        const unsigned long long all_here = exchange_number * gridDim.x;
-        while (!gave_up && load_acquire_gpu(mine + TP_WORD_ARRIVALS) < all_here) {
-            if (++spins > EXCHANGE_SPIN_LIMIT) {
-                atomicExch(error_flag, 2);
-                gave_up = true;
-            } else if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) {
-                gave_up = true;
-            }
-        }
-        for (int r = 0; r < tp.size && !gave_up; r++) {
-            if (r == tp.rank) continue;
-            while (load_acquire_sys(mine + TP_WORD_PEER + r) < exchange_number) {
-                if (++spins > EXCHANGE_SPIN_LIMIT) {
-                    atomicExch(error_flag, 2);
-                    gave_up = true;
-                    break;
-                }
-                if ((spins & 63u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) {
-                    gave_up = true;
-                    break;
-                }
-            }
-        }
-    }
-    __syncthreads();
-}
-
-// After an exchange: hidden = bf16(bf16(sum over ranks of the partial sums) + hidden) for this CTA's share of the
-// [lanes][width] elements, four at a time (add_bf16.comp.template:17-24 on the all-reduced linear output).  Every
-// rank keeps its own partial sums in its own buffer and the others read them from there (peer loads, all in flight
-// at once: one NVLink round trip).  The partials are added in rank order on every rank, so the replicated residual
-// streams stay bit-identical.
-__device__ __noinline__ void reduce_exchanged(const StackTp &tp, int parity, uint16_t *hidden, int lanes, int width) {
-    const int per_lane = width >> 2, items = lanes * per_lane;
-    for (int item = blockIdx.x * STACK_THREADS + threadIdx.x; item < items; item += gridDim.x * STACK_THREADS) {
-        const int m = item / per_lane, quad = item - m * per_lane;
-        const size_t offset = (static_cast<size_t>(parity) * 8 + m) * per_lane + quad;
-        float4 part[STACK_TP_MAX_RANKS];
-#pragma unroll
-        for (int r = 0; r < STACK_TP_MAX_RANKS; r++)
-            if (r < tp.size) part[r] = __ldcg(reinterpret_cast<const float4 *>(tp.exchange[r]) + offset);
-        uint2 *destination = reinterpret_cast<uint2 *>(hidden) + static_cast<size_t>(m) * per_lane + quad;
-        const uint2 residual = __ldcg(destination);
-        float4 sum = part[0];
-#pragma unroll
-        for (int r = 1; r < STACK_TP_MAX_RANKS; r++)
-            if (r < tp.size) {
-                sum.x += part[r].x;
-                sum.y += part[r].y;
-                sum.z += part[r].z;
-                sum.w += part[r].w;
-            }
-        uint2 out;
-        out.x = pack_bf16(round_bf16(sum.x) + bf16_lo(residual.x), round_bf16(sum.y) + bf16_hi(residual.x));
-        out.y = pack_bf16(round_bf16(sum.z) + bf16_lo(residual.y), round_bf16(sum.w) + bf16_hi(residual.y));
-        *destination = out;
-    }
-}
-
-// Shared-memory carve-up of the matrix phases.
-struct StackSmem {
-    uint4 *fragments;    // [groups][4 words][staged lanes][4] activations in B-fragment order
-    uint16_t *rows;      // [staged lanes][hidden] normalised rows before they are permuted
-    float *correction;   // [groups][8] -24 * sum(x) per lane
-    float *reduce;       // [2][warps][32 rows][8]
-    float *partial;      // [8 lanes][warps]
-    uint8_t *ring;       // [warps][RING_UNITS][RING_UNIT_BYTES] packed weights in flight (asynchronous copies)
-};
-
-// ------------------------------------------------------------------------------------------ weight stream
-// Every thread copies its own 2 x 16 bytes of packed weights and its 4-byte scale pair of a 16x128 block with
-// cp.async and later reads back exactly those bytes, so no thread waits on another: cp.async.wait_group is the
-// only synchronisation.  Copy groups complete in issue order and blocks are consumed in issue order, also
-// across matrices, so "all but the newest n groups" is always the right thing to wait for.  A warp's producer
-// cursor runs ahead of its consumer by up to RING_UNITS blocks and crosses into the next matrix as soon as the
-// current one is fully requested: the next phase's first weights are in flight while the grid is still at the
-// barrier in front of it.
-
-constexpr int RING_UNIT_BYTES = 2 * 512 + 128;
-
-// cp.async with shared-space destination addresses and byte offsets folded into the instruction.
-template <int DST_OFFSET, int SRC_OFFSET>
-__device__ __forceinline__ void async_copy16(uint32_t shared_address, const void *source) {
-    asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;" ::"r"(shared_address), "l"(source), "n"(DST_OFFSET), "n"(SRC_OFFSET) : "memory");
-}
-template <int SRC_OFFSET>
-__device__ __forceinline__ void async_copy4(uint32_t shared_address, const void *source) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1+%2], 4;" ::"r"(shared_address), "l"(source), "n"(SRC_OFFSET) : "memory");
-}
-__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// Waits until at most `newer` of this thread's copy groups are still in flight.
-__device__ __forceinline__ void async_wait(int newer) {
-    switch (newer) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
-    }
-}
-
-// Waits for the oldest of this thread's `in_flight` (>= 1) copy groups; the usual depths are tested first.
-__device__ __forceinline__ void async_wait_oldest(int in_flight) {
-    if (in_flight == 4) asm volatile("cp.async.wait_group 3;" ::: "memory");
-    else if (in_flight == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
-    else async_wait(in_flight - 1);
-}
-// Shared-memory loads by shared-space address (32-bit address arithmetic, offsets folded into the instruction).
+// Shared-memory loads by shared-space address (kept in program order behind the waits that make their data valid).
 template <int OFFSET>
 __device__ __forceinline__ uint4 shared_load16(uint32_t address) {
     uint4 v;
@@ -311,210 +257,234 @@ __device__ __forceinline__ uint32_t shared_load4(uint32_t address) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address) : "memory");
     return v;
 }
-__device__ __forceinline__ float2 shared_load_float2(uint32_t address) {
-    float2 v;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(address) : "memory");
-    return v;
-}
 
-// One matrix as a warp sees it: for each of the CTA's tiles (blockIdx.x, += gridDim.x) the warp's groups
-// (warp, += 16); an item is `rt` ring units (rt = 2 for a gate/up pair).
-struct MatrixWalk {
-    TiledInt4 matrix;
-    int rt, per_tile, tiles, total;
-};
-__device__ __forceinline__ MatrixWalk walk_of(const TiledInt4 &matrix, int rt) {
-    const int warp = threadIdx.x >> 5;
-    MatrixWalk walk;
-    walk.matrix = matrix;
-    walk.rt = rt;
-    walk.per_tile = matrix.groups > warp ? (matrix.groups - warp + STACK_WARPS - 1) / STACK_WARPS : 0;
-    walk.tiles = matrix.tiles > static_cast<int>(blockIdx.x)
-                     ? (matrix.tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
-                     : 0;
-    walk.total = walk.per_tile * walk.tiles;
-    return walk;
-}
 
-struct WeightStream {
-    uint32_t ring_begin, ring_end;  // shared-space address of this thread's 16 bytes (first half) of ring unit 0 / one past the last unit
-    uint32_t head, tail;            // the same position in the unit to consume next / to request next
-    uint32_t scale_offset;          // from there to this thread's scale word: 1024 + lane * 4 - lane * 16
-    int units;                      // ring units of this warp (2..MAX_RING_UNITS, as shared memory allows)
-    int used;                       // units requested and not yet consumed
-    int in_flight;                  // items (copy groups) requested and not yet consumed
-    // producer: the matrix being requested from, and the position in it
-    int source_phase, rt, per_tile, remaining, gi;
-    const uint4 *weights;           // the matrix, moved on by this thread's lane: + offset = its 16 bytes of the next block
-    const uint32_t *scales;         // the scale pairs, moved on by lane / 4: + (offset >> 3) = this thread's pair of that block
-    uint32_t offset;                // in 16-byte words; one block is 64 of them
-    uint32_t step, tile_step;       // to the warp's next block inside a tile / to its first block of the CTA's next tile
-    MatrixWalk following;           // the matrix after it (valid when has_following)
-    bool has_following;
+// ------------------------------------------------------------------------------------------ the CTA's view of a matrix
+
+struct PhaseInfo {
+    int tiles_here;       // 16-row tiles of this CTA (tile = cta + i * grid)
+    int passes;           // rounds of `slots` tiles
+    int slots, width, steps, units, rt, groups;
+    uint32_t cta_offset;  // bytes from the matrix's stream to this CTA's share
+    int streamed;         // the activations ride the ring (o, down)
 };
 
-__device__ __forceinline__ void stream_start(WeightStream &stream, const MatrixWalk &walk, int phase) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    stream.source_phase = phase;
-    stream.rt = walk.rt;
-    stream.per_tile = walk.per_tile;
-    stream.remaining = walk.total;
-    stream.gi = 0;
-    stream.weights = walk.matrix.weights + lane;
-    stream.scales = walk.matrix.scales + (lane >> 2);
-    stream.offset = (blockIdx.x * static_cast<uint32_t>(walk.matrix.groups) + warp) * walk.rt * 64u;
-    stream.step = static_cast<uint32_t>(STACK_WARPS) * walk.rt * 64u;
-    stream.tile_step = (gridDim.x * static_cast<uint32_t>(walk.matrix.groups) - (walk.per_tile - 1) * STACK_WARPS) * walk.rt * 64u;
+struct StackArgs {
+    const StackLayer *layers;
+    int layer_count;
+    StackShape shape;
+    StackBuffers buffers;
+    LaneTable lanes_meta;
+    int lanes, lanes_per_stream, max_splits;
+    int stages, stage_bytes, prefetch_stages, debug_flags;
+    int steps_per_stage;                 // consecutive steps of a pass that travel as one ring stage (1 or 2)
+    int slice_slots, slice_bytes;        // ring of activation slices (o, down) inside the scratch area
+    uint32_t scratch_bytes;
+    const StackTp *tp;  // device copy of the exchange description, or nullptr (single GPU)
+    int tp_size;
+};
+
+__device__ __forceinline__ const uint8_t *layer_stream(const StackLayer &layer, int phase) {
+    return phase == 0 ? layer.qkv : (phase == 1 ? layer.o : (phase == 2 ? layer.gate_up : layer.down));
 }
 
-// Requests the producer's next item of RT units (the ring has room and the matrix has items left).
-template <int RT>
-__device__ __forceinline__ void stream_issue_item(WeightStream &stream) {
-    const uint4 *source = stream.weights + stream.offset;
-    const uint32_t *scale_source = stream.scales + (stream.offset >> 3);
-#pragma unroll
-    for (int r = 0; r < RT; r++) {
-        if (r == 0) {
-            async_copy16<0, 0>(stream.tail, source);
-            async_copy16<512, 512>(stream.tail, source);
-            async_copy4<0>(stream.tail + stream.scale_offset, scale_source);
-        } else {
-            async_copy16<0, 1024>(stream.tail, source);
-            async_copy16<512, 1536>(stream.tail, source);
-            async_copy4<32>(stream.tail + stream.scale_offset, scale_source);
-        }
-        stream.tail += RING_UNIT_BYTES;
-        if (stream.tail == stream.ring_end) stream.tail = stream.ring_begin;
-    }
-    async_commit();
-    stream.used += RT;
-    stream.in_flight++;
-    stream.remaining--;
-    // next block of this warp: 16 groups on, or the first group of the CTA's next tile
-    uint32_t advance = stream.step;
-    if (++stream.gi == stream.per_tile) {
-        stream.gi = 0;
-        advance = stream.tile_step;
-    }
-    stream.offset += advance;
-}
-__device__ __forceinline__ void stream_issue(WeightStream &stream) {
-    if (stream.rt == 2) stream_issue_item<2>(stream);
-    else stream_issue_item<1>(stream);
+__device__ __forceinline__ int stage_present(const PhaseInfo &pi, int pass) {
+    const int left = pi.tiles_here - pass * pi.slots;
+    return left < pi.slots ? left : pi.slots;
 }
 
-// Requests as many blocks as the ring has room for, moving on to the following matrix when this one is done.
-__device__ __forceinline__ void stream_advance(WeightStream &stream) {
-    while (true) {
-        if (stream.remaining == 0) {
-            if (!stream.has_following) break;
-            stream_start(stream, stream.following, stream.source_phase + 1);
-            stream.has_following = false;
-            continue;
+// ------------------------------------------------------------------------------------------ producers
+// Three single threads (lane 0 of warps 16, 17, 18) walk the CTA's stage sequence - for every layer the four
+// matrices, for every matrix its passes and steps - each on its own: one requests the weights of a stage, one the
+// activation slice of the stages of o and down (once the grid barrier in front of the step has opened), one asks
+// L2 for stages further ahead.  A stage's slot is free when the consumer warps have released its previous use
+// (the `empty` barrier); its `full` barrier completes with two arrivals plus the bytes of the copies.
+
+struct RingAddresses {
+    uint32_t ring, full, empty;                       // weight stages (shared-space addresses)
+    uint32_t slices, slice_full, slice_empty;         // activation slices of the o and down steps
+    uint32_t open_word, issued_word;
+};
+
+struct RingPosition {
+    uint32_t slot, parity;  // parity of the `empty` phase that frees the slot for the next use
+};
+__device__ __forceinline__ void ring_advance(RingPosition &position, uint32_t stages) {
+    if (++position.slot == stages) {
+        position.slot = 0;
+        position.parity ^= 1u;
+    }
+}
+__device__ __forceinline__ void ring_skip(RingPosition &position, uint32_t count, uint32_t stages) {
+    const uint32_t to = position.slot + count;
+    position.parity ^= (to / stages) & 1u;
+    position.slot = to % stages;
+}
+// false: gave up (the error flag is set, or was set by somebody else)
+__device__ __forceinline__ bool wait_slot_free(uint32_t empty_address, const RingPosition &position, int *error_flag) {
+    unsigned int spins = 0;
+    while (!mbarrier_test(empty_address + position.slot * 8, position.parity)) {
+        if (++spins > PIPE_SPIN_LIMIT) {
+            atomicExch(error_flag, 3);
+            return false;
         }
-        if (stream.units - stream.used < stream.rt) break;
-        stream_issue(stream);
+        if ((spins & 255u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) return false;
+    }
+    return true;
+}
+// After giving up: let the copies that are still in flight land before the CTA's shared memory goes away.
+__device__ __forceinline__ void linger() {
+    for (int i = 0; i < 64; i++) __nanosleep(1000);
+}
+
+__device__ __noinline__ void produce_weights(const StackArgs &a, const PhaseInfo *info, const RingAddresses &ring) {
+    int *error_flag = a.buffers.error_flag;
+    RingPosition position{0u, 1u};
+    uint32_t issued = 0;
+    for (int layer = 0; layer < a.layer_count; layer++) {
+        const StackLayer *spec = a.layers + layer;
+        for (int phase = 0; phase < 4; phase++) {
+            const PhaseInfo pi = info[phase];
+            if (pi.passes == 0) continue;
+            const uint8_t *source = layer_stream(*spec, phase) + pi.cta_offset;
+            for (int pass = 0; pass < pi.passes; pass++) {
+                const uint32_t step_bytes = static_cast<uint32_t>(stage_present(pi, pass) * pi.width * UNIT_TOTAL);
+                for (int step = 0; step < pi.steps; step += a.steps_per_stage) {
+                    const int count = pi.steps - step < a.steps_per_stage ? pi.steps - step : a.steps_per_stage;
+                    const uint32_t bytes = step_bytes * static_cast<uint32_t>(count);
+                    if (!wait_slot_free(ring.empty, position, error_flag)) return linger();
+                    const uint32_t full = ring.full + position.slot * 8;
+                    if ((a.debug_flags & 4) && issued >= static_cast<uint32_t>(a.stages)) {
+                        mbarrier_arrive(full);  // timing probe: the consumers work on what the slot already holds
+                    } else {
+                        mbarrier_arrive_expect(full, bytes);
+                        bulk_load(ring.ring + position.slot * static_cast<uint32_t>(a.stage_bytes), source, bytes, full);
+                    }
+                    source += bytes;
+                    ring_advance(position, static_cast<uint32_t>(a.stages));
+                    if (a.debug_flags & 4) issued++;
+                    if (a.prefetch_stages > 0) asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(ring.issued_word), "r"(++issued) : "memory");
+                }
+            }
+        }
     }
 }
 
-// Asks the memory system to bring the CTA's tiles of a matrix into L2 (no registers or shared memory are tied
-// up, nothing waits on it): issued one step ahead, so that HBM keeps streaming through the barriers, the staging
-// and the attention of the step in between and the ring's copies then find their bytes in L2.
-__device__ __forceinline__ void prefetch_l2(const void *address, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(address)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void prefetch_matrix_l2(const TiledInt4 &matrix, int rt) {
-    constexpr uint32_t PIECE = 16384;
-    const uint32_t tile_bytes = static_cast<uint32_t>(matrix.groups) * rt * 1024u, pieces = (tile_bytes + PIECE - 1) / PIECE;
-    const int tiles = matrix.tiles > static_cast<int>(blockIdx.x)
-                          ? (matrix.tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
-                          : 0;
-    for (uint32_t index = threadIdx.x; index < tiles * (pieces + 1); index += STACK_THREADS) {
-        const uint32_t t = index / (pieces + 1), piece = index % (pieces + 1);
-        const size_t tile = blockIdx.x + static_cast<size_t>(t) * gridDim.x;
-        if (piece == pieces) {
-            prefetch_l2(matrix.scales + tile * matrix.groups * rt * 8, static_cast<uint32_t>(matrix.groups) * rt * 32u);
-        } else {
-            const uint32_t offset = piece * PIECE, bytes = tile_bytes - offset < PIECE ? tile_bytes - offset : PIECE;
-            prefetch_l2(reinterpret_cast<const uint8_t *>(matrix.weights + tile * matrix.groups * rt * 64) + offset, bytes);
+__device__ __noinline__ void produce_activations(const StackArgs &a, const PhaseInfo *info, const RingAddresses &ring, int staged) {
+    int *error_flag = a.buffers.error_flag;
+    RingPosition position{0u, 1u};  // in the ring of slices: only the stages of o and down count
+    const uint32_t slice_group_bytes = static_cast<uint32_t>(staged) * 256u;
+    for (int layer = 0; layer < a.layer_count; layer++) {
+        for (int phase = 1; phase < 4; phase += 2) {
+            const PhaseInfo pi = info[phase];
+            if (pi.passes == 0) continue;
+            // the slices were written by other CTAs with ordinary stores before the grid barrier counted here; the
+            // scratch area they land in is free once this CTA's consumers have passed that barrier, too
+            const uint32_t needed = static_cast<uint32_t>(layer * BARRIERS_PER_LAYER + (phase == 1 ? 2 : 4));
+            unsigned int spins = 0;
+            while (shared_load_acquire(ring.open_word) < needed) {
+                if (++spins > OPEN_SPIN_LIMIT) {
+                    atomicExch(error_flag, 3);
+                    return linger();
+                }
+                if ((spins & 255u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) return linger();
+                __nanosleep(20);
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");  // ... and the copy engine reads them
+            const uint8_t *base = reinterpret_cast<const uint8_t *>(phase == 1 ? a.buffers.attention_out : a.buffers.activation);
+            const int groups_per_stage = pi.width * a.steps_per_stage;
+            for (int pass = 0; pass < pi.passes; pass++) {
+                for (int first_group = 0; first_group < pi.steps * pi.width; first_group += groups_per_stage) {
+                    if (!wait_slot_free(ring.slice_empty, position, error_flag)) return linger();
+                    int groups = pi.groups - first_group;
+                    if (groups > groups_per_stage) groups = groups_per_stage;
+                    const uint32_t full = ring.slice_full + position.slot * 8;
+                    if (groups > 0) {
+                        const uint32_t bytes = static_cast<uint32_t>(groups) * slice_group_bytes;
+                        mbarrier_arrive_expect(full, bytes);
+                        bulk_load(ring.slices + position.slot * static_cast<uint32_t>(a.slice_bytes), base + static_cast<size_t>(first_group) * slice_group_bytes,
+                                  bytes, full);
+                    } else {
+                        mbarrier_arrive(full);  // a stage of padding only
+                    }
+                    ring_advance(position, static_cast<uint32_t>(a.slice_slots));
+                }
+            }
         }
+    }
+}
+
+// Keeps `prefetch_stages` stages beyond the last requested one on their way into L2.
+__device__ __noinline__ void produce_prefetches(const StackArgs &a, const PhaseInfo *info, const RingAddresses &ring) {
+    int *error_flag = a.buffers.error_flag;
+    uint32_t index = 0;
+    for (int layer = 0; layer < a.layer_count; layer++) {
+        const StackLayer *spec = a.layers + layer;
+        for (int phase = 0; phase < 4; phase++) {
+            const PhaseInfo pi = info[phase];
+            if (pi.passes == 0) continue;
+            const uint8_t *source = layer_stream(*spec, phase) + pi.cta_offset;
+            for (int pass = 0; pass < pi.passes; pass++) {
+                const uint32_t step_bytes = static_cast<uint32_t>(stage_present(pi, pass) * pi.width * UNIT_TOTAL);
+                for (int step = 0; step < pi.steps; step += a.steps_per_stage, index++) {
+                    const int count = pi.steps - step < a.steps_per_stage ? pi.steps - step : a.steps_per_stage;
+                    const uint32_t bytes = step_bytes * static_cast<uint32_t>(count);
+                    unsigned int spins = 0;
+                    uint32_t issued;
+                    while (true) {
+                        asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(issued) : "r"(ring.issued_word) : "memory");
+                        if (index < issued + static_cast<uint32_t>(a.prefetch_stages)) break;
+                        if (++spins > OPEN_SPIN_LIMIT || ((spins & 255u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0)) return;
+                        __nanosleep(100);
+                    }
+                    if (index >= issued + static_cast<uint32_t>(a.stages)) prefetch_l2(source, bytes);  // nearer stages are being loaded already
+                    source += bytes;
+                }
+            }
+        }
+    }
+}
+
+// Consumer side of the ring: waits (bounded) until stage `slot` holds its data.
+__device__ __forceinline__ void wait_stage(uint32_t full_address, uint32_t parity, int *error_flag) {
+    unsigned int spins = 0;
+    while (!mbarrier_test(full_address, parity)) {
+        if (++spins > PIPE_SPIN_LIMIT) {
+            atomicExch(error_flag, 3);
+            break;
+        }
+        if ((spins & 255u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) break;
     }
 }
 
 // ------------------------------------------------------------------------------------------ activation staging
 
-// A chunk is a uint4 of 8 consecutive bf16 of one lane; 16 consecutive chunks are one group of 128 columns.
-// Chunk c of lane m -> fragment slot of thread (g = m, j) for word w, with group = c / 16, j = (c / 4) % 4,
-// w = c % 4, is ((group * 4 + w) * staged + m) * 4 + j and holds (v0,v4) (v1,v5) (v2,v6) (v3,v7): the B operands of
-// the two MMAs that consume nibble pairs (0,4) (1,5) and (2,6) (3,7) of the matching weight word.
-__device__ __forceinline__ void stage_chunk(const StackSmem &sm, uint4 raw, bool active, int m, int chunk, int staged) {
+// Chunk c (8 consecutive columns) of lane m -> the fragment slot of thread (g = m, j) for word w, with
+// group = c / 16, j = (c / 4) % 4, w = c % 4: uint4 index ((group * 4 + w) * staged + m) * 4 + j, holding the fp16
+// pairs (v0,v4) (v1,v5) (v2,v6) (v3,v7) - the B operands of the MMAs that consume nibble pairs (0,4) (1,5) and
+// (2,6) (3,7) of the matching weight word.
+__device__ __forceinline__ int fragment_index(int chunk, int m, int staged) {
     const int group = chunk >> 4, j = (chunk >> 2) & 3, word = chunk & 3;
-    float sum = 0.0f;
-    if (active) {
-        uint4 out;
-        out.x = __byte_perm(raw.x, raw.z, 0x5410);
-        out.y = __byte_perm(raw.x, raw.z, 0x7632);
-        out.z = __byte_perm(raw.y, raw.w, 0x5410);
-        out.w = __byte_perm(raw.y, raw.w, 0x7632);
-        sm.fragments[((group * 4 + word) * staged + m) * 4 + j] = out;
-        sum = bf16_lo(raw.x) + bf16_hi(raw.x) + bf16_lo(raw.y) + bf16_hi(raw.y) + bf16_lo(raw.z) + bf16_hi(raw.z) + bf16_lo(raw.w) +
-              bf16_hi(raw.w);
-    }
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 8);
-    if (active && (chunk & 15) == 0) sm.correction[group * 8 + m] = -NIBBLE_BIAS * sum;  // the accumulation chains start from it
+    return ((group * 4 + word) * staged + m) * 4 + j;
 }
-
-// Permutes [staged][width] bf16 rows into fragment order.  from_global: the rows were written by other CTAs of
-// this launch and are read through L2; otherwise they are sm.rows.  Loads go out in batches of eight (two chunks of
-// four lanes) before any of them is used: a pass costs one memory latency per batch, not one per chunk.
-__device__ __forceinline__ void stage_rows(const StackSmem &sm, const uint16_t *x, bool from_global, int width, int staged) {
-    const int per_lane = width >> 3;  // chunks of a lane, a multiple of 16
-    const uint4 *source = from_global ? reinterpret_cast<const uint4 *>(x) : reinterpret_cast<const uint4 *>(sm.rows);
-    for (int m0 = 0; m0 < staged; m0 += 4) {
-        for (int base = 0; base < per_lane; base += STACK_THREADS * 2) {
-            uint4 raw[2][4];
-#pragma unroll
-            for (int i = 0; i < 2; i++)
-#pragma unroll
-                for (int mm = 0; mm < 4; mm++) {
-                    const int chunk = base + i * STACK_THREADS + threadIdx.x;
-                    raw[i][mm] = make_uint4(0, 0, 0, 0);
-                    if (chunk < per_lane && m0 + mm < staged) {
-                        const uint4 *address = source + static_cast<size_t>(m0 + mm) * per_lane + chunk;
-                        raw[i][mm] = from_global ? __ldcg(address) : *address;
-                    }
-                }
-#pragma unroll
-            for (int i = 0; i < 2; i++)
-#pragma unroll
-                for (int mm = 0; mm < 4; mm++) {
-                    const int chunk = base + i * STACK_THREADS + threadIdx.x;
-                    // uniform over the CTA: whole warps take part in the shuffles
-                    if (base + i * STACK_THREADS < per_lane && m0 + mm < staged)
-                        stage_chunk(sm, raw[i][mm], chunk < per_lane, m0 + mm, chunk < per_lane ? chunk : 0, staged);
-                }
-        }
-    }
-    for (int c = threadIdx.x; c < (width >> 7) * 8; c += STACK_THREADS)
-        if ((c & 7) >= staged) sm.correction[c] = 0.0f;
-    __syncthreads();
+// Position (in 16-bit elements) of column `column` of lane m in a fragment-ordered buffer.
+__device__ __forceinline__ size_t fragment_element(int column, int m, int staged) {
+    const int e = column & 7;
+    return static_cast<size_t>(fragment_index(column >> 3, m, staged)) * 8 + (e & 3) * 2 + (e >> 2);
 }
 
 // rms_norm_bf16.comp.template:49-72 of every staged lane, straight into fragment order (each CTA repeats it:
 // 8 KB per lane from L2).  A thread owns chunk t (and t + 512 when CHUNKS = 2) of each lane, four lanes at a time:
 // one pass over registers for the sums of squares, one block-wide exchange, then normalise, round and permute.
-template <int CHUNKS>  // chunks per thread and lane: width <= CHUNKS * 8 * STACK_THREADS
-__device__ __forceinline__ void stage_normalised(const StackSmem &sm, const uint16_t *x, const uint16_t *weight, int width, int staged,
-                                                 float eps, float offset) {
+template <int CHUNKS>  // chunks per thread and lane: width <= CHUNKS * 8 * CONSUMER_THREADS
+__device__ __noinline__ void stage_normalised(uint4 *fragments, float *partial, const uint16_t *x, const uint16_t *weight, int width,
+                                                 int staged, float eps, float offset) {
     const int per_lane = width >> 3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint4 *source = reinterpret_cast<const uint4 *>(x);
     uint4 scale_words[CHUNKS];
 #pragma unroll
     for (int c = 0; c < CHUNKS; c++) {
-        const int chunk = threadIdx.x + c * STACK_THREADS;
+        const int chunk = threadIdx.x + c * CONSUMER_THREADS;
         scale_words[c] = chunk < per_lane ? __ldg(reinterpret_cast<const uint4 *>(weight) + chunk) : make_uint4(0, 0, 0, 0);
     }
     for (int m0 = 0; m0 < staged; m0 += 4) {
@@ -523,7 +493,7 @@ __device__ __forceinline__ void stage_normalised(const StackSmem &sm, const uint
         for (int mm = 0; mm < 4; mm++)
 #pragma unroll
             for (int c = 0; c < CHUNKS; c++) {
-                const int chunk = threadIdx.x + c * STACK_THREADS;
+                const int chunk = threadIdx.x + c * CONSUMER_THREADS;
                 raw[mm][c] = (m0 + mm < staged && chunk < per_lane) ? __ldcg(source + static_cast<size_t>(m0 + mm) * per_lane + chunk)
                                                                     : make_uint4(0, 0, 0, 0);
             }
@@ -541,11 +511,11 @@ __device__ __forceinline__ void stage_normalised(const StackSmem &sm, const uint
                 }
             }
             sum = warp_sum(sum);
-            if (lane == 0) sm.partial[mm * STACK_WARPS + warp] = sum;
+            if (lane == 0) partial[mm * CONSUMER_WARPS + warp] = sum;
         }
-        __syncthreads();
+        consumer_sync();
         // every warp adds up the 16 partials of the four lanes: lanes 8k .. 8k+7 of the warp take lane m0 + k
-        float total = sm.partial[(lane >> 3) * STACK_WARPS + (lane & 7) * 2] + sm.partial[(lane >> 3) * STACK_WARPS + (lane & 7) * 2 + 1];
+        float total = partial[(lane >> 3) * CONSUMER_WARPS + (lane & 7) * 2] + partial[(lane >> 3) * CONSUMER_WARPS + (lane & 7) * 2 + 1];
         total += __shfl_xor_sync(0xffffffffu, total, 1);
         total += __shfl_xor_sync(0xffffffffu, total, 2);
         total += __shfl_xor_sync(0xffffffffu, total, 4);
@@ -556,23 +526,24 @@ __device__ __forceinline__ void stage_normalised(const StackSmem &sm, const uint
             const float inv_rms = __shfl_sync(0xffffffffu, my_inverse, mm * 8);
 #pragma unroll
             for (int c = 0; c < CHUNKS; c++) {
-                const int chunk = threadIdx.x + c * STACK_THREADS;
-                if (c * STACK_THREADS < per_lane && m0 + mm < staged) {  // uniform over the CTA
+                const int chunk = threadIdx.x + c * CONSUMER_THREADS;
+                if (chunk < per_lane && m0 + mm < staged) {
                     const uint32_t in[4] = {raw[mm][c].x, raw[mm][c].y, raw[mm][c].z, raw[mm][c].w};
                     const uint32_t sc[4] = {scale_words[c].x, scale_words[c].y, scale_words[c].z, scale_words[c].w};
-                    uint32_t out[4];
+                    float v[8];
 #pragma unroll
-                    for (int w = 0; w < 4; w++)
-                        out[w] = pack_bf16(bf16_lo(in[w]) * inv_rms * (bf16_lo(sc[w]) + offset), bf16_hi(in[w]) * inv_rms * (bf16_hi(sc[w]) + offset));
-                    stage_chunk(sm, make_uint4(out[0], out[1], out[2], out[3]), chunk < per_lane, m0 + mm, chunk < per_lane ? chunk : 0, staged);
+                    for (int w = 0; w < 4; w++) {
+                        v[2 * w] = round_bf16(bf16_lo(in[w]) * inv_rms * (bf16_lo(sc[w]) + offset));
+                        v[2 * w + 1] = round_bf16(bf16_hi(in[w]) * inv_rms * (bf16_hi(sc[w]) + offset));
+                    }
+                    fragments[fragment_index(chunk, m0 + mm, staged)] =
+                        make_uint4(half_pair(v[0], v[4]), half_pair(v[1], v[5]), half_pair(v[2], v[6]), half_pair(v[3], v[7]));
                 }
             }
         }
-        if (m0 + 4 < staged) __syncthreads();  // sm.partial is rewritten for the next four lanes
+        if (m0 + 4 < staged) consumer_sync();  // `partial` is rewritten for the next four lanes
     }
-    for (int c = threadIdx.x; c < (width >> 7) * 8; c += STACK_THREADS)
-        if ((c & 7) >= staged) sm.correction[c] = 0.0f;
-    __syncthreads();
+    consumer_sync();
 }
 
 // ------------------------------------------------------------------------------------------ attention
@@ -583,35 +554,141 @@ __device__ __forceinline__ void stage_normalised(const StackSmem &sm, const uint
 // loads; the head dimension is permuted identically on both sides); the probabilities are re-used from the
 // accumulator registers as the A operand of O = P V, split into a bf16 high and low part (p = hi + lo to 2^-17),
 // and V is the B operand, its token pairs assembled with byte permutes.  The warps agree on the split's row
-// maxima through shared memory, add up their partial outputs there, and the team writes one partial
-// (unnormalised output, maximum, sum) to the scratch the merge step reads.
-
-__device__ __forceinline__ void team_barrier(int barrier_id) { asm volatile("bar.sync %0, 128;" ::"r"(barrier_id) : "memory"); }
+// maxima through shared memory, add up their partial outputs there (HALF head dims per pass), and the team writes
+// one partial (unnormalised output, maximum, sum) per query to the scratch.  The team that completes a kv head's
+// last split merges all of them (log-sum-exp) and writes the head's outputs, fp16 in fragment order, where the o
+// projection's activation slices are copied from.
 
 template <int HD>
 __host__ __device__ constexpr size_t attention_team_bytes() {
-    return (4 * 16 * HD + 2 * 4 * 16) * sizeof(float);  // partial outputs [warp][row][dim], maxima and sums [warp][row]
+    return (4 * 16 * ((HD < 64 ? HD : 64) + 4) + 2 * 4 * 16 + 4) * sizeof(float);  // partial outputs [warp][row][HALF + 4], maxima and sums [warp][row], one flag
 }
 
+// Log-sum-exp merge of the split partials of one (lane, q head) row by one warp: lane s of the warp weighs split s
+// (s + 32, ...), every lane owns HD / 32 consecutive output dims, and the weighted rows are summed in split order,
+// the loads of eight splits in flight at a time.  The result goes out as fp16 in fragment order.
+template <int HD>
+__device__ __forceinline__ void attention_merge_row(const float *__restrict__ scratch, uint16_t *__restrict__ out_fragments, uint32_t capacity,
+                                                    uint32_t tick, int query_lane, int head, int q_heads, int max_splits, int staged) {
+    constexpr int VEC = HD / 32, STRIDE = HD + 2;  // a partial is HD + 2 floats: 8-byte pieces stay aligned
+    static_assert(VEC == 1 || VEC % 2 == 0, "a lane owns whole 8-byte pieces (or one float)");
+    const int lane_id = threadIdx.x & 31;
+    const uint32_t tokens = tick + 1u < capacity ? tick + 1u : capacity;
+    int splits = static_cast<int>((tokens + 63u) / 64u);
+    if (splits > max_splits) splits = max_splits;
+    const float *base = scratch + (static_cast<size_t>(query_lane) * q_heads + head) * max_splits * STRIDE;
+    float maximum = -3.4028234663852886e38f;
+    for (int s = lane_id; s < splits; s += 32) maximum = fmaxf(maximum, __ldcg(base + static_cast<size_t>(s) * STRIDE + HD));
+    maximum = warp_max(maximum);
+    float denominator = 0.0f, acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; v++) acc[v] = 0.0f;
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        float weight = 0.0f;
+        if (s0 + lane_id < splits) {
+            const float2 stats = __ldcg(reinterpret_cast<const float2 *>(base + static_cast<size_t>(s0 + lane_id) * STRIDE + HD));
+            weight = expf(stats.x - maximum);
+            denominator += stats.y * weight;
+        }
+        const int end = splits - s0 < 32 ? splits - s0 : 32;
+        for (int s = 0; s < end; s += 8) {
+            float part[8][VEC];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float *row = base + static_cast<size_t>(s0 + s + u) * STRIDE + lane_id * VEC;
+                if (VEC == 1) {
+                    part[u][0] = s + u < end ? __ldcg(row) : 0.0f;
+                } else {
+#pragma unroll
+                    for (int v = 0; v < VEC; v += 2) {
+                        const float2 pair = s + u < end ? __ldcg(reinterpret_cast<const float2 *>(row + v)) : make_float2(0.0f, 0.0f);
+                        part[u][v] = pair.x;
+                        part[u][v + 1 < VEC ? v + 1 : v] = pair.y;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float w = __shfl_sync(0xffffffffu, weight, (s + u) & 31);
+#pragma unroll
+                for (int v = 0; v < VEC; v++) acc[v] += part[u][v] * (s + u < end ? w : 0.0f);
+            }
+        }
+    }
+    denominator = warp_sum(denominator);
+#pragma unroll
+    for (int v = 0; v < VEC; v++) {
+        const float rounded = round_bf16(denominator == 0.0f ? 0.0f : acc[v] / denominator);
+        out_fragments[fragment_element(head * HD + lane_id * VEC + v, query_lane, staged)] = __half_as_ushort(__float2half_rn(rounded));
+    }
+}
+
+// Loads through L2 that stay where they are written (the compiler may not sink them towards their use).
+__device__ __forceinline__ uint4 load16_now(const void *address) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(address) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 load8_now(const void *address) {
+    uint2 v;
+    asm volatile("ld.global.cg.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(address) : "memory");
+    return v;
+}
+
+template <int HD>
+__device__ __forceinline__ size_t attention_row_base(const KvLayer &kv, int slot, uint32_t ring_base, int token) {
+    uint32_t ring = ring_base + static_cast<uint32_t>(token);
+    if (ring >= kv.capacity) ring -= kv.capacity;
+    const int page = static_cast<int>(ring / kv.page_tokens), within = static_cast<int>(ring % kv.page_tokens);
+    const int physical = kv.block_table[static_cast<size_t>(slot) * kv.pages_per_slot + page];
+    return static_cast<size_t>(physical) * 2 * kv.kv_heads * kv.page_tokens * HD + static_cast<size_t>(within) * HD;
+}
+
+constexpr int ATTENTION_MERGE_LIST = 63;
+// Per-CTA copies of what every layer needs again: the lanes' ticks and stream slots, and for each team the KV rows
+// of its first work item (the block table is shared by all layers, so the rows of a (split, lane group) are the
+// same in every layer's pool).
+struct AttentionCache {
+    uint32_t tick[8];
+    int32_t slot[8];
+    int32_t item[4];          // the work item whose rows `row_base` holds, or -1
+    int32_t rows[4];          // how many tokens that item has
+    int32_t merge_count;      // (kv head, lane group) pairs whose last split this CTA's teams completed in this layer ...
+    int32_t merge_list[ATTENTION_MERGE_LIST];  // ... and which: kv_head * group_slots + group_slot
+    uint32_t row_base[4][64]; // offset (in rows of HD elements) of token t's K row of kv head 0 in a layer's pool
+};
+
 template <int HD, int GROUP, int QL>
-__device__ __forceinline__ void attention_team_item(const uint16_t *__restrict__ q, const KvLayer &kv, const LaneTable &lanes_meta,
+__device__ __noinline__ void attention_team_item(const uint16_t *__restrict__ q, const KvLayer &kv, AttentionCache &cache, int item,
                                                     int lanes, int lanes_per_stream, int q_heads, float scale, int max_splits,
-                                                    float *__restrict__ scratch, int kv_head, int split, int group_slot,
-                                                    float *team_smem, int team_warp, int barrier_id) {
+                                                    float *__restrict__ scratch, uint16_t *__restrict__ out_fragments,
+                                                    unsigned int *__restrict__ arrivals, int group_slots, int kv_head, int split,
+                                                    int group_slot, float *team_smem, int team, int team_warp, int barrier_id, int staged,
+                                                    unsigned long long *stamps) {
     constexpr int Q = QL * GROUP;
+    auto mark = [&](int index) {
+        if (stamps != nullptr) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            stamps[index] = now;
+        }
+    };
+    mark(20);
     constexpr int QW = HD / 32;                    // 16-byte pieces of a q / k row per thread
     constexpr int HALF = HD < 64 ? HD : 64;        // head dims handled per output pass
     constexpr int DPT = HALF / 8;                  // of which one thread column owns this many
     static_assert(Q <= 16 && HD % 32 == 0, "attention team shape");
     const int lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
-    float *partial_out = team_smem;                       // [4][16][HD]
-    float *team_max = team_smem + 4 * 16 * HD;            // [4][16]
+    constexpr int PITCH = HALF + 4;                       // row pitch of the partial outputs (bank spread)
+    float *partial_out = team_smem;                       // [4][16][PITCH]
+    float *team_max = team_smem + 4 * 16 * PITCH;         // [4][16]
     float *team_sum = team_max + 4 * 16;                  // [4][16]
+    unsigned int *team_flag = reinterpret_cast<unsigned int *>(team_sum + 4 * 16);
     const int groups_per_stream = (lanes_per_stream + QL - 1) / QL;
     const int stream_index = group_slot / groups_per_stream, group_index = group_slot % groups_per_stream;
     const int lane0 = stream_index * lanes_per_stream + group_index * QL;
     if (lane0 >= lanes) return;
-    const int slot = lanes_meta.slot[lane0];
+    const int slot = cache.slot[lane0];
     if (slot < 0) return;
     const uint32_t capacity = kv.capacity;
 
@@ -619,7 +696,7 @@ __device__ __forceinline__ void attention_team_item(const uint16_t *__restrict__
 #pragma unroll
     for (int i = 0; i < QL; i++) {
         const bool valid = lane0 + i < lanes && group_index * QL + i < lanes_per_stream;
-        const uint32_t tick = valid ? lanes_meta.position[lane0 + i] : 0xffffffffu;
+        const uint32_t tick = valid ? cache.tick[lane0 + i] : 0xffffffffu;
         if (valid && tick > newest) newest = tick;
         if (g < Q && g / GROUP == i) tick_row[0] = tick;
         if (g + 8 < Q && (g + 8) / GROUP == i) tick_row[1] = tick;
@@ -628,20 +705,22 @@ __device__ __forceinline__ void attention_team_item(const uint16_t *__restrict__
     const uint32_t first_tick = newest + 1u - tokens;
     const uint32_t begin = static_cast<uint32_t>(split) * 64u;
     if (begin >= tokens) return;  // the whole team leaves: nobody waits at the team barrier
+    int expected_splits = static_cast<int>((tokens + 63u) / 64u);
+    if (expected_splits > max_splits) expected_splits = max_splits;
     const int count = static_cast<int>(tokens - begin < 64u ? tokens - begin : 64u);
     const int token0 = 16 * team_warp;  // this warp's tokens of the split
-    // ring index of the split's first token; element offset of token t's K (or V) row of this kv head
-    const uint32_t ring_base = (first_tick + begin) % capacity;
-    const int page_shift = (kv.page_tokens & (kv.page_tokens - 1)) == 0 ? __ffs(kv.page_tokens) - 1 : -1;
+    // element offset of token t's K (or V) row of this kv head: from the team's cached rows, or through the block table
     const size_t half_page = static_cast<size_t>(kv.kv_heads) * kv.page_tokens * HD;
+    const bool cached = cache.item[team] == item;
+    const uint32_t ring_base = (first_tick + begin) % capacity;
     auto row_offset = [&](int token, bool value) {
-        uint32_t ring = ring_base + static_cast<uint32_t>(token);
-        if (ring >= capacity) ring -= capacity;
-        const int page = page_shift >= 0 ? static_cast<int>(ring >> page_shift) : static_cast<int>(ring / kv.page_tokens);
-        const int within = page_shift >= 0 ? static_cast<int>(ring & (kv.page_tokens - 1)) : static_cast<int>(ring % kv.page_tokens);
-        const int physical = kv.block_table[static_cast<size_t>(slot) * kv.pages_per_slot + page];
-        return static_cast<size_t>(physical) * (2 * half_page) + (value ? half_page : 0) +
-               (static_cast<size_t>(kv_head) * kv.page_tokens + within) * HD;
+        size_t base;
+        if (cached) {
+            base = static_cast<size_t>(cache.row_base[team][token]) * HD;
+        } else {
+            base = attention_row_base<HD>(kv, slot, ring_base, token);
+        }
+        return base + (value ? half_page : 0) + static_cast<size_t>(kv_head) * kv.page_tokens * HD;
     };
 
     // ---- S = Q K^T for 16 tokens
@@ -652,35 +731,65 @@ __device__ __forceinline__ void attention_team_item(const uint16_t *__restrict__
         const bool valid = tick_row[r] != 0xffffffffu;
         const uint16_t *source = q + (static_cast<size_t>(lane0 + row / GROUP) * q_heads + kv_head * GROUP + row % GROUP) * HD + j * (HD / 4);
 #pragma unroll
-        for (int w = 0; w < QW; w++) qf[r][w] = valid ? __ldcg(reinterpret_cast<const uint4 *>(source) + w) : make_uint4(0, 0, 0, 0);
+        for (int w = 0; w < QW; w++) qf[r][w] = valid ? load16_now(reinterpret_cast<const uint4 *>(source) + w) : make_uint4(0, 0, 0, 0);
     }
-    float s[2][4];
+    // K rows of tokens g and g + 8, V rows of tokens 2j, 2j+1, 2j+8, 2j+9 of this warp: all requested before the
+    // arithmetic (the V rows of the first output pass now, those of the second when the q registers are free)
+    uint4 kf[2][QW];
 #pragma unroll
     for (int nt = 0; nt < 2; nt++) {
         const int token = token0 + nt * 8 + g;
-        uint4 kf[QW];
         if (token < count) {
             const uint16_t *krow = kv.pool + row_offset(token, false) + j * (HD / 4);
 #pragma unroll
-            for (int w = 0; w < QW; w++) kf[w] = __ldcg(reinterpret_cast<const uint4 *>(krow) + w);
+            for (int w = 0; w < QW; w++) kf[nt][w] = load16_now(reinterpret_cast<const uint4 *>(krow) + w);
         } else {
 #pragma unroll
-            for (int w = 0; w < QW; w++) kf[w] = make_uint4(0, 0, 0, 0);
-        }
-        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
-#pragma unroll
-        for (int w = 0; w < QW; w++) {
-            mma_bf16_16816(s[nt], qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, kf[w].x, kf[w].y);
-            mma_bf16_16816(s[nt], qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, kf[w].z, kf[w].w);
+            for (int w = 0; w < QW; w++) kf[nt][w] = make_uint4(0, 0, 0, 0);
         }
     }
-    // V rows of this warp's tokens 2j, 2j+1, 2j+8, 2j+9 (requested now, used after the softmax)
     size_t v_offset[4];
 #pragma unroll
     for (int t = 0; t < 4; t++) {
         const int token = token0 + 2 * j + (t & 1) + 8 * (t >> 1);
         v_offset[t] = token < count ? row_offset(token, true) : static_cast<size_t>(-1);
     }
+    uint32_t v[HD / HALF][4][DPT / 2];
+    auto load_values = [&](int pass) {
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+            if (v_offset[t] != static_cast<size_t>(-1)) {
+                const uint16_t *vrow = kv.pool + v_offset[t] + pass * HALF + DPT * g;
+                if (DPT == 8) {
+                    const uint4 raw = load16_now(vrow);
+                    v[pass][t][0] = raw.x;
+                    v[pass][t][1] = raw.y;
+                    v[pass][t][DPT / 2 - 2] = raw.z;
+                    v[pass][t][DPT / 2 - 1] = raw.w;
+                } else {
+                    const uint2 raw = load8_now(vrow);
+                    v[pass][t][0] = raw.x;
+                    v[pass][t][DPT / 2 - 1] = raw.y;
+                }
+            } else {
+#pragma unroll
+                for (int w = 0; w < DPT / 2; w++) v[pass][t][w] = 0u;
+            }
+        }
+    };
+    load_values(0);
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; nt++) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+#pragma unroll
+        for (int w = 0; w < QW; w++) {
+            mma_bf16_16816(s[nt], qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, kf[nt][w].x, kf[nt][w].y);
+            mma_bf16_16816(s[nt], qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, kf[nt][w].z, kf[nt][w].w);
+        }
+    }
+    if (HD / HALF > 1) load_values(HD / HALF - 1);
+    mark(21);
 
     // ---- causal / ring mask, scale; the team's row maxima; probabilities
     float row_max[2] = {-INFINITY, -INFINITY};
@@ -721,6 +830,7 @@ __device__ __forceinline__ void attention_team_item(const uint16_t *__restrict__
         row_sum[r] += __shfl_xor_sync(0xffffffffu, row_sum[r], 2);
         if (j == 0) team_sum[team_warp * 16 + g + 8 * r] = row_sum[r];
     }
+    mark(22);
     // probabilities as the A fragment of this warp's 16 tokens: high and low bf16 parts
     uint32_t ph[4], pl[4];
 #pragma unroll
@@ -731,37 +841,16 @@ __device__ __forceinline__ void attention_team_item(const uint16_t *__restrict__
     }
 
     // ---- O = P V over the warp's tokens, HALF head dims per pass; thread column g owns dims DPT*g .. DPT*g+DPT-1
-    float *mine = partial_out + static_cast<size_t>(team_warp) * 16 * HD;
+    float *mine = partial_out + static_cast<size_t>(team_warp) * 16 * PITCH;
 #pragma unroll
     for (int pass = 0; pass < HD / HALF; pass++) {
         float o[DPT][4];
 #pragma unroll
         for (int i = 0; i < DPT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-        uint32_t v[4][DPT / 2];
-#pragma unroll
-        for (int t = 0; t < 4; t++) {
-            if (v_offset[t] != static_cast<size_t>(-1)) {
-                const uint16_t *vrow = kv.pool + v_offset[t] + pass * HALF + DPT * g;
-                if (DPT == 8) {
-                    const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(vrow));
-                    v[t][0] = raw.x;
-                    v[t][1] = raw.y;
-                    v[t][DPT / 2 - 2] = raw.z;
-                    v[t][DPT / 2 - 1] = raw.w;
-                } else {
-                    const uint2 raw = __ldcg(reinterpret_cast<const uint2 *>(vrow));
-                    v[t][0] = raw.x;
-                    v[t][DPT / 2 - 1] = raw.y;
-                }
-            } else {
-#pragma unroll
-                for (int w = 0; w < DPT / 2; w++) v[t][w] = 0u;
-            }
-        }
 #pragma unroll
         for (int i = 0; i < DPT; i++) {
             const uint32_t selector = (i & 1) ? 0x7632u : 0x5410u;
-            const uint32_t b0 = __byte_perm(v[0][i >> 1], v[1][i >> 1], selector), b1 = __byte_perm(v[2][i >> 1], v[3][i >> 1], selector);
+            const uint32_t b0 = __byte_perm(v[pass][0][i >> 1], v[pass][1][i >> 1], selector), b1 = __byte_perm(v[pass][2][i >> 1], v[pass][3][i >> 1], selector);
             mma_bf16_16816(o[i], ph[0], ph[1], ph[2], ph[3], b0, b1);
             mma_bf16_16816(o[i], pl[0], pl[1], pl[2], pl[3], b0, b1);
         }
@@ -770,181 +859,60 @@ __device__ __forceinline__ void attention_team_item(const uint16_t *__restrict__
         for (int r = 0; r < 2; r++)
 #pragma unroll
             for (int i = 0; i < DPT; i++) {
-                mine[(g + 8 * r) * HD + pass * HALF + DPT * (2 * j) + i] = o[i][2 * r];
-                mine[(g + 8 * r) * HD + pass * HALF + DPT * (2 * j + 1) + i] = o[i][2 * r + 1];
+                mine[(g + 8 * r) * PITCH + DPT * (2 * j) + i] = o[i][2 * r];
+                mine[(g + 8 * r) * PITCH + DPT * (2 * j + 1) + i] = o[i][2 * r + 1];
             }
+        team_barrier(barrier_id);
+        // the four partial outputs add up; warp w writes dims [w * HALF / 4, (w + 1) * HALF / 4) of the pass for every row
+        for (int index = lane; index < 16 * (HALF / 4); index += 32) {
+            const int row = index / (HALF / 4), d = team_warp * (HALF / 4) + index % (HALF / 4);
+            const int query_lane = lane0 + row / GROUP;  // rows beyond Q are padding
+            const bool valid = row < Q && query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream;
+            if (!valid) continue;
+            const float sum = partial_out[row * PITCH + d] + partial_out[(16 + row) * PITCH + d] + partial_out[(32 + row) * PITCH + d] +
+                              partial_out[(48 + row) * PITCH + d];
+            float *out = scratch + ((static_cast<size_t>(query_lane) * q_heads + kv_head * GROUP + row % GROUP) * max_splits + split) * (HD + 2);
+            out[pass * HALF + d] = sum;
+            if (pass == 0 && d == 0) {
+                out[HD] = fmaxf(fmaxf(fmaxf(team_max[row], team_max[16 + row]), fmaxf(team_max[32 + row], team_max[48 + row])), -3.4028234663852886e38f);
+                out[HD + 1] = team_sum[row] + team_sum[16 + row] + team_sum[32 + row] + team_sum[48 + row];
+            }
+        }
+        if (pass + 1 < HD / HALF) team_barrier(barrier_id);  // the partial outputs are rewritten by the next pass
     }
+    // ---- the team that completes the kv head's last split merges the splits of its queries
+    mark(23);
+    __threadfence();
     team_barrier(barrier_id);
-    // ---- the four partial outputs add up; warp w writes head dims [w * HD / 4, (w + 1) * HD / 4) of every row
-    for (int index = lane; index < 16 * (HD / 4); index += 32) {
-        const int row = index / (HD / 4), d = team_warp * (HD / 4) + index % (HD / 4);
-        const int query_lane = lane0 + row / GROUP;  // rows beyond Q are padding
-        const bool valid = row < Q && query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream;
-        if (!valid) continue;
-        const float sum = partial_out[row * HD + d] + partial_out[(16 + row) * HD + d] + partial_out[(32 + row) * HD + d] +
-                          partial_out[(48 + row) * HD + d];
-        float *out = scratch + ((static_cast<size_t>(query_lane) * q_heads + kv_head * GROUP + row % GROUP) * max_splits + split) * (HD + 2);
-        out[d] = sum;
-        if (d == 0) {
-            out[HD] = fmaxf(fmaxf(fmaxf(team_max[row], team_max[16 + row]), fmaxf(team_max[32 + row], team_max[48 + row])), -3.4028234663852886e38f);
-            out[HD + 1] = team_sum[row] + team_sum[16 + row] + team_sum[32 + row] + team_sum[48 + row];
+    unsigned int *arrival = arrivals + kv_head * group_slots + group_slot;
+    if (team_warp == 0 && lane == 0) *team_flag = atomicAdd(arrival, 1u);
+    team_barrier(barrier_id);
+    const bool last = *team_flag == static_cast<unsigned int>(expected_splits - 1);
+    mark(24);
+    if (last) {
+        // all splits of this kv head and lane group are in the scratch: the CTA merges them after its items (one row
+        // per warp); a CTA with more such heads than its list holds merges the rest right here
+        team_barrier(barrier_id);  // everybody has read the flag
+        if (team_warp == 0 && lane == 0) {
+            __threadfence();
+            *arrival = 0u;  // for the next layer (several grid barriers away)
+            const int request = atomicAdd(&cache.merge_count, 1);
+            if (request < ATTENTION_MERGE_LIST) cache.merge_list[request] = kv_head * group_slots + group_slot;
+            *team_flag = static_cast<unsigned int>(request);
+        }
+        team_barrier(barrier_id);
+        if (*team_flag >= static_cast<unsigned int>(ATTENTION_MERGE_LIST)) {
+            __threadfence();
+            for (int row = team_warp; row < Q; row += 4) {
+                const int query_lane = lane0 + row / GROUP;
+                if (query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream)
+                    attention_merge_row<HD>(scratch, out_fragments, capacity, cache.tick[query_lane], query_lane, kv_head * GROUP + row % GROUP, q_heads,
+                                            max_splits, staged);
+            }
         }
     }
     team_barrier(barrier_id);  // the team's shared arrays are free for its next item
-}
-
-// Log-sum-exp merge of the split partials of one (lane, q head) pair by one warp: lane s of the warp weighs
-// split s (s + 32, ...), every lane owns HD / 32 consecutive output dims, and the weighted rows are summed in
-// split order with four vector loads in flight.
-template <int HD>
-__device__ __forceinline__ void attention_merge_warp(const float *__restrict__ scratch, uint16_t *__restrict__ out, const KvLayer &kv,
-                                                     const LaneTable &lanes_meta, int pair, int q_heads, int max_splits) {
-    constexpr int VEC = HD / 32, STRIDE = HD + 2;
-    const int lane_id = threadIdx.x & 31, lane = pair / q_heads;
-    if (lanes_meta.slot[lane] < 0) return;
-    const uint32_t tick = lanes_meta.position[lane];
-    const uint32_t tokens = tick + 1u < kv.capacity ? tick + 1u : kv.capacity;
-    int splits = static_cast<int>((tokens + 63u) / 64u);
-    if (splits > max_splits) splits = max_splits;
-    const float *base = scratch + static_cast<size_t>(pair) * max_splits * STRIDE;
-    float maximum = -3.4028234663852886e38f;
-    for (int s = lane_id; s < splits; s += 32) maximum = fmaxf(maximum, __ldcg(base + static_cast<size_t>(s) * STRIDE + HD));
-    maximum = warp_max(maximum);
-    float denominator = 0.0f, acc[VEC];
-#pragma unroll
-    for (int v = 0; v < VEC; v++) acc[v] = 0.0f;
-    for (int s0 = 0; s0 < splits; s0 += 32) {
-        float weight = 0.0f;
-        if (s0 + lane_id < splits) {
-            weight = expf(__ldcg(base + static_cast<size_t>(s0 + lane_id) * STRIDE + HD) - maximum);
-            denominator += __ldcg(base + static_cast<size_t>(s0 + lane_id) * STRIDE + HD + 1) * weight;
-        }
-        const int end = splits - s0 < 32 ? splits - s0 : 32;
-        for (int s = 0; s < end; s += 4) {
-            float part[4][VEC];
-#pragma unroll
-            for (int u = 0; u < 4; u++)
-#pragma unroll
-                for (int v = 0; v < VEC; v++)
-                    part[u][v] = s + u < end ? __ldcg(base + static_cast<size_t>(s0 + s + u) * STRIDE + lane_id * VEC + v) : 0.0f;
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const float w = __shfl_sync(0xffffffffu, weight, (s + u) & 31);
-#pragma unroll
-                for (int v = 0; v < VEC; v++) acc[v] += part[u][v] * (s + u < end ? w : 0.0f);
-            }
-        }
-    }
-    denominator = warp_sum(denominator);
-#pragma unroll
-    for (int v = 0; v < VEC; v++)
-        out[static_cast<size_t>(pair) * HD + lane_id * VEC + v] =
-            static_cast<uint16_t>(f32_to_bf16_bits(denominator == 0.0f ? 0.0f : acc[v] / denominator));
-}
-
-// ------------------------------------------------------------------------------------------ the kernel
-
-struct StackArgs {
-    const StackLayer *layers;
-    int layer_count;
-    StackShape shape;
-    StackBuffers buffers;
-    LaneTable lanes_meta;
-    int lanes, lanes_per_stream, split_tokens, max_splits;
-    int ring_units, l2_prefetch;
-    const StackTp *tp;  // device copy of the exchange description, or nullptr (single GPU)
-    int tp_size;
-};
-
-struct StackSmemLayout {
-    size_t fragments, rows, correction, reduce, partial, ring, total;
-};
-__host__ __device__ inline StackSmemLayout stack_smem_layout(const StackShape &shape, int staged, int ring_units) {
-    const size_t q_width = static_cast<size_t>(shape.q_heads) * shape.head_width;
-    size_t widest = shape.hidden > shape.ffn ? shape.hidden : shape.ffn;
-    if (q_width > widest) widest = q_width;
-    size_t region = static_cast<size_t>(staged) * widest * 2;
-    const size_t norm_region = static_cast<size_t>(staged) * shape.hidden * 2 * 2;  // fragments + plain rows
-    if (norm_region > region) region = norm_region;
-    StackSmemLayout layout;
-    layout.fragments = 0;
-    layout.rows = static_cast<size_t>(staged) * shape.hidden * 2;
-    layout.correction = region;
-    layout.reduce = layout.correction + (widest >> 7) * 8 * sizeof(float);
-    layout.partial = layout.reduce + static_cast<size_t>(2) * STACK_WARPS * 32 * 8 * sizeof(float);
-    layout.ring = layout.partial + 8 * STACK_WARPS * sizeof(float);
-    layout.total = layout.ring + static_cast<size_t>(STACK_WARPS) * ring_units * RING_UNIT_BYTES;
-    const size_t attention = 4 * (4 * 16 * static_cast<size_t>(shape.head_width) + 2 * 4 * 16) * sizeof(float);  // four attention teams
-    if (attention > layout.total) layout.total = attention;
-    return layout;
-}
-
-// One 16x128 block of the ring against the staged activations: eight MMAs over bf16 (16 + q) in two accumulation
-// chains.  The first chain starts from -24 * sum(x) of the group (`negative_bias`, per lane), which takes the
-// 16 + 8 offset of the nibbles out again; the sum of the chains is the block's product.
-__device__ __forceinline__ void unit_products(uint32_t mine, const uint4 (&b)[4], float2 negative_bias, float (&c)[4]) {
-    const uint4 first = shared_load16<0>(mine);
-    const uint4 second = shared_load16<512>(mine);
-    const uint32_t wa[4] = {first.x, first.y, first.z, first.w};
-    const uint32_t wb[4] = {second.x, second.y, second.z, second.w};
-    float even[4] = {negative_bias.x, negative_bias.y, negative_bias.x, negative_bias.y}, odd[4];
-#pragma unroll
-    for (int word = 0; word < 4; word++) {
-        mma_bf16_16816(even, biased_pair<0>(wa[word]), biased_pair<0>(wb[word]), biased_pair<1>(wa[word]), biased_pair<1>(wb[word]), b[word].x,
-                       b[word].y);
-        if (word == 0)
-            mma_bf16_16816_first(odd, biased_pair<2>(wa[word]), biased_pair<2>(wb[word]), biased_pair<3>(wa[word]), biased_pair<3>(wb[word]),
-                                 b[word].z, b[word].w);
-        else
-            mma_bf16_16816(odd, biased_pair<2>(wa[word]), biased_pair<2>(wb[word]), biased_pair<3>(wa[word]), biased_pair<3>(wb[word]), b[word].z,
-                           b[word].w);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; i++) c[i] = even[i] + odd[i];
-}
-
-// The block's two scales (rows g and g + 8).
-__device__ __forceinline__ void unit_accumulate(uint32_t scales, const float (&c)[4], float (&acc)[4]) {
-    const float sa = __uint_as_float(scales << 16), sb = __uint_as_float(scales & 0xffff0000u);
-    acc[0] = fmaf(sa, c[0], acc[0]);
-    acc[1] = fmaf(sa, c[1], acc[1]);
-    acc[2] = fmaf(sb, c[2], acc[2]);
-    acc[3] = fmaf(sb, c[3], acc[3]);
-}
-
-// A tile's items of this warp (RT ring units each): wait for the item's copies, issue its MMAs, put the freed ring
-// units back to work while the tensor pipe runs, then fold the products into the tile's accumulators.
-// xitem / bias_item: shared-space addresses of the thread's fragments and bias pair of the warp's first group.
-template <int RT>
-__device__ __forceinline__ void tile_items(WeightStream &stream, int items, uint32_t xitem, uint32_t bias_item, uint32_t word_stride,
-                                           float (&acc)[2][4]) {
-    const uint32_t item_stride = STACK_WARPS * 4 * word_stride;
-    for (int gi = 0; gi < items; gi++) {
-        uint4 b[4];
-        b[0] = shared_load16<0>(xitem);
-        b[1] = shared_load16<0>(xitem + word_stride);
-        b[2] = shared_load16<0>(xitem + 2 * word_stride);
-        b[3] = shared_load16<0>(xitem + 3 * word_stride);
-        const float2 negative_bias = shared_load_float2(bias_item);
-        xitem += item_stride;
-        bias_item += STACK_WARPS * 8 * sizeof(float);
-        async_wait_oldest(stream.in_flight);
-        stream.in_flight--;
-        float c[RT][4];
-        uint32_t scales[RT];
-#pragma unroll
-        for (int r = 0; r < RT; r++) {
-            scales[r] = shared_load4(stream.head + stream.scale_offset);
-            unit_products(stream.head, b, negative_bias, c[r]);
-            stream.head += RING_UNIT_BYTES;
-            if (stream.head == stream.ring_end) stream.head = stream.ring_begin;
-        }
-        stream.used -= RT;
-        if (stream.remaining > 0 && stream.rt == RT) stream_issue_item<RT>(stream);  // the freed units go straight back to work
-        else stream_advance(stream);
-#pragma unroll
-        for (int r = 0; r < RT; r++) unit_accumulate(scales[r], c[r], acc[r]);
-    }
+    mark(25);
 }
 
 template <int GROUP>
@@ -952,53 +920,241 @@ struct AttentionTeam {
     static constexpr int QL = GROUP >= 8 ? 2 : (GROUP >= 4 ? 4 : (16 / GROUP > 8 ? 8 : 16 / GROUP));
 };
 
+// ------------------------------------------------------------------------------------------ matrix blocks
+
+// One 16x128 block at `weights` (this thread's 16 bytes of rows g and, 512 bytes on, g + 8) against the staged
+// activations of its group: eight MMAs over exact fp16 (q - 8) operands in two accumulation chains.
+struct UnitOperands {
+    uint4 low, high;  // this thread's 32 nibbles of rows g and g + 8
+    uint4 b[4];       // its B fragments of the block's group
+    uint32_t scales;  // bf16 scale of row g | row g + 8
+};
+__device__ __forceinline__ void unit_load(UnitOperands &u, uint32_t weights, uint32_t scales, uint32_t x, uint32_t word_stride) {
+    u.b[0] = shared_load16<0>(x);
+    u.b[1] = shared_load16<0>(x + word_stride);
+    u.b[2] = shared_load16<0>(x + 2 * word_stride);
+    u.b[3] = shared_load16<0>(x + 3 * word_stride);
+    u.low = shared_load16<0>(weights);
+    u.high = shared_load16<512>(weights);
+    u.scales = shared_load4(scales);
+}
+// Word `WORD` of the block: two MMAs into two of the block's four accumulation chains.
+template <int WORD>
+__device__ __forceinline__ void unit_word(const UnitOperands &u, float (&chains)[4][4]) {
+    const uint32_t wa = WORD == 0 ? u.low.x : (WORD == 1 ? u.low.y : (WORD == 2 ? u.low.z : u.low.w));
+    const uint32_t wb = WORD == 0 ? u.high.x : (WORD == 1 ? u.high.y : (WORD == 2 ? u.high.z : u.high.w));
+    const uint4 &b = u.b[WORD];
+    mma_f16_16816(chains[2 * (WORD & 1)], nibbles_low(wa), nibbles_low(wb), nibbles_high(wa), nibbles_high(wb), b.x, b.y);
+    const uint32_t upper_a = wa >> 8, upper_b = wb >> 8;
+    mma_f16_16816(chains[2 * (WORD & 1) + 1], nibbles_low(upper_a), nibbles_low(upper_b), nibbles_high(upper_a), nibbles_high(upper_b), b.z, b.w);
+}
+__device__ __forceinline__ void unit_finish(const UnitOperands &u, const float (&chains)[4][4], float (&acc)[4]) {
+    const float sa = __uint_as_float(u.scales << 16), sb = __uint_as_float(u.scales & 0xffff0000u);
+    acc[0] = fmaf(sa, (chains[0][0] + chains[1][0]) + (chains[2][0] + chains[3][0]), acc[0]);
+    acc[1] = fmaf(sa, (chains[0][1] + chains[1][1]) + (chains[2][1] + chains[3][1]), acc[1]);
+    acc[2] = fmaf(sb, (chains[0][2] + chains[1][2]) + (chains[2][2] + chains[3][2]), acc[2]);
+    acc[3] = fmaf(sb, (chains[0][3] + chains[1][3]) + (chains[2][3] + chains[3][3]), acc[3]);
+}
+// One 16x128 block against the staged activations of its group: eight MMAs over exact fp16 (q - 8) operands in
+// four accumulation chains; the group scale multiplies the block's f32 product.
+__device__ __forceinline__ void unit_single(const UnitOperands &u, float (&acc)[4]) {
+    float chains[4][4] = {};
+    unit_word<0>(u, chains);
+    unit_word<1>(u, chains);
+    unit_word<2>(u, chains);
+    unit_word<3>(u, chains);
+    unit_finish(u, chains, acc);
+}
+// Two blocks at once, their MMAs interleaved (eight independent chains).
+__device__ __forceinline__ void unit_pair(const UnitOperands &u, const UnitOperands &v, float (&acc)[4]) {
+    float cu[4][4] = {}, cv[4][4] = {};
+    unit_word<0>(u, cu);
+    unit_word<0>(v, cv);
+    unit_word<1>(u, cu);
+    unit_word<1>(v, cv);
+    unit_word<2>(u, cu);
+    unit_word<2>(v, cv);
+    unit_word<3>(u, cu);
+    unit_word<3>(v, cv);
+    unit_finish(u, cu, acc);
+    unit_finish(v, cv, acc);
+}
+
+// The steps of one pass as a warp sees them, in a function of its own so that the loop's registers are allotted
+// apart from the long-lived state of the kernel body.  For every stage of the pass: wait until it has landed,
+// multiply this warp's block (if it has one in this stage) and release the stage.  `x` is the shared-space address
+// of the thread's B fragments of the first step - relative to the stage for activation slices that ride the ring,
+// absolute (moving on by x_step per step) for the normalised rows.
+struct PassResult {
+    float acc[4];
+    uint32_t slot, parity, slice_slot, slice_parity;
+    uint32_t payload[4];  // what the epilogue needs from global memory (the residual values), requested before the steps
+};
+struct PassRing {  // where the stages are and where this warp stands in them
+    uint32_t ring, full, empty, stages, stage_bytes;
+    uint32_t slices, slice_full, slice_empty, slice_slots, slice_bytes;
+};
+__device__ __noinline__ PassResult consume_pass(const PassRing ring, uint32_t slot, uint32_t parity, uint32_t slice_slot, uint32_t slice_parity,
+                                                int steps, int steps_per_stage, int active_steps, uint32_t step_bytes, uint32_t weight_offset,
+                                                uint32_t scale_offset, uint32_t x, uint32_t x_step, bool x_in_slice, uint32_t word_stride,
+                                                int *error_flag, const uint16_t *payload, uint32_t payload_stride, int payload_rounds) {
+    uint32_t residual[4];
+#pragma unroll
+    for (int round = 0; round < 4; round++) residual[round] = round < payload_rounds ? __ldcg(payload + static_cast<size_t>(round) * payload_stride) : 0;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const int lane = threadIdx.x & 31;
+    const bool handshake = (steps_per_stage & 256) == 0;  // timing probe: 256 = run on whatever the ring holds
+    steps_per_stage &= 255;
+    for (int step = 0; step < steps; step += steps_per_stage) {
+        const uint32_t stage_address = ring.ring + slot * ring.stage_bytes;
+        const uint32_t slice_address = ring.slices + slice_slot * ring.slice_bytes;
+        if (handshake) {
+            wait_stage(ring.full + slot * 8, parity, error_flag);
+            if (x_in_slice) wait_stage(ring.slice_full + slice_slot * 8, slice_parity, error_flag);
+        }
+        int here = active_steps - step;  // this warp's blocks in the stage
+        if (here > steps_per_stage) here = steps_per_stage;
+        if (here > 0) {
+            const uint32_t x_first = x_in_slice ? slice_address + x : x;
+            UnitOperands u;
+            unit_load(u, stage_address + weight_offset, stage_address + scale_offset, x_first, word_stride);
+            unit_single(u, acc);
+            if (here == 2) {
+                unit_load(u, stage_address + step_bytes + weight_offset, stage_address + step_bytes + scale_offset, x_first + x_step, word_stride);
+                unit_single(u, acc);
+            }
+            if (!x_in_slice) x += static_cast<uint32_t>(here) * x_step;
+        }
+        __syncwarp();
+        if (lane == 0 && handshake) {
+            mbarrier_arrive(ring.empty + slot * 8);
+            if (x_in_slice) mbarrier_arrive(ring.slice_empty + slice_slot * 8);
+        }
+        if (++slot == ring.stages) {
+            slot = 0;
+            parity ^= 1u;
+        }
+        if (x_in_slice && ++slice_slot == ring.slice_slots) {
+            slice_slot = 0;
+            slice_parity ^= 1u;
+        }
+    }
+    PassResult result;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        result.acc[i] = acc[i];
+        result.payload[i] = residual[i];
+    }
+    result.slot = slot;
+    result.parity = parity;
+    result.slice_slot = slice_slot;
+    result.slice_parity = slice_parity;
+    return result;
+}
+
+// ------------------------------------------------------------------------------------------ the kernel
+
 // EXCHANGE: the tensor-parallel form (o and down leave partial sums that are exchanged between the ranks).
 template <int HD, int GROUP, bool EXCHANGE>
 __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const StackArgs a) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     constexpr int QL = AttentionTeam<GROUP>::QL;
     const StackShape &shape = a.shape;
     const int lanes = a.lanes, staged = lanes < 8 ? lanes : 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, j = lane & 3;
-    const StackSmemLayout layout = stack_smem_layout(shape, staged, a.ring_units);
-    StackSmem sm;
-    sm.fragments = reinterpret_cast<uint4 *>(smem_raw + layout.fragments);
-    sm.rows = reinterpret_cast<uint16_t *>(smem_raw + layout.rows);
-    sm.correction = reinterpret_cast<float *>(smem_raw + layout.correction);
-    sm.reduce = reinterpret_cast<float *>(smem_raw + layout.reduce);
-    sm.partial = reinterpret_cast<float *>(smem_raw + layout.partial);
-    sm.ring = smem_raw + layout.ring;
 
-    const int q_width = shape.q_heads * HD, q_tiles = q_width >> 4, k_tiles = (shape.kv_heads * HD) >> 4;
-    unsigned int target = 0;
-    constexpr bool exchanging = EXCHANGE;
-    unsigned long long exchange_target = 0ull;  // exchanges done so far, earlier launches included
-    float *exchange_mine = nullptr;
-    if constexpr (EXCHANGE) {
-        exchange_target = a.tp->counter[a.tp->rank][TP_WORD_CONSUMED];
-        exchange_mine = a.tp->exchange[a.tp->rank];
+    // shared memory: scratch (fragments / attention teams) | reduce [2][16][16][8] f32 | norm partials | phase table |
+    // barriers | ring
+    uint4 *fragments = reinterpret_cast<uint4 *>(smem_raw);
+    float *reduce = reinterpret_cast<float *>(smem_raw + a.scratch_bytes);
+    float *norm_partial = reduce + 2 * CONSUMER_WARPS * 128;
+    uint32_t *rope_rows = reinterpret_cast<uint32_t *>(norm_partial + 4 * CONSUMER_WARPS);  // [8 lanes][HD / 2] rotary factors of the lanes' positions
+    AttentionCache *attention_cache = reinterpret_cast<AttentionCache *>(rope_rows + 8 * (HD >> 1));
+    PhaseInfo *info = reinterpret_cast<PhaseInfo *>(attention_cache + 1);
+    uint64_t *barriers = reinterpret_cast<uint64_t *>(info + 4);
+    uint32_t *open_word = reinterpret_cast<uint32_t *>(barriers + 4 * MAX_STAGES);  // [0] grid barriers passed, [1] stages requested
+    uint8_t *ring_base = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(open_word + 4) + 127) & ~static_cast<uintptr_t>(127));
+    RingAddresses ring;
+    ring.ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring_base));
+    ring.full = static_cast<uint32_t>(__cvta_generic_to_shared(barriers));
+    ring.empty = ring.full + MAX_STAGES * 8;
+    ring.slices = static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw));  // the slices share the scratch area with the fragments
+    ring.slice_full = ring.empty + MAX_STAGES * 8;
+    ring.slice_empty = ring.slice_full + MAX_STAGES * 8;
+    ring.open_word = static_cast<uint32_t>(__cvta_generic_to_shared(open_word));
+    ring.issued_word = ring.open_word + 4;
+
+    const int q_width = shape.q_heads * HD, kv_width = shape.kv_heads * HD;
+    const int q_tiles = q_width >> 4, k_tiles = kv_width >> 4;
+    if (threadIdx.x == 0) {
+        const int grid = static_cast<int>(gridDim.x), cta = static_cast<int>(blockIdx.x);
+        const MatrixSchedule schedules[4] = {stack_schedule((q_width + 2 * kv_width) >> 4, shape.hidden >> 7, 1, grid),
+                                             stack_schedule(shape.hidden >> 4, q_width >> 7, 1, grid),
+                                             stack_schedule(shape.ffn >> 4, shape.hidden >> 7, 2, grid),
+                                             stack_schedule(shape.hidden >> 4, shape.ffn >> 7, 1, grid)};
+        for (int p = 0; p < 4; p++) {
+            const MatrixSchedule &s = schedules[p];
+            PhaseInfo pi;
+            pi.tiles_here = stack_cta_tiles(s, cta);
+            pi.passes = (pi.tiles_here + s.slots - 1) / s.slots;
+            pi.slots = s.slots;
+            pi.width = s.width;
+            pi.steps = s.steps;
+            pi.units = s.units;
+            pi.rt = s.rt;
+            pi.groups = s.units / s.rt;
+            pi.cta_offset = static_cast<uint32_t>(stack_cta_offset(s, cta));
+            pi.streamed = (p == 1 || p == 3) ? 1 : 0;
+            info[p] = pi;
+        }
+        for (int s = 0; s < a.stages; s++) {
+            mbarrier_init(ring.full + s * 8, 1);                 // the producer's arrival with the byte count
+            mbarrier_init(ring.empty + s * 8, CONSUMER_WARPS);  // one arrival per consumer warp
+        }
+        for (int s = 0; s < a.slice_slots; s++) {
+            mbarrier_init(ring.slice_full + s * 8, 1);
+            mbarrier_init(ring.slice_empty + s * 8, CONSUMER_WARPS);
+        }
+        open_word[0] = 0u;
+        open_word[1] = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async;" ::: "memory");
     }
-    int exchange_parity = 0;
+    __syncthreads();
+
+    if (warp >= CONSUMER_WARPS) {
+        if (lane == 0 && !(a.debug_flags & 8)) {
+            if (warp == CONSUMER_WARPS) produce_weights(a, info, ring);
+            else if (warp == CONSUMER_WARPS + 1) produce_activations(a, info, ring, staged);
+            else if (warp == CONSUMER_WARPS + 2 && a.prefetch_stages > 0) produce_prefetches(a, info, ring);
+        }
+        return;
+    }
+
+    // ------------------------------------------------------------------ consumers
+    unsigned int target = 0, barriers_passed = 0;
     unsigned int *counter = a.buffers.barrier;
+    unsigned int *arrivals = a.buffers.barrier + ARRIVAL_WORDS_OFFSET;
     int *error_flag = a.buffers.error_flag;
-    int parity = 0, phase = 0;
-    WeightStream stream;
-    stream.ring_begin = static_cast<uint32_t>(__cvta_generic_to_shared(sm.ring + static_cast<size_t>(warp) * a.ring_units * RING_UNIT_BYTES + lane * 16));
-    stream.ring_end = stream.ring_begin + a.ring_units * RING_UNIT_BYTES;
-    stream.head = stream.tail = stream.ring_begin;
-    stream.scale_offset = 1024 + lane * 4 - lane * 16;
-    stream.units = a.ring_units;
-    stream.used = 0;
-    stream.rt = 1;
-    stream.per_tile = 0;
-    stream.gi = 0;
-    stream.in_flight = 0;
-    stream.has_following = false;
-    stream.source_phase = -1;
-    stream.remaining = 0;
-    stream.weights = nullptr;
-    stream.scales = nullptr;
-    stream.offset = stream.step = stream.tile_step = 0;
+    uint32_t tag = 0;  // exchanges done so far, earlier launches included
+    unsigned long long *inbox_mine = nullptr;
+    if constexpr (EXCHANGE) {
+        tag = static_cast<uint32_t>(a.tp->counter[a.tp->rank][STACK_TP_WORD_CONSUMED]);
+        inbox_mine = reinterpret_cast<unsigned long long *>(a.tp->exchange[a.tp->rank]);
+    }
+    uint32_t ring_slot = 0, ring_parity = 0, slice_slot = 0, slice_parity = 0;
+    int reduce_parity = 0;
+    PassRing pass_ring;
+    pass_ring.ring = ring.ring;
+    pass_ring.full = ring.full;
+    pass_ring.empty = ring.empty;
+    pass_ring.stages = static_cast<uint32_t>(a.stages);
+    pass_ring.stage_bytes = static_cast<uint32_t>(a.stage_bytes);
+    pass_ring.slices = ring.slices;
+    pass_ring.slice_full = ring.slice_full;
+    pass_ring.slice_empty = ring.slice_empty;
+    pass_ring.slice_slots = static_cast<uint32_t>(a.slice_slots);
+    pass_ring.slice_bytes = static_cast<uint32_t>(a.slice_bytes);
 
     auto stamp = [&](int layer, int index) {
         if (a.buffers.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -1007,143 +1163,185 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
             a.buffers.timing[layer * 32 + index] = now;
         }
     };
-    // Epilogue roles: thread t < 128 finishes output (high = t & 1, lane m = (t >> 1) & 7, row = (t >> 4) + 8 * high)
-    // of a tile's 16 rows x 8 lanes, so the rotary partner rows r and r + 8 of a lane sit in neighbouring threads.
-    // Only four warps do this; the other twelve go straight on to the next tile's blocks.
-    const int epilogue_m = (threadIdx.x >> 1) & 7, epilogue_row = (threadIdx.x >> 4) + 8 * (threadIdx.x & 1);
-    const bool epilogue_active = threadIdx.x < 128 && epilogue_m < lanes;
+    auto meet = [&]() {
+        grid_barrier(counter, target, error_flag);
+        barriers_passed++;
+        if (threadIdx.x == 0) shared_store_release(ring.open_word, barriers_passed);
+    };
+
+    // Epilogue roles: thread t finishes output (high = t & 1, lane m = (t >> 1) & 7, row = ((t >> 4) & 7) + 8 * high)
+    // of tile slot (t >> 7) + 4 * round, so the rotary partner rows r and r + 8 of a lane sit in neighbouring threads.
+    const int epilogue_m = (threadIdx.x >> 1) & 7, epilogue_row = ((threadIdx.x >> 4) & 7) + 8 * (threadIdx.x & 1);
+    const int epilogue_slot = threadIdx.x >> 7;
+    const bool epilogue_lane = epilogue_m < lanes;
     // per-lane constants of the epilogue: position, rotary table row, and the lane's KV row inside a page (the
     // block table is shared by all layers)
     uint32_t lane_position = 0;
-    const uint32_t *rope_row = shape.rope_table;
     size_t kv_token_base = 0;
     bool kv_writable = false;
-    if (threadIdx.x < 128 && epilogue_m < lanes) {
+    if (epilogue_lane) {
         lane_position = a.lanes_meta.position[epilogue_m];
-        rope_row = shape.rope_table + static_cast<size_t>(lane_position % shape.rope_positions) * (HD >> 1);
         const KvLayer &kv0 = a.layers[0].kv;
         const int slot = a.lanes_meta.slot[epilogue_m];
         if (slot >= 0 && kv0.capacity != 0) {
-            const uint32_t ring = lane_position % kv0.capacity;
-            const int physical = kv0.block_table[static_cast<size_t>(slot) * kv0.pages_per_slot + ring / kv0.page_tokens];
-            kv_token_base = static_cast<size_t>(physical) * 2 * kv0.kv_heads * kv0.page_tokens * HD + static_cast<size_t>(ring % kv0.page_tokens) * HD;
+            const uint32_t ring_token = lane_position % kv0.capacity;
+            const int physical = kv0.block_table[static_cast<size_t>(slot) * kv0.pages_per_slot + ring_token / kv0.page_tokens];
+            kv_token_base = static_cast<size_t>(physical) * 2 * kv0.kv_heads * kv0.page_tokens * HD + static_cast<size_t>(ring_token % kv0.page_tokens) * HD;
             kv_writable = true;
         }
     }
+    for (int index = threadIdx.x; index < staged * (HD >> 1); index += CONSUMER_THREADS) {
+        const int m = index / (HD >> 1);
+        rope_rows[index] = __ldg(shape.rope_table + static_cast<size_t>(a.lanes_meta.position[m] % shape.rope_positions) * (HD >> 1) + (index - m * (HD >> 1)));
+    }
+    if (threadIdx.x < 8) {
+        attention_cache->tick[threadIdx.x] = static_cast<int>(threadIdx.x) < lanes ? a.lanes_meta.position[threadIdx.x] : 0u;
+        attention_cache->slot[threadIdx.x] = static_cast<int>(threadIdx.x) < lanes ? a.lanes_meta.slot[threadIdx.x] : -1;
+    }
+    consumer_sync();
+    {
+        // the KV rows of each team's first attention item, looked up once for all layers
+        const int streams = lanes / a.lanes_per_stream;
+        const int groups_per_stream = (a.lanes_per_stream + QL - 1) / QL;
+        const int group_slots = streams * groups_per_stream;
+        const int total = shape.kv_heads * a.max_splits * group_slots;
+        const int team = warp >> 2, team_thread = threadIdx.x & 127;
+        const int item = static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) * team;
+        int cached_item = -1, cached_rows = 0;
+        if (item < total) {
+            const int rest = item / shape.kv_heads, split = rest % a.max_splits, group_slot = rest / a.max_splits;
+            const int lane0 = (group_slot / groups_per_stream) * a.lanes_per_stream + (group_slot % groups_per_stream) * QL;
+            const KvLayer &kv0 = a.layers[0].kv;
+            const int slot = lane0 < lanes ? attention_cache->slot[lane0] : -1;
+            if (slot >= 0 && kv0.capacity != 0) {
+                uint32_t newest = 0;
+                for (int i = 0; i < QL; i++)
+                    if (lane0 + i < lanes && (group_slot % groups_per_stream) * QL + i < a.lanes_per_stream && attention_cache->tick[lane0 + i] > newest)
+                        newest = attention_cache->tick[lane0 + i];
+                const uint32_t tokens = newest + 1u < kv0.capacity ? newest + 1u : kv0.capacity;
+                const uint32_t begin = static_cast<uint32_t>(split) * 64u;
+                if (begin < tokens) {
+                    const uint32_t ring_base = (newest + 1u - tokens + begin) % kv0.capacity;
+                    if (team_thread < 64 && begin + team_thread < tokens)
+                        attention_cache->row_base[team][team_thread] = static_cast<uint32_t>(attention_row_base<HD>(kv0, slot, ring_base, team_thread) / HD);
+                    cached_item = item;
+                    cached_rows = static_cast<int>(tokens - begin < 64u ? tokens - begin : 64u);
+                }
+            }
+        }
+        if (threadIdx.x == 0) attention_cache->merge_count = 0;
+        if (team_thread == 0) {
+            attention_cache->item[team] = cached_item;
+            attention_cache->rows[team] = cached_rows;
+        }
+    }
+    consumer_sync();
     const int ge = g < staged ? g : 0;  // lanes beyond the batch recompute lane 0; their results are dropped
-    const uint32_t xlane = static_cast<uint32_t>(__cvta_generic_to_shared(sm.fragments + ge * 4 + j));
-    const uint32_t bias_lane = static_cast<uint32_t>(__cvta_generic_to_shared(sm.correction + 2 * j));
-    const uint32_t word_stride = static_cast<uint32_t>(staged) * 4 * sizeof(uint4);
+    const uint32_t fragment_lane = static_cast<uint32_t>(__cvta_generic_to_shared(fragments)) + static_cast<uint32_t>(ge * 4 + j) * 16u;
+    const uint32_t word_stride = static_cast<uint32_t>(staged) * 4 * sizeof(uint4);  // between the four words of a group
+    const uint32_t group_stride = 4 * word_stride;
+    const int grid = static_cast<int>(gridDim.x);
 
     for (int layer = 0; layer < a.layer_count; layer++) {
         const StackLayer *spec = a.layers + layer;
         const KvLayer kv = spec->kv;
-        for (int step = 0; step < 4; step++, phase++) {
-            // ---- the matrix of this step, and the one whose first blocks may be requested while this one drains
-            TiledInt4 matrix, next_matrix;
-            int rt = 1, next_rt = 1;
-            bool has_next = true;
-            if (step == 0) {
-                matrix = spec->qkv;
-                next_matrix = matrix;
-                has_next = false;  // attention sits in between; the o projection is requested after it
-            } else if (step == 1) {
-                matrix = spec->o;
-                next_matrix = spec->gate_up;
-                next_rt = 2;
-            } else if (step == 2) {
-                matrix = spec->gate_up;
-                rt = 2;
-                next_matrix = spec->down;
-            } else {
-                matrix = spec->down;
-                has_next = layer + 1 < a.layer_count;
-                next_matrix = has_next ? a.layers[layer + 1].qkv : matrix;
+        {
+            // the K and V rows this CTA's teams will read in this layer's attention step: on their way into L2 now
+            const int team = warp >> 2, team_thread = threadIdx.x & 127;
+            const int item = attention_cache->item[team];
+            if (item >= 0 && team_thread < attention_cache->rows[team] && kv.capacity != 0) {
+                const int kv_head = item % shape.kv_heads;
+                const size_t half_page = static_cast<size_t>(kv.kv_heads) * kv.page_tokens * HD;
+                const uint16_t *row = kv.pool + static_cast<size_t>(attention_cache->row_base[team][team_thread]) * HD + static_cast<size_t>(kv_head) * kv.page_tokens * HD;
+#pragma unroll
+                for (int line = 0; line < (HD * 2 + 127) / 128; line++) {
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(row) + line * 128));
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(row + half_page) + line * 128));
+                }
             }
-            const MatrixWalk walk = walk_of(matrix, rt);
-            if (stream.source_phase != phase) stream_start(stream, walk, phase);
-            stream.has_following = has_next;
-            if (has_next) stream.following = walk_of(next_matrix, next_rt);
-            stream_advance(stream);
-            // the matrix after this one goes to L2 now (the gate/up pair already while attention runs)
-            if (!a.l2_prefetch) {
-            } else if (step == 0) {
-                prefetch_matrix_l2(spec->o, 1);
-                prefetch_matrix_l2(spec->gate_up, 2);
-            } else if (step == 2) {
-                prefetch_matrix_l2(spec->down, 1);
-            } else if (step == 3 && layer + 1 < a.layer_count) {
-                prefetch_matrix_l2(a.layers[layer + 1].qkv, 1);
-            }
-            stamp(layer, 4 * step);
-
-            // ---- activations of this step into fragment order
-            if (step == 0 || step == 2) {
-                const uint16_t *norm_weight = step == 0 ? spec->input_norm : spec->post_norm;
-                if (shape.hidden <= 8 * STACK_THREADS)
-                    stage_normalised<1>(sm, a.buffers.hidden, norm_weight, shape.hidden, staged, shape.eps, shape.norm_offset);
+        }
+        for (int phase = 0; phase < 4; phase++) {
+            const PhaseInfo pi = info[phase];
+            stamp(layer, 4 * phase);
+            // ---- activations of q/k/v and gate/up: normalised rows into fragment order
+            if (phase == 0 || phase == 2) {
+                const uint16_t *norm_weight = phase == 0 ? spec->input_norm : spec->post_norm;
+                if (shape.hidden <= 8 * CONSUMER_THREADS)
+                    stage_normalised<1>(fragments, norm_partial, a.buffers.hidden, norm_weight, shape.hidden, staged, shape.eps, shape.norm_offset);
                 else
-                    stage_normalised<2>(sm, a.buffers.hidden, norm_weight, shape.hidden, staged, shape.eps, shape.norm_offset);
-                if (step == 2) stamp(layer, 16);
-            } else if (step == 1) {
-                stage_rows(sm, a.buffers.attention_out, true, q_width, staged);
-            } else {
-                stage_rows(sm, a.buffers.activation, true, shape.ffn, staged);
+                    stage_normalised<2>(fragments, norm_partial, a.buffers.hidden, norm_weight, shape.hidden, staged, shape.eps, shape.norm_offset);
             }
-            stamp(layer, 4 * step + 1);
+            stamp(layer, 4 * phase + 1);
 
-            // ---- the CTA's tiles: every warp takes each 16th group of K, then the tile is reduced and finished
-            float acc[2][4];
-#pragma unroll
-            for (int r = 0; r < 2; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
-            int tile = blockIdx.x;
-            for (int t = 0; t < walk.tiles; t++, tile += gridDim.x) {
-                // what the epilogue needs from memory is requested before the tile's arithmetic
-                uint32_t payload = 0;
-                if (epilogue_active) {
-                    if (step == 0) {
-                        if (tile < q_tiles + k_tiles) {
-                            const int local = tile < q_tiles ? tile : tile - q_tiles;
-                            payload = __ldg(rope_row + 8 * (local % (HD >> 4)) + (epilogue_row & 7));
-                        }
-                    } else if (step != 2 && !exchanging) {
-                        payload = __ldcg(a.buffers.hidden + static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row);
-                    }
+            const int slot_of_warp = warp / pi.width, index_in_slot = warp - slot_of_warp * pi.width;
+            for (int pass = 0; pass < pi.passes; pass++) {
+                const int present = stage_present(pi, pass);
+                const bool active = warp < present * pi.width;
+                // the epilogue's residual values are requested before the arithmetic: rounds of four tile slots
+                const uint16_t *payload_address = a.buffers.hidden;
+                int payload_rounds = 0;
+                if (epilogue_lane && (phase == 1 || phase == 3) && epilogue_slot < present) {
+                    payload_address = a.buffers.hidden + static_cast<size_t>(epilogue_m) * shape.hidden +
+                                      (static_cast<size_t>(blockIdx.x) + static_cast<size_t>(pass * pi.slots + epilogue_slot) * grid) * 16 + epilogue_row;
+                    payload_rounds = (present - epilogue_slot + 3) / 4;
                 }
-                const uint32_t xitem = xlane + warp * 4 * word_stride;  // fragments of group `warp`, then 16 groups on per item
-                const uint32_t bias_item = bias_lane + warp * 8 * sizeof(float);
-                if (rt == 2) tile_items<2>(stream, walk.per_tile, xitem, bias_item, word_stride, acc);
-                else tile_items<1>(stream, walk.per_tile, xitem, bias_item, word_stride, acc);
-                float *mine = sm.reduce + static_cast<size_t>((parity * STACK_WARPS + warp) * 32) * 8;
+                // this warp's units of the pass: index_in_slot, + width, ... while below `units`
+                int active_steps = 0;
+                if (active && index_in_slot < pi.units && !(a.debug_flags & 1)) active_steps = (pi.units - index_in_slot + pi.width - 1) / pi.width;
+                const uint32_t lane_fragment = static_cast<uint32_t>(ge * 4 + j) * 16u;
+                // B fragments: of the group the warp's first unit belongs to - in the slice of the stage (o, down), or in
+                // the normalised rows, moving on by width / rt groups per step
+                const uint32_t x_step = static_cast<uint32_t>(pi.width / pi.rt) * group_stride;
+                const uint32_t x_start = pi.streamed ? static_cast<uint32_t>(index_in_slot) * group_stride + lane_fragment
+                                                     : fragment_lane + static_cast<uint32_t>(index_in_slot / pi.rt) * group_stride;
+                const PassResult done = consume_pass(pass_ring, ring_slot, ring_parity, slice_slot, slice_parity, pi.steps, a.steps_per_stage | ((a.debug_flags & 8) ? 256 : 0), active_steps,
+                                                     static_cast<uint32_t>(present * pi.width * UNIT_TOTAL),
+                                                     static_cast<uint32_t>(warp) * UNIT_BYTES + static_cast<uint32_t>(lane) * 16u,
+                                                     static_cast<uint32_t>(present * pi.width) * UNIT_BYTES + static_cast<uint32_t>(warp) * UNIT_SCALE_BYTES +
+                                                         static_cast<uint32_t>(g) * 4u,
+                                                     x_start, x_step, pi.streamed != 0, word_stride, error_flag, payload_address,
+                                                     static_cast<uint32_t>(4 * grid * 16), payload_rounds);
+                ring_slot = done.slot;
+                ring_parity = done.parity;
+                slice_slot = done.slice_slot;
+                slice_parity = done.slice_parity;
+                stamp(layer, 26 + phase);
+                const float (&acc)[4] = done.acc;
+                // ---- the warps' partial sums meet: reduce[parity][warp][row][lane]
+                float *mine = reduce + static_cast<size_t>((reduce_parity * CONSUMER_WARPS + warp) * 128);
+                *reinterpret_cast<float2 *>(mine + g * 8 + 2 * j) = make_float2(acc[0], acc[1]);
+                *reinterpret_cast<float2 *>(mine + (g + 8) * 8 + 2 * j) = make_float2(acc[2], acc[3]);
+                consumer_sync();
+                const float *sums = reduce + static_cast<size_t>(reduce_parity * CONSUMER_WARPS * 128);
+                reduce_parity ^= 1;
 #pragma unroll
-                for (int r = 0; r < 2; r++) {
-                    if (r < rt) {
-                        *reinterpret_cast<float2 *>(mine + (r * 16 + g) * 8 + 2 * j) = make_float2(acc[r][0], acc[r][1]);
-                        *reinterpret_cast<float2 *>(mine + (r * 16 + g + 8) * 8 + 2 * j) = make_float2(acc[r][2], acc[r][3]);
-                    }
-                    acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
-                }
-                __syncthreads();
-                if (threadIdx.x < 128) {  // whole warps: the q/k epilogue exchanges partner rows by shuffle
-                    const float *src = sm.reduce + static_cast<size_t>(parity * STACK_WARPS * 32 + epilogue_row) * 8 + epilogue_m;
+                for (int round = 0; round < 4; round++) {
+                    const int slot = epilogue_slot + 4 * round;
+                    if (slot >= present) break;  // uniform over the warp
+                    const int tile = static_cast<int>(blockIdx.x) + (pass * pi.slots + slot) * grid;
+                    const float *src = sums + static_cast<size_t>(slot * pi.width) * 128 + epilogue_row * 8 + epilogue_m;
                     float first = 0.0f, second = 0.0f;
-#pragma unroll
-                    for (int w = 0; w < STACK_WARPS; w++) {
-                        first += src[w * 32 * 8];
-                        if (rt == 2) second += src[(w * 32 + 16) * 8];
+                    if (pi.rt == 2) {
+                        for (int w = 0; w < pi.width; w += 2) {
+                            first += src[w * 128];
+                            second += src[(w + 1) * 128];
+                        }
+                    } else {
+                        for (int w = 0; w < pi.width; w++) first += src[w * 128];
                     }
-                    if (step == 0) {
+                    if (phase == 0) {
                         // q / k: rotary_bf16.comp.template:99-109 (non-interleaved, rotary width = head width, five bf16
                         // roundings); k and v go into the lane's KV page (append_gqa_attention_bf16.comp.template:189-215)
                         const float mine_value = round_bf16(first);
                         const float partner = __shfl_xor_sync(0xffffffffu, mine_value, 1);  // the row 8 further (or 8 back)
-                        if (epilogue_active) {
+                        if (epilogue_lane) {
                             const size_t kv_half = static_cast<size_t>(kv.kv_heads) * kv.page_tokens * HD;
                             if (tile < q_tiles + k_tiles) {
                                 const bool is_q = tile < q_tiles, high = epilogue_row >= 8;
                                 const int local = is_q ? tile : tile - q_tiles;
                                 const int head = local / (HD >> 4), d = 8 * (local % (HD >> 4)) + (epilogue_row & 7) + (high ? HD / 2 : 0);
-                                const float cosine = bf16_lo(payload), sine = bf16_hi(payload);
+                                const uint32_t rotation = rope_rows[epilogue_m * (HD >> 1) + 8 * (local % (HD >> 4)) + (epilogue_row & 7)];
+                                const float cosine = bf16_lo(rotation), sine = bf16_hi(rotation);
                                 // d < half: x cos + (-x[d + half]) sin;  d >= half: x cos + x[d - half] sin
                                 const float other = high ? partner : -partner;
                                 const uint16_t value = static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(mine_value * cosine) + round_bf16(other * sine)));
@@ -1155,37 +1353,68 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                                     static_cast<uint16_t>(f32_to_bf16_bits(first));
                             }
                         }
-                    } else if (epilogue_active) {
-                        if (step == 2) {
-                            // silu_multiply_bf16.comp.template:30-52: bf16(silu_bf16(bf16 gate) * bf16 up)
-                            a.buffers.activation[static_cast<size_t>(epilogue_m) * shape.ffn + tile * 16 + epilogue_row] =
-                                static_cast<uint16_t>(f32_to_bf16_bits(rounded_silu(round_bf16(first)) * round_bf16(second)));
-                        } else if constexpr (EXCHANGE) {
-                            // this rank's share of the sum over K, unrounded, into its exchange buffer (the others fetch it)
-                            exchange_mine[(static_cast<size_t>(exchange_parity) * 8 + epilogue_m) * shape.hidden + tile * 16 + epilogue_row] = first;
+                    } else if (epilogue_lane) {
+                        const int column = tile * 16 + epilogue_row;
+                        if (phase == 2) {
+                            // silu_multiply_bf16.comp.template:30-52: bf16(silu_bf16(bf16 gate) * bf16 up), kept as fp16 in
+                            // fragment order for the down projection
+                            const float product = round_bf16(rounded_silu(round_bf16(first)) * round_bf16(second));
+                            a.buffers.activation[fragment_element(column, epilogue_m, staged)] = __half_as_ushort(__float2half_rn(product));
                         } else {
+                            float total = first;
+                            if constexpr (EXCHANGE) {
+                                // this rank's share of the sum over K goes to every peer's inbox, value and exchange number in
+                                // one 8-byte store; the peers' shares arrive in this rank's inbox the same way
+                                const StackTp &tp = *a.tp;
+                                const uint32_t number = tag + 1u;
+                                const size_t element = (static_cast<size_t>(number & 1u) * STACK_TP_MAX_RANKS * 8 + epilogue_m) * shape.hidden + column;
+                                const unsigned long long word = (static_cast<unsigned long long>(number) << 32) | __float_as_uint(first);
+                                for (int r = 0; r < tp.size; r++)
+                                    if (r != tp.rank)
+                                        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(reinterpret_cast<unsigned long long *>(tp.exchange[r]) + element +
+                                                                                              static_cast<size_t>(tp.rank) * 8 * shape.hidden),
+                                                     "l"(word)
+                                                     : "memory");
+                                total = 0.0f;
+                                unsigned int spins = 0;
+                                bool gave_up = false;
+                                for (int r = 0; r < tp.size; r++) {  // rank order on every rank: the replicas stay bit-identical
+                                    float part = first;
+                                    if (r != tp.rank) {
+                                        const unsigned long long *source = inbox_mine + element + static_cast<size_t>(r) * 8 * shape.hidden;
+                                        unsigned long long got = 0;
+                                        while (!gave_up) {
+                                            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(got) : "l"(source) : "memory");
+                                            if (static_cast<uint32_t>(got >> 32) == number) break;
+                                            if (++spins > STACK_TP_SPIN_LIMIT) {
+                                                atomicExch(error_flag, 2);
+                                                gave_up = true;
+                                            } else if ((spins & 255u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) {
+                                                gave_up = true;
+                                            }
+                                        }
+                                        part = __uint_as_float(static_cast<uint32_t>(got));
+                                    }
+                                    total += part;
+                                }
+                            }
                             // linear + residual_add (add_bf16.comp.template:17-24): bf16(bf16(product) + residual), in place
-                            a.buffers.hidden[static_cast<size_t>(epilogue_m) * shape.hidden + tile * 16 + epilogue_row] =
-                                static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(first) + bf16_bits_to_f32(payload)));
+                            a.buffers.hidden[static_cast<size_t>(epilogue_m) * shape.hidden + column] =
+                                static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(total) + bf16_bits_to_f32(done.payload[round])));
                         }
                     }
                 }
-                parity ^= 1;
             }
-            stamp(layer, 4 * step + 2);
             if constexpr (EXCHANGE) {
-              if (step == 1 || step == 3) {
-                exchange_barrier(*a.tp, exchange_target, error_flag);
-                reduce_exchanged(*a.tp, exchange_parity, a.buffers.hidden, lanes, shape.hidden);
-                exchange_parity ^= 1;
-              }
+                if (phase == 1 || phase == 3) tag += 1u;
             }
-            grid_barrier(counter, target, error_flag);
-            stamp(layer, 4 * step + 3);
+            stamp(layer, 4 * phase + 2);
+            if (layer + 1 < a.layer_count || phase < 3) meet();
+            stamp(layer, 4 * phase + 3);
 
-            if (step == 0) {
+            if (phase == 0) {
                 // ---- attention: (kv head, split, stream x lane group) items, one team of four warps each, spread
-                // over the SMs first; the teams' shared arrays reuse the staging area (nothing is staged right now)
+                // over the SMs first; the teams' shared arrays reuse the fragment area (nothing is staged right now)
                 const int streams = lanes / a.lanes_per_stream;
                 const int group_slots = streams * ((a.lanes_per_stream + QL - 1) / QL);
                 const int total = shape.kv_heads * a.max_splits * group_slots;
@@ -1193,24 +1422,35 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                 float *team_smem = reinterpret_cast<float *>(smem_raw + static_cast<size_t>(team) * attention_team_bytes<HD>());
                 for (int item = blockIdx.x + gridDim.x * team; item < total; item += gridDim.x * 4) {
                     const int kv_head = item % shape.kv_heads, rest = item / shape.kv_heads;
-                    attention_team_item<HD, GROUP, QL>(a.buffers.q, kv, a.lanes_meta, lanes, a.lanes_per_stream, shape.q_heads,
-                                                       shape.attention_scale, a.max_splits, a.buffers.attention_scratch, kv_head,
-                                                       rest % a.max_splits, rest / a.max_splits, team_smem, warp & 3, 1 + team);
+                    attention_team_item<HD, GROUP, QL>(a.buffers.q, kv, *attention_cache, item, lanes, a.lanes_per_stream, shape.q_heads,
+                                                       shape.attention_scale, a.max_splits, a.buffers.attention_scratch,
+                                                       a.buffers.attention_out, arrivals, group_slots, kv_head, rest % a.max_splits,
+                                                       rest / a.max_splits, team_smem, team, warp & 3, 2 + team, staged,
+                                                       (a.buffers.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) ? a.buffers.timing + layer * 32 : nullptr);
                 }
-                __syncthreads();  // the ring shares bytes with the teams' arrays
+                consumer_sync();
                 stamp(layer, 17);
-                // the o projection's first blocks stream while the grid meets and merges
-                stream_start(stream, walk_of(spec->o, 1), phase + 1);
-                stream.has_following = false;
-                stream_advance(stream);
-                grid_barrier(counter, target, error_flag);
+                {
+                    // merge the heads whose last split was completed here: one (lane, q head) row per warp and round
+                    int requests = attention_cache->merge_count;
+                    if (requests > ATTENTION_MERGE_LIST) requests = ATTENTION_MERGE_LIST;
+                    if (requests > 0) {
+                        __threadfence();
+                        const int groups_per_stream = (a.lanes_per_stream + QL - 1) / QL;
+                        for (int index = warp; index < requests * QL * GROUP; index += CONSUMER_WARPS) {
+                            const int request = attention_cache->merge_list[index / (QL * GROUP)], row = index % (QL * GROUP);
+                            const int kv_head = request / group_slots, group_slot = request % group_slots;
+                            const int group_index = group_slot % groups_per_stream;
+                            const int query_lane = (group_slot / groups_per_stream) * a.lanes_per_stream + group_index * QL + row / GROUP;
+                            if (query_lane < lanes && group_index * QL + row / GROUP < a.lanes_per_stream && attention_cache->slot[query_lane] >= 0)
+                                attention_merge_row<HD>(a.buffers.attention_scratch, a.buffers.attention_out, kv.capacity, attention_cache->tick[query_lane],
+                                                        query_lane, kv_head * GROUP + row % GROUP, shape.q_heads, a.max_splits, staged);
+                        }
+                    }
+                }
+                meet();
+                if (threadIdx.x == 0) attention_cache->merge_count = 0;  // read again after the next layer's q/k/v barrier at the earliest
                 stamp(layer, 18);
-                const int pairs = lanes * shape.q_heads;
-                for (int pair = blockIdx.x + gridDim.x * warp; pair < pairs; pair += gridDim.x * STACK_WARPS)
-                    attention_merge_warp<HD>(a.buffers.attention_scratch, a.buffers.attention_out, kv, a.lanes_meta, pair, shape.q_heads,
-                                             a.max_splits);
-                stamp(layer, 19);
-                grid_barrier(counter, target, error_flag);
             }
         }
     }
@@ -1222,27 +1462,66 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
         if (gone == gridDim.x - 1) {
             counter[0] = 0u;
             counter[1] = 0u;
-            if constexpr (EXCHANGE) a.tp->counter[a.tp->rank][TP_WORD_CONSUMED] = exchange_target;  // the next launch counts on from here
+            if constexpr (EXCHANGE) a.tp->counter[a.tp->rank][STACK_TP_WORD_CONSUMED] = tag;  // the next launch counts on from here
             __threadfence();
         }
     }
 }
 
+struct StackPlanSmem {
+    size_t scratch, total;
+    int stages, stage_bytes, steps_per_stage, slice_slots, slice_bytes;
+};
+
+template <int HD>
+bool plan_smem_for(const StackShape &shape, int lanes, int grid, StackPlanSmem *plan) {
+    const int staged = lanes < 8 ? lanes : 8;
+    const int q_width = shape.q_heads * shape.head_width;
+    const MatrixSchedule o = stack_schedule(shape.hidden >> 4, q_width >> 7, 1, grid);
+    const MatrixSchedule down = stack_schedule(shape.hidden >> 4, shape.ffn >> 7, 1, grid);
+    const int slice_groups = o.width > down.width ? o.width : down.width;
+    // two steps per stage while the slices of a stage stay small: fewer hand-overs, two independent blocks per warp
+    const int steps_per_stage = staged <= 4 ? 2 : 1;
+    const size_t slice = static_cast<size_t>(steps_per_stage) * slice_groups * staged * 256;
+    size_t scratch = static_cast<size_t>(staged) * shape.hidden * 2;  // fragments of a normalised row set
+    const size_t teams = 4 * attention_team_bytes<HD>();
+    if (teams > scratch) scratch = teams;
+    if (2 * slice > scratch) scratch = 2 * slice;
+    scratch = (scratch + 127) & ~static_cast<size_t>(127);
+    int slice_slots = static_cast<int>(scratch / slice);
+    if (slice_slots > MAX_STAGES) slice_slots = MAX_STAGES;
+    const size_t fixed = scratch + 2 * CONSUMER_WARPS * 128 * sizeof(float) + 4 * CONSUMER_WARPS * sizeof(float) + 8 * (HD / 2) * sizeof(uint32_t) +
+                         sizeof(AttentionCache) + 4 * sizeof(PhaseInfo) + 4 * MAX_STAGES * sizeof(uint64_t) + 4 * sizeof(uint32_t) + 128;
+    const size_t stage = (static_cast<size_t>(steps_per_stage) * STAGE_WEIGHT_BYTES + 127) & ~static_cast<size_t>(127);
+    const size_t limit = 227 * 1024;
+    if (fixed + 2 * stage > limit) return false;
+    int stages = static_cast<int>((limit - fixed) / stage);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    plan->scratch = scratch;
+    plan->stages = stages;
+    plan->stage_bytes = static_cast<int>(stage);
+    plan->steps_per_stage = steps_per_stage;
+    plan->slice_slots = slice_slots;
+    plan->slice_bytes = static_cast<int>(slice);
+    plan->total = fixed + static_cast<size_t>(stages) * stage;
+    return true;
+}
+
+bool plan_smem(const StackShape &shape, int lanes, int grid, StackPlanSmem *plan) {
+    const int group = shape.kv_heads > 0 ? shape.q_heads / shape.kv_heads : 0;
+    if (shape.head_width == 128 && (group == 4 || group == 8)) return plan_smem_for<128>(shape, lanes, grid, plan);
+    if (shape.head_width == 64 && group == 4) return plan_smem_for<64>(shape, lanes, grid, plan);
+    if (shape.head_width == 32 && group == 2) return plan_smem_for<32>(shape, lanes, grid, plan);
+    return false;
+}
+
 template <int HD, int GROUP, bool EXCHANGE>
-cudaError_t launch_instance_of(const StackArgs &args, size_t smem, cudaStream_t stream) {
-    static int configured_device = -1, sm_count = 0;
-    int device = 0;
-    cudaError_t status = cudaGetDevice(&device);
+cudaError_t launch_instance_of(const StackArgs &args, size_t smem, int grid, cudaStream_t stream) {
+    // the attribute is per device and per kernel instance: set it on every launch (a cheap host-side call)
+    cudaError_t status = cudaFuncSetAttribute(decode_stack_kernel<HD, GROUP, EXCHANGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (status != cudaSuccess) return status;
-    if (configured_device != device) {
-        status = cudaFuncSetAttribute(decode_stack_kernel<HD, GROUP, EXCHANGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (status != cudaSuccess) return status;
-        status = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-        if (status != cudaSuccess) return status;
-        configured_device = device;
-    }
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(sm_count);
+    config.gridDim = dim3(grid);
     config.blockDim = dim3(STACK_THREADS);
     config.dynamicSmemBytes = smem;
     config.stream = stream;
@@ -1255,30 +1534,18 @@ cudaError_t launch_instance_of(const StackArgs &args, size_t smem, cudaStream_t 
 }
 
 template <int HD, int GROUP>
-cudaError_t launch_instance(const StackArgs &args, size_t smem, cudaStream_t stream) {
-    return args.tp_size > 1 ? launch_instance_of<HD, GROUP, true>(args, smem, stream) : launch_instance_of<HD, GROUP, false>(args, smem, stream);
-}
-
-bool instance_smem(const StackShape &shape, int lanes, size_t *bytes, int *ring_units) {
-    const int group = shape.kv_heads > 0 ? shape.q_heads / shape.kv_heads : 0;
-    const bool built = (shape.head_width == 128 && (group == 4 || group == 8)) || (shape.head_width == 64 && group == 4) ||
-                       (shape.head_width == 32 && group == 2);
-    if (!built) return false;
-    // the deepest ring the 227 KB of shared memory leave room for (an even count: a gate/up item takes two units)
-    int units = MAX_RING_UNITS;
-    static const char *forced = getenv("NERVE_B200_STACK_RING");
-    if (forced != nullptr && atoi(forced) >= 2 && atoi(forced) <= MAX_RING_UNITS) units = atoi(forced) & ~1;
-    while (units > 2 && stack_smem_layout(shape, lanes < 8 ? lanes : 8, units).total > 227 * 1024) units -= 2;
-    *bytes = stack_smem_layout(shape, lanes < 8 ? lanes : 8, units).total;
-    if (ring_units) *ring_units = units;
-    return true;
+cudaError_t launch_instance(const StackArgs &args, size_t smem, int grid, cudaStream_t stream) {
+    return args.tp_size > 1 ? launch_instance_of<HD, GROUP, true>(args, smem, grid, stream) : launch_instance_of<HD, GROUP, false>(args, smem, grid, stream);
 }
 
 }  // namespace
 
-cudaError_t launch_int4_tile_major(const RelayoutSegment *segments, int count, bool pair, int k, uint4 *weights_out,
-                                   uint32_t *scales_out, cudaStream_t stream) {
-    if (count < 1 || count > 3 || (pair && count != 2) || k % 128 != 0) return cudaErrorInvalidValue;
+size_t int4_cta_stream_bytes(int rows, int k, bool pair, int grid) {
+    return stack_stream_bytes(stack_schedule(rows / 16, k / 128, pair ? 2 : 1, grid));
+}
+
+cudaError_t launch_int4_cta_streams(const RelayoutSegment *segments, int count, bool pair, int k, int grid, uint8_t *out, cudaStream_t stream) {
+    if (count < 1 || count > 3 || (pair && count != 2) || k % 128 != 0 || grid < 1) return cudaErrorInvalidValue;
     RelayoutArgs args = {};
     args.count = count;
     args.pair = pair ? 1 : 0;
@@ -1294,26 +1561,29 @@ cudaError_t launch_int4_tile_major(const RelayoutSegment *segments, int count, b
     }
     if (pair && segments[0].rows != segments[1].rows) return cudaErrorInvalidValue;
     args.first_tile[count] = tiles;
-    args.tiles = tiles;
-    int4_tile_major_kernel<<<148 * 4, 256, 0, stream>>>(args, weights_out, scales_out);
+    args.schedule = stack_schedule(tiles, k / 128, pair ? 2 : 1, grid);
+    const int passes = ((tiles + grid - 1) / grid + args.schedule.slots - 1) / args.schedule.slots;
+    if (tiles == 0) return cudaSuccess;
+    int4_cta_stream_kernel<<<dim3(passes * args.schedule.steps, grid), 256, 0, stream>>>(args, out);
     return cudaGetLastError();
 }
 
 bool decode_stack_supported(const StackShape &shape, int lanes, size_t *smem_bytes) {
-    size_t bytes = 0;
-    if (lanes < 1 || lanes > 8) return false;
-    if (shape.hidden > 2 * 8 * STACK_THREADS || shape.hidden % 128 != 0 || shape.ffn % 128 != 0 || (shape.q_heads * shape.head_width) % 128 != 0) return false;
-    if (!instance_smem(shape, lanes, &bytes, nullptr)) return false;
-    if (bytes > 227 * 1024) return false;
-    if (smem_bytes) *smem_bytes = bytes;
+    if (lanes < 1 || lanes > 8 || shape.grid < 1) return false;
+    if (shape.hidden > 2 * 8 * CONSUMER_THREADS || shape.hidden % 128 != 0 || shape.ffn % 128 != 0 || (shape.q_heads * shape.head_width) % 128 != 0) return false;
+    if (((shape.q_heads + 2 * shape.kv_heads) * shape.head_width) % 16 != 0) return false;
+    StackPlanSmem plan;
+    if (!plan_smem(shape, lanes, shape.grid, &plan)) return false;
+    if (smem_bytes) *smem_bytes = plan.total;
     return true;
 }
 
 cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count, const StackShape &shape,
                                 const StackBuffers &buffers, const LaneTable &lanes_meta, int lanes, int lanes_per_stream,
                                 int split_tokens, int max_splits, cudaStream_t stream, const StackTp *tp_device, int tp_size) {
-    size_t smem = 0;
-    if (!decode_stack_supported(shape, lanes, &smem) || lanes_per_stream <= 0 || lanes % lanes_per_stream != 0 || layer_count < 1)
+    StackPlanSmem plan;
+    if (lanes < 1 || lanes > 8 || !plan_smem(shape, lanes, shape.grid, &plan) || lanes_per_stream <= 0 || lanes % lanes_per_stream != 0 ||
+        layer_count < 1 || split_tokens != 64)
         return cudaErrorInvalidValue;
     StackArgs args;
     args.layers = layers_device;
@@ -1323,19 +1593,27 @@ cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count
     args.lanes_meta = lanes_meta;
     args.lanes = lanes;
     args.lanes_per_stream = lanes_per_stream;
-    args.split_tokens = split_tokens;
     args.max_splits = max_splits;
-    if (tp_size < 1 || tp_size > STACK_TP_MAX_RANKS || (tp_size > 1 && (tp_device == nullptr || shape.hidden % 4 != 0))) return cudaErrorInvalidValue;
+    if (tp_size < 1 || tp_size > STACK_TP_MAX_RANKS || (tp_size > 1 && tp_device == nullptr)) return cudaErrorInvalidValue;
     args.tp = tp_size > 1 ? tp_device : nullptr;
     args.tp_size = tp_size;
-    instance_smem(shape, lanes, &smem, &args.ring_units);
-    static const char *prefetch = getenv("NERVE_B200_STACK_L2_PREFETCH");
-    args.l2_prefetch = (prefetch != nullptr && prefetch[0] == '1') ? 1 : 0;  // off: the tile loops are not HBM-bound (yet)
+    args.stages = plan.stages;
+    args.stage_bytes = plan.stage_bytes;
+    args.steps_per_stage = plan.steps_per_stage;
+    args.slice_slots = plan.slice_slots;
+    args.slice_bytes = plan.slice_bytes;
+    args.scratch_bytes = static_cast<uint32_t>(plan.scratch);
+    // how many stages beyond the ring the producer asks L2 for
+    static const char *ahead = getenv("NERVE_B200_STACK_L2_AHEAD");
+    args.prefetch_stages = ahead != nullptr ? atoi(ahead) : 0;
+    if (args.prefetch_stages < 0) args.prefetch_stages = 0;
+    static const char *debug = getenv("NERVE_B200_STACK_DEBUG");
+    args.debug_flags = debug != nullptr ? atoi(debug) : 0;
     const int group = shape.q_heads / shape.kv_heads;
-    if (shape.head_width == 128 && group == 4) return launch_instance<128, 4>(args, smem, stream);
-    if (shape.head_width == 128 && group == 8) return launch_instance<128, 8>(args, smem, stream);
-    if (shape.head_width == 64 && group == 4) return launch_instance<64, 4>(args, smem, stream);
-    return launch_instance<32, 2>(args, smem, stream);
+    if (shape.head_width == 128 && group == 4) return launch_instance<128, 4>(args, plan.total, shape.grid, stream);
+    if (shape.head_width == 128 && group == 8) return launch_instance<128, 8>(args, plan.total, shape.grid, stream);
+    if (shape.head_width == 64 && group == 4) return launch_instance<64, 4>(args, plan.total, shape.grid, stream);
+    return launch_instance<32, 2>(args, plan.total, shape.grid, stream);
 }
 
 }  // namespace nerve

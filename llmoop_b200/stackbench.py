@@ -80,11 +80,13 @@ def main():
     for step, label in enumerate(["qkv", "o", "gate_up", "down"]):
         s0, s1, s2, s3 = (layers[:, 4 * step + i] for i in range(4))
         phases[label] = {"stage_us": float(np.mean(s1 - s0) / 1e3), "tiles_us": float(np.mean(s2 - s1) / 1e3),
+                         "steps_us": float(np.mean(layers[:, 26 + step] - s1) / 1e3),
                          "barrier_us": float(np.mean(s3 - s2) / 1e3)}
     phases["attention"] = {"teams_us": float(np.mean(layers[:, 17] - layers[:, 3]) / 1e3),
                            "barrier_us": float(np.mean(layers[:, 18] - layers[:, 17]) / 1e3),
                            "merge_us": float(np.mean(layers[:, 19] - layers[:, 18]) / 1e3),
                            "barrier2_us": float(np.mean(layers[:, 4] - layers[:, 19]) / 1e3)}
+    phases["attention_item"] = {f"t{i}_us": float(np.mean(layers[:, 20 + i] - layers[:, 3]) / 1e3) for i in range(6)}
     layer_us = float(np.mean(layers[:, 15] - layers[:, 0]) / 1e3)
     weight_bytes = package.info["target_stack_weight_bytes"] / max(1, args.layers)
     if rank == 0:

@@ -533,15 +533,28 @@ class Oracle:
         stream.next_tick += 1
         return (int(self.sample(logits, tick)[0]), logits) if emit else (None, None)
 
+    # -- stream state a cycle changes besides the (positional, overwritable) KV slots ------------------------
+    @staticmethod
+    def checkpoint(stream):
+        return stream.next_tick, None if stream.pending_hidden is None else stream.pending_hidden.copy()
+
+    @staticmethod
+    def restore(stream, saved):
+        stream.next_tick, stream.pending_hidden = saved[0], None if saved[1] is None else saved[1].copy()
+
     # -- one speculative cycle: feedback_generation.rs:66-194 ---------------------------------------------
-    def speculative_cycle(self, stream, initial_token, draft_count, stop_tokens=(), forced_drafts=None):
+    def speculative_cycle(self, stream, initial_token, draft_count, stop_tokens=(), forced_drafts=None, forced_targets=None):
+        """forced_drafts / forced_targets replace the sampled draft / target tokens (the sampled ones are kept in
+        `sampled_draft_token_ids` / `sampled_target_token_ids`): teacher forcing, and following another
+        implementation's run through a near-tie."""
         start = stream.next_tick
         drafts = []
         token, hidden = initial_token, stream.pending_hidden
-        draft_logits = []
+        draft_logits, sampled_drafts = [], []
         for j in range(draft_count):
             normalized, logits = self.draft_forward(stream, [token], hidden, start + j, want_logits=True)
             token = int(self.sample(logits, start + j)[0])
+            sampled_drafts.append(token)
             draft_logits.append(logits[0])
             if forced_drafts is not None:
                 token = int(forced_drafts[j])
@@ -549,7 +562,12 @@ class Oracle:
             hidden = normalized
         inputs = [initial_token] + drafts
         normalized, logits = self.target_forward(stream, inputs, start, want_logits=True)
-        targets = [int(t) for t in self.sample(logits, start)]
+        sampled_targets = [int(t) for t in self.sample(logits, start)]
+        targets = list(sampled_targets)
+        if forced_targets is not None:
+            for position, forced in enumerate(forced_targets):
+                if position < len(targets):
+                    targets[position] = int(forced)
         accepted, committed, emitted = verify_prefix(drafts, targets, stop_tokens)
         # draft catch-up: state steps for the committed inputs with hidden = pending / target frame i-1
         hidden = np.concatenate([stream.pending_hidden, normalized[:committed - 1]], axis=0)
@@ -559,6 +577,7 @@ class Oracle:
         return {
             "draft_token_ids": drafts, "target_token_ids": targets, "accepted": accepted, "committed": committed,
             "emitted": emitted, "target_logits": logits, "draft_logits": draft_logits, "start_tick": start,
+            "sampled_draft_token_ids": sampled_drafts, "sampled_target_token_ids": sampled_targets,
         }
 
     # -- a whole input event: placed_prompt_event.rs:167-291 + placed_prompt_stream.rs:570-645 ------------

@@ -1,7 +1,7 @@
 """Tensor-parallel engine on two GPUs of one box (skipped where fewer are visible): each rank mounts its shard of a
 synthetic INT4 package, joins the NCCL group through the C ABI and runs the same stream; the ranks must emit the
-same tokens, and those must be the oracle's (sequences may part where the oracle's top-2 logit gap is below 2e-2:
-the ranks' partial sums are added in another order than one GPU's).  Two forms: kernel by kernel with NCCL
+same tokens, and those must be the oracle's (a divergence only where the oracle's top-2 logit gap is below 1e-3,
+and every later token and cycle is still compared).  Two forms: kernel by kernel with NCCL
 all-reduces, and the persistent decode kernel with its exchange over peer memory (far fewer launches)."""
 
 import os
@@ -46,9 +46,9 @@ def _worker(rank, size, port, directory, prompt, drafts, exchange, out):
     engine.set_cycle_logging(True)
     engine.add_stream(1, speculative_draft_tokens=drafts)
     tokens, report = engine.submit_input_event_until_idle(1, prompt, 20)
-    accepted = [c["accepted"] for c in engine.cycle_log()]
+    cycles = [{key: (list(value) if isinstance(value, list) else int(value)) for key, value in cycle.items()} for cycle in engine.cycle_log()]
     gathered = [None] * size
-    dist.all_gather_object(gathered, (tokens, accepted, report.kernel_launches))
+    dist.all_gather_object(gathered, (tokens, cycles, report.kernel_launches))
     if rank == 0:
         out.put(pickle.dumps(gathered))
     engine.close()
@@ -67,6 +67,7 @@ def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, drafts, exchange):
     from llmoop_b200.package_writer import write_package
     from llmoop_b200.synth import ModelSpec
     from oracle.nerve_oracle import Oracle, OraclePackage, OracleStream
+    from oracle.parity import follow_generation, summary
 
     spec = ModelSpec(name="tp_int4", hidden=1024, layers=2, q_heads=8, kv_heads=2, head_dim=128, ffn=3584, vocab=1024,
                      max_positions=512, quant="int4", std=0.02, seed=21)
@@ -75,7 +76,6 @@ def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, drafts, exchange):
     prompt = [int(t) for t in np.random.default_rng(4).integers(0, spec.vocab, size=11)]
     opkg = OraclePackage(directory)
     oracle = Oracle(opkg)
-    expected = oracle.generate(OracleStream(opkg, 128), prompt, 20, drafts, collect_logits=True)
 
     context = mp.get_context("spawn")
     out = context.Queue()
@@ -93,15 +93,12 @@ def test_two_gpu_tensor_parallel_matches_oracle(tmp_path, drafts, exchange):
                 process.kill()
     gathered = pickle.loads(out.get(timeout=10))
     assert gathered[0][:2] == gathered[1][:2]  # the ranks agree token for token
-    tokens, accepted, launches = gathered[0]
+    tokens, cycles, launches = gathered[0]
     print(f"kernel launches: {launches}")
     # kernel by kernel every layer is ~20 launches per forward; the persistent kernel is one per stack
     assert (launches < LAUNCH_BOUND[drafts]) == exchange, launches
-    for index, (got, want) in enumerate(zip(tokens, expected["tokens"])):
-        if got != want:
-            gap = oracle.top2_gap(expected["logits"][index])
-            assert gap < 2e-2, f"token {index}: tensor-parallel {got} != oracle {want} with top-2 gap {gap}"
-            break
-    else:
-        assert len(tokens) == len(expected["tokens"])
-        assert accepted == [c["accepted"] for c in expected["cycles"]]
+    # the north star's rule, every token and cycle compared (oracle/parity.py follows the run through near-ties)
+    assert len(tokens) == 20
+    outcome = follow_generation(oracle, OracleStream(opkg, 128), prompt, tokens, cycles, drafts)
+    assert outcome["tokens_compared"] == len(tokens) and not outcome["violations"] and outcome["accepted_equal"], outcome
+    print("tensor-parallel generation parity:", summary(outcome))
