@@ -162,6 +162,7 @@ int32_t nerve_b200_engine_stream_tick(const nerve_b200_engine *engine, int64_t s
 int32_t nerve_b200_engine_set_teacher_tokens(nerve_b200_engine *engine, int64_t stream_id, const uint32_t *tokens,
                                              size_t count);
 int32_t nerve_b200_engine_set_prefill_chunk(nerve_b200_engine *engine, int32_t tokens);
+/* Keeps one record per speculative cycle (nerve_b200_engine_cycle_log); switching it on starts a new log. */
 int32_t nerve_b200_engine_set_cycle_logging(nerve_b200_engine *engine, int32_t enabled);
 /* Records CUDA events around every INT4 linear launch (adds launch overhead; for roofline measurement only). */
 int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabled);

@@ -214,7 +214,10 @@ public:
     StreamSnapshot stream_snapshot(int64_t id) const;
     EngineSnapshot snapshot() const;
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
-    void set_cycle_logging(bool enabled) { log_cycles_ = enabled; }
+    void set_cycle_logging(bool enabled) {  // switching it on starts a new log
+        log_cycles_ = enabled;
+        if (enabled) cycle_log_.clear();
+    }
     void set_use_graphs(bool enabled) { use_graphs_ = enabled; }
     // The persistent decode stack kernel serves batches of at most 8 lanes of dense INT4 stacks; off = the
     // kernel-per-operator path for everything.

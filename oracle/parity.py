@@ -17,14 +17,19 @@ from __future__ import annotations
 GAP_LIMIT = 1e-3
 
 
-def follow_generation(oracle, stream, prompt, cuda_tokens, cuda_cycles, drafts, gap_limit=GAP_LIMIT, prefill_chunk=64, max_cycles=None):
+def follow_generation(oracle, stream, prompt, cuda_tokens, cuda_cycles, drafts, gap_limit=GAP_LIMIT, prefill_chunk=64, max_cycles=None,
+                      cycle_seconds=None, seconds_budget=None):
     """Replays `prompt` + the generated `cuda_tokens` on `oracle`/`stream`.
 
     cuda_cycles: the engine's cycle log (dicts with accepted, committed, emitted, target_token_ids) - empty for a run
     without speculation.  Returns a dict: tokens_compared, cycles_compared, tokens_equal (no divergence at all),
     divergences (list of dicts: position, kind, gap, cuda, oracle), violations (divergences whose gap is not below
     gap_limit: parity failures), accepted_equal (per-cycle acceptance counts equal wherever the tokens were).
+    cycle_seconds: optional list that receives the wall time of every (first, unforced) oracle cycle; with
+    seconds_budget the replay stops once those add up to it (a bounded sample of a long run).
     """
+    import time
+
     report = {"tokens_compared": 0, "cycles_compared": 0, "tokens_equal": True, "accepted_equal": True, "divergences": [], "violations": []}
 
     def note(position, kind, gap, cuda, mine):
@@ -47,13 +52,18 @@ def follow_generation(oracle, stream, prompt, cuda_tokens, cuda_cycles, drafts, 
     while position < len(cuda_tokens):
         if max_cycles is not None and report["cycles_compared"] >= max_cycles:
             break
+        if seconds_budget is not None and cycle_seconds is not None and sum(cycle_seconds) > seconds_budget:
+            break
         remaining = len(cuda_tokens) - position
         if drafts > 0 and oracle.pkg.draft is not None and cycle_index < len(cuda_cycles) and remaining >= 2:
             theirs = cuda_cycles[cycle_index]
             cycle_index += 1
             count = min(drafts, remaining - 1)
             saved = oracle.checkpoint(stream)
+            started = time.perf_counter()
             mine = oracle.speculative_cycle(stream, token, count)
+            if cycle_seconds is not None:
+                cycle_seconds.append(time.perf_counter() - started)
             emitted = [int(t) for t in theirs["emitted"]]
             same = mine["emitted"] == emitted and mine["accepted"] == int(theirs["accepted"])
             if not same:
