@@ -164,6 +164,12 @@ int32_t nerve_b200_engine_set_teacher_tokens(nerve_b200_engine *engine, int64_t 
 int32_t nerve_b200_engine_set_prefill_chunk(nerve_b200_engine *engine, int32_t tokens);
 /* Keeps one record per speculative cycle (nerve_b200_engine_cycle_log); switching it on starts a new log. */
 int32_t nerve_b200_engine_set_cycle_logging(nerve_b200_engine *engine, int32_t enabled);
+/* Failure injection without a fault: the next `launches` launches of the persistent decode kernel wait at their first
+ * grid barrier for arrivals that cannot come; the bounded wait gives up after a few milliseconds, the kernel reports
+ * it and the run call fails with the streams as they were before the batch (nothing emitted, ticks unchanged; the
+ * reference restores a failed cycle the same way, placed_stream_processor/feedback_generation.rs:188-192).  The
+ * engine stays usable. */
+int32_t nerve_b200_engine_inject_barrier_timeouts(nerve_b200_engine *engine, int32_t launches);
 /* Records CUDA events around every INT4 linear launch (adds launch overhead; for roofline measurement only). */
 int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabled);
 /* Tensor parallelism (the reference's sharding plan: vulkan_distributed/planning.rs:180-528).  A package mounted

@@ -335,6 +335,14 @@ int32_t nerve_b200_engine_set_profiling(nerve_b200_engine *engine, int32_t enabl
     });
 }
 
+int32_t nerve_b200_engine_inject_barrier_timeouts(nerve_b200_engine *engine, int32_t launches) {
+    return guarded([&] {
+        require(engine != nullptr, "null engine");
+        require(launches >= 0, "launches must not be negative");
+        engine->engine->inject_barrier_timeouts(launches);
+    });
+}
+
 int32_t nerve_b200_engine_run(nerve_b200_engine *engine, uint64_t max_batches, nerve_b200_output_callback on_output, void *user,
                               nerve_b200_run_report *out) {
     return guarded([&] {

@@ -470,6 +470,10 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     cuda_check(cudaStreamCreateWithFlags(&cuda_stream_, cudaStreamNonBlocking), "cudaStreamCreate");
     cuda_check(cudaEventCreate(&event_a_), "cudaEventCreate");
     cuda_check(cudaEventCreate(&event_b_), "cudaEventCreate");
+    cuda_check(cudaEventCreate(&event_begin_), "cudaEventCreate");
+    cuda_check(cudaEventCreate(&run_begin_), "cudaEventCreate");
+    cuda_check(cudaEventCreate(&run_end_), "cudaEventCreate");
+    cuda_check(cudaEventCreate(&event_end_), "cudaEventCreate");
     const size_t lanes = options.max_lanes;
     const size_t frame = static_cast<size_t>(plan.hidden) * 2;
 
@@ -502,6 +506,7 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     lane_positions_ = device_alloc(lanes * sizeof(uint32_t));
     lane_slots_ = device_alloc(lanes * sizeof(int32_t));
     pending_hidden_ = device_alloc(static_cast<size_t>(options.max_streams) * frame);
+    pending_backup_ = device_alloc(static_cast<size_t>(options.max_streams) * frame);
 
     split_tokens_ = 64;
     max_splits_ = static_cast<int>((model_->capacity() + split_tokens_ - 1) / split_tokens_);
@@ -557,7 +562,7 @@ Engine::~Engine() {
     set_int4_error_flag(nullptr);
     for (auto &entry : signals_) cudaFree(entry.second.ptr);
     for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
-                                 &records_, &argmax_scratch_, &sampler_scratch_, &sampler_table_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &attention_scratch_,
+                                 &records_, &argmax_scratch_, &sampler_scratch_, &sampler_table_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &pending_backup_, &attention_scratch_,
                                  &cycle_state_, &kernel_error_, &tp_partial_, &tp_exchange_, &tp_description_, &stack_q_, &stack_attention_out_, &stack_activation_, &stack_barrier_, &stack_timing_})
         cudaFree(buffer->ptr);
     cudaFreeHost(staging_);
@@ -567,6 +572,10 @@ Engine::~Engine() {
         if (entry.second.exec) cudaGraphExecDestroy(entry.second.exec);
     cudaEventDestroy(event_a_);
     cudaEventDestroy(event_b_);
+    cudaEventDestroy(event_begin_);
+    cudaEventDestroy(run_begin_);
+    cudaEventDestroy(run_end_);
+    cudaEventDestroy(event_end_);
     cudaStreamDestroy(cuda_stream_);
 }
 
@@ -1216,8 +1225,16 @@ int Engine::splits_for(uint64_t newest_tick) const {
 // Runs `body` (stream-ordered launches only: no uploads, read-backs or synchronisation) directly the first time a
 // key is seen, then captures it into a CUDA graph and replays the graph from the third call on.
 void Engine::run_phase(const std::vector<int> &key, const std::function<void()> &body) {
-    // tensor-parallel engines launch directly: the all-reduces are not replayed from a captured graph
-    if (!use_graphs_ || profile_ || model_->options().tp_size > 1) {
+    // Tensor-parallel engines replay graphs only for phases that contain no NCCL call: every forward of the phase
+    // runs in the persistent kernel (at most 8 lanes), whose exchange goes over peer memory.  A launch with the
+    // barrier test hook armed is never captured (the hook is a kernel argument).
+    bool direct = !use_graphs_ || profile_ || inject_barrier_timeouts_ > 0;
+    if (model_->options().tp_size > 1) {
+        const bool stacks = model_->target_stack().available && (!model_->plan().has_draft || model_->draft_stack().available);
+        const bool small = key.size() >= 3 && key[1] * (key[2] + 1) <= 8;
+        if (!(tp_connected_ && stack_enabled_ && stacks && small)) direct = true;
+    }
+    if (direct) {
         body();
         return;
     }
@@ -1265,6 +1282,11 @@ bool Engine::run_stack(const StackPlan &stack, int lanes, void *hidden) {
     buffers.barrier = static_cast<unsigned int *>(stack_barrier_.ptr);
     buffers.error_flag = static_cast<int *>(kernel_error_.ptr);
     buffers.timing = (profile_ && &stack == &model_->target_stack()) ? static_cast<unsigned long long *>(stack_timing_.ptr) : nullptr;
+    buffers.barrier_handicap = 0;
+    if (inject_barrier_timeouts_ > 0) {
+        inject_barrier_timeouts_--;
+        buffers.barrier_handicap = 1u << 20;
+    }
     profile_begin(stack.weight_bytes);
     check(launch_decode_stack(static_cast<const StackLayer *>(stack.device_layers.ptr), static_cast<int>(stack.layers.size()), stack.shape,
                               buffers, current_lanes_, lanes, current_width_, split_tokens_, current_splits_, cuda_stream_,
@@ -1410,6 +1432,29 @@ void Engine::emit(Stream &s, uint32_t token, uint64_t tick, const std::function<
     if (on_output) on_output(output);
 }
 
+// ---------------------------------------------------------------------------- kernel errors
+// A kernel whose bounded wait expired sets the error word and finishes on garbage.  The word travels back with every
+// batch's read-back; when it is set nothing of the batch is emitted or committed - stream ticks are untouched, the
+// pending hidden states are put back as they were (the KV slots the batch wrote are rewritten when the ticks are
+// replayed) - and the call fails, as the reference restores the state of a failed cycle
+// (placed_stream_processor/feedback_generation.rs:188-192).
+
+void Engine::backup_pending() {
+    cuda_check(cudaMemcpyAsync(pending_backup_.ptr, pending_hidden_.ptr, pending_hidden_.bytes, cudaMemcpyDeviceToDevice, cuda_stream_), "pending hidden backup");
+}
+
+void Engine::check_kernel_status(const uint32_t *status_word) {
+    if (*status_word == 0) return;
+    const int code = static_cast<int>(*status_word);
+    cuda_check(cudaMemsetAsync(kernel_error_.ptr, 0, sizeof(int), cuda_stream_), "kernel status reset");
+    if (stack_barrier_.ptr) cuda_check(cudaMemsetAsync(stack_barrier_.ptr, 0, stack_barrier_.bytes, cuda_stream_), "barrier reset");
+    cuda_check(cudaMemcpyAsync(pending_hidden_.ptr, pending_backup_.ptr, pending_hidden_.bytes, cudaMemcpyDeviceToDevice, cuda_stream_), "pending hidden restore");
+    synchronize("restore synchronize");
+    if (model_->options().tp_size > 1) failed_ = true;  // the peers' exchange counters have moved on without this rank
+    fail(code == 2 ? "the decode stack kernel gave up waiting at a grid barrier (or for a tensor-parallel peer); the batch was discarded and the streams are as before it"
+                   : "a kernel gave up waiting on its copy pipeline; the batch was discarded and the streams are as before it");
+}
+
 // ---------------------------------------------------------------------------- single ticks (placed_prompt_stream.rs:353-420)
 
 void Engine::run_single_ticks(std::vector<Stream *> &batch, const std::function<void(const OutputEvent &)> &on_output, RunReport &report) {
@@ -1431,6 +1476,7 @@ void Engine::run_single_ticks(std::vector<Stream *> &batch, const std::function<
     upload_lanes(positions, slots);
     upload_tokens(tokens.data(), lanes);
     current_width_ = 1;
+    if (plan.has_draft) backup_pending();
     target_forward(lanes, any_emit);
     if (plan.has_draft) {
         check(launch_gather_rows(static_cast<const uint16_t *>(pending_hidden_.ptr), static_cast<const int32_t *>(lane_slots_.ptr),
@@ -1448,7 +1494,11 @@ void Engine::run_single_ticks(std::vector<Stream *> &batch, const std::function<
                    "record readback");
         counters_.d2h_bytes += lanes * 16;
     }
+    uint32_t *status_word = host_records_ + static_cast<size_t>(lanes) * 4;
+    cuda_check(cudaMemcpyAsync(status_word, kernel_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, cuda_stream_), "kernel status readback");
+    counters_.d2h_bytes += 4;
     synchronize("tick synchronize");
+    check_kernel_status(status_word);
     for (int i = 0; i < lanes; i++) {
         Stream &s = *batch[i];
         ActiveEvent &event = *s.active;
@@ -1519,7 +1569,8 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
     const int splits = splits_for(newest_tick);
     current_splits_ = splits;
 
-    uint64_t t0 = now_ns();
+    backup_pending();
+    cuda_check(cudaEventRecord(event_begin_, cuda_stream_), "event record");
     // ---- draft loop: `drafts` serial steps over `streams` lanes
     run_phase({0, streams, drafts, splits, stochastic_streams_ != 0 ? 1 : 0, stack_enabled_ ? 1 : 0}, [&] {
         for (int j = 0; j < drafts; j++) {
@@ -1567,13 +1618,18 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
               "accept");
         draft_forward(lanes, static_cast<const uint16_t *>(draft_hidden_in_.ptr), false);
     });
+    cuda_check(cudaEventRecord(event_end_, cuda_stream_), "event record");
     cuda_check(cudaMemcpyAsync(host_records_, accept_rows, streams * row_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, cuda_stream_),
                "accept readback");
-    counters_.d2h_bytes += streams * row_words * 4;
+    uint32_t *status_word = host_records_ + static_cast<size_t>(streams) * row_words;
+    cuda_check(cudaMemcpyAsync(status_word, kernel_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, cuda_stream_), "kernel status readback");
+    counters_.d2h_bytes += streams * row_words * 4 + 4;
     synchronize("cycle synchronize");
-    uint64_t t1 = now_ns();
-    float verify_ms = 0.0f;
+    check_kernel_status(status_word);  // nothing of a failed cycle is emitted
+    float verify_ms = 0.0f, draft_ms = 0.0f, catch_up_ms = 0.0f;
     cuda_check(cudaEventElapsedTime(&verify_ms, event_a_, event_b_), "event elapsed");
+    cuda_check(cudaEventElapsedTime(&draft_ms, event_begin_, event_a_), "event elapsed");
+    cuda_check(cudaEventElapsedTime(&catch_up_ms, event_b_, event_end_), "event elapsed");
     report.verify_ms_sum += verify_ms;
     report.verify_steps++;
     uint64_t kv_bytes = 0;
@@ -1606,9 +1662,8 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
         }
     }
     report.speculative.target_verification_time_ns += static_cast<uint64_t>(verify_ms * 1e6);
-    report.speculative.draft_time_ns += 0;
-    (void)t0;
-    (void)t1;
+    report.speculative.draft_time_ns += static_cast<uint64_t>(draft_ms * 1e6);            // feedback_generation.rs:100-131
+    report.speculative.draft_catch_up_time_ns += static_cast<uint64_t>(catch_up_ms * 1e6);  // feedback_generation.rs:160-174 (acceptance included)
 }
 
 // ---------------------------------------------------------------------------- run loop
@@ -1616,14 +1671,12 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
 RunReport Engine::run_until_idle(const std::function<void(const OutputEvent &)> &on_output) { return run(0, on_output); }
 
 RunReport Engine::run(uint64_t max_batches, const std::function<void(const OutputEvent &)> &on_output) {
+    if (failed_) fail("this tensor-parallel rank gave up waiting for its peers in an earlier run: the group's engines must be created anew");
     RunReport report;
     counters_ = ExecCounters{};
     profile_ms_ = 0.0;
     profile_bytes_ = profile_launches_ = 0;
-    cudaEvent_t run_begin, run_end;
-    cuda_check(cudaEventCreate(&run_begin), "cudaEventCreate");
-    cuda_check(cudaEventCreate(&run_end), "cudaEventCreate");
-    cuda_check(cudaEventRecord(run_begin, cuda_stream_), "event record");
+    cuda_check(cudaEventRecord(run_begin_, cuda_stream_), "event record");
     while (true) {
         if (max_batches && report.batch_count >= max_batches) {
             report.idle = false;
@@ -1710,20 +1763,12 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
         report.decode_ns += now_ns() - start;
         if (!any) break;
     }
-    cuda_check(cudaEventRecord(run_end, cuda_stream_), "event record");
+    cuda_check(cudaEventRecord(run_end_, cuda_stream_), "event record");
     cuda_check(cudaMemcpyAsync(host_records_, kernel_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, cuda_stream_), "kernel status readback");
     synchronize("run synchronize");
-    if (host_records_[0] != 0) {
-        const int code = static_cast<int>(host_records_[0]);
-        cuda_check(cudaMemsetAsync(kernel_error_.ptr, 0, sizeof(int), cuda_stream_), "kernel status reset");
-        if (stack_barrier_.ptr) cuda_check(cudaMemsetAsync(stack_barrier_.ptr, 0, stack_barrier_.bytes, cuda_stream_), "barrier reset");
-        fail(code == 2 ? "the decode stack kernel gave up waiting at a grid barrier; results of this run are invalid"
-                       : "a pipelined kernel gave up waiting on its copy pipeline; results of this run are invalid");
-    }
+    check_kernel_status(host_records_);  // batches that read nothing back (prompt chunks without a sampled token)
     float device_ms = 0.0f;
-    cuda_check(cudaEventElapsedTime(&device_ms, run_begin, run_end), "event elapsed");
-    cudaEventDestroy(run_begin);
-    cudaEventDestroy(run_end);
+    cuda_check(cudaEventElapsedTime(&device_ms, run_begin_, run_end_), "event elapsed");
     report.device_ms = device_ms;
     report.int4_ms = profile_ms_;
     report.int4_bytes = profile_bytes_;

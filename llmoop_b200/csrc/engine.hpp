@@ -214,6 +214,9 @@ public:
     StreamSnapshot stream_snapshot(int64_t id) const;
     EngineSnapshot snapshot() const;
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
+    // Test hook: the next `launches` launches of the persistent decode kernel wait (briefly) at their first grid barrier for
+    // an arrival count the grid cannot reach, give up and report it - a failure made without faulting anything.
+    void inject_barrier_timeouts(int launches) { inject_barrier_timeouts_ = launches; }
     void set_cycle_logging(bool enabled) {  // switching it on starts a new log
         log_cycles_ = enabled;
         if (enabled) cycle_log_.clear();
@@ -296,7 +299,7 @@ private:
     std::vector<int32_t> page_refcount_;
     std::vector<int32_t> block_table_host_;
     cudaStream_t cuda_stream_ = nullptr;
-    cudaEvent_t event_a_ = nullptr, event_b_ = nullptr;
+    cudaEvent_t event_a_ = nullptr, event_b_ = nullptr, event_begin_ = nullptr, event_end_ = nullptr, run_begin_ = nullptr, run_end_ = nullptr;
 
     // workspaces
     std::map<std::string, DeviceBuffer> signals_;
@@ -314,6 +317,7 @@ private:
     void sample_lanes(const float *logits, uint32_t *records, int lanes, const int32_t *slots, const uint32_t *ticks, const char *what);
     DeviceBuffer lane_tokens_, lane_positions_, lane_slots_;
     DeviceBuffer pending_hidden_;           // [max_streams][hidden]
+    DeviceBuffer pending_backup_;           // the same rows as they were before the batch in flight (restored when a kernel reports an error)
     DeviceBuffer attention_scratch_;
     DeviceBuffer kernel_error_;             // device word set by pipelined kernels whose bounded waits expired
     DeviceBuffer tp_partial_;               // f32 [max_lanes][hidden] partial sums of row-parallel linears
@@ -327,6 +331,8 @@ private:
     DeviceBuffer stack_q_, stack_attention_out_, stack_activation_, stack_barrier_, stack_timing_;
     bool stack_enabled_ = true;
     bool run_stack(const StackPlan &stack, int lanes, void *hidden);
+    void backup_pending();
+    void check_kernel_status(const uint32_t *status_word);  // throws (after restoring the pending hidden states) when a kernel reported an error
     DeviceBuffer cycle_state_;              // device-side per-batch cycle arrays (see engine.cu)
     // Pinned staging arena for host->device uploads: every upload between two host synchronisations gets its
     // own region (an asynchronous copy reads the pinned source when it executes, not when it is enqueued).
@@ -336,6 +342,8 @@ private:
     int split_tokens_ = 256, max_splits_ = 1;
     int prefill_chunk_ = 64;
     bool use_graphs_ = true, log_cycles_ = false;
+    bool failed_ = false;                   // a tensor-parallel rank whose kernel gave up is out of step with its peers for good
+    int inject_barrier_timeouts_ = 0;       // test hook: this many decode stack launches wait for arrivals that cannot come
     std::vector<CycleRecord> cycle_log_;
     ExecCounters counters_;
     // per-launch CUDA events around the INT4 linears (profiling mode only)

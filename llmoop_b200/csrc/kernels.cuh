@@ -180,6 +180,8 @@ struct StackBuffers {
     unsigned int *barrier;       // STACK_BARRIER_WORDS words, zero before the first launch
     int *error_flag;             // set when a bounded wait expires (2: grid barrier or peer, 3: weight pipeline)
     unsigned long long *timing;  // optional [layers][32] nanosecond stamps of CTA 0 (step boundaries), or nullptr
+    unsigned int barrier_handicap;  // test hook: arrivals the grid barriers wait for on top of the grid's own (0 in service);
+                                    // they can never come, so the first barrier gives up after a short bounded wait
 };
 constexpr int STACK_BARRIER_WORDS = 1024;  // two barrier words, then the attention arrival counters (kv heads x lane groups)
 // Tensor-parallel exchange of the persistent kernel: every rank holds the same residual stream and its shard of

@@ -185,14 +185,14 @@ __device__ __forceinline__ void team_barrier(int barrier_id) { asm volatile("bar
 // All CTAs of the (cooperative, co-resident) grid meet here; only the consumer warps take part.  `target` counts
 // the arrivals expected so far.  A wait that does not complete within the spin limit sets the error flag and lets
 // the CTA go on (its results are then garbage, the host sees the flag); once the flag is up nobody waits any more.
-__device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int &target, int *error_flag) {
+__device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int &target, int *error_flag, unsigned int spin_limit) {
     consumer_sync();
     if (threadIdx.x == 0) {
         target += gridDim.x;
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");  // covers the CTA's writes before the barrier above
         unsigned int spins = 0;
         while (load_acquire(counter) < target) {
-            if (++spins > BARRIER_SPIN_LIMIT) {
+            if (++spins > spin_limit) {
                 atomicExch(error_flag, 2);
                 break;
             }
@@ -1132,7 +1132,8 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     }
 
     // ------------------------------------------------------------------ consumers
-    unsigned int target = 0, barriers_passed = 0;
+    unsigned int target = a.buffers.barrier_handicap, barriers_passed = 0;
+    const unsigned int barrier_spin_limit = a.buffers.barrier_handicap != 0 ? (1u << 12) : BARRIER_SPIN_LIMIT;
     unsigned int *counter = a.buffers.barrier;
     unsigned int *arrivals = a.buffers.barrier + ARRIVAL_WORDS_OFFSET;
     int *error_flag = a.buffers.error_flag;
@@ -1164,7 +1165,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
         }
     };
     auto meet = [&]() {
-        grid_barrier(counter, target, error_flag);
+        grid_barrier(counter, target, error_flag, barrier_spin_limit);
         barriers_passed++;
         if (threadIdx.x == 0) shared_store_release(ring.open_word, barriers_passed);
     };

@@ -76,7 +76,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_destroy", "nerve_b200_engine_add_stream", "nerve_b200_engine_fork_stream",
     "nerve_b200_engine_reset_stream", "nerve_b200_engine_remove_stream", "nerve_b200_engine_interrupt_stream",
     "nerve_b200_engine_enqueue", "nerve_b200_engine_run_until_idle", "nerve_b200_engine_run",
-    "nerve_b200_engine_set_profiling", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_stop_after_current", "nerve_b200_engine_stream_snapshot_of", "nerve_b200_engine_snapshot", "nerve_b200_engine_init_tp", "nerve_b200_engine_tp_exchange_handle", "nerve_b200_engine_tp_connect", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
+    "nerve_b200_engine_set_profiling", "nerve_b200_engine_inject_barrier_timeouts", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_stop_after_current", "nerve_b200_engine_stream_snapshot_of", "nerve_b200_engine_snapshot", "nerve_b200_engine_init_tp", "nerve_b200_engine_tp_exchange_handle", "nerve_b200_engine_tp_connect", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
     "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair", "nerve_b200_set_int4_kernel",
@@ -295,6 +295,10 @@ class Engine:
 
     def set_profiling(self, enabled: bool):
         _check(library().nerve_b200_engine_set_profiling(self._handle, int(enabled)))
+
+    def inject_barrier_timeouts(self, launches: int):
+        """Test hook: the next `launches` persistent-kernel launches give up at their first grid barrier."""
+        _check(library().nerve_b200_engine_inject_barrier_timeouts(self._handle, int(launches)))
 
     def run(self, max_batches: int = 0, on_output=None):
         """Bounded run: stops after `max_batches` decode batches (0 = until idle)."""
