@@ -229,9 +229,6 @@ int32_t nerve_b200_op_linear_int4_silu_pair(const void *x_device, const void *ga
                                             const void *gate_scales_device, const void *up_qweight_device,
                                             const void *up_scales_device, void *y_device, int32_t lanes, int32_t n,
                                             int32_t k, void *stream);
-/* Selects the INT4 kernel: 0 = register-prefetch kernel (default), 1 = bulk-copy pipelined kernel (used where
- * k % 2048 == 0, otherwise the register kernel still runs). Process-wide; not to be changed while work is queued. */
-int32_t nerve_b200_set_int4_kernel(int32_t pipelined);
 /* linear_bf16.comp.template:38-95; to_f32 != 0 gives tied_output_projection_bf16.comp.template:33-91 (f32 * scale). */
 int32_t nerve_b200_op_linear_bf16(const void *x_device, const void *w_device, void *y_device,
                                   const void *residual_device, int32_t lanes, int32_t n, int32_t k, int32_t to_f32,
@@ -265,8 +262,7 @@ uint64_t nerve_b200_op_sample_scratch_bytes(int32_t lanes);
  * buffer the runtime allocated at mount).
  * Who needs it: a sampler thread inside a serving process whose device memory was carved up once at start-up
  * (a later cudaMalloc may fail under fragmentation, and it synchronises the whole device, stalling every other
- * stream's decode step), or code that runs where allocation is forbidden outright, such as a host callback
- * enqueued on a stream.
+ * stream's decode step).
  * Limits and rules:
  *  - at most 64 lanes per call; more is rejected with an error naming the limit (use nerve_b200_op_greedy);
  *  - the first call on each device looks up the array's device address (with that device current) and caches

@@ -459,11 +459,6 @@ int32_t nerve_b200_op_linear_int4_silu_pair(const void *x, const void *gate_q, c
                        "nerve_b200_op_linear_int4_silu_pair");
 }
 
-int32_t nerve_b200_set_int4_kernel(int32_t pipelined) {
-    set_int4_stream_enabled(pipelined);
-    return NERVE_B200_OK;
-}
-
 int32_t nerve_b200_op_linear_bf16(const void *x, const void *w, void *y, const void *residual, int32_t lanes, int32_t n, int32_t k,
                                   int32_t to_f32, float scale, void *stream) {
     int epilogue = to_f32 ? EPILOGUE_F32_SCALED : (residual ? EPILOGUE_RESIDUAL_ROUNDED : EPILOGUE_BF16);

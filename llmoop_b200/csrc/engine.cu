@@ -529,7 +529,6 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     cuda_check(cudaMallocHost(&host_records_, lanes * 64 * sizeof(uint32_t)), "cudaMallocHost");
 
     kernel_error_ = device_alloc(sizeof(int));
-    set_int4_error_flag(static_cast<int *>(kernel_error_.ptr));
     if (options.tp_size > 1) tp_partial_ = device_alloc(lanes * static_cast<size_t>(plan.hidden) * sizeof(float));
     {
         size_t q_width = 0, ffn = 0;
@@ -559,7 +558,6 @@ Engine::~Engine() {
     cudaStreamSynchronize(cuda_stream_);
     if (nccl_comm_ != nullptr) g_nccl.comm_destroy(nccl_comm_);
     for (void *mapping : tp_peer_mappings_) cudaIpcCloseMemHandle(mapping);
-    set_int4_error_flag(nullptr);
     for (auto &entry : signals_) cudaFree(entry.second.ptr);
     for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
                                  &records_, &argmax_scratch_, &sampler_scratch_, &sampler_table_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &pending_backup_, &attention_scratch_,

@@ -106,20 +106,6 @@ cudaError_t launch_linear_int4_silu_pair(const uint16_t *x, const uint32_t *gate
                                          const uint32_t *up_q, const uint16_t *up_s, uint16_t *y, int lanes, int n,
                                          int k, cudaStream_t stream);
 
-// Bulk-copy pipelined INT4 kernel (kernels_int4_stream.cu); used by the launchers above when k % 1024 == 0.
-bool linear_int4_stream_supported(int k);
-cudaError_t launch_linear_int4_stream(const uint16_t *x, int branches, const uint32_t *const *qweights,
-                                      const uint16_t *const *scales, uint16_t *const *ys, const int *ns,
-                                      const uint16_t *residual, int lanes, int k, int epilogue, int *error_flag,
-                                      cudaStream_t stream);
-cudaError_t launch_linear_int4_stream_silu_pair(const uint16_t *x, const uint32_t *gate_q, const uint16_t *gate_s,
-                                                const uint32_t *up_q, const uint16_t *up_s, uint16_t *y, int lanes,
-                                                int n, int k, int *error_flag, cudaStream_t stream);
-// Device word the pipelined kernels set to 1 when a bounded wait expires (nullptr = not reported).
-void set_int4_error_flag(int *device_word);
-// 0 = register-prefetch kernel (default), 1 = bulk-copy pipelined kernel; NERVE_B200_INT4_STREAM=1 selects the latter.
-void set_int4_stream_enabled(int enabled);
-
 // ---- persistent decode stack (kernels_stack.cu) ----
 // One cooperative launch runs a whole stack of dense INT4 g128 Llama-style layers for a batch of at most 8 lanes:
 // every CTA (one per SM) streams its share of each weight matrix while grid-wide barriers separate the steps of a

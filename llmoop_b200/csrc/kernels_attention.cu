@@ -13,6 +13,8 @@
 // combine.  HBM traffic per launch = the KV bytes of the attended context
 // (2 * kv_heads * head_width * 2 B per token) per lane; the scratch partials
 // are (head_width + 2) f32 per (lane, q head, split).
+#include <atomic>
+
 #include "attention_body.cuh"
 #include "common.cuh"
 #include "kernels.cuh"
@@ -278,18 +280,18 @@ int argmax_static_max_lanes() { return STATIC_ARGMAX_MAX_LANES; }
 cudaError_t launch_argmax_static(const float *logits, uint32_t *records, int lanes, int vocab, cudaStream_t stream) {
     if (lanes <= 0) return cudaSuccess;
     if (lanes > STATIC_ARGMAX_MAX_LANES) return cudaErrorInvalidValue;
-    static void *device_address[STATIC_ARGMAX_MAX_DEVICES] = {};
+    static std::atomic<void *> device_address[STATIC_ARGMAX_MAX_DEVICES];  // zero-initialised; every thread that looks it up stores the same value
     int device = 0;
     cudaError_t status = cudaGetDevice(&device);
     if (status != cudaSuccess) return status;
     if (device < 0 || device >= STATIC_ARGMAX_MAX_DEVICES) return cudaErrorInvalidDevice;
-    if (device_address[device] == nullptr) {
-        void *address = nullptr;
+    void *address = device_address[device].load(std::memory_order_acquire);
+    if (address == nullptr) {
         status = cudaGetSymbolAddress(&address, static_argmax_scratch);
         if (status != cudaSuccess) return status;
-        device_address[device] = address;
+        device_address[device].store(address, std::memory_order_release);
     }
-    return launch_argmax(logits, records, lanes, vocab, device_address[device], stream);
+    return launch_argmax(logits, records, lanes, vocab, address, stream);
 }
 
 }  // namespace nerve

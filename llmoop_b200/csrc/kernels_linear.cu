@@ -380,27 +380,11 @@ static cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t
     return cudaLaunchKernelEx(&config, kernel, params);
 }
 
-static int *g_int4_error_flag = nullptr;
-static int g_int4_stream_enabled = -1;
-
-void set_int4_error_flag(int *device_word) { g_int4_error_flag = device_word; }
-void set_int4_stream_enabled(int enabled) { g_int4_stream_enabled = enabled ? 1 : 0; }
-
-static bool use_stream_kernel(int k) {
-    if (g_int4_stream_enabled < 0) {
-        const char *value = getenv("NERVE_B200_INT4_STREAM");
-        g_int4_stream_enabled = (value != nullptr && value[0] == '1') ? 1 : 0;
-    }
-    return g_int4_stream_enabled == 1 && linear_int4_stream_supported(k);
-}
-
 cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint32_t *const *qweights,
                                      const uint16_t *const *scales, uint16_t *const *ys, const int *ns,
                                      const uint16_t *residual, int lanes, int k, int epilogue, cudaStream_t stream) {
     if (lanes <= 0) return cudaSuccess;
     if (k % 128 != 0 || branches < 1 || branches > 3) return cudaErrorInvalidValue;
-    if (use_stream_kernel(k) && epilogue != EPILOGUE_F32_SCALED)
-        return launch_linear_int4_stream(x, branches, qweights, scales, ys, ns, residual, lanes, k, epilogue, g_int4_error_flag, stream);
     Int4Launch params = {};
     params.branches = branches;
     params.x = x;
@@ -434,8 +418,6 @@ cudaError_t launch_linear_int4_silu_pair(const uint16_t *x, const uint32_t *gate
                                          int k, cudaStream_t stream) {
     if (lanes <= 0) return cudaSuccess;
     if (k % 128 != 0) return cudaErrorInvalidValue;
-    if (use_stream_kernel(k))
-        return launch_linear_int4_stream_silu_pair(x, gate_q, gate_s, up_q, up_s, y, lanes, n, k, g_int4_error_flag, stream);
     Int4Launch params = {};
     params.branches = 2;
     params.x = x;

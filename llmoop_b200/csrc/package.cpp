@@ -93,6 +93,26 @@ const TensorInfo &HostPackage::tensor(const std::string &name) const {
     return found->second;
 }
 
+namespace {
+// Bytes per element of the safetensors dtypes a package can hold (0: unknown to this backend, checked where used).
+uint64_t dtype_bytes(const std::string &dtype) {
+    if (dtype == "BF16" || dtype == "F16" || dtype == "I16" || dtype == "U16") return 2;
+    if (dtype == "F32" || dtype == "I32" || dtype == "U32") return 4;
+    if (dtype == "F8_E4M3" || dtype == "F8_E5M2" || dtype == "I8" || dtype == "U8" || dtype == "BOOL") return 1;
+    if (dtype == "F64" || dtype == "I64" || dtype == "U64") return 8;
+    return 0;
+}
+}  // namespace
+
+// Fails unless `name` holds exactly `elements` values of `dtype`.
+void HostPackage::require_elements(const std::string &name, const std::string &dtype, uint64_t elements, const std::string &what) const {
+    const TensorInfo &info = tensor(name);
+    if (info.dtype != dtype) fail(what + " " + name + " must be " + dtype + " (it is " + info.dtype + ")");
+    if (info.byte_count() != elements * dtype_bytes(dtype))
+        fail(what + " " + name + ": " + std::to_string(info.byte_count()) + " bytes where the plan's dimensions need " +
+             std::to_string(elements * dtype_bytes(dtype)));
+}
+
 void HostPackage::load(const std::string &path, VerifyLevel verify) {
     std::string manifest_path = path;
     if (is_directory(path)) manifest_path = path + "/vulkan_resident_package.json";
@@ -122,8 +142,21 @@ void HostPackage::load(const std::string &path, VerifyLevel verify) {
         info.source_file = entry.at("source_file").as_string();
         info.begin = static_cast<uint64_t>(entry.at("data_offsets")[0].as_int());
         info.end = static_cast<uint64_t>(entry.at("data_offsets")[1].as_int());
+        if (info.end < info.begin) fail("tensor " + info.name + ": data_offsets end before they begin");
         if (entry["byte_count"].is_number() && static_cast<uint64_t>(entry["byte_count"].as_int()) != info.end - info.begin)
             fail("tensor " + info.name + ": byte_count disagrees with data_offsets");
+        // the kernels take their extents from the shapes: the bytes on disk must cover them exactly
+        // (the reference refuses such a tensor too: vulkan_distributed/planning.rs:582, "byte count does not match ... shape")
+        if (const uint64_t element = dtype_bytes(info.dtype)) {
+            uint64_t elements = 1;
+            for (int64_t dim : info.shape) {
+                if (dim < 0) fail("tensor " + info.name + ": negative dimension");
+                elements *= static_cast<uint64_t>(dim);
+            }
+            if (elements * element != info.end - info.begin)
+                fail("tensor " + info.name + ": byte count " + std::to_string(info.end - info.begin) + " does not match shape x " + info.dtype + " = " +
+                     std::to_string(elements * element));
+        }
         info.sha256 = entry["data_sha256"].is_string() ? entry["data_sha256"].as_string() : "";
         if (entry["layout"].is_string() && entry["layout"].as_string() != "row_major")
             fail("tensor " + info.name + ": unsupported layout " + entry["layout"].as_string());
@@ -217,13 +250,20 @@ WeightRef HostPackage::weight_ref(const Json &refs, const std::string &param) co
     out.k = info.logical_shape[info.logical_shape.size() - 1];
     if (info.dtype == "BF16") {
         out.storage = TensorStorage::BF16;
+        if (out.n <= 0 || out.k <= 0) fail("linear weight " + out.tensor + ": empty matrix");
+        require_elements(out.tensor, "BF16", static_cast<uint64_t>(out.n) * out.k, "linear weight");
     } else if (info.dtype == "I32" && info.quantized) {
         out.storage = TensorStorage::INT4_CT;
         out.scale = info.scales;
         out.group = info.group_size;
         const TensorInfo &scale = tensor(out.scale);
         if (scale.dtype != "BF16") fail("INT4 scales " + out.scale + " must be BF16");
+        if (out.n <= 0 || out.k <= 0 || out.group <= 0) fail("INT4 weight " + out.tensor + ": empty matrix or group");
         if (out.k % out.group != 0 || out.k % 8 != 0) fail("INT4 weight " + out.tensor + ": K is not a multiple of the group size");
+        if (info.byte_count() != static_cast<uint64_t>(out.n) * out.k / 2)
+            fail("INT4 weight " + out.tensor + ": " + std::to_string(info.byte_count()) + " packed bytes where its logical shape needs " +
+                 std::to_string(static_cast<uint64_t>(out.n) * out.k / 2));
+        require_elements(out.scale, "BF16", static_cast<uint64_t>(out.n) * (out.k / out.group), "INT4 scales");
     } else if (info.dtype == "F8_E4M3") {
         out.storage = TensorStorage::FP8_BLOCK;
         out.scale = out.tensor + "_scale_inv";
@@ -233,7 +273,15 @@ WeightRef HostPackage::weight_ref(const Json &refs, const std::string &param) co
         }
         if (tensor(out.scale).dtype != "BF16") fail("FP8 block scales " + out.scale + " must be BF16");
         out.group = 128;
+        if (out.n <= 0 || out.k <= 0) fail("FP8 weight " + out.tensor + ": empty matrix");
         if (out.k % 128 != 0) fail("FP8 weight " + out.tensor + ": K is not a multiple of 128");
+        // stacked expert tensors carry their expert count in front of [n][k]
+        uint64_t stack = 1;
+        for (size_t d = 0; d + 2 < info.logical_shape.size(); d++) stack *= static_cast<uint64_t>(info.logical_shape[d]);
+        if (info.byte_count() != stack * static_cast<uint64_t>(out.n) * out.k)
+            fail("FP8 weight " + out.tensor + ": " + std::to_string(info.byte_count()) + " bytes where its shape needs " +
+                 std::to_string(stack * static_cast<uint64_t>(out.n) * out.k));
+        require_elements(out.scale, "BF16", stack * static_cast<uint64_t>((out.n + 127) / 128) * (out.k / 128), "FP8 block scales");
     } else {
         fail("unsupported weight dtype " + info.dtype + " for " + out.tensor);
     }
@@ -282,6 +330,7 @@ ComponentPlan HostPackage::build_component(const Json &execution, const Json &co
             spec.norm_weights.push_back(refs[params.at(0)].at("tensor").as_string());
             spec.eps = shader_float(attrs.at("eps").as_double());
             spec.weight_offset = shader_float(attrs.at("weight_offset").as_double());
+            require_elements(spec.norm_weights.back(), "BF16", static_cast<uint64_t>(width_of(spec.inputs.at(0))), "norm weight");
             declare(0, width_of(spec.inputs.at(0)));
         } else if (op == "linear" || op == "parallel_linear_2way" || op == "parallel_linear_3way") {
             spec.kind = OpKind::Linear;
@@ -419,14 +468,14 @@ void HostPackage::build_plan() {
     plan_.embedding_scale = shader_float(graph.at("input_transducer")["attrs"]["scale"].is_number()
                                              ? graph.at("input_transducer")["attrs"]["scale"].as_double()
                                              : 1.0);
-    const TensorInfo &embedding = tensor(plan_.embedding_tensor);
-    if (embedding.dtype != "BF16") fail("embedding table must be BF16");
+    if (plan_.hidden <= 0 || plan_.vocab <= 0) fail("hidden_size and vocab_size must be positive");
+    require_elements(plan_.embedding_tensor, "BF16", static_cast<uint64_t>(plan_.vocab) * plan_.hidden, "embedding table");
 
     const Json &out_spec = manifest_.at("output_transducer").at("spec");
     plan_.output.norm_tensor = out_spec.at("norm_parameter_tensor").as_string();
     plan_.output.projection_tensor = out_spec.at("projection_parameter_tensor").as_string();
-    if (tensor(plan_.output.projection_tensor).dtype != "BF16")
-        fail("output projection " + plan_.output.projection_tensor + " must be BF16");
+    require_elements(plan_.output.projection_tensor, "BF16", static_cast<uint64_t>(plan_.vocab) * plan_.hidden, "output projection");
+    require_elements(plan_.output.norm_tensor, "BF16", static_cast<uint64_t>(plan_.hidden), "output norm");
     for (const Json &component : graph.at("output_transducer").at("components").items()) {
         const std::string type = component.at("type").as_string();
         if (type == "rms_norm") {
@@ -480,6 +529,8 @@ void HostPackage::build_plan() {
         const Json &out = decoder.at("output_transducer");
         plan_.draft_output.norm_tensor = out.at("norm_parameter_tensor").as_string();
         plan_.draft_output.projection_tensor = out.at("projection_parameter_tensor").as_string();
+        require_elements(plan_.draft_output.projection_tensor, "BF16", static_cast<uint64_t>(plan_.vocab) * plan_.hidden, "draft output projection");
+        require_elements(plan_.draft_output.norm_tensor, "BF16", static_cast<uint64_t>(plan_.hidden), "draft output norm");
         const Json *out_component = find_by(components, "component_id", out.at("component_id").as_string());
         if (!out_component) fail("draft output transducer component is missing");
         for (const Json &node : out_component->at("circuit").at("nodes").items()) {

@@ -164,6 +164,7 @@ private:
     void build_plan();
     ComponentPlan build_component(const Json &execution, const Json &component);
     WeightRef weight_ref(const Json &refs, const std::string &param) const;
+    void require_elements(const std::string &name, const std::string &dtype, uint64_t elements, const std::string &what) const;
 
     std::string dir_;
     Json manifest_;

@@ -79,7 +79,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_set_profiling", "nerve_b200_engine_inject_barrier_timeouts", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_stop_after_current", "nerve_b200_engine_stream_snapshot_of", "nerve_b200_engine_snapshot", "nerve_b200_engine_init_tp", "nerve_b200_engine_tp_exchange_handle", "nerve_b200_engine_tp_connect", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
     "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
-    "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair", "nerve_b200_set_int4_kernel",
+    "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair",
     "nerve_b200_op_linear_bf16", "nerve_b200_op_rms_norm", "nerve_b200_op_linear_fp8",
     "nerve_b200_op_greedy", "nerve_b200_op_greedy_scratch_bytes", "nerve_b200_op_greedy_static", "nerve_b200_op_sample_top_k_top_p", "nerve_b200_op_sample_scratch_bytes", "nerve_b200_verify_prefix",
     "nerve_b200_stream_control_bytes", "nerve_b200_state_page_table_bytes",

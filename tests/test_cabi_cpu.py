@@ -48,6 +48,46 @@ def test_integrity_failures_name_the_artifact(tmp_path):
         nb.validate_package(broken, 1)
 
 
+def test_a_tensor_index_that_promises_more_than_the_bytes_hold_is_rejected(tmp_path):
+    """The kernels take their extents from the index's shapes, so a shape the stored bytes do not cover must stop
+    the mount on the host (the reference: vulkan_distributed/planning.rs:582)."""
+    import json
+
+    import llmoop_b200 as nb
+
+    def mutated(edit):
+        package = tmp_path / "pkg"
+        if package.exists():
+            shutil.rmtree(package)
+        shutil.copytree(GOLDEN / "tiny_int4_mtp_v16", package)
+        index = json.loads((package / "tensors.json").read_text())
+        edit(index["tensors"])
+        (package / "tensors.json").write_text(json.dumps(index))
+        return package
+
+    def double_rows(name_filter):
+        def edit(tensors):
+            name = next(n for n, t in sorted(tensors.items()) if name_filter(n, t))
+            for key in ("shape", "logical_shape"):
+                if key in tensors[name]:
+                    tensors[name][key][0] *= 2
+        return edit
+
+    quantized = lambda n, t: "quantization" in t
+    scales = lambda n, t: n.endswith("weight_scale")
+    norms = lambda n, t: "norm" in n and len(t["shape"]) == 1
+    for edit in (double_rows(quantized), double_rows(scales), double_rows(norms)):
+        with pytest.raises(nb.NerveError, match="does not match shape|bytes where"):
+            nb.validate_package(mutated(edit), 0)
+
+    def end_before_begin(tensors):
+        name = sorted(tensors)[0]
+        tensors[name]["data_offsets"] = [8, 4]
+        tensors[name].pop("byte_count", None)
+    with pytest.raises(nb.NerveError, match="end before they begin"):
+        nb.validate_package(mutated(end_before_begin), 0)
+
+
 def test_unknown_schema_and_ops_are_rejected(tmp_path):
     import json
 

@@ -43,20 +43,9 @@ def _ulp_report(got_bits, want_bits):
     return exact, worst
 
 
-@pytest.fixture
-def int4_kernel(request):
-    """Runs the test under one of the two INT4 kernels and restores the default afterwards."""
-    import llmoop_b200 as nb
-
-    nb.library().nerve_b200_set_int4_kernel(request.param)
-    yield request.param
-    nb.library().nerve_b200_set_int4_kernel(0)
-
-
-@pytest.mark.parametrize("int4_kernel", [0, 1], indirect=True)
 @pytest.mark.parametrize("lanes", [1, 4, 8, 11])
 @pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 4096), (4096, 14336), (272, 256)])
-def test_linear_int4_matches_oracle(lanes, n, k, int4_kernel):
+def test_linear_int4_matches_oracle(lanes, n, k):
     import torch
 
     import llmoop_b200 as nb
@@ -89,10 +78,9 @@ def test_linear_int4_matches_oracle(lanes, n, k, int4_kernel):
     assert exact > 0.97, (exact, worst)
 
 
-@pytest.mark.parametrize("int4_kernel", [0, 1], indirect=True)
 @pytest.mark.parametrize("lanes", [1, 4, 7])
 @pytest.mark.parametrize("n,k", [(14336, 4096), (528, 2048), (96, 384)])
-def test_linear_int4_silu_pair_matches_oracle(lanes, n, k, int4_kernel):
+def test_linear_int4_silu_pair_matches_oracle(lanes, n, k):
     """gate/up projections + rounded SiLU multiply in one launch against the oracle's
     three separate steps (linear, linear, silu_multiply)."""
     import torch
