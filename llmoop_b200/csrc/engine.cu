@@ -719,6 +719,33 @@ void Engine::release_pages(Stream &s) {
     s.block_table_dirty = true;
 }
 
+// Output projection + sampler of `lanes` normalised rows (output transducer: tied_output_projection_batch_bf16.comp.template:52-142,
+// then the sampler dispatch).  A tensor-parallel group with the peer exchange connected and only greedy streams
+// splits the vocabulary: every rank projects its own slice of the (replicated) table, takes the slice's arg-max and
+// the ranks vote (launch_tensor_parallel_argmax) - V / T rows of the table per rank instead of V.
+void Engine::project_and_sample(const uint16_t *normalized, const std::string &projection_tensor, float scale, int lanes, const int32_t *slots,
+                                const uint32_t *ticks, const char *what) {
+    const ModelPlan &plan = model_->plan();
+    const int vocab = static_cast<int>(plan.vocab), hidden = static_cast<int>(plan.hidden);
+    const uint16_t *table = static_cast<const uint16_t *>(model_->tensor(projection_tensor));
+    const int size = model_->options().tp_size, rank = model_->options().tp_rank;
+    if (size > 1 && tp_connected_ && vocabulary_parallel_ && stochastic_streams_ == 0 && !full_logits_ && lanes <= STACK_TP_VOTE_LANES) {
+        const int per_rank = (vocab + size - 1) / size, first = rank * per_rank;
+        const int count = std::max(0, std::min(vocab, first + per_rank) - first);
+        check(launch_linear_bf16(normalized, table + static_cast<size_t>(first) * hidden, logits_.ptr, nullptr, lanes, count, hidden, EPILOGUE_F32_SCALED, scale,
+                                 cuda_stream_),
+              "output projection (vocabulary slice)");
+        check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, count, argmax_scratch_.ptr, cuda_stream_), what);
+        counters_.kernel_launches++;
+        check(launch_tensor_parallel_argmax(static_cast<const uint32_t *>(records_.ptr), static_cast<uint32_t>(first), static_cast<uint32_t *>(records_.ptr), lanes,
+                                            static_cast<const StackTp *>(tp_description_.ptr), static_cast<int *>(kernel_error_.ptr), cuda_stream_),
+              "arg-max vote");
+        return;
+    }
+    check(launch_linear_bf16(normalized, table, logits_.ptr, nullptr, lanes, vocab, hidden, EPILOGUE_F32_SCALED, scale, cuda_stream_), "output projection");
+    sample_lanes(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, slots, ticks, what);
+}
+
 void Engine::sample_lanes(const float *logits, uint32_t *records, int lanes, const int32_t *slots, const uint32_t *ticks, const char *what) {
     const int vocab = static_cast<int>(model_->plan().vocab);
     if (stochastic_streams_ == 0) {
@@ -1324,13 +1351,8 @@ void Engine::target_forward(int lanes, bool want_logits) {
                           plan.output.weight_offset, cuda_stream_),
           "output norm");
     if (want_logits) {
-        check(launch_linear_bf16(static_cast<const uint16_t *>(normalized_.ptr),
-                                 static_cast<const uint16_t *>(model_->tensor(plan.output.projection_tensor)), logits_.ptr, nullptr, lanes,
-                                 static_cast<int>(plan.vocab), static_cast<int>(plan.hidden), EPILOGUE_F32_SCALED, plan.output.logits_scale,
-                                 cuda_stream_),
-              "output projection");
-        sample_lanes(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, current_lanes_.slot,
-                     current_lanes_.position, "sampler");
+        project_and_sample(static_cast<const uint16_t *>(normalized_.ptr), plan.output.projection_tensor, plan.output.logits_scale, lanes,
+                           current_lanes_.slot, current_lanes_.position, "sampler");
     }
 }
 
@@ -1359,13 +1381,8 @@ void Engine::draft_forward(int lanes, const uint16_t *hidden_in, bool want_logit
                           static_cast<uint16_t *>(draft_normalized_.ptr), lanes, static_cast<int>(plan.hidden), plan.draft_output.eps,
                           plan.draft_output.weight_offset, cuda_stream_),
           "draft output norm");
-    check(launch_linear_bf16(static_cast<const uint16_t *>(draft_normalized_.ptr),
-                             static_cast<const uint16_t *>(model_->tensor(plan.draft_output.projection_tensor)), logits_.ptr, nullptr, lanes,
-                             static_cast<int>(plan.vocab), static_cast<int>(plan.hidden), EPILOGUE_F32_SCALED, plan.draft_output.logits_scale,
-                             cuda_stream_),
-          "draft output projection");
-    sample_lanes(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, current_lanes_.slot,
-                 current_lanes_.position, "draft sampler");
+    project_and_sample(static_cast<const uint16_t *>(draft_normalized_.ptr), plan.draft_output.projection_tensor, plan.draft_output.logits_scale, lanes,
+                       current_lanes_.slot, current_lanes_.position, "draft sampler");
 }
 
 // ---------------------------------------------------------------------------- prefill (temporal_prompt.rs:298-478)
@@ -1396,13 +1413,8 @@ void Engine::run_prefill_chunk(Stream &s, const uint32_t *tokens, int count, boo
                    "commit target hidden");
     }
     if (sample_last) {
-        check(launch_linear_bf16(static_cast<const uint16_t *>(normalized_.ptr) + static_cast<size_t>(count - 1) * plan.hidden,
-                                 static_cast<const uint16_t *>(model_->tensor(plan.output.projection_tensor)), logits_.ptr, nullptr, 1,
-                                 static_cast<int>(plan.vocab), static_cast<int>(plan.hidden), EPILOGUE_F32_SCALED, plan.output.logits_scale,
-                                 cuda_stream_),
-              "prefill output projection");
-        sample_lanes(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), 1, current_lanes_.slot + (count - 1),
-                     current_lanes_.position + (count - 1), "prefill sampler");
+        project_and_sample(static_cast<const uint16_t *>(normalized_.ptr) + static_cast<size_t>(count - 1) * plan.hidden, plan.output.projection_tensor,
+                           plan.output.logits_scale, 1, current_lanes_.slot + (count - 1), current_lanes_.position + (count - 1), "prefill sampler");
         cuda_check(cudaMemcpyAsync(host_records_, records_.ptr, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, cuda_stream_), "record readback");
         synchronize("prefill synchronize");
         counters_.d2h_bytes += 16;
@@ -1788,7 +1800,14 @@ void Engine::debug_target_logits(int64_t id, const std::vector<uint32_t> &tokens
     upload_lanes(positions, slots);
     upload_tokens(tokens.data(), lanes);
     current_width_ = lanes;
-    target_forward(lanes, true);
+    full_logits_ = true;  // the whole vocabulary on every rank, whatever the sampling path would project
+    try {
+        target_forward(lanes, true);
+    } catch (...) {
+        full_logits_ = false;
+        throw;
+    }
+    full_logits_ = false;
     synchronize("debug synchronize");
     if (logits_out)
         cuda_check(cudaMemcpy(logits_out, logits_.ptr, static_cast<size_t>(lanes) * plan.vocab * sizeof(float), cudaMemcpyDeviceToHost), "logits readback");

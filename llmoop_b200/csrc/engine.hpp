@@ -331,6 +331,8 @@ private:
     DeviceBuffer stack_q_, stack_attention_out_, stack_activation_, stack_barrier_, stack_timing_;
     bool stack_enabled_ = true;
     bool run_stack(const StackPlan &stack, int lanes, void *hidden);
+    void project_and_sample(const uint16_t *normalized, const std::string &projection_tensor, float scale, int lanes, const int32_t *slots,
+                            const uint32_t *ticks, const char *what);
     void backup_pending();
     void check_kernel_status(const uint32_t *status_word);  // throws (after restoring the pending hidden states) when a kernel reported an error
     DeviceBuffer cycle_state_;              // device-side per-batch cycle arrays (see engine.cu)
@@ -342,6 +344,8 @@ private:
     int split_tokens_ = 256, max_splits_ = 1;
     int prefill_chunk_ = 64;
     bool use_graphs_ = true, log_cycles_ = false;
+    bool vocabulary_parallel_ = true;       // tensor-parallel greedy sampling splits the vocabulary over the ranks
+    bool full_logits_ = false;              // debug_target_logits wants every rank to project the whole vocabulary
     bool failed_ = false;                   // a tensor-parallel rank whose kernel gave up is out of step with its peers for good
     int inject_barrier_timeouts_ = 0;       // test hook: this many decode stack launches wait for arrivals that cannot come
     std::vector<CycleRecord> cycle_log_;

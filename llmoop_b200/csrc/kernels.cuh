@@ -183,7 +183,10 @@ struct StackTp {
     float *exchange[STACK_TP_MAX_RANKS] = {};          // every rank's inbox as seen from this GPU (own entry: local memory)
     unsigned long long *counter[STACK_TP_MAX_RANKS] = {};  // every rank's 16 control words
 };
-constexpr size_t STACK_TP_CONTROL_BYTES = 16 * sizeof(unsigned long long);
+constexpr int STACK_TP_WORD_VOTES = 3;                   // control word: arg-max votes taken so far (tensor_parallel_argmax)
+constexpr int STACK_TP_VOTE_LANES = 64;                  // lanes one vote can carry
+// Behind the 16 control words: the vote area [2 parities][STACK_TP_MAX_RANKS][STACK_TP_VOTE_LANES][2] 8-byte words.
+constexpr size_t STACK_TP_CONTROL_BYTES = 16 * sizeof(unsigned long long) + 2 * STACK_TP_MAX_RANKS * STACK_TP_VOTE_LANES * 2 * sizeof(unsigned long long);
 inline size_t stack_tp_exchange_floats(int hidden) { return static_cast<size_t>(2) * STACK_TP_MAX_RANKS * 8 * hidden * 2; }
 
 // One source matrix of a stream copy.  rope_head_width > 0 orders the rows of every head so that MMA rows
@@ -228,6 +231,14 @@ cudaError_t launch_accept(const uint32_t *verify_tokens, const uint32_t *target_
                           const int32_t *stop_counts, int max_stop, int streams, int drafts, uint32_t *out,
                           const uint16_t *normalized, uint16_t *pending, const int32_t *slots, int hidden,
                           cudaStream_t stream);
+
+// Vocabulary-parallel greedy sampling under tensor parallelism: every rank has taken the arg-max of its own slice of
+// the vocabulary (records_local: {token within the slice, logit bits, ..} per lane, as launch_argmax writes them);
+// the ranks push (logit, global token), tagged with the vote number, into each other's vote areas over NVLink, wait
+// (bounded) for all of them and all pick the same winner - highest logit, ties to the lowest token id.  One block.
+// The vote number lives on the device (control word STACK_TP_WORD_VOTES), so the launch can be replayed from a graph.
+cudaError_t launch_tensor_parallel_argmax(const uint32_t *records_local, uint32_t first_token, uint32_t *records, int lanes, const StackTp *tp_device,
+                                          int *error_flag, cudaStream_t stream);
 
 // Greedy arg-max (ties -> lowest id); record = {token, logit bits, 0, 0} per lane.
 // `scratch` holds argmax_scratch_bytes(lanes) bytes of per-chunk partial winners.

@@ -120,4 +120,72 @@ cudaError_t launch_accept(const uint32_t *verify_tokens, const uint32_t *target_
     return cudaGetLastError();
 }
 
+// ---- vocabulary-parallel arg-max ------------------------------------------------------------------------------
+// See launch_tensor_parallel_argmax in kernels.cuh.  Thread l serves lane l.  A vote word is (vote number << 32 |
+// payload): the logit bits in the first word, the global token id in the second; a reader accepts a pair once both
+// carry the number of the vote in progress.  Parities alternate per vote: a rank can only be one vote ahead of a
+// peer (it needs the peer's word of vote v before it can finish v), so the slot of vote v + 2 is free by then.
+__global__ void tensor_parallel_argmax_kernel(const uint32_t *__restrict__ records_local, uint32_t first_token, uint32_t *__restrict__ records,
+                                              int lanes, const StackTp *__restrict__ tp_pointer, int *error_flag) {
+    const StackTp &tp = *tp_pointer;
+    unsigned long long *control = tp.counter[tp.rank];
+    const uint32_t vote = static_cast<uint32_t>(control[STACK_TP_WORD_VOTES]) + 1u;  // every thread reads it before thread 0 moves it on (below)
+    const int lane = threadIdx.x;
+    const size_t parity_offset = static_cast<size_t>(vote & 1u) * STACK_TP_MAX_RANKS * STACK_TP_VOTE_LANES * 2;
+    float best = 0.0f;
+    uint32_t token = 0xffffffffu;
+    if (lane < lanes) {
+        const uint32_t local_token = records_local[lane * 4], logit_bits = records_local[lane * 4 + 1];
+        const unsigned long long tag = static_cast<unsigned long long>(vote) << 32;
+        for (int r = 0; r < tp.size; r++) {
+            if (r == tp.rank) continue;
+            unsigned long long *theirs = tp.counter[r] + 16 + parity_offset + (static_cast<size_t>(tp.rank) * STACK_TP_VOTE_LANES + lane) * 2;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(theirs), "l"(tag | logit_bits) : "memory");
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(theirs + 1), "l"(tag | (local_token + first_token)) : "memory");
+        }
+        unsigned int spins = 0;
+        bool gave_up = false;
+        for (int r = 0; r < tp.size; r++) {
+            float candidate = __uint_as_float(logit_bits);
+            uint32_t candidate_token = local_token + first_token;
+            if (r != tp.rank) {
+                const unsigned long long *mine = control + 16 + parity_offset + (static_cast<size_t>(r) * STACK_TP_VOTE_LANES + lane) * 2;
+                unsigned long long first = 0, second = 0;
+                while (!gave_up) {
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(first) : "l"(mine) : "memory");
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(second) : "l"(mine + 1) : "memory");
+                    if (static_cast<uint32_t>(first >> 32) == vote && static_cast<uint32_t>(second >> 32) == vote) break;
+                    if (++spins > STACK_TP_SPIN_LIMIT) {
+                        atomicExch(error_flag, 2);
+                        gave_up = true;
+                    } else if ((spins & 255u) == 0 && *reinterpret_cast<volatile int *>(error_flag) != 0) {
+                        gave_up = true;
+                    }
+                }
+                candidate = __uint_as_float(static_cast<uint32_t>(first));
+                candidate_token = static_cast<uint32_t>(second);
+            }
+            if (token == 0xffffffffu || candidate > best || (candidate == best && candidate_token < token)) {
+                best = candidate;
+                token = candidate_token;
+            }
+        }
+        uint32_t *record = records + static_cast<size_t>(lane) * 4;
+        record[0] = token;
+        record[1] = __float_as_uint(best);
+        record[2] = 0u;
+        record[3] = 0u;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) control[STACK_TP_WORD_VOTES] = vote;
+}
+
+cudaError_t launch_tensor_parallel_argmax(const uint32_t *records_local, uint32_t first_token, uint32_t *records, int lanes, const StackTp *tp_device,
+                                          int *error_flag, cudaStream_t stream) {
+    if (lanes <= 0) return cudaSuccess;
+    if (lanes > STACK_TP_VOTE_LANES || tp_device == nullptr) return cudaErrorInvalidValue;
+    tensor_parallel_argmax_kernel<<<1, STACK_TP_VOTE_LANES, 0, stream>>>(records_local, first_token, records, lanes, tp_device, error_flag);
+    return cudaGetLastError();
+}
+
 }  // namespace nerve
