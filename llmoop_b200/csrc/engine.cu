@@ -974,8 +974,10 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                 break;
             }
             if (is_int4_single(op)) {
-                // gate/up + SiLU*up in one launch
-                if (index + 2 < plan.ops.size() && is_int4_single(plan.ops[index + 1]) && plan.ops[index + 2].kind == OpKind::SiluMultiply &&
+                // gate/up + SiLU*up in one launch (batches below the GEMM threshold; wide batches run the three operators
+                // as the package lists them, the two projections as tensor-core GEMMs)
+                if (!linear_int4_gemm_supported(lanes, static_cast<int>(op.weights[0].n), static_cast<int>(op.weights[0].k)) &&
+                    index + 2 < plan.ops.size() && is_int4_single(plan.ops[index + 1]) && plan.ops[index + 2].kind == OpKind::SiluMultiply &&
                     plan.ops[index + 1].inputs[0] == op.inputs[0] && plan.ops[index + 2].inputs[0] == op.outputs[0] &&
                     plan.ops[index + 2].inputs[1] == plan.ops[index + 1].outputs[0] && op.weights[0].n == plan.ops[index + 1].weights[0].n &&
                     consumers(op.outputs[0], index + 3) == 0 && consumers(plan.ops[index + 1].outputs[0], index + 3) == 0) {

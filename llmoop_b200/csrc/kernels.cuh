@@ -106,6 +106,14 @@ cudaError_t launch_linear_int4_silu_pair(const uint16_t *x, const uint32_t *gate
                                          const uint32_t *up_q, const uint16_t *up_s, uint16_t *y, int lanes, int n,
                                          int k, cudaStream_t stream);
 
+// ---- INT4 g128 GEMM on the tcgen05 tensor cores for 64 lanes and more (kernels_int4_gemm.cu) ----
+// One CTA per 128 rows x 64 lanes; the launchers above use it for such batches.  y and the epilogues as for
+// launch_linear_int4 (EPILOGUE_F32_SCALED writes f32 * scale).  error_flag (optional device word) is set to 3 if a
+// bounded wait for the tensor core expires.
+bool linear_int4_gemm_supported(int lanes, int n, int k);
+cudaError_t launch_linear_int4_gemm(const uint16_t *x, const uint32_t *qweight, const uint16_t *scales, void *y, const uint16_t *residual, int lanes,
+                                    int n, int k, int epilogue, float scale, int *error_flag, cudaStream_t stream);
+
 // ---- persistent decode stack (kernels_stack.cu) ----
 // One cooperative launch runs a whole stack of dense INT4 g128 Llama-style layers for a batch of at most 8 lanes:
 // every CTA (one per SM) streams its share of each weight matrix while grid-wide barriers separate the steps of a

@@ -385,6 +385,15 @@ cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint
                                      const uint16_t *residual, int lanes, int k, int epilogue, cudaStream_t stream) {
     if (lanes <= 0) return cudaSuccess;
     if (k % 128 != 0 || branches < 1 || branches > 3) return cudaErrorInvalidValue;
+    if (linear_int4_gemm_supported(lanes, ns[0], k)) {
+        // wide batches (prefill chunks, many-stream verify): one tcgen05 GEMM per matrix, the weights read once per 64 lanes
+        for (int b = 0; b < branches; b++) {
+            cudaError_t status = launch_linear_int4_gemm(x, qweights[b], scales[b], ys[b], branches == 1 ? residual : nullptr, lanes, ns[b], k, epilogue, 1.0f,
+                                                         nullptr, stream);
+            if (status != cudaSuccess) return status;
+        }
+        return cudaSuccess;
+    }
     Int4Launch params = {};
     params.branches = branches;
     params.x = x;

@@ -43,8 +43,12 @@ def _ulp_report(got_bits, want_bits):
     return exact, worst
 
 
-@pytest.mark.parametrize("lanes", [1, 4, 8, 11])
-@pytest.mark.parametrize("n,k", [(4096, 4096), (1024, 4096), (4096, 14336), (272, 256)])
+GEMM_CASES = [  # 64 lanes and more run the tcgen05 GEMM: 8B and 70B layer shapes, a ragged row block, ragged lane tiles
+    (64, 4096, 4096), (160, 4096, 4096), (512, 6144, 4096), (200, 4096, 14336), (160, 8192, 8192), (96, 272, 256), (64, 1024, 28672),
+]
+
+
+@pytest.mark.parametrize("lanes,n,k", [(lanes, n, k) for lanes in (1, 4, 8, 11) for n, k in ((4096, 4096), (1024, 4096), (4096, 14336), (272, 256))] + GEMM_CASES)
 def test_linear_int4_matches_oracle(lanes, n, k):
     import torch
 
