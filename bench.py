@@ -147,12 +147,26 @@ def run_event(engine, stream_id, prompt, max_tokens, teacher=None):
     engine.reset_stream_transient_state(stream_id)
     engine.set_teacher_tokens(stream_id, teacher or [])
     engine.enqueue_input_event(stream_id, prompt, max_tokens)
-    first, _ = engine.run(1)
+    first, first_report = engine.run(1)
+    run_event.prefill_ms = first_report.prefill_ns * 1e-6  # host clock around the prompt's chunk(s), synchronised at the sampled token
     start = time.perf_counter()
     outputs, report = engine.run_until_idle()
     wall = time.perf_counter() - start
     tokens = [token for _, token, _, _ in first] + [token for _, token, _, _ in outputs]
     return tokens, report, len(outputs) / wall
+
+
+def prefill_line(spec, milliseconds):
+    """The 512-token prompt as one chunk: INT4 GEMMs on the tcgen05 tensor cores (target layers and the MTP layer's
+    warm-up), tiled attention, one sampled token; flops = 2 x tokens x dense-layer weights."""
+    path = ROOT / "MEASURED_PEAKS.json"
+    sustained = float(json.loads(path.read_text()).get("bf16_tflops_sustained", 1400.0)) if path.exists() else 1400.0
+    q_width, kv_width = spec.q_heads * spec.head_dim, spec.kv_heads * spec.head_dim
+    per_layer = spec.hidden * (q_width + 2 * kv_width) + q_width * spec.hidden + 3 * spec.hidden * spec.ffn
+    flops = 2.0 * PROMPT_TOKENS * per_layer * (spec.layers + 1)
+    tflops = flops / (milliseconds * 1e-3) / 1e12 if milliseconds > 0 else 0.0
+    return {"tokens": PROMPT_TOKENS, "ms": milliseconds, "tokens_per_s": PROMPT_TOKENS / (milliseconds * 1e-3) if milliseconds > 0 else 0.0,
+            "tflops": tflops, "frac_of_measured_sustained_bf16": tflops / sustained, "peak_tflops": sustained}
 
 
 def timed_cycles(engine, stream_id, prompt, budget_tokens, warmup, steps, teacher, barrier):
@@ -432,6 +446,7 @@ def main():
                 "d2h_bytes_per_step": natural_report.d2h_bytes / max(1, natural_report.cycle_count),
                 "event": f"prompt {PROMPT_TOKENS} + {EVENT_TOKENS} tokens via enqueue_input_event / run / run_until_idle; host wall clock around the "
                          "run_until_idle call that decodes everything after the first cycle"},
+        "prefill": prefill_line(spec, run_event.prefill_ms),
         "gpu_launches": natural_timed.kernel_launches,
         "clocks": clocks,
         "package": {"verify_step_weight_bytes": info["verify_step_weight_bytes"], "draft_step_weight_bytes": info["draft_step_weight_bytes"],

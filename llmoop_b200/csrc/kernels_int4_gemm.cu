@@ -127,9 +127,23 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
     for (int i = 0; i < 32; i++) acc[i] = 0.0f;
     bool alive = true;
 
-    auto fetch = [&](int group, int buffer) {
-        const uint4 first = __ldg(weight_source + group * 4), second = __ldg(weight_source + group * 4 + 1);
-        const uint32_t words[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
+    // The packed nibbles and the activations of a group are requested one group ahead (into registers) and turned
+    // into the shared-memory tiles when their turn comes, so the memory latency of group g + 1 hides behind the
+    // MMAs of group g and the scaling of group g - 1.
+    uint4 raw_weights[2], raw_x[GEMM_LANES * 16 / GEMM_THREADS];
+    auto request = [&](int group) {
+        raw_weights[0] = __ldg(weight_source + group * 4);
+        raw_weights[1] = __ldg(weight_source + group * 4 + 1);
+#pragma unroll
+        for (int i = 0; i < GEMM_LANES * 16 / GEMM_THREADS; i++) {
+            const int piece = threadIdx.x + i * GEMM_THREADS, n = piece >> 4, block = piece & 15;
+            raw_x[i] = make_uint4(0, 0, 0, 0);
+            if (m0 + n < a.lanes) raw_x[i] = __ldg(reinterpret_cast<const uint4 *>(a.x + static_cast<size_t>(m0 + n) * a.k + group * 128) + block);
+        }
+    };
+    auto store_tiles = [&](int buffer) {
+        const uint32_t words[8] = {raw_weights[0].x, raw_weights[0].y, raw_weights[0].z, raw_weights[0].w,
+                                   raw_weights[1].x, raw_weights[1].y, raw_weights[1].z, raw_weights[1].w};
         uint8_t *destination = tile_a[buffer] + weight_offset;
 #pragma unroll
         for (int w = 0; w < 8; w++)
@@ -138,8 +152,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
 #pragma unroll
         for (int i = 0; i < GEMM_LANES * 16 / GEMM_THREADS; i++) {
             const int piece = threadIdx.x + i * GEMM_THREADS, n = piece >> 4, block = piece & 15;
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (m0 + n < a.lanes) raw = __ldg(reinterpret_cast<const uint4 *>(a.x + static_cast<size_t>(m0 + n) * a.k + group * 128) + block);
+            const uint4 raw = raw_x[i];
             // (x0,x1)(x2,x3)(x4,x5)(x6,x7) -> (x0,x4)(x1,x5)(x2,x6)(x3,x7): the order the nibble pairs come out in
             const uint4 ordered = make_uint4(__byte_perm(raw.x, raw.z, 0x5410), __byte_perm(raw.x, raw.z, 0x7632), __byte_perm(raw.y, raw.w, 0x5410),
                                              __byte_perm(raw.y, raw.w, 0x7632));
@@ -167,9 +180,11 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     };
 
+    if (groups > 0) request(0);
     for (int group = 0; group < groups && alive; group++) {
         const int buffer = group & 1;
-        fetch(group, buffer);  // the MMAs that read this buffer two groups ago were waited for in the last drain
+        store_tiles(buffer);  // the MMAs that read this buffer two groups ago were waited for in the last drain
+        if (group + 1 < groups) request(group + 1);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tiles were written with ordinary stores; the tensor core reads them
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
