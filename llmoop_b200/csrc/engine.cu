@@ -191,6 +191,16 @@ std::shared_ptr<MountedModel> MountedModel::mount(const std::string &path, const
     model->block_table_ = device_alloc(sizeof(int32_t) * options.max_streams * model->pages_per_stream_);
     model->build_rope_tables();
     cuda_check(cudaDeviceGetAttribute(&model->sm_count_, cudaDevAttrMultiProcessorCount, options.device), "cudaDeviceGetAttribute");
+    // the output projection tables, once more in the order the streaming kernel reads them
+    for (const std::string &name : {plan.output.projection_tensor, plan.has_draft ? plan.draft_output.projection_tensor : std::string()}) {
+        if (name.empty() || model->projection_tables_.count(name) || !output_projection_supported(1, static_cast<int>(plan.hidden))) continue;
+        DeviceBuffer table = device_alloc(projection_table_bytes(static_cast<int>(plan.vocab), static_cast<int>(plan.hidden)), false);
+        cuda_check(launch_projection_table(static_cast<const uint16_t *>(model->tensor(name)), table.ptr, static_cast<int>(plan.vocab),
+                                           static_cast<int>(plan.hidden), nullptr),
+                   "output projection table copy");
+        model->projection_tables_.emplace(name, table);
+    }
+    cuda_check(cudaDeviceSynchronize(), "output projection table copies");
     {
         int target_kv_layers = 0;
         for (const ComponentPlan &layer : plan.layers) target_kv_layers += layer.has_kv ? 1 : 0;
@@ -204,6 +214,7 @@ MountedModel::~MountedModel() {
     for (auto &entry : tensors_) cudaFree(entry.second.ptr);
     for (auto &pool : kv_pools_) cudaFree(pool.ptr);
     for (auto &entry : rope_tables_) cudaFree(entry.second.ptr);
+    for (auto &entry : projection_tables_) cudaFree(entry.second.ptr);
     for (StackPlan *stack : {&target_stack_, &draft_stack_}) {
         for (DeviceBuffer &buffer : stack->storage) cudaFree(buffer.ptr);
         cudaFree(stack->device_layers.ptr);
@@ -728,13 +739,24 @@ void Engine::project_and_sample(const uint16_t *normalized, const std::string &p
     const ModelPlan &plan = model_->plan();
     const int vocab = static_cast<int>(plan.vocab), hidden = static_cast<int>(plan.hidden);
     const uint16_t *table = static_cast<const uint16_t *>(model_->tensor(projection_tensor));
+    const void *streamed = lanes <= 8 && streaming_projection_ ? model_->projection_table(projection_tensor) : nullptr;
     const int size = model_->options().tp_size, rank = model_->options().tp_rank;
+    // rows [first, first + count) into logits [lanes][count]
+    auto project = [&](int first, int count, const char *label) {
+        if (streamed != nullptr && first % 16 == 0) {
+            check(launch_output_projection(normalized, streamed, first, static_cast<float *>(logits_.ptr), lanes, count, hidden, scale, model_->sm_count(),
+                                           static_cast<int *>(kernel_error_.ptr), cuda_stream_),
+                  label);
+        } else {
+            check(launch_linear_bf16(normalized, table + static_cast<size_t>(first) * hidden, logits_.ptr, nullptr, lanes, count, hidden, EPILOGUE_F32_SCALED, scale,
+                                     cuda_stream_),
+                  label);
+        }
+    };
     if (size > 1 && tp_connected_ && vocabulary_parallel_ && stochastic_streams_ == 0 && !full_logits_ && lanes <= STACK_TP_VOTE_LANES) {
-        const int per_rank = (vocab + size - 1) / size, first = rank * per_rank;
+        const int per_rank = ((vocab + size - 1) / size + 15) / 16 * 16, first = std::min(vocab, rank * per_rank);
         const int count = std::max(0, std::min(vocab, first + per_rank) - first);
-        check(launch_linear_bf16(normalized, table + static_cast<size_t>(first) * hidden, logits_.ptr, nullptr, lanes, count, hidden, EPILOGUE_F32_SCALED, scale,
-                                 cuda_stream_),
-              "output projection (vocabulary slice)");
+        project(first, count, "output projection (vocabulary slice)");
         check(launch_argmax(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, count, argmax_scratch_.ptr, cuda_stream_), what);
         counters_.kernel_launches++;
         check(launch_tensor_parallel_argmax(static_cast<const uint32_t *>(records_.ptr), static_cast<uint32_t>(first), static_cast<uint32_t *>(records_.ptr), lanes,
@@ -742,7 +764,7 @@ void Engine::project_and_sample(const uint16_t *normalized, const std::string &p
               "arg-max vote");
         return;
     }
-    check(launch_linear_bf16(normalized, table, logits_.ptr, nullptr, lanes, vocab, hidden, EPILOGUE_F32_SCALED, scale, cuda_stream_), "output projection");
+    project(0, vocab, "output projection");
     sample_lanes(static_cast<const float *>(logits_.ptr), static_cast<uint32_t *>(records_.ptr), lanes, slots, ticks, what);
 }
 

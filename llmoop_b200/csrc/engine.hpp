@@ -95,6 +95,12 @@ public:
     uint64_t kv_bytes_per_token() const { return kv_bytes_per_token_; }
     const StackPlan &target_stack() const { return target_stack_; }
     const StackPlan &draft_stack() const { return draft_stack_; }
+    // The output projection tables in the streaming kernel's order (by tensor name), or nullptr.
+    const void *projection_table(const std::string &name) const {
+        auto found = projection_tables_.find(name);
+        return found == projection_tables_.end() ? nullptr : found->second.ptr;
+    }
+    int sm_count() const { return sm_count_; }
 
 private:
     MountedModel() = default;
@@ -116,6 +122,7 @@ private:
     uint32_t rope_positions_ = 0;
     int sm_count_ = 0;  // CTAs of the persistent kernels (one per SM of the mount device)
     StackPlan target_stack_, draft_stack_;
+    std::map<std::string, DeviceBuffer> projection_tables_;
 };
 
 struct SamplerConfig {
@@ -344,6 +351,7 @@ private:
     int split_tokens_ = 256, max_splits_ = 1;
     int prefill_chunk_ = 64;
     bool use_graphs_ = true, log_cycles_ = false;
+    bool streaming_projection_ = true;      // output projections of at most 8 lanes run the streaming kernel on the mount-time table copy
     bool vocabulary_parallel_ = true;       // tensor-parallel greedy sampling splits the vocabulary over the ranks
     bool full_logits_ = false;              // debug_target_logits wants every rank to project the whole vocabulary
     bool failed_ = false;                   // a tensor-parallel rank whose kernel gave up is out of step with its peers for good
