@@ -185,7 +185,7 @@ __device__ __forceinline__ void team_barrier(int barrier_id) { asm volatile("bar
 // All CTAs of the (cooperative, co-resident) grid meet here; only the consumer warps take part.  `target` counts
 // the arrivals expected so far.  A wait that does not complete within the spin limit sets the error flag and lets
 // the CTA go on (its results are then garbage, the host sees the flag); once the flag is up nobody waits any more.
-__device__ __forceinline__ void grid_barrier(unsigned int *counter, unsigned int &target, int *error_flag, unsigned int spin_limit) {
+__device__ __noinline__ void grid_barrier(unsigned int *counter, unsigned int &target, int *error_flag, unsigned int spin_limit) {
     consumer_sync();
     if (threadIdx.x == 0) {
         target += gridDim.x;
@@ -564,54 +564,77 @@ __host__ __device__ constexpr size_t attention_team_bytes() {
     return (4 * 16 * ((HD < 64 ? HD : 64) + 4) + 2 * 4 * 16 + 4) * sizeof(float);  // partial outputs [warp][row][HALF + 4], maxima and sums [warp][row], one flag
 }
 
+struct AttentionJob {  // what every attention item of a launch shares
+    const uint16_t *q;
+    float *scratch;
+    uint16_t *out_fragments;
+    unsigned int *arrivals;
+    int lanes, lanes_per_stream, q_heads, kv_heads, max_splits, group_slots, staged;
+    float scale;
+};
+// The scratch of a layer's attention step: every (lane, q head, split) partial is HD floats of unnormalised output in
+// `values` [lane][q head][split][HD] (16-byte aligned rows) and (maximum, sum) in `stats` [lane][q head][split][2]
+// behind all the values - together the (HD + 2) floats per partial the scratch is sized for.
+__device__ __forceinline__ float *attention_stats(float *scratch, int lanes, int q_heads, int max_splits, int head_width) {
+    return scratch + static_cast<size_t>(lanes) * q_heads * max_splits * head_width;
+}
+
 // Log-sum-exp merge of the split partials of one (lane, q head) row by one warp: lane s of the warp weighs split s
 // (s + 32, ...), every lane owns HD / 32 consecutive output dims, and the weighted rows are summed in split order,
 // the loads of eight splits in flight at a time.  The result goes out as fp16 in fragment order.
 template <int HD>
-__device__ __forceinline__ void attention_merge_row(const float *__restrict__ scratch, uint16_t *__restrict__ out_fragments, uint32_t capacity,
-                                                    uint32_t tick, int query_lane, int head, int q_heads, int max_splits, int staged) {
-    constexpr int VEC = HD / 32, STRIDE = HD + 2;  // a partial is HD + 2 floats: 8-byte pieces stay aligned
-    static_assert(VEC == 1 || VEC % 2 == 0, "a lane owns whole 8-byte pieces (or one float)");
+__device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32_t capacity, uint32_t tick, int query_lane, int head) {
+    constexpr int VEC = HD / 32;
+    static_assert(VEC == 1 || VEC == 2 || VEC == 4, "a lane owns one, two or four output dims");
     const int lane_id = threadIdx.x & 31;
     const uint32_t tokens = tick + 1u < capacity ? tick + 1u : capacity;
+    const int max_splits = job.max_splits, staged = job.staged;
     int splits = static_cast<int>((tokens + 63u) / 64u);
     if (splits > max_splits) splits = max_splits;
-    const float *base = scratch + (static_cast<size_t>(query_lane) * q_heads + head) * max_splits * STRIDE;
-    float maximum = -3.4028234663852886e38f;
-    for (int s = lane_id; s < splits; s += 32) maximum = fmaxf(maximum, __ldcg(base + static_cast<size_t>(s) * STRIDE + HD));
-    maximum = warp_max(maximum);
-    float denominator = 0.0f, acc[VEC];
+    const size_t row = (static_cast<size_t>(query_lane) * job.q_heads + head) * max_splits;
+    const float *__restrict__ values = job.scratch + row * HD;
+    const float *__restrict__ stats = attention_stats(job.scratch, job.lanes, job.q_heads, max_splits, HD) + row * 2;
+    uint16_t *__restrict__ out_fragments = job.out_fragments;
+    const float *mine = values + lane_id * VEC;
+    float acc[VEC], denominator = 0.0f, maximum = -3.4028234663852886e38f;
 #pragma unroll
     for (int v = 0; v < VEC; v++) acc[v] = 0.0f;
+    auto fetch = [&](int s, float (&part)[VEC]) {
+        if (VEC == 4) {
+            const float4 raw = s < splits ? __ldcg(reinterpret_cast<const float4 *>(mine + static_cast<size_t>(s) * HD)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            part[0] = raw.x, part[VEC > 1 ? 1 : 0] = raw.y, part[VEC > 2 ? 2 : 0] = raw.z, part[VEC > 3 ? 3 : 0] = raw.w;
+        } else if (VEC == 2) {
+            const float2 raw = s < splits ? __ldcg(reinterpret_cast<const float2 *>(mine + static_cast<size_t>(s) * HD)) : make_float2(0.0f, 0.0f);
+            part[0] = raw.x, part[VEC > 1 ? 1 : 0] = raw.y;
+        } else {
+            part[0] = s < splits ? __ldcg(mine + static_cast<size_t>(s) * HD) : 0.0f;
+        }
+    };
+    // the first eight rows are requested together with the statistics
+    float part[8][VEC];
+#pragma unroll
+    for (int u = 0; u < 8; u++) fetch(u, part[u]);
+    for (int s = lane_id; s < splits; s += 32) maximum = fmaxf(maximum, __ldcg(stats + 2 * s));
+    maximum = warp_max(maximum);
+#pragma unroll 1
     for (int s0 = 0; s0 < splits; s0 += 32) {
         float weight = 0.0f;
         if (s0 + lane_id < splits) {
-            const float2 stats = __ldcg(reinterpret_cast<const float2 *>(base + static_cast<size_t>(s0 + lane_id) * STRIDE + HD));
-            weight = expf(stats.x - maximum);
-            denominator += stats.y * weight;
+            const float2 pair = __ldcg(reinterpret_cast<const float2 *>(stats) + s0 + lane_id);
+            weight = expf(pair.x - maximum);
+            denominator += pair.y * weight;
         }
-        const int end = splits - s0 < 32 ? splits - s0 : 32;
-        for (int s = 0; s < end; s += 8) {
-            float part[8][VEC];
+#pragma unroll 1
+        for (int s = s0; s < splits && s < s0 + 32; s += 8) {
+            if (s != 0) {
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const float *row = base + static_cast<size_t>(s0 + s + u) * STRIDE + lane_id * VEC;
-                if (VEC == 1) {
-                    part[u][0] = s + u < end ? __ldcg(row) : 0.0f;
-                } else {
-#pragma unroll
-                    for (int v = 0; v < VEC; v += 2) {
-                        const float2 pair = s + u < end ? __ldcg(reinterpret_cast<const float2 *>(row + v)) : make_float2(0.0f, 0.0f);
-                        part[u][v] = pair.x;
-                        part[u][v + 1 < VEC ? v + 1 : v] = pair.y;
-                    }
-                }
+                for (int u = 0; u < 8; u++) fetch(s + u, part[u]);
             }
 #pragma unroll
             for (int u = 0; u < 8; u++) {
-                const float w = __shfl_sync(0xffffffffu, weight, (s + u) & 31);
+                const float w = __shfl_sync(0xffffffffu, weight, (s + u) & 31);  // 0 beyond the last split: the row was not read
 #pragma unroll
-                for (int v = 0; v < VEC; v++) acc[v] += part[u][v] * (s + u < end ? w : 0.0f);
+                for (int v = 0; v < VEC; v++) acc[v] += part[u][v] * (s + u < splits ? w : 0.0f);
             }
         }
     }
@@ -636,7 +659,7 @@ __device__ __forceinline__ uint2 load8_now(const void *address) {
 }
 
 template <int HD>
-__device__ __forceinline__ size_t attention_row_base(const KvLayer &kv, int slot, uint32_t ring_base, int token) {
+__device__ __noinline__ size_t attention_row_base(const KvLayer &kv, int slot, uint32_t ring_base, int token) {
     uint32_t ring = ring_base + static_cast<uint32_t>(token);
     if (ring >= kv.capacity) ring -= kv.capacity;
     const int page = static_cast<int>(ring / kv.page_tokens), within = static_cast<int>(ring % kv.page_tokens);
@@ -649,6 +672,7 @@ constexpr int ATTENTION_MERGE_LIST = 63;
 // of its first work item (the block table is shared by all layers, so the rows of a (split, lane group) are the
 // same in every layer's pool).
 struct AttentionCache {
+    AttentionJob job;
     uint32_t tick[8];
     int32_t slot[8];
     int32_t item[4];          // the work item whose rows `row_base` holds, or -1
@@ -656,16 +680,26 @@ struct AttentionCache {
     int32_t merge_count;      // (kv head, lane group) pairs whose last split this CTA's teams completed in this layer ...
     int32_t merge_list[ATTENTION_MERGE_LIST];  // ... and which: kv_head * group_slots + group_slot
     uint32_t row_base[4][64]; // offset (in rows of HD elements) of token t's K row of kv head 0 in a layer's pool
+    StackLayer layer[2];      // the current layer's description (layer & 1) and the next one's, copied ahead of their use
 };
 
 template <int HD, int GROUP, int QL>
-__device__ __noinline__ void attention_team_item(const uint16_t *__restrict__ q, const KvLayer &kv, AttentionCache &cache, int item,
-                                                    int lanes, int lanes_per_stream, int q_heads, float scale, int max_splits,
-                                                    float *__restrict__ scratch, uint16_t *__restrict__ out_fragments,
-                                                    unsigned int *__restrict__ arrivals, int group_slots, int kv_head, int split,
-                                                    int group_slot, float *team_smem, int team, int team_warp, int barrier_id, int staged,
-                                                    unsigned long long *stamps) {
+__device__ __noinline__ void attention_team_item(AttentionCache &cache, const KvLayer &kv_shared, int item, uint8_t *scratch_area,
+                                                    unsigned long long *stamps, bool dry) {
     constexpr int Q = QL * GROUP;
+    // the launch's and the layer's descriptions by value: behind a reference every field would be read again after
+    // each of the ordered loads below
+    const KvLayer kv = kv_shared;
+    const AttentionJob job = cache.job;
+    const uint16_t *__restrict__ q = job.q;
+    float *__restrict__ scratch = job.scratch;
+    const int lanes = job.lanes, lanes_per_stream = job.lanes_per_stream, q_heads = job.q_heads, max_splits = job.max_splits;
+    const int group_slots = job.group_slots;
+    const float scale = job.scale;
+    const int team = static_cast<int>(threadIdx.x >> 7), team_warp = static_cast<int>(threadIdx.x >> 5) & 3, barrier_id = 2 + team;
+    float *team_smem = reinterpret_cast<float *>(scratch_area + static_cast<size_t>(team) * attention_team_bytes<HD>());
+    const int kv_head = item % job.kv_heads, split = (item / job.kv_heads) % max_splits, group_slot = (item / job.kv_heads) / max_splits;
+    unsigned int *__restrict__ arrivals = job.arrivals;
     auto mark = [&](int index) {
         if (stamps != nullptr) {
             unsigned long long now;
@@ -723,15 +757,27 @@ __device__ __noinline__ void attention_team_item(const uint16_t *__restrict__ q,
         return base + (value ? half_page : 0) + static_cast<size_t>(kv_head) * kv.page_tokens * HD;
     };
 
-    // ---- S = Q K^T for 16 tokens
-    uint4 qf[2][QW];
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        const int row = g + 8 * r;
-        const bool valid = tick_row[r] != 0xffffffffu;
-        const uint16_t *source = q + (static_cast<size_t>(lane0 + row / GROUP) * q_heads + kv_head * GROUP + row % GROUP) * HD + j * (HD / 4);
-#pragma unroll
-        for (int w = 0; w < QW; w++) qf[r][w] = valid ? load16_now(reinterpret_cast<const uint4 *>(source) + w) : make_uint4(0, 0, 0, 0);
+    // ---- S = Q K^T for 16 tokens.  The team's Q query rows go to shared memory with asynchronous copies (they
+    // would otherwise hold 32 registers per thread while the K and V rows are in flight); a row is kept as HD / 32
+    // pieces of 64 bytes, thread column j reading 16 bytes of each - K rows are read from memory the same way, so
+    // the head dimension is permuted identically on both sides of the product.
+    constexpr uint32_t Q_PITCH = HD * 2 + 64;  // bytes; 16-byte reads of a quarter warp fall into distinct banks
+    const uint32_t q_shared = static_cast<uint32_t>(__cvta_generic_to_shared(partial_out));  // free until the first output pass
+    {
+        const int team_thread = team_warp * 32 + lane;
+        for (int piece = team_thread; piece < 16 * QW * 4; piece += 128) {
+            const int row = piece / (QW * 4), part = piece % (QW * 4);
+            const int query_lane = lane0 + row / GROUP;
+            const bool valid = row < Q && query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream;
+            const uint32_t destination = q_shared + static_cast<uint32_t>(row) * Q_PITCH + static_cast<uint32_t>(part) * 16u;
+            if (valid) {
+                const uint16_t *source = q + (static_cast<size_t>(query_lane) * q_heads + kv_head * GROUP + row % GROUP) * HD + part * 8;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(destination), "l"(source) : "memory");
+            } else {
+                asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(destination), "r"(0u) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     }
     // K rows of tokens g and g + 8, V rows of tokens 2j, 2j+1, 2j+8, 2j+9 of this warp: all requested before the
     // arithmetic (the V rows of the first output pass now, those of the second when the q registers are free)
@@ -740,9 +786,9 @@ __device__ __noinline__ void attention_team_item(const uint16_t *__restrict__ q,
     for (int nt = 0; nt < 2; nt++) {
         const int token = token0 + nt * 8 + g;
         if (token < count) {
-            const uint16_t *krow = kv.pool + row_offset(token, false) + j * (HD / 4);
+            const uint16_t *krow = kv.pool + row_offset(token, false) + j * 8;
 #pragma unroll
-            for (int w = 0; w < QW; w++) kf[nt][w] = load16_now(reinterpret_cast<const uint4 *>(krow) + w);
+            for (int w = 0; w < QW; w++) kf[nt][w] = load16_now(krow + w * 32);
         } else {
 #pragma unroll
             for (int w = 0; w < QW; w++) kf[nt][w] = make_uint4(0, 0, 0, 0);
@@ -778,14 +824,19 @@ __device__ __noinline__ void attention_team_item(const uint16_t *__restrict__ q,
         }
     };
     load_values(0);
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    team_barrier(barrier_id);  // the query rows are in shared memory
     float s[2][4];
 #pragma unroll
-    for (int nt = 0; nt < 2; nt++) {
-        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+    for (int nt = 0; nt < 2; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
 #pragma unroll
-        for (int w = 0; w < QW; w++) {
-            mma_bf16_16816(s[nt], qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, kf[nt][w].x, kf[nt][w].y);
-            mma_bf16_16816(s[nt], qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, kf[nt][w].z, kf[nt][w].w);
+    for (int w = 0; w < QW; w++) {
+        const uint32_t at = q_shared + static_cast<uint32_t>(g) * Q_PITCH + static_cast<uint32_t>(w) * 64u + static_cast<uint32_t>(j) * 16u;
+        const uint4 q0 = shared_load16<0>(at), q1 = shared_load16<8 * Q_PITCH>(at);
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) {
+            mma_bf16_16816(s[nt], q0.x, q1.x, q0.y, q1.y, kf[nt][w].x, kf[nt][w].y);
+            mma_bf16_16816(s[nt], q0.z, q1.z, q0.w, q1.w, kf[nt][w].z, kf[nt][w].w);
         }
     }
     if (HD / HALF > 1) load_values(HD / HALF - 1);
@@ -854,33 +905,51 @@ __device__ __noinline__ void attention_team_item(const uint16_t *__restrict__ q,
             mma_bf16_16816(o[i], ph[0], ph[1], ph[2], ph[3], b0, b1);
             mma_bf16_16816(o[i], pl[0], pl[1], pl[2], pl[3], b0, b1);
         }
+        mark(pass == 0 ? 30 : 16);
         // accumulator column 2j (+1) of output tile i is head dim DPT * (2j (+1)) + i of the pass
 #pragma unroll
         for (int r = 0; r < 2; r++)
 #pragma unroll
-            for (int i = 0; i < DPT; i++) {
-                mine[(g + 8 * r) * PITCH + DPT * (2 * j) + i] = o[i][2 * r];
-                mine[(g + 8 * r) * PITCH + DPT * (2 * j + 1) + i] = o[i][2 * r + 1];
-            }
+            for (int half = 0; half < 2; half++)
+#pragma unroll
+                for (int i = 0; i < DPT; i += 4)
+                    *reinterpret_cast<float4 *>(mine + (g + 8 * r) * PITCH + DPT * (2 * j + half) + i) =
+                        make_float4(o[i][2 * r + half], o[i + 1][2 * r + half], o[i + 2][2 * r + half], o[i + 3][2 * r + half]);
         team_barrier(barrier_id);
-        // the four partial outputs add up; warp w writes dims [w * HALF / 4, (w + 1) * HALF / 4) of the pass for every row
-        for (int index = lane; index < 16 * (HALF / 4); index += 32) {
-            const int row = index / (HALF / 4), d = team_warp * (HALF / 4) + index % (HALF / 4);
+        if (pass == 0) mark(31);
+        // the four partial outputs add up; warp w writes dims [w * HALF / 4, (w + 1) * HALF / 4) of the pass for every
+        // row, four dims per thread and round
+        constexpr int QUADS = HALF / 16;
+#pragma unroll
+        for (int round = 0; round < (16 * QUADS + 31) / 32; round++) {
+            const int task = round * 32 + lane, row = task / QUADS, d = team_warp * (HALF / 4) + (task % QUADS) * 4;
             const int query_lane = lane0 + row / GROUP;  // rows beyond Q are padding
-            const bool valid = row < Q && query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream;
-            if (!valid) continue;
-            const float sum = partial_out[row * PITCH + d] + partial_out[(16 + row) * PITCH + d] + partial_out[(32 + row) * PITCH + d] +
-                              partial_out[(48 + row) * PITCH + d];
-            float *out = scratch + ((static_cast<size_t>(query_lane) * q_heads + kv_head * GROUP + row % GROUP) * max_splits + split) * (HD + 2);
-            out[pass * HALF + d] = sum;
-            if (pass == 0 && d == 0) {
-                out[HD] = fmaxf(fmaxf(fmaxf(team_max[row], team_max[16 + row]), fmaxf(team_max[32 + row], team_max[48 + row])), -3.4028234663852886e38f);
-                out[HD + 1] = team_sum[row] + team_sum[16 + row] + team_sum[32 + row] + team_sum[48 + row];
+            if (row < Q && query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream) {
+                const float *in = partial_out + row * PITCH + d;
+                const float4 p0 = *reinterpret_cast<const float4 *>(in), p1 = *reinterpret_cast<const float4 *>(in + 16 * PITCH),
+                             p2 = *reinterpret_cast<const float4 *>(in + 32 * PITCH), p3 = *reinterpret_cast<const float4 *>(in + 48 * PITCH);
+                const size_t partial = (static_cast<size_t>(query_lane) * q_heads + kv_head * GROUP + row % GROUP) * max_splits + split;
+                *reinterpret_cast<float4 *>(scratch + partial * HD + pass * HALF + d) =
+                    make_float4(p0.x + p1.x + p2.x + p3.x, p0.y + p1.y + p2.y + p3.y, p0.z + p1.z + p2.z + p3.z, p0.w + p1.w + p2.w + p3.w);
             }
         }
+        if (pass == 0 && team_warp == 0 && lane < Q) {
+            const int row = lane, query_lane = lane0 + row / GROUP;
+            if (query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream) {
+                const size_t partial = (static_cast<size_t>(query_lane) * q_heads + kv_head * GROUP + row % GROUP) * max_splits + split;
+                *reinterpret_cast<float2 *>(attention_stats(scratch, lanes, q_heads, max_splits, HD) + partial * 2) = make_float2(
+                    fmaxf(fmaxf(fmaxf(team_max[row], team_max[16 + row]), fmaxf(team_max[32 + row], team_max[48 + row])), -3.4028234663852886e38f),
+                    team_sum[row] + team_sum[16 + row] + team_sum[32 + row] + team_sum[48 + row]);
+            }
+        }
+        if (pass == 0) mark(19);
         if (pass + 1 < HD / HALF) team_barrier(barrier_id);  // the partial outputs are rewritten by the next pass
     }
     // ---- the team that completes the kv head's last split merges the splits of its queries
+    if (dry) {
+        team_barrier(barrier_id);
+        return;
+    }
     mark(23);
     __threadfence();
     team_barrier(barrier_id);
@@ -906,8 +975,7 @@ __device__ __noinline__ void attention_team_item(const uint16_t *__restrict__ q,
             for (int row = team_warp; row < Q; row += 4) {
                 const int query_lane = lane0 + row / GROUP;
                 if (query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream)
-                    attention_merge_row<HD>(scratch, out_fragments, capacity, cache.tick[query_lane], query_lane, kv_head * GROUP + row % GROUP, q_heads,
-                                            max_splits, staged);
+                    attention_merge_row<HD>(cache.job, capacity, cache.tick[query_lane], query_lane, kv_head * GROUP + row % GROUP);
             }
         }
     }
@@ -1135,7 +1203,6 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     unsigned int target = a.buffers.barrier_handicap, barriers_passed = 0;
     const unsigned int barrier_spin_limit = a.buffers.barrier_handicap != 0 ? (1u << 12) : BARRIER_SPIN_LIMIT;
     unsigned int *counter = a.buffers.barrier;
-    unsigned int *arrivals = a.buffers.barrier + ARRIVAL_WORDS_OFFSET;
     int *error_flag = a.buffers.error_flag;
     uint32_t tag = 0;  // exchanges done so far, earlier launches included
     unsigned long long *inbox_mine = nullptr;
@@ -1195,6 +1262,10 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
         const int m = index / (HD >> 1);
         rope_rows[index] = __ldg(shape.rope_table + static_cast<size_t>(a.lanes_meta.position[m] % shape.rope_positions) * (HD >> 1) + (index - m * (HD >> 1)));
     }
+    constexpr int LAYER_WORDS = static_cast<int>(sizeof(StackLayer) / sizeof(uint32_t));
+    static_assert(sizeof(StackLayer) % sizeof(uint32_t) == 0, "layer descriptions are copied word by word");
+    if (threadIdx.x >= 32 && threadIdx.x < 32 + LAYER_WORDS)
+        reinterpret_cast<uint32_t *>(&attention_cache->layer[0])[threadIdx.x - 32] = reinterpret_cast<const uint32_t *>(a.layers)[threadIdx.x - 32];
     if (threadIdx.x < 8) {
         attention_cache->tick[threadIdx.x] = static_cast<int>(threadIdx.x) < lanes ? a.lanes_meta.position[threadIdx.x] : 0u;
         attention_cache->slot[threadIdx.x] = static_cast<int>(threadIdx.x) < lanes ? a.lanes_meta.slot[threadIdx.x] : -1;
@@ -1230,7 +1301,23 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                 }
             }
         }
-        if (threadIdx.x == 0) attention_cache->merge_count = 0;
+        if (threadIdx.x == 0) {
+            attention_cache->merge_count = 0;
+            AttentionJob job;
+            job.q = a.buffers.q;
+            job.scratch = a.buffers.attention_scratch;
+            job.out_fragments = a.buffers.attention_out;
+            job.arrivals = a.buffers.barrier + ARRIVAL_WORDS_OFFSET;
+            job.lanes = lanes;
+            job.lanes_per_stream = a.lanes_per_stream;
+            job.q_heads = shape.q_heads;
+            job.kv_heads = shape.kv_heads;
+            job.max_splits = a.max_splits;
+            job.group_slots = group_slots;
+            job.staged = staged;
+            job.scale = shape.attention_scale;
+            attention_cache->job = job;
+        }
         if (team_thread == 0) {
             attention_cache->item[team] = cached_item;
             attention_cache->rows[team] = cached_rows;
@@ -1244,8 +1331,12 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     const int grid = static_cast<int>(gridDim.x);
 
     for (int layer = 0; layer < a.layer_count; layer++) {
-        const StackLayer *spec = a.layers + layer;
+        const StackLayer *spec = &attention_cache->layer[layer & 1];
         const KvLayer kv = spec->kv;
+        // the next layer's description: into the other copy (last read before the previous layer's final barrier)
+        if (threadIdx.x >= 32 && threadIdx.x < 32 + LAYER_WORDS && layer + 1 < a.layer_count)
+            reinterpret_cast<uint32_t *>(&attention_cache->layer[(layer + 1) & 1])[threadIdx.x - 32] =
+                reinterpret_cast<const uint32_t *>(a.layers + layer + 1)[threadIdx.x - 32];
         {
             // the K and V rows this CTA's teams will read in this layer's attention step: on their way into L2 now
             const int team = warp >> 2, team_thread = threadIdx.x & 127;
@@ -1315,7 +1406,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                 consumer_sync();
                 const float *sums = reduce + static_cast<size_t>(reduce_parity * CONSUMER_WARPS * 128);
                 reduce_parity ^= 1;
-#pragma unroll
+#pragma unroll 1
                 for (int round = 0; round < 4; round++) {
                     const int slot = epilogue_slot + 4 * round;
                     if (slot >= present) break;  // uniform over the warp
@@ -1401,7 +1492,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                             }
                             // linear + residual_add (add_bf16.comp.template:17-24): bf16(bf16(product) + residual), in place
                             a.buffers.hidden[static_cast<size_t>(epilogue_m) * shape.hidden + column] =
-                                static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(total) + bf16_bits_to_f32(done.payload[round])));
+                                static_cast<uint16_t>(f32_to_bf16_bits(round_bf16(total) + bf16_bits_to_f32(round == 0 ? done.payload[0] : (round == 1 ? done.payload[1] : (round == 2 ? done.payload[2] : done.payload[3])))));
                         }
                     }
                 }
@@ -1420,15 +1511,12 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                 const int group_slots = streams * ((a.lanes_per_stream + QL - 1) / QL);
                 const int total = shape.kv_heads * a.max_splits * group_slots;
                 const int team = warp >> 2;
-                float *team_smem = reinterpret_cast<float *>(smem_raw + static_cast<size_t>(team) * attention_team_bytes<HD>());
-                for (int item = blockIdx.x + gridDim.x * team; item < total; item += gridDim.x * 4) {
-                    const int kv_head = item % shape.kv_heads, rest = item / shape.kv_heads;
-                    attention_team_item<HD, GROUP, QL>(a.buffers.q, kv, *attention_cache, item, lanes, a.lanes_per_stream, shape.q_heads,
-                                                       shape.attention_scale, a.max_splits, a.buffers.attention_scratch,
-                                                       a.buffers.attention_out, arrivals, group_slots, kv_head, rest % a.max_splits,
-                                                       rest / a.max_splits, team_smem, team, warp & 3, 2 + team, staged,
-                                                       (a.buffers.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) ? a.buffers.timing + layer * 32 : nullptr);
-                }
+                unsigned long long *item_stamps = (a.buffers.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) ? a.buffers.timing + layer * 32 : nullptr;
+                if (a.debug_flags & 16)
+                    for (int item = blockIdx.x + gridDim.x * team; item < total; item += gridDim.x * 4)
+                        attention_team_item<HD, GROUP, QL>(*attention_cache, spec->kv, item, smem_raw, nullptr, true);
+                for (int item = blockIdx.x + gridDim.x * team; item < total; item += gridDim.x * 4)
+                    attention_team_item<HD, GROUP, QL>(*attention_cache, spec->kv, item, smem_raw, item_stamps, false);
                 consumer_sync();
                 stamp(layer, 17);
                 {
@@ -1444,8 +1532,8 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                             const int group_index = group_slot % groups_per_stream;
                             const int query_lane = (group_slot / groups_per_stream) * a.lanes_per_stream + group_index * QL + row / GROUP;
                             if (query_lane < lanes && group_index * QL + row / GROUP < a.lanes_per_stream && attention_cache->slot[query_lane] >= 0)
-                                attention_merge_row<HD>(a.buffers.attention_scratch, a.buffers.attention_out, kv.capacity, attention_cache->tick[query_lane],
-                                                        query_lane, kv_head * GROUP + row % GROUP, shape.q_heads, a.max_splits, staged);
+                                attention_merge_row<HD>(attention_cache->job, kv.capacity, attention_cache->tick[query_lane], query_lane,
+                                                        kv_head * GROUP + row % GROUP);
                         }
                     }
                 }
