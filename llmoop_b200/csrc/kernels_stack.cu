@@ -476,6 +476,15 @@ __device__ __forceinline__ size_t fragment_element(int column, int m, int staged
 // rms_norm_bf16.comp.template:49-72 of every staged lane, straight into fragment order (each CTA repeats it:
 // 8 KB per lane from L2).  A thread owns chunk t (and t + 512 when CHUNKS = 2) of each lane, four lanes at a time:
 // one pass over registers for the sums of squares, one block-wide exchange, then normalise, round and permute.
+// Two f32 values rounded to bf16 (nearest even, as the shaders' f32_to_bf16 for every finite value) and carried on
+// as the fp16 pair the tensor cores read: exact, a bf16 of this range fits fp16.
+__device__ __forceinline__ uint32_t bf16_rounded_half_pair(float lo, float hi) {
+    uint32_t packed, halves;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(halves) : "f"(bf16_hi(packed)), "f"(bf16_lo(packed)));
+    return halves;
+}
+
 template <int CHUNKS>  // chunks per thread and lane: width <= CHUNKS * 8 * CONSUMER_THREADS
 __device__ __noinline__ void stage_normalised(uint4 *fragments, float *partial, const uint16_t *x, const uint16_t *weight, int width,
                                                  int staged, float eps, float offset) {
@@ -487,6 +496,7 @@ __device__ __noinline__ void stage_normalised(uint4 *fragments, float *partial, 
         const int chunk = threadIdx.x + c * CONSUMER_THREADS;
         scale_words[c] = chunk < per_lane ? __ldg(reinterpret_cast<const uint4 *>(weight) + chunk) : make_uint4(0, 0, 0, 0);
     }
+#pragma unroll 1
     for (int m0 = 0; m0 < staged; m0 += 4) {
         uint4 raw[4][CHUNKS];
 #pragma unroll
@@ -494,14 +504,17 @@ __device__ __noinline__ void stage_normalised(uint4 *fragments, float *partial, 
 #pragma unroll
             for (int c = 0; c < CHUNKS; c++) {
                 const int chunk = threadIdx.x + c * CONSUMER_THREADS;
-                raw[mm][c] = (m0 + mm < staged && chunk < per_lane) ? __ldcg(source + static_cast<size_t>(m0 + mm) * per_lane + chunk)
-                                                                    : make_uint4(0, 0, 0, 0);
+                // lanes beyond the batch read the last lane again (their results are not stored)
+                const int m = m0 + mm < staged ? m0 + mm : staged - 1;
+                raw[mm][c] = __ldcg(source + static_cast<size_t>(m) * per_lane + (chunk < per_lane ? chunk : 0));
             }
+        float sums[4];
 #pragma unroll
         for (int mm = 0; mm < 4; mm++) {
             float sum = 0.0f;
 #pragma unroll
             for (int c = 0; c < CHUNKS; c++) {
+                if (CHUNKS > 1 && threadIdx.x + c * CONSUMER_THREADS >= per_lane) continue;
                 const uint32_t words[4] = {raw[mm][c].x, raw[mm][c].y, raw[mm][c].z, raw[mm][c].w};
 #pragma unroll
                 for (int w = 0; w < 4; w++) {
@@ -510,8 +523,20 @@ __device__ __noinline__ void stage_normalised(uint4 *fragments, float *partial, 
                     sum = fmaf(hi, hi, sum);
                 }
             }
-            sum = warp_sum(sum);
-            if (lane == 0) partial[mm * CONSUMER_WARPS + warp] = sum;
+            sums[mm] = (CHUNKS > 1 || static_cast<int>(threadIdx.x) < per_lane) ? sum : 0.0f;
+        }
+        // the four sums cross the warp together: after two exchanges a thread holds the sum of lane 2 * bit0 + bit1
+        {
+            const bool odd = lane & 1;
+            const float keep0 = odd ? sums[2] : sums[0], keep1 = odd ? sums[3] : sums[1];
+            const float send0 = odd ? sums[0] : sums[2], send1 = odd ? sums[1] : sums[3];
+            const float a0 = keep0 + __shfl_xor_sync(0xffffffffu, send0, 1), a1 = keep1 + __shfl_xor_sync(0xffffffffu, send1, 1);
+            const bool upper = lane & 2;
+            float sum = (upper ? a1 : a0) + __shfl_xor_sync(0xffffffffu, upper ? a0 : a1, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+            if (lane < 4) partial[(2 * (lane & 1) + (lane >> 1)) * CONSUMER_WARPS + warp] = sum;
         }
         consumer_sync();
         // every warp adds up the 16 partials of the four lanes: lanes 8k .. 8k+7 of the warp take lane m0 + k
@@ -533,11 +558,12 @@ __device__ __noinline__ void stage_normalised(uint4 *fragments, float *partial, 
                     float v[8];
 #pragma unroll
                     for (int w = 0; w < 4; w++) {
-                        v[2 * w] = round_bf16(bf16_lo(in[w]) * inv_rms * (bf16_lo(sc[w]) + offset));
-                        v[2 * w + 1] = round_bf16(bf16_hi(in[w]) * inv_rms * (bf16_hi(sc[w]) + offset));
+                        v[2 * w] = bf16_lo(in[w]) * inv_rms * (bf16_lo(sc[w]) + offset);
+                        v[2 * w + 1] = bf16_hi(in[w]) * inv_rms * (bf16_hi(sc[w]) + offset);
                     }
                     fragments[fragment_index(chunk, m0 + mm, staged)] =
-                        make_uint4(half_pair(v[0], v[4]), half_pair(v[1], v[5]), half_pair(v[2], v[6]), half_pair(v[3], v[7]));
+                        make_uint4(bf16_rounded_half_pair(v[0], v[4]), bf16_rounded_half_pair(v[1], v[5]), bf16_rounded_half_pair(v[2], v[6]),
+                                   bf16_rounded_half_pair(v[3], v[7]));
                 }
             }
         }
@@ -592,51 +618,57 @@ __device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32
     int splits = static_cast<int>((tokens + 63u) / 64u);
     if (splits > max_splits) splits = max_splits;
     const size_t row = (static_cast<size_t>(query_lane) * job.q_heads + head) * max_splits;
-    const float *__restrict__ values = job.scratch + row * HD;
-    const float *__restrict__ stats = attention_stats(job.scratch, job.lanes, job.q_heads, max_splits, HD) + row * 2;
+    const float *__restrict__ mine = job.scratch + row * HD + lane_id * VEC;
+    const float2 *__restrict__ stats = reinterpret_cast<const float2 *>(attention_stats(job.scratch, job.lanes, job.q_heads, max_splits, HD)) + row;
     uint16_t *__restrict__ out_fragments = job.out_fragments;
-    const float *mine = values + lane_id * VEC;
-    float acc[VEC], denominator = 0.0f, maximum = -3.4028234663852886e38f;
+    const int last = splits - 1;
+    // Rows beyond the last split are read as the last split again and weigh nothing, so no load is predicated.
+    float part[8][VEC];
+    auto fetch = [&](int first) {
 #pragma unroll
-    for (int v = 0; v < VEC; v++) acc[v] = 0.0f;
-    auto fetch = [&](int s, float (&part)[VEC]) {
-        if (VEC == 4) {
-            const float4 raw = s < splits ? __ldcg(reinterpret_cast<const float4 *>(mine + static_cast<size_t>(s) * HD)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            part[0] = raw.x, part[VEC > 1 ? 1 : 0] = raw.y, part[VEC > 2 ? 2 : 0] = raw.z, part[VEC > 3 ? 3 : 0] = raw.w;
-        } else if (VEC == 2) {
-            const float2 raw = s < splits ? __ldcg(reinterpret_cast<const float2 *>(mine + static_cast<size_t>(s) * HD)) : make_float2(0.0f, 0.0f);
-            part[0] = raw.x, part[VEC > 1 ? 1 : 0] = raw.y;
-        } else {
-            part[0] = s < splits ? __ldcg(mine + static_cast<size_t>(s) * HD) : 0.0f;
+        for (int u = 0; u < 8; u++) {
+            const float *source = mine + static_cast<size_t>(first + u < last ? first + u : last) * HD;
+            if (VEC == 4) {
+                const float4 raw = __ldcg(reinterpret_cast<const float4 *>(source));
+                part[u][0] = raw.x, part[u][VEC > 1 ? 1 : 0] = raw.y, part[u][VEC > 2 ? 2 : 0] = raw.z, part[u][VEC > 3 ? 3 : 0] = raw.w;
+            } else if (VEC == 2) {
+                const float2 raw = __ldcg(reinterpret_cast<const float2 *>(source));
+                part[u][0] = raw.x, part[u][VEC > 1 ? 1 : 0] = raw.y;
+            } else {
+                part[u][0] = __ldcg(source);
+            }
         }
     };
-    // the first eight rows are requested together with the statistics
-    float part[8][VEC];
+    float acc[VEC];
 #pragma unroll
-    for (int u = 0; u < 8; u++) fetch(u, part[u]);
-    for (int s = lane_id; s < splits; s += 32) maximum = fmaxf(maximum, __ldcg(stats + 2 * s));
+    for (int v = 0; v < VEC; v++) acc[v] = 0.0f;
+    auto accumulate = [&](int first, float weight) {
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const float w = __shfl_sync(0xffffffffu, weight, (first + u) & 31);
+#pragma unroll
+            for (int v = 0; v < VEC; v++) acc[v] += part[u][v] * w;
+        }
+    };
+    // the statistics of the first 32 splits and the first eight rows are requested together
+    float2 pair = __ldcg(stats + (lane_id < last ? lane_id : last));
+    fetch(0);
+    float maximum = lane_id < splits ? pair.x : -3.4028234663852886e38f;
+#pragma unroll 1
+    for (int s = lane_id + 32; s < splits; s += 32) maximum = fmaxf(maximum, __ldcg(stats + s).x);
     maximum = warp_max(maximum);
+    float weight = lane_id < splits ? expf(pair.x - maximum) : 0.0f;
+    float denominator = lane_id < splits ? pair.y * weight : 0.0f;
+    accumulate(0, weight);
 #pragma unroll 1
-    for (int s0 = 0; s0 < splits; s0 += 32) {
-        float weight = 0.0f;
-        if (s0 + lane_id < splits) {
-            const float2 pair = __ldcg(reinterpret_cast<const float2 *>(stats) + s0 + lane_id);
-            weight = expf(pair.x - maximum);
-            denominator += pair.y * weight;
+    for (int s = 8; s < splits; s += 8) {
+        if ((s & 31) == 0) {  // the next 32 splits: this lane weighs split s + lane
+            pair = __ldcg(stats + (s + lane_id < last ? s + lane_id : last));
+            weight = s + lane_id < splits ? expf(pair.x - maximum) : 0.0f;
+            denominator += s + lane_id < splits ? pair.y * weight : 0.0f;
         }
-#pragma unroll 1
-        for (int s = s0; s < splits && s < s0 + 32; s += 8) {
-            if (s != 0) {
-#pragma unroll
-                for (int u = 0; u < 8; u++) fetch(s + u, part[u]);
-            }
-#pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const float w = __shfl_sync(0xffffffffu, weight, (s + u) & 31);  // 0 beyond the last split: the row was not read
-#pragma unroll
-                for (int v = 0; v < VEC; v++) acc[v] += part[u][v] * (s + u < splits ? w : 0.0f);
-            }
-        }
+        fetch(s);
+        accumulate(s, weight);
     }
     denominator = warp_sum(denominator);
 #pragma unroll
