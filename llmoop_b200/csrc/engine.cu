@@ -530,7 +530,15 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     };
     for (const ComponentPlan &layer : plan.layers) scan(layer);
     for (const ComponentPlan &layer : plan.draft_layers) scan(layer);
-    attention_scratch_ = device_alloc(attention_scratch_bytes(options.max_lanes, max_q_heads, max_head_width, max_splits_));
+    // Scratch of the split attention: 64-token splits over the whole ring for the small batches of decode and verify
+    // steps (what the persistent kernel needs for its eight lanes), at least one split per lane of the largest batch
+    // (a prefill chunk), and up to 64 MB beyond that; batches whose partials would not fit attend in longer splits.
+    max_q_heads_ = max_q_heads;
+    const size_t all = static_cast<size_t>(options.max_lanes) * max_q_heads * max_splits_;
+    const size_t small_batches = static_cast<size_t>(std::min(options.max_lanes, 8)) * max_q_heads * max_splits_;
+    const size_t budget = (size_t(64) << 20) / (static_cast<size_t>(max_head_width + 2) * sizeof(float));
+    scratch_partials_ = std::min(all, std::max({small_batches, static_cast<size_t>(options.max_lanes) * max_q_heads, budget}));
+    attention_scratch_ = device_alloc(scratch_partials_ * static_cast<size_t>(max_head_width + 2) * sizeof(float));
 
     // cycle arrays: verify tokens, forced drafts, stop tokens/counts, accept rows, per-step draft tokens, slots
     cycle_state_ = device_alloc(lanes * 64 * sizeof(uint32_t) + static_cast<size_t>(options.max_streams) * (MAX_STOP_TOKENS + 64) * sizeof(uint32_t) * 4);
@@ -1153,7 +1161,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
             if (kv_index < 0) fail("attention op in a component without KV state");
             KvLayer kv = model_->kv_layer(kv_index);
             check(launch_kv_append(u16(op.inputs[1]), u16(op.inputs[2]), kv, lane_table, lanes, st), "kv_append");
-            check(launch_attention(u16(op.inputs[0]), u16(op.outputs[0]), kv, lane_table, lanes, current_width_, op.q_heads, op.attention_scale, split_tokens_,
+            check(launch_attention(u16(op.inputs[0]), u16(op.outputs[0]), kv, lane_table, lanes, current_width_, op.q_heads, op.attention_scale, current_split_tokens_,
                                    current_splits_, static_cast<float *>(attention_scratch_.ptr), st),
                   "attention");
             counters_.kernel_launches++;
@@ -1253,7 +1261,7 @@ void Engine::upload_lanes(const std::vector<uint32_t> &positions, const std::vec
     current_lanes_ = LaneTable{static_cast<const uint32_t *>(lane_positions_.ptr), static_cast<const int32_t *>(lane_slots_.ptr)};
     uint32_t newest = 0;
     for (uint32_t position : positions) newest = std::max(newest, position);
-    current_splits_ = splits_for(newest);
+    plan_splits(static_cast<int>(positions.size()), newest);
 }
 
 void Engine::upload_tokens(const uint32_t *tokens, int count) {
@@ -1261,14 +1269,26 @@ void Engine::upload_tokens(const uint32_t *tokens, int count) {
     current_tokens_ = static_cast<const uint32_t *>(lane_tokens_.ptr);
 }
 
-// Attention launches cover ceil(context / split_tokens) splits, rounded up to a power of two so that a handful of
-// graph shapes serves a growing context.
-int Engine::splits_for(uint64_t newest_tick) const {
-    uint64_t tokens = std::min<uint64_t>(newest_tick + 1, model_->capacity());
-    int needed = static_cast<int>((tokens + split_tokens_ - 1) / split_tokens_);
-    int bucket = 1;
-    while (bucket < needed) bucket <<= 1;
-    return std::min(bucket, max_splits_);
+// Attention launches cover ceil(context / 64) splits of 64 tokens, rounded up to a power of two so that a handful of
+// graph shapes serves a growing context.  A batch with so many lanes that these partials would not fit the scratch
+// (prefill chunks over a long context) attends in longer splits instead: a multiple of 64 tokens each, walked tile
+// by tile inside the kernel.  Returns a word that tells the two apart in a graph key.
+int Engine::plan_splits(int lanes, uint64_t newest_tick) {
+    const uint64_t tokens = std::min<uint64_t>(newest_tick + 1, model_->capacity());
+    const int needed = std::max(1, static_cast<int>((tokens + split_tokens_ - 1) / split_tokens_));
+    const size_t per_split = static_cast<size_t>(std::max(1, lanes)) * max_q_heads_;
+    const int allowed = static_cast<int>(std::max<size_t>(1, std::min<size_t>(scratch_partials_ / per_split, static_cast<size_t>(max_splits_))));
+    if (needed <= allowed) {
+        int bucket = 1;
+        while (bucket < needed) bucket <<= 1;
+        current_split_tokens_ = split_tokens_;
+        current_splits_ = std::min(bucket, allowed);
+    } else {
+        const int factor = (needed + allowed - 1) / allowed;
+        current_split_tokens_ = split_tokens_ * factor;
+        current_splits_ = (needed + factor - 1) / factor;
+    }
+    return current_splits_ | ((current_split_tokens_ / split_tokens_) << 16);
 }
 
 // Runs `body` (stream-ordered launches only: no uploads, read-backs or synchronisation) directly the first time a
@@ -1320,6 +1340,7 @@ bool Engine::run_stack(const StackPlan &stack, int lanes, void *hidden) {
     const int tp_size = model_->options().tp_size;
     if (tp_size > 1 && !tp_connected_) return false;  // without the peer exchange the shards meet in NCCL all-reduces, kernel by kernel
     if (!stack_enabled_ || !stack.available || lanes < 1 || lanes > 8 || current_width_ <= 0 || lanes % current_width_ != 0) return false;
+    if (current_split_tokens_ != split_tokens_) return false;  // the kernel's teams take 64-token splits
     size_t smem = 0;
     if (!decode_stack_supported(stack.shape, lanes, &smem)) return false;
     StackBuffers buffers{};
@@ -1600,8 +1621,7 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
     }
     sync_block_tables();
     upload(base, staging.data(), upload_words * sizeof(uint32_t), "cycle state upload");
-    const int splits = splits_for(newest_tick);
-    current_splits_ = splits;
+    const int splits = plan_splits(streams * (drafts + 1), newest_tick);
 
     backup_pending();
     cuda_check(cudaEventRecord(event_begin_, cuda_stream_), "event record");

@@ -372,6 +372,9 @@ private:
     const uint32_t *current_tokens_ = nullptr;
     int current_width_ = 1;                 // lanes per stream of the current batch (stream-major lane order)
     int current_splits_ = 1;                // attention split count (stride of the scratch partials) of this launch
+    int current_split_tokens_ = 64;         // tokens per split of this launch (64 unless the scratch bounds the split count)
+    size_t scratch_partials_ = 0;           // (lane, q head, split) partials the attention scratch holds
+    int max_q_heads_ = 1;
     struct GraphEntry {
         cudaGraphExec_t exec = nullptr;
         uint64_t kernel_nodes = 0;
@@ -379,7 +382,7 @@ private:
     };
     std::map<std::vector<int>, GraphEntry> graphs_;
     void run_phase(const std::vector<int> &key, const std::function<void()> &body);
-    int splits_for(uint64_t newest_tick) const;
+    int plan_splits(int lanes, uint64_t newest_tick);  // sets the split length and count of the next launches, returns a graph-key word
 };
 
 }  // namespace nerve
