@@ -200,6 +200,22 @@ std::shared_ptr<MountedModel> MountedModel::mount(const std::string &path, const
                    "output projection table copy");
         model->projection_tables_.emplace(name, table);
     }
+    // ... and the bf16 linears of the draft adapter (one launch per draft step each, a single lane wide)
+    if (plan.has_draft) {
+        for (const OpSpec &op : plan.draft_adapter.ops) {
+            if (op.kind != OpKind::Linear) continue;
+            for (const WeightRef &w : op.weights) {
+                if (w.storage != TensorStorage::BF16 || w.n < 256 || model->projection_tables_.count(w.tensor) ||
+                    !output_projection_supported(1, static_cast<int>(w.k)))
+                    continue;
+                DeviceBuffer table = device_alloc(projection_table_bytes(static_cast<int>(w.n), static_cast<int>(w.k)), false);
+                cuda_check(launch_projection_table(static_cast<const uint16_t *>(model->tensor(w.tensor)), table.ptr, static_cast<int>(w.n),
+                                                   static_cast<int>(w.k), nullptr),
+                           "linear table copy");
+                model->projection_tables_.emplace(w.tensor, table);
+            }
+        }
+    }
     cuda_check(cudaDeviceSynchronize(), "output projection table copies");
     {
         int target_kv_layers = 0;
@@ -1069,9 +1085,16 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
             for (size_t branch = 0; branch < op.weights.size(); branch++) {
                 const WeightRef &w = op.weights[branch];
                 if (w.storage == TensorStorage::BF16) {
-                    check(launch_linear_bf16(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(w.tensor)), ptr(op.outputs[branch]), nullptr,
-                                             lanes, static_cast<int>(w.n), static_cast<int>(w.k), EPILOGUE_BF16, 1.0f, st),
-                          "linear_bf16");
+                    const void *streamed = lanes <= 8 && streaming_projection_ ? model_->projection_table(w.tensor) : nullptr;
+                    if (streamed != nullptr) {
+                        check(launch_output_projection(u16(op.inputs[0]), streamed, 0, nullptr, lanes, static_cast<int>(w.n), static_cast<int>(w.k), 1.0f,
+                                                       model_->sm_count(), static_cast<int *>(kernel_error_.ptr), st, u16(op.outputs[branch])),
+                              "linear_bf16 (streamed)");
+                    } else {
+                        check(launch_linear_bf16(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(w.tensor)), ptr(op.outputs[branch]), nullptr,
+                                                 lanes, static_cast<int>(w.n), static_cast<int>(w.k), EPILOGUE_BF16, 1.0f, st),
+                              "linear_bf16");
+                    }
                 } else if (w.storage == TensorStorage::INT4_CT) {
                     check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(w.tensor)),
                                              static_cast<const uint16_t *>(weight(w.scale)), u16(op.outputs[branch]), nullptr, lanes,

@@ -109,11 +109,12 @@ cudaError_t launch_linear_int4_silu_pair(const uint16_t *x, const uint32_t *gate
 // ---- streaming output projection for at most 8 lanes (kernels_projection.cu) ----
 // logits[lane][row] = scale * x[lane] . table[first_row + row], f32, rows of a slice that starts at a multiple of 16.
 // `streamed_table` is the copy launch_projection_table makes of the whole bf16 table (projection_table_bytes bytes).
+// With `rounded` set the kernel is a plain bf16 linear instead: rounded[lane][row] = bf16(sum), `logits` and `scale` unused.
 size_t projection_table_bytes(int rows, int k);
 cudaError_t launch_projection_table(const uint16_t *table, void *out, int rows, int k, cudaStream_t stream);
 bool output_projection_supported(int lanes, int k);
 cudaError_t launch_output_projection(const uint16_t *x, const void *streamed_table, int first_row, float *logits, int lanes, int rows, int k, float scale,
-                                     int grid, int *error_flag, cudaStream_t stream);
+                                     int grid, int *error_flag, cudaStream_t stream, uint16_t *rounded = nullptr);
 
 // ---- INT4 g128 GEMM on the tcgen05 tensor cores for 64 lanes and more (kernels_int4_gemm.cu) ----
 // One CTA per 128 rows x 64 lanes; the launchers above use it for such batches.  y and the epilogues as for

@@ -68,8 +68,9 @@ __device__ __forceinline__ bool projection_wait(uint32_t barrier, uint32_t parit
 struct ProjectionArgs {
     const uint16_t *x;      // [lanes][k] normalised rows
     const uint4 *table;     // the mount-time copy, first tile of the slice to project
-    float *logits;          // [lanes][rows]
-    int lanes, rows, k;     // rows of the slice (logits row stride)
+    float *logits;          // [lanes][rows] f32 * scale, or ...
+    uint16_t *rounded;      // ... [lanes][rows] bf16(sum) when this is set (a plain bf16 linear)
+    int lanes, rows, k;     // rows of the slice (output row stride)
     float scale;
     int *error_flag;
 };
@@ -159,7 +160,10 @@ __global__ void __launch_bounds__(PROJECTION_THREADS, 1) output_projection_kerne
 #pragma unroll
             for (int w = 0; w < PROJECTION_WARPS; w++) sum += source[w * 128];
             const int out_row = (static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x)) * 16 + row;
-            if (m < a.lanes && out_row < a.rows) a.logits[static_cast<size_t>(m) * a.rows + out_row] = sum * a.scale;
+            if (m < a.lanes && out_row < a.rows) {
+                if (a.rounded != nullptr) a.rounded[static_cast<size_t>(m) * a.rows + out_row] = static_cast<uint16_t>(f32_to_bf16_bits(sum));
+                else a.logits[static_cast<size_t>(m) * a.rows + out_row] = sum * a.scale;
+            }
         }
         buffer ^= 1;  // the next tile's partial sums go to the other half; this one is read until the next barrier at the latest
     }
@@ -178,7 +182,7 @@ cudaError_t launch_projection_table(const uint16_t *table, void *out, int rows, 
 bool output_projection_supported(int lanes, int k) { return lanes >= 1 && lanes <= 8 && k % 32 == 0; }
 
 cudaError_t launch_output_projection(const uint16_t *x, const void *streamed_table, int first_row, float *logits, int lanes, int rows, int k, float scale,
-                                     int grid, int *error_flag, cudaStream_t stream) {
+                                     int grid, int *error_flag, cudaStream_t stream, uint16_t *rounded) {
     if (lanes <= 0 || rows <= 0) return cudaSuccess;
     if (!output_projection_supported(lanes, k) || first_row % 16 != 0 || grid < 1) return cudaErrorInvalidValue;
     const size_t smem = 128 + 2 * PROJECTION_WARPS * 128 * sizeof(float) + static_cast<size_t>(PROJECTION_STAGES) * PROJECTION_STAGE_BYTES;
@@ -188,6 +192,7 @@ cudaError_t launch_output_projection(const uint16_t *x, const void *streamed_tab
     args.x = x;
     args.table = reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(streamed_table) + static_cast<size_t>(first_row / 16) * (k / 32) * 1024);
     args.logits = logits;
+    args.rounded = rounded;
     args.lanes = lanes;
     args.rows = rows;
     args.k = k;
