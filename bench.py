@@ -87,18 +87,46 @@ def prompt_tokens(vocab: int, seed: int = 0):
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: through NVML every 10 ms (read-only
+    queries), or with nvidia-smi every 100 ms where the NVML binding is missing."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    REASON_BITS = (("sw_power_cap", 0x4), ("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
 
     def __init__(self, index: int):
         self.index = index
         self.process = None
+        self.thread = None
         self.lines = []
+        self.stop = threading.Event()
+
+    def _nvml_loop(self, nvml, handle):
+        maximum = nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM)
+        while not self.stop.is_set():
+            try:
+                clock = nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
+                reasons = nvml.nvmlDeviceGetCurrentClocksEventReasons(handle) if hasattr(nvml, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+            except Exception:
+                break
+            flags = ["Active" if reasons & bit else "Not Active" for _, bit in self.REASON_BITS]
+            # the column order of the nvidia-smi query: hw_slowdown, hw_thermal_slowdown, sw_thermal_slowdown, sw_power_cap
+            self.lines.append(f"{clock}, {maximum}, {hex(reasons)}, {flags[1]}, {flags[3]}, {flags[2]}, {flags[0]}")
+            self.stop.wait(0.01)
 
     def __enter__(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.thread = threading.Thread(target=self._nvml_loop, args=(pynvml, handle), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.thread = None
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
@@ -114,12 +142,15 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def __exit__(self, *_):
+        self.stop.set()
         if self.process is not None:
             self.process.terminate()
             try:
                 self.process.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.process.kill()
+        elif self.thread is not None:
+            self.thread.join(timeout=2)
 
     def summary(self):
         clocks, maxima, reasons = [], [], set()
