@@ -997,7 +997,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                     profile_begin(static_cast<uint64_t>(w.n) * (w.k / 2 + w.k / 64));
                     check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(w.tensor)),
                                              static_cast<const uint16_t *>(weight(w.scale)), reinterpret_cast<uint16_t *>(partial), nullptr, lanes,
-                                             static_cast<int>(w.n), static_cast<int>(w.k), w.group, EPILOGUE_F32_SCALED, st),
+                                             static_cast<int>(w.n), static_cast<int>(w.k), w.group, EPILOGUE_F32_SCALED, st, static_cast<int *>(kernel_error_.ptr)),
                           "linear_int4 (row-parallel)");
                     profile_end();
                 } else {
@@ -1055,7 +1055,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                     check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(op.weights[0].tensor)),
                                              static_cast<const uint16_t *>(weight(op.weights[0].scale)), u16(add.outputs[0]), u16(residual),
                                              lanes, static_cast<int>(op.weights[0].n), static_cast<int>(op.weights[0].k), 128,
-                                             EPILOGUE_RESIDUAL_ROUNDED, st),
+                                             EPILOGUE_RESIDUAL_ROUNDED, st, static_cast<int *>(kernel_error_.ptr)),
                           "linear_int4 + residual");
                     profile_end();
                     index += 1;
@@ -1076,7 +1076,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                 }
                 profile_begin(branch_bytes);
                 check(launch_linear_int4_multi(u16(op.inputs[0]), branches, qweights, scales, outputs, ns, nullptr, lanes,
-                                               static_cast<int>(op.weights[0].k), EPILOGUE_BF16, st),
+                                               static_cast<int>(op.weights[0].k), EPILOGUE_BF16, st, static_cast<int *>(kernel_error_.ptr)),
                       "linear_int4");
                 profile_end();
                 index = last;
@@ -1098,7 +1098,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                 } else if (w.storage == TensorStorage::INT4_CT) {
                     check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(w.tensor)),
                                              static_cast<const uint16_t *>(weight(w.scale)), u16(op.outputs[branch]), nullptr, lanes,
-                                             static_cast<int>(w.n), static_cast<int>(w.k), w.group, EPILOGUE_BF16, st),
+                                             static_cast<int>(w.n), static_cast<int>(w.k), w.group, EPILOGUE_BF16, st, static_cast<int *>(kernel_error_.ptr)),
                           "linear_int4");
                 } else if (w.storage == TensorStorage::FP8_BLOCK) {
                     if (!op.prequantized_input) fail("FP8 linear " + op.node_id + " without a prequantised input is not mounted");
@@ -1127,7 +1127,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
             } else {
                 check(launch_linear_int4(u16(op.inputs[0]), static_cast<const uint32_t *>(weight(w.tensor)),
                                          static_cast<const uint16_t *>(weight(w.scale)), u16(op.outputs[0]), u16(op.residual_input), lanes,
-                                         static_cast<int>(w.n), static_cast<int>(w.k), w.group, EPILOGUE_RESIDUAL_ROUNDED, st),
+                                         static_cast<int>(w.n), static_cast<int>(w.k), w.group, EPILOGUE_RESIDUAL_ROUNDED, st, static_cast<int *>(kernel_error_.ptr)),
                       "linear_residual_int4");
             }
             break;

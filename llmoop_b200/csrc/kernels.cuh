@@ -61,9 +61,10 @@ cudaError_t launch_linear_silu_multiply_bf16(const uint16_t *x, const uint16_t *
                                              int lanes, int n, int k, cudaStream_t stream);
 
 // INT4 compressed-tensors weight-only linear: qweight [n][k/8] u32, scales bf16 [n][k/group].
+// error_flag (optional device word): set to 3 by the wide-batch GEMM if one of its bounded waits expires.
 cudaError_t launch_linear_int4(const uint16_t *x, const uint32_t *qweight, const uint16_t *scales, uint16_t *y,
                                const uint16_t *residual, int lanes, int n, int k, int group, int epilogue,
-                               cudaStream_t stream);
+                               cudaStream_t stream, int *error_flag = nullptr);
 
 // FP8 W8A8: xq e4m3 [lanes][k], xscale f32 [lanes][k/128]; w e4m3 [n][k]; wscale bf16 [ceil(n/128)][k/128].
 cudaError_t launch_quantize_fp8(const uint16_t *x, uint8_t *q, float *scales, int lanes, int k, cudaStream_t stream);
@@ -101,7 +102,8 @@ cudaError_t launch_attention(const uint16_t *q, uint16_t *out, const KvLayer &kv
 // INT4 multi-branch forms (one launch for q/k/v; gate/up with the SiLU*up epilogue).
 cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint32_t *const *qweights,
                                      const uint16_t *const *scales, uint16_t *const *ys, const int *ns,
-                                     const uint16_t *residual, int lanes, int k, int epilogue, cudaStream_t stream);
+                                     const uint16_t *residual, int lanes, int k, int epilogue, cudaStream_t stream,
+                                     int *error_flag = nullptr);
 cudaError_t launch_linear_int4_silu_pair(const uint16_t *x, const uint32_t *gate_q, const uint16_t *gate_s,
                                          const uint32_t *up_q, const uint16_t *up_s, uint16_t *y, int lanes, int n,
                                          int k, cudaStream_t stream);

@@ -382,14 +382,14 @@ static cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, cudaStream_t
 
 cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint32_t *const *qweights,
                                      const uint16_t *const *scales, uint16_t *const *ys, const int *ns,
-                                     const uint16_t *residual, int lanes, int k, int epilogue, cudaStream_t stream) {
+                                     const uint16_t *residual, int lanes, int k, int epilogue, cudaStream_t stream, int *error_flag) {
     if (lanes <= 0) return cudaSuccess;
     if (k % 128 != 0 || branches < 1 || branches > 3) return cudaErrorInvalidValue;
     if (linear_int4_gemm_supported(lanes, ns[0], k)) {
         // wide batches (prefill chunks, many-stream verify): one tcgen05 GEMM per matrix, the weights read once per 64 lanes
         for (int b = 0; b < branches; b++) {
             cudaError_t status = launch_linear_int4_gemm(x, qweights[b], scales[b], ys[b], branches == 1 ? residual : nullptr, lanes, ns[b], k, epilogue, 1.0f,
-                                                         nullptr, stream);
+                                                         error_flag, stream);
             if (status != cudaSuccess) return status;
         }
         return cudaSuccess;
@@ -415,9 +415,9 @@ cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint
 
 cudaError_t launch_linear_int4(const uint16_t *x, const uint32_t *qweight, const uint16_t *scales, uint16_t *y,
                                const uint16_t *residual, int lanes, int n, int k, int group, int epilogue,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, int *error_flag) {
     if (group != 128) return cudaErrorInvalidValue;
-    return launch_linear_int4_multi(x, 1, &qweight, &scales, &y, &n, residual, lanes, k, epilogue, stream);
+    return launch_linear_int4_multi(x, 1, &qweight, &scales, &y, &n, residual, lanes, k, epilogue, stream, error_flag);
 }
 
 // gate/up pair with the SiLU*up epilogue (gate -> bf16, SiLU -> bf16, up -> bf16, product -> bf16: the
