@@ -118,6 +118,12 @@ typedef struct {
 } nerve_b200_engine_snapshot_counts;
 int32_t nerve_b200_engine_stream_snapshot_of(nerve_b200_engine *engine, int64_t stream_id, nerve_b200_engine_stream_snapshot *out);
 int32_t nerve_b200_engine_snapshot(nerve_b200_engine *engine, nerve_b200_engine_snapshot_counts *out);
+/* The runtime scheduler's view of one of the engine's streams (RuntimeStreamSnapshot, stream_runtime.rs:258-300; the
+ * engine owns a scheduler as placed_prompt_engine.rs:455-520 does and runs what it schedules): out_counts[0] =
+ * scheduled activations, [1] = completed input events, [2] = generated tokens, [3] = activations in flight,
+ * [4] = queued input events, [5] = 1 while an input event is current.  Counts restart when the stream's events are
+ * dropped (reset, interrupt, stop after current). */
+int32_t nerve_b200_engine_scheduler_stream_counts(nerve_b200_engine *engine, int64_t stream_id, uint64_t out_counts[6]);
 
 /* enqueue_input_event (placed_prompt_engine.rs:256-331): VulkanResidentTokenInputEvent
  * {id, token_ids, max_public_tokens, stop_token_ids}. */

@@ -288,6 +288,13 @@ int32_t nerve_b200_engine_stream_snapshot_of(nerve_b200_engine *engine, int64_t 
     });
 }
 
+int32_t nerve_b200_engine_scheduler_stream_counts(nerve_b200_engine *engine, int64_t stream_id, uint64_t out_counts[6]) {
+    return guarded([&] {
+        require(engine != nullptr && out_counts != nullptr, "null argument");
+        engine->engine->scheduler_stream_counts(stream_id, out_counts);
+    });
+}
+
 int32_t nerve_b200_engine_snapshot(nerve_b200_engine *engine, nerve_b200_engine_snapshot_counts *out) {
     return guarded([&] {
         require(engine != nullptr && out != nullptr, "null argument");

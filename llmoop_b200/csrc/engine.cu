@@ -705,6 +705,21 @@ const Engine::Stream &Engine::stream(int64_t id) const {
 uint64_t Engine::stream_tick(int64_t id) const { return stream(id).next_tick; }
 
 void Engine::add_stream(int64_t id, uint32_t seed, int speculative_draft_tokens, const SamplerConfig &sampler) {
+    register_stream(id, seed, speculative_draft_tokens, sampler);
+    scheduler_.add_stream(scheduler_id(id));
+}
+
+void Engine::rejoin_scheduler(int64_t id) {
+    const std::string name = scheduler_id(id);
+    carried_activations_.erase(std::remove_if(carried_activations_.begin(), carried_activations_.end(),
+                                              [&](const runtime::Activation &activation) { return activation.stream_id == name; }),
+                               carried_activations_.end());
+    scheduler_.interrupt_stream(name, "the stream's events were dropped");  // also forgets activations in flight
+    scheduler_.remove_stream(name);
+    scheduler_.add_stream(name);
+}
+
+void Engine::register_stream(int64_t id, uint32_t seed, int speculative_draft_tokens, const SamplerConfig &sampler) {
     if (streams_.count(id)) fail("stream " + std::to_string(id) + " already exists");
     if (free_slots_.empty()) fail("no free stream slot (max_streams = " + std::to_string(model_->options().max_streams) + ")");
     if (sampler.method != 0 && sampler.method != 1) fail("sampler method must be 0 (greedy) or 1 (temperature_top_k_top_p)");
@@ -811,6 +826,8 @@ void Engine::remove_stream(int64_t id) {
     if (s.sampler.method != 0) stochastic_streams_--;
     free_slots_.push_back(s.slot);
     streams_.erase(id);
+    rejoin_scheduler(id);
+    scheduler_.remove_stream(scheduler_id(id));
 }
 
 void Engine::reset_stream(int64_t id) {
@@ -819,6 +836,8 @@ void Engine::reset_stream(int64_t id) {
     s.next_tick = 0;
     s.queue.clear();
     s.active.reset();
+    s.detached = false;
+    rejoin_scheduler(id);
     const size_t frame = static_cast<size_t>(model_->plan().hidden) * 2;
     cuda_check(cudaMemsetAsync(static_cast<uint8_t *>(pending_hidden_.ptr) + s.slot * frame, 0, frame, cuda_stream_), "pending reset");
 }
@@ -827,6 +846,8 @@ void Engine::interrupt_stream(int64_t id) {
     Stream &s = stream(id);
     s.queue.clear();
     s.active.reset();
+    s.detached = false;
+    rejoin_scheduler(id);  // interrupt (stream_runtime.rs:770-817), then a fresh entry: the scheduler keeps an interrupted stream closed to new events, the engine's streams take them
 }
 
 // stop_stream_after_current (placed_prompt_engine.rs:307-331, placed_prompt_event.rs:320-341): the active event
@@ -838,6 +859,11 @@ void Engine::stop_stream_after_current(int64_t id) {
     s.queue.clear();
     s.active->remaining = 0;
     if (s.active->has_feedback) s.active->feedback_closes = true;
+    // the scheduler drops the stream's queued events and its view of the current one; what is left of the event -
+    // the closing tick - runs as a control step at the start of the next run
+    scheduler_.close_stream_after_current(scheduler_id(id));
+    rejoin_scheduler(id);
+    s.detached = true;
 }
 
 Engine::StreamSnapshot Engine::stream_snapshot(int64_t id) const {
@@ -855,6 +881,22 @@ Engine::StreamSnapshot Engine::stream_snapshot(int64_t id) const {
     return snapshot;
 }
 
+void Engine::scheduler_stream_counts(int64_t id, uint64_t out_counts[6]) const {
+    stream(id);  // unknown stream: the engine's error
+    const std::string name = scheduler_id(id);
+    for (const runtime::StreamSnapshot &snapshot : scheduler_.snapshot().streams) {
+        if (snapshot.stream_id != name) continue;
+        out_counts[0] = snapshot.scheduled_activation_count;
+        out_counts[1] = snapshot.completed_input_event_count;
+        out_counts[2] = snapshot.generated_token_count;
+        out_counts[3] = snapshot.in_flight_activation_count;
+        out_counts[4] = snapshot.queued_input_event_count;
+        out_counts[5] = snapshot.current_input_event_id.has_value() ? 1 : 0;
+        return;
+    }
+    fail("stream " + name + " is unknown to the scheduler");
+}
+
 Engine::EngineSnapshot Engine::snapshot() const {
     EngineSnapshot snapshot;
     snapshot.stream_count = streams_.size();
@@ -866,7 +908,8 @@ Engine::EngineSnapshot Engine::snapshot() const {
 void Engine::fork_stream(int64_t source, int64_t destination, uint32_t seed) {
     Stream &src = stream(source);
     if (src.active) fail("cannot fork stream " + std::to_string(source) + " while an input event is active");
-    add_stream(destination, seed, src.k, src.sampler);
+    register_stream(destination, seed, src.k, src.sampler);
+    scheduler_.fork_stream_transient_state(scheduler_id(source), scheduler_id(destination), "default");
     Stream &dst = stream(destination);
     dst.next_tick = src.next_tick;
     // Every mapped page is shared by reference count, no copies (stream_state.rs:474-496); the first write of
@@ -890,6 +933,11 @@ void Engine::enqueue(int64_t id, const InputEvent &event) {
     if (event.stop_token_ids.size() > MAX_STOP_TOKENS) fail("at most 8 stop tokens are supported per event");
     for (uint32_t token : event.token_ids)
         if (token >= static_cast<uint32_t>(model_->plan().vocab)) fail("input token id is outside the vocabulary");
+    runtime::InputEvent scheduled;
+    scheduled.id = event.id.empty() ? std::string("event") : event.id;
+    scheduled.token_ids = event.token_ids;
+    scheduled.max_public_tokens = event.max_public_tokens;
+    scheduler_.enqueue_input_event(scheduler_id(id), scheduled);
     s.queue.push_back(event);
 }
 
@@ -1754,59 +1802,130 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
     profile_ms_ = 0.0;
     profile_bytes_ = profile_launches_ = 0;
     cuda_check(cudaEventRecord(run_begin_, cuda_stream_), "event record");
+    // One scheduled activation in execution: the stream, where it stood, and what it has emitted so far.
+    struct Work {
+        runtime::Activation activation;
+        Stream *stream;
+        uint64_t start_tick;
+        size_t emitted_before;
+        std::vector<uint32_t> generated;
+    };
+    auto note_generated = [](Work &work) {
+        if (work.stream->active == nullptr) return;
+        const std::vector<uint32_t> &all = work.stream->active->generated;
+        work.generated.assign(all.begin() + static_cast<std::ptrdiff_t>(std::min(work.emitted_before, all.size())), all.end());
+    };
+    auto run_ticks_in_batches = [&](std::vector<Stream *> &streams) {
+        const size_t per_batch = model_->options().max_lanes;
+        for (size_t offset = 0; offset < streams.size(); offset += per_batch) {
+            std::vector<Stream *> batch(streams.begin() + offset, streams.begin() + std::min(streams.size(), offset + per_batch));
+            run_single_ticks(batch, on_output, report);
+            report.batch_count++;
+            report.activation_count += batch.size();
+            report.max_batch_width = std::max<uint64_t>(report.max_batch_width, batch.size());
+        }
+    };
     while (true) {
         if (max_batches && report.batch_count >= max_batches) {
             report.idle = false;
             break;
         }
-        bool any = false;
-        // 1. prefill: streams with external inputs left, one chunk each per round
-        for (auto &entry : streams_) {
-            Stream &s = entry.second;
-            activate_next_event(s);
-            if (!s.active) continue;
-            ActiveEvent &event = *s.active;
-            if (event.next_external >= event.input.token_ids.size()) continue;
-            any = true;
-            uint64_t start = now_ns();
-            size_t left = event.input.token_ids.size() - event.next_external;
-            int budget = std::min(prefill_chunk_, model_->options().max_lanes);
-            int count = static_cast<int>(std::min<size_t>(left, budget));
-            // A batch appends the K/V of all its lanes before any lane attends.  Once the KV ring wraps, a later
-            // lane's slot is the one an earlier lane's window still ends in, and the reference runs the lanes one
-            // after the other (append_gqa_attention_bf16.comp.template:189-215 per tick).  So a chunk stops at the
-            // wrap, and beyond it every tick is a batch of its own.
-            const uint64_t ring = model_->capacity();
-            if (s.next_tick + static_cast<uint64_t>(count) > ring) count = s.next_tick < ring ? static_cast<int>(ring - s.next_tick) : 1;
-            bool last = static_cast<size_t>(count) == left;
-            bool sample = last && event.remaining > 0;
-            uint32_t sampled = 0;
-            uint64_t tick_of_last = s.next_tick + count - 1;
-            run_prefill_chunk(s, event.input.token_ids.data() + event.next_external, count, sample, &sampled);
-            event.next_external += count;
-            report.prefill_tokens += count;
-            report.activation_count++;
-            if (sample) emit(s, sampled, tick_of_last, on_output, report);
-            else if (last) {
-                synchronize("prefill synchronize");
-                s.active.reset();  // no public outputs requested: the event ends with the prompt
-                s.completed_events++;
+        // 0. control steps: events that were stopped from outside still feed their last token back (the closing
+        // tick, placed_prompt_event.rs:320-341); the scheduler no longer tracks them
+        {
+            std::vector<Stream *> closing;
+            for (auto &entry : streams_) {
+                Stream &s = entry.second;
+                if (!s.detached) continue;
+                s.detached = false;
+                if (!s.active) continue;
+                if (s.active->has_feedback) {
+                    closing.push_back(&s);
+                } else {
+                    s.active.reset();
+                    s.completed_events++;
+                }
             }
+            if (!closing.empty()) {
+                uint64_t start = now_ns();
+                run_ticks_in_batches(closing);
+                report.decode_ns += now_ns() - start;
+            }
+        }
+        // 1. the scheduler's step: at most one activation per stream - a prefill chunk or a decode window
+        size_t widest_window = 1;
+        for (auto &entry : streams_) widest_window = std::max<size_t>(widest_window, static_cast<size_t>(entry.second.k) + 1);
+        const size_t chunk_budget = static_cast<size_t>(std::max(1, std::min(prefill_chunk_, model_->options().max_lanes)));
+        const runtime::SchedulerBudget budget =
+            runtime::SchedulerBudget(std::max<size_t>(1, streams_.size()), chunk_budget, std::numeric_limits<size_t>::max())
+                .with_max_decode_tokens_per_activation(widest_window);
+        std::vector<runtime::Activation> scheduled;
+        if (!carried_activations_.empty()) {
+            scheduled.swap(carried_activations_);  // the activations of a batch that failed: the same work again
+        } else {
+            scheduled = scheduler_.schedule_step(budget).activations;
+        }
+        if (scheduled.empty()) break;
+        std::vector<Work> works;
+        works.reserve(scheduled.size());
+        for (runtime::Activation &activation : scheduled) {
+            Stream &s = stream(std::stoll(activation.stream_id));
+            activate_next_event(s);
+            if (!s.active) fail("scheduler activation for stream " + activation.stream_id + " without an input event");
+            works.push_back(Work{std::move(activation), &s, s.next_tick, s.active->generated.size(), {}});
+        }
+        try {
+        // 2. prefill chunks, one stream at a time
+        for (Work &work : works) {
+            if (work.activation.kind != runtime::ActivationKind::PrefillChunk) continue;
+            Stream &s = *work.stream;
+            ActiveEvent &event = *s.active;
+            if (event.next_external != work.activation.token_offset || event.input.token_ids.size() < work.activation.token_offset + work.activation.token_ids.size())
+                fail("scheduler and engine disagree about the prompt position of stream " + work.activation.stream_id);
+            uint64_t start = now_ns();
+            size_t left = work.activation.token_ids.size();
+            const bool ends_prompt = work.activation.remaining_prompt_token_count == 0;
+            while (left > 0) {
+                int count = static_cast<int>(left);
+                // A batch appends the K/V of all its lanes before any lane attends.  Once the KV ring wraps, a later
+                // lane's slot is the one an earlier lane's window still ends in, and the reference runs the lanes one
+                // after the other (append_gqa_attention_bf16.comp.template:189-215 per tick).  So a chunk stops at the
+                // wrap, and beyond it every tick is a batch of its own.
+                const uint64_t ring = model_->capacity();
+                if (s.next_tick + static_cast<uint64_t>(count) > ring) count = s.next_tick < ring ? static_cast<int>(ring - s.next_tick) : 1;
+                const bool last = ends_prompt && static_cast<size_t>(count) == left;
+                const bool sample = last && event.remaining > 0;
+                uint32_t sampled = 0;
+                const uint64_t tick_of_last = s.next_tick + count - 1;
+                run_prefill_chunk(s, event.input.token_ids.data() + event.next_external, count, sample, &sampled);
+                event.next_external += count;
+                left -= static_cast<size_t>(count);
+                report.prefill_tokens += count;
+                if (sample) emit(s, sampled, tick_of_last, on_output, report);
+                else if (last) {
+                    synchronize("prefill synchronize");
+                    note_generated(work);
+                    s.active.reset();  // no public outputs requested: the event ends with the prompt
+                    s.completed_events++;
+                }
+            }
+            report.activation_count++;
             report.prefill_ns += now_ns() - start;
         }
-        // 2. decode: group feedback activations
+        // 3. decode windows: grouped into speculative cycles of equal draft count and single ticks
         std::map<int, std::vector<Stream *>> speculative;
         std::vector<Stream *> single;
-        for (auto &entry : streams_) {
-            Stream &s = entry.second;
-            if (!s.active) continue;
+        for (Work &work : works) {
+            if (work.activation.kind != runtime::ActivationKind::DecodeFeedback) continue;
+            Stream &s = *work.stream;
             ActiveEvent &event = *s.active;
-            if (event.next_external < event.input.token_ids.size() || !event.has_feedback) continue;
+            if (!event.has_feedback) fail("scheduler decode window for stream " + work.activation.stream_id + " without a token to feed back");
+            const size_t window = std::min<size_t>(work.activation.max_tokens, event.remaining);
             // no speculation across or beyond the wrap of the KV ring (see the prefill chunks above): the rejected
             // lanes of a cycle would also overwrite slots that are still inside the window
             const bool ring_wraps = s.next_tick + static_cast<uint64_t>(s.k) + 1 > model_->capacity();
-            if (s.k > 0 && model_->plan().has_draft && !event.feedback_closes && event.remaining >= 2 && !ring_wraps) {
-                int drafts = static_cast<int>(std::min<size_t>(s.k, event.remaining - 1));
+            if (s.k > 0 && model_->plan().has_draft && !event.feedback_closes && window >= 2 && !ring_wraps) {
+                int drafts = static_cast<int>(std::min<size_t>(s.k, window - 1));
                 speculative[drafts].push_back(&s);
             } else {
                 single.push_back(&s);
@@ -1814,7 +1933,6 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
         }
         uint64_t start = now_ns();
         for (auto &group : speculative) {
-            any = true;
             // split groups that would exceed the lane budget
             size_t per_batch = std::max<size_t>(1, model_->options().max_lanes / (group.first + 1));
             for (size_t offset = 0; offset < group.second.size(); offset += per_batch) {
@@ -1826,19 +1944,51 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
                 report.max_batch_width = std::max<uint64_t>(report.max_batch_width, batch.size());
             }
         }
-        if (!single.empty()) {
-            any = true;
-            size_t per_batch = model_->options().max_lanes;
-            for (size_t offset = 0; offset < single.size(); offset += per_batch) {
-                std::vector<Stream *> batch(single.begin() + offset, single.begin() + std::min(single.size(), offset + per_batch));
-                run_single_ticks(batch, on_output, report);
-                report.batch_count++;
-                report.activation_count += batch.size();
-                report.max_batch_width = std::max<uint64_t>(report.max_batch_width, batch.size());
-            }
+        if (!single.empty()) run_ticks_in_batches(single);
+        // 4. what the activations emitted; then the closing tick of every event that has emitted its last token (the
+        // scheduler reserves one state activation beyond the window for it, stream_runtime.rs:1262-1290)
+        std::vector<Stream *> closing;
+        for (Work &work : works) {
+            note_generated(work);
+            Stream &s = *work.stream;
+            if (s.active && s.active->has_feedback && s.active->feedback_closes) closing.push_back(&s);
         }
+        if (!closing.empty()) run_ticks_in_batches(closing);
         report.decode_ns += now_ns() - start;
-        if (!any) break;
+        // 5. outcomes: generated tokens, whether the event goes on, and the ticks the stream advanced by
+        for (Work &work : works) {
+            Stream &s = *work.stream;
+            runtime::ActivationOutcome outcome;
+            outcome.generated_token_ids = work.generated;
+            outcome.continue_generation = s.active != nullptr;
+            outcome.processed_state_activation_count = static_cast<size_t>(s.next_tick - work.start_tick);
+            scheduler_.complete_activation(work.activation.id, outcome);
+        }
+        } catch (...) {
+            // A batch failed and was discarded: its streams stand where they stood.  Activations that did run are
+            // completed (an event that still owes its closing tick gets it as a control step of the next run), the
+            // others are carried into the next run, which repeats them before it asks the scheduler for more.
+            for (Work &work : works) {
+                Stream &s = *work.stream;
+                note_generated(work);
+                const bool ran = s.next_tick != work.start_tick || !work.generated.empty() || s.active == nullptr;
+                if (!ran) {
+                    carried_activations_.push_back(work.activation);
+                    continue;
+                }
+                runtime::ActivationOutcome outcome;
+                outcome.generated_token_ids = work.generated;
+                const bool owes_closing_tick = s.active && s.active->has_feedback && s.active->feedback_closes;
+                outcome.continue_generation = s.active != nullptr && !owes_closing_tick;
+                outcome.processed_state_activation_count = static_cast<size_t>(s.next_tick - work.start_tick);
+                if (owes_closing_tick) s.detached = true;
+                try {
+                    scheduler_.complete_activation(work.activation.id, outcome);
+                } catch (...) {
+                }
+            }
+            throw;
+        }
     }
     cuda_check(cudaEventRecord(run_end_, cuda_stream_), "event record");
     cuda_check(cudaMemcpyAsync(host_records_, kernel_error_.ptr, sizeof(int), cudaMemcpyDeviceToHost, cuda_stream_), "kernel status readback");

@@ -29,6 +29,7 @@
 
 #include "kernels.cuh"
 #include "package.hpp"
+#include "stream_runtime.hpp"
 
 namespace nerve {
 
@@ -220,6 +221,7 @@ public:
     };
     StreamSnapshot stream_snapshot(int64_t id) const;
     EngineSnapshot snapshot() const;
+    void scheduler_stream_counts(int64_t id, uint64_t out_counts[6]) const;
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
     // Test hook: the next `launches` launches of the persistent decode kernel wait (briefly) at their first grid barrier for
     // an arrival count the grid cannot reach, give up and report it - a failure made without faulting anything.
@@ -267,11 +269,20 @@ private:
         std::vector<uint32_t> teacher;
         bool block_table_dirty = true;
         uint64_t completed_events = 0;
+        bool detached = false;  // the active event was stopped from outside: the scheduler no longer tracks it
     };
 
     Stream &stream(int64_t id);
     const Stream &stream(int64_t id) const;
     void activate_next_event(Stream &s);
+    void register_stream(int64_t id, uint32_t seed, int speculative_draft_tokens, const SamplerConfig &sampler);
+    void rejoin_scheduler(int64_t id);  // a fresh scheduler entry for the stream (its events were dropped)
+    static std::string scheduler_id(int64_t id) { return std::to_string(id); }
+    // Admission: which stream runs what next (events -> prefill chunks -> decode windows, running before waiting,
+    // one activation per stream and step) is decided by the scheduler unit that restates stream_runtime.rs; the
+    // engine executes the activations and reports their outcomes (placed_prompt_engine.rs:455-520).
+    runtime::StreamScheduler scheduler_;
+    std::vector<runtime::Activation> carried_activations_;  // scheduled, but their batch failed: executed first by the next run
     void ensure_pages(Stream &s, uint64_t last_tick);
     void release_pages(Stream &s);
     void sync_block_tables();

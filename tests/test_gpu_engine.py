@@ -429,3 +429,44 @@ def test_stop_after_current_and_snapshots(drafts):
     assert engine.stream_snapshot(3)["idle"]
     engine.close()
     package.unmount()
+
+
+def test_engine_runs_what_the_scheduler_schedules():
+    """The engine owns a runtime scheduler (placed_prompt_engine.rs:455-520) and executes its activations: prompt
+    chunks of the configured length, then decode windows of k + 1 tokens; every outcome is reported back, so the
+    scheduler's counters follow the event exactly, also across a fork and a dropped event."""
+    import llmoop_b200 as nb
+
+    name = "tiny_int4_mtp"
+    opkg, _ = _oracle(name)
+    prompt = _prompt(opkg.vocab, 40, seed=91)
+    package = nb.Package(GOLDEN / name, capacity_tokens=128, page_tokens=16, max_streams=3, max_lanes=32)
+    engine = nb.Engine(package)
+    engine.set_prefill_chunk(16)
+    engine.add_stream(1, speculative_draft_tokens=3)
+    engine.enqueue_input_event(1, prompt, 9)
+    queued = engine.scheduler_stream_counts(1)
+    assert queued["queued_input_event_count"] == 1 and queued["scheduled_activation_count"] == 0
+    outputs, report = engine.run_until_idle()
+    assert len(outputs) == 9
+    counts = engine.scheduler_stream_counts(1)
+    # 40 prompt tokens in chunks of 16 -> 3 prefill activations (the last one samples the first token), then decode
+    # windows until the 9 tokens are out: one activation per speculative cycle
+    assert counts["completed_input_event_count"] == 1 and counts["generated_token_count"] == 9
+    assert counts["in_flight_activation_count"] == 0 and counts["has_current_input_event"] == 0 and counts["queued_input_event_count"] == 0
+    # (8 tokens after the first: between two full windows of four and eight windows of one accepted token)
+    assert 3 + 2 <= counts["scheduled_activation_count"] <= 3 + 8
+    assert counts["scheduled_activation_count"] >= 3 + report.cycle_count  # + single ticks when one token is left
+    assert engine.stream_tick(1) == 40 + 9
+    # a fork starts with its own (empty) scheduler entry and takes events of its own
+    engine.fork_stream(1, 2)
+    assert engine.scheduler_stream_counts(2)["scheduled_activation_count"] == 0
+    engine.enqueue_input_event(2, prompt[:3], 2)
+    engine.enqueue_input_event(1, prompt[:5], 4)
+    engine.interrupt_stream(1)                       # the event is dropped before it ran
+    outputs, _ = engine.run_until_idle()
+    assert [sid for sid, _, _, _ in outputs] == [2, 2]
+    assert engine.scheduler_stream_counts(1)["queued_input_event_count"] == 0
+    assert engine.scheduler_stream_counts(2)["generated_token_count"] == 2
+    engine.close()
+    package.unmount()
