@@ -546,15 +546,20 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     };
     for (const ComponentPlan &layer : plan.layers) scan(layer);
     for (const ComponentPlan &layer : plan.draft_layers) scan(layer);
-    // Scratch of the split attention: 64-token splits over the whole ring for the small batches of decode and verify
-    // steps (what the persistent kernel needs for its eight lanes), at least one split per lane of the largest batch
-    // (a prefill chunk), and up to 64 MB beyond that; batches whose partials would not fit attend in longer splits.
+    // Scratch of the split attention.  The persistent kernel (at most eight lanes) takes 64-token splits over the
+    // whole ring.  The kernel-per-operator path takes splits of a length fixed per engine - 64 tokens where the
+    // partials of the largest batch over the whole ring fit 1 GB, else the next multiple of 64 that makes them fit
+    // (a prefill chunk of 2048 lanes over a 32K ring: 1152 tokens), walked tile by tile inside the kernel - so the
+    // arithmetic of a lane never depends on which batch it runs in.
     max_q_heads_ = max_q_heads;
+    const size_t partial_bytes = static_cast<size_t>(max_head_width + 2) * sizeof(float);
+    const size_t budget = (size_t(1) << 30) / partial_bytes;
     const size_t all = static_cast<size_t>(options.max_lanes) * max_q_heads * max_splits_;
+    const int factor = static_cast<int>(std::max<size_t>(1, (all + budget - 1) / budget));
+    op_split_tokens_ = split_tokens_ * factor;
+    const size_t op_splits = (model_->capacity() + op_split_tokens_ - 1) / op_split_tokens_;
     const size_t small_batches = static_cast<size_t>(std::min(options.max_lanes, 8)) * max_q_heads * max_splits_;
-    const size_t budget = (size_t(64) << 20) / (static_cast<size_t>(max_head_width + 2) * sizeof(float));
-    scratch_partials_ = std::min(all, std::max({small_batches, static_cast<size_t>(options.max_lanes) * max_q_heads, budget}));
-    attention_scratch_ = device_alloc(scratch_partials_ * static_cast<size_t>(max_head_width + 2) * sizeof(float));
+    attention_scratch_ = device_alloc(std::max(small_batches, static_cast<size_t>(options.max_lanes) * max_q_heads * op_splits) * partial_bytes);
 
     // cycle arrays: verify tokens, forced drafts, stop tokens/counts, accept rows, per-step draft tokens, slots
     cycle_state_ = device_alloc(lanes * 64 * sizeof(uint32_t) + static_cast<size_t>(options.max_streams) * (MAX_STOP_TOKENS + 64) * sizeof(uint32_t) * 4);
@@ -1232,8 +1237,8 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
             if (kv_index < 0) fail("attention op in a component without KV state");
             KvLayer kv = model_->kv_layer(kv_index);
             check(launch_kv_append(u16(op.inputs[1]), u16(op.inputs[2]), kv, lane_table, lanes, st), "kv_append");
-            check(launch_attention(u16(op.inputs[0]), u16(op.outputs[0]), kv, lane_table, lanes, current_width_, op.q_heads, op.attention_scale, current_split_tokens_,
-                                   current_splits_, static_cast<float *>(attention_scratch_.ptr), st),
+            check(launch_attention(u16(op.inputs[0]), u16(op.outputs[0]), kv, lane_table, lanes, current_width_, op.q_heads, op.attention_scale, op_split_tokens_,
+                                   current_op_splits_, static_cast<float *>(attention_scratch_.ptr), st),
                   "attention");
             counters_.kernel_launches++;
             break;
@@ -1340,26 +1345,22 @@ void Engine::upload_tokens(const uint32_t *tokens, int count) {
     current_tokens_ = static_cast<const uint32_t *>(lane_tokens_.ptr);
 }
 
-// Attention launches cover ceil(context / 64) splits of 64 tokens, rounded up to a power of two so that a handful of
-// graph shapes serves a growing context.  A batch with so many lanes that these partials would not fit the scratch
-// (prefill chunks over a long context) attends in longer splits instead: a multiple of 64 tokens each, walked tile
-// by tile inside the kernel.  Returns a word that tells the two apart in a graph key.
+// Attention launches cover ceil(context / split) splits, rounded up to a power of two so that a handful of graph
+// shapes serves a growing context: splits of 64 tokens in the persistent kernel, of the engine's fixed length on the
+// kernel-per-operator path.  Returns a word for graph keys.
 int Engine::plan_splits(int lanes, uint64_t newest_tick) {
+    (void)lanes;
     const uint64_t tokens = std::min<uint64_t>(newest_tick + 1, model_->capacity());
-    const int needed = std::max(1, static_cast<int>((tokens + split_tokens_ - 1) / split_tokens_));
-    const size_t per_split = static_cast<size_t>(std::max(1, lanes)) * max_q_heads_;
-    const int allowed = static_cast<int>(std::max<size_t>(1, std::min<size_t>(scratch_partials_ / per_split, static_cast<size_t>(max_splits_))));
-    if (needed <= allowed) {
-        int bucket = 1;
-        while (bucket < needed) bucket <<= 1;
-        current_split_tokens_ = split_tokens_;
-        current_splits_ = std::min(bucket, allowed);
-    } else {
-        const int factor = (needed + allowed - 1) / allowed;
-        current_split_tokens_ = split_tokens_ * factor;
-        current_splits_ = (needed + factor - 1) / factor;
-    }
-    return current_splits_ | ((current_split_tokens_ / split_tokens_) << 16);
+    auto bucket = [&](int split_tokens) {
+        const int needed = std::max(1, static_cast<int>((tokens + split_tokens - 1) / split_tokens));
+        const int most = std::max(1, static_cast<int>((model_->capacity() + split_tokens - 1) / split_tokens));
+        int count = 1;
+        while (count < needed) count <<= 1;
+        return std::min(count, most);
+    };
+    current_splits_ = bucket(split_tokens_);
+    current_op_splits_ = bucket(op_split_tokens_);
+    return current_splits_ | (current_op_splits_ << 16);
 }
 
 // Runs `body` (stream-ordered launches only: no uploads, read-backs or synchronisation) directly the first time a
@@ -1411,7 +1412,6 @@ bool Engine::run_stack(const StackPlan &stack, int lanes, void *hidden) {
     const int tp_size = model_->options().tp_size;
     if (tp_size > 1 && !tp_connected_) return false;  // without the peer exchange the shards meet in NCCL all-reduces, kernel by kernel
     if (!stack_enabled_ || !stack.available || lanes < 1 || lanes > 8 || current_width_ <= 0 || lanes % current_width_ != 0) return false;
-    if (current_split_tokens_ != split_tokens_) return false;  // the kernel's teams take 64-token splits
     size_t smem = 0;
     if (!decode_stack_supported(stack.shape, lanes, &smem)) return false;
     StackBuffers buffers{};

@@ -383,8 +383,9 @@ private:
     const uint32_t *current_tokens_ = nullptr;
     int current_width_ = 1;                 // lanes per stream of the current batch (stream-major lane order)
     int current_splits_ = 1;                // attention split count (stride of the scratch partials) of this launch
-    int current_split_tokens_ = 64;         // tokens per split of this launch (64 unless the scratch bounds the split count)
-    size_t scratch_partials_ = 0;           // (lane, q head, split) partials the attention scratch holds
+    int op_split_tokens_ = 64;              // tokens per split on the kernel-per-operator path: fixed per engine, so that a lane's
+                                            // arithmetic does not depend on the batch it runs in
+    int current_op_splits_ = 1;             // split count of this launch on that path
     int max_q_heads_ = 1;
     struct GraphEntry {
         cudaGraphExec_t exec = nullptr;
