@@ -268,7 +268,9 @@ def cpu_cycle_sample(directory, seconds_budget=150.0, max_cycles=None, cuda_run=
         parity["note"] = ("32 layers of random weights amplify one bf16 rounding of the hidden state to a few 1e-2 of a logit (logits reach +-6): the "
                           "oracle, the kernel-per-operator path and the persistent kernel differ mutually by that much "
                           "(tests/test_gpu_config2_parity.py), so near-ties up to that size may fall either way; accepted_equal says the "
-                          "per-cycle bookkeeping followed the oracle through every one of them")
+                          "per-cycle bookkeeping followed the oracle through every one of them; control_kernel_per_operator_path is the "
+                          "same replay of the path whose operators match the oracle bit for bit one by one - it parts from the oracle "
+                          "just as often")
     else:
         token, _ = oracle.prefill(stream, prompt, sample_last=True)
         begin = time.perf_counter()
@@ -401,6 +403,13 @@ def main():
         raise RuntimeError("teacher-forced run diverged from the natural greedy run")
     # the short event the CPU oracle replays afterwards (rank 0): tokens and per-cycle acceptance of this very mount
     sample_run = short_event(engine, 0, prompt, 40)
+    # the control of that replay (one GPU): the same event on the kernel-per-operator path, whose operators agree with
+    # the oracle bit for bit at operator level - what the model's own chaos does to a token sequence
+    control_run = None
+    if world == 1 and info["target_decode_stack"] and os.environ.get("NERVE_B200_DECODE_STACK", "1") != "0":
+        engine.set_decode_stack(False)
+        control_run = short_event(engine, 0, prompt, 40)
+        engine.set_decode_stack(True)
 
     # ---- value: exactly K cycles, device-timed, clocks sampled meanwhile
     teacher_long = None
@@ -491,6 +500,10 @@ def main():
             package.unmount()
         sample = cpu_cycle_sample(directory, seconds_budget=25.0 if world == 1 else 12.0, cuda_run=sample_run)
         line["parity"] = sample["parity"]
+        if control_run is not None:
+            control = cpu_cycle_sample(directory, seconds_budget=12.0, cuda_run=control_run)["parity"]
+            line["parity"]["control_kernel_per_operator_path"] = {key: control[key] for key in (
+                "tokens_compared", "cycles_compared", "tokens_equal", "accepted_equal", "divergences", "violations", "largest_gap_at_a_divergence")}
         if world == 1:
             line["cpu_baseline"] = {
                 "value": sample["tokens_per_s"], "unit": UNIT, "cores": cores, "kind": "port",
