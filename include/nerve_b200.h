@@ -213,6 +213,7 @@ int32_t nerve_b200_engine_set_decode_stack(nerve_b200_engine *engine, int32_t en
 /* Profiling aid (no reference counterpart): with profiling on, CTA 0 of the persistent kernel stamps the GPU's
  * nanosecond timer at each layer's start and after each staging step, matrix or attention step and grid barrier
  * of the layer, in program order; this copies the stamps of the last target-stack launch, [layers][32].
+ * Row 0 also carries the kernel's entry (index 16) and the end of its last layer (index 30).
  * *out_count = stamps available. */
 int32_t nerve_b200_engine_decode_stack_timing(nerve_b200_engine *engine, uint64_t *out_stamps, size_t max_stamps, size_t *out_count);
 /* Cycle log rows: {stream_id, start_tick, accepted, committed, emitted_count, width, emitted[8], targets[8]} as u64. */

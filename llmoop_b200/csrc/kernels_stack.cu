@@ -1156,6 +1156,11 @@ __device__ __noinline__ PassResult consume_pass(const PassRing ring, uint32_t sl
 template <int HD, int GROUP, bool EXCHANGE>
 __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const StackArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
+    if (a.buffers.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        a.buffers.timing[16] = now;
+    }
     constexpr int QL = AttentionTeam<GROUP>::QL;
     const StackShape &shape = a.shape;
     const int lanes = a.lanes, staged = lanes < 8 ? lanes : 8;
@@ -1571,6 +1576,11 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
         }
     }
 
+    if (a.buffers.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        a.buffers.timing[30] = now;
+    }
     // The last CTA to leave rearms the barrier words for the next launch (every CTA has passed its last barrier
     // before it counts itself out).
     if (threadIdx.x == 0) {
