@@ -612,7 +612,7 @@ __device__ __forceinline__ float *attention_stats(float *scratch, int lanes, int
 
 // Log-sum-exp merge of the split partials of one (lane, q head) row by one warp: lane s of the warp weighs split s
 // (s + 32, ...), every lane owns HD / 32 consecutive output dims, and the weighted rows are summed in split order,
-// the loads of eight splits in flight at a time.  The result goes out as fp16 in fragment order.
+// the loads of twelve or sixteen splits in flight at a time.  The result goes out as fp16 in fragment order.
 template <int HD>
 __device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32_t capacity, uint32_t tick, int query_lane, int head) {
     constexpr int VEC = HD / 32;
@@ -628,10 +628,11 @@ __device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32
     uint16_t *__restrict__ out_fragments = job.out_fragments;
     const int last = splits - 1;
     // Rows beyond the last split are read as the last split again and weigh nothing, so no load is predicated.
-    float part[8][VEC];
+    constexpr int CHUNK = VEC == 4 ? 12 : 16;  // rows in flight at a time (as many as the registers hold): contexts of up to 768 tokens merge in one round trip
+    float part[CHUNK][VEC];
     auto fetch = [&](int first) {
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < CHUNK; u++) {
             const float *source = mine + static_cast<size_t>(first + u < last ? first + u : last) * HD;
             if (VEC == 4) {
                 const float4 raw = __ldcg(reinterpret_cast<const float4 *>(source));
@@ -649,13 +650,13 @@ __device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32
     for (int v = 0; v < VEC; v++) acc[v] = 0.0f;
     auto accumulate = [&](int first, float weight) {
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
+        for (int u = 0; u < CHUNK; u++) {
             const float w = __shfl_sync(0xffffffffu, weight, (first + u) & 31);
 #pragma unroll
             for (int v = 0; v < VEC; v++) acc[v] += part[u][v] * w;
         }
     };
-    // the statistics of the first 32 splits and the first eight rows are requested together
+    // the statistics of the first 32 splits and the first rows are requested together
     float2 pair = __ldcg(stats + (lane_id < last ? lane_id : last));
     fetch(0);
     float maximum = lane_id < splits ? pair.x : -3.4028234663852886e38f;
@@ -666,7 +667,7 @@ __device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32
     float denominator = lane_id < splits ? pair.y * weight : 0.0f;
     accumulate(0, weight);
 #pragma unroll 1
-    for (int s = 8; s < splits; s += 8) {
+    for (int s = CHUNK; s < splits; s += CHUNK) {
         if ((s & 31) == 0) {  // the next 32 splits: this lane weighs split s + lane
             pair = __ldcg(stats + (s + lane_id < last ? s + lane_id : last));
             weight = s + lane_id < splits ? expf(pair.x - maximum) : 0.0f;
