@@ -1151,6 +1151,89 @@ __device__ __noinline__ PassResult consume_pass(const PassRing ring, uint32_t sl
     return result;
 }
 
+// The gate/up step when a stage holds two steps of two blocks per tile slot (gate and up of one group of K each):
+// the slot's two warps take one step each and multiply BOTH its blocks - gate and up rows against the same
+// activations, read once - with the sixteen MMAs interleaved in eight accumulation chains.  Returns the warp's partial
+// sums of the gate rows (acc) and of the up rows (second).
+struct PairResult {
+    float acc[4], second[4];
+    uint32_t slot, parity;
+};
+struct PairOperands {
+    uint4 low_a, high_a, low_b, high_b;  // this thread's nibbles of rows g and g + 8: gate block, up block
+    uint4 b[4];                          // its B fragments of the group
+    uint32_t scales_a, scales_b;
+};
+template <int WORD>
+__device__ __forceinline__ void pair_word(const PairOperands &p, float (&ca)[4][4], float (&cb)[4][4]) {
+    const uint4 &b = p.b[WORD];
+    const uint32_t wa = WORD == 0 ? p.low_a.x : (WORD == 1 ? p.low_a.y : (WORD == 2 ? p.low_a.z : p.low_a.w));
+    const uint32_t wb = WORD == 0 ? p.high_a.x : (WORD == 1 ? p.high_a.y : (WORD == 2 ? p.high_a.z : p.high_a.w));
+    const uint32_t va = WORD == 0 ? p.low_b.x : (WORD == 1 ? p.low_b.y : (WORD == 2 ? p.low_b.z : p.low_b.w));
+    const uint32_t vb = WORD == 0 ? p.high_b.x : (WORD == 1 ? p.high_b.y : (WORD == 2 ? p.high_b.z : p.high_b.w));
+    mma_f16_16816(ca[2 * (WORD & 1)], nibbles_low(wa), nibbles_low(wb), nibbles_high(wa), nibbles_high(wb), b.x, b.y);
+    mma_f16_16816(cb[2 * (WORD & 1)], nibbles_low(va), nibbles_low(vb), nibbles_high(va), nibbles_high(vb), b.x, b.y);
+    const uint32_t upper_wa = wa >> 8, upper_wb = wb >> 8, upper_va = va >> 8, upper_vb = vb >> 8;
+    mma_f16_16816(ca[2 * (WORD & 1) + 1], nibbles_low(upper_wa), nibbles_low(upper_wb), nibbles_high(upper_wa), nibbles_high(upper_wb), b.z, b.w);
+    mma_f16_16816(cb[2 * (WORD & 1) + 1], nibbles_low(upper_va), nibbles_low(upper_vb), nibbles_high(upper_va), nibbles_high(upper_vb), b.z, b.w);
+}
+__device__ __forceinline__ void pair_finish(uint32_t scales, const float (&chains)[4][4], float (&acc)[4]) {
+    const float sa = __uint_as_float(scales << 16), sb = __uint_as_float(scales & 0xffff0000u);
+    acc[0] = fmaf(sa, (chains[0][0] + chains[1][0]) + (chains[2][0] + chains[3][0]), acc[0]);
+    acc[1] = fmaf(sa, (chains[0][1] + chains[1][1]) + (chains[2][1] + chains[3][1]), acc[1]);
+    acc[2] = fmaf(sb, (chains[0][2] + chains[1][2]) + (chains[2][2] + chains[3][2]), acc[2]);
+    acc[3] = fmaf(sb, (chains[0][3] + chains[1][3]) + (chains[2][3] + chains[3][3]), acc[3]);
+}
+// `first_block`: byte offset of the gate block of the warp's slot inside a step; `first_scales`: of its scale row;
+// `mine`: which of the stage's two steps this warp takes; `x`: its B fragments of that step's group in the first stage.
+__device__ __noinline__ PairResult consume_pass_pairs(const PassRing ring, uint32_t slot, uint32_t parity, int steps, bool active, int mine, uint32_t step_bytes,
+                                                      uint32_t first_block, uint32_t first_scales, uint32_t x, uint32_t x_stage_step, uint32_t word_stride,
+                                                      int *error_flag) {
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, second[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const int lane = threadIdx.x & 31;
+    for (int step = 0; step < steps; step += 2) {
+        const uint32_t stage_address = ring.ring + slot * ring.stage_bytes;
+        wait_stage(ring.full + slot * 8, parity, error_flag);
+        if (active && step + mine < steps) {
+            const uint32_t base = stage_address + static_cast<uint32_t>(mine) * step_bytes;
+            PairOperands p;
+            p.b[0] = shared_load16<0>(x);
+            p.b[1] = shared_load16<0>(x + word_stride);
+            p.b[2] = shared_load16<0>(x + 2 * word_stride);
+            p.b[3] = shared_load16<0>(x + 3 * word_stride);
+            p.low_a = shared_load16<0>(base + first_block);
+            p.high_a = shared_load16<512>(base + first_block);
+            p.low_b = shared_load16<UNIT_BYTES>(base + first_block);
+            p.high_b = shared_load16<UNIT_BYTES + 512>(base + first_block);
+            p.scales_a = shared_load4(base + first_scales);
+            p.scales_b = shared_load4(base + first_scales + UNIT_SCALE_BYTES);
+            float ca[4][4] = {}, cb[4][4] = {};
+            pair_word<0>(p, ca, cb);
+            pair_word<1>(p, ca, cb);
+            pair_word<2>(p, ca, cb);
+            pair_word<3>(p, ca, cb);
+            pair_finish(p.scales_a, ca, acc);
+            pair_finish(p.scales_b, cb, second);
+            x += x_stage_step;
+        }
+        __syncwarp();
+        if (lane == 0) mbarrier_arrive(ring.empty + slot * 8);
+        if (++slot == ring.stages) {
+            slot = 0;
+            parity ^= 1u;
+        }
+    }
+    PairResult result;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        result.acc[i] = acc[i];
+        result.second[i] = second[i];
+    }
+    result.slot = slot;
+    result.parity = parity;
+    return result;
+}
+
 // ------------------------------------------------------------------------------------------ the kernel
 
 // EXCHANGE: the tensor-parallel form (o and down leave partial sums that are exchanged between the ranks).
@@ -1360,6 +1443,12 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
         }
     }
     consumer_sync();
+    // gate/up in pairs (consume_pass_pairs): when a stage is two steps of (gate, up) blocks per tile slot and the scratch
+    // has room for the up rows' partial sums behind the normalised rows
+    const size_t pair_reduce_offset = static_cast<size_t>(staged) * shape.hidden * 2;
+    const bool pairs_enabled = info[2].rt == 2 && info[2].width == 2 && a.steps_per_stage == 2 && !(a.debug_flags & (1 | 8)) &&
+                               pair_reduce_offset + 2 * CONSUMER_WARPS * 128 * sizeof(float) <= a.scratch_bytes;
+    float *reduce_second = reinterpret_cast<float *>(smem_raw + pair_reduce_offset);
     const int ge = g < staged ? g : 0;  // lanes beyond the batch recompute lane 0; their results are dropped
     const uint32_t fragment_lane = static_cast<uint32_t>(__cvta_generic_to_shared(fragments)) + static_cast<uint32_t>(ge * 4 + j) * 16u;
     const uint32_t word_stride = static_cast<uint32_t>(staged) * 4 * sizeof(uint4);  // between the four words of a group
@@ -1422,13 +1511,36 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                 const uint32_t x_step = static_cast<uint32_t>(pi.width / pi.rt) * group_stride;
                 const uint32_t x_start = pi.streamed ? static_cast<uint32_t>(index_in_slot) * group_stride + lane_fragment
                                                      : fragment_lane + static_cast<uint32_t>(index_in_slot / pi.rt) * group_stride;
-                const PassResult done = consume_pass(pass_ring, ring_slot, ring_parity, slice_slot, slice_parity, pi.steps, a.steps_per_stage | ((a.debug_flags & 8) ? 256 : 0), active_steps,
-                                                     static_cast<uint32_t>(present * pi.width * UNIT_TOTAL),
-                                                     static_cast<uint32_t>(warp) * UNIT_BYTES + static_cast<uint32_t>(lane) * 16u,
-                                                     static_cast<uint32_t>(present * pi.width) * UNIT_BYTES + static_cast<uint32_t>(warp) * UNIT_SCALE_BYTES +
-                                                         static_cast<uint32_t>(g) * 4u,
-                                                     x_start, x_step, pi.streamed != 0, word_stride, error_flag, payload_address,
-                                                     static_cast<uint32_t>(4 * grid * 16), payload_rounds);
+                const bool pair_mode = phase == 2 && pairs_enabled;
+                PassResult done;
+                float second_acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (pair_mode) {
+                    const PairResult pairs = consume_pass_pairs(pass_ring, ring_slot, ring_parity, pi.steps, active, index_in_slot,
+                                                                static_cast<uint32_t>(present * pi.width * UNIT_TOTAL),
+                                                                static_cast<uint32_t>(slot_of_warp * 2) * UNIT_BYTES + static_cast<uint32_t>(lane) * 16u,
+                                                                static_cast<uint32_t>(present * pi.width) * UNIT_BYTES +
+                                                                    static_cast<uint32_t>(slot_of_warp * 2) * UNIT_SCALE_BYTES + static_cast<uint32_t>(g) * 4u,
+                                                                fragment_lane + static_cast<uint32_t>(index_in_slot) * group_stride, 2 * group_stride, word_stride,
+                                                                error_flag);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        done.acc[i] = pairs.acc[i];
+                        second_acc[i] = pairs.second[i];
+                        done.payload[i] = 0;
+                    }
+                    done.slot = pairs.slot;
+                    done.parity = pairs.parity;
+                    done.slice_slot = slice_slot;
+                    done.slice_parity = slice_parity;
+                } else {
+                    done = consume_pass(pass_ring, ring_slot, ring_parity, slice_slot, slice_parity, pi.steps, a.steps_per_stage | ((a.debug_flags & 8) ? 256 : 0), active_steps,
+                                        static_cast<uint32_t>(present * pi.width * UNIT_TOTAL),
+                                        static_cast<uint32_t>(warp) * UNIT_BYTES + static_cast<uint32_t>(lane) * 16u,
+                                        static_cast<uint32_t>(present * pi.width) * UNIT_BYTES + static_cast<uint32_t>(warp) * UNIT_SCALE_BYTES +
+                                            static_cast<uint32_t>(g) * 4u,
+                                        x_start, x_step, pi.streamed != 0, word_stride, error_flag, payload_address,
+                                        static_cast<uint32_t>(4 * grid * 16), payload_rounds);
+                }
                 ring_slot = done.slot;
                 ring_parity = done.parity;
                 slice_slot = done.slice_slot;
@@ -1439,6 +1551,11 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                 float *mine = reduce + static_cast<size_t>((reduce_parity * CONSUMER_WARPS + warp) * 128);
                 *reinterpret_cast<float2 *>(mine + g * 8 + 2 * j) = make_float2(acc[0], acc[1]);
                 *reinterpret_cast<float2 *>(mine + (g + 8) * 8 + 2 * j) = make_float2(acc[2], acc[3]);
+                if (pair_mode) {
+                    float *up = reduce_second + static_cast<size_t>((reduce_parity * CONSUMER_WARPS + warp) * 128);
+                    *reinterpret_cast<float2 *>(up + g * 8 + 2 * j) = make_float2(second_acc[0], second_acc[1]);
+                    *reinterpret_cast<float2 *>(up + (g + 8) * 8 + 2 * j) = make_float2(second_acc[2], second_acc[3]);
+                }
                 consumer_sync();
                 const float *sums = reduce + static_cast<size_t>(reduce_parity * CONSUMER_WARPS * 128);
                 reduce_parity ^= 1;
@@ -1449,7 +1566,12 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                     const int tile = static_cast<int>(blockIdx.x) + (pass * pi.slots + slot) * grid;
                     const float *src = sums + static_cast<size_t>(slot * pi.width) * 128 + epilogue_row * 8 + epilogue_m;
                     float first = 0.0f, second = 0.0f;
-                    if (pi.rt == 2) {
+                    if (pair_mode) {
+                        // both warps of the slot hold gate sums (here) and up sums (in the second array), of alternate groups
+                        const float *up = src + (reduce_second - reduce);
+                        first = src[0] + src[128];
+                        second = up[0] + up[128];
+                    } else if (pi.rt == 2) {
                         for (int w = 0; w < pi.width; w += 2) {
                             first += src[w * 128];
                             second += src[(w + 1) * 128];
