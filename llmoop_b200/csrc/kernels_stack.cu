@@ -1093,17 +1093,19 @@ struct PassRing {  // where the stages are and where this warp stands in them
     uint32_t ring, full, empty, stages, stage_bytes;
     uint32_t slices, slice_full, slice_empty, slice_slots, slice_bytes;
 };
+template <bool X_IN_SLICE, int PER_STAGE>
 __device__ __noinline__ PassResult consume_pass(const PassRing ring, uint32_t slot, uint32_t parity, uint32_t slice_slot, uint32_t slice_parity,
-                                                int steps, int steps_per_stage, int active_steps, uint32_t step_bytes, uint32_t weight_offset,
-                                                uint32_t scale_offset, uint32_t x, uint32_t x_step, bool x_in_slice, uint32_t word_stride,
+                                                int steps, int active_steps, uint32_t step_bytes, uint32_t weight_offset,
+                                                uint32_t scale_offset, uint32_t x, uint32_t x_step, uint32_t word_stride,
                                                 int *error_flag, const uint16_t *payload, uint32_t payload_stride, int payload_rounds) {
+    constexpr bool x_in_slice = X_IN_SLICE;
+    constexpr int steps_per_stage = PER_STAGE;
+    constexpr bool handshake = true;
     uint32_t residual[4];
 #pragma unroll
     for (int round = 0; round < 4; round++) residual[round] = round < payload_rounds ? __ldcg(payload + static_cast<size_t>(round) * payload_stride) : 0;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     const int lane = threadIdx.x & 31;
-    const bool handshake = (steps_per_stage & 256) == 0;  // timing probe: 256 = run on whatever the ring holds
-    steps_per_stage &= 255;
     for (int step = 0; step < steps; step += steps_per_stage) {
         const uint32_t stage_address = ring.ring + slot * ring.stage_bytes;
         const uint32_t slice_address = ring.slices + slice_slot * ring.slice_bytes;
@@ -1118,7 +1120,7 @@ __device__ __noinline__ PassResult consume_pass(const PassRing ring, uint32_t sl
             UnitOperands u;
             unit_load(u, stage_address + weight_offset, stage_address + scale_offset, x_first, word_stride);
             unit_single(u, acc);
-            if (here == 2) {
+            if (PER_STAGE == 2 && here == 2) {
                 unit_load(u, stage_address + step_bytes + weight_offset, stage_address + step_bytes + scale_offset, x_first + x_step, word_stride);
                 unit_single(u, acc);
             }
@@ -1310,7 +1312,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     __syncthreads();
 
     if (warp >= CONSUMER_WARPS) {
-        if (lane == 0 && !(a.debug_flags & 8)) {
+        if (lane == 0) {
             if (warp == CONSUMER_WARPS) produce_weights(a, info, ring);
             else if (warp == CONSUMER_WARPS + 1) produce_activations(a, info, ring, staged);
             else if (warp == CONSUMER_WARPS + 2 && a.prefetch_stages > 0) produce_prefetches(a, info, ring);
@@ -1446,7 +1448,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     // gate/up in pairs (consume_pass_pairs): when a stage is two steps of (gate, up) blocks per tile slot and the scratch
     // has room for the up rows' partial sums behind the normalised rows
     const size_t pair_reduce_offset = static_cast<size_t>(staged) * shape.hidden * 2;
-    const bool pairs_enabled = info[2].rt == 2 && info[2].width == 2 && a.steps_per_stage == 2 && !(a.debug_flags & (1 | 8)) &&
+    const bool pairs_enabled = info[2].rt == 2 && info[2].width == 2 && a.steps_per_stage == 2 && !(a.debug_flags & 1) &&
                                pair_reduce_offset + 2 * CONSUMER_WARPS * 128 * sizeof(float) <= a.scratch_bytes;
     float *reduce_second = reinterpret_cast<float *>(smem_raw + pair_reduce_offset);
     const int ge = g < staged ? g : 0;  // lanes beyond the batch recompute lane 0; their results are dropped
@@ -1533,13 +1535,26 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                     done.slice_slot = slice_slot;
                     done.slice_parity = slice_parity;
                 } else {
-                    done = consume_pass(pass_ring, ring_slot, ring_parity, slice_slot, slice_parity, pi.steps, a.steps_per_stage | ((a.debug_flags & 8) ? 256 : 0), active_steps,
-                                        static_cast<uint32_t>(present * pi.width * UNIT_TOTAL),
-                                        static_cast<uint32_t>(warp) * UNIT_BYTES + static_cast<uint32_t>(lane) * 16u,
-                                        static_cast<uint32_t>(present * pi.width) * UNIT_BYTES + static_cast<uint32_t>(warp) * UNIT_SCALE_BYTES +
-                                            static_cast<uint32_t>(g) * 4u,
-                                        x_start, x_step, pi.streamed != 0, word_stride, error_flag, payload_address,
-                                        static_cast<uint32_t>(4 * grid * 16), payload_rounds);
+                    const uint32_t step_bytes = static_cast<uint32_t>(present * pi.width * UNIT_TOTAL);
+                    const uint32_t weight_offset = static_cast<uint32_t>(warp) * UNIT_BYTES + static_cast<uint32_t>(lane) * 16u;
+                    const uint32_t scale_offset = static_cast<uint32_t>(present * pi.width) * UNIT_BYTES + static_cast<uint32_t>(warp) * UNIT_SCALE_BYTES +
+                                                  static_cast<uint32_t>(g) * 4u;
+                    const uint32_t payload_stride = static_cast<uint32_t>(4 * grid * 16);
+                    if (a.steps_per_stage == 2) {
+                        done = pi.streamed ? consume_pass<true, 2>(pass_ring, ring_slot, ring_parity, slice_slot, slice_parity, pi.steps, active_steps, step_bytes,
+                                                                   weight_offset, scale_offset, x_start, x_step, word_stride, error_flag, payload_address,
+                                                                   payload_stride, payload_rounds)
+                                           : consume_pass<false, 2>(pass_ring, ring_slot, ring_parity, slice_slot, slice_parity, pi.steps, active_steps, step_bytes,
+                                                                    weight_offset, scale_offset, x_start, x_step, word_stride, error_flag, payload_address,
+                                                                    payload_stride, payload_rounds);
+                    } else {
+                        done = pi.streamed ? consume_pass<true, 1>(pass_ring, ring_slot, ring_parity, slice_slot, slice_parity, pi.steps, active_steps, step_bytes,
+                                                                   weight_offset, scale_offset, x_start, x_step, word_stride, error_flag, payload_address,
+                                                                   payload_stride, payload_rounds)
+                                           : consume_pass<false, 1>(pass_ring, ring_slot, ring_parity, slice_slot, slice_parity, pi.steps, active_steps, step_bytes,
+                                                                    weight_offset, scale_offset, x_start, x_step, word_stride, error_flag, payload_address,
+                                                                    payload_stride, payload_rounds);
+                    }
                 }
                 ring_slot = done.slot;
                 ring_parity = done.parity;
