@@ -38,7 +38,7 @@ EVENT_TOKENS = 256
 DRAFTS = 3
 METRIC = "accepted tokens/s (8B INT4, MTP k=3)"
 UNIT = "tokens/s"
-STACK_TRAFFIC_RATIO = 1.121  # DRAM bytes over algorithmic bytes of a four-layer verify launch (ncu; summary under profiles/)
+STACK_TRAFFIC_RATIO = 1.134  # DRAM bytes over algorithmic bytes of a four-layer verify launch (ncu; summary under profiles/)
 NOMINAL_HBM_GBS = 8000.0
 
 
