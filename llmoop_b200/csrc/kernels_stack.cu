@@ -1448,8 +1448,10 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
     // gate/up in pairs (consume_pass_pairs): when a stage is two steps of (gate, up) blocks per tile slot and the scratch
     // has room for the up rows' partial sums behind the normalised rows
     const size_t pair_reduce_offset = static_cast<size_t>(staged) * shape.hidden * 2;
+    // (two copies, alternating like the main array, when the step takes several passes)
+    const int pair_copies = info[2].passes > 1 ? 2 : 1;
     const bool pairs_enabled = info[2].rt == 2 && info[2].width == 2 && a.steps_per_stage == 2 && !(a.debug_flags & 1) &&
-                               pair_reduce_offset + 2 * CONSUMER_WARPS * 128 * sizeof(float) <= a.scratch_bytes;
+                               pair_reduce_offset + pair_copies * CONSUMER_WARPS * 128 * sizeof(float) <= a.scratch_bytes;
     float *reduce_second = reinterpret_cast<float *>(smem_raw + pair_reduce_offset);
     const int ge = g < staged ? g : 0;  // lanes beyond the batch recompute lane 0; their results are dropped
     const uint32_t fragment_lane = static_cast<uint32_t>(__cvta_generic_to_shared(fragments)) + static_cast<uint32_t>(ge * 4 + j) * 16u;
@@ -1567,12 +1569,13 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                 *reinterpret_cast<float2 *>(mine + g * 8 + 2 * j) = make_float2(acc[0], acc[1]);
                 *reinterpret_cast<float2 *>(mine + (g + 8) * 8 + 2 * j) = make_float2(acc[2], acc[3]);
                 if (pair_mode) {
-                    float *up = reduce_second + static_cast<size_t>((reduce_parity * CONSUMER_WARPS + warp) * 128);
+                    float *up = reduce_second + static_cast<size_t>(((pair_copies == 2 ? reduce_parity : 0) * CONSUMER_WARPS + warp) * 128);
                     *reinterpret_cast<float2 *>(up + g * 8 + 2 * j) = make_float2(second_acc[0], second_acc[1]);
                     *reinterpret_cast<float2 *>(up + (g + 8) * 8 + 2 * j) = make_float2(second_acc[2], second_acc[3]);
                 }
                 consumer_sync();
                 const float *sums = reduce + static_cast<size_t>(reduce_parity * CONSUMER_WARPS * 128);
+                const float *second_sums = reduce_second + static_cast<size_t>((pair_copies == 2 ? reduce_parity : 0) * CONSUMER_WARPS * 128);
                 reduce_parity ^= 1;
 #pragma unroll 1
                 for (int round = 0; round < 4; round++) {
@@ -1583,7 +1586,7 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                     float first = 0.0f, second = 0.0f;
                     if (pair_mode) {
                         // both warps of the slot hold gate sums (here) and up sums (in the second array), of alternate groups
-                        const float *up = src + (reduce_second - reduce);
+                        const float *up = second_sums + static_cast<size_t>(slot * pi.width) * 128 + epilogue_row * 8 + epilogue_m;
                         first = src[0] + src[128];
                         second = up[0] + up[128];
                     } else if (pi.rt == 2) {
@@ -1744,13 +1747,17 @@ bool plan_smem_for(const StackShape &shape, int lanes, int grid, StackPlanSmem *
     const MatrixSchedule o = stack_schedule(shape.hidden >> 4, q_width >> 7, 1, grid);
     const MatrixSchedule down = stack_schedule(shape.hidden >> 4, shape.ffn >> 7, 1, grid);
     const int slice_groups = o.width > down.width ? o.width : down.width;
-    // two steps per stage while the slices of a stage stay small: fewer hand-overs, two independent blocks per warp
-    const int steps_per_stage = staged <= 4 ? 2 : 1;
+    // two steps per stage: fewer hand-overs, two blocks per warp and wait, and the gate/up step in pairs - for every
+    // lane count alike, so that the order of a lane's additions does not depend on how many lanes share its launch
+    const int steps_per_stage = 2;
     const size_t slice = static_cast<size_t>(steps_per_stage) * slice_groups * staged * 256;
     size_t scratch = static_cast<size_t>(staged) * shape.hidden * 2;  // fragments of a normalised row set
     const size_t teams = 4 * attention_team_bytes<HD>();
     if (teams > scratch) scratch = teams;
     if (2 * slice > scratch) scratch = 2 * slice;
+    // the up rows' partial sums of the gate/up pairs sit behind the normalised rows (one copy at least)
+    const size_t pairs = static_cast<size_t>(staged) * shape.hidden * 2 + CONSUMER_WARPS * 128 * sizeof(float);
+    if (pairs > scratch) scratch = pairs;
     scratch = (scratch + 127) & ~static_cast<size_t>(127);
     int slice_slots = static_cast<int>(scratch / slice);
     if (slice_slots > MAX_STAGES) slice_slots = MAX_STAGES;
