@@ -793,7 +793,7 @@ void Engine::project_and_sample(const uint16_t *normalized, const std::string &p
                   label);
         } else {
             check(launch_linear_bf16(normalized, table + static_cast<size_t>(first) * hidden, logits_.ptr, nullptr, lanes, count, hidden, EPILOGUE_F32_SCALED, scale,
-                                     cuda_stream_),
+                                     cuda_stream_, static_cast<int *>(kernel_error_.ptr)),
                   label);
         }
     };
@@ -1055,7 +1055,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                     profile_end();
                 } else {
                     check(launch_linear_bf16(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(w.tensor)), partial, nullptr, lanes,
-                                             static_cast<int>(w.n), static_cast<int>(w.k), EPILOGUE_F32_SCALED, 1.0f, st),
+                                             static_cast<int>(w.n), static_cast<int>(w.k), EPILOGUE_F32_SCALED, 1.0f, st, static_cast<int *>(kernel_error_.ptr)),
                           "linear_bf16 (row-parallel)");
                 }
                 tp_all_reduce(partial, static_cast<size_t>(lanes) * w.n);
@@ -1145,7 +1145,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
                               "linear_bf16 (streamed)");
                     } else {
                         check(launch_linear_bf16(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(w.tensor)), ptr(op.outputs[branch]), nullptr,
-                                                 lanes, static_cast<int>(w.n), static_cast<int>(w.k), EPILOGUE_BF16, 1.0f, st),
+                                                 lanes, static_cast<int>(w.n), static_cast<int>(w.k), EPILOGUE_BF16, 1.0f, st, static_cast<int *>(kernel_error_.ptr)),
                               "linear_bf16");
                     }
                 } else if (w.storage == TensorStorage::INT4_CT) {
@@ -1169,7 +1169,7 @@ void Engine::run_component(const ComponentPlan &plan, int kv_index, int lanes, c
             if (w.storage == TensorStorage::BF16) {
                 check(launch_linear_bf16(u16(op.inputs[0]), static_cast<const uint16_t *>(weight(w.tensor)), ptr(op.outputs[0]),
                                          u16(op.residual_input), lanes, static_cast<int>(w.n), static_cast<int>(w.k),
-                                         EPILOGUE_RESIDUAL_ROUNDED, 1.0f, st),
+                                         EPILOGUE_RESIDUAL_ROUNDED, 1.0f, st, static_cast<int *>(kernel_error_.ptr)),
                       "linear_residual_bf16");
             } else if (w.storage == TensorStorage::FP8_BLOCK) {
                 check(launch_linear_fp8(static_cast<const uint8_t *>(ptr(op.inputs[0])), static_cast<const float *>(ptr(op.inputs[1])),

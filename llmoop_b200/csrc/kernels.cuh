@@ -55,7 +55,7 @@ enum LinearEpilogue {
 
 // y[m][n] = sum_k x[m][k] * W[n][k], bf16 weights.
 cudaError_t launch_linear_bf16(const uint16_t *x, const uint16_t *w, void *y, const uint16_t *residual, int lanes,
-                               int n, int k, int epilogue, float scale, cudaStream_t stream);
+                               int n, int k, int epilogue, float scale, cudaStream_t stream, int *error_flag = nullptr);
 // y = bf16( silu_bf16(bf16(x.Wg)) * bf16(x.Wu) )
 cudaError_t launch_linear_silu_multiply_bf16(const uint16_t *x, const uint16_t *wg, const uint16_t *wu, uint16_t *y,
                                              int lanes, int n, int k, cudaStream_t stream);
@@ -123,6 +123,10 @@ cudaError_t launch_output_projection(const uint16_t *x, const void *streamed_tab
 // launch_linear_int4 (EPILOGUE_F32_SCALED writes f32 * scale).  error_flag (optional device word) is set to 3 if a
 // bounded wait for the tensor core expires.
 bool linear_int4_gemm_supported(int lanes, int n, int k);
+// bf16 weights, batches of 16 lanes and more (tcgen05): called by launch_linear_bf16.
+bool linear_bf16_gemm_supported(int lanes, int n, int k);
+cudaError_t launch_linear_bf16_gemm(const uint16_t *x, const uint16_t *w, void *y, const uint16_t *residual, int lanes, int n, int k, int epilogue,
+                                    float scale, int *error_flag, cudaStream_t stream);
 cudaError_t launch_linear_int4_gemm(const uint16_t *x, const uint32_t *qweight, const uint16_t *scales, void *y, const uint16_t *residual, int lanes,
                                     int n, int k, int epilogue, float scale, int *error_flag, cudaStream_t stream);
 

@@ -107,8 +107,10 @@ linear_bf16_kernel(const uint16_t *__restrict__ x, const uint16_t *__restrict__ 
 }
 
 cudaError_t launch_linear_bf16(const uint16_t *x, const uint16_t *w, void *y, const uint16_t *residual, int lanes,
-                               int n, int k, int epilogue, float scale, cudaStream_t stream) {
+                               int n, int k, int epilogue, float scale, cudaStream_t stream, int *error_flag) {
     if (lanes <= 0) return cudaSuccess;
+    // wide batches: the tensor-core GEMM (weights read once per 64 lanes instead of once per 8)
+    if (linear_bf16_gemm_supported(lanes, n, k)) return launch_linear_bf16_gemm(x, w, y, residual, lanes, n, k, epilogue, scale, error_flag, stream);
     constexpr int ROWS = 4;
     int row_ctas = (n + 8 * ROWS - 1) / (8 * ROWS);
     if (lanes <= 4) {

@@ -119,7 +119,7 @@ def test_linear_int4_silu_pair_matches_oracle(lanes, n, k):
     assert worst <= 3.0 and exact > 0.93, (exact, worst)
 
 
-@pytest.mark.parametrize("lanes", [1, 4, 9])
+@pytest.mark.parametrize("lanes", [1, 4, 9, 16, 64, 160])  # 16 lanes and more: the tensor-core GEMM
 def test_linear_bf16_and_logits_match_oracle(lanes):
     import torch
 
