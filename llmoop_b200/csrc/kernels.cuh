@@ -127,6 +127,9 @@ bool linear_int4_gemm_supported(int lanes, int n, int k);
 bool linear_bf16_gemm_supported(int lanes, int n, int k);
 cudaError_t launch_linear_bf16_gemm(const uint16_t *x, const uint16_t *w, void *y, const uint16_t *residual, int lanes, int n, int k, int epilogue,
                                     float scale, int *error_flag, cudaStream_t stream);
+cudaError_t launch_linear_int4_gemm_multi(const uint16_t *x, int branches, const uint32_t *const *qweights, const uint16_t *const *scales, void *const *ys,
+                                          const int *ns, const uint16_t *residual, int lanes, int k, int epilogue, float scale, int *error_flag,
+                                          cudaStream_t stream);
 cudaError_t launch_linear_int4_gemm(const uint16_t *x, const uint32_t *qweight, const uint16_t *scales, void *y, const uint16_t *residual, int lanes,
                                     int n, int k, int epilogue, float scale, int *error_flag, cudaStream_t stream);
 

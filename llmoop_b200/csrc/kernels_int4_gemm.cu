@@ -78,13 +78,21 @@ __device__ __forceinline__ bool wait_barrier(uint32_t barrier, uint32_t parity, 
 
 struct GemmArgs {
     const uint16_t *x;
+    const uint32_t *qweights[3];  // up to three matrices that share the activations (q, k, v) in one launch:
+    const uint16_t *scale_rows[3];
+    void *ys[3];
+    int ns[3];
+    int first_tile[4];            // ... matrix b owns the row tiles first_tile[b] .. first_tile[b + 1] - 1 of the grid
+    const uint16_t *residual;
+    int lanes, k, epilogue;
+    float scale;
+    int *error_flag;
+};
+struct GemmMatrix {  // the matrix a CTA works on
     const uint32_t *qweight;
     const uint16_t *scales;
     void *y;
-    const uint16_t *residual;
-    int lanes, n, k, epilogue;
-    float scale;
-    int *error_flag;
+    int n;
 };
 
 __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const GemmArgs a) {
@@ -95,7 +103,14 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(barriers + 2);
     const uint32_t barrier_address = static_cast<uint32_t>(__cvta_generic_to_shared(barriers));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * GEMM_LANES, row0 = blockIdx.y * GEMM_ROWS;
+    int branch = 0;
+    while (branch < 2 && static_cast<int>(blockIdx.y) >= a.first_tile[branch + 1]) branch++;
+    GemmMatrix matrix;  // the same fields under the names the single-matrix kernel used: a.qweight, a.scales, a.y, a.n
+    matrix.qweight = a.qweights[branch];
+    matrix.scales = a.scale_rows[branch];
+    matrix.y = a.ys[branch];
+    matrix.n = a.ns[branch];
+    const int m0 = blockIdx.x * GEMM_LANES, row0 = (static_cast<int>(blockIdx.y) - a.first_tile[branch]) * GEMM_ROWS;
     const int groups = a.k >> 7, words_per_row = a.k >> 3;
 
     if (threadIdx.x == 0) {
@@ -116,12 +131,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
     // fetch roles: thread t turns the 64 nibbles of half `t & 1` of row `t >> 1` into eight 16-byte pieces, and
     // moves four 16-byte pieces of the activations
     const int fetch_row = threadIdx.x >> 1, fetch_half = threadIdx.x & 1;
-    const int weight_row = row0 + fetch_row < a.n ? row0 + fetch_row : a.n - 1;
-    const uint4 *weight_source = reinterpret_cast<const uint4 *>(a.qweight + static_cast<size_t>(weight_row) * words_per_row) + fetch_half * 2;
+    const int weight_row = row0 + fetch_row < matrix.n ? row0 + fetch_row : matrix.n - 1;
+    const uint4 *weight_source = reinterpret_cast<const uint4 *>(matrix.qweight + static_cast<size_t>(weight_row) * words_per_row) + fetch_half * 2;
     const uint32_t weight_offset = static_cast<uint32_t>((fetch_row >> 3) * GEMM_BLOCK_STRIDE + fetch_half * 8 * 128 + (fetch_row & 7) * 16);
     // accumulator roles: thread = row 32 * (warp & 3) + lane of the tile, columns 32 * (warp >> 2) .. + 31
     const int out_row = 32 * (warp & 3) + lane, column0 = 32 * (warp >> 2);
-    const uint16_t *scale_row = a.scales + static_cast<size_t>(row0 + out_row < a.n ? row0 + out_row : a.n - 1) * groups;
+    const uint16_t *scale_row = matrix.scales + static_cast<size_t>(row0 + out_row < matrix.n ? row0 + out_row : matrix.n - 1) * groups;
     float acc[32];
 #pragma unroll
     for (int i = 0; i < 32; i++) acc[i] = 0.0f;
@@ -213,19 +228,19 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
     if (alive && groups > 0) drain(groups - 1, (groups - 1) & 1);
 
     // ---- epilogue: this thread's row, 32 lanes
-    if (alive && row0 + out_row < a.n) {
+    if (alive && row0 + out_row < matrix.n) {
 #pragma unroll
         for (int i = 0; i < 32; i++) {
             const int m = m0 + column0 + i;
             if (m >= a.lanes) break;
-            const size_t index = static_cast<size_t>(m) * a.n + row0 + out_row;
+            const size_t index = static_cast<size_t>(m) * matrix.n + row0 + out_row;
             float sum = acc[i];
             if (a.epilogue == EPILOGUE_F32_SCALED) {
-                reinterpret_cast<float *>(a.y)[index] = sum * a.scale;
+                reinterpret_cast<float *>(matrix.y)[index] = sum * a.scale;
             } else {
                 if (a.epilogue == EPILOGUE_RESIDUAL_ROUNDED) sum = round_bf16(sum) + bf16_bits_to_f32(a.residual[index]);
                 else if (a.epilogue == EPILOGUE_RESIDUAL_F32) sum = sum + bf16_bits_to_f32(a.residual[index]);
-                reinterpret_cast<uint16_t *>(a.y)[index] = static_cast<uint16_t>(f32_to_bf16_bits(sum));
+                reinterpret_cast<uint16_t *>(matrix.y)[index] = static_cast<uint16_t>(f32_to_bf16_bits(sum));
             }
         }
     }
@@ -238,16 +253,42 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
 
 bool linear_int4_gemm_supported(int lanes, int n, int k) { return lanes >= GEMM_LANES && k % 128 == 0 && k >= 128 && n >= 1; }
 
-cudaError_t launch_linear_int4_gemm(const uint16_t *x, const uint32_t *qweight, const uint16_t *scales, void *y, const uint16_t *residual, int lanes,
-                                    int n, int k, int epilogue, float scale, int *error_flag, cudaStream_t stream) {
+cudaError_t launch_linear_int4_gemm_multi(const uint16_t *x, int branches, const uint32_t *const *qweights, const uint16_t *const *scales, void *const *ys,
+                                          const int *ns, const uint16_t *residual, int lanes, int k, int epilogue, float scale, int *error_flag,
+                                          cudaStream_t stream) {
     if (lanes <= 0) return cudaSuccess;
-    if (!linear_int4_gemm_supported(lanes, n, k)) return cudaErrorInvalidValue;
+    if (branches < 1 || branches > 3 || (residual != nullptr && branches != 1)) return cudaErrorInvalidValue;
+    GemmArgs args = {};
+    args.x = x;
+    int tiles = 0;
+    for (int b = 0; b < 3; b++) {
+        const int source = b < branches ? b : branches - 1;
+        if (b < branches && !linear_int4_gemm_supported(lanes, ns[b], k)) return cudaErrorInvalidValue;
+        args.qweights[b] = qweights[source];
+        args.scale_rows[b] = scales[source];
+        args.ys[b] = ys[source];
+        args.ns[b] = ns[source];
+        args.first_tile[b] = tiles;
+        if (b < branches) tiles += (ns[b] + GEMM_ROWS - 1) / GEMM_ROWS;
+    }
+    args.first_tile[3] = tiles;
+    for (int b = branches; b < 3; b++) args.first_tile[b] = tiles;  // no tile belongs to an absent matrix
+    args.residual = residual;
+    args.lanes = lanes;
+    args.k = k;
+    args.epilogue = epilogue;
+    args.scale = scale;
+    args.error_flag = error_flag;
     cudaError_t status = cudaFuncSetAttribute(linear_int4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_SMEM));
     if (status != cudaSuccess) return status;
-    GemmArgs args{x, qweight, scales, y, residual, lanes, n, k, epilogue, scale, error_flag};
-    dim3 grid((lanes + GEMM_LANES - 1) / GEMM_LANES, (n + GEMM_ROWS - 1) / GEMM_ROWS);
+    dim3 grid((lanes + GEMM_LANES - 1) / GEMM_LANES, tiles);
     linear_int4_gemm_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(args);
     return cudaGetLastError();
+}
+
+cudaError_t launch_linear_int4_gemm(const uint16_t *x, const uint32_t *qweight, const uint16_t *scales, void *y, const uint16_t *residual, int lanes,
+                                    int n, int k, int epilogue, float scale, int *error_flag, cudaStream_t stream) {
+    return launch_linear_int4_gemm_multi(x, 1, &qweight, &scales, &y, &n, residual, lanes, k, epilogue, scale, error_flag, stream);
 }
 
 }  // namespace nerve

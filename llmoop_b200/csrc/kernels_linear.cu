@@ -388,13 +388,13 @@ cudaError_t launch_linear_int4_multi(const uint16_t *x, int branches, const uint
     if (lanes <= 0) return cudaSuccess;
     if (k % 128 != 0 || branches < 1 || branches > 3) return cudaErrorInvalidValue;
     if (linear_int4_gemm_supported(lanes, ns[0], k)) {
-        // wide batches (prefill chunks, many-stream verify): one tcgen05 GEMM per matrix, the weights read once per 64 lanes
-        for (int b = 0; b < branches; b++) {
-            cudaError_t status = launch_linear_int4_gemm(x, qweights[b], scales[b], ys[b], branches == 1 ? residual : nullptr, lanes, ns[b], k, epilogue, 1.0f,
-                                                         error_flag, stream);
-            if (status != cudaSuccess) return status;
-        }
-        return cudaSuccess;
+        // wide batches (prefill chunks, many-stream verify): one tcgen05 GEMM launch for all the matrices that share
+        // the activations, the weights read once per 64 lanes
+        for (int b = 1; b < branches; b++)
+            if (!linear_int4_gemm_supported(lanes, ns[b], k)) return cudaErrorInvalidValue;
+        void *outputs[3] = {ys[0], branches > 1 ? ys[1] : nullptr, branches > 2 ? ys[2] : nullptr};
+        return launch_linear_int4_gemm_multi(x, branches, qweights, scales, outputs, ns, branches == 1 ? residual : nullptr, lanes, k, epilogue, 1.0f, error_flag,
+                                             stream);
     }
     Int4Launch params = {};
     params.branches = branches;
