@@ -26,18 +26,21 @@ namespace nerve {
 namespace {
 
 constexpr int GEMM_ROWS = 128;     // weight rows per CTA (MMA M)
-constexpr int GEMM_LANES = 64;     // lanes per CTA (MMA N)
+constexpr int GEMM_MIN_LANES = 64; // lanes per CTA (MMA N): 64, or 128 for batches of 128 lanes and more - the weights
+                                   // are then dequantised once per 128 lanes
 constexpr int GEMM_THREADS = 256;
 constexpr int GEMM_A_BYTES = GEMM_ROWS * 128 * 2;    // one group of a row block, bf16
-constexpr int GEMM_B_BYTES = GEMM_LANES * 128 * 2;
 constexpr int GEMM_BLOCK_STRIDE = 16 * 128;          // bytes between 8-row blocks: 16 core matrices of a group's K
 constexpr unsigned int GEMM_SPIN_LIMIT = 1u << 22;
-constexpr size_t GEMM_SMEM = 2 * (GEMM_A_BYTES + GEMM_B_BYTES) + 64;
+template <int LANES>
+constexpr size_t gemm_smem() { return 2 * (GEMM_A_BYTES + LANES * 128 * 2) + 64; }
 
 // 32-bit instruction descriptor of tcgen05.mma kind::f16: f32 accumulator (bits 4-5 = 1), A and B bf16 (bits 7-9 and
 // 10-12 = 1), both K-major (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
-constexpr uint32_t GEMM_INSTRUCTION = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(GEMM_LANES / 8) << 17) |
-                                      (static_cast<uint32_t>(GEMM_ROWS / 16) << 24);
+template <int LANES>
+constexpr uint32_t gemm_instruction() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(LANES / 8) << 17) | (static_cast<uint32_t>(GEMM_ROWS / 16) << 24);
+}
 
 // Shared-memory matrix descriptor, K-major without swizzle: start address / 16 in bits 0-13, the byte distance
 // between the two core matrices of a K = 16 step (128) / 16 in bits 16-29, the distance between 8-row blocks / 16 in
@@ -95,7 +98,9 @@ struct GemmMatrix {  // the matrix a CTA works on
     int n;
 };
 
+template <int GEMM_LANES>
 __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const GemmArgs a) {
+    constexpr int GEMM_B_BYTES = GEMM_LANES * 128 * 2;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *tile_a[2] = {smem, smem + GEMM_A_BYTES + GEMM_B_BYTES};
     uint8_t *tile_b[2] = {smem + GEMM_A_BYTES, smem + 2 * GEMM_A_BYTES + GEMM_B_BYTES};
@@ -118,8 +123,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(barrier_address + 8) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {  // 128 columns of tensor memory: two accumulators of 64 columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(tmem_slot))), "r"(128u)
+    if (warp == 0) {  // two accumulators of LANES columns of tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(tmem_slot))), "r"(static_cast<uint32_t>(2 * GEMM_LANES))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -134,12 +139,13 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
     const int weight_row = row0 + fetch_row < matrix.n ? row0 + fetch_row : matrix.n - 1;
     const uint4 *weight_source = reinterpret_cast<const uint4 *>(matrix.qweight + static_cast<size_t>(weight_row) * words_per_row) + fetch_half * 2;
     const uint32_t weight_offset = static_cast<uint32_t>((fetch_row >> 3) * GEMM_BLOCK_STRIDE + fetch_half * 8 * 128 + (fetch_row & 7) * 16);
-    // accumulator roles: thread = row 32 * (warp & 3) + lane of the tile, columns 32 * (warp >> 2) .. + 31
-    const int out_row = 32 * (warp & 3) + lane, column0 = 32 * (warp >> 2);
+    // accumulator roles: thread = row 32 * (warp & 3) + lane of the tile, one half of the tile's columns
+    constexpr int COLUMNS = GEMM_LANES / 2;
+    const int out_row = 32 * (warp & 3) + lane, column0 = COLUMNS * (warp >> 2);
     const uint16_t *scale_row = matrix.scales + static_cast<size_t>(row0 + out_row < matrix.n ? row0 + out_row : matrix.n - 1) * groups;
-    float acc[32];
+    float acc[COLUMNS];
 #pragma unroll
-    for (int i = 0; i < 32; i++) acc[i] = 0.0f;
+    for (int i = 0; i < COLUMNS; i++) acc[i] = 0.0f;
     bool alive = true;
 
     // The packed nibbles and the activations of a group are requested one group ahead (into registers) and turned
@@ -181,7 +187,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
         const float scale = bf16_bits_to_f32(scale_row[group]);
         const uint32_t address = tmem_base + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + static_cast<uint32_t>(buffer * GEMM_LANES + column0);
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
+        for (int half = 0; half < COLUMNS / 16; half++) {
             uint32_t d[16];
             asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                          : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]), "=r"(d[9]),
@@ -218,7 +224,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
                     "setp.ne.b32 p, %4, 0;\n"
                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n"
                     "}\n" ::"r"(d_address),
-                    "l"(a_descriptor), "l"(b_descriptor), "r"(GEMM_INSTRUCTION), "r"(accumulate), "r"(0u)
+                    "l"(a_descriptor), "l"(b_descriptor), "r"(gemm_instruction<GEMM_LANES>()), "r"(accumulate), "r"(0u)
                     : "memory");
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barrier_address + buffer * 8) : "memory");
@@ -230,7 +236,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
     // ---- epilogue: this thread's row, 32 lanes
     if (alive && row0 + out_row < matrix.n) {
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
+        for (int i = 0; i < COLUMNS; i++) {
             const int m = m0 + column0 + i;
             if (m >= a.lanes) break;
             const size_t index = static_cast<size_t>(m) * matrix.n + row0 + out_row;
@@ -246,12 +252,12 @@ __global__ void __launch_bounds__(GEMM_THREADS) linear_int4_gemm_kernel(const Ge
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(static_cast<uint32_t>(2 * GEMM_LANES)) : "memory");
 }
 
 }  // namespace
 
-bool linear_int4_gemm_supported(int lanes, int n, int k) { return lanes >= GEMM_LANES && k % 128 == 0 && k >= 128 && n >= 1; }
+bool linear_int4_gemm_supported(int lanes, int n, int k) { return lanes >= GEMM_MIN_LANES && k % 128 == 0 && k >= 128 && n >= 1; }
 
 cudaError_t launch_linear_int4_gemm_multi(const uint16_t *x, int branches, const uint32_t *const *qweights, const uint16_t *const *scales, void *const *ys,
                                           const int *ns, const uint16_t *residual, int lanes, int k, int epilogue, float scale, int *error_flag,
@@ -279,10 +285,15 @@ cudaError_t launch_linear_int4_gemm_multi(const uint16_t *x, int branches, const
     args.epilogue = epilogue;
     args.scale = scale;
     args.error_flag = error_flag;
-    cudaError_t status = cudaFuncSetAttribute(linear_int4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(GEMM_SMEM));
-    if (status != cudaSuccess) return status;
-    dim3 grid((lanes + GEMM_LANES - 1) / GEMM_LANES, tiles);
-    linear_int4_gemm_kernel<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(args);
+    if (lanes >= 128) {
+        cudaError_t status = cudaFuncSetAttribute(linear_int4_gemm_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(gemm_smem<128>()));
+        if (status != cudaSuccess) return status;
+        linear_int4_gemm_kernel<128><<<dim3((lanes + 127) / 128, tiles), GEMM_THREADS, gemm_smem<128>(), stream>>>(args);
+    } else {
+        cudaError_t status = cudaFuncSetAttribute(linear_int4_gemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(gemm_smem<64>()));
+        if (status != cudaSuccess) return status;
+        linear_int4_gemm_kernel<64><<<dim3((lanes + 63) / 64, tiles), GEMM_THREADS, gemm_smem<64>(), stream>>>(args);
+    }
     return cudaGetLastError();
 }
 
