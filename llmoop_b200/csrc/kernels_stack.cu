@@ -612,7 +612,7 @@ __device__ __forceinline__ float *attention_stats(float *scratch, int lanes, int
 
 // Log-sum-exp merge of the split partials of one (lane, q head) row by one warp: lane s of the warp weighs split s
 // (s + 32, ...), every lane owns HD / 32 consecutive output dims, and the weighted rows are summed in split order,
-// the loads of twelve or sixteen splits in flight at a time.  The result goes out as fp16 in fragment order.
+// the loads of eight or sixteen splits in flight at a time.  The result goes out as fp16 in fragment order.
 template <int HD>
 __device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32_t capacity, uint32_t tick, int query_lane, int head) {
     constexpr int VEC = HD / 32;
@@ -628,7 +628,8 @@ __device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32
     uint16_t *__restrict__ out_fragments = job.out_fragments;
     const int last = splits - 1;
     // Rows beyond the last split are read as the last split again and weigh nothing, so no load is predicated.
-    constexpr int CHUNK = VEC == 4 ? 12 : 16;  // rows in flight at a time (as many as the registers hold): contexts of up to 768 tokens merge in one round trip
+    constexpr int CHUNK = VEC == 4 ? 8 : 16;  // rows in flight at a time; a divisor of 32, so that a round never straddles two blocks of 32 splits (whose weights sit in the warp's lanes)
+    static_assert(32 % CHUNK == 0, "rounds of the merge must not straddle the blocks of 32 splits");
     float part[CHUNK][VEC];
     auto fetch = [&](int first) {
 #pragma unroll
