@@ -558,7 +558,8 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
     const int factor = static_cast<int>(std::max<size_t>(1, (all + budget - 1) / budget));
     op_split_tokens_ = split_tokens_ * factor;
     const size_t op_splits = (model_->capacity() + op_split_tokens_ - 1) / op_split_tokens_;
-    const size_t small_batches = static_cast<size_t>(std::min(options.max_lanes, 8)) * max_q_heads * max_splits_;
+    // (the persistent kernel merges rows of more than 32 splits in two levels: one more partial per 32 splits)
+    const size_t small_batches = static_cast<size_t>(std::min(options.max_lanes, 8)) * max_q_heads * (max_splits_ + (max_splits_ + 31) / 32);
     attention_scratch_ = device_alloc(std::max(small_batches, static_cast<size_t>(options.max_lanes) * max_q_heads * op_splits) * partial_bytes);
 
     // cycle arrays: verify tokens, forced drafts, stop tokens/counts, accept rows, per-step draft tokens, slots
@@ -1413,7 +1414,7 @@ bool Engine::run_stack(const StackPlan &stack, int lanes, void *hidden) {
     if (tp_size > 1 && !tp_connected_) return false;  // without the peer exchange the shards meet in NCCL all-reduces, kernel by kernel
     if (!stack_enabled_ || !stack.available || lanes < 1 || lanes > 8 || current_width_ <= 0 || lanes % current_width_ != 0) return false;
     size_t smem = 0;
-    if (!decode_stack_supported(stack.shape, lanes, &smem)) return false;
+    if (!decode_stack_supported(stack.shape, lanes, &smem) || current_splits_ > 1024) return false;  // two merge levels of 32 splits
     StackBuffers buffers{};
     buffers.hidden = static_cast<uint16_t *>(hidden);
     buffers.q = static_cast<uint16_t *>(stack_q_.ptr);

@@ -27,7 +27,9 @@
 //  * attention: a team of four warps per (kv head, 64-token split, lane group) on the tensor cores (query rows in
 //    shared memory, K and V rows in registers, all loads of an item requested before its arithmetic); the team that
 //    completes a kv head's last split queues the merge, and after its items the CTA's sixteen warps merge one
-//    (lane, q head) row each - no grid barrier between the splits and their merge.
+//    (lane, q head) row each - no grid barrier between the splits and their merge.  Lane groups of more than 32
+//    splits are merged in two levels (ranges of 32 splits spread over every warp of the grid, then the ranges of a
+//    row by one warp), with a grid barrier before each level.
 //  * code that runs once per layer (staging, attention, merge, epilogues) is kept short and free of re-read state:
 //    such straight-line code was measured at about 0.27 us per KB of instructions on this kernel (instruction
 //    fetch, not arithmetic), and a value behind a reference is read again after every ordered load.
@@ -610,31 +612,26 @@ __device__ __forceinline__ float *attention_stats(float *scratch, int lanes, int
     return scratch + static_cast<size_t>(lanes) * q_heads * max_splits * head_width;
 }
 
-// Log-sum-exp merge of the split partials of one (lane, q head) row by one warp: lane s of the warp weighs split s
-// (s + 32, ...), every lane owns HD / 32 consecutive output dims, and the weighted rows are summed in split order,
-// the loads of eight or sixteen splits in flight at a time.  The result goes out as fp16 in fragment order.
+// Log-sum-exp merge of up to 32 partials of one (lane, q head) row by one warp: lane s of the warp weighs partial s,
+// every lane owns HD / 32 consecutive output dims, and the weighted rows are summed in order, the loads of eight or
+// sixteen partials in flight at a time.  `values` points at the lane's dims of the first partial (rows of HD floats),
+// `stats` at its (maximum, sum).  Leaves the block's maximum, its sum and the lane's unnormalised dims.
+constexpr int MERGE_BLOCK = 32;
 template <int HD>
-__device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32_t capacity, uint32_t tick, int query_lane, int head) {
+__device__ __forceinline__ void attention_merge_block(const float *__restrict__ values, const float2 *__restrict__ stats, int count, float &maximum,
+                                                      float &denominator, float (&acc)[HD / 32]) {
     constexpr int VEC = HD / 32;
     static_assert(VEC == 1 || VEC == 2 || VEC == 4, "a lane owns one, two or four output dims");
+    constexpr int CHUNK = VEC == 4 ? 8 : 16;  // rows in flight at a time; a divisor of the block, whose weights sit in the warp's lanes
+    static_assert(MERGE_BLOCK % CHUNK == 0, "rounds of the merge must not straddle a block");
     const int lane_id = threadIdx.x & 31;
-    const uint32_t tokens = tick + 1u < capacity ? tick + 1u : capacity;
-    const int max_splits = job.max_splits, staged = job.staged;
-    int splits = static_cast<int>((tokens + 63u) / 64u);
-    if (splits > max_splits) splits = max_splits;
-    const size_t row = (static_cast<size_t>(query_lane) * job.q_heads + head) * max_splits;
-    const float *__restrict__ mine = job.scratch + row * HD + lane_id * VEC;
-    const float2 *__restrict__ stats = reinterpret_cast<const float2 *>(attention_stats(job.scratch, job.lanes, job.q_heads, max_splits, HD)) + row;
-    uint16_t *__restrict__ out_fragments = job.out_fragments;
-    const int last = splits - 1;
-    // Rows beyond the last split are read as the last split again and weigh nothing, so no load is predicated.
-    constexpr int CHUNK = VEC == 4 ? 8 : 16;  // rows in flight at a time; a divisor of 32, so that a round never straddles two blocks of 32 splits (whose weights sit in the warp's lanes)
-    static_assert(32 % CHUNK == 0, "rounds of the merge must not straddle the blocks of 32 splits");
+    const int last = count - 1;
+    // Rows beyond the last partial are read as the last one again and weigh nothing, so no load is predicated.
     float part[CHUNK][VEC];
     auto fetch = [&](int first) {
 #pragma unroll
         for (int u = 0; u < CHUNK; u++) {
-            const float *source = mine + static_cast<size_t>(first + u < last ? first + u : last) * HD;
+            const float *source = values + static_cast<size_t>(first + u < last ? first + u : last) * HD;
             if (VEC == 4) {
                 const float4 raw = __ldcg(reinterpret_cast<const float4 *>(source));
                 part[u][0] = raw.x, part[u][VEC > 1 ? 1 : 0] = raw.y, part[u][VEC > 2 ? 2 : 0] = raw.z, part[u][VEC > 3 ? 3 : 0] = raw.w;
@@ -646,42 +643,110 @@ __device__ __noinline__ void attention_merge_row(const AttentionJob &job, uint32
             }
         }
     };
-    float acc[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; v++) acc[v] = 0.0f;
-    auto accumulate = [&](int first, float weight) {
+    // the statistics and the first rows are requested together
+    const float2 pair = __ldcg(stats + (lane_id < last ? lane_id : last));
+    fetch(0);
+    maximum = warp_max(lane_id < count ? pair.x : -3.4028234663852886e38f);
+    const float weight = lane_id < count ? expf(pair.x - maximum) : 0.0f;
+    denominator = warp_sum(lane_id < count ? pair.y * weight : 0.0f);
+#pragma unroll 1
+    for (int s = 0; s < count; s += CHUNK) {
+        if (s != 0) fetch(s);
 #pragma unroll
         for (int u = 0; u < CHUNK; u++) {
-            const float w = __shfl_sync(0xffffffffu, weight, (first + u) & 31);
+            const float w = __shfl_sync(0xffffffffu, weight, s + u);  // 0 in the lanes beyond the last partial
 #pragma unroll
             for (int v = 0; v < VEC; v++) acc[v] += part[u][v] * w;
         }
-    };
-    // the statistics of the first 32 splits and the first rows are requested together
-    float2 pair = __ldcg(stats + (lane_id < last ? lane_id : last));
-    fetch(0);
-    float maximum = lane_id < splits ? pair.x : -3.4028234663852886e38f;
-#pragma unroll 1
-    for (int s = lane_id + 32; s < splits; s += 32) maximum = fmaxf(maximum, __ldcg(stats + s).x);
-    maximum = warp_max(maximum);
-    float weight = lane_id < splits ? expf(pair.x - maximum) : 0.0f;
-    float denominator = lane_id < splits ? pair.y * weight : 0.0f;
-    accumulate(0, weight);
-#pragma unroll 1
-    for (int s = CHUNK; s < splits; s += CHUNK) {
-        if ((s & 31) == 0) {  // the next 32 splits: this lane weighs split s + lane
-            pair = __ldcg(stats + (s + lane_id < last ? s + lane_id : last));
-            weight = s + lane_id < splits ? expf(pair.x - maximum) : 0.0f;
-            denominator += s + lane_id < splits ? pair.y * weight : 0.0f;
-        }
-        fetch(s);
-        accumulate(s, weight);
     }
-    denominator = warp_sum(denominator);
+}
+
+// How many 64-token splits the partials of a query lane's rows cover: those of the newest lane of its group of QL
+// lanes (a team writes every row of its group for every split of the group; rows of older lanes are masked there).
+__device__ __forceinline__ int attention_group_splits(const AttentionJob &job, const uint32_t *ticks, uint32_t capacity, int query_lane, int ql) {
+    const int stream = query_lane / job.lanes_per_stream, first = ((query_lane % job.lanes_per_stream) / ql) * ql;
+    uint32_t tick = 0;
+    for (int i = first; i < first + ql && i < job.lanes_per_stream; i++) {
+        const uint32_t other = ticks[stream * job.lanes_per_stream + i];
+        if (other > tick) tick = other;
+    }
+    const uint32_t tokens = tick + 1u < capacity ? tick + 1u : capacity;
+    const int splits = static_cast<int>((tokens + 63u) / 64u);
+    return splits < job.max_splits ? splits : job.max_splits;
+}
+
+// The splits of one lane's own attended window.
+__device__ __forceinline__ int attention_own_splits(const AttentionJob &job, uint32_t capacity, uint32_t tick) {
+    const uint32_t tokens = tick + 1u < capacity ? tick + 1u : capacity;
+    const int splits = static_cast<int>((tokens + 63u) / 64u);
+    return splits < job.max_splits ? splits : job.max_splits;
+}
+
+// The scratch behind the split partials: per row and range of MERGE_BLOCK splits one merged partial, laid out like
+// the split partials (values, then statistics).  Used by rows of more than MERGE_BLOCK splits.
+__device__ __forceinline__ float *attention_range_values(const AttentionJob &job, int head_width) {
+    return job.scratch + static_cast<size_t>(job.lanes) * job.q_heads * job.max_splits * (head_width + 2);
+}
+__device__ __forceinline__ int attention_ranges(int max_splits) { return (max_splits + MERGE_BLOCK - 1) / MERGE_BLOCK; }
+
+// A row of at most MERGE_BLOCK splits: merged and written out as fp16 in fragment order by one warp.
+template <int HD>
+__device__ __noinline__ void attention_merge_row(const AttentionJob &job, int splits, int query_lane, int head) {
+    constexpr int VEC = HD / 32;
+    const int lane_id = threadIdx.x & 31;
+    const size_t row = (static_cast<size_t>(query_lane) * job.q_heads + head) * job.max_splits;
+    float maximum, denominator, acc[VEC];
+    attention_merge_block<HD>(job.scratch + row * HD + lane_id * VEC,
+                              reinterpret_cast<const float2 *>(attention_stats(job.scratch, job.lanes, job.q_heads, job.max_splits, HD)) + row, splits, maximum,
+                              denominator, acc);
 #pragma unroll
     for (int v = 0; v < VEC; v++) {
         const float rounded = round_bf16(denominator == 0.0f ? 0.0f : acc[v] / denominator);
-        out_fragments[fragment_element(head * HD + lane_id * VEC + v, query_lane, staged)] = __half_as_ushort(__float2half_rn(rounded));
+        job.out_fragments[fragment_element(head * HD + lane_id * VEC + v, query_lane, job.staged)] = __half_as_ushort(__float2half_rn(rounded));
+    }
+}
+
+// Longer rows, first level: one range of MERGE_BLOCK splits of a row into one partial.
+template <int HD>
+__device__ __noinline__ void attention_merge_range(const AttentionJob &job, int splits, int query_lane, int head, int range) {
+    constexpr int VEC = HD / 32;
+    const int lane_id = threadIdx.x & 31;
+    const size_t row = static_cast<size_t>(query_lane) * job.q_heads + head;
+    const size_t first = row * job.max_splits + static_cast<size_t>(range) * MERGE_BLOCK;
+    const int count = splits - range * MERGE_BLOCK < MERGE_BLOCK ? splits - range * MERGE_BLOCK : MERGE_BLOCK;
+    float maximum, denominator, acc[VEC];
+    attention_merge_block<HD>(job.scratch + first * HD + lane_id * VEC,
+                              reinterpret_cast<const float2 *>(attention_stats(job.scratch, job.lanes, job.q_heads, job.max_splits, HD)) + first, count, maximum,
+                              denominator, acc);
+    const int ranges = attention_ranges(job.max_splits);
+    float *values = attention_range_values(job, HD);
+    float *out = values + (row * ranges + range) * HD + lane_id * VEC;
+#pragma unroll
+    for (int v = 0; v < VEC; v++) out[v] = acc[v];
+    if (lane_id == 0) {
+        float2 *statistics = reinterpret_cast<float2 *>(values + static_cast<size_t>(job.lanes) * job.q_heads * ranges * HD) + row * ranges + range;
+        *statistics = make_float2(maximum, denominator);
+    }
+}
+
+// Second level: the row's range partials merged and written out.
+template <int HD>
+__device__ __noinline__ void attention_merge_ranges(const AttentionJob &job, int splits, int query_lane, int head) {
+    constexpr int VEC = HD / 32;
+    const int lane_id = threadIdx.x & 31;
+    const size_t row = static_cast<size_t>(query_lane) * job.q_heads + head;
+    const int ranges = attention_ranges(job.max_splits), count = (splits + MERGE_BLOCK - 1) / MERGE_BLOCK;
+    const float *values = attention_range_values(job, HD);
+    float maximum, denominator, acc[VEC];
+    attention_merge_block<HD>(values + row * ranges * HD + lane_id * VEC,
+                              reinterpret_cast<const float2 *>(values + static_cast<size_t>(job.lanes) * job.q_heads * ranges * HD) + row * ranges, count, maximum,
+                              denominator, acc);
+#pragma unroll
+    for (int v = 0; v < VEC; v++) {
+        const float rounded = round_bf16(denominator == 0.0f ? 0.0f : acc[v] / denominator);
+        job.out_fragments[fragment_element(head * HD + lane_id * VEC + v, query_lane, job.staged)] = __half_as_ushort(__float2half_rn(rounded));
     }
 }
 
@@ -981,8 +1046,13 @@ __device__ __noinline__ void attention_team_item(AttentionCache &cache, const Kv
         }
         if (pass + 1 < HD / HALF) team_barrier(barrier_id);  // the partial outputs are rewritten by the next pass
     }
-    // ---- the team that completes the kv head's last split merges the splits of its queries
+    // ---- the team that completes the kv head's last split merges the splits of its queries; groups of more than
+    // MERGE_BLOCK splits are merged in two levels by the whole grid after the items
     mark(23);
+    if (expected_splits > MERGE_BLOCK) {
+        team_barrier(barrier_id);  // the team's shared arrays are free for its next item
+        return;
+    }
     __threadfence();
     team_barrier(barrier_id);
     unsigned int *arrival = arrivals + kv_head * group_slots + group_slot;
@@ -1007,7 +1077,8 @@ __device__ __noinline__ void attention_team_item(AttentionCache &cache, const Kv
             for (int row = team_warp; row < Q; row += 4) {
                 const int query_lane = lane0 + row / GROUP;
                 if (query_lane < lanes && group_index * QL + row / GROUP < lanes_per_stream)
-                    attention_merge_row<HD>(cache.job, capacity, cache.tick[query_lane], query_lane, kv_head * GROUP + row % GROUP);
+                    attention_merge_row<HD>(cache.job, attention_own_splits(cache.job, capacity, cache.tick[query_lane]), query_lane,
+                                            kv_head * GROUP + row % GROUP);
             }
         }
     }
@@ -1706,9 +1777,30 @@ __global__ void __launch_bounds__(STACK_THREADS, 1) decode_stack_kernel(const St
                             const int group_index = group_slot % groups_per_stream;
                             const int query_lane = (group_slot / groups_per_stream) * a.lanes_per_stream + group_index * QL + row / GROUP;
                             if (query_lane < lanes && group_index * QL + row / GROUP < a.lanes_per_stream && attention_cache->slot[query_lane] >= 0)
-                                attention_merge_row<HD>(attention_cache->job, kv.capacity, attention_cache->tick[query_lane], query_lane,
-                                                        kv_head * GROUP + row % GROUP);
+                                attention_merge_row<HD>(attention_cache->job, attention_own_splits(attention_cache->job, kv.capacity, attention_cache->tick[query_lane]),
+                                                        query_lane, kv_head * GROUP + row % GROUP);
                         }
+                    }
+                }
+                if (a.max_splits > MERGE_BLOCK) {
+                    // ---- groups of more than MERGE_BLOCK splits: every warp of the grid merges ranges of MERGE_BLOCK
+                    // splits into one partial each, then one warp per row merges the row's range partials.  The two
+                    // barriers in between are not counted for the producer of slices (it waits for the one below).
+                    const int ranges = attention_ranges(a.max_splits), rows = lanes * shape.q_heads;
+                    grid_barrier(counter, target, error_flag, barrier_spin_limit);
+                    for (int task = blockIdx.x + gridDim.x * warp; task < rows * ranges; task += gridDim.x * CONSUMER_WARPS) {
+                        const int row = task / ranges, range = task % ranges, query_lane = row / shape.q_heads;
+                        if (attention_cache->slot[query_lane] < 0) continue;
+                        const int splits = attention_group_splits(attention_cache->job, attention_cache->tick, kv.capacity, query_lane, QL);
+                        if (splits > MERGE_BLOCK && range * MERGE_BLOCK < splits)
+                            attention_merge_range<HD>(attention_cache->job, splits, query_lane, row % shape.q_heads, range);
+                    }
+                    grid_barrier(counter, target, error_flag, barrier_spin_limit);
+                    for (int row = blockIdx.x + gridDim.x * warp; row < rows; row += gridDim.x * CONSUMER_WARPS) {
+                        const int query_lane = row / shape.q_heads;
+                        if (attention_cache->slot[query_lane] < 0) continue;
+                        const int splits = attention_group_splits(attention_cache->job, attention_cache->tick, kv.capacity, query_lane, QL);
+                        if (splits > MERGE_BLOCK) attention_merge_ranges<HD>(attention_cache->job, splits, query_lane, row % shape.q_heads);
                     }
                 }
                 meet();
@@ -1855,7 +1947,7 @@ cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count
                                 int split_tokens, int max_splits, cudaStream_t stream, const StackTp *tp_device, int tp_size) {
     StackPlanSmem plan;
     if (lanes < 1 || lanes > 8 || !plan_smem(shape, lanes, shape.grid, &plan) || lanes_per_stream <= 0 || lanes % lanes_per_stream != 0 ||
-        layer_count < 1 || split_tokens != 64)
+        layer_count < 1 || split_tokens != 64 || max_splits > MERGE_BLOCK * MERGE_BLOCK)
         return cudaErrorInvalidValue;
     StackArgs args;
     args.layers = layers_device;

@@ -141,16 +141,17 @@ def long_context_package(tmp_path_factory, request):
 
     head = request.param
     spec = ModelSpec(name=f"stack_long_context_{head}", hidden=512, layers=2, q_heads=512 // head, kv_heads=128 // head, head_dim=head, ffn=1408,
-                     vocab=512, max_positions=4096, quant="int4", std=0.01, seed=11)
+                     vocab=512, max_positions=8192, quant="int4", std=0.01, seed=11)
     directory = tmp_path_factory.mktemp("packages") / spec.name
     write_package(spec, directory)
     return directory, spec
 
 
-@pytest.mark.parametrize("capacity,context_tokens,probe_tokens", [(4096, 2100, 4), (4096, 1900, 4), (128, 300, 1)],
-                         ids=["33_splits", "30_splits", "ring_wrapped_twice"])
+@pytest.mark.parametrize("capacity,context_tokens,probe_tokens", [(4096, 2100, 4), (4096, 1900, 4), (8192, 4500, 4), (128, 300, 1)],
+                         ids=["33_splits", "30_splits", "71_splits", "ring_wrapped_twice"])
 def test_stack_kernel_long_context_and_ring_wrap(long_context_package, capacity, context_tokens, probe_tokens):
-    """More attention splits than a warp has lanes (the merge walks them in rounds of 32), and a KV ring that has
+    """More attention splits than a warp has lanes (the stack kernel merges such rows in two levels: ranges of 32
+    splits first - 71 splits make two full ranges and a ragged one - then the ranges), and a KV ring that has
     wrapped: probe lanes after the context, stack kernel against the oracle and against the kernel-per-operator
     path.  Behind the wrap a batch is one tick (all lanes of a batch append before any attends, and a later lane's
     slot is the far end of an earlier lane's window), so the probe there is a single lane."""
