@@ -811,7 +811,6 @@ __device__ __noinline__ void attention_team_item(AttentionCache &cache, const Kv
             stamps[index] = now;
         }
     };
-    mark(20);
     constexpr int QW = HD / 32;                    // 16-byte pieces of a q / k row per thread
     constexpr int HALF = HD < 64 ? HD : 64;        // head dims handled per output pass
     constexpr int DPT = HALF / 8;                  // of which one thread column owns this many
@@ -843,6 +842,7 @@ __device__ __noinline__ void attention_team_item(AttentionCache &cache, const Kv
     const uint32_t first_tick = newest + 1u - tokens;
     const uint32_t begin = static_cast<uint32_t>(split) * 64u;
     if (begin >= tokens) return;  // the whole team leaves: nobody waits at the team barrier
+    mark(20);
     int expected_splits = static_cast<int>((tokens + 63u) / 64u);
     if (expected_splits > max_splits) expected_splits = max_splits;
     const int count = static_cast<int>(tokens - begin < 64u ? tokens - begin : 64u);
@@ -851,15 +851,24 @@ __device__ __noinline__ void attention_team_item(AttentionCache &cache, const Kv
     const size_t half_page = static_cast<size_t>(kv.kv_heads) * kv.page_tokens * HD;
     const bool cached = cache.item[team] == item;
     const uint32_t ring_base = (first_tick + begin) % capacity;
-    auto row_offset = [&](int token, bool value) {
-        size_t base;
-        if (cached) {
-            base = static_cast<size_t>(cache.row_base[team][token]) * HD;
-        } else {
-            base = attention_row_base<HD>(kv, slot, ring_base, token);
-        }
-        return base + (value ? half_page : 0) + static_cast<size_t>(kv_head) * kv.page_tokens * HD;
-    };
+    // Row numbers (units of HD elements, kv head 0) of the K rows this thread reads (tokens g and g + 8 of the warp's
+    // sixteen) and of its V rows (tokens 2j, 2j + 1, 2j + 8, 2j + 9).  Without cached rows every thread walks the
+    // block table for one token and the warp passes the rows round: one dependent load instead of six in a row.
+    uint32_t k_row[2], v_row[4];
+    if (cached) {
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) k_row[nt] = cache.row_base[team][(token0 + nt * 8 + g) & 63];
+#pragma unroll
+        for (int t = 0; t < 4; t++) v_row[t] = cache.row_base[team][(token0 + 2 * j + (t & 1) + 8 * (t >> 1)) & 63];
+    } else {
+        const int token = token0 + (lane & 15);
+        const uint32_t mine = token < count ? static_cast<uint32_t>(attention_row_base<HD>(kv, slot, ring_base, token) / HD) : 0u;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++) k_row[nt] = __shfl_sync(0xffffffffu, mine, nt * 8 + g);
+#pragma unroll
+        for (int t = 0; t < 4; t++) v_row[t] = __shfl_sync(0xffffffffu, mine, 2 * j + (t & 1) + 8 * (t >> 1));
+    }
+    const size_t head_offset = static_cast<size_t>(kv_head) * kv.page_tokens * HD;
 
     // ---- S = Q K^T for 16 tokens.  The team's Q query rows go to shared memory with asynchronous copies (they
     // would otherwise hold 32 registers per thread while the K and V rows are in flight); a row is kept as HD / 32
@@ -890,7 +899,7 @@ __device__ __noinline__ void attention_team_item(AttentionCache &cache, const Kv
     for (int nt = 0; nt < 2; nt++) {
         const int token = token0 + nt * 8 + g;
         if (token < count) {
-            const uint16_t *krow = kv.pool + row_offset(token, false) + j * 8;
+            const uint16_t *krow = kv.pool + static_cast<size_t>(k_row[nt]) * HD + head_offset + j * 8;
 #pragma unroll
             for (int w = 0; w < QW; w++) kf[nt][w] = load16_now(krow + w * 32);
         } else {
@@ -902,7 +911,7 @@ __device__ __noinline__ void attention_team_item(AttentionCache &cache, const Kv
 #pragma unroll
     for (int t = 0; t < 4; t++) {
         const int token = token0 + 2 * j + (t & 1) + 8 * (t >> 1);
-        v_offset[t] = token < count ? row_offset(token, true) : static_cast<size_t>(-1);
+        v_offset[t] = token < count ? static_cast<size_t>(v_row[t]) * HD + half_page + head_offset : static_cast<size_t>(-1);
     }
     uint32_t v[HD / HALF][4][DPT / 2];
     auto load_values = [&](int pass) {
