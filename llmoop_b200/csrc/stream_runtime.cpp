@@ -378,6 +378,143 @@ std::optional<size_t> StateTable::next_append_block_boundary_distance(size_t max
     return std::nullopt;
 }
 
+// ---------------------------------------------------------------------------------------------- prefix cache
+
+namespace {
+
+constexpr uint64_t FNV64_OFFSET = 0xcbf29ce484222325ull, FNV64_PRIME = 0x100000001b3ull;
+
+uint64_t fnv_bytes(uint64_t hash, const uint8_t *bytes, size_t count) {
+    for (size_t i = 0; i < count; i++) hash = (hash ^ bytes[i]) * FNV64_PRIME;
+    return hash;
+}
+uint64_t fnv_text(uint64_t hash, const char *text) { return fnv_bytes(hash, reinterpret_cast<const uint8_t *>(text), std::char_traits<char>::length(text)); }
+uint64_t fnv_u64(uint64_t hash, uint64_t value) {
+    uint8_t bytes[8];
+    for (int i = 0; i < 8; i++) bytes[i] = static_cast<uint8_t>(value >> (8 * i));
+    return fnv_bytes(hash, bytes, 8);
+}
+
+}  // namespace
+
+uint64_t stable_token_prefix_hash(const uint32_t *token_ids, size_t count) {
+    uint64_t hash = fnv_u64(fnv_text(FNV64_OFFSET, "nerve:token-prefix:v1"), count);
+    for (size_t i = 0; i < count; i++) {
+        const uint32_t token = token_ids[i];
+        const uint8_t bytes[4] = {static_cast<uint8_t>(token), static_cast<uint8_t>(token >> 8), static_cast<uint8_t>(token >> 16), static_cast<uint8_t>(token >> 24)};
+        hash = fnv_bytes(hash, bytes, 4);
+    }
+    return hash;
+}
+
+uint64_t stable_runtime_modifier_hash(const uint8_t *bytes, size_t count) {
+    return fnv_bytes(fnv_u64(fnv_text(FNV64_OFFSET, "nerve:runtime-modifiers:v1"), count), bytes, count);
+}
+
+void check_prefix_lookup_ids(const std::string &execution_class_id, const std::string &runtime_graph_id) {
+    if (execution_class_id.empty()) fail("prefix cache execution class id must not be empty");
+    if (runtime_graph_id.empty()) fail("prefix cache runtime graph id must not be empty");
+}
+
+std::vector<StateKey> normalized_state_keys(std::vector<StateKey> state_keys) {
+    std::sort(state_keys.begin(), state_keys.end());
+    state_keys.erase(std::unique(state_keys.begin(), state_keys.end()), state_keys.end());
+    return state_keys;
+}
+
+PrefixStateCacheKey PrefixStateCacheKey::from_token_prefix(const std::string &execution_class_id, const std::string &runtime_graph_id,
+                                                           const std::vector<uint32_t> &token_ids, const std::string &runtime_modifier_bytes,
+                                                           std::vector<StateKey> state_keys) {
+    check_prefix_lookup_ids(execution_class_id, runtime_graph_id);
+    if (token_ids.empty()) fail("prefix cache token prefix must not be empty");
+    PrefixStateCacheKey key;
+    key.state_keys = normalized_state_keys(std::move(state_keys));
+    if (key.state_keys.empty()) fail("prefix cache state key set must not be empty");
+    key.execution_class_id = execution_class_id;
+    key.runtime_graph_id = runtime_graph_id;
+    key.token_count = token_ids.size();
+    key.token_ids = token_ids;
+    key.token_hash = stable_token_prefix_hash(token_ids.data(), token_ids.size());
+    key.runtime_modifier_hash = stable_runtime_modifier_hash(reinterpret_cast<const uint8_t *>(runtime_modifier_bytes.data()), runtime_modifier_bytes.size());
+    return key;
+}
+
+bool PrefixStateCacheKey::operator<(const PrefixStateCacheKey &other) const {
+    return std::tie(execution_class_id, runtime_graph_id, token_count, token_ids, token_hash, runtime_modifier_hash, state_keys) <
+           std::tie(other.execution_class_id, other.runtime_graph_id, other.token_count, other.token_ids, other.token_hash, other.runtime_modifier_hash,
+                    other.state_keys);
+}
+bool PrefixStateCacheKey::operator==(const PrefixStateCacheKey &other) const { return !(*this < other) && !(other < *this); }
+
+std::vector<PrefixStateCacheKey> PrefixStateCache::release(StateArena &arena, PrefixCacheIndex<Retained>::Removed removed) {
+    std::vector<PrefixStateCacheKey> keys;
+    for (auto &item : removed) {
+        item.second.table.reset_all(arena);
+        keys.push_back(std::move(item.first));
+    }
+    return keys;
+}
+
+std::vector<PrefixStateCacheKey> PrefixStateCache::set_capacity(StateArena &arena, size_t capacity_entries) {
+    return release(arena, index_.set_capacity(capacity_entries));
+}
+
+bool PrefixStateCache::evict(StateArena &arena, const PrefixStateCacheKey &key) {
+    std::optional<Retained> removed = index_.evict(key);
+    if (!removed) return false;
+    removed->table.reset_all(arena);
+    return true;
+}
+
+PrefixStateCacheInsert PrefixStateCache::insert(StateArena &arena, const PrefixStateCacheKey &key, const StateTable &source) {
+    PrefixStateCacheInsert result;
+    if (index_.capacity_entries() == 0) return result;
+    const TableSnapshot state = source.snapshot();
+    for (const StateKey &state_key : key.state_keys) {
+        const auto entry = std::find_if(state.entries.begin(), state.entries.end(), [&](const EntrySnapshot &e) { return e.key == state_key; });
+        if (entry == state.entries.end()) fail("prefix cache source stream " + quoted(state.stream_id) + " has no state " + key_name(state_key));
+        if (entry->shape.retention == Retention::Append) {
+            if (entry->logical_activation_count != key.token_count)
+                fail("prefix cache key for " + std::to_string(key.token_count) + " tokens does not match source state " + key_name(state_key) + " with " +
+                     std::to_string(entry->logical_activation_count) + " activations");
+            if (entry->logical_activation_count % entry->shape.activation_capacity != 0)
+                fail("prefix cache source state " + key_name(state_key) + " has " + std::to_string(entry->logical_activation_count) +
+                     " activations, which is not aligned to block capacity " + std::to_string(entry->shape.activation_capacity));
+        } else if (entry->logical_activation_count != 1 || entry->block_ids.size() != 1) {
+            fail("prefix cache source mutable state " + key_name(state_key) + " is not initialized");
+        }
+    }
+    std::string cached_stream_id = index_.next_cached_stream_id();
+    StateTable retained = source.fork(arena, cached_stream_id);
+    auto inserted = index_.insert(key, Retained{std::move(cached_stream_id), std::move(retained)});
+    if (inserted.replaced) {
+        inserted.replaced->table.reset_all(arena);
+        result.replaced_existing = true;
+    }
+    result.evicted_keys = release(arena, std::move(inserted.evicted));
+    return result;
+}
+
+bool PrefixStateCache::restore_into(StateArena &arena, const PrefixStateCacheKey &key, StateTable &target) {
+    Retained *retained = index_.use(key);
+    if (retained == nullptr) return false;
+    target.share_states_from(arena, retained->table, key.state_keys);
+    return true;
+}
+
+PrefixStateCacheSnapshot PrefixStateCache::snapshot() const {
+    PrefixStateCacheSnapshot snapshot;
+    snapshot.capacity_entries = index_.capacity_entries();
+    snapshot.entry_count = index_.entries().size();
+    snapshot.eviction_count = index_.eviction_count();
+    for (const auto &item : index_.entries()) {
+        const TableSnapshot state = item.second.payload.table.snapshot();
+        snapshot.entries.push_back(PrefixStateCacheEntrySnapshot{item.first, item.second.payload.cached_stream_id, state.block_count, state.logical_activation_count,
+                                                                 item.second.last_used_tick, item.second.use_count});
+    }
+    return snapshot;
+}
+
 // ---------------------------------------------------------------------------------------------- scheduler
 
 StreamScheduler::Stream::Stream(std::string id, std::string execution_class, StateTable state_table)
@@ -467,6 +604,41 @@ StreamSnapshot StreamScheduler::share_stream_state(const std::string &target_str
     Stream &target = stream(target_stream_id);
     target.table.share_states_from(arena_, source_table, {key});
     return target.snapshot();
+}
+
+PrefixStateCacheInsert StreamScheduler::cache_stream_prefix_state(const std::string &stream_id, const PrefixStateCacheKey &key) {
+    const Stream &source = stream(stream_id);
+    if (source.execution_class_id != key.execution_class_id)
+        fail("cannot cache stream " + quoted(stream_id) + " with execution class " + quoted(source.execution_class_id) + " under prefix key execution class " +
+             quoted(key.execution_class_id));
+    return prefix_cache_.insert(arena_, key, source.table);
+}
+
+PrefixStateCacheKey StreamScheduler::cache_stream_prefix_state_for_tokens(const std::string &stream_id, const std::string &runtime_graph_id,
+                                                                          const std::vector<uint32_t> &token_ids, const std::string &runtime_modifier_bytes,
+                                                                          std::vector<StateKey> state_keys) {
+    PrefixStateCacheKey key =
+        PrefixStateCacheKey::from_token_prefix(stream(stream_id).execution_class_id, runtime_graph_id, token_ids, runtime_modifier_bytes, std::move(state_keys));
+    cache_stream_prefix_state(stream_id, key);
+    return key;
+}
+
+bool StreamScheduler::restore_stream_prefix_state(const std::string &target_stream_id, const PrefixStateCacheKey &key) {
+    Stream &target = stream(target_stream_id);
+    if (target.execution_class_id != key.execution_class_id)
+        fail("cannot restore prefix key execution class " + quoted(key.execution_class_id) + " into stream " + quoted(target_stream_id) +
+             " with execution class " + quoted(target.execution_class_id));
+    return prefix_cache_.restore_into(arena_, key, target.table);
+}
+
+std::optional<PrefixStateCacheKey> StreamScheduler::restore_longest_stream_prefix_state(const std::string &target_stream_id, const std::string &runtime_graph_id,
+                                                                                        const std::vector<uint32_t> &token_ids,
+                                                                                        const std::string &runtime_modifier_bytes,
+                                                                                        std::vector<StateKey> state_keys) {
+    std::optional<PrefixStateCacheKey> key =
+        prefix_cache_.longest_matching_key(stream(target_stream_id).execution_class_id, runtime_graph_id, token_ids, runtime_modifier_bytes, std::move(state_keys));
+    if (key) restore_stream_prefix_state(target_stream_id, *key);
+    return key;
 }
 
 StreamSnapshot StreamScheduler::enqueue_input_event(const std::string &stream_id, const InputEvent &event) {

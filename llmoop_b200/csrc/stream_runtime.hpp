@@ -5,11 +5,15 @@
 //   runtime-rs/src/stream_runtime.rs:15-1433 (input events, prefill chunks cut at page boundaries, decode feedback
 //                                            windows, reservations of state slots ahead of execution, rollback of
 //                                            the slots an activation did not use, interrupt / close / remove / fork,
-//                                            grouping of compatible activations into batches)
-// without the prefix-state cache (stream_runtime.rs:541-705).  Pure host code, no CUDA: errors are exceptions of
-// type RuntimeError, the C ABI turns them into a status and a message.
+//                                            grouping of compatible activations into batches; the scheduler's
+//                                            hooks of the prefix-state cache, :541-705)
+//   runtime-rs/src/stream_prefix_cache.rs:1-379 (prefix-state cache: states retained under the token prefix that
+//                                            produced them, least-recently-used eviction, longest-prefix lookup)
+// Pure host code, no CUDA: errors are exceptions of type RuntimeError, the C ABI turns them into a status and a
+// message.
 #pragma once
 
+#include <algorithm>
 #include <cstddef>
 #include <cstdint>
 #include <deque>
@@ -18,6 +22,7 @@
 #include <optional>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace nerve {
@@ -143,6 +148,183 @@ class StateTable {
     std::map<StateKey, Entry> entries_;
 };
 
+// ---------------------------------------------------------------------------------------------- prefix cache
+
+// FNV-1a over a domain string, the length and the little-endian contents (stream_prefix_cache.rs:330-353).
+uint64_t stable_token_prefix_hash(const uint32_t *token_ids, size_t count);
+uint64_t stable_runtime_modifier_hash(const uint8_t *bytes, size_t count);
+
+// What a retained state is filed under: who may use it (execution class, runtime graph, the hash of the runtime
+// modifiers - sampler, draft count - that shaped it), the tokens that produced it, and the states it holds
+// (stream_prefix_cache.rs:12-71).  Ordered field by field, which is also the order of the snapshots.
+struct PrefixStateCacheKey {
+    std::string execution_class_id, runtime_graph_id;
+    size_t token_count = 0;
+    std::vector<uint32_t> token_ids;
+    uint64_t token_hash = 0, runtime_modifier_hash = 0;
+    std::vector<StateKey> state_keys;  // sorted, without duplicates
+
+    static PrefixStateCacheKey from_token_prefix(const std::string &execution_class_id, const std::string &runtime_graph_id,
+                                                 const std::vector<uint32_t> &token_ids, const std::string &runtime_modifier_bytes,
+                                                 std::vector<StateKey> state_keys);
+    bool operator<(const PrefixStateCacheKey &other) const;
+    bool operator==(const PrefixStateCacheKey &other) const;
+    bool operator!=(const PrefixStateCacheKey &other) const { return !(*this == other); }
+};
+
+// The filing system itself, for any payload: entries under their keys with the time and the number of their uses,
+// a capacity in entries, eviction of the least recently used entry (ties: the less used one), and the lookup of the
+// longest filed prefix of a token sequence.  Whoever owns the payloads releases what a call hands back.
+// (stream_prefix_cache.rs:104-312, without the state tables.)  The lookup walks the entries - a handful, one per
+// stream - and compares tokens, instead of hashing every prefix length of the query as the reference does: a
+// 32 768-token prompt would cost 5 * 10^8 hash steps there.
+template <class Payload>
+class PrefixCacheIndex {
+  public:
+    struct Entry {
+        Payload payload;
+        uint64_t last_used_tick = 0;
+        size_t use_count = 0;
+    };
+    using Removed = std::vector<std::pair<PrefixStateCacheKey, Payload>>;
+
+    explicit PrefixCacheIndex(size_t capacity_entries = 0) : capacity_entries_(capacity_entries) {}
+    size_t capacity_entries() const { return capacity_entries_; }
+    size_t eviction_count() const { return eviction_count_; }
+    const std::map<PrefixStateCacheKey, Entry> &entries() const { return entries_; }
+
+    Removed set_capacity(size_t capacity_entries) {
+        capacity_entries_ = capacity_entries;
+        return evict_until_within_capacity();
+    }
+    std::optional<Payload> evict(const PrefixStateCacheKey &key) {
+        auto found = entries_.find(key);
+        if (found == entries_.end()) return std::nullopt;
+        Payload payload = std::move(found->second.payload);
+        entries_.erase(found);
+        eviction_count_++;
+        return payload;
+    }
+    // Files the payload (an entry of the same key is handed back as `replaced`), then evicts down to the capacity.
+    struct Inserted {
+        std::optional<Payload> replaced;
+        Removed evicted;
+    };
+    Inserted insert(const PrefixStateCacheKey &key, Payload payload) {
+        Inserted result;
+        auto found = entries_.find(key);
+        if (found != entries_.end()) {
+            result.replaced = std::move(found->second.payload);
+            entries_.erase(found);
+        }
+        entries_.emplace(key, Entry{std::move(payload), next_tick(), 0});
+        result.evicted = evict_until_within_capacity();
+        return result;
+    }
+    // The payload under `key`, counted as a use; nullptr when nothing is filed there.
+    Payload *use(const PrefixStateCacheKey &key) {
+        const uint64_t tick = next_tick();
+        auto found = entries_.find(key);
+        if (found == entries_.end()) return nullptr;
+        found->second.last_used_tick = tick;
+        found->second.use_count++;
+        return &found->second.payload;
+    }
+    std::optional<PrefixStateCacheKey> longest_matching_key(const std::string &execution_class_id, const std::string &runtime_graph_id,
+                                                            const std::vector<uint32_t> &token_ids, const std::string &runtime_modifier_bytes,
+                                                            std::vector<StateKey> state_keys) const;
+    std::string next_cached_stream_id() { return "prefix_cache_" + std::to_string(next_cached_stream_id_++); }
+
+  private:
+    uint64_t next_tick() { return next_tick_++; }
+    Removed evict_until_within_capacity() {
+        Removed removed;
+        while (entries_.size() > capacity_entries_) {
+            auto oldest = entries_.begin();
+            for (auto it = entries_.begin(); it != entries_.end(); ++it)
+                if (std::make_pair(it->second.last_used_tick, it->second.use_count) < std::make_pair(oldest->second.last_used_tick, oldest->second.use_count))
+                    oldest = it;
+            removed.emplace_back(oldest->first, std::move(oldest->second.payload));
+            entries_.erase(oldest);
+            eviction_count_++;
+        }
+        return removed;
+    }
+    size_t capacity_entries_;
+    std::map<PrefixStateCacheKey, Entry> entries_;
+    uint64_t next_tick_ = 0, next_cached_stream_id_ = 0;
+    size_t eviction_count_ = 0;
+};
+
+void check_prefix_lookup_ids(const std::string &execution_class_id, const std::string &runtime_graph_id);
+std::vector<StateKey> normalized_state_keys(std::vector<StateKey> state_keys);
+
+template <class Payload>
+std::optional<PrefixStateCacheKey> PrefixCacheIndex<Payload>::longest_matching_key(const std::string &execution_class_id, const std::string &runtime_graph_id,
+                                                                                   const std::vector<uint32_t> &token_ids,
+                                                                                   const std::string &runtime_modifier_bytes,
+                                                                                   std::vector<StateKey> state_keys) const {
+    check_prefix_lookup_ids(execution_class_id, runtime_graph_id);
+    if (token_ids.empty()) return std::nullopt;
+    state_keys = normalized_state_keys(std::move(state_keys));
+    if (state_keys.empty()) throw RuntimeError("prefix cache state key set must not be empty");
+    const uint64_t modifier_hash =
+        stable_runtime_modifier_hash(reinterpret_cast<const uint8_t *>(runtime_modifier_bytes.data()), runtime_modifier_bytes.size());
+    const PrefixStateCacheKey *best = nullptr;
+    for (const auto &item : entries_) {
+        const PrefixStateCacheKey &key = item.first;
+        if (key.execution_class_id != execution_class_id || key.runtime_graph_id != runtime_graph_id || key.runtime_modifier_hash != modifier_hash ||
+            key.state_keys != state_keys || key.token_count > token_ids.size() || (best != nullptr && key.token_count <= best->token_count))
+            continue;
+        if (std::equal(key.token_ids.begin(), key.token_ids.end(), token_ids.begin())) best = &key;
+    }
+    return best != nullptr ? std::optional<PrefixStateCacheKey>(*best) : std::nullopt;
+}
+
+struct PrefixStateCacheEntrySnapshot {
+    PrefixStateCacheKey key;
+    std::string cached_stream_id;
+    size_t block_count = 0, logical_activation_count = 0;
+    uint64_t last_used_tick = 0;
+    size_t use_count = 0;
+};
+struct PrefixStateCacheSnapshot {
+    size_t capacity_entries = 0, entry_count = 0, eviction_count = 0;
+    std::vector<PrefixStateCacheEntrySnapshot> entries;  // by key
+};
+struct PrefixStateCacheInsert {
+    bool replaced_existing = false;
+    std::vector<PrefixStateCacheKey> evicted_keys;
+};
+
+// The cache of state tables (stream_prefix_cache.rs:104-312): an entry is a fork of the source stream's table, so
+// its blocks stay alive in the arena after the source has moved on or gone; restoring shares them into a fresh table.
+class PrefixStateCache {
+  public:
+    explicit PrefixStateCache(size_t capacity_entries = 0) : index_(capacity_entries) {}
+    size_t capacity_entries() const { return index_.capacity_entries(); }
+    std::vector<PrefixStateCacheKey> set_capacity(StateArena &arena, size_t capacity_entries);
+    bool evict(StateArena &arena, const PrefixStateCacheKey &key);
+    // The source's append states must stand exactly at the key's token count, on a block boundary; its mutable
+    // states must be initialised (stream_prefix_cache.rs:354-403).  With capacity 0 nothing is retained.
+    PrefixStateCacheInsert insert(StateArena &arena, const PrefixStateCacheKey &key, const StateTable &source);
+    bool restore_into(StateArena &arena, const PrefixStateCacheKey &key, StateTable &target);
+    std::optional<PrefixStateCacheKey> longest_matching_key(const std::string &execution_class_id, const std::string &runtime_graph_id,
+                                                            const std::vector<uint32_t> &token_ids, const std::string &runtime_modifier_bytes,
+                                                            std::vector<StateKey> state_keys) const {
+        return index_.longest_matching_key(execution_class_id, runtime_graph_id, token_ids, runtime_modifier_bytes, std::move(state_keys));
+    }
+    PrefixStateCacheSnapshot snapshot() const;
+
+  private:
+    struct Retained {
+        std::string cached_stream_id;
+        StateTable table;
+    };
+    std::vector<PrefixStateCacheKey> release(StateArena &arena, PrefixCacheIndex<Retained>::Removed removed);
+    PrefixCacheIndex<Retained> index_;
+};
+
 // ---------------------------------------------------------------------------------------------- scheduler
 
 enum class StreamStatus { Idle = 0, Active = 1, Interrupted = 2, Closing = 3 };
@@ -265,6 +447,19 @@ struct SchedulerRun {
 class StreamScheduler {
   public:
     using Declarations = std::vector<std::pair<StateKey, BlockShape>>;
+    explicit StreamScheduler(size_t prefix_state_cache_capacity = 0) : prefix_cache_(prefix_state_cache_capacity) {}
+    // prefix-state cache (stream_runtime.rs:541-559, 616-705)
+    PrefixStateCacheSnapshot prefix_state_cache_snapshot() const { return prefix_cache_.snapshot(); }
+    std::vector<PrefixStateCacheKey> set_prefix_state_cache_capacity(size_t capacity_entries) { return prefix_cache_.set_capacity(arena_, capacity_entries); }
+    bool evict_prefix_state(const PrefixStateCacheKey &key) { return prefix_cache_.evict(arena_, key); }
+    PrefixStateCacheInsert cache_stream_prefix_state(const std::string &stream_id, const PrefixStateCacheKey &key);
+    PrefixStateCacheKey cache_stream_prefix_state_for_tokens(const std::string &stream_id, const std::string &runtime_graph_id,
+                                                             const std::vector<uint32_t> &token_ids, const std::string &runtime_modifier_bytes,
+                                                             std::vector<StateKey> state_keys);
+    bool restore_stream_prefix_state(const std::string &target_stream_id, const PrefixStateCacheKey &key);
+    std::optional<PrefixStateCacheKey> restore_longest_stream_prefix_state(const std::string &target_stream_id, const std::string &runtime_graph_id,
+                                                                           const std::vector<uint32_t> &token_ids,
+                                                                           const std::string &runtime_modifier_bytes, std::vector<StateKey> state_keys);
     StreamSnapshot add_stream(const std::string &stream_id, const std::string &execution_class_id = "default",
                               const Declarations &state_declarations = {});
     StreamSnapshot declare_stream_state(const std::string &stream_id, const StateKey &key, const BlockShape &shape);
@@ -324,6 +519,7 @@ class StreamScheduler {
     std::deque<std::string> active_queue_;
     std::map<uint64_t, Activation> in_flight_;
     StateArena arena_;
+    PrefixStateCache prefix_cache_;
     uint64_t next_activation_id_ = 0;
 };
 

@@ -1,6 +1,7 @@
 // Behavioural cases for llmoop_b200/csrc/stream_runtime.cpp, one per scenario the reference's own unit tests pin:
 //   runtime-rs/src/stream_state.rs:761-985           (arena and state tables)
-//   runtime-rs/src/stream_runtime_tests.rs:16-516, 771-1337 (scheduler; the prefix-cache cases :518-769 are out of scope)
+//   runtime-rs/src/stream_runtime_tests.rs:16-1337   (scheduler, its prefix-cache hooks :518-769 included)
+//   runtime-rs/src/stream_prefix_cache.rs:406-583     (prefix-state cache)
 // Same inputs, same expected values, written against the C++ API.  Usage: stream_runtime_cases [case name]; prints
 // "ok <name>" or "FAIL <name>: <what>" per case and exits with the number of failures.
 #include <cstdio>
@@ -608,6 +609,187 @@ std::vector<Case> cases() {
         const StreamSnapshot done = scheduler.complete_activation(decode.id, ActivationOutcome::generated({5}, true));
         CHECK(done.status == StreamStatus::Idle && done.completed_input_event_count == 1);
         scheduler.enqueue_input_event("stream_a", event("event_3", {4}, 1));  // open again once the event is over
+    }});
+
+    // ------------------------------------------------------------------ prefix-state cache (stream_prefix_cache.rs:406-583)
+    auto layer_key = [](const char *state_id) { return StateKey{"layer_00", state_id}; };
+    auto cache_key = [](std::vector<uint32_t> tokens, std::vector<StateKey> state_keys) {
+        return PrefixStateCacheKey::from_token_prefix("package_a", "graph_a", tokens, "reasoning=true", std::move(state_keys));
+    };
+    all.push_back({"prefix_cache_key_normalizes_state_keys_and_hashes_prefix_contents", [=] {
+        const PrefixStateCacheKey left = cache_key({1, 2, 3}, {layer_key("v"), layer_key("k"), layer_key("k")});
+        const PrefixStateCacheKey right = cache_key({1, 2, 3}, {layer_key("k"), layer_key("v")});
+        const PrefixStateCacheKey different_tokens = cache_key({1, 2, 4}, {layer_key("k"), layer_key("v")});
+        CHECK(left == right);
+        CHECK(left.token_hash != different_tokens.token_hash);
+        CHECK(left.state_keys == (std::vector<StateKey>{layer_key("k"), layer_key("v")}));
+        // FNV-1a, 64 bit, of "nerve:token-prefix:v1" | u64 count | u32 tokens, all little-endian: worked by hand for
+        // the empty sequence from the published offset and prime
+        uint64_t expected = 0xcbf29ce484222325ull;
+        for (const char *c = "nerve:token-prefix:v1"; *c; c++) expected = (expected ^ static_cast<uint8_t>(*c)) * 0x100000001b3ull;
+        for (int i = 0; i < 8; i++) expected = (expected ^ 0u) * 0x100000001b3ull;
+        CHECK(stable_token_prefix_hash(nullptr, 0) == expected);
+        CHECK(error_of([&] { cache_key({}, {layer_key("k")}); }).find("token prefix must not be empty") != std::string::npos);
+        CHECK(error_of([&] { cache_key({1}, {}); }).find("state key set must not be empty") != std::string::npos);
+    }});
+    all.push_back({"prefix_cache_eviction_releases_retained_state_blocks", [=] {
+        StateArena arena;
+        StateTable first("source_a"), second("source_b");
+        const BlockShape shape = BlockShape::append(16, 2);
+        first.declare_state(layer_key("kv"), shape);
+        second.declare_state(layer_key("kv"), shape);
+        first.append_activations(arena, layer_key("kv"), 2);
+        second.append_activations(arena, layer_key("kv"), 2);
+        const BlockId first_block = first.snapshot().entries[0].block_ids[0], second_block = second.snapshot().entries[0].block_ids[0];
+        PrefixStateCache cache(1);
+        cache.insert(arena, cache_key({1, 2}, {layer_key("kv")}), first);
+        CHECK(arena.ref_count(first_block) == 2);
+        const PrefixStateCacheInsert inserted = cache.insert(arena, cache_key({3, 4}, {layer_key("kv")}), second);
+        CHECK(inserted.evicted_keys.size() == 1 && inserted.evicted_keys[0] == cache_key({1, 2}, {layer_key("kv")}) && !inserted.replaced_existing);
+        CHECK(cache.snapshot().entry_count == 1 && cache.snapshot().eviction_count == 1);
+        CHECK(arena.ref_count(first_block) == 1);
+        CHECK(arena.ref_count(second_block) == 2);
+    }});
+    all.push_back({"prefix_cache_rejects_non_block_aligned_state", [=] {
+        StateArena arena;
+        StateTable source("source");
+        source.declare_state(layer_key("kv"), BlockShape::append(16, 2));
+        source.append_activations(arena, layer_key("kv"), 1);
+        PrefixStateCache cache(1);
+        const std::string error = error_of([&] { cache.insert(arena, cache_key({1}, {layer_key("kv")}), source); });
+        CHECK(error.find("is not aligned to block capacity") != std::string::npos);
+        CHECK(cache.snapshot().entry_count == 0);
+        CHECK(arena.snapshot().blocks[0].ref_count == 1);
+    }});
+    all.push_back({"prefix_cache_accepts_initialized_mutable_state_alongside_aligned_append_state", [=] {
+        StateArena arena;
+        StateTable source("source");
+        source.declare_state(layer_key("kv"), BlockShape::append(16, 2));
+        source.declare_state(layer_key("recurrent"), BlockShape::mutable_singleton(64));
+        source.append_activations(arena, layer_key("kv"), 2);
+        source.append_activations(arena, layer_key("recurrent"), 2);
+        PrefixStateCache cache(1);
+        cache.insert(arena, cache_key({1, 2}, {layer_key("kv"), layer_key("recurrent")}), source);
+        CHECK(cache.snapshot().entry_count == 1);
+        CHECK(cache.snapshot().entries[0].block_count == 2);
+        CHECK(cache.snapshot().entries[0].cached_stream_id == "prefix_cache_0");
+    }});
+    all.push_back({"prefix_cache_rejects_key_that_does_not_match_source_state_depth", [=] {
+        StateArena arena;
+        StateTable source("source");
+        source.declare_state(layer_key("kv"), BlockShape::append(16, 2));
+        source.append_activations(arena, layer_key("kv"), 2);
+        PrefixStateCache cache(1);
+        const std::string error = error_of([&] { cache.insert(arena, cache_key({1, 2, 3, 4}, {layer_key("kv")}), source); });
+        CHECK(error.find("does not match source state") != std::string::npos);
+        CHECK(cache.snapshot().entry_count == 0);
+        CHECK(arena.snapshot().blocks[0].ref_count == 1);
+    }});
+    all.push_back({"prefix_cache_finds_longest_compatible_token_prefix", [=] {
+        StateArena arena;
+        StateTable short_source("short_source"), long_source("long_source");
+        short_source.declare_state(layer_key("kv"), BlockShape::append(16, 2));
+        long_source.declare_state(layer_key("kv"), BlockShape::append(16, 2));
+        short_source.append_activations(arena, layer_key("kv"), 2);
+        long_source.append_activations(arena, layer_key("kv"), 4);
+        PrefixStateCache cache(4);
+        cache.insert(arena, cache_key({1, 2}, {layer_key("kv")}), short_source);
+        cache.insert(arena, cache_key({1, 2, 3, 4}, {layer_key("kv")}), long_source);
+        const auto matched = cache.longest_matching_key("package_a", "graph_a", {1, 2, 3, 4, 5, 6}, "reasoning=true", {layer_key("kv")});
+        CHECK(matched.has_value() && matched->token_count == 4);
+        const uint32_t four[4] = {1, 2, 3, 4};
+        CHECK(matched->token_hash == stable_token_prefix_hash(four, 4));
+        CHECK(!cache.longest_matching_key("package_a", "graph_a", {1, 2, 3, 4, 5, 6}, "reasoning=false", {layer_key("kv")}).has_value());
+        // a sequence that parts from the long entry after two tokens falls back to the short one; other packages and
+        // graphs see nothing
+        const auto shorter = cache.longest_matching_key("package_a", "graph_a", {1, 2, 9, 4}, "reasoning=true", {layer_key("kv")});
+        CHECK(shorter.has_value() && shorter->token_count == 2);
+        CHECK(!cache.longest_matching_key("package_b", "graph_a", {1, 2, 3, 4}, "reasoning=true", {layer_key("kv")}).has_value());
+        CHECK(!cache.longest_matching_key("package_a", "graph_b", {1, 2, 3, 4}, "reasoning=true", {layer_key("kv")}).has_value());
+        CHECK(!cache.longest_matching_key("package_a", "graph_a", {}, "reasoning=true", {layer_key("kv")}).has_value());
+    }});
+    all.push_back({"prefix_cache_evicts_the_least_recently_used_entry_and_keeps_nothing_at_capacity_zero", [=] {
+        StateArena arena;
+        StateTable a("a"), b("b"), c("c"), target("target");
+        for (StateTable *table : {&a, &b, &c}) {
+            table->declare_state(layer_key("kv"), BlockShape::append(16, 2));
+            table->append_activations(arena, layer_key("kv"), 2);
+        }
+        target.declare_state(layer_key("kv"), BlockShape::append(16, 2));
+        PrefixStateCache cache(2);
+        cache.insert(arena, cache_key({1, 2}, {layer_key("kv")}), a);
+        cache.insert(arena, cache_key({3, 4}, {layer_key("kv")}), b);
+        CHECK(cache.restore_into(arena, cache_key({1, 2}, {layer_key("kv")}), target));  // a is now the more recently used one
+        CHECK(target.snapshot().logical_activation_count == 2);
+        const PrefixStateCacheInsert inserted = cache.insert(arena, cache_key({5, 6}, {layer_key("kv")}), c);
+        CHECK(inserted.evicted_keys.size() == 1 && inserted.evicted_keys[0] == cache_key({3, 4}, {layer_key("kv")}));
+        CHECK(!cache.restore_into(arena, cache_key({3, 4}, {layer_key("kv")}), target));
+        const std::vector<PrefixStateCacheKey> dropped = cache.set_capacity(arena, 0);
+        CHECK(dropped.size() == 2 && cache.snapshot().entry_count == 0 && cache.snapshot().eviction_count == 3);
+        CHECK(!cache.insert(arena, cache_key({1, 2}, {layer_key("kv")}), a).replaced_existing && cache.snapshot().entry_count == 0);
+    }});
+
+    // ------------------------------------------------------------------ scheduler hooks (stream_runtime_tests.rs:518-769)
+    all.push_back({"scheduler_prefix_cache_restores_state_after_source_reset", [] {
+        const PrefixStateCacheKey prefix_key = PrefixStateCacheKey::from_token_prefix("package_a", "graph_a", {1, 2}, "reasoning=true", {state_key()});
+        StreamScheduler scheduler(2);
+        scheduler.add_stream("source", "package_a", {{state_key(), state_shape()}});
+        scheduler.enqueue_input_event("source", event("event_0", {1, 2}, 8));
+        const Activation prefill = first_activation(scheduler, budget(1));
+        scheduler.complete_activation(prefill.id, ActivationOutcome::prefill_complete());
+        scheduler.cache_stream_prefix_state("source", prefix_key);
+        const BlockId cached_block = scheduler.stream_transient_state_snapshot("source").entries[0].block_ids[0];
+        auto ref_count = [&](BlockId id) {
+            for (const BlockSnapshot &block : scheduler.transient_state_arena_snapshot().blocks)
+                if (block.block_id == id) return block.ref_count;
+            throw CaseFailure{"block not in the arena"};
+        };
+        CHECK(ref_count(cached_block) == 2);
+        scheduler.interrupt_stream("source", "drop source");
+        scheduler.reset_stream_transient_state("source");
+        scheduler.add_stream("target", "package_a", {{state_key(), state_shape()}});
+        CHECK(scheduler.restore_stream_prefix_state("target", prefix_key));
+        CHECK(scheduler.stream_transient_state_snapshot("target").entries[0].block_ids == std::vector<BlockId>{cached_block});
+        const PrefixStateCacheSnapshot cache = scheduler.prefix_state_cache_snapshot();
+        CHECK(cache.entry_count == 1 && cache.entries[0].use_count == 1);
+        CHECK(ref_count(cached_block) == 2);
+    }});
+    all.push_back({"scheduler_prefix_cache_rejects_execution_class_mismatch_without_mutation", [] {
+        const PrefixStateCacheKey prefix_key = PrefixStateCacheKey::from_token_prefix("package_a", "graph_a", {1, 2}, "reasoning=true", {state_key()});
+        StreamScheduler scheduler(2);
+        scheduler.add_stream("source", "package_a", {{state_key(), state_shape()}});
+        scheduler.add_stream("target", "package_b", {{state_key(), state_shape()}});
+        scheduler.enqueue_input_event("source", event("event_0", {1, 2}, 8));
+        const Activation prefill = first_activation(scheduler, budget(1));
+        scheduler.complete_activation(prefill.id, ActivationOutcome::prefill_complete());
+        scheduler.cache_stream_prefix_state("source", prefix_key);
+        const TableSnapshot before_target = scheduler.stream_transient_state_snapshot("target");
+        const std::string error = error_of([&] { scheduler.restore_stream_prefix_state("target", prefix_key); });
+        CHECK(error.find("cannot restore prefix key execution class") != std::string::npos);
+        CHECK(scheduler.stream_transient_state_snapshot("target") == before_target);
+        CHECK(scheduler.prefix_state_cache_snapshot().entries[0].use_count == 0);
+        CHECK(error_of([&] { scheduler.cache_stream_prefix_state("target", prefix_key); }).find("under prefix key execution class") != std::string::npos);
+    }});
+    all.push_back({"scheduler_restores_longest_matching_prefix_state", [] {
+        StreamScheduler scheduler(4);
+        scheduler.add_stream("short_source", "package_a", {{state_key(), state_shape()}});
+        scheduler.add_stream("long_source", "package_a", {{state_key(), state_shape()}});
+        scheduler.enqueue_input_event("short_source", event("short_event", {1, 2}, 0));
+        const Activation short_prefill = first_activation(scheduler, budget(1));
+        scheduler.complete_activation(short_prefill.id, ActivationOutcome::prefill_complete());
+        scheduler.enqueue_input_event("long_source", event("long_event", {1, 2, 3, 4}, 0));
+        for (int i = 0; i < 2; i++) {
+            const Activation prefill = first_activation(scheduler, budget(1));
+            scheduler.complete_activation(prefill.id, ActivationOutcome::prefill_complete());
+        }
+        const PrefixStateCacheKey short_key = scheduler.cache_stream_prefix_state_for_tokens("short_source", "graph_a", {1, 2}, "reasoning=true", {state_key()});
+        const PrefixStateCacheKey long_key = scheduler.cache_stream_prefix_state_for_tokens("long_source", "graph_a", {1, 2, 3, 4}, "reasoning=true", {state_key()});
+        scheduler.add_stream("target", "package_a", {{state_key(), state_shape()}});
+        const auto matched = scheduler.restore_longest_stream_prefix_state("target", "graph_a", {1, 2, 3, 4, 5}, "reasoning=true", {state_key()});
+        CHECK(matched.has_value() && *matched == long_key && *matched != short_key);
+        CHECK(scheduler.stream_transient_state_snapshot("target").logical_activation_count == 4);
+        for (const PrefixStateCacheEntrySnapshot &entry : scheduler.prefix_state_cache_snapshot().entries)
+            CHECK(entry.use_count == (entry.key == long_key ? 1u : 0u));
     }});
     return all;
 }

@@ -27,7 +27,7 @@ def cases_binary(tmp_path_factory):
 
 def test_reference_pinned_cases_all_pass(cases_binary):
     names = subprocess.run([str(cases_binary), "--list"], capture_output=True, text=True, check=True).stdout.split()
-    assert len(names) >= 40
+    assert len(names) >= 50
     result = subprocess.run([str(cases_binary)], capture_output=True, text=True)
     lines = result.stdout.strip().splitlines()
     failed = [line for line in lines if not line.startswith("ok ")]
