@@ -125,6 +125,22 @@ int32_t nerve_b200_engine_snapshot(nerve_b200_engine *engine, nerve_b200_engine_
  * dropped (reset, interrupt, stop after current). */
 int32_t nerve_b200_engine_scheduler_stream_counts(nerve_b200_engine *engine, int64_t stream_id, uint64_t out_counts[6]);
 
+/* Prefix-state cache (stream_prefix_cache.rs:104-312; placed_prefix_state_cache.rs:50-365; the engine's use of both,
+ * placed_prompt_engine.rs:190-280 and 964-1060).  With a capacity of N > 0 entries, a prompt's prefill stops once at
+ * the prompt's last KV page boundary and retains the stream's state there under the tokens that produced it (one
+ * checkpoint per stream, the latest; least recently used entries leave first); nerve_b200_engine_enqueue on a fresh
+ * stream (tick 0, nothing queued) whose tokens - all but the last - begin with a retained prefix starts the stream at
+ * that state and prefills only the rest.  The sampler settings and the draft count of the stream are part of the key.
+ * Retaining copies no KV: the entry holds references to the stream's pages (copy-on-write, as after a fork) and one
+ * hidden-state frame.  Capacity 0 (the default) switches the cache off; every call drops what was retained.  The
+ * reference keeps the cache always on with streams + 1 entries; here it is the caller's choice because a prefill
+ * cut at the boundary runs other batch shapes, so the low bits of the logits may differ from an uncut prefill.
+ * out_stats (VulkanResidentPlacedPrefixStateCacheStats, placed_prefix_state_cache.rs:38-48): [0] hit_count,
+ * [1] miss_count, [2] insertion_count, [3] eviction_count, [4] reused_token_count, [5] saved_prefill_token_count,
+ * [6] resident_entry_count, [7] resident_byte_count (KV bytes the entries keep alive, shared pages counted per entry). */
+int32_t nerve_b200_engine_set_prefix_cache_capacity(nerve_b200_engine *engine, uint64_t entries);
+int32_t nerve_b200_engine_prefix_cache_stats(nerve_b200_engine *engine, uint64_t out_stats[8]);
+
 /* enqueue_input_event (placed_prompt_engine.rs:256-331): VulkanResidentTokenInputEvent
  * {id, token_ids, max_public_tokens, stop_token_ids}. */
 int32_t nerve_b200_engine_enqueue(nerve_b200_engine *engine, int64_t stream_id, const char *event_id,

@@ -295,6 +295,25 @@ int32_t nerve_b200_engine_scheduler_stream_counts(nerve_b200_engine *engine, int
     });
 }
 
+int32_t nerve_b200_engine_set_prefix_cache_capacity(nerve_b200_engine *engine, uint64_t entries) {
+    return guarded([&] {
+        require(engine != nullptr, "null argument");
+        engine->engine->set_prefix_cache_capacity(static_cast<size_t>(entries));
+    });
+}
+
+int32_t nerve_b200_engine_prefix_cache_stats(nerve_b200_engine *engine, uint64_t out_stats[8]) {
+    return guarded([&] {
+        require(engine != nullptr && out_stats != nullptr, "null argument");
+        const Engine::PrefixCacheStats stats = engine->engine->prefix_cache_stats();
+        const uint64_t values[8] = {stats.hit_count,          stats.miss_count,
+                                    stats.insertion_count,    stats.eviction_count,
+                                    stats.reused_token_count, stats.saved_prefill_token_count,
+                                    stats.resident_entry_count, stats.resident_byte_count};
+        for (int i = 0; i < 8; i++) out_stats[i] = values[i];
+    });
+}
+
 int32_t nerve_b200_engine_snapshot(nerve_b200_engine *engine, nerve_b200_engine_snapshot_counts *out) {
     return guarded([&] {
         require(engine != nullptr && out != nullptr, "null argument");

@@ -602,7 +602,7 @@ Engine::~Engine() {
     for (auto &entry : signals_) cudaFree(entry.second.ptr);
     for (DeviceBuffer *buffer : {&frame_a_, &frame_b_, &embedding_out_, &normalized_, &draft_normalized_, &draft_hidden_in_, &logits_,
                                  &records_, &argmax_scratch_, &sampler_scratch_, &sampler_table_, &lane_tokens_, &lane_positions_, &lane_slots_, &pending_hidden_, &pending_backup_, &attention_scratch_,
-                                 &cycle_state_, &kernel_error_, &tp_partial_, &tp_exchange_, &tp_description_, &stack_q_, &stack_attention_out_, &stack_activation_, &stack_barrier_, &stack_timing_})
+                                 &cycle_state_, &kernel_error_, &tp_partial_, &tp_exchange_, &tp_description_, &stack_q_, &stack_attention_out_, &stack_activation_, &stack_barrier_, &stack_timing_, &prefix_pending_})
         cudaFree(buffer->ptr);
     cudaFreeHost(staging_);
     cudaFreeHost(host_records_);
@@ -831,6 +831,7 @@ void Engine::remove_stream(int64_t id) {
     release_pages(s);
     if (s.sampler.method != 0) stochastic_streams_--;
     free_slots_.push_back(s.slot);
+    latest_checkpoint_by_stream_.erase(id);
     streams_.erase(id);
     rejoin_scheduler(id);
     scheduler_.remove_stream(scheduler_id(id));
@@ -840,6 +841,8 @@ void Engine::reset_stream(int64_t id) {
     Stream &s = stream(id);
     release_pages(s);
     s.next_tick = 0;
+    s.history.clear();
+    latest_checkpoint_by_stream_.erase(id);  // the retained state itself stays until it is the least recently used
     s.queue.clear();
     s.active.reset();
     s.detached = false;
@@ -918,6 +921,7 @@ void Engine::fork_stream(int64_t source, int64_t destination, uint32_t seed) {
     scheduler_.fork_stream_transient_state(scheduler_id(source), scheduler_id(destination), "default");
     Stream &dst = stream(destination);
     dst.next_tick = src.next_tick;
+    dst.history = src.history;
     // Every mapped page is shared by reference count, no copies (stream_state.rs:474-496); the first write of
     // either stream to a shared page replaces it with a private copy (ensure_pages, copy-on-write).
     for (size_t page = 0; page < src.pages.size(); page++) {
@@ -933,18 +937,150 @@ void Engine::fork_stream(int64_t source, int64_t destination, uint32_t seed) {
                "fork pending hidden");
 }
 
+// ---------------------------------------------------------------------------- prefix-state cache
+
+namespace {
+const char *const PREFIX_EXECUTION_CLASS = "default";
+const runtime::StateKey PREFIX_STATE_KEY{"kv", "pages"};
+}  // namespace
+
+// What shaped the state besides the tokens (placed_prompt_engine.rs:1463-1480): the sampler and the draft count.
+std::string Engine::prefix_modifier_bytes(const Stream &s) const {
+    char text[192];
+    std::snprintf(text, sizeof(text), "nerve.prefix_state_runtime_modifiers.v1;method=%d;temperature=%.9g;top_k=%d;top_p=%.9g;min_p=%.9g;drafts=%d",
+                  s.sampler.method, s.sampler.temperature, s.sampler.top_k, s.sampler.top_p, s.sampler.min_p, s.k);
+    return text;
+}
+
+void Engine::release_checkpoint(PrefixCheckpoint &checkpoint) {
+    for (int32_t page : checkpoint.pages)
+        if (page >= 0 && --page_refcount_[page] == 0) free_pages_.push_back(page);
+    checkpoint.pages.clear();
+    if (checkpoint.pending_slot >= 0) free_pending_slots_.push_back(checkpoint.pending_slot);
+    checkpoint.pending_slot = -1;
+}
+
+void Engine::set_prefix_cache_capacity(size_t entries) {
+    if (entries > 4096) fail("prefix cache capacity must be at most 4096 entries");
+    for (auto &removed : prefix_index_.set_capacity(0)) release_checkpoint(removed.second);
+    latest_checkpoint_by_stream_.clear();
+    cuda_check(cudaStreamSynchronize(cuda_stream_), "prefix cache synchronize");
+    cudaFree(prefix_pending_.ptr);
+    prefix_pending_ = DeviceBuffer{};
+    free_pending_slots_.clear();
+    if (entries == 0) return;
+    const size_t frame = static_cast<size_t>(model_->plan().hidden) * 2;
+    prefix_pending_ = device_alloc((entries + 1) * frame);  // one frame more: an entry is filed before the oldest one leaves
+    for (size_t slot = 0; slot <= entries; slot++) free_pending_slots_.push_back(static_cast<int>(slot));
+    prefix_index_.set_capacity(entries);
+}
+
+Engine::PrefixCacheStats Engine::prefix_cache_stats() const {
+    PrefixCacheStats stats = prefix_stats_;
+    stats.resident_entry_count = prefix_index_.entries().size();
+    const uint64_t page_bytes = model_->kv_bytes_per_token() * static_cast<uint64_t>(model_->options().page_tokens);
+    for (const auto &item : prefix_index_.entries())
+        stats.resident_byte_count += item.second.payload.pages.size() * page_bytes + static_cast<uint64_t>(model_->plan().hidden) * 2;
+    return stats;
+}
+
+// The tick at which the prompt being prefilled gets its checkpoint: the last page boundary of the prompt (fewer
+// than a page of prompt tokens remain there, capture_aligned_prefix_checkpoint, placed_prompt_engine.rs:964-1005),
+// provided the stream's tokens are known from tick 0 and the ring has not wrapped.  0 = no checkpoint.
+uint64_t Engine::prefix_checkpoint_tick(const Stream &s) const {
+    if (!prefix_cache_on() || !s.active || s.history.size() != s.next_tick) return 0;
+    const uint64_t page = static_cast<uint64_t>(model_->options().page_tokens);
+    const uint64_t prompt_end = s.next_tick + (s.active->input.token_ids.size() - s.active->next_external);
+    const uint64_t boundary = prompt_end / page * page;
+    return boundary <= model_->capacity() ? boundary : 0;
+}
+
+void Engine::capture_prefix_checkpoint(Stream &s) {
+    const size_t page_tokens = static_cast<size_t>(model_->options().page_tokens);
+    const size_t page_count = static_cast<size_t>(s.next_tick) / page_tokens;
+    if (page_count == 0 || s.history.size() != s.next_tick || free_pending_slots_.empty()) return;
+    PrefixCheckpoint checkpoint;
+    for (size_t page = 0; page < page_count; page++) {
+        if (s.pages[page] < 0) return;  // not all of the prefix is resident
+        checkpoint.pages.push_back(s.pages[page]);
+    }
+    const runtime::PrefixStateCacheKey key = runtime::PrefixStateCacheKey::from_token_prefix(PREFIX_EXECUTION_CLASS, model_->package().directory(), s.history,
+                                                                                             prefix_modifier_bytes(s), {PREFIX_STATE_KEY});
+    for (int32_t page : checkpoint.pages) page_refcount_[page]++;
+    checkpoint.pending_slot = free_pending_slots_.back();
+    free_pending_slots_.pop_back();
+    const size_t frame = static_cast<size_t>(model_->plan().hidden) * 2;
+    cuda_check(cudaMemcpyAsync(static_cast<uint8_t *>(prefix_pending_.ptr) + checkpoint.pending_slot * frame,
+                               static_cast<uint8_t *>(pending_hidden_.ptr) + s.slot * frame, frame, cudaMemcpyDeviceToDevice, cuda_stream_),
+               "prefix checkpoint pending hidden");
+    auto inserted = prefix_index_.insert(key, std::move(checkpoint));
+    prefix_stats_.insertion_count++;
+    if (inserted.replaced) release_checkpoint(*inserted.replaced);
+    std::set<runtime::PrefixStateCacheKey> gone;
+    for (auto &removed : inserted.evicted) {
+        release_checkpoint(removed.second);
+        gone.insert(removed.first);
+        prefix_stats_.eviction_count++;
+    }
+    // a stream keeps one checkpoint, its latest (placed_prompt_engine.rs:1046-1057)
+    auto previous = latest_checkpoint_by_stream_.find(s.id);
+    if (previous != latest_checkpoint_by_stream_.end() && previous->second != key && !gone.count(previous->second)) {
+        if (auto removed = prefix_index_.evict(previous->second)) {
+            release_checkpoint(*removed);
+            prefix_stats_.eviction_count++;
+        }
+    }
+    for (auto it = latest_checkpoint_by_stream_.begin(); it != latest_checkpoint_by_stream_.end();)
+        it = gone.count(it->second) ? latest_checkpoint_by_stream_.erase(it) : std::next(it);
+    latest_checkpoint_by_stream_.insert_or_assign(s.id, key);
+}
+
+// Only a fresh, idle stream takes a retained prefix, and the prompt's last token is always prefilled (it produces
+// the first output): placed_prompt_engine.rs:198-253.
+size_t Engine::restore_longest_prefix(Stream &s, const std::vector<uint32_t> &token_ids) {
+    if (!prefix_cache_on() || s.next_tick != 0 || s.active || !s.queue.empty() || !s.history.empty() || token_ids.size() <= 1) return 0;
+    for (int32_t page : s.pages)
+        if (page >= 0) return 0;
+    const std::vector<uint32_t> restorable(token_ids.begin(), token_ids.end() - 1);
+    const std::optional<runtime::PrefixStateCacheKey> key =
+        prefix_index_.longest_matching_key(PREFIX_EXECUTION_CLASS, model_->package().directory(), restorable, prefix_modifier_bytes(s), {PREFIX_STATE_KEY});
+    if (!key) {
+        prefix_stats_.miss_count++;
+        return 0;
+    }
+    const PrefixCheckpoint &checkpoint = *prefix_index_.use(*key);
+    for (size_t page = 0; page < checkpoint.pages.size(); page++) {
+        s.pages[page] = checkpoint.pages[page];
+        page_refcount_[checkpoint.pages[page]]++;
+    }
+    s.block_table_dirty = true;
+    const size_t frame = static_cast<size_t>(model_->plan().hidden) * 2;
+    cuda_check(cudaMemcpyAsync(static_cast<uint8_t *>(pending_hidden_.ptr) + s.slot * frame,
+                               static_cast<uint8_t *>(prefix_pending_.ptr) + checkpoint.pending_slot * frame, frame, cudaMemcpyDeviceToDevice, cuda_stream_),
+               "prefix restore pending hidden");
+    s.next_tick = key->token_count;
+    s.history = key->token_ids;
+    prefix_stats_.hit_count++;
+    prefix_stats_.reused_token_count += key->token_count;
+    prefix_stats_.saved_prefill_token_count += key->token_count;
+    return key->token_count;
+}
+
 void Engine::enqueue(int64_t id, const InputEvent &event) {
     Stream &s = stream(id);
     if (event.token_ids.empty()) fail("input event has no tokens");
     if (event.stop_token_ids.size() > MAX_STOP_TOKENS) fail("at most 8 stop tokens are supported per event");
     for (uint32_t token : event.token_ids)
         if (token >= static_cast<uint32_t>(model_->plan().vocab)) fail("input token id is outside the vocabulary");
+    InputEvent accepted = event;
+    const size_t reused = restore_longest_prefix(s, event.token_ids);
+    if (reused > 0) accepted.token_ids.erase(accepted.token_ids.begin(), accepted.token_ids.begin() + static_cast<std::ptrdiff_t>(reused));
     runtime::InputEvent scheduled;
-    scheduled.id = event.id.empty() ? std::string("event") : event.id;
-    scheduled.token_ids = event.token_ids;
-    scheduled.max_public_tokens = event.max_public_tokens;
+    scheduled.id = accepted.id.empty() ? std::string("event") : accepted.id;
+    scheduled.token_ids = accepted.token_ids;
+    scheduled.max_public_tokens = accepted.max_public_tokens;
     scheduler_.enqueue_input_event(scheduler_id(id), scheduled);
-    s.queue.push_back(event);
+    s.queue.push_back(std::move(accepted));
 }
 
 void Engine::set_teacher_tokens(int64_t id, const std::vector<uint32_t> &tokens) { stream(id).teacher = tokens; }
@@ -1630,6 +1766,7 @@ void Engine::run_single_ticks(std::vector<Stream *> &batch, const std::function<
         Stream &s = *batch[i];
         ActiveEvent &event = *s.active;
         uint64_t tick = s.next_tick;
+        if (prefix_cache_on() && s.history.size() == s.next_tick) s.history.push_back(tokens[i]);
         s.next_tick += 1;
         bool was_closing = event.feedback_closes;
         bool should_emit = !was_closing && event.remaining > 0;
@@ -1781,8 +1918,10 @@ void Engine::run_speculative_cycles(std::vector<Stream *> &batch, int drafts, co
             cycle_log_.push_back(std::move(record));
         }
         st.active->has_feedback = false;
+        const uint32_t fed_back = st.active->feedback_token;  // the input of the cycle's first tick; every later tick takes the token before it
         for (uint32_t i = 0; i < count; i++) {
             uint64_t tick = st.next_tick;
+            if (prefix_cache_on() && st.history.size() == st.next_tick) st.history.push_back(i == 0 ? fed_back : row[4 + i - 1]);
             st.next_tick += 1;
             emit(st, row[4 + i], tick, on_output, report);
         }
@@ -1894,11 +2033,19 @@ RunReport Engine::run(uint64_t max_batches, const std::function<void(const Outpu
                 // wrap, and beyond it every tick is a batch of its own.
                 const uint64_t ring = model_->capacity();
                 if (s.next_tick + static_cast<uint64_t>(count) > ring) count = s.next_tick < ring ? static_cast<int>(ring - s.next_tick) : 1;
+                // with the prefix cache on, a chunk also stops at the prompt's last page boundary: the state there is retained
+                const uint64_t checkpoint_tick = prefix_checkpoint_tick(s);
+                if (checkpoint_tick > s.next_tick && checkpoint_tick < s.next_tick + static_cast<uint64_t>(count)) count = static_cast<int>(checkpoint_tick - s.next_tick);
                 const bool last = ends_prompt && static_cast<size_t>(count) == left;
                 const bool sample = last && event.remaining > 0;
                 uint32_t sampled = 0;
                 const uint64_t tick_of_last = s.next_tick + count - 1;
                 run_prefill_chunk(s, event.input.token_ids.data() + event.next_external, count, sample, &sampled);
+                if (prefix_cache_on() && s.history.size() + static_cast<size_t>(count) == s.next_tick) {
+                    s.history.insert(s.history.end(), event.input.token_ids.begin() + static_cast<std::ptrdiff_t>(event.next_external),
+                                     event.input.token_ids.begin() + static_cast<std::ptrdiff_t>(event.next_external + count));
+                    if (checkpoint_tick != 0 && s.next_tick == checkpoint_tick) capture_prefix_checkpoint(s);
+                }
                 event.next_external += count;
                 left -= static_cast<size_t>(count);
                 report.prefill_tokens += count;

@@ -222,6 +222,18 @@ public:
     StreamSnapshot stream_snapshot(int64_t id) const;
     EngineSnapshot snapshot() const;
     void scheduler_stream_counts(int64_t id, uint64_t out_counts[6]) const;
+    // Prefix-state cache (stream_prefix_cache.rs:104-312, placed_prefix_state_cache.rs:50-365,
+    // placed_prompt_engine.rs:190-280, 964-1060).  While a prompt is prefilled, the stream's state at the last
+    // page boundary of the prompt is retained under the tokens that produced it; an input event for a fresh stream
+    // that begins with a retained prefix starts from that state and prefills only the rest.  Retaining copies no KV:
+    // the entry holds references to the stream's (full, never rewritten) pages, as a fork does, plus a copy of the
+    // draft head's pending hidden state.  Off (capacity 0) unless set; setting a capacity drops what is retained.
+    struct PrefixCacheStats {
+        uint64_t hit_count = 0, miss_count = 0, insertion_count = 0, eviction_count = 0, reused_token_count = 0, saved_prefill_token_count = 0,
+                 resident_entry_count = 0, resident_byte_count = 0;
+    };
+    void set_prefix_cache_capacity(size_t entries);
+    PrefixCacheStats prefix_cache_stats() const;
     const std::vector<CycleRecord> &cycle_log() const { return cycle_log_; }
     // Test hook: the next `launches` launches of the persistent decode kernel wait (briefly) at their first grid barrier for
     // an arrival count the grid cannot reach, give up and report it - a failure made without faulting anything.
@@ -267,6 +279,7 @@ private:
         std::unique_ptr<ActiveEvent> active;
         std::vector<int32_t> pages;  // logical page -> physical page (-1 = unmapped)
         std::vector<uint32_t> teacher;
+        std::vector<uint32_t> history;  // the token fed at every tick so far (kept while the prefix cache is on)
         bool block_table_dirty = true;
         uint64_t completed_events = 0;
         bool detached = false;  // the active event was stopped from outside: the scheduler no longer tracks it
@@ -283,6 +296,22 @@ private:
     // engine executes the activations and reports their outcomes (placed_prompt_engine.rs:455-520).
     runtime::StreamScheduler scheduler_;
     std::vector<runtime::Activation> carried_activations_;  // scheduled, but their batch failed: executed first by the next run
+    // prefix-state cache: the index decides what stays (least recently used goes first), the payload is the page list
+    struct PrefixCheckpoint {
+        std::vector<int32_t> pages;  // physical pages of ticks [0, token_count), one reference held on each
+        int pending_slot = -1;       // frame of prefix_pending_ with the draft head's pending hidden state
+    };
+    runtime::PrefixCacheIndex<PrefixCheckpoint> prefix_index_{0};
+    std::map<int64_t, runtime::PrefixStateCacheKey> latest_checkpoint_by_stream_;
+    DeviceBuffer prefix_pending_;  // [capacity + 1][hidden]
+    std::vector<int> free_pending_slots_;
+    PrefixCacheStats prefix_stats_;
+    bool prefix_cache_on() const { return prefix_index_.capacity_entries() > 0; }
+    std::string prefix_modifier_bytes(const Stream &s) const;
+    uint64_t prefix_checkpoint_tick(const Stream &s) const;  // where the active event's prompt gets its checkpoint (0 = nowhere)
+    void capture_prefix_checkpoint(Stream &s);
+    size_t restore_longest_prefix(Stream &s, const std::vector<uint32_t> &token_ids);  // tokens reused
+    void release_checkpoint(PrefixCheckpoint &checkpoint);
     void ensure_pages(Stream &s, uint64_t last_tick);
     void release_pages(Stream &s);
     void sync_block_tables();

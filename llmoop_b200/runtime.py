@@ -76,7 +76,7 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_engine_destroy", "nerve_b200_engine_add_stream", "nerve_b200_engine_fork_stream",
     "nerve_b200_engine_reset_stream", "nerve_b200_engine_remove_stream", "nerve_b200_engine_interrupt_stream",
     "nerve_b200_engine_enqueue", "nerve_b200_engine_run_until_idle", "nerve_b200_engine_run",
-    "nerve_b200_engine_set_profiling", "nerve_b200_engine_inject_barrier_timeouts", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_stop_after_current", "nerve_b200_engine_stream_snapshot_of", "nerve_b200_engine_snapshot", "nerve_b200_engine_scheduler_stream_counts", "nerve_b200_engine_init_tp", "nerve_b200_engine_tp_exchange_handle", "nerve_b200_engine_tp_connect", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
+    "nerve_b200_engine_set_profiling", "nerve_b200_engine_inject_barrier_timeouts", "nerve_b200_tp_unique_id", "nerve_b200_tp_shard_range", "nerve_b200_engine_stop_after_current", "nerve_b200_engine_stream_snapshot_of", "nerve_b200_engine_snapshot", "nerve_b200_engine_scheduler_stream_counts", "nerve_b200_engine_set_prefix_cache_capacity", "nerve_b200_engine_prefix_cache_stats", "nerve_b200_engine_init_tp", "nerve_b200_engine_tp_exchange_handle", "nerve_b200_engine_tp_connect", "nerve_b200_engine_set_decode_stack", "nerve_b200_engine_decode_stack_timing", "nerve_b200_engine_stream_tick",
     "nerve_b200_engine_set_teacher_tokens", "nerve_b200_engine_set_prefill_chunk",
     "nerve_b200_engine_set_cycle_logging", "nerve_b200_engine_cycle_log", "nerve_b200_debug_target_logits",
     "nerve_b200_op_linear_int4", "nerve_b200_op_linear_int4_silu_pair",
@@ -255,6 +255,17 @@ class Engine:
         names = ("scheduled_activation_count", "completed_input_event_count", "generated_token_count", "in_flight_activation_count",
                  "queued_input_event_count", "has_current_input_event")
         return {name: int(value) for name, value in zip(names, counts)}
+
+    def set_prefix_cache_capacity(self, entries: int) -> None:
+        """Retain up to `entries` prompt prefixes (0 = off, the default); see nerve_b200_engine_set_prefix_cache_capacity."""
+        _check(library().nerve_b200_engine_set_prefix_cache_capacity(self._handle, ctypes.c_uint64(entries)))
+
+    def prefix_cache_stats(self) -> dict:
+        stats = (ctypes.c_uint64 * 8)()
+        _check(library().nerve_b200_engine_prefix_cache_stats(self._handle, stats))
+        names = ("hit_count", "miss_count", "insertion_count", "eviction_count", "reused_token_count", "saved_prefill_token_count",
+                 "resident_entry_count", "resident_byte_count")
+        return {name: int(value) for name, value in zip(names, stats)}
 
     def snapshot(self) -> dict:
         raw = _EngineSnapshotCounts()
