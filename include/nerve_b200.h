@@ -385,6 +385,26 @@ int32_t nerve_b200_scheduler_complete(nerve_b200_scheduler *scheduler, uint64_t 
 int32_t nerve_b200_scheduler_snapshot(nerve_b200_scheduler *scheduler, nerve_b200_scheduler_counts *out);
 int32_t nerve_b200_scheduler_stream_snapshot(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out);
 
+/* The scheduler's prefix-state cache (stream_runtime.rs:541-559, 616-705; stream_prefix_cache.rs:104-312).  A new
+ * scheduler has capacity 0 (RuntimeStreamScheduler::default); set_prefix_state_cache_capacity evicts down to the new
+ * capacity and reports how many entries left.  cache_stream_prefix_state_for_tokens retains a fork of the stream's
+ * state table under (the stream's execution class, runtime_graph_id, token_ids, the hash of runtime_modifier_bytes,
+ * all of the stream's state keys): the append states must stand exactly at token_count activations, on a block
+ * boundary.  out_flags bit 0 = an entry of the same key was replaced; out_evicted = entries evicted to make room.
+ * restore_longest_stream_prefix_state shares the blocks of the longest retained prefix of token_ids into the target
+ * stream's (empty) states - the key set is the target's declared states - and writes its token count, 0 when nothing
+ * matches.  prefix_state_cache_counts: [0] capacity_entries, [1] entry_count, [2] eviction_count. */
+int32_t nerve_b200_scheduler_set_prefix_state_cache_capacity(nerve_b200_scheduler *scheduler, uint64_t capacity_entries, uint64_t *out_evicted);
+int32_t nerve_b200_scheduler_cache_stream_prefix_state_for_tokens(nerve_b200_scheduler *scheduler, const char *stream_id, const char *runtime_graph_id,
+                                                                  const uint32_t *token_ids, size_t token_count,
+                                                                  const uint8_t *runtime_modifier_bytes, size_t runtime_modifier_count,
+                                                                  int32_t *out_flags, uint64_t *out_evicted);
+int32_t nerve_b200_scheduler_restore_longest_stream_prefix_state(nerve_b200_scheduler *scheduler, const char *target_stream_id,
+                                                                 const char *runtime_graph_id, const uint32_t *token_ids, size_t token_count,
+                                                                 const uint8_t *runtime_modifier_bytes, size_t runtime_modifier_count,
+                                                                 uint64_t *out_restored_token_count);
+int32_t nerve_b200_scheduler_prefix_state_cache_counts(nerve_b200_scheduler *scheduler, uint64_t out_counts[3]);
+
 #ifdef __cplusplus
 }
 #endif

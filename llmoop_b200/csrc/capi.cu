@@ -809,6 +809,64 @@ int32_t nerve_b200_scheduler_snapshot(nerve_b200_scheduler *scheduler, nerve_b20
     });
 }
 
+int32_t nerve_b200_scheduler_set_prefix_state_cache_capacity(nerve_b200_scheduler *scheduler, uint64_t capacity_entries, uint64_t *out_evicted) {
+    return guarded([&] {
+        require(scheduler != nullptr, "scheduler must not be NULL");
+        const size_t evicted = scheduler->scheduler.set_prefix_state_cache_capacity(static_cast<size_t>(capacity_entries)).size();
+        if (out_evicted != nullptr) *out_evicted = evicted;
+    });
+}
+
+int32_t nerve_b200_scheduler_cache_stream_prefix_state_for_tokens(nerve_b200_scheduler *scheduler, const char *stream_id, const char *runtime_graph_id,
+                                                                  const uint32_t *token_ids, size_t token_count,
+                                                                  const uint8_t *runtime_modifier_bytes, size_t runtime_modifier_count,
+                                                                  int32_t *out_flags, uint64_t *out_evicted) {
+    return guarded([&] {
+        require(scheduler != nullptr && stream_id != nullptr && runtime_graph_id != nullptr, "scheduler and ids must not be NULL");
+        require((token_count == 0 || token_ids != nullptr) && (runtime_modifier_count == 0 || runtime_modifier_bytes != nullptr), "NULL array with a non-zero count");
+        std::vector<nerve::runtime::StateKey> keys;
+        for (const nerve::runtime::EntrySnapshot &entry : scheduler->scheduler.stream_transient_state_snapshot(stream_id).entries) keys.push_back(entry.key);
+        const std::string execution_class = [&] {
+            for (const nerve::runtime::StreamSnapshot &stream : scheduler->scheduler.snapshot().streams)
+                if (stream.stream_id == stream_id) return stream.execution_class_id;
+            throw std::runtime_error(std::string("unknown stream \"") + stream_id + "\"");
+        }();
+        const nerve::runtime::PrefixStateCacheKey key = nerve::runtime::PrefixStateCacheKey::from_token_prefix(
+            execution_class, runtime_graph_id, std::vector<uint32_t>(token_ids, token_ids + token_count),
+            std::string(reinterpret_cast<const char *>(runtime_modifier_bytes), runtime_modifier_count), std::move(keys));
+        const nerve::runtime::PrefixStateCacheInsert inserted = scheduler->scheduler.cache_stream_prefix_state(stream_id, key);
+        if (out_flags != nullptr) *out_flags = inserted.replaced_existing ? 1 : 0;
+        if (out_evicted != nullptr) *out_evicted = inserted.evicted_keys.size();
+    });
+}
+
+int32_t nerve_b200_scheduler_restore_longest_stream_prefix_state(nerve_b200_scheduler *scheduler, const char *target_stream_id,
+                                                                 const char *runtime_graph_id, const uint32_t *token_ids, size_t token_count,
+                                                                 const uint8_t *runtime_modifier_bytes, size_t runtime_modifier_count,
+                                                                 uint64_t *out_restored_token_count) {
+    return guarded([&] {
+        require(scheduler != nullptr && target_stream_id != nullptr && runtime_graph_id != nullptr && out_restored_token_count != nullptr,
+                "scheduler, ids and out must not be NULL");
+        require((token_count == 0 || token_ids != nullptr) && (runtime_modifier_count == 0 || runtime_modifier_bytes != nullptr), "NULL array with a non-zero count");
+        std::vector<nerve::runtime::StateKey> keys;
+        for (const nerve::runtime::EntrySnapshot &entry : scheduler->scheduler.stream_transient_state_snapshot(target_stream_id).entries) keys.push_back(entry.key);
+        const std::optional<nerve::runtime::PrefixStateCacheKey> key = scheduler->scheduler.restore_longest_stream_prefix_state(
+            target_stream_id, runtime_graph_id, std::vector<uint32_t>(token_ids, token_ids + token_count),
+            std::string(reinterpret_cast<const char *>(runtime_modifier_bytes), runtime_modifier_count), std::move(keys));
+        *out_restored_token_count = key ? key->token_count : 0;
+    });
+}
+
+int32_t nerve_b200_scheduler_prefix_state_cache_counts(nerve_b200_scheduler *scheduler, uint64_t out_counts[3]) {
+    return guarded([&] {
+        require(scheduler != nullptr && out_counts != nullptr, "scheduler and out must not be NULL");
+        const nerve::runtime::PrefixStateCacheSnapshot snapshot = scheduler->scheduler.prefix_state_cache_snapshot();
+        out_counts[0] = snapshot.capacity_entries;
+        out_counts[1] = snapshot.entry_count;
+        out_counts[2] = snapshot.eviction_count;
+    });
+}
+
 int32_t nerve_b200_scheduler_stream_snapshot(nerve_b200_scheduler *scheduler, const char *stream_id, nerve_b200_stream_snapshot *out) {
     return guarded([&] {
         require(scheduler != nullptr && stream_id != nullptr && out != nullptr, "scheduler, stream_id and out must not be NULL");

@@ -89,6 +89,8 @@ EXPORTED_SYMBOLS = (
     "nerve_b200_scheduler_close_after_current", "nerve_b200_scheduler_schedule_step",
     "nerve_b200_scheduler_step_activation", "nerve_b200_scheduler_step_reservation", "nerve_b200_scheduler_complete",
     "nerve_b200_scheduler_snapshot", "nerve_b200_scheduler_stream_snapshot",
+    "nerve_b200_scheduler_set_prefix_state_cache_capacity", "nerve_b200_scheduler_cache_stream_prefix_state_for_tokens",
+    "nerve_b200_scheduler_restore_longest_stream_prefix_state", "nerve_b200_scheduler_prefix_state_cache_counts",
 )
 
 _library = None

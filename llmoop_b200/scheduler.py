@@ -151,6 +151,37 @@ class Scheduler:
     def stream_snapshot(self, stream_id: str) -> dict:
         return self._stream_call(self._lib.nerve_b200_scheduler_stream_snapshot, stream_id.encode())
 
+    # prefix-state cache (stream_runtime.rs:541-559, 616-705)
+    def set_prefix_state_cache_capacity(self, capacity_entries: int) -> int:
+        """Returns how many entries were evicted to get down to the new capacity."""
+        evicted = ctypes.c_uint64()
+        _check(self._lib.nerve_b200_scheduler_set_prefix_state_cache_capacity(self._handle, ctypes.c_uint64(capacity_entries), ctypes.byref(evicted)))
+        return evicted.value
+
+    def cache_stream_prefix_state_for_tokens(self, stream_id: str, runtime_graph_id: str, token_ids, runtime_modifier_bytes: bytes = b"") -> dict:
+        tokens = (ctypes.c_uint32 * max(1, len(token_ids)))(*[int(t) for t in token_ids])
+        modifiers = (ctypes.c_uint8 * max(1, len(runtime_modifier_bytes)))(*runtime_modifier_bytes)
+        flags, evicted = ctypes.c_int32(), ctypes.c_uint64()
+        _check(self._lib.nerve_b200_scheduler_cache_stream_prefix_state_for_tokens(
+            self._handle, stream_id.encode(), runtime_graph_id.encode(), tokens, ctypes.c_size_t(len(token_ids)), modifiers,
+            ctypes.c_size_t(len(runtime_modifier_bytes)), ctypes.byref(flags), ctypes.byref(evicted)))
+        return {"replaced_existing": bool(flags.value & 1), "evicted_count": evicted.value}
+
+    def restore_longest_stream_prefix_state(self, target_stream_id: str, runtime_graph_id: str, token_ids, runtime_modifier_bytes: bytes = b"") -> int:
+        """Token count of the retained prefix whose state the target stream now shares; 0 when none matches."""
+        tokens = (ctypes.c_uint32 * max(1, len(token_ids)))(*[int(t) for t in token_ids])
+        modifiers = (ctypes.c_uint8 * max(1, len(runtime_modifier_bytes)))(*runtime_modifier_bytes)
+        restored = ctypes.c_uint64()
+        _check(self._lib.nerve_b200_scheduler_restore_longest_stream_prefix_state(
+            self._handle, target_stream_id.encode(), runtime_graph_id.encode(), tokens, ctypes.c_size_t(len(token_ids)), modifiers,
+            ctypes.c_size_t(len(runtime_modifier_bytes)), ctypes.byref(restored)))
+        return restored.value
+
+    def prefix_state_cache_counts(self) -> dict:
+        counts = (ctypes.c_uint64 * 3)()
+        _check(self._lib.nerve_b200_scheduler_prefix_state_cache_counts(self._handle, counts))
+        return {"capacity_entries": counts[0], "entry_count": counts[1], "eviction_count": counts[2]}
+
     def snapshot(self) -> dict:
         raw = _Counts()
         _check(self._lib.nerve_b200_scheduler_snapshot(self._handle, ctypes.byref(raw)))

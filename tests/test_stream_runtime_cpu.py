@@ -109,3 +109,53 @@ def test_scheduler_through_the_c_abi():
     counts = scheduler.snapshot()
     assert counts["stream_count"] == 0 and counts["live_block_count"] == 0 and counts["free_block_count"] == counts["allocated_block_count"]
     scheduler.close()
+
+
+def test_prefix_state_cache_through_the_c_abi():
+    """The scenario of stream_runtime_tests.rs:665-769 (two sources, the longer retained prefix wins), extended by
+    the capacity rule, through the C ABI."""
+    from llmoop_b200.runtime import NerveError
+    from llmoop_b200.scheduler import Budget, Scheduler, StateDeclaration
+
+    scheduler = Scheduler()
+    kv = StateDeclaration("layer_00", "kv_memory", bytes_per_activation=16, activation_capacity=2)
+    budget = Budget(max_activations=1, max_prefill_tokens_per_activation=2, max_work_units=16)
+
+    def prefill(stream_id, tokens):
+        scheduler.add_stream(stream_id, "package_a", [kv])
+        scheduler.enqueue_input_event(stream_id, "event", tokens, max_public_tokens=0)
+        while scheduler.stream_snapshot(stream_id)["status"] != "idle":
+            scheduler.complete_activation(scheduler.schedule_step(budget)["activations"][0].id)
+
+    assert scheduler.prefix_state_cache_counts() == {"capacity_entries": 0, "entry_count": 0, "eviction_count": 0}
+    prefill("short_source", [1, 2])
+    # capacity 0 retains nothing (stream_prefix_cache.rs:155-160)
+    scheduler.cache_stream_prefix_state_for_tokens("short_source", "graph_a", [1, 2], b"reasoning=true")
+    assert scheduler.prefix_state_cache_counts()["entry_count"] == 0
+    assert scheduler.set_prefix_state_cache_capacity(2) == 0
+
+    prefill("long_source", [1, 2, 3, 4])
+    assert scheduler.cache_stream_prefix_state_for_tokens("short_source", "graph_a", [1, 2], b"reasoning=true") == {"replaced_existing": False, "evicted_count": 0}
+    assert scheduler.cache_stream_prefix_state_for_tokens("long_source", "graph_a", [1, 2, 3, 4], b"reasoning=true")["evicted_count"] == 0
+    assert scheduler.cache_stream_prefix_state_for_tokens("long_source", "graph_a", [1, 2, 3, 4], b"reasoning=true")["replaced_existing"]
+    with pytest.raises(NerveError, match="does not match source state"):
+        scheduler.cache_stream_prefix_state_for_tokens("long_source", "graph_a", [1, 2], b"reasoning=true")
+    live_before = scheduler.snapshot()["live_block_count"]
+
+    scheduler.add_stream("target", "package_a", [kv])
+    assert scheduler.restore_longest_stream_prefix_state("target", "graph_a", [1, 2, 3, 4, 5], b"reasoning=false") == 0
+    assert scheduler.restore_longest_stream_prefix_state("target", "graph_b", [1, 2, 3, 4, 5], b"reasoning=true") == 0
+    assert scheduler.restore_longest_stream_prefix_state("target", "graph_a", [1, 2, 3, 4, 5], b"reasoning=true") == 4
+    restored = scheduler.stream_snapshot("target")
+    assert restored["transient_state_logical_activation_count"] == 4 and restored["transient_state_block_count"] == 2
+    assert scheduler.snapshot()["live_block_count"] == live_before  # shared, not copied
+    with pytest.raises(NerveError, match="cannot replace non-empty transient state"):
+        scheduler.restore_longest_stream_prefix_state("target", "graph_a", [1, 2, 9], b"reasoning=true")
+
+    # the sources go; what the cache retains stays alive until the capacity drops
+    for stream_id in ("short_source", "long_source"):
+        scheduler.remove_stream(stream_id)
+    assert scheduler.snapshot()["live_block_count"] == live_before
+    assert scheduler.set_prefix_state_cache_capacity(0) == 2
+    assert scheduler.prefix_state_cache_counts() == {"capacity_entries": 0, "entry_count": 0, "eviction_count": 2}
+    assert scheduler.snapshot()["live_block_count"] == 2  # the target's two blocks
