@@ -17,7 +17,12 @@ same synthetic checkpoints.
 Kernel lists follow nerve/circuit_optimizer.py: BF16 weights fuse q/k/v into
 parallel_linear_3way, o/down into linear_residual and gate/up/SiLU/multiply
 into parallel_linear_silu_multiply; INT4 weights stay as separate linear,
-residual_add and silu_multiply kernels.
+residual_add and silu_multiply kernels.  FP8 (e4m3, block-scaled) weights fuse
+like BF16 ones where the branches' scale grids imply the same block shape
+(nerve/model_package_tensors.py:618-660, 1278-1323) - else q stays a linear of
+its own and k/v become parallel_linear_2way - and every consumer of an
+activation reads it through one quantize_fp8_e4m3 node per (signal, width)
+(nerve/circuit_optimizer.py:150-250).
 """
 
 from __future__ import annotations
@@ -60,6 +65,8 @@ def _layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_index,
         "operator_norm": {"tensor": f"{prefix}.input_layernorm.weight", "role": "operator_normalization_weight"},
         "ffn_norm": {"tensor": f"{prefix}.post_attention_layernorm.weight", "role": "feed_forward_normalization_weight"},
     }
+    if quant == "fp8":
+        return _fp8_layer_circuit(spec, component_id, prefix, layer_index)
     suffix = ".weight_packed" if quant == "int4" else ".weight"
     for ref, tensor, role in (
         ("ffn_gate", "mlp.gate_proj", "feed_forward_swiglu_gate_projection"),
@@ -192,6 +199,11 @@ def _layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_index,
             ("linear_residual", "ffn_down_projection__ffn_residual", ["ffn_down_projection", "ffn_residual"]),
         ]
 
+    return _layer_component(spec, component_id, layer_index, refs, semantic, fused, kernels)
+
+
+def _layer_component(spec: ModelSpec, component_id: str, layer_index, refs, semantic, fused, kernels):
+    h = spec.hidden
     state_port = {
         "id": "kv_memory", "type": "append_only_attention_memory", "query_heads": spec.q_heads,
         "key_shape_per_token": [spec.kv_heads, spec.head_dim], "value_shape_per_token": [spec.kv_heads, spec.head_dim],
@@ -227,6 +239,151 @@ def _layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_index,
                      "execution_domain": "decode"} for index, (op, node_id, sources) in enumerate(kernels)],
     }
     return component, execution
+
+
+FP8_CONTRACT = "bf16_blockwise_fp8_e4m3_f32_scale.v1"
+
+
+def _fp8_block_shape(rows: int, columns: int, block: int = 128):
+    """The block shape the reference infers from a weight's scale grid (nerve/model_package_tensors.py:1302-1303);
+    the grid itself is ceil(dim / 128) per side (synth.quantize_fp8_block)."""
+    grid = (-(-rows // block), -(-columns // block))
+    return (-(-rows // grid[0]), -(-columns // grid[1]))
+
+
+def _fp8_layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_index):
+    """One full-attention layer with e4m3 block-scaled linears, as the reference compiler lowers it."""
+    h, ffn = spec.hidden, spec.ffn
+    q_width, kv_width = spec.q_heads * spec.head_dim, spec.kv_heads * spec.head_dim
+    att = _attention_attrs(spec)
+    norm_attrs = {"eps": spec.eps, "weight_offset": 0.0}
+    rope = {"position_source": "stream_tick", "theta": float(spec.rope_theta), "rope_type": "default", "scaling": None,
+            "interleaved": False, "rotary_width": spec.head_dim, **att}
+    linears = (
+        ("ffn_gate", "mlp.gate_proj", "feed_forward_swiglu_gate_projection"),
+        ("ffn_down", "mlp.down_proj", "feed_forward_down_projection"),
+        ("ffn_up", "mlp.up_proj", "feed_forward_up_projection"),
+        ("q_projection", "self_attn.q_proj", "attention_query_projection"),
+        ("k_projection", "self_attn.k_proj", "attention_key_projection"),
+        ("v_projection", "self_attn.v_proj", "attention_value_projection"),
+        ("attention_out_projection", "self_attn.o_proj", "attention_output_projection"),
+    )
+    refs = {
+        "operator_norm": {"tensor": f"{prefix}.input_layernorm.weight", "role": "operator_normalization_weight"},
+        "ffn_norm": {"tensor": f"{prefix}.post_attention_layernorm.weight", "role": "feed_forward_normalization_weight"},
+    }
+    for ref, tensor, role in linears:
+        refs[ref] = {"tensor": f"{prefix}.{tensor}.weight", "role": role}
+    for ref, tensor, role in linears:
+        refs[ref + "_scale_inv"] = {"tensor": f"{prefix}.{tensor}.weight_scale_inv", "role": role + "_block_scale_inverse"}
+
+    def pair(ref):
+        return [ref, ref + "_scale_inv"]
+
+    semantic = [
+        {"id": "operator_norm", "op": "rms_norm", "inputs": ["input_frame"], "outputs": ["operator_norm_out"],
+         "params": ["operator_norm"], "attrs": dict(norm_attrs)},
+        {"id": "q_projection", "op": "linear", "inputs": ["operator_norm_out"], "outputs": ["q_projected"], "params": pair("q_projection")},
+        {"id": "k_projection", "op": "linear", "inputs": ["operator_norm_out"], "outputs": ["k_projected"], "params": pair("k_projection")},
+        {"id": "v_projection", "op": "linear", "inputs": ["operator_norm_out"], "outputs": ["v_projected"], "params": pair("v_projection")},
+        {"id": "q_rope", "op": "rotary_position_embedding", "inputs": ["q_projected"], "outputs": ["q_positioned"],
+         "attrs": {**rope, "head_count": spec.q_heads}},
+        {"id": "k_rope", "op": "rotary_position_embedding", "inputs": ["k_projected"], "outputs": ["k_positioned"],
+         "attrs": {**rope, "head_count": spec.kv_heads}},
+        {"id": "kv_memory_append", "op": "append_state_update", "inputs": ["k_positioned", "v_projected", "kv_memory"],
+         "outputs": ["k_memory", "v_memory"], "state_reads": ["kv_memory"], "state_writes": ["kv_memory"],
+         "attrs": {"growth": "per_activation", **att}},
+        {"id": "attention_read", "op": "scaled_dot_product_attention", "inputs": ["q_positioned", "k_memory", "v_memory"],
+         "outputs": ["attention_out"], "params": [],
+         "attrs": {"causal": True, "scale": spec.head_dim ** -0.5, "window_size": None, "attention_sinks": False, **att}},
+        {"id": "attention_out_projection", "op": "linear", "inputs": ["attention_out"], "outputs": ["operator_out"],
+         "params": pair("attention_out_projection")},
+        {"id": "operator_residual", "op": "residual_add", "inputs": ["input_frame", "operator_out"], "outputs": ["operator_residual_out"]},
+        {"id": "ffn_norm", "op": "rms_norm", "inputs": ["operator_residual_out"], "outputs": ["ffn_norm_out"],
+         "params": ["ffn_norm"], "attrs": dict(norm_attrs)},
+        {"id": "ffn_gate_projection", "op": "linear", "inputs": ["ffn_norm_out"], "outputs": ["ffn_gate"], "params": pair("ffn_gate")},
+        {"id": "ffn_up_projection", "op": "linear", "inputs": ["ffn_norm_out"], "outputs": ["ffn_up"], "params": pair("ffn_up")},
+        {"id": "ffn_gate_activation", "op": "silu", "inputs": ["ffn_gate"], "outputs": ["ffn_gate_activated"], "attrs": {"element_count": ffn}},
+        {"id": "ffn_gate_multiply", "op": "multiply", "inputs": ["ffn_gate_activated", "ffn_up"], "outputs": ["ffn_hidden"]},
+        {"id": "ffn_down_projection", "op": "linear", "inputs": ["ffn_hidden"], "outputs": ["ffn_out"], "params": pair("ffn_down")},
+        {"id": "ffn_residual", "op": "residual_add", "inputs": ["operator_residual_out", "ffn_out"], "outputs": ["output_frame"]},
+    ]
+    by_id = {node["id"]: node for node in semantic}
+    eb = {"output_element_bytes": [2]}
+
+    def plain(node_id):
+        node = dict(by_id[node_id])
+        node["attrs"] = {**node.get("attrs", {}), **eb}
+        return node
+
+    # q/k/v: the widest group of consecutive projections whose block shapes agree (three, else two, else one)
+    projections = [("q_projection", q_width), ("k_projection", kv_width), ("v_projection", kv_width)]
+    groups, index = [], 0
+    while index < len(projections):
+        for count in (3, 2, 1):
+            group = projections[index:index + count]
+            if len(group) == count and len({_fp8_block_shape(width, h) for _, width in group}) == 1:
+                break
+        groups.append([name for name, _ in group])
+        index += len(group)
+    projection_nodes = []
+    for group in groups:
+        if len(group) == 1:
+            node = plain(group[0])
+        else:
+            node = {"id": "__".join(group), "op": f"parallel_linear_{len(group)}way", "inputs": ["operator_norm_out"],
+                    "outputs": [by_id[name]["outputs"][0] for name in group], "params": [p for name in group for p in pair(name)],
+                    "attrs": {"compiled_from": list(group), "branch_count": len(group), "branch_parameter_counts": [2] * len(group),
+                              "output_element_bytes": [2] * len(group)}}
+        projection_nodes.append((node, group))
+
+    fused, kernels = [], []
+
+    def emit(node, sources):
+        fused.append(node)
+        kernels.append((node["op"], node["id"], list(sources)))
+
+    def emit_prequantized(consumers, signal, width):
+        """One quantize node for all `consumers` [(node, semantic source ids)] of `signal`, then the consumers."""
+        first = consumers[0][0]["id"]
+        helper, quantized, scale = f"{first}__quantize_input", f"{first}__input_fp8_e4m3", f"{first}__input_scale_f32"
+        sources = [source for _, ids in consumers for source in ids]
+        emit({"id": helper, "op": "quantize_fp8_e4m3", "inputs": [signal], "outputs": [quantized, scale],
+              "attrs": {"physical_representation_contract": FP8_CONTRACT, "consumer_node_ids": [node["id"] for node, _ in consumers],
+                        "semantic_source_node_ids": sources, "element_count": width, "block_columns": 128,
+                        "output_element_bytes": [1, 4]}}, sources)
+        for node, ids in consumers:
+            logical = list(node["inputs"])
+            node["inputs"] = [quantized, scale, *logical[1:]]
+            node["attrs"] = {**node["attrs"], "physical_input_contract": FP8_CONTRACT, "physical_input_provider_id": helper,
+                             "physical_logical_inputs": logical}
+            emit(node, ids)
+
+    emit(plain("operator_norm"), ["operator_norm"])
+    emit_prequantized(projection_nodes, "operator_norm_out", h)
+    emit(plain("q_rope"), ["q_rope"])
+    emit(plain("k_rope"), ["k_rope"])
+    emit({"id": "kv_memory_append__attention_read", "op": "append_scaled_dot_product_attention",
+          "inputs": ["q_positioned", "k_positioned", "v_projected", "kv_memory"], "outputs": ["attention_out"], "params": [],
+          "state_reads": ["kv_memory"], "state_writes": ["kv_memory"],
+          "attrs": {"compiled_from": ["kv_memory_append", "attention_read"], "append": by_id["kv_memory_append"]["attrs"],
+                    "attention": by_id["attention_read"]["attrs"], "current_kv_source": "direct_bf16_input", **eb}},
+         ["kv_memory_append", "attention_read"])
+    out_sources = ["attention_out_projection", "operator_residual"]
+    emit_prequantized([({"id": "__".join(out_sources), "op": "linear_residual", "inputs": ["attention_out", "input_frame"],
+                         "outputs": ["operator_residual_out"], "params": pair("attention_out_projection"),
+                         "attrs": {"compiled_from": out_sources, "intermediate_rounding": "BF16", **eb}}, out_sources)], "attention_out", q_width)
+    emit(plain("ffn_norm"), ["ffn_norm"])
+    gate_sources = ["ffn_gate_projection", "ffn_up_projection", "ffn_gate_activation", "ffn_gate_multiply"]
+    emit_prequantized([({"id": "__".join(gate_sources), "op": "parallel_linear_silu_multiply", "inputs": ["ffn_norm_out"],
+                         "outputs": ["ffn_hidden"], "params": pair("ffn_gate") + pair("ffn_up"),
+                         "attrs": {"compiled_from": gate_sources, "branch_count": 2, "intermediate_rounding": "BF16",
+                                   "element_count": ffn, **eb}}, gate_sources)], "ffn_norm_out", h)
+    down_sources = ["ffn_down_projection", "ffn_residual"]
+    emit_prequantized([({"id": "__".join(down_sources), "op": "linear_residual", "inputs": ["ffn_hidden", "operator_residual_out"],
+                         "outputs": ["output_frame"], "params": pair("ffn_down"),
+                         "attrs": {"compiled_from": down_sources, "intermediate_rounding": "BF16", **eb}}, down_sources)], "ffn_hidden", ffn)
+    return _layer_component(spec, component_id, layer_index, refs, semantic, fused, kernels)
 
 
 def _adapter_circuit(spec: ModelSpec, decoder_id: str):
@@ -311,8 +468,8 @@ def _draft_output_component(spec: ModelSpec, decoder_id: str, projection_tensor:
 
 
 def build_manifest(spec: ModelSpec) -> dict:
-    if spec.experts or spec.quant not in ("bf16", "int4"):
-        raise ValueError("the native writer covers dense BF16 and INT4 decoders; use the reference compiler for FP8/MoE")
+    if spec.experts or spec.quant not in ("bf16", "int4", "fp8"):
+        raise ValueError("the native writer covers dense BF16, INT4 and FP8 decoders; use the reference compiler for MoE")
     projection_tensor = "model.embed_tokens.weight" if spec.tied else "lm_head.weight"
     components, executions, edges = [], [], []
     previous = ("input_transducer", "output_frame")

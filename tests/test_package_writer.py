@@ -34,7 +34,7 @@ def _executions(manifest):
     return out
 
 
-@pytest.mark.parametrize("name", ["cfg1_bf16_mtp", "tiny_int4_mtp", "tiny_int4_mtp_v16"])
+@pytest.mark.parametrize("name", ["cfg1_bf16_mtp", "tiny_int4_mtp", "tiny_int4_mtp_v16", "tiny_fp8_mtp"])
 def test_native_writer_matches_reference_compiler(name, tmp_path):
     from llmoop_b200.package_writer import write_package
     from llmoop_b200.synth import ModelSpec
@@ -96,3 +96,25 @@ def test_native_package_passes_the_mounter_validation(tmp_path):
     ops, tensors = nb.validate_package(tmp_path / "pkg", 2)
     assert ops == 3 * 15 + 4 + 15
     assert tensors == 2 + 1 + 3 * 16 + 4 + 16  # embed+lm_head, norm, layers, mtp head, mtp layer
+
+
+def test_native_fp8_package_fuses_projections_by_block_shape_and_passes_the_mounter_validation(tmp_path):
+    """q/k/v whose scale grids imply one block shape become parallel_linear_3way behind one quantize node
+    (nerve/model_package_tensors.py:618-660); narrower k/v leave q a linear of its own, as in the golden package."""
+    import llmoop_b200 as nb
+    from llmoop_b200.package_writer import write_package
+    from llmoop_b200.synth import ModelSpec
+
+    spec = ModelSpec(name="writer_fp8_check", hidden=256, layers=2, q_heads=8, kv_heads=4, head_dim=32, ffn=512, vocab=64,
+                     quant="fp8", seed=12)
+    write_package(spec, tmp_path / "pkg")
+    manifest = _load(tmp_path / "pkg")
+    ops = [kernel["op"] for kernel in manifest["component_executions"][0]["kernels"]]
+    assert ops == ["rms_norm", "quantize_fp8_e4m3", "parallel_linear_3way", "rotary_position_embedding", "rotary_position_embedding",
+                   "append_scaled_dot_product_attention", "quantize_fp8_e4m3", "linear_residual", "rms_norm", "quantize_fp8_e4m3",
+                   "parallel_linear_silu_multiply", "quantize_fp8_e4m3", "linear_residual"]
+    fused = manifest["circuit_graph"]["components"][0]["circuit"]["nodes"][2]
+    assert fused["attrs"]["branch_parameter_counts"] == [2, 2, 2] and len(fused["params"]) == 6
+    op_count, tensor_count = nb.validate_package(tmp_path / "pkg", 2)
+    assert op_count == 2 * 13 + 4 + 13
+    assert tensor_count == 2 + 1 + 2 * 16 + 4 + 16
