@@ -1,5 +1,6 @@
-"""Native writer for compiled packages of dense Llama-style decoders (+ one MTP
-layer) in the schema the reference compiler emits
+"""Native writer for compiled packages of Llama-style decoders (+ one MTP
+layer; dense BF16 / INT4 / FP8, or FP8 with sparse experts and per-head q/k
+norms) in the schema the reference compiler emits
 (nerve.vulkan_resident_model_package.v3 / nerve.tensor_index.v1 /
 nerve.stream_circuit.v1), without importing the reference.
 
@@ -22,7 +23,11 @@ like BF16 ones where the branches' scale grids imply the same block shape
 (nerve/model_package_tensors.py:618-660, 1278-1323) - else q stays a linear of
 its own and k/v become parallel_linear_2way - and every consumer of an
 activation reads it through one quantize_fp8_e4m3 node per (signal, width)
-(nerve/circuit_optimizer.py:150-250).
+(nerve/circuit_optimizer.py:150-250).  Sparse-expert layers keep the router
+as a BF16 linear, route with moe_topk and run sparse_moe_gate_up /
+sparse_moe_down / moe_reduce on expert tensors packed [expert, row, column]
+(nerve/model_transpiler_quantization.py:22-250); per-head q/k norms fuse with
+the rotary embedding into parallel_head_norm_rope_2way.
 """
 
 from __future__ import annotations
@@ -30,6 +35,7 @@ from __future__ import annotations
 import hashlib
 import json
 import math
+import re
 from pathlib import Path
 
 import numpy as np
@@ -202,7 +208,8 @@ def _layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_index,
     return _layer_component(spec, component_id, layer_index, refs, semantic, fused, kernels)
 
 
-def _layer_component(spec: ModelSpec, component_id: str, layer_index, refs, semantic, fused, kernels):
+def _layer_component(spec: ModelSpec, component_id: str, layer_index, refs, semantic, fused, kernels,
+                     layout: str = "gqa_attention_layer_params_v1_dense_swiglu"):
     h = spec.hidden
     state_port = {
         "id": "kv_memory", "type": "append_only_attention_memory", "query_heads": spec.q_heads,
@@ -212,8 +219,7 @@ def _layer_component(spec: ModelSpec, component_id: str, layer_index, refs, sema
         "source_layout": "batch_kvheads_seq_headdim",
     }
     circuit_id = f"{component_id}_gqa_attention_circuit_v1"
-    params = {"schema": "nerve.circuit_params.v1", "circuit": circuit_id, "layout": "gqa_attention_layer_params_v1_dense_swiglu",
-              "storage": "source_tensor_refs", "refs": refs}
+    params = {"schema": "nerve.circuit_params.v1", "circuit": circuit_id, "layout": layout, "storage": "source_tensor_refs", "refs": refs}
     circuit = {
         "schema": "nerve.stream_circuit.v1", "id": circuit_id,
         "source": {"component_id": component_id, "source_layer_index": layer_index, "source_operator_type": "full_attention"},
@@ -272,8 +278,22 @@ def _fp8_layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_in
         "operator_norm": {"tensor": f"{prefix}.input_layernorm.weight", "role": "operator_normalization_weight"},
         "ffn_norm": {"tensor": f"{prefix}.post_attention_layernorm.weight", "role": "feed_forward_normalization_weight"},
     }
+    moe = bool(spec.experts)
+    if moe:
+        linears = tuple(entry for entry in linears if not entry[0].startswith("ffn_"))
+        refs["moe_input"] = {"tensor": f"{prefix}.mlp.experts.gate_up_proj", "role": "mixture_of_experts_gate_up_weights"}
+        refs["moe_output"] = {"tensor": f"{prefix}.mlp.experts.down_proj", "role": "mixture_of_experts_down_weights"}
+        refs["moe_router"] = {"tensor": f"{prefix}.mlp.gate.weight", "role": "mixture_of_experts_router_projection"}
     for ref, tensor, role in linears:
         refs[ref] = {"tensor": f"{prefix}.{tensor}.weight", "role": role}
+    if spec.qk_norm:
+        refs["q_norm"] = {"tensor": f"{prefix}.self_attn.q_norm.weight", "role": "attention_query_head_normalization"}
+        refs["k_norm"] = {"tensor": f"{prefix}.self_attn.k_norm.weight", "role": "attention_key_head_normalization"}
+    if moe:
+        refs["moe_input_scale_inv"] = {"tensor": f"{prefix}.mlp.experts.gate_up_proj_scale_inv",
+                                       "role": "mixture_of_experts_gate_up_weights_block_scale_inverse"}
+        refs["moe_output_scale_inv"] = {"tensor": f"{prefix}.mlp.experts.down_proj_scale_inv",
+                                        "role": "mixture_of_experts_down_weights_block_scale_inverse"}
     for ref, tensor, role in linears:
         refs[ref + "_scale_inv"] = {"tensor": f"{prefix}.{tensor}.weight_scale_inv", "role": role + "_block_scale_inverse"}
 
@@ -286,9 +306,18 @@ def _fp8_layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_in
         {"id": "q_projection", "op": "linear", "inputs": ["operator_norm_out"], "outputs": ["q_projected"], "params": pair("q_projection")},
         {"id": "k_projection", "op": "linear", "inputs": ["operator_norm_out"], "outputs": ["k_projected"], "params": pair("k_projection")},
         {"id": "v_projection", "op": "linear", "inputs": ["operator_norm_out"], "outputs": ["v_projected"], "params": pair("v_projection")},
-        {"id": "q_rope", "op": "rotary_position_embedding", "inputs": ["q_projected"], "outputs": ["q_positioned"],
+    ]
+    if spec.qk_norm:
+        semantic += [
+            {"id": "q_head_norm", "op": "rms_norm_per_head", "inputs": ["q_projected"], "outputs": ["q_normed"], "params": ["q_norm"],
+             "attrs": {**norm_attrs, **att, "head_count": spec.q_heads}},
+            {"id": "k_head_norm", "op": "rms_norm_per_head", "inputs": ["k_projected"], "outputs": ["k_normed"], "params": ["k_norm"],
+             "attrs": {**norm_attrs, **att, "head_count": spec.kv_heads}},
+        ]
+    semantic += [
+        {"id": "q_rope", "op": "rotary_position_embedding", "inputs": ["q_normed" if spec.qk_norm else "q_projected"], "outputs": ["q_positioned"],
          "attrs": {**rope, "head_count": spec.q_heads}},
-        {"id": "k_rope", "op": "rotary_position_embedding", "inputs": ["k_projected"], "outputs": ["k_positioned"],
+        {"id": "k_rope", "op": "rotary_position_embedding", "inputs": ["k_normed" if spec.qk_norm else "k_projected"], "outputs": ["k_positioned"],
          "attrs": {**rope, "head_count": spec.kv_heads}},
         {"id": "kv_memory_append", "op": "append_state_update", "inputs": ["k_positioned", "v_projected", "kv_memory"],
          "outputs": ["k_memory", "v_memory"], "state_reads": ["kv_memory"], "state_writes": ["kv_memory"],
@@ -301,13 +330,30 @@ def _fp8_layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_in
         {"id": "operator_residual", "op": "residual_add", "inputs": ["input_frame", "operator_out"], "outputs": ["operator_residual_out"]},
         {"id": "ffn_norm", "op": "rms_norm", "inputs": ["operator_residual_out"], "outputs": ["ffn_norm_out"],
          "params": ["ffn_norm"], "attrs": dict(norm_attrs)},
-        {"id": "ffn_gate_projection", "op": "linear", "inputs": ["ffn_norm_out"], "outputs": ["ffn_gate"], "params": pair("ffn_gate")},
-        {"id": "ffn_up_projection", "op": "linear", "inputs": ["ffn_norm_out"], "outputs": ["ffn_up"], "params": pair("ffn_up")},
-        {"id": "ffn_gate_activation", "op": "silu", "inputs": ["ffn_gate"], "outputs": ["ffn_gate_activated"], "attrs": {"element_count": ffn}},
-        {"id": "ffn_gate_multiply", "op": "multiply", "inputs": ["ffn_gate_activated", "ffn_up"], "outputs": ["ffn_hidden"]},
-        {"id": "ffn_down_projection", "op": "linear", "inputs": ["ffn_hidden"], "outputs": ["ffn_out"], "params": pair("ffn_down")},
-        {"id": "ffn_residual", "op": "residual_add", "inputs": ["operator_residual_out", "ffn_out"], "outputs": ["output_frame"]},
     ]
+    if moe:
+        expert_attrs = {"hidden_size": h, "intermediate_size": spec.moe_ffn, "num_experts": spec.experts, "experts_per_token": spec.experts_per_token}
+        semantic += [
+            {"id": "moe_router_projection", "op": "linear", "inputs": ["ffn_norm_out"], "outputs": ["moe_router_logits"], "params": ["moe_router"]},
+            {"id": "moe_topk", "op": "moe_topk", "inputs": ["moe_router_logits"], "outputs": ["moe_routes"], "params": [],
+             "attrs": {"num_experts": spec.experts, "experts_per_token": spec.experts_per_token, "activation": "softmax",
+                       "normalize_selected": True, "logit_softcap": 0.0, "selection_bias": False}},
+            {"id": "sparse_moe_gate_up", "op": "sparse_moe_gate_up", "inputs": ["ffn_norm_out", "moe_routes"],
+             "outputs": ["moe_expert_intermediates"], "params": pair("moe_input"), "attrs": dict(expert_attrs)},
+            {"id": "sparse_moe_down", "op": "sparse_moe_down", "inputs": ["moe_expert_intermediates", "moe_routes"],
+             "outputs": ["moe_expert_outputs"], "params": pair("moe_output"), "attrs": dict(expert_attrs)},
+            {"id": "moe_reduce", "op": "moe_reduce", "inputs": ["moe_expert_outputs"], "outputs": ["ffn_out"],
+             "attrs": {"hidden_size": h, "experts_per_token": spec.experts_per_token, "routed_scaling_factor": 1.0}},
+        ]
+    else:
+        semantic += [
+            {"id": "ffn_gate_projection", "op": "linear", "inputs": ["ffn_norm_out"], "outputs": ["ffn_gate"], "params": pair("ffn_gate")},
+            {"id": "ffn_up_projection", "op": "linear", "inputs": ["ffn_norm_out"], "outputs": ["ffn_up"], "params": pair("ffn_up")},
+            {"id": "ffn_gate_activation", "op": "silu", "inputs": ["ffn_gate"], "outputs": ["ffn_gate_activated"], "attrs": {"element_count": ffn}},
+            {"id": "ffn_gate_multiply", "op": "multiply", "inputs": ["ffn_gate_activated", "ffn_up"], "outputs": ["ffn_hidden"]},
+            {"id": "ffn_down_projection", "op": "linear", "inputs": ["ffn_hidden"], "outputs": ["ffn_out"], "params": pair("ffn_down")},
+        ]
+    semantic.append({"id": "ffn_residual", "op": "residual_add", "inputs": ["operator_residual_out", "ffn_out"], "outputs": ["output_frame"]})
     by_id = {node["id"]: node for node in semantic}
     eb = {"output_element_bytes": [2]}
 
@@ -361,8 +407,17 @@ def _fp8_layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_in
 
     emit(plain("operator_norm"), ["operator_norm"])
     emit_prequantized(projection_nodes, "operator_norm_out", h)
-    emit(plain("q_rope"), ["q_rope"])
-    emit(plain("k_rope"), ["k_rope"])
+    if spec.qk_norm:
+        branch_ids = ["q_head_norm", "q_rope", "k_head_norm", "k_rope"]
+        emit({"id": "__".join(branch_ids), "op": "parallel_head_norm_rope_2way", "inputs": ["q_projected", "k_projected"],
+              "outputs": ["q_positioned", "k_positioned"], "params": ["q_norm", "k_norm"],
+              "attrs": {"compiled_from": branch_ids,
+                        "branches": [{"norm": dict(by_id["q_head_norm"]["attrs"]), "rope": dict(by_id["q_rope"]["attrs"])},
+                                     {"norm": dict(by_id["k_head_norm"]["attrs"]), "rope": dict(by_id["k_rope"]["attrs"])}],
+                        "intermediate_rounding": "BF16", "output_element_bytes": [2, 2]}}, branch_ids)
+    else:
+        emit(plain("q_rope"), ["q_rope"])
+        emit(plain("k_rope"), ["k_rope"])
     emit({"id": "kv_memory_append__attention_read", "op": "append_scaled_dot_product_attention",
           "inputs": ["q_positioned", "k_positioned", "v_projected", "kv_memory"], "outputs": ["attention_out"], "params": [],
           "state_reads": ["kv_memory"], "state_writes": ["kv_memory"],
@@ -374,6 +429,11 @@ def _fp8_layer_circuit(spec: ModelSpec, component_id: str, prefix: str, layer_in
                          "outputs": ["operator_residual_out"], "params": pair("attention_out_projection"),
                          "attrs": {"compiled_from": out_sources, "intermediate_rounding": "BF16", **eb}}, out_sources)], "attention_out", q_width)
     emit(plain("ffn_norm"), ["ffn_norm"])
+    if moe:
+        # the router is a BF16 linear and the expert kernels quantise their own input: no quantize nodes here
+        for node_id in ("moe_router_projection", "moe_topk", "sparse_moe_gate_up", "sparse_moe_down", "moe_reduce", "ffn_residual"):
+            emit(plain(node_id), [node_id])
+        return _layer_component(spec, component_id, layer_index, refs, semantic, fused, kernels, layout="gqa_attention_layer_params_v1_sparse_moe")
     gate_sources = ["ffn_gate_projection", "ffn_up_projection", "ffn_gate_activation", "ffn_gate_multiply"]
     emit_prequantized([({"id": "__".join(gate_sources), "op": "parallel_linear_silu_multiply", "inputs": ["ffn_norm_out"],
                          "outputs": ["ffn_hidden"], "params": pair("ffn_gate") + pair("ffn_up"),
@@ -468,8 +528,8 @@ def _draft_output_component(spec: ModelSpec, decoder_id: str, projection_tensor:
 
 
 def build_manifest(spec: ModelSpec) -> dict:
-    if spec.experts or spec.quant not in ("bf16", "int4", "fp8"):
-        raise ValueError("the native writer covers dense BF16, INT4 and FP8 decoders; use the reference compiler for MoE")
+    if spec.quant not in ("bf16", "int4", "fp8") or ((spec.experts or spec.qk_norm) and spec.quant != "fp8"):
+        raise ValueError("the native writer covers dense BF16 / INT4 / FP8 decoders and FP8 decoders with sparse experts or per-head q/k norms")
     projection_tensor = "model.embed_tokens.weight" if spec.tied else "lm_head.weight"
     components, executions, edges = [], [], []
     previous = ("input_transducer", "output_frame")
@@ -489,10 +549,10 @@ def build_manifest(spec: ModelSpec) -> dict:
                   "source": {"component_id": "output_transducer", "port_id": "logits"},
                   "destination": {"component_id": "sampler", "port_id": "logits"}})
     dimensions = {
-        "hidden_size": spec.hidden, "intermediate_sizes": [spec.ffn] * spec.layers, "num_hidden_layers": spec.layers,
+        "hidden_size": spec.hidden, "intermediate_sizes": [spec.moe_ffn if spec.experts else spec.ffn] * spec.layers, "num_hidden_layers": spec.layers,
         "num_attention_heads": spec.q_heads, "num_key_value_heads": spec.kv_heads, "head_width": spec.head_dim,
         "rotary_width": spec.head_dim, "attention_window_size": None, "conv_l_cache": 0, "vocab_size": spec.vocab,
-        "max_position_embeddings": spec.max_positions, "num_experts": None, "experts_per_token": None,
+        "max_position_embeddings": spec.max_positions, "num_experts": spec.experts or None, "experts_per_token": spec.experts_per_token or None,
         "attention_layer_shapes": [
             {"layer": layer, "query_heads": spec.q_heads, "key_value_heads": spec.kv_heads, "head_width": spec.head_dim,
              "rotary_width": spec.head_dim, "rope_theta": float(spec.rope_theta), "rope_type": "default",
@@ -588,6 +648,42 @@ def runtime_config(spec: ModelSpec) -> dict:
     }
 
 
+_EXPERT_TENSOR = re.compile(r"^(.*\.mlp\.experts)\.(\d+)\.(gate|up|down)_proj\.(weight|weight_scale_inv)$")
+
+
+def _pack_expert_tensors(tensors):
+    """Separately stored experts become the packed [expert, row, column] tensors every sparse MoE component reads
+    (nerve/model_transpiler_quantization.py:22-250): `experts.gate_up_proj` = per expert the gate rows, then the up
+    rows; `experts.down_proj` = the down matrices stacked; their block scales packed the same way."""
+    parts, order = {}, []
+    for name, dtype, shape, data in tensors:
+        match = _EXPERT_TENSOR.match(name)
+        if match is None:
+            yield name, dtype, shape, data
+            continue
+        base, expert, projection, kind = match.group(1), int(match.group(2)), match.group(3), match.group(4)
+        if base not in parts:
+            parts[base] = {}
+            order.append(base)
+        raw = data if isinstance(data, (bytes, bytearray, memoryview)) else np.ascontiguousarray(data).tobytes()
+        parts[base][(expert, projection, kind)] = (dtype, [int(d) for d in shape], bytes(raw))
+    for base in order:
+        group = parts[base]
+        experts = sorted({expert for expert, _, _ in group})
+        if experts != list(range(len(experts))):
+            raise ValueError(f"{base}: expert indices are not contiguous")
+        for kind, suffix in (("weight", ""), ("weight_scale_inv", "_scale_inv")):
+            gate_dtype, gate_shape, _ = group[(0, "gate", kind)]
+            down_dtype, down_shape, _ = group[(0, "down", kind)]
+            for expert in experts:
+                if group[(expert, "gate", kind)][1] != gate_shape or group[(expert, "up", kind)][1] != gate_shape or group[(expert, "down", kind)][1] != down_shape:
+                    raise ValueError(f"{base}: expert {expert} has other projection shapes than expert 0")
+            yield (f"{base}.gate_up_proj{suffix}", gate_dtype, [len(experts), 2 * gate_shape[0], gate_shape[1]],
+                   b"".join(group[(expert, projection, kind)][2] for expert in experts for projection in ("gate", "up")))
+            yield (f"{base}.down_proj{suffix}", down_dtype, [len(experts), down_shape[0], down_shape[1]],
+                   b"".join(group[(expert, "down", kind)][2] for expert in experts))
+
+
 def write_package(spec: ModelSpec, directory, tensors=None, hash_tensors: bool = True) -> Path:
     """Writes a complete package directory.  `tensors` is an iterable of (name, dtype, shape, array-or-bytes);
     default = the seeded numpy checkpoint of llmoop_b200.synth.build_checkpoint(spec)."""
@@ -596,6 +692,8 @@ def write_package(spec: ModelSpec, directory, tensors=None, hash_tensors: bool =
     if tensors is None:
         _, built = build_checkpoint(spec)
         tensors = ((name, dtype, shape, data) for name, (dtype, shape, data) in built.items())
+    if spec.experts:
+        tensors = _pack_expert_tensors(tensors)
     index = {}
     for name, dtype, shape, data in tensors:
         if name.endswith(".weight_shape"):

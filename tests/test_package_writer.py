@@ -34,7 +34,7 @@ def _executions(manifest):
     return out
 
 
-@pytest.mark.parametrize("name", ["cfg1_bf16_mtp", "tiny_int4_mtp", "tiny_int4_mtp_v16", "tiny_fp8_mtp"])
+@pytest.mark.parametrize("name", ["cfg1_bf16_mtp", "tiny_int4_mtp", "tiny_int4_mtp_v16", "tiny_fp8_mtp", "tiny_moe_fp8_mtp"])
 def test_native_writer_matches_reference_compiler(name, tmp_path):
     from llmoop_b200.package_writer import write_package
     from llmoop_b200.synth import ModelSpec
@@ -118,3 +118,24 @@ def test_native_fp8_package_fuses_projections_by_block_shape_and_passes_the_moun
     op_count, tensor_count = nb.validate_package(tmp_path / "pkg", 2)
     assert op_count == 2 * 13 + 4 + 13
     assert tensor_count == 2 + 1 + 2 * 16 + 4 + 16
+
+
+def test_native_moe_package_passes_the_mounter_validation(tmp_path):
+    import llmoop_b200 as nb
+    from llmoop_b200.package_writer import write_package
+    from llmoop_b200.synth import ModelSpec
+
+    spec = ModelSpec(name="writer_moe_check", hidden=256, layers=2, q_heads=8, kv_heads=4, head_dim=32, ffn=256, vocab=64,
+                     quant="fp8", seed=13, experts=4, experts_per_token=2, moe_ffn=128, qk_norm=True)
+    write_package(spec, tmp_path / "pkg")
+    manifest = _load(tmp_path / "pkg")
+    ops = [kernel["op"] for kernel in manifest["component_executions"][0]["kernels"]]
+    assert ops == ["rms_norm", "quantize_fp8_e4m3", "parallel_linear_3way", "parallel_head_norm_rope_2way",
+                   "append_scaled_dot_product_attention", "quantize_fp8_e4m3", "linear_residual", "rms_norm", "linear", "moe_topk",
+                   "sparse_moe_gate_up", "sparse_moe_down", "moe_reduce", "residual_add"]
+    index = json.loads((tmp_path / "pkg" / "tensors.json").read_text())["tensors"]
+    assert index["model.layers.0.mlp.experts.gate_up_proj"]["shape"] == [4, 256, 256]
+    assert index["model.layers.0.mlp.experts.down_proj_scale_inv"]["shape"] == [4, 2, 1]
+    assert not any(".experts.0." in name for name in index)
+    op_count, tensor_count = nb.validate_package(tmp_path / "pkg", 2)
+    assert op_count == 2 * 14 + 4 + 14
