@@ -1079,7 +1079,19 @@ void Engine::enqueue(int64_t id, const InputEvent &event) {
     scheduled.id = accepted.id.empty() ? std::string("event") : accepted.id;
     scheduled.token_ids = accepted.token_ids;
     scheduled.max_public_tokens = accepted.max_public_tokens;
-    scheduler_.enqueue_input_event(scheduler_id(id), scheduled);
+    try {
+        scheduler_.enqueue_input_event(scheduler_id(id), scheduled);
+    } catch (...) {
+        if (reused > 0) {  // the event was not taken: the stream is fresh again
+            release_pages(s);
+            s.next_tick = 0;
+            s.history.clear();
+            prefix_stats_.hit_count--;
+            prefix_stats_.reused_token_count -= reused;
+            prefix_stats_.saved_prefill_token_count -= reused;
+        }
+        throw;
+    }
     s.queue.push_back(std::move(accepted));
 }
 
