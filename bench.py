@@ -392,6 +392,8 @@ def main():
             if int(connected.item()) == 0:  # all ranks or none: the others would wait for this one inside the kernel
                 engine.set_decode_stack(False)
                 peer_exchange = False
+    if os.environ.get("NERVE_B200_DECODE_STACK", "1") == "0":  # the kernel-per-operator path, for comparisons
+        engine.set_decode_stack(False)
     engine.set_prefill_chunk(PROMPT_TOKENS)
     engine.add_stream(0, seed=0, speculative_draft_tokens=DRAFTS)
 

@@ -585,8 +585,6 @@ Engine::Engine(std::shared_ptr<MountedModel> model) : model_(std::move(model)) {
             stack_barrier_ = device_alloc(STACK_BARRIER_WORDS * sizeof(unsigned int));
             stack_timing_ = device_alloc(std::max<size_t>(1, plan.layers.size()) * 32 * sizeof(unsigned long long));
         }
-        const char *value = getenv("NERVE_B200_DECODE_STACK");
-        if (value != nullptr) stack_enabled_ = value[0] == '1';
     }
 
     for (int slot = options.max_streams - 1; slot >= 0; slot--) free_slots_.push_back(slot);

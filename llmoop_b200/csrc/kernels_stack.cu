@@ -1976,12 +1976,8 @@ cudaError_t launch_decode_stack(const StackLayer *layers_device, int layer_count
     args.slice_slots = plan.slice_slots;
     args.slice_bytes = plan.slice_bytes;
     args.scratch_bytes = static_cast<uint32_t>(plan.scratch);
-    // how many stages beyond the ring the producer asks L2 for
-    static const char *ahead = getenv("NERVE_B200_STACK_L2_AHEAD");
-    args.prefetch_stages = ahead != nullptr ? atoi(ahead) : 0;
-    if (args.prefetch_stages < 0) args.prefetch_stages = 0;
-    static const char *debug = getenv("NERVE_B200_STACK_DEBUG");
-    args.debug_flags = debug != nullptr ? atoi(debug) : 0;
+    args.prefetch_stages = 0;  // stages beyond the ring the producer would ask L2 for: measured, no gain
+    args.debug_flags = 0;      // probe switches of the kernel (1: no hand-over checks, 4: weight stream off after the ring has filled)
     const int group = shape.q_heads / shape.kv_heads;
     if (shape.head_width == 128 && group == 4) return launch_instance<128, 4>(args, plan.total, shape.grid, stream);
     if (shape.head_width == 128 && group == 8) return launch_instance<128, 8>(args, plan.total, shape.grid, stream);
