@@ -35,6 +35,22 @@ def test_reference_pinned_cases_all_pass(cases_binary):
     assert [line[3:] for line in lines] == names
 
 
+def test_cases_are_clean_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+    """The scheduler, the arena and the prefix cache are plain host code: every case again in a build instrumented
+    by ASan and UBSan (leaks, out-of-bounds and use-after-free accesses, signed overflow, misaligned or null
+    dereferences abort the run)."""
+    out = tmp_path / "stream_runtime_cases_sanitized"
+    command = ["g++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined",
+               str(ROOT / "tests" / "stream_runtime_cases.cpp"), str(ROOT / "llmoop_b200" / "csrc" / "stream_runtime.cpp"), "-o", str(out)]
+    built = subprocess.run(command, capture_output=True, text=True)
+    if built.returncode != 0 and "sanitize" in built.stderr and ("cannot find" in built.stderr or "unrecognized" in built.stderr):
+        pytest.skip("the sanitizer runtimes are not installed")
+    assert built.returncode == 0, built.stdout + built.stderr
+    result = subprocess.run([str(out)], capture_output=True, text=True)
+    failed = [line for line in result.stdout.strip().splitlines() if not line.startswith("ok ")]
+    assert result.returncode == 0 and not failed and not result.stderr.strip(), "\n".join(failed) + result.stderr[-2000:]
+
+
 def test_unknown_case_name_is_an_error(cases_binary):
     result = subprocess.run([str(cases_binary), "no_such_case"], capture_output=True, text=True)
     assert result.returncode != 0
