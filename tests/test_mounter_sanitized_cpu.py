@@ -77,3 +77,105 @@ def test_damaged_packages_end_in_an_error_message(sanitized_mounter, tmp_path):
     assert code == 4, lines
     assert [line.split()[0] for line in lines] == ["error", "error", "error", "error", "ok"], lines
     assert all(len(line.split(":", 1)[1].strip()) > 10 for line in lines[:4]), lines  # each names what is wrong
+
+
+def test_mutated_package_metadata_never_crashes_the_mounter(sanitized_mounter, tmp_path):
+    """Seeded fuzzing of what the mounter parses: spans deleted or doubled, numbers replaced by zero, negative,
+    2^32, 2^64 - 1 or the wrong type, strings replaced (other dtypes, paths outside the package, 5000 characters),
+    files cut anywhere - in tensors.json, config.json, a lowered circuit and the manifest, with the manifest's integrity
+    table brought up to date so that the mutation reaches the parser.  Every package must end as `ok` (a harmless
+    mutation) or in an error message; the sanitizers must stay silent."""
+    import hashlib
+    import random
+    import re
+
+    rng = random.Random(7)
+    source = GOLDEN / "tiny_int4_mtp"
+
+    def mutate(text):
+        kind = rng.randrange(6)
+        if kind == 0:
+            a = rng.randrange(len(text))
+            return text[:a] + text[min(len(text), a + rng.randrange(1, 200)):]
+        if kind == 1:
+            match = rng.choice(list(re.finditer(r"-?\d+(\.\d+)?", text)))
+            replacement = rng.choice(["-1", "0", "18446744073709551615", "9223372036854775808", "1e400", "4294967296", '""', "null", "[]", "7"])
+            return text[:match.start()] + replacement + text[match.end():]
+        if kind == 2:
+            match = rng.choice(list(re.finditer(r'"[^"]*"', text)))
+            replacement = rng.choice(['""', '"../../etc/passwd"', "123", "null", '"\\u0000"', '"' + "A" * 5000 + '"', '"BF16"', '"I32"', '"F8_E4M3"'])
+            return text[:match.start()] + replacement + text[match.end():]
+        if kind == 3:
+            return text[:rng.randrange(len(text))]
+        if kind == 4:
+            a = rng.randrange(len(text))
+            b = min(len(text), a + rng.randrange(1, 300))
+            return text[:b] + text[a:b] + text[b:]
+        a = rng.randrange(len(text))
+        return text[:a] + rng.choice('{}[],:"0 ') + text[a + 1:]
+
+    directories = []
+    for index in range(160):
+        directory = tmp_path / f"mutation_{index:03d}"
+        shutil.copytree(source, directory)
+        target = rng.choice(["tensors.json", "tensors.json", "config.json", "lowered/layer_00/circuit.json"])
+        path = directory / target
+        path.write_text(mutate(path.read_text()))
+        manifest_path = directory / "vulkan_resident_package.json"
+        manifest = json.loads(manifest_path.read_text())
+        blob = path.read_bytes()
+        if target in manifest["artifact_integrity"]["files"]:
+            manifest["artifact_integrity"]["files"][target] = {"byte_count": len(blob), "sha256": hashlib.sha256(blob).hexdigest()}
+        text = json.dumps(manifest)
+        manifest_path.write_text(mutate(text) if rng.random() < 0.3 else text)
+        directories.append(directory)
+    _, lines = _run(sanitized_mounter, *directories)
+    assert len(lines) == len(directories), "the mounter stopped early"
+    assert all(line.startswith(("ok ", "error ")) for line in lines)
+    assert sum(line.startswith("error ") for line in lines) >= len(lines) // 3  # the mutations do reach the checks
+
+
+def test_mutated_weights_files_never_crash_the_mounter(sanitized_mounter, tmp_path):
+    """The same for the safetensors files: header lengths of 0, 2^63, 2^64 - 1 or one off the file size, damaged header
+    text, data offsets that are negative, reversed or far beyond the file, files cut anywhere or emptied."""
+    import hashlib
+    import random
+    import struct
+
+    rng = random.Random(3)
+    source = GOLDEN / "tiny_int4_mtp"
+    index = json.loads((source / "tensors.json").read_text())["tensors"]
+    directories = []
+    for number in range(80):
+        directory = tmp_path / f"weights_{number:03d}"
+        shutil.copytree(source, directory)
+        relative = index[rng.choice(sorted(index))]["source_file"]
+        path = directory / relative
+        blob = bytearray(path.read_bytes())
+        header_bytes = struct.unpack("<Q", blob[:8])[0]
+        kind = rng.randrange(5)
+        if kind == 0:
+            blob[0:8] = struct.pack("<Q", rng.choice([0, 1, 7, 2 ** 63, 2 ** 64 - 1, len(blob), len(blob) + 1, len(blob) - 1, 2 ** 32]))
+        elif kind == 1:
+            blob[8 + rng.randrange(header_bytes)] = rng.choice(b'{}[]",:0 x')
+        elif kind == 2:
+            blob = blob[:rng.randrange(len(blob))]
+        elif kind == 3:
+            header = json.loads(bytes(blob[8:8 + header_bytes]))
+            name = [key for key in header if key != "__metadata__"][0]
+            header[name]["data_offsets"] = rng.choice([[0, 2 ** 62], [5, 3], [-1, 4], [0, 0], [2 ** 40, 2 ** 40 + 8]])
+            text = json.dumps(header).encode()
+            blob = bytearray(struct.pack("<Q", len(text)) + text + bytes(blob[8 + header_bytes:]))
+        else:
+            blob = bytearray()
+        path.write_bytes(bytes(blob))
+        manifest_path = directory / "vulkan_resident_package.json"
+        manifest = json.loads(manifest_path.read_text())
+        if relative in manifest["artifact_integrity"]["files"]:
+            manifest["artifact_integrity"]["files"][relative] = {"byte_count": len(blob), "sha256": hashlib.sha256(bytes(blob)).hexdigest()}
+            manifest_path.write_text(json.dumps(manifest))
+        directories.append(directory)
+    _, lines = _run(sanitized_mounter, *directories)
+    assert len(lines) == len(directories), "the mounter stopped early"
+    assert all(line.startswith(("ok ", "error ")) for line in lines)
+    assert sum(line.startswith("error ") for line in lines) >= len(lines) // 3
