@@ -222,8 +222,8 @@ int32_t nerve_b200_engine_init_tp(nerve_b200_engine *engine, const char *nccl_li
 int32_t nerve_b200_engine_tp_exchange_handle(nerve_b200_engine *engine, uint8_t *out_64_bytes);
 int32_t nerve_b200_engine_tp_connect(nerve_b200_engine *engine, const uint8_t *handles_64_bytes_each, int32_t count);
 /* Batches of at most 8 lanes of a dense INT4 g128 layer stack (the verify batch, draft and single-tick steps) run
- * as one persistent kernel per stack; 0 selects the kernel-per-operator path for them as well.  Default on
- * (NERVE_B200_DECODE_STACK=0 in the environment turns it off).  No counterpart in the reference: its Vulkan
+ * as one persistent kernel per stack; 0 selects the kernel-per-operator path for them as well.  Default on; the
+ * library reads no environment switch for it.  No counterpart in the reference: its Vulkan
  * runtime always records one dispatch per kernel (placed_stream_processor/temporal_prompt.rs:480-657). */
 int32_t nerve_b200_engine_set_decode_stack(nerve_b200_engine *engine, int32_t enabled);
 /* Profiling aid (no reference counterpart): with profiling on, CTA 0 of the persistent kernel stamps the GPU's
